@@ -1,0 +1,17 @@
+"""apt_b200: the mini-batch data path of APT (sampling, relabelling,
+cache-aware feature gather, seed/feature shuffle, SpMM/SDDMM) as hand-written
+sm_100a CUDA behind the reference's ``torch.ops.npc`` operator interface.
+
+Importing the package loads libapt_b200.so (raising if it is not built) and
+registers the ``npc`` operators.
+"""
+from . import _lib  # noqa: F401  (raises when the CUDA library is missing)
+from . import npc_ops  # noqa: F401  (registers torch.ops.npc.*)
+from . import ops
+from .ops import (  # noqa: F401
+    STATE, alltoall, cache_feats_shared, check_status, cpu_load_subtensor, feat_shuffle, init,
+    load_subtensor, local_sample_one_layer, mix_cache_graphs, nccl_get_unique_id, np_sample_and_shuffle,
+    register_min_vids, relabel_csc, rows_gather, rows_scatter, sddmm_u_add_v, sddmm_u_mul_v, set_sampling,
+    shuffle_seeds, sp_sample_shuffle_src, spmm_copy_e_sum, spmm_copy_u_sum, spmm_u_mul_e_sum, unique_sorted,
+)
+from .sampler import Block, DPNeighborSampler, MixedNeighborSampler, create_block  # noqa: F401

@@ -1,0 +1,195 @@
+// Shared device/host helpers of libapt_b200: error plumbing, launch counting,
+// optional per-kernel event timing, Philox4x32-10, 16-byte row movers and a
+// block-wide exclusive scan.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/apt_b200.h"
+
+namespace apt {
+
+// ---------------------------------------------------------------- host side
+void set_error(const char* fmt, ...);
+void count_launch();
+// RAII bracket that records events around one tagged kernel when profiling is on.
+struct ProfScope {
+  ProfScope(const char* tag, cudaStream_t s);
+  ~ProfScope();
+  const char* tag;
+  cudaStream_t stream;
+  int slot;
+};
+
+#define APT_CHECK_ARG(cond, ...)        \
+  do {                                  \
+    if (!(cond)) {                      \
+      apt::set_error(__VA_ARGS__);      \
+      return APT_ERR_BAD_ARG;           \
+    }                                   \
+  } while (0)
+
+#define APT_CUDA(call)                                                        \
+  do {                                                                        \
+    cudaError_t e__ = (call);                                                 \
+    if (e__ != cudaSuccess) {                                                 \
+      apt::set_error("%s:%d %s -> %s", __FILE__, __LINE__, #call,             \
+                     cudaGetErrorString(e__));                                \
+      return APT_ERR_CUDA;                                                    \
+    }                                                                         \
+  } while (0)
+
+// Launch + count + launch-error check (cudaPeekAtLastError keeps sticky
+// errors visible to the caller's own checks).
+#define APT_LAUNCH(kernel, grid, block, smem, stream, ...)                    \
+  do {                                                                        \
+    kernel<<<(grid), (block), (smem), (stream)>>>(__VA_ARGS__);               \
+    apt::count_launch();                                                      \
+    cudaError_t e__ = cudaPeekAtLastError();                                  \
+    if (e__ != cudaSuccess) {                                                 \
+      apt::set_error("%s:%d launch of %s -> %s", __FILE__, __LINE__, #kernel, \
+                     cudaGetErrorString(e__));                                \
+      return APT_ERR_CUDA;                                                    \
+    }                                                                         \
+  } while (0)
+
+constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Grid for a grid-stride kernel: enough blocks for `work_blocks`, rounded up
+// to whole waves of `per_sm` resident blocks on each of the 148 SMs, capped
+// at `max_waves` waves.
+inline int wave_grid(int64_t work_blocks, int per_sm, int max_waves = 8) {
+  if (work_blocks < 1) work_blocks = 1;
+  const int64_t wave = (int64_t)kNumSMs * per_sm;
+  int64_t waves = ceil_div(work_blocks, wave);
+  if (waves > max_waves) waves = max_waves;
+  int64_t g = work_blocks < wave ? work_blocks : waves * wave;
+  return (int)g;
+}
+
+// -------------------------------------------------------------- device side
+#ifdef __CUDACC__
+
+// Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3",
+// SC'11). Counter-based: the same (key, counter) gives the same four words on
+// the GPU and in the CPU oracle.
+struct Philox4 {
+  uint32_t w[4];
+};
+
+__host__ __device__ inline Philox4 philox4x32_10(uint32_t c0, uint32_t c1,
+                                                 uint32_t c2, uint32_t c3,
+                                                 uint32_t k0, uint32_t k1) {
+  const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u;
+  const uint32_t W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint64_t p0 = (uint64_t)M0 * c0;
+    const uint64_t p1 = (uint64_t)M1 * c2;
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ k0;
+    const uint32_t n1 = (uint32_t)p1;
+    const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ k1;
+    const uint32_t n3 = (uint32_t)p0;
+    c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+    k0 += W0; k1 += W1;
+  }
+  Philox4 out;
+  out.w[0] = c0; out.w[1] = c1; out.w[2] = c2; out.w[3] = c3;
+  return out;
+}
+
+__device__ __forceinline__ uint4 ld_stream_16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream_16(void* p, uint4 v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+// Plain (coherent) 16-byte store: used for stores into a peer GPU's memory.
+__device__ __forceinline__ void st_plain_16(void* p, uint4 v) {
+  asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+// Coherent 16-byte load (no .nc): for memory another GPU has just written.
+__device__ __forceinline__ uint4 ld_plain_16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Exclusive scan of one int per thread over a block of up to 1024 threads.
+// Returns the thread's exclusive prefix; *total gets the block sum (all threads).
+// `warp_sums` is a shared array of 33 ints. Ends with a __syncthreads().
+__device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums,
+                                                    int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    int t = __shfl_up_sync(0xffffffffu, inc, d);
+    if (lane >= d) inc += t;
+  }
+  if (lane == 31) warp_sums[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    int s = lane < nw ? warp_sums[lane] : 0;
+    int sinc = s;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      int t = __shfl_up_sync(0xffffffffu, sinc, d);
+      if (lane >= d) sinc += t;
+    }
+    warp_sums[lane] = sinc - s;  // exclusive warp offset
+    if (lane == 31) warp_sums[32] = sinc;
+  }
+  __syncthreads();
+  const int res = warp_sums[warp] + inc - v;
+  *total = warp_sums[32];
+  __syncthreads();
+  return res;
+}
+
+// One block: in-place exclusive scan of sums[0..nblocks); the total goes to
+// sums[nblocks] and, if given, to *out_total.
+static __global__ void __launch_bounds__(1024)
+k_scan_blocks(int32_t* sums, int nblocks, int64_t* out_total) {
+  __shared__ int warp_sums[33];
+  int carry = 0;
+  for (int base = 0; base < nblocks; base += blockDim.x) {
+    const int idx = base + threadIdx.x;
+    const int v = idx < nblocks ? sums[idx] : 0;
+    int total;
+    const int ex = block_exclusive_scan(v, warp_sums, &total);
+    if (idx < nblocks) sums[idx] = carry + ex;
+    carry += total;
+  }
+  if (threadIdx.x == 0) {
+    sums[nblocks] = carry;
+    if (out_total) *out_total = carry;
+  }
+}
+
+#endif  // __CUDACC__
+
+}  // namespace apt

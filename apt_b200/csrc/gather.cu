@@ -1,0 +1,276 @@
+// Cache-aware feature-row gather.
+//
+//   k_classify   one thread per requested row: id -> feat_pos_map entry, kept
+//                in a dense scratch array; rows that live in host memory are
+//                also appended (warp-aggregated) to a miss list.
+//   k_copy_hits  HBM -> HBM. One warp moves kRowsPerWarp rows at a time, each
+//                lane one 16-byte vector per row, all loads issued before the
+//                first store, so every warp keeps 4 x 512 B in flight.
+//   k_copy_miss  pinned host memory -> HBM over the host link, same mover over
+//                the miss list, on a side stream so that it overlaps the hits.
+//
+// Rows are opaque bytes. The vector width V is the widest of 16/8/4/2/1 bytes
+// that divides every row size, column offset and base address involved.
+#include "common.cuh"
+
+namespace apt {
+
+constexpr int kRowsPerWarp = 4;
+constexpr int kGatherBlock = 256;
+
+struct GatherWs {
+  int64_t* src_pos;    // [n]  feat_pos_map[index[r]], -1 = no such row
+  int32_t* miss_rows;  // [n]  output rows whose source is host memory
+  int32_t* miss_count; // [1]
+};
+
+static size_t gather_layout(int64_t n, char* base, GatherWs* ws) {
+  const size_t rows = (size_t)(n > 0 ? n : 1);
+  const size_t b0 = align_up(rows * 8, 256);
+  const size_t b1 = align_up(rows * 4, 256);
+  if (ws) {
+    ws->src_pos = (int64_t*)base;
+    ws->miss_rows = (int32_t*)(base + b0);
+    ws->miss_count = (int32_t*)(base + b0 + b1);
+  }
+  return b0 + b1 + 256;
+}
+
+__global__ void __launch_bounds__(256)
+k_classify(const int64_t* __restrict__ index, int64_t n,
+           const int64_t* __restrict__ pos_map, int64_t num_nodes,
+           int64_t num_dev_rows, int64_t num_uva_rows, GatherWs ws,
+           int32_t* status) {
+  const int lane = threadIdx.x & 31;
+  int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int flags = 0;
+  // Whole warps iterate together so that the ballot below is convergent.
+  for (int64_t r0 = r - lane; r0 < n; r0 += stride, r += stride) {
+    int64_t p = -1;
+    if (r < n) {
+      const int64_t id = index[r];
+      if (id < 0 || id >= num_nodes) {
+        flags |= APT_FLAG_ID_OUT_OF_RANGE;
+      } else {
+        p = pos_map[id];
+        if (p == -1) {
+          flags |= APT_FLAG_FEAT_NOT_EXIST;
+        } else if (p >= num_dev_rows || (-p - 2) >= num_uva_rows) {
+          flags |= APT_FLAG_ID_OUT_OF_RANGE;
+          p = -1;
+        }
+      }
+      ws.src_pos[r] = p;
+    }
+    const bool miss = p < -1;
+    const unsigned m = __ballot_sync(0xffffffffu, miss);
+    if (m) {
+      int base = 0;
+      const int leader = __ffs(m) - 1;
+      if (lane == leader) base = atomicAdd(ws.miss_count, __popc(m));
+      base = __shfl_sync(0xffffffffu, base, leader);
+      if (miss) ws.miss_rows[base + __popc(m & ((1u << lane) - 1u))] = (int32_t)r;
+    }
+  }
+  if (flags) atomicOr(status, flags);
+}
+
+template <typename V>
+__device__ __forceinline__ V ld_vec(const V* p) { return __ldg(p); }
+template <>
+__device__ __forceinline__ uint4 ld_vec<uint4>(const uint4* p) { return ld_stream_16(p); }
+template <typename V>
+__device__ __forceinline__ void st_vec(V* p, V v) { *p = v; }
+template <>
+__device__ __forceinline__ void st_vec<uint4>(uint4* p, uint4 v) { st_stream_16(p, v); }
+template <typename V>
+__device__ __forceinline__ V zero_vec() { return V(0); }
+template <>
+__device__ __forceinline__ uint4 zero_vec<uint4>() { return make_uint4(0, 0, 0, 0); }
+template <>
+__device__ __forceinline__ uint2 zero_vec<uint2>() { return make_uint2(0, 0); }
+
+// Rows r0..r0+3 of the output come from dev row src_pos[r] (>= 0), are zero
+// (src_pos == -1), or belong to the miss kernel (src_pos < -1).
+template <typename V>
+__global__ void __launch_bounds__(kGatherBlock)
+k_copy_hits(int64_t n, const int64_t* __restrict__ src_pos,
+            const char* __restrict__ dev_feats, int64_t row_bytes,
+            char* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int chunks = (int)(row_bytes / (int64_t)sizeof(V));
+  for (int64_t r0 = warp * kRowsPerWarp; r0 < n; r0 += warps * kRowsPerWarp) {
+    int64_t p[kRowsPerWarp];
+#pragma unroll
+    for (int k = 0; k < kRowsPerWarp; ++k)
+      p[k] = r0 + k < n ? src_pos[r0 + k] : (int64_t)-2;
+    for (int c = lane; c < chunks; c += 32) {
+      V v[kRowsPerWarp];
+#pragma unroll
+      for (int k = 0; k < kRowsPerWarp; ++k) {
+        v[k] = zero_vec<V>();
+        if (p[k] >= 0) v[k] = ld_vec<V>((const V*)(dev_feats + p[k] * row_bytes) + c);
+      }
+#pragma unroll
+      for (int k = 0; k < kRowsPerWarp; ++k)
+        if (p[k] >= -1) st_vec<V>((V*)(out + (r0 + k) * row_bytes) + c, v[k]);
+    }
+  }
+}
+
+template <typename V>
+__global__ void __launch_bounds__(kGatherBlock)
+k_copy_miss(const int32_t* __restrict__ miss_count,
+            const int32_t* __restrict__ miss_rows,
+            const int64_t* __restrict__ src_pos,
+            const char* __restrict__ uva_feats, int64_t uva_row_bytes,
+            int64_t col_offset_bytes, int64_t row_bytes, char* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t n = *miss_count;
+  const int chunks = (int)(row_bytes / (int64_t)sizeof(V));
+  for (int64_t m0 = warp * kRowsPerWarp; m0 < n; m0 += warps * kRowsPerWarp) {
+    int64_t r[kRowsPerWarp], p[kRowsPerWarp];
+#pragma unroll
+    for (int k = 0; k < kRowsPerWarp; ++k) {
+      r[k] = m0 + k < n ? (int64_t)miss_rows[m0 + k] : (int64_t)-1;
+      p[k] = r[k] >= 0 ? -src_pos[r[k]] - 2 : (int64_t)0;
+    }
+    for (int c = lane; c < chunks; c += 32) {
+      V v[kRowsPerWarp];
+#pragma unroll
+      for (int k = 0; k < kRowsPerWarp; ++k) {
+        v[k] = zero_vec<V>();
+        if (r[k] >= 0)
+          v[k] = ld_vec<V>((const V*)(uva_feats + p[k] * uva_row_bytes + col_offset_bytes) + c);
+      }
+#pragma unroll
+      for (int k = 0; k < kRowsPerWarp; ++k)
+        if (r[k] >= 0) st_vec<V>((V*)(out + r[k] * row_bytes) + c, v[k]);
+    }
+  }
+}
+
+// Two events per device, reused by every call, order the side stream between
+// the classify kernel and the end of the call.
+static cudaEvent_t g_ev[64][2];
+static bool g_ev_ready[64];
+
+static int vec_width(uint64_t bits) {
+  for (int w = 16; w > 1; w >>= 1)
+    if ((bits & (uint64_t)(w - 1)) == 0) return w;
+  return 1;
+}
+
+}  // namespace apt
+
+extern "C" size_t apt_gather_workspace_bytes(int64_t num_rows) {
+  if (num_rows < 0) return 0;
+  return apt::gather_layout(num_rows, nullptr, nullptr);
+}
+
+extern "C" int apt_gather_rows(const int64_t* index, int64_t num_rows,
+                               const int64_t* feat_pos_map, int64_t num_nodes,
+                               const void* dev_feats, int64_t num_dev_rows,
+                               int64_t dev_row_bytes, const void* uva_feats,
+                               int64_t num_uva_rows, int64_t uva_row_bytes,
+                               int64_t uva_col_offset_bytes, void* out,
+                               void* workspace, size_t workspace_bytes,
+                               int32_t* status_word, void* stream,
+                               void* side_stream) {
+  using namespace apt;
+  APT_CHECK_ARG(num_rows >= 0 && num_rows < (int64_t)0x7fffffff, "apt_gather_rows: bad num_rows");
+  APT_CHECK_ARG(dev_row_bytes > 0 && num_dev_rows >= 0 && num_uva_rows >= 0 && num_nodes >= 0,
+                "apt_gather_rows: bad table sizes");
+  APT_CHECK_ARG(num_uva_rows == 0 ||
+                    (uva_col_offset_bytes >= 0 && uva_col_offset_bytes + dev_row_bytes <= uva_row_bytes),
+                "apt_gather_rows: column window [%lld,+%lld) outside a %lld-byte host row",
+                (long long)uva_col_offset_bytes, (long long)dev_row_bytes, (long long)uva_row_bytes);
+  if (num_rows == 0) return APT_OK;
+  APT_CHECK_ARG(index && feat_pos_map && out && workspace && status_word, "apt_gather_rows: null pointer");
+  APT_CHECK_ARG((num_dev_rows == 0 || dev_feats) && (num_uva_rows == 0 || uva_feats),
+                "apt_gather_rows: null feature table");
+  APT_CHECK_ARG(((uintptr_t)workspace & 255) == 0, "apt_gather_rows: workspace must be 256-byte aligned");
+  GatherWs ws;
+  const size_t need = gather_layout(num_rows, (char*)workspace, &ws);
+  if (workspace_bytes < need) {
+    set_error("apt_gather_rows: workspace %zu < %zu bytes", workspace_bytes, need);
+    return APT_ERR_CAPACITY;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  cudaStream_t side = (cudaStream_t)side_stream;
+  const bool overlap = side != nullptr && side != s && num_uva_rows > 0;
+
+  uint64_t bits = (uint64_t)dev_row_bytes | (uintptr_t)out;
+  if (num_dev_rows > 0) bits |= (uintptr_t)dev_feats;
+  const int vw_hit = vec_width(bits);
+  if (num_uva_rows > 0)
+    bits |= (uint64_t)uva_row_bytes | (uint64_t)uva_col_offset_bytes | (uintptr_t)uva_feats;
+  const int vw_miss = vec_width(bits);
+
+  APT_CUDA(cudaMemsetAsync(ws.miss_count, 0, sizeof(int32_t), s));
+  {
+    ProfScope prof("gather_classify", s);
+    const int grid = wave_grid(ceil_div(num_rows, 256), 8);
+    APT_LAUNCH(k_classify, grid, 256, 0, s, index, num_rows, feat_pos_map, num_nodes,
+               num_dev_rows, num_uva_rows, ws, status_word);
+  }
+  int dev = 0;
+  if (overlap) {
+    APT_CUDA(cudaGetDevice(&dev));
+    APT_CHECK_ARG(dev >= 0 && dev < 64, "apt_gather_rows: device ordinal %d", dev);
+    if (!g_ev_ready[dev]) {
+      APT_CUDA(cudaEventCreateWithFlags(&g_ev[dev][0], cudaEventDisableTiming));
+      APT_CUDA(cudaEventCreateWithFlags(&g_ev[dev][1], cudaEventDisableTiming));
+      g_ev_ready[dev] = true;
+    }
+    APT_CUDA(cudaEventRecord(g_ev[dev][0], s));
+    APT_CUDA(cudaStreamWaitEvent(side, g_ev[dev][0], 0));
+  }
+  const char* devp = (const char*)dev_feats;
+  const char* uvap = (const char*)uva_feats;
+  char* outp = (char*)out;
+
+#define APT_MISS(V)                                                             \
+  do {                                                                          \
+    ProfScope prof("gather_miss", ms);                                          \
+    APT_LAUNCH(k_copy_miss<V>, kNumSMs, kGatherBlock, 0, ms, ws.miss_count,     \
+               ws.miss_rows, ws.src_pos, uvap, uva_row_bytes,                   \
+               uva_col_offset_bytes, dev_row_bytes, outp);                      \
+  } while (0)
+#define APT_HITS(V)                                                             \
+  do {                                                                          \
+    ProfScope prof("gather_hit", s);                                            \
+    const int grid = wave_grid(ceil_div(num_rows, (kGatherBlock / 32) * kRowsPerWarp), 8, 4); \
+    APT_LAUNCH(k_copy_hits<V>, grid, kGatherBlock, 0, s, num_rows, ws.src_pos,  \
+               devp, dev_row_bytes, outp);                                      \
+  } while (0)
+#define APT_BY_WIDTH(W, MACRO)                                                  \
+  do {                                                                          \
+    switch (W) {                                                                \
+      case 16: MACRO(uint4); break;                                             \
+      case 8: MACRO(uint2); break;                                              \
+      case 4: MACRO(uint32_t); break;                                           \
+      case 2: MACRO(uint16_t); break;                                           \
+      default: MACRO(uint8_t); break;                                           \
+    }                                                                           \
+  } while (0)
+
+  if (num_uva_rows > 0) {
+    cudaStream_t ms = overlap ? side : s;
+    APT_BY_WIDTH(vw_miss, APT_MISS);
+  }
+  APT_BY_WIDTH(vw_hit, APT_HITS);
+  if (overlap) {
+    APT_CUDA(cudaEventRecord(g_ev[dev][1], side));
+    APT_CUDA(cudaStreamWaitEvent(s, g_ev[dev][1], 0));
+  }
+#undef APT_MISS
+#undef APT_HITS
+#undef APT_BY_WIDTH
+  return APT_OK;
+}

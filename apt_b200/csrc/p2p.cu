@@ -1,0 +1,430 @@
+// Row movers inside one GPU, and the all-to-all between GPUs done with plain
+// stores into the receiving GPU's memory over NVLink.
+//
+// Inbox layout of every rank (one cudaMalloc, exported by CUDA IPC):
+//   [0, 4096)             header: flags[2][32] (uint64: epoch << 32 | rows),
+//                         then the push kernel's block counter
+//   [4096, ...)           data[parity][source rank][region_bytes]
+// A push writes rows for peer r into data[parity][me] of r's inbox; when the
+// last block of the push kernel has finished (block counter) it publishes
+// flags[parity][me] on every peer. The wait kernel polls the local flags with
+// a time bound; the pull kernel reads the rows out of the local inbox.
+#include <string.h>
+
+#include "common.cuh"
+
+namespace apt {
+
+constexpr int kMoveRows = 4;   // rows in flight per warp
+constexpr int kMoveBlock = 256;
+constexpr int kP2pMaxRanks = 32;
+constexpr size_t kHeaderBytes = 4096;
+constexpr size_t kCounterOffset = 2048;
+
+template <typename V>
+__device__ __forceinline__ V mv_load(const V* p) { return *p; }
+template <>
+__device__ __forceinline__ uint4 mv_load<uint4>(const uint4* p) { return ld_plain_16(p); }
+template <typename V>
+__device__ __forceinline__ void mv_store(V* p, V v) { *p = v; }
+template <>
+__device__ __forceinline__ void mv_store<uint4>(uint4* p, uint4 v) { st_plain_16(p, v); }
+
+// mode 0: out[i] = in[index[i]]   (i < n rows of out)
+// mode 1: out[index[i]] = in[i]   (i < n rows of in)
+template <typename V, int MODE>
+__global__ void __launch_bounds__(kMoveBlock)
+k_rows_move(const char* __restrict__ in, const int64_t* __restrict__ index, int64_t n,
+            int64_t row_bytes, char* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int chunks = (int)(row_bytes / (int64_t)sizeof(V));
+  for (int64_t r0 = warp * kMoveRows; r0 < n; r0 += warps * kMoveRows) {
+    int64_t ix[kMoveRows];
+#pragma unroll
+    for (int k = 0; k < kMoveRows; ++k) ix[k] = r0 + k < n ? index[r0 + k] : (int64_t)-1;
+    for (int c = lane; c < chunks; c += 32) {
+      V v[kMoveRows];
+#pragma unroll
+      for (int k = 0; k < kMoveRows; ++k) {
+        const int64_t src = MODE == 0 ? ix[k] : r0 + k;
+        if (ix[k] >= 0) v[k] = mv_load<V>((const V*)(in + src * row_bytes) + c);
+      }
+#pragma unroll
+      for (int k = 0; k < kMoveRows; ++k) {
+        const int64_t dst = MODE == 0 ? r0 + k : ix[k];
+        if (ix[k] >= 0) mv_store<V>((V*)(out + dst * row_bytes) + c, v[k]);
+      }
+    }
+  }
+}
+
+static int vec_width_of(uint64_t bits) {
+  for (int w = 16; w > 1; w >>= 1)
+    if ((bits & (uint64_t)(w - 1)) == 0) return w;
+  return 1;
+}
+
+template <int MODE>
+static int rows_move(const void* in, const int64_t* index, int64_t n, int64_t row_bytes,
+                     void* out, cudaStream_t s, const char* tag) {
+  if (n == 0) return APT_OK;
+  APT_CHECK_ARG(in && index && out && row_bytes > 0 && n > 0, "%s: bad argument", tag);
+  const int w = vec_width_of((uint64_t)row_bytes | (uintptr_t)in | (uintptr_t)out);
+  const int grid = wave_grid(ceil_div(n, (kMoveBlock / 32) * kMoveRows), 8, 4);
+  ProfScope prof(tag, s);
+  const char* ip = (const char*)in;
+  char* op = (char*)out;
+  switch (w) {
+    case 16: APT_LAUNCH((k_rows_move<uint4, MODE>), grid, kMoveBlock, 0, s, ip, index, n, row_bytes, op); break;
+    case 8: APT_LAUNCH((k_rows_move<uint2, MODE>), grid, kMoveBlock, 0, s, ip, index, n, row_bytes, op); break;
+    case 4: APT_LAUNCH((k_rows_move<uint32_t, MODE>), grid, kMoveBlock, 0, s, ip, index, n, row_bytes, op); break;
+    case 2: APT_LAUNCH((k_rows_move<uint16_t, MODE>), grid, kMoveBlock, 0, s, ip, index, n, row_bytes, op); break;
+    default: APT_LAUNCH((k_rows_move<uint8_t, MODE>), grid, kMoveBlock, 0, s, ip, index, n, row_bytes, op); break;
+  }
+  return APT_OK;
+}
+
+// ---------------------------------------------------------------- all-to-all
+struct PeerTable {
+  char* base[kP2pMaxRanks];
+};
+
+__device__ __forceinline__ void st_release_sys(uint64_t* p, uint64_t v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t ld_acquire_sys(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+template <typename V>
+__global__ void __launch_bounds__(kMoveBlock)
+k_p2p_push(const char* __restrict__ src, const int64_t* __restrict__ src_index,
+           int index_is_dest, const int64_t* __restrict__ send_offsets, int world_size,
+           int me, int64_t row_bytes, size_t region_bytes, PeerTable peers, int parity,
+           uint32_t epoch, int32_t* status) {
+  __shared__ int64_t soff[kP2pMaxRanks + 1];
+  __shared__ bool is_last;
+  if (threadIdx.x == 0) soff[0] = 0;
+  if (threadIdx.x < world_size) soff[threadIdx.x + 1] = send_offsets[threadIdx.x];
+  __syncthreads();
+  const int64_t n = soff[world_size];
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int chunks = (int)(row_bytes / (int64_t)sizeof(V));
+  const size_t slot_off = kHeaderBytes + ((size_t)parity * world_size + me) * region_bytes;
+  const int64_t cap_rows = (int64_t)(region_bytes / (size_t)row_bytes);
+  bool overflow = false;
+  for (int64_t j0 = warp * kMoveRows; j0 < n; j0 += warps * kMoveRows) {
+    const char* sp[kMoveRows];
+    char* dp[kMoveRows];
+#pragma unroll
+    for (int k = 0; k < kMoveRows; ++k) {
+      // t walks the source rows when the index names destinations
+      // (stream position j = index[t]) and the stream otherwise.
+      const int64_t t = j0 + k;
+      sp[k] = nullptr;
+      dp[k] = nullptr;
+      if (t < n) {
+        const int64_t j = (src_index && index_is_dest) ? src_index[t] : t;
+        const int64_t srow = (src_index && !index_is_dest) ? src_index[t] : t;
+        if (j < 0 || j >= n) {
+          overflow = true;
+          continue;
+        }
+        int r = 0;
+        while (soff[r + 1] <= j) ++r;
+        const int64_t local = j - soff[r];
+        if (local >= cap_rows) {
+          overflow = true;
+        } else {
+          sp[k] = src + srow * row_bytes;
+          dp[k] = peers.base[r] + slot_off + local * row_bytes;
+        }
+      }
+    }
+    for (int c = lane; c < chunks; c += 32) {
+      V v[kMoveRows];
+#pragma unroll
+      for (int k = 0; k < kMoveRows; ++k)
+        if (sp[k]) v[k] = mv_load<V>((const V*)sp[k] + c);
+#pragma unroll
+      for (int k = 0; k < kMoveRows; ++k)
+        if (sp[k]) mv_store<V>((V*)dp[k] + c, v[k]);
+    }
+  }
+  if (overflow) atomicOr(status, APT_FLAG_TABLE_FULL);
+  // Publish: every thread orders its own stores system-wide, the last block to
+  // arrive releases the flags on all peers.
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int32_t* counter = (int32_t*)(peers.base[me] + kCounterOffset);
+    const int ticket = atomicAdd(counter, 1);
+    is_last = ticket == (int)gridDim.x - 1;
+    if (is_last) *counter = 0;
+  }
+  __syncthreads();
+  if (is_last && threadIdx.x < world_size) {
+    __threadfence_system();
+    const int r = threadIdx.x;
+    int64_t rows = soff[r + 1] - soff[r];
+    if (rows > cap_rows) rows = cap_rows;
+    uint64_t* flag = (uint64_t*)peers.base[r] + (size_t)parity * kP2pMaxRanks + me;
+    st_release_sys(flag, ((uint64_t)epoch << 32) | (uint64_t)(uint32_t)rows);
+  }
+}
+
+__global__ void k_p2p_wait(const char* local_base, int world_size, int parity,
+                           uint32_t epoch, int64_t timeout_ns,
+                           int64_t* __restrict__ out_counts, int32_t* status) {
+  const int r = threadIdx.x;
+  if (r >= world_size) return;
+  const uint64_t* flag = (const uint64_t*)local_base + (size_t)parity * kP2pMaxRanks + r;
+  const uint64_t t0 = global_timer_ns();
+  uint64_t v = ld_acquire_sys(flag);
+  // Bounded both by wall time and by an iteration count, in case the timer stalls.
+  for (uint64_t it = 0; (uint32_t)(v >> 32) != epoch && it < (1ull << 34); ++it) {
+    if ((it & 63) == 63 && (int64_t)(global_timer_ns() - t0) > timeout_ns) break;
+    __nanosleep(64);
+    v = ld_acquire_sys(flag);
+  }
+  if ((uint32_t)(v >> 32) == epoch) {
+    out_counts[r] = (int64_t)(uint32_t)v;
+  } else {
+    out_counts[r] = 0;
+    atomicOr(status, APT_FLAG_PEER_TIMEOUT);
+  }
+}
+
+// mode 0: dst row j = concatenation row j; 1: dst row i = concat row index[i];
+// 2: concat row j -> dst row index[j].
+template <typename V, int MODE>
+__global__ void __launch_bounds__(kMoveBlock)
+k_p2p_pull(const char* __restrict__ local_base, const int64_t* __restrict__ recv_counts,
+           int world_size, int parity, size_t region_bytes,
+           const int64_t* __restrict__ index, int64_t num_dst_rows, int64_t row_bytes,
+           char* __restrict__ dst) {
+  __shared__ int64_t roff[kP2pMaxRanks + 1];
+  if (threadIdx.x == 0) {
+    int64_t run = 0;
+    roff[0] = 0;
+    for (int r = 0; r < world_size; ++r) {
+      run += recv_counts[r];
+      roff[r + 1] = run;
+    }
+  }
+  __syncthreads();
+  const int64_t total = roff[world_size];
+  const int64_t n = MODE == 1 ? num_dst_rows : total;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int chunks = (int)(row_bytes / (int64_t)sizeof(V));
+  const char* data = local_base + kHeaderBytes + (size_t)parity * world_size * region_bytes;
+  for (int64_t i0 = warp * kMoveRows; i0 < n; i0 += warps * kMoveRows) {
+    const char* sp[kMoveRows];
+    char* dp[kMoveRows];
+#pragma unroll
+    for (int k = 0; k < kMoveRows; ++k) {
+      const int64_t i = i0 + k;
+      sp[k] = nullptr;
+      dp[k] = nullptr;
+      if (i < n) {
+        const int64_t j = MODE == 1 ? index[i] : i;          // concatenation row
+        const int64_t d = MODE == 2 ? index[i] : i;          // destination row
+        if (j >= 0 && j < total && d >= 0) {
+          int r = 0;
+          while (roff[r + 1] <= j) ++r;
+          sp[k] = data + (size_t)r * region_bytes + (j - roff[r]) * row_bytes;
+          dp[k] = dst + d * row_bytes;
+        }
+      }
+    }
+    for (int c = lane; c < chunks; c += 32) {
+      V v[kMoveRows];
+#pragma unroll
+      for (int k = 0; k < kMoveRows; ++k)
+        if (sp[k]) v[k] = mv_load<V>((const V*)sp[k] + c);
+#pragma unroll
+      for (int k = 0; k < kMoveRows; ++k)
+        if (sp[k]) mv_store<V>((V*)dp[k] + c, v[k]);
+    }
+  }
+}
+
+}  // namespace apt
+
+struct apt_p2p {
+  int rank, world_size, device;
+  size_t region_bytes, alloc_bytes;
+  char* local_base;
+  char* peer_base[apt::kP2pMaxRanks];
+  bool peer_is_ipc[apt::kP2pMaxRanks];
+  uint32_t epoch;
+};
+
+extern "C" int apt_rows_gather(const void* in, const int64_t* index, int64_t num_out_rows,
+                               int64_t row_bytes, void* out, void* stream) {
+  return apt::rows_move<0>(in, index, num_out_rows, row_bytes, out, (cudaStream_t)stream, "rows_gather");
+}
+extern "C" int apt_rows_scatter(const void* in, const int64_t* index, int64_t num_in_rows,
+                                int64_t row_bytes, void* out, void* stream) {
+  return apt::rows_move<1>(in, index, num_in_rows, row_bytes, out, (cudaStream_t)stream, "rows_scatter");
+}
+
+extern "C" int apt_p2p_create(int rank, int world_size, size_t region_bytes, apt_p2p** out_ctx,
+                              void* out_handle) {
+  using namespace apt;
+  APT_CHECK_ARG(out_ctx && world_size >= 1 && world_size <= kP2pMaxRanks && rank >= 0 &&
+                    rank < world_size && region_bytes > 0,
+                "apt_p2p_create: bad argument (rank %d of %d)", rank, world_size);
+  apt_p2p* c = new apt_p2p();
+  c->rank = rank;
+  c->world_size = world_size;
+  c->region_bytes = align_up(region_bytes, 256);
+  c->alloc_bytes = kHeaderBytes + 2 * (size_t)world_size * c->region_bytes;
+  c->epoch = 0;
+  for (int r = 0; r < kP2pMaxRanks; ++r) {
+    c->peer_base[r] = nullptr;
+    c->peer_is_ipc[r] = false;
+  }
+  cudaError_t e = cudaGetDevice(&c->device);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&c->local_base, c->alloc_bytes);
+  if (e == cudaSuccess) e = cudaMemset(c->local_base, 0, kHeaderBytes);
+  if (e == cudaSuccess && out_handle) {
+    cudaIpcMemHandle_t h;
+    e = cudaIpcGetMemHandle(&h, c->local_base);
+    if (e == cudaSuccess) memcpy(out_handle, &h, sizeof(h));
+  }
+  if (e != cudaSuccess) {
+    set_error("apt_p2p_create: %s", cudaGetErrorString(e));
+    if (c->local_base) cudaFree(c->local_base);
+    delete c;
+    return APT_ERR_CUDA;
+  }
+  c->peer_base[rank] = c->local_base;
+  *out_ctx = c;
+  return APT_OK;
+}
+
+extern "C" int apt_p2p_attach(apt_p2p* ctx, int peer, const void* handle) {
+  using namespace apt;
+  APT_CHECK_ARG(ctx && handle && peer >= 0 && peer < ctx->world_size, "apt_p2p_attach: bad argument");
+  if (peer == ctx->rank) return APT_OK;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* p = nullptr;
+  APT_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  ctx->peer_base[peer] = (char*)p;
+  ctx->peer_is_ipc[peer] = true;
+  return APT_OK;
+}
+
+extern "C" int apt_p2p_attach_ptr(apt_p2p* ctx, int peer, void* base) {
+  using namespace apt;
+  APT_CHECK_ARG(ctx && base && peer >= 0 && peer < ctx->world_size, "apt_p2p_attach_ptr: bad argument");
+  if (peer == ctx->rank) return APT_OK;
+  ctx->peer_base[peer] = (char*)base;
+  ctx->peer_is_ipc[peer] = false;
+  return APT_OK;
+}
+
+extern "C" void* apt_p2p_local_base(apt_p2p* ctx) { return ctx ? ctx->local_base : nullptr; }
+extern "C" size_t apt_p2p_region_bytes(const apt_p2p* ctx) { return ctx ? ctx->region_bytes : 0; }
+
+extern "C" int apt_p2p_destroy(apt_p2p* ctx) {
+  if (!ctx) return APT_OK;
+  for (int r = 0; r < ctx->world_size; ++r)
+    if (ctx->peer_is_ipc[r] && ctx->peer_base[r]) cudaIpcCloseMemHandle(ctx->peer_base[r]);
+  if (ctx->local_base) cudaFree(ctx->local_base);
+  delete ctx;
+  return APT_OK;
+}
+
+extern "C" int apt_p2p_push(apt_p2p* ctx, const void* src, const int64_t* src_index,
+                            int index_is_dest, const int64_t* send_offsets, int64_t max_rows, int64_t row_bytes,
+                            int32_t* status_word, void* stream) {
+  using namespace apt;
+  APT_CHECK_ARG(ctx && send_offsets && status_word && row_bytes > 0 && max_rows >= 0, "apt_p2p_push: bad argument");
+  APT_CHECK_ARG(max_rows == 0 || src, "apt_p2p_push: null source");
+  APT_CHECK_ARG((size_t)row_bytes <= ctx->region_bytes, "apt_p2p_push: a %lld-byte row exceeds the %zu-byte region",
+                (long long)row_bytes, ctx->region_bytes);
+  for (int r = 0; r < ctx->world_size; ++r)
+    APT_CHECK_ARG(ctx->peer_base[r], "apt_p2p_push: peer %d is not attached", r);
+  cudaStream_t s = (cudaStream_t)stream;
+  ctx->epoch += 1;
+  const int parity = (int)(ctx->epoch & 1u);
+  PeerTable pt;
+  for (int r = 0; r < kP2pMaxRanks; ++r) pt.base[r] = ctx->peer_base[r];
+  const int w = vec_width_of((uint64_t)row_bytes | (uintptr_t)src | (uint64_t)ctx->region_bytes);
+  const int grid = wave_grid(ceil_div(max_rows > 0 ? max_rows : 1, (kMoveBlock / 32) * kMoveRows), 8, 2);
+  ProfScope prof("p2p_push", s);
+  const char* sp = (const char*)src;
+#define APT_PUSH(V)                                                                       \
+  APT_LAUNCH(k_p2p_push<V>, grid, kMoveBlock, 0, s, sp, src_index, index_is_dest, send_offsets,          \
+             ctx->world_size, ctx->rank, row_bytes, ctx->region_bytes, pt, parity,        \
+             ctx->epoch, status_word)
+  switch (w) {
+    case 16: APT_PUSH(uint4); break;
+    case 8: APT_PUSH(uint2); break;
+    case 4: APT_PUSH(uint32_t); break;
+    case 2: APT_PUSH(uint16_t); break;
+    default: APT_PUSH(uint8_t); break;
+  }
+#undef APT_PUSH
+  return APT_OK;
+}
+
+extern "C" int apt_p2p_wait(apt_p2p* ctx, int64_t* out_recv_counts, int32_t* status_word,
+                            int64_t timeout_ns, void* stream) {
+  using namespace apt;
+  APT_CHECK_ARG(ctx && out_recv_counts && status_word, "apt_p2p_wait: bad argument");
+  APT_CHECK_ARG(ctx->epoch > 0, "apt_p2p_wait: no push has been issued");
+  if (timeout_ns <= 0) timeout_ns = 2000000000ll;
+  cudaStream_t s = (cudaStream_t)stream;
+  ProfScope prof("p2p_wait", s);
+  APT_LAUNCH(k_p2p_wait, 1, 32, 0, s, ctx->local_base, ctx->world_size, (int)(ctx->epoch & 1u),
+             ctx->epoch, timeout_ns, out_recv_counts, status_word);
+  return APT_OK;
+}
+
+extern "C" int apt_p2p_pull(apt_p2p* ctx, const int64_t* recv_counts, const int64_t* dst_index,
+                            int index_is_source, int64_t num_dst_rows, int64_t max_rows,
+                            int64_t row_bytes, void* dst, void* stream) {
+  using namespace apt;
+  APT_CHECK_ARG(ctx && recv_counts && row_bytes > 0 && max_rows >= 0, "apt_p2p_pull: bad argument");
+  if (max_rows == 0) return APT_OK;
+  APT_CHECK_ARG(dst, "apt_p2p_pull: null destination");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int parity = (int)(ctx->epoch & 1u);
+  const int w = vec_width_of((uint64_t)row_bytes | (uintptr_t)dst | (uint64_t)ctx->region_bytes);
+  const int grid = wave_grid(ceil_div(max_rows, (kMoveBlock / 32) * kMoveRows), 8, 4);
+  const int mode = !dst_index ? 0 : (index_is_source ? 1 : 2);
+  ProfScope prof("p2p_pull", s);
+  char* dp = (char*)dst;
+#define APT_PULL(V, M)                                                                     \
+  APT_LAUNCH((k_p2p_pull<V, M>), grid, kMoveBlock, 0, s, ctx->local_base, recv_counts,     \
+             ctx->world_size, parity, ctx->region_bytes, dst_index, num_dst_rows,          \
+             row_bytes, dp)
+#define APT_PULL_W(V)                                   \
+  do {                                                  \
+    if (mode == 0) { APT_PULL(V, 0); }                  \
+    else if (mode == 1) { APT_PULL(V, 1); }             \
+    else { APT_PULL(V, 2); }                            \
+  } while (0)
+  switch (w) {
+    case 16: APT_PULL_W(uint4); break;
+    case 8: APT_PULL_W(uint2); break;
+    case 4: APT_PULL_W(uint32_t); break;
+    case 2: APT_PULL_W(uint16_t); break;
+    default: APT_PULL_W(uint8_t); break;
+  }
+#undef APT_PULL_W
+#undef APT_PULL
+  return APT_OK;
+}

@@ -1,0 +1,450 @@
+// Segment-batched COO SpMM (sum reduce) and SDDMM over sampled blocks.
+//
+// A sampled block lists its edges grouped by destination (col is
+// non-decreasing). SpMM then needs no atomics: k_edge_ranges turns col into a
+// CSR-style range per output row (and detects the unsorted case), and
+// k_spmm_rows gives each output row to a group of G lanes (G = the power of
+// two covering the row's 16-byte vectors, at most a warp) that walks the
+// row's edges in order, keeps the running sum in fp32 registers and writes the
+// row once. Every output row is written, so the caller's buffer needs no
+// zero-fill. For unsorted col (the backward call, which swaps row and col)
+// k_spmm_rows writes zeros and k_spmm_scatter adds edge by edge with vector
+// reductions. Both decisions are taken on the device from a flag word, so the
+// host never waits.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace apt {
+
+constexpr int kMaxSegments = 64;
+
+struct SegTable {
+  // Copied into shared memory by each block: first edge and row bases per segment.
+  const int64_t* coo_off;
+  const int64_t* in_off;
+  const int64_t* out_off;
+  int nseg;
+};
+
+__device__ __forceinline__ int seg_of(const int64_t* coo, int nseg, int64_t e) {
+  int k = 0;
+  while (k + 1 < nseg && coo[k + 1] <= e) ++k;
+  return k;
+}
+
+struct SpmmWs {
+  int64_t* range;  // [num_out_rows + 1] first edge of each output row
+  int32_t* flags;  // [0] = 1 when col is not grouped by output row
+};
+
+// ---- element <-> fp32 helpers ------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+  static __device__ __forceinline__ float to_f(float x) { return x; }
+  static __device__ __forceinline__ float from_f(float x) { return x; }
+};
+template <> struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 x) { return __bfloat162float(x); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float x) { return __float2bfloat16_rn(x); }
+};
+template <> struct Elem<__half> {
+  static __device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
+  static __device__ __forceinline__ __half from_f(float x) { return __float2half_rn(x); }
+};
+
+// A 16-byte (VE > 1) or single-element (VE == 1) slice of a row.
+template <typename T, int VE>
+struct alignas(sizeof(T) * VE) Pack {
+  T v[VE];
+};
+
+template <typename T, int VE>
+__device__ __forceinline__ Pack<T, VE> load_pack(const T* p) {
+  Pack<T, VE> r;
+  if constexpr (sizeof(T) * VE == 16) {
+    const uint4 u = __ldg((const uint4*)p);
+    *(uint4*)&r = u;
+  } else {
+    r.v[0] = *p;
+  }
+  return r;
+}
+template <typename T, int VE>
+__device__ __forceinline__ void store_pack(T* p, const Pack<T, VE>& r) {
+  if constexpr (sizeof(T) * VE == 16) {
+    *(uint4*)p = *(const uint4*)&r;
+  } else {
+    *p = r.v[0];
+  }
+}
+
+// ---- edge ranges ---------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+k_edge_ranges(const int64_t* __restrict__ col, int64_t E, SegTable st,
+              int64_t num_out_rows, SpmmWs ws) {
+  __shared__ int64_t coo[kMaxSegments + 1], ooff[kMaxSegments + 1];
+  for (int t = threadIdx.x; t <= st.nseg; t += blockDim.x) {
+    coo[t] = st.coo_off[t];
+    ooff[t] = st.out_off[t];
+  }
+  __syncthreads();
+  int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  bool bad = false;
+  for (; e < E; e += stride) {
+    const int64_t d = ooff[seg_of(coo, st.nseg, e)] + col[e];
+    const int64_t prev = e > 0 ? ooff[seg_of(coo, st.nseg, e - 1)] + col[e - 1] : (int64_t)-1;
+    if (d < prev || d < 0 || d >= num_out_rows) {
+      bad = true;
+      continue;
+    }
+    for (int64_t t = prev + 1; t <= d; ++t) ws.range[t] = e;
+    if (e == E - 1)
+      for (int64_t t = d + 1; t <= num_out_rows; ++t) ws.range[t] = E;
+  }
+  if (bad) atomicOr(ws.flags, 1);
+}
+
+enum { kCopyU = 0, kCopyE = 1, kUMulE = 2, kUAddE = 3 };
+
+template <typename T, int VE, int OP>
+__device__ __forceinline__ void edge_value(float* acc, const T* __restrict__ in,
+                                           const T* __restrict__ edata, int64_t src_row,
+                                           int64_t e, int64_t feat_dim, int64_t edata_dim,
+                                           int64_t per, int64_t col0) {
+  float x[VE];
+  if constexpr (OP != kCopyE) {
+    const Pack<T, VE> p = load_pack<T, VE>(in + src_row * feat_dim + col0);
+#pragma unroll
+    for (int t = 0; t < VE; ++t) x[t] = Elem<T>::to_f(p.v[t]);
+  }
+  if constexpr (OP == kCopyE) {
+    const Pack<T, VE> p = load_pack<T, VE>(edata + e * feat_dim + col0);
+#pragma unroll
+    for (int t = 0; t < VE; ++t) x[t] = Elem<T>::to_f(p.v[t]);
+  } else if constexpr (OP == kUMulE || OP == kUAddE) {
+    if (per == 1) {
+      const Pack<T, VE> p = load_pack<T, VE>(edata + e * feat_dim + col0);
+#pragma unroll
+      for (int t = 0; t < VE; ++t) {
+        const float w = Elem<T>::to_f(p.v[t]);
+        x[t] = OP == kUMulE ? x[t] * w : x[t] + w;
+      }
+    } else {
+#pragma unroll
+      for (int t = 0; t < VE; ++t) {
+        const float w = Elem<T>::to_f(edata[e * edata_dim + (col0 + t) / per]);
+        x[t] = OP == kUMulE ? x[t] * w : x[t] + w;
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < VE; ++t) acc[t] += x[t];
+}
+
+template <typename T, int VE, int OP>
+__global__ void __launch_bounds__(256)
+k_spmm_rows(const int64_t* __restrict__ row, int64_t E, const T* __restrict__ in,
+            const T* __restrict__ edata, int64_t edata_dim, int64_t feat_dim,
+            SegTable st, int64_t num_out_rows, SpmmWs ws, T* __restrict__ out,
+            int group /* lanes per output row, power of two <= 32 */) {
+  __shared__ int64_t coo[kMaxSegments + 1], ioff[kMaxSegments + 1];
+  for (int t = threadIdx.x; t <= st.nseg; t += blockDim.x) {
+    coo[t] = st.coo_off[t];
+    ioff[t] = OP == kCopyE ? 0 : st.in_off[t];
+  }
+  __syncthreads();
+  const bool unsorted = *ws.flags != 0;
+  const int sub = threadIdx.x % group;
+  const int64_t rows_per_block = blockDim.x / group;
+  const int64_t nvec = feat_dim / VE;
+  const int64_t per = feat_dim / edata_dim;
+  int64_t d = (int64_t)blockIdx.x * rows_per_block + threadIdx.x / group;
+  const int64_t stride = (int64_t)gridDim.x * rows_per_block;
+  for (; d < num_out_rows; d += stride) {
+    const int64_t e0 = unsorted ? 0 : ws.range[d];
+    const int64_t e1 = unsorted ? 0 : ws.range[d + 1];
+    for (int64_t c = sub; c < nvec; c += group) {
+      float acc[VE];
+#pragma unroll
+      for (int t = 0; t < VE; ++t) acc[t] = 0.f;
+      for (int64_t e = e0; e < e1; ++e) {
+        const int64_t src = OP == kCopyE ? 0 : ioff[st.nseg > 1 ? seg_of(coo, st.nseg, e) : 0] + row[e];
+        edge_value<T, VE, OP>(acc, in, edata, src, e, feat_dim, edata_dim, per, c * VE);
+      }
+      Pack<T, VE> o;
+#pragma unroll
+      for (int t = 0; t < VE; ++t) o.v[t] = Elem<T>::from_f(acc[t]);
+      store_pack<T, VE>(out + d * feat_dim + c * VE, o);
+    }
+  }
+}
+
+// ---- scatter path (col not grouped) ---------------------------------------------
+__device__ __forceinline__ void red_add(float* p, const float* x, int n) {
+  if (n == 4) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(x[0]),
+                 "f"(x[1]), "f"(x[2]), "f"(x[3])
+                 : "memory");
+  } else {
+    for (int t = 0; t < n; ++t) atomicAdd(p + t, x[t]);
+  }
+}
+__device__ __forceinline__ void red_add(__nv_bfloat16* p, const float* x, int n) {
+  if (n % 2 == 0) {
+    for (int t = 0; t < n; t += 2)
+      atomicAdd((__nv_bfloat162*)(p + t), __floats2bfloat162_rn(x[t], x[t + 1]));
+  } else {
+    for (int t = 0; t < n; ++t) atomicAdd(p + t, __float2bfloat16_rn(x[t]));
+  }
+}
+__device__ __forceinline__ void red_add(__half* p, const float* x, int n) {
+  if (n % 2 == 0) {
+    for (int t = 0; t < n; t += 2)
+      atomicAdd((__half2*)(p + t), __floats2half2_rn(x[t], x[t + 1]));
+  } else {
+    for (int t = 0; t < n; ++t) atomicAdd(p + t, __float2half_rn(x[t]));
+  }
+}
+
+template <typename T, int VE, int OP>
+__global__ void __launch_bounds__(256)
+k_spmm_scatter(const int64_t* __restrict__ row, const int64_t* __restrict__ col,
+               int64_t E, const T* __restrict__ in, const T* __restrict__ edata,
+               int64_t edata_dim, int64_t feat_dim, SegTable st,
+               int64_t num_out_rows, SpmmWs ws, T* __restrict__ out) {
+  __shared__ int64_t coo[kMaxSegments + 1], ioff[kMaxSegments + 1], ooff[kMaxSegments + 1];
+  for (int t = threadIdx.x; t <= st.nseg; t += blockDim.x) {
+    coo[t] = st.coo_off[t];
+    ioff[t] = OP == kCopyE ? 0 : st.in_off[t];
+    ooff[t] = st.out_off[t];
+  }
+  __syncthreads();
+  if (*ws.flags == 0) return;
+  const int64_t nvec = feat_dim / VE;
+  const int64_t per = feat_dim / edata_dim;
+  const int64_t total = E * nvec;
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) {
+    const int64_t e = idx / nvec, c = idx - e * nvec;
+    const int k = st.nseg > 1 ? seg_of(coo, st.nseg, e) : 0;
+    const int64_t d = ooff[k] + col[e];
+    if (d < 0 || d >= num_out_rows) continue;
+    float acc[VE];
+#pragma unroll
+    for (int t = 0; t < VE; ++t) acc[t] = 0.f;
+    const int64_t src = OP == kCopyE ? 0 : ioff[k] + row[e];
+    edge_value<T, VE, OP>(acc, in, edata, src, e, feat_dim, edata_dim, per, c * VE);
+    red_add(out + d * feat_dim + c * VE, acc, VE);
+  }
+}
+
+// ---- SDDMM -------------------------------------------------------------------------
+template <typename T, int VE, int OP>
+__global__ void __launch_bounds__(256)
+k_sddmm(const int64_t* __restrict__ row, const int64_t* __restrict__ col, int64_t E,
+        const T* __restrict__ lhs, const T* __restrict__ rhs, int64_t feat_dim,
+        SegTable st, const int64_t* __restrict__ rhs_off, T* __restrict__ out) {
+  __shared__ int64_t coo[kMaxSegments + 1], loff[kMaxSegments + 1], roff[kMaxSegments + 1];
+  for (int t = threadIdx.x; t <= st.nseg; t += blockDim.x) {
+    coo[t] = st.coo_off[t];
+    loff[t] = st.in_off[t];
+    roff[t] = rhs_off[t];
+  }
+  __syncthreads();
+  const int64_t nvec = feat_dim / VE;
+  const int64_t total = E * nvec;
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) {
+    const int64_t e = idx / nvec, c = idx - e * nvec;
+    const int k = st.nseg > 1 ? seg_of(coo, st.nseg, e) : 0;
+    const Pack<T, VE> a = load_pack<T, VE>(lhs + (loff[k] + row[e]) * feat_dim + c * VE);
+    const Pack<T, VE> b = load_pack<T, VE>(rhs + (roff[k] + col[e]) * feat_dim + c * VE);
+    Pack<T, VE> o;
+#pragma unroll
+    for (int t = 0; t < VE; ++t) {
+      const float x = Elem<T>::to_f(a.v[t]), y = Elem<T>::to_f(b.v[t]);
+      o.v[t] = Elem<T>::from_f(OP == 0 ? x + y : x * y);
+    }
+    store_pack<T, VE>(out + e * feat_dim + c * VE, o);
+  }
+}
+
+static int pow2_at_least(int64_t x) {
+  int g = 1;
+  while (g < x && g < 32) g <<= 1;
+  return g;
+}
+
+template <typename T, int VE, int OP>
+static int launch_spmm(const int64_t* row, const int64_t* col, int64_t E, const T* in,
+                       const T* edata, int64_t edata_dim, int64_t feat_dim, SegTable st,
+                       int64_t num_out_rows, SpmmWs ws, T* out, cudaStream_t s) {
+  const int64_t nvec = feat_dim / VE;
+  const int group = pow2_at_least(nvec);
+  {
+    ProfScope prof("spmm_rows", s);
+    const int grid = wave_grid(ceil_div(num_out_rows, 256 / group), 8);
+    APT_LAUNCH((k_spmm_rows<T, VE, OP>), grid, 256, 0, s, row, E, in, edata, edata_dim,
+               feat_dim, st, num_out_rows, ws, out, group);
+  }
+  {
+    ProfScope prof("spmm_scatter", s);
+    const int grid = wave_grid(ceil_div(E * nvec, 256), 8);
+    APT_LAUNCH((k_spmm_scatter<T, VE, OP>), grid, 256, 0, s, row, col, E, in, edata,
+               edata_dim, feat_dim, st, num_out_rows, ws, out);
+  }
+  return APT_OK;
+}
+
+template <typename T, int VE>
+static int dispatch_spmm_op(int op, const int64_t* row, const int64_t* col, int64_t E,
+                            const T* in, const T* edata, int64_t edata_dim,
+                            int64_t feat_dim, SegTable st, int64_t num_out_rows,
+                            SpmmWs ws, T* out, cudaStream_t s) {
+  switch (op) {
+    case kCopyU: return launch_spmm<T, VE, kCopyU>(row, col, E, in, edata, edata_dim, feat_dim, st, num_out_rows, ws, out, s);
+    case kCopyE: return launch_spmm<T, VE, kCopyE>(row, col, E, in, edata, edata_dim, feat_dim, st, num_out_rows, ws, out, s);
+    case kUMulE: return launch_spmm<T, VE, kUMulE>(row, col, E, in, edata, edata_dim, feat_dim, st, num_out_rows, ws, out, s);
+    default: return launch_spmm<T, VE, kUAddE>(row, col, E, in, edata, edata_dim, feat_dim, st, num_out_rows, ws, out, s);
+  }
+}
+
+template <typename T>
+static int dispatch_spmm(int op, bool vec, const int64_t* row, const int64_t* col, int64_t E,
+                         const void* in, const void* edata, int64_t edata_dim,
+                         int64_t feat_dim, SegTable st, int64_t num_out_rows, SpmmWs ws,
+                         void* out, cudaStream_t s) {
+  constexpr int VE = 16 / sizeof(T);
+  if (vec)
+    return dispatch_spmm_op<T, VE>(op, row, col, E, (const T*)in, (const T*)edata, edata_dim,
+                                   feat_dim, st, num_out_rows, ws, (T*)out, s);
+  return dispatch_spmm_op<T, 1>(op, row, col, E, (const T*)in, (const T*)edata, edata_dim,
+                                feat_dim, st, num_out_rows, ws, (T*)out, s);
+}
+
+template <typename T, int VE>
+static int launch_sddmm(int op, const int64_t* row, const int64_t* col, int64_t E,
+                        const T* lhs, const T* rhs, int64_t feat_dim, SegTable st,
+                        const int64_t* rhs_off, T* out, cudaStream_t s) {
+  ProfScope prof("sddmm", s);
+  const int grid = wave_grid(ceil_div(E * (feat_dim / VE), 256), 8);
+  if (op == 0) {
+    APT_LAUNCH((k_sddmm<T, VE, 0>), grid, 256, 0, s, row, col, E, lhs, rhs, feat_dim, st, rhs_off, out);
+  } else {
+    APT_LAUNCH((k_sddmm<T, VE, 1>), grid, 256, 0, s, row, col, E, lhs, rhs, feat_dim, st, rhs_off, out);
+  }
+  return APT_OK;
+}
+
+template <typename T>
+static int dispatch_sddmm(int op, bool vec, const int64_t* row, const int64_t* col, int64_t E,
+                          const void* lhs, const void* rhs, int64_t feat_dim, SegTable st,
+                          const int64_t* rhs_off, void* out, cudaStream_t s) {
+  constexpr int VE = 16 / sizeof(T);
+  if (vec)
+    return launch_sddmm<T, VE>(op, row, col, E, (const T*)lhs, (const T*)rhs, feat_dim, st, rhs_off, (T*)out, s);
+  return launch_sddmm<T, 1>(op, row, col, E, (const T*)lhs, (const T*)rhs, feat_dim, st, rhs_off, (T*)out, s);
+}
+
+static size_t elem_size(int dtype) { return dtype == APT_F32 ? 4 : 2; }
+
+}  // namespace apt
+
+extern "C" size_t apt_spmm_workspace_bytes(int64_t num_out_rows) {
+  if (num_out_rows < 0) return 0;
+  return apt::align_up((size_t)(num_out_rows + 1) * 8, 256) + 256;
+}
+
+extern "C" int apt_spmm_sum(int op, int dtype, const int64_t* coo_row, const int64_t* coo_col,
+                            int64_t num_edges, const void* input, const void* edata,
+                            int64_t edata_dim, int64_t feat_dim, const int64_t* coo_offset,
+                            const int64_t* input_offset, const int64_t* output_offset,
+                            int num_segments, int64_t num_out_rows, void* out,
+                            void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace apt;
+  APT_CHECK_ARG(op >= 0 && op <= 3, "apt_spmm_sum: op %d", op);
+  APT_CHECK_ARG(dtype >= APT_F32 && dtype <= APT_F16, "apt_spmm_sum: dtype %d", dtype);
+  APT_CHECK_ARG(num_edges >= 0 && feat_dim > 0 && num_out_rows >= 0, "apt_spmm_sum: bad sizes");
+  APT_CHECK_ARG(num_segments >= 1 && num_segments <= kMaxSegments,
+                "apt_spmm_sum: %d segments outside [1,%d]", num_segments, kMaxSegments);
+  if (op == kCopyU) edata_dim = feat_dim;
+  APT_CHECK_ARG(edata_dim > 0 && feat_dim % edata_dim == 0 && (op != kCopyE || edata_dim == feat_dim),
+                "apt_spmm_sum: edata_dim %lld does not divide feat_dim %lld",
+                (long long)edata_dim, (long long)feat_dim);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (num_out_rows == 0) return APT_OK;
+  const size_t esz = elem_size(dtype);
+  APT_CHECK_ARG(out, "apt_spmm_sum: null output");
+  if (num_edges == 0) {
+    APT_CUDA(cudaMemsetAsync(out, 0, (size_t)num_out_rows * feat_dim * esz, s));
+    return APT_OK;
+  }
+  APT_CHECK_ARG(coo_row && coo_col && coo_offset && output_offset && workspace &&
+                    (op == kCopyE || (input && input_offset)) && (op == kCopyU || edata),
+                "apt_spmm_sum: null pointer");
+  APT_CHECK_ARG(((uintptr_t)workspace & 255) == 0, "apt_spmm_sum: workspace must be 256-byte aligned");
+  const size_t need = apt_spmm_workspace_bytes(num_out_rows);
+  if (workspace_bytes < need) {
+    set_error("apt_spmm_sum: workspace %zu < %zu bytes", workspace_bytes, need);
+    return APT_ERR_CAPACITY;
+  }
+  SpmmWs ws;
+  ws.range = (int64_t*)workspace;
+  ws.flags = (int32_t*)((char*)workspace + need - 256);
+  SegTable st{coo_offset, input_offset, output_offset, num_segments};
+  // edata is read as whole vectors only when it has one value per column.
+  uint64_t bits = (uint64_t)(feat_dim * esz) | (uintptr_t)out;
+  if (op != kCopyE) bits |= (uintptr_t)input;
+  if (op != kCopyU && edata_dim == feat_dim) bits |= (uintptr_t)edata;
+  const bool vec = (bits & 15) == 0;
+  APT_CUDA(cudaMemsetAsync(ws.flags, 0, 4, s));
+  {
+    ProfScope prof("spmm_ranges", s);
+    const int grid = wave_grid(ceil_div(num_edges, 256), 8);
+    APT_LAUNCH(k_edge_ranges, grid, 256, 0, s, coo_col, num_edges, st, num_out_rows, ws);
+  }
+  switch (dtype) {
+    case APT_F32:
+      return dispatch_spmm<float>(op, vec, coo_row, coo_col, num_edges, input, edata, edata_dim,
+                                  feat_dim, st, num_out_rows, ws, out, s);
+    case APT_BF16:
+      return dispatch_spmm<__nv_bfloat16>(op, vec, coo_row, coo_col, num_edges, input, edata,
+                                          edata_dim, feat_dim, st, num_out_rows, ws, out, s);
+    default:
+      return dispatch_spmm<__half>(op, vec, coo_row, coo_col, num_edges, input, edata, edata_dim,
+                                   feat_dim, st, num_out_rows, ws, out, s);
+  }
+}
+
+extern "C" int apt_sddmm(int op, int dtype, const int64_t* coo_row, const int64_t* coo_col,
+                         int64_t num_edges, const void* lhs, const void* rhs, int64_t feat_dim,
+                         const int64_t* coo_offset, const int64_t* lhs_offset,
+                         const int64_t* rhs_offset, int num_segments, void* out, void* stream) {
+  using namespace apt;
+  APT_CHECK_ARG(op == 0 || op == 1, "apt_sddmm: op %d", op);
+  APT_CHECK_ARG(dtype >= APT_F32 && dtype <= APT_F16, "apt_sddmm: dtype %d", dtype);
+  APT_CHECK_ARG(num_edges >= 0 && feat_dim > 0, "apt_sddmm: bad sizes");
+  APT_CHECK_ARG(num_segments >= 1 && num_segments <= kMaxSegments,
+                "apt_sddmm: %d segments outside [1,%d]", num_segments, kMaxSegments);
+  if (num_edges == 0) return APT_OK;
+  APT_CHECK_ARG(coo_row && coo_col && lhs && rhs && out && coo_offset && lhs_offset && rhs_offset,
+                "apt_sddmm: null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t esz = elem_size(dtype);
+  SegTable st{coo_offset, lhs_offset, nullptr, num_segments};
+  const uint64_t bits = (uint64_t)(feat_dim * esz) | (uintptr_t)lhs | (uintptr_t)rhs | (uintptr_t)out;
+  const bool vec = (bits & 15) == 0;
+  switch (dtype) {
+    case APT_F32:
+      return dispatch_sddmm<float>(op, vec, coo_row, coo_col, num_edges, lhs, rhs, feat_dim, st, rhs_offset, out, s);
+    case APT_BF16:
+      return dispatch_sddmm<__nv_bfloat16>(op, vec, coo_row, coo_col, num_edges, lhs, rhs, feat_dim, st, rhs_offset, out, s);
+    default:
+      return dispatch_sddmm<__half>(op, vec, coo_row, coo_col, num_edges, lhs, rhs, feat_dim, st, rhs_offset, out, s);
+  }
+}

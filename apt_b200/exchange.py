@@ -1,0 +1,246 @@
+"""The exchange step between ranks (seed ids one way, feature rows the other)
+behind ShuffleSeeds (src/sampling.cc:176-191), FeatShuffle
+(src/feat_shuffle.cc:9-30) and AlltoAll (src/ops/collective.cc:223-266).
+
+Three interchangeable backends with identical results:
+
+``LocalExchange``   world_size == 1: nothing crosses a link; rows are permuted
+                    by the local row-mover kernels.
+``P2PExchange``     the product path: each rank stores its rows straight into
+                    the receiving GPU's inbox over NVLink (apt_p2p_* in the
+                    C ABI), one flag per (sender, receiver) pair, no host
+                    round trip for sizes.
+``NcclExchange``    torch.distributed all_to_all_single, the counterpart of the
+                    reference's grouped ncclSend/ncclRecv; kept as the measured
+                    baseline (APT_SHUFFLE_BACKEND=nccl).
+"""
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from ._lib import check, lib
+
+
+def _ptr(t):
+    return None if t is None or t.numel() == 0 else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _counts(offsets_cpu: torch.Tensor):
+    """Inclusive cumulative offsets -> per-rank counts (python ints)."""
+    o = [int(x) for x in offsets_cpu.tolist()]
+    return [o[0]] + [o[i] - o[i - 1] for i in range(1, len(o))]
+
+
+class LocalExchange:
+    name = "local"
+
+    def __init__(self, state):
+        self.state = state
+
+    def exchange_ids(self, sorted_ids, sizes, offsets):
+        off = offsets.cpu()
+        return sorted_ids, off, off.clone()
+
+    def exchange_rows(self, inputs, send_offset, recv_offset, permutation, fwd):
+        from . import ops
+
+        if fwd:
+            return ops.rows_gather(inputs, permutation)
+        return ops.rows_scatter(inputs, permutation, int(recv_offset[-1]))
+
+    def alltoall(self, inp, out, send_offset, recv_offset, expand):
+        n = int(send_offset[-1]) * expand
+        out.view(-1)[:n].copy_(inp.view(-1)[:n])
+
+
+class NcclExchange:
+    """Baseline: the collective library's all-to-all-v."""
+
+    name = "nccl"
+
+    def __init__(self, state, group=None):
+        self.state = state
+        self.group = group
+
+    def _a2a(self, inp, send_counts, recv_counts, width):
+        out = inp.new_empty((sum(recv_counts), width))
+        dist.all_to_all_single(out, inp.reshape(-1, width), output_split_sizes=recv_counts,
+                               input_split_sizes=send_counts, group=self.group)
+        return out
+
+    def exchange_ids(self, sorted_ids, sizes, offsets):
+        recv_sizes = torch.empty_like(sizes)
+        dist.all_to_all_single(recv_sizes, sizes, group=self.group)
+        send_counts = [int(x) for x in sizes.tolist()]
+        recv_counts = [int(x) for x in recv_sizes.tolist()]
+        recv = self._a2a(sorted_ids.view(-1, 1), send_counts, recv_counts, 1).view(-1)
+        return recv, torch.tensor(recv_counts).cumsum(0), offsets.cpu()
+
+    def exchange_rows(self, inputs, send_offset, recv_offset, permutation, fwd):
+        from . import ops
+
+        send_counts, recv_counts = _counts(send_offset), _counts(recv_offset)
+        if fwd:
+            buf = self._a2a(inputs, send_counts, recv_counts, inputs.shape[1])
+            return ops.rows_gather(buf, permutation)
+        tmp = ops.rows_scatter(inputs, permutation, inputs.shape[0])
+        return self._a2a(tmp, send_counts, recv_counts, inputs.shape[1])
+
+    def alltoall(self, inp, out, send_offset, recv_offset, expand):
+        send_counts, recv_counts = _counts(send_offset), _counts(recv_offset)
+        res = self._a2a(inp.view(-1, expand)[: sum(send_counts)], send_counts, recv_counts, expand)
+        out.view(-1)[: res.numel()].copy_(res.view(-1))
+
+
+class P2PExchange:
+    """Rows go from the sender's tensor straight into the receiver's inbox with
+    16-byte stores over NVLink. Inboxes are created once and mapped into every
+    peer through CUDA IPC handles exchanged over torch.distributed."""
+
+    name = "p2p"
+
+    def __init__(self, state, region_bytes, group=None, ctx=None, timeout_ns=0):
+        self.state = state
+        self.group = group
+        self.timeout_ns = int(timeout_ns)
+        self._off_dev = None
+        self._off_host = None
+        if ctx is not None:  # same-process ranks (tests): contexts are wired by the caller
+            self.ctx = ctx
+            return
+        handle = ctypes.create_string_buffer(_lib.IPC_HANDLE_BYTES)
+        ctx_p = ctypes.c_void_p()
+        check(lib.apt_p2p_create(state.rank, state.world_size, int(region_bytes), ctypes.byref(ctx_p), handle))
+        self.ctx = ctx_p
+        handles = exchange_blobs(bytes(handle.raw), group)
+        for r, h in enumerate(handles):
+            if r != state.rank:
+                check(lib.apt_p2p_attach(self.ctx, r, ctypes.c_char_p(h)))
+        dist.barrier(group=group)
+
+    @property
+    def region_bytes(self):
+        return int(lib.apt_p2p_region_bytes(self.ctx))
+
+    def _offsets_to_device(self, offsets_cpu):
+        """CPU offsets -> device, through a pinned staging word block so the
+        copy does not stall the stream. Two alternating slots let back-to-back
+        calls keep their own copy."""
+        ws = self.state.world_size
+        if self._off_dev is None:
+            self._off_host = torch.empty((4, 32), dtype=torch.int64).pin_memory()
+            self._off_dev = torch.empty((4, 32), dtype=torch.int64, device=self.state.device())
+            self._slot = 0
+            self._events = [None] * 4
+        k = self._slot
+        self._slot = (k + 1) % 4
+        if self._events[k] is not None:
+            self._events[k].synchronize()  # the staging slot's last copy has left the host
+        self._off_host[k, :ws].copy_(offsets_cpu.to(torch.int64))
+        self._off_dev[k, :ws].copy_(self._off_host[k, :ws], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._events[k] = ev
+        return self._off_dev[k]
+
+    def _push(self, src, index, index_is_dest, offsets_dev, max_rows, row_bytes):
+        check(lib.apt_p2p_push(self.ctx, _ptr(src), _ptr(index), int(index_is_dest), _ptr(offsets_dev),
+                               int(max_rows), int(row_bytes), self.state.status_ptr(), _stream()))
+
+    def _wait(self, counts_dev):
+        check(lib.apt_p2p_wait(self.ctx, _ptr(counts_dev), self.state.status_ptr(), self.timeout_ns, _stream()))
+
+    def _pull(self, counts_dev, index, index_is_source, num_dst_rows, max_rows, row_bytes, dst):
+        check(lib.apt_p2p_pull(self.ctx, _ptr(counts_dev), _ptr(index), int(index_is_source), int(num_dst_rows),
+                               int(max_rows), int(row_bytes), _ptr(dst), _stream()))
+
+    def _check_capacity(self, max_rows_per_peer, row_bytes):
+        if max_rows_per_peer * row_bytes > self.region_bytes:
+            raise RuntimeError(
+                f"p2p inbox region of {self.region_bytes} bytes cannot hold {max_rows_per_peer} rows of "
+                f"{row_bytes} bytes; raise APT_P2P_REGION_MB")
+
+    def exchange_ids(self, sorted_ids, sizes, offsets):
+        st = self.state
+        ws = st.world_size
+        n = sorted_ids.numel()
+        self._check_capacity(n, 8)
+        words = st.words()
+        counts_dev = torch.empty(ws, dtype=torch.int64, device=sorted_ids.device)
+        self._push(sorted_ids, None, 0, offsets, n, 8)
+        self._wait(counts_dev)
+        # one host read brings the received counts, my bucket offsets and the status word
+        host = torch.cat([counts_dev, offsets]).cpu()
+        st.read_words()
+        recv_counts = host[:ws]
+        recv_offset = recv_counts.cumsum(0)
+        total = int(recv_offset[-1])
+        recv = torch.empty(total, dtype=torch.int64, device=sorted_ids.device)
+        self._pull(counts_dev, None, 0, total, total, 8, recv)
+        return recv, recv_offset, host[ws:].clone()
+
+    def exchange_rows(self, inputs, send_offset, recv_offset, permutation, fwd):
+        st = self.state
+        ws = st.world_size
+        row_bytes = inputs.shape[1] * inputs.element_size()
+        self._check_capacity(max(_counts(send_offset)), row_bytes)
+        off_dev = self._offsets_to_device(send_offset)
+        counts_dev = torch.empty(ws, dtype=torch.int64, device=inputs.device)
+        rows_in = inputs.shape[0]
+        total_out = int(recv_offset[-1])
+        if fwd:
+            self._push(inputs, None, 0, off_dev, rows_in, row_bytes)
+            self._wait(counts_dev)
+            out = torch.empty((permutation.numel(), inputs.shape[1]), dtype=inputs.dtype, device=inputs.device)
+            self._pull(counts_dev, permutation, 1, permutation.numel(), permutation.numel(), row_bytes, out)
+        else:
+            self._push(inputs, permutation, 1, off_dev, rows_in, row_bytes)
+            self._wait(counts_dev)
+            out = torch.empty((total_out, inputs.shape[1]), dtype=inputs.dtype, device=inputs.device)
+            self._pull(counts_dev, None, 0, total_out, total_out, row_bytes, out)
+        return out
+
+    def alltoall(self, inp, out, send_offset, recv_offset, expand):
+        st = self.state
+        row_bytes = expand * inp.element_size()
+        self._check_capacity(max(_counts(send_offset)), row_bytes)
+        off_dev = self._offsets_to_device(send_offset)
+        counts_dev = torch.empty(st.world_size, dtype=torch.int64, device=inp.device)
+        rows_in = int(send_offset[-1])
+        total_out = int(recv_offset[-1])
+        self._push(inp, None, 0, off_dev, rows_in, row_bytes)
+        self._wait(counts_dev)
+        self._pull(counts_dev, None, 0, total_out, total_out, row_bytes, out)
+
+    def close(self):
+        if self.ctx is not None:
+            lib.apt_p2p_destroy(self.ctx)
+            self.ctx = None
+
+
+def exchange_blobs(blob: bytes, group=None):
+    """All-gather of one small bytes object per rank over the process group
+    (any backend; gloo on CPU works). Returns the list in rank order."""
+    out = [None] * dist.get_world_size(group)
+    dist.all_gather_object(out, blob, group=group)
+    return out
+
+
+def make_exchange(state):
+    """Backend for this process: local for one rank; otherwise
+    APT_SHUFFLE_BACKEND (default p2p; nccl = the library baseline)."""
+    if state.world_size == 1:
+        return LocalExchange(state)
+    if not dist.is_initialized():
+        raise RuntimeError("world_size > 1 needs torch.distributed.init_process_group before npc.init")
+    if state.shuffle_backend == "nccl":
+        return NcclExchange(state)
+    if state.shuffle_backend == "p2p":
+        return P2PExchange(state, state.p2p_region_bytes)
+    raise RuntimeError(f"unknown APT_SHUFFLE_BACKEND {state.shuffle_backend!r}")

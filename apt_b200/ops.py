@@ -1,0 +1,549 @@
+"""Host side of the data path: the operators of the reference's ``npc`` library
+(``TORCH_LIBRARY(npc, m)``, src/pybind.cc:18-48) with the same names, argument
+meaning and result layout, implemented on libapt_b200's C ABI.
+
+PyTorch is used for device memory, streams and ``torch.distributed`` only; all
+arithmetic of the path runs in the CUDA library. There is no CPU fallback:
+every operator except ``cpu_load_subtensor`` requires CUDA tensors.
+
+State lives in one process-wide object like the reference's ``NPCState``
+(src/state.h:32-63): one process drives one GPU.
+"""
+import ctypes
+import os
+from typing import List, Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import check, lib
+
+_DTYPE_CODE = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _lib.F16}
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    if t is None or t.numel() == 0:
+        return None
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(t: torch.Tensor, name: str, dtype=torch.int64):
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor (apt_b200 has no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError(f"{name} must have dtype {dtype}, got {t.dtype}")
+    return t.contiguous()
+
+
+def _device_visible(t: torch.Tensor, name: str) -> torch.Tensor:
+    """A tensor kernels can dereference: CUDA memory, or page-locked host memory
+    (registered here if needed, as the reference's pin_tensor does,
+    python/npc/utils/utils.py:70-75)."""
+    if t.is_cuda:
+        return t.contiguous()
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if t.numel() > 0 and not t.is_pinned():
+        err = torch.cuda.cudart().cudaHostRegister(t.data_ptr(), t.numel() * t.element_size(), 0)
+        if int(err) != 0:
+            raise RuntimeError(f"cudaHostRegister({name}) failed with {err}")
+    return t
+
+
+class FeatStorage:
+    """FeatStorage, src/state.h:10-16."""
+
+    def __init__(self):
+        self.dev_feats = None
+        self.uva_feats = None
+        self.feat_pos_map = None
+        self._cpu_feat_pos_map = None
+        self._cpu_map_args = None
+        self.num_total_nodes = 0
+        self.feat_dim = 0
+        self.rank_feat_dim = 0
+        self.feat_dim_offset = 0
+
+    @property
+    def cpu_feat_pos_map(self):
+        if self._cpu_feat_pos_map is None and self._cpu_map_args is not None:
+            n, localnode_idx = self._cpu_map_args
+            m = torch.full((n,), -1, dtype=torch.int64)
+            m[localnode_idx] = -torch.arange(localnode_idx.numel(), dtype=torch.int64) - 2
+            self._cpu_feat_pos_map = m
+        return self._cpu_feat_pos_map
+
+
+class GraphStorage:
+    """GraphStorage, src/state.h:18-23."""
+
+    def __init__(self):
+        self.dev_indptr = None
+        self.dev_indices = None
+        self.uva_indptr = None
+        self.uva_indices = None
+        self.adj_pos_map = None
+        self.num_total_nodes = 0
+        self.num_cached_nodes = 0
+
+
+class NPCState:
+    """NPCState, src/state.h:32-63, plus what the CUDA library needs from the
+    host: cached workspaces, the device status word and the exchange backend."""
+
+    def __init__(self):
+        self.rank = 0
+        self.local_rank = 0
+        self.world_size = 1
+        self.node_size = 1
+        self.initialized = False
+        self.shuffle_min_vids = None
+        self._min_vids_host = None
+        self.shuffle_id_offset = 0
+        self.graph = GraphStorage()
+        self.feat = FeatStorage()
+        self.sample_key = 7777777  # the reference's seed constant, src/cuda/npc_kernel.cu:292
+        self.sample_calls = 0
+        self.sample_replace = True
+        self._ws = {}
+        self._words = None
+        self._host_words = None
+        self._side_stream = None
+        self.exchange = None  # set by apt_b200.exchange.make_exchange at init
+        self.shuffle_backend = os.environ.get("APT_SHUFFLE_BACKEND", "p2p")
+        self.p2p_region_bytes = int(os.environ.get("APT_P2P_REGION_MB", "256")) << 20
+
+    # -- device scratch --------------------------------------------------
+    def device(self):
+        return torch.device("cuda", torch.cuda.current_device())
+
+    def workspace(self, name: str, nbytes: int) -> torch.Tensor:
+        """A cached, 256-byte aligned scratch tensor of at least nbytes."""
+        key = (name, torch.cuda.current_device())
+        buf = self._ws.get(key)
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.empty(max(int(nbytes * 1.25), 1 << 16), dtype=torch.uint8, device=self.device())
+            self._ws[key] = buf
+        return buf
+
+    def words(self) -> torch.Tensor:
+        """int64[8] device words: [0..6] small results (counts), [7] status flags."""
+        if self._words is None or self._words.device != self.device():
+            self._words = torch.zeros(8, dtype=torch.int64, device=self.device())
+            self._host_words = torch.zeros(8, dtype=torch.int64).pin_memory()
+        return self._words
+
+    def status_ptr(self):
+        return ctypes.c_void_p(self.words().data_ptr() + 56)
+
+    def read_words(self) -> torch.Tensor:
+        """Copies the device words to the host (one stream sync) and raises on
+        any status flag except zero-degree, which is only a notice."""
+        w = self.words()
+        self._host_words.copy_(w, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        flags = int(self._host_words[7]) & 0xFFFFFFFF
+        if flags & ~_lib.FLAG_ZERO_DEGREE:
+            w[7] = 0
+            raise RuntimeError(f"apt_b200 device status flags 0x{flags:x}: " + _flag_text(flags))
+        return self._host_words
+
+    def side_stream(self):
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream()
+        return self._side_stream
+
+
+def _flag_text(flags):
+    names = {
+        _lib.FLAG_ID_OUT_OF_RANGE: "id outside the registered tables",
+        _lib.FLAG_FEAT_NOT_EXIST: "feature row neither cached nor in host memory",
+        _lib.FLAG_ZERO_DEGREE: "node without in-neighbours sampled",
+        _lib.FLAG_TABLE_FULL: "workspace or inbox region too small",
+        _lib.FLAG_PEER_TIMEOUT: "a peer's data did not arrive in time",
+    }
+    return ", ".join(v for k, v in names.items() if flags & k)
+
+
+STATE = NPCState()
+
+
+def _exchange():
+    """The exchange backend; a process that never called init() is a world of one."""
+    if STATE.exchange is None:
+        from .exchange import make_exchange
+
+        STATE.exchange = make_exchange(STATE)
+    return STATE.exchange
+
+
+def check_status():
+    """Synchronises and raises if any kernel since the last check flagged an error."""
+    STATE.read_words()
+
+
+# ---------------------------------------------------------------- init / state
+def nccl_get_unique_id() -> torch.Tensor:
+    """NCCLGetUniqueId, src/core.cc:38-44: int64[16] on the CPU. The exchange
+    here rides on torch.distributed's process group, so the id is a
+    placeholder kept for callers that broadcast it (python/npc/__init__.py:33-49)."""
+    return torch.zeros(16, dtype=torch.int64)
+
+
+def init(rank: int, local_rank: int, world_size: int, nccl_id_tensor_list: torch.Tensor, node_size: int) -> None:
+    """Initialize, src/core.cc:54-100."""
+    from .exchange import make_exchange
+
+    s = STATE
+    s.rank, s.local_rank, s.world_size, s.node_size = int(rank), int(local_rank), int(world_size), int(node_size)
+    torch.cuda.set_device(s.local_rank)
+    s.exchange = make_exchange(s)
+    s.initialized = True
+
+
+def register_min_vids(shuffle_min_vids: torch.Tensor, shuffle_id_offset: int = 0) -> None:
+    """RegisterMinVids, src/core.cc:102-108."""
+    mv = shuffle_min_vids.to(device=STATE.device(), dtype=torch.int64).contiguous()
+    if mv.numel() != STATE.world_size + 1:
+        raise RuntimeError(f"min_vids needs world_size+1 = {STATE.world_size + 1} entries, got {mv.numel()}")
+    STATE.shuffle_min_vids = mv
+    STATE._min_vids_host = [int(x) for x in shuffle_min_vids.cpu().tolist()]
+    STATE.shuffle_id_offset = int(shuffle_id_offset)
+
+
+def mix_cache_graphs(num_cached_nodes: int, cached_node_idx: torch.Tensor, cached_indptr: torch.Tensor,
+                     cached_indices: torch.Tensor, global_indptr: torch.Tensor, global_indices: torch.Tensor) -> None:
+    """MixCacheGraphs, src/cache_graphs.cc:12-49. The global CSC may be pinned
+    host memory (read over the host link, as in the reference) or CUDA memory
+    (the whole topology resident in HBM)."""
+    g = STATE.graph
+    if int(num_cached_nodes) != cached_node_idx.numel():
+        raise RuntimeError("num_cached_nodes != cached_node_idx.numel()")
+    g.num_cached_nodes = int(num_cached_nodes)
+    g.num_total_nodes = global_indptr.numel() - 1
+    g.uva_indptr = _device_visible(global_indptr, "global_indptr")
+    g.uva_indices = _device_visible(global_indices, "global_indices")
+    if g.num_cached_nodes > 0:
+        g.dev_indptr = _need_cuda(cached_indptr, "cached_indptr")
+        g.dev_indices = _need_cuda(cached_indices, "cached_indices")
+        m = -torch.arange(g.num_total_nodes, dtype=torch.int64, device=STATE.device()) - 2
+        m[cached_node_idx.to(STATE.device())] = torch.arange(g.num_cached_nodes, dtype=torch.int64, device=STATE.device())
+        g.adj_pos_map = m
+    else:
+        # Every node reads the global CSC: the position map would be the
+        # identity encoding, so it is not materialised.
+        g.dev_indptr = g.dev_indices = g.adj_pos_map = None
+
+
+def cache_feats_shared(num_total_nodes: int, localnode_feats: torch.Tensor, cached_feats: torch.Tensor,
+                       cached_idx: torch.Tensor, localnode_idx: torch.Tensor, feat_dim_offset: int = 0) -> None:
+    """CacheFeatsShared, src/cache_feats.cc:14-61."""
+    f = STATE.feat
+    dev = STATE.device()
+    if localnode_feats.dim() != 2 or cached_feats.dim() != 2:
+        raise RuntimeError("feature tables must be 2-D")
+    if cached_feats.dtype != localnode_feats.dtype or cached_feats.dtype not in _DTYPE_CODE:
+        raise RuntimeError(f"unsupported feature dtypes {localnode_feats.dtype}/{cached_feats.dtype}")
+    f.num_total_nodes = int(num_total_nodes)
+    f.uva_feats = _device_visible(localnode_feats, "localnode_feats")
+    f.dev_feats = _need_cuda(cached_feats, "cached_feats", dtype=None)
+    f.feat_dim = localnode_feats.shape[1]
+    f.rank_feat_dim = cached_feats.shape[1]
+    f.feat_dim_offset = int(feat_dim_offset)
+    m = torch.full((f.num_total_nodes,), -1, dtype=torch.int64, device=dev)
+    li = localnode_idx.to(dev)
+    m[li] = -torch.arange(li.numel(), dtype=torch.int64, device=dev) - 2
+    m[cached_idx.to(dev)] = torch.arange(cached_idx.numel(), dtype=torch.int64, device=dev)
+    f.feat_pos_map = m
+    f._cpu_feat_pos_map = None
+    f._cpu_map_args = (f.num_total_nodes, localnode_idx.cpu())
+
+
+def set_sampling(key: Optional[int] = None, call_id: Optional[int] = None, replace: Optional[bool] = None):
+    """Sampler stream control: draws depend only on (key, call_id, seed slot,
+    draw slot); call_id advances by one per sampling call."""
+    if key is not None:
+        STATE.sample_key = int(key)
+    if call_id is not None:
+        STATE.sample_calls = int(call_id)
+    if replace is not None:
+        STATE.sample_replace = bool(replace)
+
+
+# -------------------------------------------------------------------- sampling
+def _sample(seeds: torch.Tensor, fanout: int) -> torch.Tensor:
+    g = STATE.graph
+    if g.uva_indptr is None:
+        raise RuntimeError("mix_cache_graphs has not been called")
+    seeds = _need_cuda(seeds, "seeds")
+    out = torch.empty(seeds.numel() * int(fanout), dtype=torch.int64, device=seeds.device)
+    call_id = STATE.sample_calls
+    STATE.sample_calls += 1
+    check(lib.apt_sample_csc_fanout(
+        _ptr(seeds), seeds.numel(), int(fanout), _ptr(g.adj_pos_map), g.num_total_nodes,
+        _ptr(g.dev_indptr), _ptr(g.dev_indices), _ptr(g.uva_indptr), _ptr(g.uva_indices),
+        STATE.sample_key, call_id & 0xFFFFFFFF, 1 if STATE.sample_replace else 0,
+        _ptr(out), STATE.status_ptr(), _stream()))
+    return out
+
+
+def local_sample_one_layer(seeds: torch.Tensor, fanout: int) -> List[torch.Tensor]:
+    """LocalSamplingNeibhorsOneLayer, src/sampling.cc:13-17: [seeds, neighbors]."""
+    return [seeds, _sample(seeds, fanout)]
+
+
+def relabel_csc(seeds: torch.Tensor, neighbors: torch.Tensor) -> List[torch.Tensor]:
+    """RelabelCSC, src/relabel.cc:9-15: [all_unique, relabeled_neighbors]."""
+    seeds = _need_cuda(seeds, "seeds")
+    neighbors = _need_cuda(neighbors, "neighbors")
+    n = seeds.numel() + neighbors.numel()
+    uniq = torch.empty(n, dtype=torch.int64, device=seeds.device)
+    rel = torch.empty(neighbors.numel(), dtype=torch.int64, device=seeds.device)
+    nbytes = lib.apt_relabel_workspace_bytes(n)
+    ws = STATE.workspace("relabel", nbytes)
+    words = STATE.words()
+    check(lib.apt_relabel_csc(_ptr(seeds), seeds.numel(), _ptr(neighbors), neighbors.numel(),
+                              _ptr(ws), ws.numel(), _ptr(uniq), _ptr(rel),
+                              ctypes.c_void_p(words.data_ptr()), STATE.status_ptr(), _stream()))
+    num_unique = int(STATE.read_words()[0])
+    return [uniq[:num_unique], rel]
+
+
+# ---------------------------------------------------------------- seed shuffle
+def _bucket(seeds: torch.Tensor):
+    s = STATE
+    if s.shuffle_min_vids is None:
+        raise RuntimeError("register_min_vids has not been called")
+    n = seeds.numel()
+    dev = seeds.device
+    sorted_ids = torch.empty(n, dtype=torch.int64, device=dev)
+    perm = torch.empty(n, dtype=torch.int64, device=dev)
+    sizes = torch.empty(s.world_size, dtype=torch.int64, device=dev)
+    offsets = torch.empty(s.world_size, dtype=torch.int64, device=dev)
+    nbytes = lib.apt_bucket_workspace_bytes(n, s.world_size)
+    ws = s.workspace("bucket", nbytes)
+    node_beg = s.rank - s.rank % s.node_size
+    check(lib.apt_bucket_by_owner(_ptr(seeds), n, _ptr(s.shuffle_min_vids), s.world_size, s.shuffle_id_offset,
+                                  s.rank, node_beg, node_beg + s.node_size, _ptr(ws), ws.numel(),
+                                  _ptr(sorted_ids), _ptr(perm), _ptr(sizes), _ptr(offsets), _stream()))
+    return sorted_ids, perm, sizes, offsets
+
+
+def shuffle_seeds(seeds: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """ShuffleSeeds, src/sampling.cc:159-193: (recv_frontier [cuda],
+    permutation [cuda], recv_offset [cpu], dev_offset [cpu]); offsets are
+    inclusive cumulative counts. Ids of one owner keep their input order."""
+    seeds = _need_cuda(seeds, "seeds")
+    sorted_ids, perm, sizes, offsets = _bucket(seeds)
+    recv, recv_offset, dev_offset = _exchange().exchange_ids(sorted_ids, sizes, offsets)
+    return recv, perm, recv_offset, dev_offset
+
+
+def unique_sorted(ids: torch.Tensor, id_lo: int, id_hi: int):
+    """Sorted unique + inverse of ids in [id_lo, id_hi): torch::_unique2(sorted,
+    return_inverse) of src/sampling.cc:58-59, via a bitmap over the id range."""
+    ids = _need_cuda(ids, "ids")
+    n = ids.numel()
+    rng = int(id_hi) - int(id_lo)
+    uniq = torch.empty(min(n, max(rng, 0)), dtype=torch.int64, device=ids.device)
+    inv = torch.empty(n, dtype=torch.int64, device=ids.device)
+    nbytes = lib.apt_unique_workspace_bytes(rng)
+    ws = STATE.workspace("unique", nbytes)
+    words = STATE.words()
+    check(lib.apt_unique_sorted(_ptr(ids), n, int(id_lo), int(id_hi), _ptr(ws), ws.numel(), _ptr(uniq), _ptr(inv),
+                                ctypes.c_void_p(words.data_ptr()), STATE.status_ptr(), _stream()))
+    num_unique = int(STATE.read_words()[0])
+    return uniq[:num_unique], inv
+
+
+def _owned_range():
+    """Ids this rank can receive from a seed shuffle. On one machine these are
+    the ids it owns; with several machines foreign ids are re-mapped to the
+    sender itself (src/cuda/npc_kernel.cu:340-342), so any id may arrive."""
+    s = STATE
+    n_total = s.graph.num_total_nodes
+    if s.node_size == s.world_size and s.shuffle_id_offset == 0 and s._min_vids_host is not None:
+        lo = int(s._min_vids_host[s.rank])
+        hi = int(s._min_vids_host[s.rank + 1])
+        if s.rank == 0:
+            lo = min(lo, 0)
+        if s.rank == s.world_size - 1:
+            hi = max(hi, n_total)
+        return lo, hi
+    return 0, n_total
+
+
+def np_sample_and_shuffle(seeds: torch.Tensor, fanout: int) -> List[torch.Tensor]:
+    """NPSampleAndShuffle, src/sampling.cc:52-69: [unique_frontier, neighbors,
+    permutation, recv_offset, dev_offset, inverse_idx]."""
+    recv, perm, recv_offset, dev_offset = shuffle_seeds(seeds)
+    lo, hi = _owned_range()
+    uniq, inverse_idx = unique_sorted(recv, lo, hi)
+    neighbors = _sample(uniq, fanout)
+    return [uniq, neighbors, perm, recv_offset, dev_offset, inverse_idx]
+
+
+def sp_sample_shuffle_src(unique_src: torch.Tensor) -> List[torch.Tensor]:
+    """SPSampleShuffleSrc, src/sampling.cc:151-157."""
+    return list(shuffle_seeds(unique_src))
+
+
+# ---------------------------------------------------------------------- gather
+def load_subtensor(node_id: torch.Tensor) -> torch.Tensor:
+    """LoadSubtensor, src/load_subtensor.cc:19-40: rows of the GPU cache or,
+    on a miss, of the page-locked host table, in one call."""
+    f = STATE.feat
+    if f.feat_pos_map is None:
+        raise RuntimeError("cache_feats_shared has not been called")
+    node_id = _need_cuda(node_id, "node_id")
+    n = node_id.numel()
+    esz = f.dev_feats.element_size()
+    out = torch.empty((n, f.rank_feat_dim), dtype=f.dev_feats.dtype, device=node_id.device)
+    nbytes = lib.apt_gather_workspace_bytes(n)
+    ws = STATE.workspace("gather", nbytes)
+    side = STATE.side_stream() if f.uva_feats.shape[0] > 0 else None
+    check(lib.apt_gather_rows(
+        _ptr(node_id), n, _ptr(f.feat_pos_map), f.num_total_nodes,
+        _ptr(f.dev_feats), f.dev_feats.shape[0], f.rank_feat_dim * esz,
+        _ptr(f.uva_feats), f.uva_feats.shape[0], f.feat_dim * esz, f.feat_dim_offset * esz,
+        _ptr(out), _ptr(ws), ws.numel(), STATE.status_ptr(), _stream(),
+        ctypes.c_void_p(side.cuda_stream) if side is not None else None))
+    if side is not None:
+        # the workspace and output are also in use on the side stream
+        ws.record_stream(side)
+        out.record_stream(side)
+    return out
+
+
+def cpu_load_subtensor(node_id: torch.Tensor) -> torch.Tensor:
+    """CPULoadSubtensor, src/load_subtensor.cc:10-17: host table only, on the
+    CPU, as the reference does it (two index_selects)."""
+    f = STATE.feat
+    pos = -f.cpu_feat_pos_map.index_select(0, node_id.cpu()) - 2
+    table = f.uva_feats if not f.uva_feats.is_cuda else f.uva_feats.cpu()
+    return table.index_select(0, pos)
+
+
+# -------------------------------------------------------------- feature shuffle
+def feat_shuffle(inputs: torch.Tensor, send_offset: torch.Tensor, recv_offset: torch.Tensor,
+                 permutation: torch.Tensor, feat_dim: int, fwd_flag: int) -> torch.Tensor:
+    """FeatShuffle, src/feat_shuffle.cc:9-30. Offsets are CPU int64 inclusive
+    cumulative row counts. fwd: rows travel to the ranks that asked for them
+    and come out in the asker's original seed order (``buf[permutation]``);
+    bwd: rows are scattered by permutation and travel back."""
+    if inputs.dtype not in _DTYPE_CODE:
+        raise RuntimeError(f"feat_shuffle: unsupported dtype {inputs.dtype}")
+    inputs = _need_cuda(inputs, "inputs", dtype=None)
+    permutation = _need_cuda(permutation, "permutation")
+    rows_in = inputs.numel() // int(feat_dim)
+    return _exchange().exchange_rows(inputs.view(rows_in, int(feat_dim)), send_offset, recv_offset,
+                                        permutation, bool(fwd_flag))
+
+
+def alltoall(input: torch.Tensor, output: torch.Tensor, send_offset: torch.Tensor, recv_offset: torch.Tensor,
+             expand: int = 1, comm_type: int = 0) -> None:
+    """AlltoAll, src/ops/collective.cc:252-266: in place into `output`; any
+    dtype (the reference silently ignores everything but int64/fp32)."""
+    _exchange().alltoall(_need_cuda(input, "input", dtype=None), output, send_offset, recv_offset, int(expand))
+
+
+# ---------------------------------------------------------------- SpMM / SDDMM
+def _spmm(op, coo_row, coo_col, inp, edata, coo_offset, input_offset, output_offset):
+    ref = inp if inp is not None else edata
+    if ref.dtype not in _DTYPE_CODE:
+        raise RuntimeError(f"spmm: unsupported dtype {ref.dtype}")
+    coo_row = _need_cuda(coo_row, "coo_row")
+    coo_col = _need_cuda(coo_col, "coo_col")
+    coo_offset = _need_cuda(coo_offset, "coo_offset")
+    output_offset = _need_cuda(output_offset, "output_offset")
+    if input_offset is not None:
+        input_offset = _need_cuda(input_offset, "input_offset")
+    ref = _need_cuda(ref, "input", dtype=None)
+    if inp is not None:
+        inp = ref
+    if edata is not None:
+        edata = _need_cuda(edata, "edata", dtype=ref.dtype)
+    out_num = int(output_offset[-1].item())  # host read, as in src/spmm.cc:13
+    feat_dim = ref.shape[1] if inp is not None or edata is None else edata.shape[1]
+    if inp is not None:
+        feat_dim = inp.shape[1]
+    out = torch.empty((out_num, feat_dim), dtype=ref.dtype, device=ref.device)
+    nbytes = lib.apt_spmm_workspace_bytes(out_num)
+    ws = STATE.workspace("spmm", nbytes)
+    edim = edata.numel() // max(coo_row.numel(), 1) if edata is not None and coo_row.numel() else feat_dim
+    check(lib.apt_spmm_sum(op, _DTYPE_CODE[ref.dtype], _ptr(coo_row), _ptr(coo_col), coo_row.numel(),
+                           _ptr(inp), _ptr(edata), int(edim), int(feat_dim), _ptr(coo_offset),
+                           _ptr(input_offset), _ptr(output_offset), coo_offset.numel() - 1, out_num,
+                           _ptr(out), _ptr(ws), ws.numel(), _stream()))
+    return out
+
+
+def spmm_copy_u_sum(coo_row, coo_col, input, coo_offset, input_offset, output_offset):
+    """CopyUSum, src/spmm.cc:9-19."""
+    return _spmm(0, coo_row, coo_col, input, None, coo_offset, input_offset, output_offset)
+
+
+def spmm_copy_e_sum(coo_row, coo_col, input, coo_offset, output_offset):
+    """CopyESum, src/spmm.cc:21-29: `input` holds one row per edge."""
+    return _spmm(1, coo_row, coo_col, None, input, coo_offset, None, output_offset)
+
+
+def spmm_u_mul_e_sum(coo_row, coo_col, input, edata, coo_offset, input_offset, output_offset, ref_quirk_add=False):
+    """UMulESum, src/spmm.cc:31-42: sum over edges of input[src] * edata[e].
+    The reference's kernel adds instead of multiplying (src/cuda/spmm.cu:78);
+    ref_quirk_add=True reproduces that."""
+    return _spmm(3 if ref_quirk_add else 2, coo_row, coo_col, input, edata, coo_offset, input_offset, output_offset)
+
+
+def _sddmm(op, coo_row, coo_col, lhs, rhs, coo_offset, lhs_offset, rhs_offset):
+    if lhs.dtype not in _DTYPE_CODE or rhs.dtype != lhs.dtype:
+        raise RuntimeError(f"sddmm: unsupported dtypes {lhs.dtype}/{rhs.dtype}")
+    coo_row = _need_cuda(coo_row, "coo_row")
+    coo_col = _need_cuda(coo_col, "coo_col")
+    lhs = _need_cuda(lhs, "lhs", dtype=None)
+    rhs = _need_cuda(rhs, "rhs", dtype=None)
+    coo_offset = _need_cuda(coo_offset, "coo_offset")
+    lhs_offset = _need_cuda(lhs_offset, "lhs_offset")
+    rhs_offset = _need_cuda(rhs_offset, "rhs_offset")
+    out = torch.empty((coo_row.numel(), lhs.shape[1]), dtype=lhs.dtype, device=lhs.device)
+    check(lib.apt_sddmm(op, _DTYPE_CODE[lhs.dtype], _ptr(coo_row), _ptr(coo_col), coo_row.numel(), _ptr(lhs),
+                        _ptr(rhs), lhs.shape[1], _ptr(coo_offset), _ptr(lhs_offset), _ptr(rhs_offset),
+                        coo_offset.numel() - 1, _ptr(out), _stream()))
+    return out
+
+
+def sddmm_u_add_v(coo_row, coo_col, lhs, rhs, coo_offset, lhs_offset, rhs_offset):
+    """UAddV, src/sddmm.cc:9-19."""
+    return _sddmm(0, coo_row, coo_col, lhs, rhs, coo_offset, lhs_offset, rhs_offset)
+
+
+def sddmm_u_mul_v(coo_row, coo_col, lhs, rhs, coo_offset, lhs_offset, rhs_offset):
+    """UMulV, src/sddmm.cc:21-31."""
+    return _sddmm(1, coo_row, coo_col, lhs, rhs, coo_offset, lhs_offset, rhs_offset)
+
+
+# ------------------------------------------------------------------ row movers
+def rows_gather(inp: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
+    """out[i] = inp[index[i]] for 2-D inp (the model's h[inverse_idx],
+    python/npc/model/sage_model.py:67)."""
+    inp = _need_cuda(inp, "inp", dtype=None)
+    index = _need_cuda(index, "index")
+    out = torch.empty((index.numel(), inp.shape[1]), dtype=inp.dtype, device=inp.device)
+    check(lib.apt_rows_gather(_ptr(inp), _ptr(index), index.numel(), inp.shape[1] * inp.element_size(),
+                              _ptr(out), _stream()))
+    return out
+
+
+def rows_scatter(inp: torch.Tensor, index: torch.Tensor, num_out_rows: int) -> torch.Tensor:
+    """out[index[i]] = inp[i]; rows of out not named by index are zero."""
+    inp = _need_cuda(inp, "inp", dtype=None)
+    index = _need_cuda(index, "index")
+    alloc = torch.empty if index.numel() == num_out_rows else torch.zeros
+    out = alloc((num_out_rows, inp.shape[1]), dtype=inp.dtype, device=inp.device)
+    check(lib.apt_rows_scatter(_ptr(inp), _ptr(index), index.numel(), inp.shape[1] * inp.element_size(),
+                               _ptr(out), _stream()))
+    return out

@@ -1,0 +1,309 @@
+/*
+ * apt_b200.h — C ABI of libapt_b200.so: the mini-batch data path of APT
+ * (neighbour sampling, relabelling, cache-aware feature gather, seed/feature
+ * shuffle between GPUs, SpMM/SDDMM over sampled blocks) as hand-written
+ * sm_100a CUDA.
+ *
+ * Conventions
+ *  - Every pointer is a raw device pointer unless its comment says "host".
+ *    "uva" pointers are page-locked host allocations that the device can
+ *    dereference (cudaHostRegister / cudaHostAlloc).
+ *  - Ids and offsets are int64_t, like the reference's IdType (src/utils.h:14).
+ *  - `stream` is a cudaStream_t passed as void*. Calls are stream-ordered and
+ *    never synchronise the host unless the comment says so.
+ *  - Outputs and workspaces are allocated by the caller. No entry point in
+ *    this header allocates device memory except apt_p2p_create.
+ *  - Return value: APT_OK or an apt_status; apt_last_error() gives the text.
+ *    Nothing here aborts the process, traps the GPU or waits without a bound.
+ *  - Each entry point cites the reference function (file:line inside the
+ *    kaihaoma/APT tree) whose role it takes.
+ */
+#ifndef APT_B200_H_
+#define APT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum apt_status {
+  APT_OK = 0,
+  APT_ERR_BAD_ARG = 1,   /* null pointer, negative size, unsupported dtype/alignment */
+  APT_ERR_CUDA = 2,      /* a CUDA runtime call failed */
+  APT_ERR_TIMEOUT = 3,   /* a bounded wait on a peer ran out */
+  APT_ERR_OOB = 4,       /* an id outside the registered tables was seen */
+  APT_ERR_CAPACITY = 5   /* workspace / inbox too small for this call */
+} apt_status;
+
+/* Element types of feature rows. The gather and shuffle are byte copies and
+ * only need the element size; SpMM/SDDMM compute in fp32 and round once. */
+typedef enum apt_dtype { APT_F32 = 0, APT_BF16 = 1, APT_F16 = 2 } apt_dtype;
+
+/* Bits of the device-side status word (int32) several kernels OR into. */
+#define APT_FLAG_ID_OUT_OF_RANGE 1  /* node id < 0 or >= num_nodes */
+#define APT_FLAG_FEAT_NOT_EXIST  2  /* feat_pos_map == -1: row neither cached nor on host */
+#define APT_FLAG_ZERO_DEGREE     4  /* sampled a node with no in-neighbour */
+#define APT_FLAG_TABLE_FULL      8  /* relabel hash table overflow (workspace too small) */
+#define APT_FLAG_PEER_TIMEOUT    16 /* a peer's flag did not arrive in time */
+
+const char* apt_last_error(void);
+int apt_version(void);
+
+/* Number of kernels this library has launched in this process, and a reset.
+ * The benchmark reports it as its launch count. */
+int64_t apt_launch_count(void);
+void apt_launch_count_reset(void);
+
+/* Optional per-kernel timing. When enabled, every launch of a tagged kernel
+ * is bracketed by CUDA events on its own stream; apt_profile_read
+ * synchronises those events and returns the summed milliseconds and launch
+ * count of one tag ("gather_hit", "gather_miss", "sample", "relabel", ...)
+ * then forgets them. Off by default (no events are recorded). */
+int apt_profile_enable(int on);
+int apt_profile_read(const char* tag, double* total_ms, int64_t* launches);
+
+/* ------------------------------------------------------------------ sampling
+ * Uniform fanout sampling of in-neighbours from a CSC graph, one dense row of
+ * `fanout` ids per seed. Takes the role of LocalSampleNeighbors /
+ * _CSRRowWiseSampleReplaceKernel (src/cuda/npc_kernel.cu:248-316) behind
+ * LocalSamplingNeibhorsOneLayer (src/sampling.cc:13-17).
+ *
+ *   p = adj_pos_map[v];  p >= 0 : row p of (dev_indptr, dev_indices)
+ *                        p <  0 : row -(p)-2 of (uva_indptr, uva_indices)
+ *   replace != 0:  out[j*fanout+i] = indices[start + draw(j,i) % deg]
+ *   replace == 0:  Floyd selection of `fanout` distinct edge slots when
+ *                  deg > fanout (fanout <= 32); otherwise every neighbour once,
+ *                  then draws with replacement for the remaining slots.
+ *   deg == 0:      the row is filled with v itself and APT_FLAG_ZERO_DEGREE is
+ *                  set (the reference leaves the row uninitialised).
+ *   draw(j,i) = word (i & 3) of Philox4x32-10 with key (key_lo, key_hi) and
+ *               counter (j & 0xffffffff, j >> 32, i >> 2, call_id).
+ * adj_pos_map may be NULL: every node then reads (uva_indptr, uva_indices),
+ * which may be plain device memory holding the whole graph.
+ */
+int apt_sample_csc_fanout(const int64_t* seeds, int64_t num_seeds, int fanout,
+                          const int64_t* adj_pos_map, int64_t num_nodes,
+                          const int64_t* dev_indptr, const int64_t* dev_indices,
+                          const int64_t* uva_indptr, const int64_t* uva_indices,
+                          uint64_t key, uint32_t call_id, int replace,
+                          int64_t* out_neighbors, int32_t* status_word,
+                          void* stream);
+
+/* ------------------------------------------------------------------ relabel
+ * First-occurrence unique of cat(seeds, neighbors) and the position of every
+ * neighbour in it. Takes the role of TensorRelabelCSC (src/cuda/relabel.cu:
+ * 175-185; Unique :78-151, Relabel :153-173) behind RelabelCSC
+ * (src/relabel.cc:9-15).
+ *
+ *   out_unique     int64[num_seeds + num_neighbors] (only the first U written)
+ *   out_relabeled  int64[num_neighbors]
+ *   out_num_unique int64[1] device word receiving U
+ * workspace: apt_relabel_workspace_bytes(num_seeds + num_neighbors) bytes,
+ * 256-byte aligned; contents need no initialisation.
+ */
+size_t apt_relabel_workspace_bytes(int64_t num_items);
+int apt_relabel_csc(const int64_t* seeds, int64_t num_seeds,
+                    const int64_t* neighbors, int64_t num_neighbors,
+                    void* workspace, size_t workspace_bytes,
+                    int64_t* out_unique, int64_t* out_relabeled,
+                    int64_t* out_num_unique, int32_t* status_word,
+                    void* stream);
+
+/* ----------------------------------------------------------- owner bucketing
+ * Stable partition of ids by owning rank. Takes the role of ClusterAndPermute
+ * (src/cuda/npc_kernel.cu:318-382, :434-470) inside ShuffleSeeds
+ * (src/sampling.cc:159-193).
+ *
+ *   owner(v): d = shuffle_id_offset; while d+1 < world_size and
+ *             min_vids[d+1] <= v: ++d;  if d outside [node_beg,node_end): d = rank
+ *   out_sorted[ out_perm[i] ] = ids[i]; ids of one owner keep their input order
+ *   out_bucket_sizes int64[world_size]; out_bucket_offsets = inclusive cumsum.
+ * min_vids is a device array of world_size+1 entries; world_size <= 32.
+ * workspace: apt_bucket_workspace_bytes(num_ids, world_size) bytes.
+ */
+size_t apt_bucket_workspace_bytes(int64_t num_ids, int world_size);
+int apt_bucket_by_owner(const int64_t* ids, int64_t num_ids,
+                        const int64_t* min_vids, int world_size,
+                        int64_t shuffle_id_offset, int rank, int node_beg,
+                        int node_end, void* workspace, size_t workspace_bytes,
+                        int64_t* out_sorted, int64_t* out_perm,
+                        int64_t* out_bucket_sizes, int64_t* out_bucket_offsets,
+                        void* stream);
+
+/* ------------------------------------------------------- sorted unique + inverse
+ * Ascending unique of ids within [id_lo, id_hi) and, per input, its position
+ * in that unique list. Takes the role of torch::_unique2(sorted, inverse) in
+ * NPSampleAndShuffle (src/sampling.cc:58-59). A bitmap over the id range
+ * replaces the sort. Ids outside the range set APT_FLAG_ID_OUT_OF_RANGE and
+ * get inverse -1.
+ *   out_unique int64[min(num_ids, id_hi-id_lo)], out_inverse int64[num_ids],
+ *   out_num_unique int64[1] device word.
+ * workspace: apt_unique_workspace_bytes(id_hi - id_lo) bytes.
+ */
+size_t apt_unique_workspace_bytes(int64_t id_range);
+int apt_unique_sorted(const int64_t* ids, int64_t num_ids, int64_t id_lo,
+                      int64_t id_hi, void* workspace, size_t workspace_bytes,
+                      int64_t* out_unique, int64_t* out_inverse,
+                      int64_t* out_num_unique, int32_t* status_word,
+                      void* stream);
+
+/* ---------------------------------------------------------------- gather
+ * Cache-aware feature-row gather. Takes the role of IndexSelectAll /
+ * _CSRRowWiseLoadSubtensorAlignedAllKernel (src/cuda/npc_kernel.cu:187-246)
+ * behind LoadSubtensor (src/load_subtensor.cc:19-40).
+ *
+ *   p = feat_pos_map[index[r]]
+ *   p >= 0 : out[r] = dev_feats row p            (dev_row_bytes each)
+ *   p < -1 : out[r] = uva_feats row -(p)-2, bytes [uva_col_offset_bytes,
+ *            uva_col_offset_bytes + dev_row_bytes) of a uva_row_bytes row
+ *   p == -1: out[r] = 0 and APT_FLAG_FEAT_NOT_EXIST (the reference reads out
+ *            of bounds here)
+ * Rows are opaque bytes, so fp32/bf16/fp16 tables share the code.
+ * Three kernels: classify (decode p, compact the miss list), hit copy on
+ * `stream`, miss copy on `side_stream` (may be NULL: then it runs on `stream`
+ * after the hit copy). The output is complete in `stream` order on return.
+ * workspace: apt_gather_workspace_bytes(num_rows) bytes.
+ */
+size_t apt_gather_workspace_bytes(int64_t num_rows);
+int apt_gather_rows(const int64_t* index, int64_t num_rows,
+                    const int64_t* feat_pos_map, int64_t num_nodes,
+                    const void* dev_feats, int64_t num_dev_rows,
+                    int64_t dev_row_bytes, const void* uva_feats,
+                    int64_t num_uva_rows, int64_t uva_row_bytes,
+                    int64_t uva_col_offset_bytes, void* out, void* workspace,
+                    size_t workspace_bytes, int32_t* status_word, void* stream,
+                    void* side_stream);
+
+/* ------------------------------------------------------------ SpMM / SDDMM
+ * Segment-batched COO operators over sampled blocks: edge e of segment k
+ * (coo_offset[k] <= e < coo_offset[k+1]) reads input row input_offset[k]+row[e]
+ * and accumulates into output row output_offset[k]+col[e]. Offsets are device
+ * arrays of num_segments+1 entries. Take the role of CopyUSumCUDA, CopyESumCUDA,
+ * UMulESumCUDA (src/cuda/spmm.cu:7-148; hosts src/spmm.cc:9-42) and UAddVCUDA,
+ * UMulVCUDA (src/cuda/sddmm.cu:7-103; hosts src/sddmm.cc:9-31).
+ *
+ * The output is fully written (rows without edges become 0); it needs no
+ * zero-fill. When col is non-decreasing inside every segment (a sampled
+ * block), each output row is reduced by one warp in edge order: no atomics,
+ * deterministic. Otherwise edges are scattered with vector red.add.
+ * op: 0 copy_u, 1 copy_e, 2 u_mul_e, 3 u_add_e (the arithmetic the reference's
+ *     UMulESum kernel actually performs, src/cuda/spmm.cu:78).
+ * edata (copy_e, u_mul_e, u_add_e) has num_edges rows of edata_dim columns,
+ * edata_dim == feat_dim, or a divisor of feat_dim (one scalar per head,
+ * broadcast over feat_dim/edata_dim columns).
+ * workspace: apt_spmm_workspace_bytes(num_out_rows) bytes.
+ */
+size_t apt_spmm_workspace_bytes(int64_t num_out_rows);
+int apt_spmm_sum(int op, int dtype, const int64_t* coo_row,
+                 const int64_t* coo_col, int64_t num_edges, const void* input,
+                 const void* edata, int64_t edata_dim, int64_t feat_dim,
+                 const int64_t* coo_offset, const int64_t* input_offset,
+                 const int64_t* output_offset, int num_segments,
+                 int64_t num_out_rows, void* out, void* workspace,
+                 size_t workspace_bytes, void* stream);
+
+/* op: 0 u_add_v, 1 u_mul_v; out has num_edges rows of feat_dim columns. */
+int apt_sddmm(int op, int dtype, const int64_t* coo_row,
+              const int64_t* coo_col, int64_t num_edges, const void* lhs,
+              const void* rhs, int64_t feat_dim, const int64_t* coo_offset,
+              const int64_t* lhs_offset, const int64_t* rhs_offset,
+              int num_segments, void* out, void* stream);
+
+/* ------------------------------------------------------- local row movers
+ * out[i] = in[index[i]] and out[index[i]] = in[i] over rows of row_bytes
+ * bytes (16-byte vectors when alignment allows). These are the index_select /
+ * index_select_backward steps of FeatShuffle (src/feat_shuffle.cc:13-28) for
+ * a permutation index, and the h[inverse_idx] step that precedes it
+ * (python/npc/model/sage_model.py:67).
+ */
+int apt_rows_gather(const void* in, const int64_t* index, int64_t num_out_rows,
+                    int64_t row_bytes, void* out, void* stream);
+int apt_rows_scatter(const void* in, const int64_t* index, int64_t num_in_rows,
+                     int64_t row_bytes, void* out, void* stream);
+
+/* ------------------------------------------------ peer-to-peer all-to-all
+ * Replaces the grouped ncclSend/ncclRecv all-to-all (_AlltoAll,
+ * src/ops/collective.cc:223-266) used by ShuffleSeeds (src/sampling.cc:176-191)
+ * and FeatShuffle (src/feat_shuffle.cc:20-22) with stores into the receiving
+ * GPU's memory over NVLink.
+ *
+ * Every rank owns an inbox of 2 (epoch parity) x world_size regions of
+ * region_bytes each plus flag words, allocated by apt_p2p_create with
+ * cudaMalloc and exported as a CUDA IPC handle. Ranks exchange the 64-byte
+ * handles out of band (the host side uses torch.distributed) and map each
+ * other's inbox with apt_p2p_attach. One all-to-all is then:
+ *   apt_p2p_push   each rank copies its rows for peer r into region [me] of
+ *                  r's inbox, fences, and releases flag (epoch, row count);
+ *   apt_p2p_wait   a one-block kernel waits (bounded by timeout_ns) for the
+ *                  world_size flags of this epoch and writes the received row
+ *                  counts to a device array;
+ *   apt_p2p_pull   copies / permutes the received rows out of the inbox.
+ * All ranks must issue the same sequence of all-to-alls on one stream each.
+ * Waiting for all flags of epoch e before any store of epoch e+1, together
+ * with the parity double buffer, keeps an inbox region from being overwritten
+ * before its owner has consumed it.
+ */
+typedef struct apt_p2p apt_p2p;
+#define APT_IPC_HANDLE_BYTES 64
+
+int apt_p2p_create(int rank, int world_size, size_t region_bytes,
+                   apt_p2p** out_ctx, void* out_handle /* host, 64 bytes */);
+int apt_p2p_attach(apt_p2p* ctx, int peer, const void* handle /* host */);
+/* Same-process variant: `base` is the inbox (apt_p2p_local_base) of a context
+ * created in this process, e.g. several ranks emulated on one GPU in tests. */
+int apt_p2p_attach_ptr(apt_p2p* ctx, int peer, void* base);
+void* apt_p2p_local_base(apt_p2p* ctx);
+int apt_p2p_destroy(apt_p2p* ctx);
+size_t apt_p2p_region_bytes(const apt_p2p* ctx);
+
+/* Push rows. Row j of the outgoing stream (0 <= j < send_offsets[world_size-1])
+ * is src row j when src_index is NULL, src row src_index[j] when
+ * index_is_dest == 0, and otherwise the src row t with src_index[t] == j
+ * (src_index is then a permutation that names each src row's position); rows
+ * [send_offsets[r-1], send_offsets[r]) go to peer r. send_offsets is a DEVICE
+ * array of world_size inclusive row offsets; max_rows is a host-side upper
+ * bound of send_offsets[world_size-1] that sizes the grid. Rows that do not
+ * fit a region are dropped and APT_FLAG_TABLE_FULL is set. Advances the epoch. */
+int apt_p2p_push(apt_p2p* ctx, const void* src, const int64_t* src_index,
+                 int index_is_dest, const int64_t* send_offsets, int64_t max_rows,
+                 int64_t row_bytes, int32_t* status_word, void* stream);
+/* Wait for this epoch's flags; out_recv_counts int64[world_size] (device)
+ * receives the rows each peer sent. timeout_ns <= 0 selects 2 s. On timeout
+ * APT_FLAG_PEER_TIMEOUT is ORed into status_word and counts are set to 0. */
+int apt_p2p_wait(apt_p2p* ctx, int64_t* out_recv_counts, int32_t* status_word,
+                 int64_t timeout_ns, void* stream);
+/* Copy received rows out of the inbox in peer order (peer 0's rows first).
+ * If dst_index is NULL row j of the concatenation lands at dst row j; else if
+ * index_is_source it is a gather: dst row i = concatenation row dst_index[i]
+ * (num_dst_rows rows); else a scatter: concatenation row j lands at
+ * dst_index[j]. recv_counts is the device array apt_p2p_wait filled. */
+int apt_p2p_pull(apt_p2p* ctx, const int64_t* recv_counts,
+                 const int64_t* dst_index, int index_is_source,
+                 int64_t num_dst_rows, int64_t max_rows, int64_t row_bytes,
+                 void* dst, void* stream);
+
+/* --------------------------------------------------------- setup utilities
+ * Not on the timed path; they prepare the synthetic graphs of the benchmark
+ * on the GPU so that a 1.6 G-edge graph is built in seconds. */
+
+/* R-MAT edge list: edge e draws its (src, dst) bits from Philox4x32-10 keyed
+ * by `seed`, counter (e, attempt); endpoints >= num_nodes are redrawn. */
+int apt_rmat_edges(uint64_t seed, int64_t first_edge, int64_t num_edges,
+                   int scale, int64_t num_nodes, float a, float b, float c,
+                   int64_t* out_src, int64_t* out_dst, void* stream);
+/* Ascending radix sort (cub) of the low `end_bit` bits of uint64 keys from
+ * keys_in into keys_out. temp: apt_sort_u64_temp_bytes(n) bytes. */
+size_t apt_sort_u64_temp_bytes(int64_t n);
+int apt_sort_u64(const uint64_t* keys_in, uint64_t* keys_out, int64_t n,
+                 void* temp, size_t temp_bytes, int end_bit, void* stream);
+/* Standard-normal rows: element (row, col) from Philox keyed by seed; written
+ * as dtype. Fills rows [first_row, first_row + num_rows). */
+int apt_normal_rows(uint64_t seed, int64_t first_row, int64_t num_rows,
+                    int64_t dim, int dtype, void* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* APT_B200_H_ */

@@ -1,0 +1,434 @@
+"""CPU oracle of APT's mini-batch data path (numpy). TEST INFRASTRUCTURE ONLY.
+
+This file restates, on the CPU, what the reference (kaihaoma/APT) computes on
+the path sampling -> relabel -> seed shuffle -> feature gather -> feature
+shuffle -> SpMM/SDDMM, one function per reference function, each citing the
+reference file:line it follows. Only the tests, the smoke check and the
+benchmark's CPU-baseline leg may import it; the product path never does.
+
+Pinning status
+  * all-to-all / all-gather / all-broadcast / all-reduce and the seed shuffle
+    are pinned by the closed-form cases of the reference's own tests
+    (tests/test_alltoall.cc, test_allgather.cc, test_allbroadcast.cc,
+    test_allreduce.cc, test_shuffle_seeds.cc), replayed over N in-process
+    ranks in tests/test_oracle_golden.py.
+  * sampling, relabelling, gather, SpMM and SDDMM have no test, fixture or
+    golden vector in the reference, the reference itself is CUDA-only (plus
+    glog/MPI/DGL, absent here) and cannot be built or imported in this
+    environment: for these stages this oracle is "parity unpinned" — it
+    follows the cited source lines, and is cross-checked against an
+    independent C restatement (oracle/apt_oracle.c) and against committed
+    fixtures (tests/golden/).
+
+Deliberate, documented differences from the reference:
+  * the sampler draws from Philox4x32-10 (counter-based) instead of cuRAND
+    XORWOW re-seeded per call (src/cuda/npc_kernel.cu:258-261); the use of the
+    draw, `indices[start + draw % deg]`, is the reference's (:279-282);
+  * a zero-degree seed yields its own id (the reference leaves the row
+    uninitialised, npc_kernel.cu:277);
+  * feat_pos_map == -1 yields a zero row (the reference reads out of bounds,
+    npc_kernel.cu:196-205);
+  * within-bucket order of the seed shuffle is the stable one (the reference's
+    is atomic-order dependent, npc_kernel.cu:345-346).
+"""
+import numpy as np
+
+U32 = np.uint32
+U64 = np.uint64
+I64 = np.int64
+
+FEAT_NOT_EXIST = -1  # src/utils.h:20
+
+
+def encode_id(i):
+    """ENCODE_ID, src/utils.h:17: i -> -(i) - 2 (its own inverse)."""
+    return -(i) - 2
+
+
+# --------------------------------------------------------------------- Philox
+_M0 = U64(0xD2511F53)
+_M1 = U64(0xCD9E8D57)
+_W0 = 0x9E3779B9
+_W1 = 0xBB67AE85
+_MASK = U64(0xFFFFFFFF)
+
+
+def philox4x32_10(c0, c1, c2, c3, k0, k1):
+    """Philox4x32-10 (Salmon et al., SC'11). Inputs broadcast; returns four
+    uint32 arrays. Known answers: counter 0/key 0 -> 6627e8d5 e169c58d bc57ac4c
+    9b00dbd8; all-ones -> 408f276d 41c83b0e a20bc7c6 6d5451fd."""
+    c0, c1, c2, c3 = [np.asarray(x, dtype=U64) & _MASK for x in np.broadcast_arrays(c0, c1, c2, c3)]
+    k0 = int(k0) & 0xFFFFFFFF
+    k1 = int(k1) & 0xFFFFFFFF
+    for _ in range(10):
+        p0 = _M0 * c0
+        p1 = _M1 * c2
+        n0 = (p1 >> U64(32)) ^ c1 ^ U64(k0)
+        n1 = p1 & _MASK
+        n2 = (p0 >> U64(32)) ^ c3 ^ U64(k1)
+        n3 = p0 & _MASK
+        c0, c1, c2, c3 = n0, n1, n2, n3
+        k0 = (k0 + _W0) & 0xFFFFFFFF
+        k1 = (k1 + _W1) & 0xFFFFFFFF
+    return c0.astype(U32), c1.astype(U32), c2.astype(U32), c3.astype(U32)
+
+
+def draw_words(j, i, call_id, key):
+    """The sampler's draw(j, i): word (i & 3) of Philox with counter
+    (j lo, j hi, i >> 2, call_id) and the 64-bit key split lo/hi."""
+    j = np.asarray(j, dtype=U64)
+    i = np.asarray(i, dtype=U64)
+    j, i = np.broadcast_arrays(j, i)
+    w = philox4x32_10(j & _MASK, j >> U64(32), i >> U64(2), call_id, key & 0xFFFFFFFF, (key >> 32) & 0xFFFFFFFF)
+    sel = (i & U64(3)).astype(np.int64)
+    return np.choose(sel, w)
+
+
+# ------------------------------------------------------------------- topology
+def build_adj_pos_map(num_total_nodes, cached_node_idx):
+    """MixCacheGraphs, src/cache_graphs.cc:36-43: every node points at its row
+    of the global CSC (encoded), cached nodes at their compact row."""
+    m = encode_id(np.arange(num_total_nodes, dtype=I64))
+    m[np.asarray(cached_node_idx, dtype=I64)] = np.arange(len(cached_node_idx), dtype=I64)
+    return m
+
+
+def sample_csc_fanout(seeds, fanout, adj_pos_map, dev_indptr, dev_indices, uva_indptr, uva_indices,
+                      key, call_id, replace=True):
+    """LocalSampleNeighbors / _CSRRowWiseSampleReplaceKernel,
+    src/cuda/npc_kernel.cu:248-316: row lookup through adj_pos_map (:263-271),
+    deg from the indptr pair (:272-276), out[j*fanout+i] = indices[start +
+    draw % deg] (:277-283). replace=False is the optional Floyd selection."""
+    seeds = np.asarray(seeds, dtype=I64)
+    S = len(seeds)
+    out = np.empty(S * fanout, dtype=I64)
+    if S == 0:
+        return out
+    if adj_pos_map is None:
+        pos = encode_id(seeds)
+    else:
+        pos = np.asarray(adj_pos_map, dtype=I64)[seeds]
+    on_dev = pos >= 0
+    row = np.where(on_dev, pos, encode_id(pos))
+    start = np.empty(S, dtype=I64)
+    deg = np.empty(S, dtype=I64)
+    for mask, indptr in ((on_dev, dev_indptr), (~on_dev, uva_indptr)):
+        if mask.any():
+            ip = np.asarray(indptr, dtype=I64)
+            start[mask] = ip[row[mask]]
+            deg[mask] = ip[row[mask] + 1] - start[mask]
+    jj = np.repeat(np.arange(S, dtype=I64), fanout)
+    ii = np.tile(np.arange(fanout, dtype=I64), S)
+    words = draw_words(jj, ii, call_id, key).astype(I64)
+    degr = np.repeat(deg, fanout)
+    slot = np.where(degr > 0, words % np.maximum(degr, 1), 0)
+    if not replace:
+        slot = slot.reshape(S, fanout)
+        words2 = words.reshape(S, fanout)
+        for j in range(S):
+            d = int(deg[j])
+            if d <= 0:
+                continue
+            if d <= fanout:
+                slot[j, :d] = np.arange(d)
+            else:
+                picks = []
+                for i in range(fanout):
+                    t = d - fanout + i
+                    r = int(words2[j, i]) % (t + 1)
+                    picks.append(t if r in picks else r)
+                slot[j, :] = picks
+        slot = slot.reshape(-1)
+    edge = np.repeat(start, fanout) + slot
+    dev_r = np.repeat(on_dev, fanout)
+    zero = degr <= 0
+    res = np.repeat(seeds, fanout).copy()
+    for mask, indices in ((dev_r & ~zero, dev_indices), (~dev_r & ~zero, uva_indices)):
+        if mask.any():
+            res[mask] = np.asarray(indices, dtype=I64)[edge[mask]]
+    return res
+
+
+# -------------------------------------------------------------------- relabel
+def relabel_csc(seeds, neighbors):
+    """TensorRelabelCSC, src/cuda/relabel.cu:175-185: total = cat(seeds,
+    neighbors) (:177); Unique keeps each id at the position of its first
+    occurrence, compacted in order (:89-147); Relabel maps every neighbour to
+    that position (:153-173). Returns (all_unique, relabeled_neighbors)."""
+    seeds = np.asarray(seeds, dtype=I64)
+    neighbors = np.asarray(neighbors, dtype=I64)
+    total = np.concatenate([seeds, neighbors])
+    if len(total) == 0:
+        return total, neighbors.copy()
+    uniq_sorted, first_idx, inverse = np.unique(total, return_index=True, return_inverse=True)
+    order = np.argsort(first_idx, kind="stable")       # sorted-unique slot -> rank by first occurrence
+    new_id_of_sorted = np.empty(len(order), dtype=I64)
+    new_id_of_sorted[order] = np.arange(len(order), dtype=I64)
+    all_unique = uniq_sorted[order]
+    relabeled = new_id_of_sorted[inverse.reshape(-1)[len(seeds):]]
+    return all_unique, relabeled
+
+
+# ------------------------------------------------------------- seed shuffle
+def owner_of(ids, min_vids, world_size, shuffle_id_offset=0, rank=0, node_beg=0, node_end=None):
+    """_CountDeviceVerticesKernel, src/cuda/npc_kernel.cu:335-342."""
+    ids = np.asarray(ids, dtype=I64)
+    mv = np.asarray(min_vids, dtype=I64)
+    if node_end is None:
+        node_end = world_size
+    d = np.full(ids.shape, shuffle_id_offset, dtype=I64)
+    for r in range(shuffle_id_offset + 1, world_size):
+        # the while loop advances only while every earlier boundary also held
+        d = np.where((d == r - 1) & (mv[r] <= ids), r, d)
+    d = np.where((d < node_beg) | (d >= node_end), rank, d)
+    return d
+
+
+def bucket_by_owner(ids, min_vids, world_size, shuffle_id_offset=0, rank=0, node_beg=0, node_end=None):
+    """ClusterAndPermute, src/cuda/npc_kernel.cu:434-470 (+ _PermuteKernel
+    :367-382): returns (bucket_size, bucket_offset (inclusive), sorted_idx,
+    permutation) with sorted_idx[permutation[i]] == ids[i]; stable order."""
+    ids = np.asarray(ids, dtype=I64)
+    own = owner_of(ids, min_vids, world_size, shuffle_id_offset, rank, node_beg, node_end)
+    order = np.argsort(own, kind="stable")
+    perm = np.empty(len(ids), dtype=I64)
+    perm[order] = np.arange(len(ids), dtype=I64)
+    sizes = np.bincount(own, minlength=world_size).astype(I64)
+    return sizes, np.cumsum(sizes), ids[order], perm
+
+
+def alltoall(inputs, send_offsets, recv_offsets, expand=1):
+    """_AlltoAll over N in-process ranks, src/ops/collective.cc:223-250: rank s
+    sends rows [send_offsets[s][r-1], send_offsets[s][r]) * expand to rank r,
+    which stores them at [recv_offsets[r][s-1], recv_offsets[r][s]) * expand.
+    Offsets are inclusive cumulative counts."""
+    n = len(inputs)
+    outs = []
+    for r in range(n):
+        total = int(recv_offsets[r][-1]) * expand if len(recv_offsets[r]) else 0
+        outs.append(np.zeros(total, dtype=np.asarray(inputs[r]).dtype))
+    for s in range(n):
+        src = np.asarray(inputs[s]).reshape(-1)
+        so = np.concatenate([[0], np.asarray(send_offsets[s], dtype=I64)])
+        for r in range(n):
+            ro = np.concatenate([[0], np.asarray(recv_offsets[r], dtype=I64)])
+            cnt = so[r + 1] - so[r]
+            assert cnt == ro[s + 1] - ro[s], "send/recv size mismatch (the reference would hang)"
+            outs[r][ro[s] * expand:(ro[s] + cnt) * expand] = src[so[r] * expand:(so[r] + cnt) * expand]
+    return outs
+
+
+def allgather(inputs):
+    """AllGather, src/ops/collective.cc:19-36: concatenation in rank order."""
+    cat = np.concatenate([np.asarray(x).reshape(-1) for x in inputs])
+    return [cat.copy() for _ in inputs]
+
+
+def allbroadcast(inputs):
+    """_AllBroadcast, src/ops/collective.cc:318-339: every rank receives the
+    concatenation of all ranks' (variable-length) inputs."""
+    return allgather(inputs)
+
+
+def allreduce_scatter_v(inputs, sizes):
+    """_AllReduce, src/ops/collective.cc:404-422: one ncclReduce per root; root
+    r receives the sum over ranks of their slice [off[r], off[r]+sizes[r])."""
+    off = np.concatenate([[0], np.cumsum(sizes)])
+    return [sum(np.asarray(x)[off[r]:off[r + 1]] for x in inputs) for r in range(len(inputs))]
+
+
+def shuffle_seeds(seeds_per_rank, min_vids, node_size=None):
+    """ShuffleSeeds, src/sampling.cc:159-193, for all ranks at once. Per rank:
+    (recv_frontier, permutation, recv_offset, dev_offset)."""
+    n = len(seeds_per_rank)
+    node_size = n if node_size is None else node_size
+    parts = []
+    for r in range(n):
+        beg = r - r % node_size
+        parts.append(bucket_by_owner(seeds_per_rank[r], min_vids, n, 0, r, beg, beg + node_size))
+    sizes = np.stack([p[0] for p in parts])            # sizes[s][r]: s sends to r
+    recv_offsets = [np.cumsum(sizes[:, r]) for r in range(n)]
+    recv = alltoall([p[2] for p in parts], [p[1] for p in parts], recv_offsets)
+    return [(recv[r], parts[r][3], recv_offsets[r], parts[r][1]) for r in range(n)]
+
+
+def unique_sorted(ids):
+    """torch::_unique2(sorted=true, return_inverse=true), src/sampling.cc:58-59."""
+    u, inv = np.unique(np.asarray(ids, dtype=I64), return_inverse=True)
+    return u, inv.reshape(-1).astype(I64)
+
+
+def np_sample_and_shuffle(seeds_per_rank, fanout, min_vids, graph, key, call_id):
+    """NPSampleAndShuffle, src/sampling.cc:52-69, for all ranks at once.
+    `graph` = (adj_pos_map, dev_indptr, dev_indices, uva_indptr, uva_indices).
+    Per rank: [unique_frontier, neighbors, permutation, recv_offset,
+    dev_offset, inverse_idx]."""
+    out = []
+    for recv, perm, recv_off, dev_off in shuffle_seeds(seeds_per_rank, min_vids):
+        uniq, inv = unique_sorted(recv)
+        nbr = sample_csc_fanout(uniq, fanout, *graph, key=key, call_id=call_id)
+        out.append([uniq, nbr, perm, recv_off, dev_off, inv])
+    return out
+
+
+# --------------------------------------------------------------------- gather
+def build_feat_pos_maps(num_total_nodes, cached_idx, localnode_idx):
+    """CacheFeatsShared, src/cache_feats.cc:45-55: returns (feat_pos_map,
+    cpu_feat_pos_map). Host row i of node localnode_idx[i] is ENCODE_ID(i);
+    cached node cached_idx[i] is i; everything else FEAT_NOT_EXIST."""
+    m = np.full(num_total_nodes, FEAT_NOT_EXIST, dtype=I64)
+    m[np.asarray(localnode_idx, dtype=I64)] = encode_id(np.arange(len(localnode_idx), dtype=I64))
+    cpu = m.copy()
+    m[np.asarray(cached_idx, dtype=I64)] = np.arange(len(cached_idx), dtype=I64)
+    return m, cpu
+
+
+def load_subtensor(node_id, feat_pos_map, dev_feats, uva_feats, feat_dim_offset=0):
+    """LoadSubtensor / gather kernel, src/load_subtensor.cc:19-40 and
+    src/cuda/npc_kernel.cu:187-224: p < -1 -> host row ENCODE_ID(p), columns
+    [offset, offset + rank_feat_dim); p >= 0 -> device-cache row p."""
+    node_id = np.asarray(node_id, dtype=I64)
+    d = dev_feats.shape[1]
+    out = np.zeros((len(node_id), d), dtype=dev_feats.dtype)
+    p = np.asarray(feat_pos_map, dtype=I64)[node_id]
+    hit = p >= 0
+    miss = p < -1
+    out[hit] = dev_feats[p[hit]]
+    out[miss] = uva_feats[encode_id(p[miss]), feat_dim_offset:feat_dim_offset + d]
+    return out
+
+
+def cpu_load_subtensor(node_id, cpu_feat_pos_map, uva_feats):
+    """CPULoadSubtensor, src/load_subtensor.cc:10-17 (the reference's own CPU
+    code): uva_feats.index_select(0, ENCODE_ID(cpu_feat_pos_map[node_id]))."""
+    pos = encode_id(np.asarray(cpu_feat_pos_map, dtype=I64)[np.asarray(node_id, dtype=I64)])
+    return uva_feats[pos]
+
+
+# ------------------------------------------------------------- feature shuffle
+def feat_shuffle(inputs, send_offsets, recv_offsets, permutations, feat_dim, fwd):
+    """FeatShuffle, src/feat_shuffle.cc:9-30, for all ranks at once.
+    fwd: out = alltoall(flatten(in))[permutation]; bwd: scatter rows by
+    permutation (index_select_backward, :13-16), then alltoall."""
+    n = len(inputs)
+    if fwd:
+        flat = [np.asarray(x).reshape(-1) for x in inputs]
+    else:
+        flat = []
+        for r in range(n):
+            x = np.asarray(inputs[r])
+            tmp = np.zeros_like(x)
+            np.add.at(tmp, np.asarray(permutations[r], dtype=I64), x)
+            flat.append(tmp.reshape(-1))
+    outs = alltoall(flat, send_offsets, recv_offsets, expand=feat_dim)
+    outs = [o.reshape(-1, feat_dim) for o in outs]
+    if fwd:
+        outs = [outs[r][np.asarray(permutations[r], dtype=I64)] for r in range(n)]
+    return outs
+
+
+# -------------------------------------------------------------- SpMM / SDDMM
+def _segments(coo_offset, num_edges):
+    coo_offset = np.asarray(coo_offset, dtype=I64)
+    # cub::UpperBound(coo_off, len, e) - 1, src/cuda/spmm.cu:20
+    return np.searchsorted(coo_offset, np.arange(num_edges, dtype=I64), side="right") - 1
+
+
+def spmm_sum(op, row, col, inp, edata, coo_offset, input_offset, output_offset, acc=np.float64):
+    """CopyUSumKernel / CopyESumKernel / UMulESumKernel, src/cuda/spmm.cu:7-83.
+    op: 'copy_u', 'copy_e', 'u_mul_e', or 'u_add_e' (what the reference's
+    UMulESum kernel computes, :78). Accumulates in `acc`, returns that dtype."""
+    row = np.asarray(row, dtype=I64)
+    col = np.asarray(col, dtype=I64)
+    E = len(row)
+    seg = _segments(coo_offset, E)
+    n_out = int(np.asarray(output_offset)[-1])
+    ref = inp if inp is not None else edata
+    D = ref.shape[1]
+    out = np.zeros((n_out, D), dtype=acc)
+    if E == 0:
+        return out
+    dst = np.asarray(output_offset, dtype=I64)[seg] + col
+    if op != "copy_e":
+        src = np.asarray(input_offset, dtype=I64)[seg] + row
+        val = inp[src].astype(acc)
+    if op == "copy_e":
+        val = edata.astype(acc)
+    elif op in ("u_mul_e", "u_add_e"):
+        e = edata.astype(acc)
+        if e.shape[1] != D:
+            e = np.repeat(e, D // e.shape[1], axis=1)
+        val = val * e if op == "u_mul_e" else val + e
+    np.add.at(out, dst, val)
+    return out
+
+
+def sddmm(op, row, col, lhs, rhs, coo_offset, lhs_offset, rhs_offset, acc=np.float64):
+    """UAddVKernel / UMulVKernel, src/cuda/sddmm.cu:7-59: out[e] =
+    lhs[lhs_off[k]+row[e]] (+|*) rhs[rhs_off[k]+col[e]]."""
+    row = np.asarray(row, dtype=I64)
+    col = np.asarray(col, dtype=I64)
+    seg = _segments(coo_offset, len(row))
+    a = lhs[np.asarray(lhs_offset, dtype=I64)[seg] + row].astype(acc)
+    b = rhs[np.asarray(rhs_offset, dtype=I64)[seg] + col].astype(acc)
+    return a + b if op == "u_add_v" else a * b
+
+
+# ------------------------------------------------------- synthetic generators
+def rmat_edges(seed, first_edge, num_edges, scale, num_nodes, a=0.57, b=0.19, c=0.19):
+    """The benchmark's R-MAT generator (counter-based; same stream as the GPU
+    setup kernel): per edge and attempt, one Philox word per level picks the
+    quadrant; endpoints >= num_nodes are redrawn (at most 64 attempts)."""
+    f32 = np.float32
+    a_, ab, abc = f32(a), f32(a) + f32(b), f32(a) + f32(b) + f32(c)
+    e = np.arange(first_edge, first_edge + num_edges, dtype=U64)
+    src = np.zeros(num_edges, dtype=I64)
+    dst = np.zeros(num_edges, dtype=I64)
+    todo = np.ones(num_edges, dtype=bool)
+    for attempt in range(64):
+        if not todo.any():
+            break
+        ee = e[todo]
+        s = np.zeros(len(ee), dtype=I64)
+        d = np.zeros(len(ee), dtype=I64)
+        for lvl in range(0, scale, 4):
+            w = philox4x32_10(ee & _MASK, ee >> U64(32), lvl >> 2, attempt, seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
+            for t in range(4):
+                if lvl + t >= scale:
+                    break
+                u = (w[t] >> U32(8)).astype(f32) * f32(1.0 / 16777216.0)
+                sbit = (u >= ab).astype(I64)
+                dbit = (((u >= a_) & (u < ab)) | (u >= abc)).astype(I64)
+                s = (s << 1) | sbit
+                d = (d << 1) | dbit
+        ok = (s < num_nodes) & (d < num_nodes)
+        idx = np.flatnonzero(todo)
+        if attempt == 63:
+            s, d, ok = s % num_nodes, d % num_nodes, np.ones_like(ok)
+        src[idx[ok]] = s[ok]
+        dst[idx[ok]] = d[ok]
+        # a rejected draw still leaves its (reduced) value behind, as the kernel does
+        src[idx[~ok]] = s[~ok] % num_nodes
+        dst[idx[~ok]] = d[~ok] % num_nodes
+        todo[idx[ok]] = False
+    return src, dst
+
+
+def csc_from_edges(src, dst, num_nodes, add_self_loops=True):
+    """CSC (indptr over destinations, indices = sources) with rows sorted by
+    source id; one self loop per node is appended first, like the reference's
+    dataset preparation (scripts/load_data.py:71), so every degree is >= 1."""
+    src = np.asarray(src, dtype=I64)
+    dst = np.asarray(dst, dtype=I64)
+    if add_self_loops:
+        loop = np.arange(num_nodes, dtype=I64)
+        src = np.concatenate([src, loop])
+        dst = np.concatenate([dst, loop])
+    bits = max(1, int(num_nodes - 1).bit_length())
+    key = (dst.astype(U64) << U64(bits)) | src.astype(U64)
+    key.sort()
+    indices = (key & U64((1 << bits) - 1)).astype(I64)
+    d = (key >> U64(bits)).astype(I64)
+    indptr = np.zeros(num_nodes + 1, dtype=I64)
+    np.cumsum(np.bincount(d, minlength=num_nodes), out=indptr[1:])
+    return indptr, indices
