@@ -468,13 +468,13 @@ def _spmm(op, coo_row, coo_col, inp, edata, coo_offset, input_offset, output_off
     if edata is not None:
         edata = _need_cuda(edata, "edata", dtype=ref.dtype)
     out_num = int(output_offset[-1].item())  # host read, as in src/spmm.cc:13
-    feat_dim = ref.shape[1] if inp is not None or edata is None else edata.shape[1]
-    if inp is not None:
-        feat_dim = inp.shape[1]
+    num_edges = coo_row.numel()
+    feat_dim = inp.shape[1] if inp is not None else edata.numel() // max(num_edges, 1)
+    # edata may be [E, D], [E, H] or [E, H, 1]: one value per column or per head
+    edim = edata.numel() // num_edges if edata is not None and num_edges else feat_dim
     out = torch.empty((out_num, feat_dim), dtype=ref.dtype, device=ref.device)
     nbytes = lib.apt_spmm_workspace_bytes(out_num)
     ws = STATE.workspace("spmm", nbytes)
-    edim = edata.numel() // max(coo_row.numel(), 1) if edata is not None and coo_row.numel() else feat_dim
     check(lib.apt_spmm_sum(op, _DTYPE_CODE[ref.dtype], _ptr(coo_row), _ptr(coo_col), coo_row.numel(),
                            _ptr(inp), _ptr(edata), int(edim), int(feat_dim), _ptr(coo_offset),
                            _ptr(input_offset), _ptr(output_offset), coo_offset.numel() - 1, out_num,

@@ -1,0 +1,82 @@
+"""The whole sampled mini-batch (NP strategy, one rank) against the oracle
+composed stage by stage, and the row movers."""
+import numpy as np
+import pytest
+import torch
+
+import apt_b200
+from apt_b200 import ops
+from oracle import oracle as orc
+from tests.gpu_util import dev, host, install_graph, reset_world
+from tests.helpers import feature_setup, small_graph
+
+pytestmark = pytest.mark.gpu
+I64 = np.int64
+
+
+def test_np_minibatch_matches_oracle():
+    n, indptr, indices = small_graph(scale=13, edge_factor=8)
+    install_graph(indptr, indices)
+    reset_world(1, 0)
+    ops.register_min_vids(torch.tensor([0, n]))
+    rng = np.random.default_rng(3)
+    feats, uva, devf, cached_idx, local_idx, pos_map, cpu_map = feature_setup(n, 128, 0.25, rng)
+    ops.cache_feats_shared(n, torch.from_numpy(uva).pin_memory(), dev(devf), torch.from_numpy(cached_idx),
+                           torch.from_numpy(local_idx), 0)
+    fanouts = [15, 10, 5]
+    seeds = rng.permutation(n)[:256].astype(I64)
+    ops.set_sampling(key=31337, call_id=0)
+    sampler = apt_b200.MixedNeighborSampler(0, fanouts)
+    input_nodes, output_nodes, blocks, perm, send_off, recv_off, inverse_idx = sampler.sample(None, dev(seeds))
+    x = ops.load_subtensor(input_nodes)
+
+    # oracle: same loop as python/npc/sampler.py:132-156
+    graph = (None, None, None, indptr, indices)
+    cur, call, want_blocks = seeds, 0, []
+    for f in reversed(fanouts[1:]):
+        nbr = orc.sample_csc_fanout(cur, f, *graph, key=31337, call_id=call)
+        call += 1
+        uniq, rel = orc.relabel_csc(cur, nbr)
+        want_blocks.insert(0, (rel, np.repeat(np.arange(len(cur)), f), uniq))
+        cur = uniq
+    res = orc.np_sample_and_shuffle([cur], fanouts[0], np.array([0, n]), graph, key=31337, call_id=call)[0]
+    uniq, rel = orc.relabel_csc(res[0], res[1])
+    want_blocks.insert(0, (rel, np.repeat(np.arange(len(res[0])), fanouts[0]), uniq))
+    assert len(blocks) == 3
+    for b, (wr, wc, wu) in zip(blocks, want_blocks):
+        assert np.array_equal(host(b.coo_row), wr) and np.array_equal(host(b.coo_col), wc)
+        assert np.array_equal(host(b.src_ids), wu) and b.num_src == len(wu)
+    assert np.array_equal(host(input_nodes), want_blocks[0][2])
+    assert np.array_equal(host(perm), res[2]) and np.array_equal(host(inverse_idx), res[5])
+    assert np.array_equal(send_off.numpy(), res[3]) and np.array_equal(recv_off.numpy(), res[4])
+    assert np.array_equal(host(x), orc.load_subtensor(want_blocks[0][2], pos_map, devf, uva))
+    # every sampled edge exists (the reference's debug hook, python/npc/sampler.py:126-130)
+    b = blocks[-1]
+    src = host(b.src_ids)[host(b.coo_row)]
+    dst = seeds[host(b.coo_col)]
+    for s_, d_ in list(zip(src, dst))[:200]:
+        assert s_ in indices[indptr[d_]:indptr[d_ + 1]]
+    # aggregation over the outermost block equals the dense definition
+    h = torch.randn((blocks[0].num_src, 64), device="cuda")
+    off = [torch.tensor(v, device="cuda") for v in ([0, blocks[0].coo_row.numel()], [0, blocks[0].num_src], [0, blocks[0].num_dst])]
+    agg = ops.spmm_copy_u_sum(blocks[0].coo_row, blocks[0].coo_col, h, *off)
+    ref = h[blocks[0].coo_row].view(blocks[0].num_dst, fanouts[0], 64).sum(1)
+    assert torch.allclose(agg, ref, rtol=1e-5, atol=1e-5)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("row_elems,dtype", [(256, torch.float32), (1024, torch.float16), (3, torch.float32), (1, torch.bfloat16)])
+def test_row_movers(row_elems, dtype):
+    g = torch.Generator(device="cuda").manual_seed(row_elems)
+    x = torch.randn((5000, row_elems), generator=g, device="cuda").to(dtype)
+    idx = torch.randint(0, 5000, (12345,), generator=g, device="cuda")
+    assert torch.equal(ops.rows_gather(x, idx), x[idx])
+    p = torch.randperm(5000, generator=g, device="cuda")
+    y = ops.rows_scatter(x, p, 5000)
+    ref = torch.empty_like(x)
+    ref[p] = x
+    assert torch.equal(y, ref)
+    z = ops.rows_scatter(x[:100], p[:100], 5000)
+    ref = torch.zeros_like(x)
+    ref[p[:100]] = x[:100]
+    assert torch.equal(z, ref)

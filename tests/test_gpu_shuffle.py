@@ -1,0 +1,226 @@
+"""GPU parity of the seed shuffle, the feature shuffle and the peer-to-peer
+all-to-all. Several ranks are emulated on one GPU as inbox contexts wired to
+each other by pointer; all pushes are issued before any wait, so no kernel
+ever waits for one that has not been launched."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import apt_b200
+from apt_b200 import _lib, ops
+from apt_b200._lib import check, lib
+from oracle import oracle as orc
+from tests.gpu_util import dev, host, install_graph, reset_world
+from tests.helpers import small_graph
+
+pytestmark = pytest.mark.gpu
+I64 = np.int64
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class Ranks:
+    """N inbox contexts in one process, each attached to the others by pointer."""
+
+    def __init__(self, ws, region_bytes=1 << 20):
+        self.ws = ws
+        self.ctx = []
+        for r in range(ws):
+            c = ctypes.c_void_p()
+            check(lib.apt_p2p_create(r, ws, region_bytes, ctypes.byref(c), None))
+            self.ctx.append(c)
+        for r in range(ws):
+            for q in range(ws):
+                if q != r:
+                    check(lib.apt_p2p_attach_ptr(self.ctx[r], q, lib.apt_p2p_local_base(self.ctx[q])))
+        self.status = torch.zeros(2, dtype=torch.int32, device="cuda")
+
+    def alltoall(self, srcs, send_offsets, row_bytes, src_index=None, index_is_dest=0):
+        """One all-to-all of all ranks; returns the per-rank received counts (device tensors)."""
+        counts = []
+        for r in range(self.ws):
+            off = dev(np.asarray(send_offsets[r], dtype=I64))
+            idx = None if src_index is None else src_index[r].data_ptr()
+            n = int(send_offsets[r][-1])
+            check(lib.apt_p2p_push(self.ctx[r], srcs[r].data_ptr() if srcs[r].numel() else None, idx, index_is_dest,
+                                   off.data_ptr(), n, row_bytes, self.status.data_ptr(), _stream()))
+        for r in range(self.ws):
+            c = torch.empty(self.ws, dtype=torch.int64, device="cuda")
+            check(lib.apt_p2p_wait(self.ctx[r], c.data_ptr(), self.status.data_ptr(), 0, _stream()))
+            counts.append(c)
+        return counts
+
+    def pull(self, r, counts, dst, row_bytes, index=None, index_is_source=0, num_dst_rows=0):
+        total = int(counts.sum().item())
+        n = num_dst_rows if index is not None and index_is_source else total
+        check(lib.apt_p2p_pull(self.ctx[r], counts.data_ptr(), None if index is None else index.data_ptr(),
+                               index_is_source, n, max(n, total), row_bytes, dst.data_ptr() if dst.numel() else None,
+                               _stream()))
+
+    def close(self):
+        for c in self.ctx:
+            lib.apt_p2p_destroy(c)
+
+
+@pytest.mark.parametrize("ws", [1, 2, 4, 8])
+@pytest.mark.parametrize("expand", [1, 16])
+def test_p2p_alltoall_reference_cases(ws, expand):
+    # the closed-form cases of the reference's tests/test_alltoall.cc:24-99
+    k, b = 7, 100
+    send_sizes = [[k * (rank - r) ** 2 + b for r in range(ws)] for rank in range(ws)]
+    recv_sizes = [[k * (r - rank) ** 2 + b for r in range(ws)] for rank in range(ws)]
+    send_off = [np.cumsum(s) for s in send_sizes]
+    ranks = Ranks(ws)
+    try:
+        for rep in range(3):  # three epochs: both parities of the inbox are reused
+            srcs = [torch.full((int(send_off[r][-1]) * expand,), r + 10 * rep, dtype=torch.int64, device="cuda")
+                    for r in range(ws)]
+            counts = ranks.alltoall(srcs, send_off, 8 * expand)
+            for r in range(ws):
+                assert host(counts[r]).tolist() == recv_sizes[r]
+                out = torch.empty(sum(recv_sizes[r]) * expand, dtype=torch.int64, device="cuda")
+                ranks.pull(r, counts[r], out, 8 * expand)
+                want = np.concatenate([np.full(recv_sizes[r][q] * expand, q + 10 * rep, dtype=I64) for q in range(ws)])
+                assert np.array_equal(host(out), want)
+        assert int(ranks.status[0].item()) == 0
+    finally:
+        ranks.close()
+
+
+@pytest.mark.parametrize("ws", [2, 4, 8])
+@pytest.mark.parametrize("dtype,D", [(torch.float32, 256), (torch.bfloat16, 256), (torch.float16, 1024), (torch.float32, 5)])
+def test_p2p_seed_and_feature_shuffle_matches_oracle(ws, dtype, D):
+    rng = np.random.default_rng(ws * 100 + D)
+    n_nodes = 4000
+    mv = np.linspace(0, n_nodes, ws + 1).astype(I64)
+    seeds = [rng.integers(0, n_nodes, 300 + 17 * r).astype(I64) for r in range(ws)]
+    want = orc.shuffle_seeds(seeds, mv)
+    table = torch.randn((n_nodes, D), device="cuda").to(dtype)
+    esz = table.element_size()
+    ranks = Ranks(ws, region_bytes=4 << 20)
+    reset_world(ws, 0)
+    try:
+        ops.register_min_vids(torch.from_numpy(mv))
+        parts = []
+        for r in range(ws):
+            apt_b200.STATE.rank = r
+            parts.append(ops._bucket(dev(seeds[r])))     # sorted, perm, sizes, offsets
+        # --- seed exchange (ShuffleSeeds, src/sampling.cc:159-193)
+        counts = ranks.alltoall([p[0] for p in parts], [host(p[3]) for p in parts], 8)
+        recv = []
+        for r in range(ws):
+            out = torch.empty(int(counts[r].sum().item()), dtype=torch.int64, device="cuda")
+            ranks.pull(r, counts[r], out, 8)
+            recv.append(out)
+            assert np.array_equal(host(out), want[r][0])
+            assert np.array_equal(host(parts[r][1]), want[r][1])
+            assert np.array_equal(np.cumsum(host(counts[r])), want[r][2])
+            assert np.array_equal(host(parts[r][3]), want[r][3])
+        # --- feature shuffle forward (FeatShuffle fwd, src/feat_shuffle.cc:9-30)
+        inputs = [table[recv[r]] for r in range(ws)]
+        send_off = [want[r][2] for r in range(ws)]
+        counts_f = ranks.alltoall(inputs, send_off, D * esz)
+        outs = []
+        for r in range(ws):
+            out = torch.empty((len(seeds[r]), D), dtype=dtype, device="cuda")
+            ranks.pull(r, counts_f[r], out, D * esz, index=parts[r][1], index_is_source=1, num_dst_rows=len(seeds[r]))
+            outs.append(out)
+            assert torch.equal(out, table[dev(seeds[r])])   # rows come back in the asker's seed order
+        # --- backward: rows scattered by permutation travel back (fwd_flag = 0)
+        grads = [torch.randn((len(seeds[r]), D), device="cuda").to(dtype) for r in range(ws)]
+        recv_off_b = [want[r][3] for r in range(ws)]
+        counts_b = ranks.alltoall(grads, recv_off_b, D * esz, src_index=[p[1] for p in parts], index_is_dest=1)
+        want_b = orc.feat_shuffle([host(g) for g in grads], recv_off_b, send_off, [want[r][1] for r in range(ws)], D, fwd=False)
+        for r in range(ws):
+            out = torch.empty((len(want[r][0]), D), dtype=dtype, device="cuda")
+            ranks.pull(r, counts_b[r], out, D * esz)
+            assert np.array_equal(host(out), want_b[r])
+        assert int(ranks.status[0].item()) == 0
+    finally:
+        reset_world()
+        ranks.close()
+
+
+def test_p2p_wait_times_out_with_a_status_not_a_hang():
+    # rank 1 never pushes: rank 0's wait must give up after its bound and report it
+    ranks = Ranks(2)
+    try:
+        src = torch.arange(8, dtype=torch.int64, device="cuda")
+        off = dev(np.array([4, 8], dtype=I64))
+        check(lib.apt_p2p_push(ranks.ctx[0], src.data_ptr(), None, 0, off.data_ptr(), 8, 8, ranks.status.data_ptr(), _stream()))
+        c = torch.full((2,), -1, dtype=torch.int64, device="cuda")
+        check(lib.apt_p2p_wait(ranks.ctx[0], c.data_ptr(), ranks.status.data_ptr(), 50_000_000, _stream()))  # 50 ms
+        torch.cuda.synchronize()
+        assert host(c).tolist() == [4, 0]
+        assert int(ranks.status[0].item()) & _lib.FLAG_PEER_TIMEOUT
+        # the context stays usable
+        assert int((src + 1).sum().item()) == 36
+    finally:
+        ranks.close()
+
+
+def test_p2p_region_overflow_is_flagged():
+    ranks = Ranks(1, region_bytes=256)
+    try:
+        src = torch.arange(100, dtype=torch.int64, device="cuda")
+        off = dev(np.array([100], dtype=I64))
+        check(lib.apt_p2p_push(ranks.ctx[0], src.data_ptr(), None, 0, off.data_ptr(), 100, 8, ranks.status.data_ptr(), _stream()))
+        c = torch.empty(1, dtype=torch.int64, device="cuda")
+        check(lib.apt_p2p_wait(ranks.ctx[0], c.data_ptr(), ranks.status.data_ptr(), 0, _stream()))
+        torch.cuda.synchronize()
+        assert int(ranks.status[0].item()) & _lib.FLAG_TABLE_FULL
+        assert host(c).tolist() == [32]
+    finally:
+        ranks.close()
+
+
+@pytest.mark.parametrize("backend", ["local", "p2p"])
+def test_operator_layer_single_rank(backend):
+    """shuffle_seeds / np_sample_and_shuffle / feat_shuffle / alltoall through the
+    operator layer with one rank; with the p2p backend rows loop through the inbox."""
+    from apt_b200.exchange import LocalExchange, P2PExchange
+
+    n, indptr, indices = small_graph(scale=11)
+    install_graph(indptr, indices)
+    reset_world(1, 0)
+    s = apt_b200.STATE
+    ex = LocalExchange(s) if backend == "local" else P2PExchange.__new__(P2PExchange)
+    if backend == "p2p":
+        c = ctypes.c_void_p()
+        check(lib.apt_p2p_create(0, 1, 8 << 20, ctypes.byref(c), None))
+        P2PExchange.__init__(ex, s, 0, ctx=c)
+    s.exchange = ex
+    try:
+        ops.register_min_vids(torch.tensor([0, n]))
+        rng = np.random.default_rng(1)
+        seeds = rng.integers(0, n, 1500).astype(I64)
+        ops.set_sampling(key=9, call_id=0)
+        res = ops.np_sample_and_shuffle(dev(seeds), 10)
+        want = orc.np_sample_and_shuffle([seeds], 10, np.array([0, n]), (None, None, None, indptr, indices), key=9, call_id=0)[0]
+        for g, w in zip(res, want):
+            assert np.array_equal(host(g), w)
+        assert not res[3].is_cuda and not res[4].is_cuda and res[2].is_cuda
+        recv, perm, recv_off, dev_off = ops.shuffle_seeds(dev(seeds))
+        assert np.array_equal(host(recv)[host(perm)], seeds)
+        D = 64
+        h = torch.randn((res[0].numel(), D), device="cuda")
+        x = ops.rows_gather(h, res[5])                       # h[inverse_idx]
+        y = ops.feat_shuffle(x, res[3], res[4], res[2], D, 1)
+        assert torch.equal(y, h[res[5]][res[2]])
+        g = torch.randn_like(y)
+        gb = ops.feat_shuffle(g, res[4], res[3], res[2], D, 0)
+        ref = torch.zeros_like(g)
+        ref.index_add_(0, res[2], g)
+        assert torch.equal(gb, ref)
+        out = torch.empty(40, dtype=torch.int64, device="cuda")
+        ops.alltoall(torch.arange(40, device="cuda"), out, torch.tensor([10]), torch.tensor([10]), 4, 0)
+        assert torch.equal(out, torch.arange(40, device="cuda"))
+        ops.check_status()
+    finally:
+        if backend == "p2p":
+            ex.close()
+        reset_world()
