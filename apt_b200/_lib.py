@@ -58,7 +58,7 @@ PROTOTYPES = {
     "apt_rmat_edges": (c_int, [c_uint64, c_int64, c_int64, c_int, c_int64, c_float, c_float, c_float, P, P, P]),
     "apt_sort_u64_temp_bytes": (c_size_t, [c_int64]),
     "apt_sort_u64": (c_int, [P, P, c_int64, P, c_size_t, c_int, P]),
-    "apt_normal_rows": (c_int, [c_uint64, c_int64, c_int64, c_int64, c_int, P, P]),
+    "apt_normal_rows": (c_int, [c_uint64, c_int64, P, c_int64, c_int64, c_int, P, P]),
 }
 
 for _name, (_res, _args) in PROTOTYPES.items():

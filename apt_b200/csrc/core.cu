@@ -33,15 +33,28 @@ static std::mutex g_prof_mu;
 static std::vector<ProfRec> g_prof;
 static const size_t kProfMax = 1 << 16;
 
+// Events are pooled: after a read they go back to the free list, so a steady
+// loop creates no events.
+static std::vector<cudaEvent_t> g_free_events;
+
+static bool take_event(cudaEvent_t* ev) {
+  if (!g_free_events.empty()) {
+    *ev = g_free_events.back();
+    g_free_events.pop_back();
+    return true;
+  }
+  return cudaEventCreate(ev) == cudaSuccess;
+}
+
 ProfScope::ProfScope(const char* t, cudaStream_t s) : tag(t), stream(s), slot(-1) {
   if (!g_prof_on.load(std::memory_order_relaxed)) return;
   std::lock_guard<std::mutex> lk(g_prof_mu);
   if (g_prof.size() >= kProfMax) return;
   ProfRec r;
   r.tag = t;
-  if (cudaEventCreate(&r.beg) != cudaSuccess) return;
-  if (cudaEventCreate(&r.end) != cudaSuccess) {
-    cudaEventDestroy(r.beg);
+  if (!take_event(&r.beg)) return;
+  if (!take_event(&r.end)) {
+    g_free_events.push_back(r.beg);
     return;
   }
   cudaEventRecord(r.beg, s);
@@ -82,8 +95,8 @@ int apt_profile_read(const char* tag, double* total_ms, int64_t* launches) {
     float t = 0.f;
     cudaError_t e = cudaEventSynchronize(r.end);
     if (e == cudaSuccess) e = cudaEventElapsedTime(&t, r.beg, r.end);
-    cudaEventDestroy(r.beg);
-    cudaEventDestroy(r.end);
+    apt::g_free_events.push_back(r.beg);
+    apt::g_free_events.push_back(r.end);
     if (e != cudaSuccess) {
       apt::set_error("apt_profile_read(%s): %s", tag, cudaGetErrorString(e));
       apt::g_prof.swap(keep);

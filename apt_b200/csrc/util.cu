@@ -55,15 +55,15 @@ template <> __device__ __forceinline__ __half cast_out<__half>(float x) { return
 // uses block col>>2 of row's stream, word pair by col&3.
 template <typename T>
 __global__ void __launch_bounds__(256)
-k_normal_rows(uint32_t k0, uint32_t k1, int64_t first_row, int64_t num_rows, int64_t dim,
-              T* __restrict__ out) {
+k_normal_rows(uint32_t k0, uint32_t k1, int64_t first_row, const int64_t* __restrict__ row_ids,
+              int64_t num_rows, int64_t dim, T* __restrict__ out) {
   const int64_t quads = (dim + 3) / 4;
   const int64_t total = num_rows * quads;
   int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (; idx < total; idx += stride) {
     const int64_t r = idx / quads, q = idx - r * quads;
-    const uint64_t row = (uint64_t)(first_row + r);
+    const uint64_t row = (uint64_t)(row_ids ? row_ids[r] : first_row + r);
     const Philox4 p = philox4x32_10((uint32_t)row, (uint32_t)(row >> 32), (uint32_t)q, 0x6e6f726du, k0, k1);
     float z[4];
 #pragma unroll
@@ -116,8 +116,8 @@ extern "C" int apt_sort_u64(const uint64_t* keys_in, uint64_t* keys_out, int64_t
   return APT_OK;
 }
 
-extern "C" int apt_normal_rows(uint64_t seed, int64_t first_row, int64_t num_rows, int64_t dim,
-                               int dtype, void* out, void* stream) {
+extern "C" int apt_normal_rows(uint64_t seed, int64_t first_row, const int64_t* row_ids,
+                               int64_t num_rows, int64_t dim, int dtype, void* out, void* stream) {
   using namespace apt;
   APT_CHECK_ARG(num_rows >= 0 && dim >= 1, "apt_normal_rows: bad sizes");
   APT_CHECK_ARG(dtype >= APT_F32 && dtype <= APT_F16, "apt_normal_rows: dtype %d", dtype);
@@ -127,9 +127,9 @@ extern "C" int apt_normal_rows(uint64_t seed, int64_t first_row, int64_t num_row
   const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
   const int grid = wave_grid(ceil_div(num_rows * ((dim + 3) / 4), 256), 8);
   switch (dtype) {
-    case APT_F32: APT_LAUNCH(k_normal_rows<float>, grid, 256, 0, s, k0, k1, first_row, num_rows, dim, (float*)out); break;
-    case APT_BF16: APT_LAUNCH(k_normal_rows<__nv_bfloat16>, grid, 256, 0, s, k0, k1, first_row, num_rows, dim, (__nv_bfloat16*)out); break;
-    default: APT_LAUNCH(k_normal_rows<__half>, grid, 256, 0, s, k0, k1, first_row, num_rows, dim, (__half*)out); break;
+    case APT_F32: APT_LAUNCH(k_normal_rows<float>, grid, 256, 0, s, k0, k1, first_row, row_ids, num_rows, dim, (float*)out); break;
+    case APT_BF16: APT_LAUNCH(k_normal_rows<__nv_bfloat16>, grid, 256, 0, s, k0, k1, first_row, row_ids, num_rows, dim, (__nv_bfloat16*)out); break;
+    default: APT_LAUNCH(k_normal_rows<__half>, grid, 256, 0, s, k0, k1, first_row, row_ids, num_rows, dim, (__half*)out); break;
   }
   return APT_OK;
 }

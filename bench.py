@@ -1,0 +1,406 @@
+"""Benchmark of the mini-batch data path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One step = one mini-batch per GPU of the papers-shaped NPC run: three-hop
+fanout sampling (the outermost hop at the owner of each frontier node),
+relabelling of every hop, the seed shuffle, and the cache-aware gather of the
+input features. The printed JSON line carries
+  value      mini-batches/s over all GPUs, seeds already resident in HBM
+  e2e        the same through host buffers: seeds copied from pinned host
+             memory every step and a digest of the gathered rows read back
+  roofline   the HBM-bound gather kernel (cache hits), timed with CUDA events
+             on its own stream inside the timed region
+  roofline_link  the host-link-bound gather kernel (cache misses)
+  cpu_baseline   the C restatement of the path (oracle/) on the host cores
+``--impl reference`` times that CPU restatement alone (the reference has no CPU
+implementation of its own beyond the gather, and cannot be built here).
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "sampled+gathered mini-batches/sec (whole box)"
+UNIT = "mini-batches/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="c1_papers_np")
+    ap.add_argument("--impl", default="apt_b200", choices=["apt_b200", "reference"])
+    ap.add_argument("--cpu-batches", type=int, default=12, help="batches of the CPU-baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of this rank's GPU during the timed region."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                p = [x.strip() for x in line.split(",")]
+                if len(p) < 9:
+                    continue
+                try:
+                    sm.append(float(p[1]))
+                    smax.append(float(p[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, p[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def batches_of(train_ids, batch, count, offset=0):
+    """`count` consecutive seed batches out of the rank's training ids (wrapping)."""
+    n = train_ids.numel()
+    out = []
+    for i in range(count):
+        lo = ((offset + i) * batch) % max(n - batch + 1, 1)
+        out.append(train_ids[lo:lo + batch].contiguous())
+    return out
+
+
+# ------------------------------------------------------------------ CPU baseline
+class CpuPath:
+    """One mini-batch of the same path on the host cores with the C restatement
+    (oracle/apt_oracle.c): every hop's sampling and relabelling, the owner
+    bucketing + sorted unique of the outermost hop, and the reference's CPU
+    gather (host table only, src/load_subtensor.cc:10-17)."""
+
+    def __init__(self, inst):
+        import numpy as np
+
+        so = os.path.join(ROOT, "oracle", "libapt_oracle.so")
+        if not os.path.exists(so):
+            subprocess.run(["make", "-C", os.path.join(ROOT, "oracle")], check=True, capture_output=True)
+        self.lib = ctypes.CDLL(so)
+        self.lib.oracle_relabel.restype = ctypes.c_int64
+        self.lib.oracle_unique_sorted.restype = ctypes.c_int64
+        self.np = np
+        self.w = inst.workload
+        self.indptr = inst.indptr.cpu().numpy()
+        self.indices = inst.indices.cpu().numpy()
+        self.feats = inst.host_feats.view(torch.uint8).numpy() if inst.host_feats.dtype == torch.bfloat16 \
+            else inst.host_feats.numpy()
+        self.row_bytes = inst.host_feats.shape[1] * inst.host_feats.element_size()
+        n = self.w.num_nodes
+        self.pos_map = -np.arange(n, dtype=np.int64) - 2      # every row in the host table
+        self.min_vids = inst.min_vids.numpy().astype(np.int64)
+        self.cores = os.cpu_count()
+
+    @staticmethod
+    def _p(a):
+        return a.ctypes.data_as(ctypes.c_void_p)
+
+    def _sample(self, seeds, fanout, call_id):
+        np = self.np
+        out = np.empty(len(seeds) * fanout, dtype=np.int64)
+        self.lib.oracle_sample(self._p(seeds), ctypes.c_int64(len(seeds)), fanout, None, None, None,
+                               self._p(self.indptr), self._p(self.indices), ctypes.c_uint64(7777777),
+                               ctypes.c_uint32(call_id), self._p(out))
+        return out
+
+    def _relabel(self, seeds, nbrs):
+        np = self.np
+        uniq = np.empty(len(seeds) + len(nbrs), dtype=np.int64)
+        rel = np.empty(len(nbrs), dtype=np.int64)
+        u = self.lib.oracle_relabel(self._p(seeds), ctypes.c_int64(len(seeds)), self._p(nbrs),
+                                    ctypes.c_int64(len(nbrs)), self._p(uniq), self._p(rel))
+        return uniq[:u], rel
+
+    def batch(self, seeds):
+        np = self.np
+        cur = np.ascontiguousarray(seeds, dtype=np.int64)
+        call = 0
+        for f in reversed(self.w.fanouts[1:]):
+            nbr = self._sample(cur, f, call)
+            call += 1
+            cur, _ = self._relabel(cur, nbr)
+        ws = len(self.min_vids) - 1
+        sorted_ids, perm = np.empty_like(cur), np.empty_like(cur)
+        sizes, offs = np.empty(ws, dtype=np.int64), np.empty(ws, dtype=np.int64)
+        self.lib.oracle_bucket(self._p(cur), ctypes.c_int64(len(cur)), self._p(self.min_vids), ws, ctypes.c_int64(0),
+                               0, 0, ws, self._p(sorted_ids), self._p(perm), self._p(sizes), self._p(offs))
+        uniq, inv = np.empty_like(cur), np.empty_like(cur)
+        u = self.lib.oracle_unique_sorted(self._p(sorted_ids), ctypes.c_int64(len(cur)), self._p(uniq), self._p(inv))
+        uniq = uniq[:u]
+        nbr = self._sample(uniq, self.w.fanouts[0], call)
+        inputs, _ = self._relabel(uniq, nbr)
+        out = np.empty((len(inputs), self.row_bytes), dtype=np.uint8)
+        self.lib.oracle_gather(self._p(inputs), ctypes.c_int64(len(inputs)), self._p(self.pos_map), None,
+                               ctypes.c_int64(self.row_bytes), self._p(self.feats), ctypes.c_int64(self.row_bytes),
+                               ctypes.c_int64(0), self._p(out))
+        return len(inputs)
+
+    def time(self, seed_batches, warmup=1):
+        for b in seed_batches[:warmup]:
+            self.batch(b)
+        t0 = time.perf_counter()
+        rows = 0
+        for b in seed_batches[warmup:]:
+            rows += self.batch(b)
+        dt = time.perf_counter() - t0
+        n = len(seed_batches) - warmup
+        return n / dt, dt, rows / max(n, 1)
+
+
+# ------------------------------------------------------------------------- main
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != max(args.gpus, 1) and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if args.impl == "reference" and rank != 0:
+        return  # the CPU arm runs on rank 0 alone
+
+    torch.cuda.set_device(local_rank)
+    if world > 1 and args.impl != "reference":
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    import apt_b200
+    from apt_b200 import ops, synthetic
+    from apt_b200._lib import lib
+
+    ws_eff = 1 if args.impl == "reference" else world
+    w = synthetic.WORKLOADS[args.workload]
+    ops.init(rank if ws_eff > 1 else 0, local_rank, ws_eff, ops.nccl_get_unique_id(), ws_eff)
+    t_setup = time.time()
+    inst = synthetic.install(w, rank if ws_eff > 1 else 0, ws_eff)
+    torch.cuda.synchronize()
+    setup_s = time.time() - t_setup
+    esz = inst.host_feats.element_size()
+    row_bytes = w.feat_dim * esz
+    config = {
+        "workload": w.name, "num_nodes": w.num_nodes, "num_edges": w.num_edges, "csc_edges": inst.info["num_csc_edges"],
+        "feat_dim": w.feat_dim, "feat_dtype": w.dtype, "cached_rows_per_gpu": inst.info["num_cached_rows"],
+        "cache_policy": f"top {w.cache_frac:.0%} rows by in-degree", "fanout": w.fanouts, "seeds_per_gpu": w.batch,
+        "strategy": "NP (outermost hop sampled at the owner, random contiguous partition)",
+        "topology": "int64 CSC resident in HBM", "host_features": "pinned host memory read by the gather kernel",
+        "l2": "inputs (CSC 13.7 GB, feature tables) exceed the 126 MB L2; every step touches other rows",
+        "shuffle_backend": ops.STATE.shuffle_backend if ws_eff > 1 else "local", "setup_s": round(setup_s, 1),
+    }
+
+    if args.impl == "reference":
+        cpu = CpuPath(inst)
+        seeds = [b.cpu().numpy() for b in batches_of(inst.train_ids, w.batch, args.warmup + args.steps)]
+        rate, dt, rows = cpu.time(seeds, warmup=args.warmup)
+        line = {
+            "impl": "reference", "metric": METRIC, "value": rate, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 / rate, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int64 ids, " + w.dtype + " rows", "data": "synthetic",
+            "config": config,
+            "cpu_baseline": {"value": rate, "unit": UNIT, "cores": cpu.cores, "kind": "port",
+                             "sample": f"{args.steps} mini-batches of {w.batch} seeds on the full graph, "
+                                       f"about {rows:.0f} gathered rows each, OpenMP over all host threads"},
+            "e2e": {"value": rate, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }
+        print(json.dumps(line))
+        return
+
+    sampler = apt_b200.MixedNeighborSampler(rank, w.fanouts)
+    total = args.warmup + args.steps
+    dev_batches = batches_of(inst.train_ids, w.batch, total)
+    host_batches = [b.cpu().pin_memory() for b in batches_of(inst.train_ids, w.batch, total, offset=total)]
+
+    def step(seeds):
+        sample = sampler.sample(None, seeds)
+        x = ops.load_subtensor(sample[0])
+        return sample, x
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def reduce_max(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def reduce_sum(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    # ---- device-resident run ------------------------------------------------
+    ops.set_sampling(key=7777777, call_id=0)
+    for b in dev_batches[:args.warmup]:
+        step(b)
+    ops.check_status()
+    clocks = ClockSampler(local_rank)
+    clocks.start()
+    lib.apt_profile_enable(1)
+    lib.apt_launch_count_reset()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    kept = []
+    barrier()
+    ev0.record()
+    for b in dev_batches[args.warmup:]:
+        sample, x = step(b)
+        kept.append(sample[0])
+    ev1.record()
+    barrier()
+    launches = int(lib.apt_launch_count())
+    lib.apt_profile_enable(0)
+    clock_info = clocks.stop()
+    ms = reduce_max(ev0.elapsed_time(ev1))
+    value = world * args.steps / (ms / 1000.0)
+    ops.check_status()
+
+    def prof(tag):
+        t, n = ctypes.c_double(), ctypes.c_int64()
+        lib.apt_profile_read(tag.encode(), ctypes.byref(t), ctypes.byref(n))
+        return t.value, n.value
+
+    stage_ms = {tag: prof(tag) for tag in ("sample", "relabel", "bucket", "unique_sorted", "gather_classify",
+                                           "gather_hit", "gather_miss", "p2p_push", "p2p_wait", "p2p_pull")}
+    pos_map = ops.STATE.feat.feat_pos_map
+    rows_total = sum(int(k.numel()) for k in kept)
+    hits_total = sum(int((pos_map[k] >= 0).sum().item()) for k in kept)
+    miss_total = rows_total - hits_total
+    peak, peak_kind = peaks()
+    hit_ms, hit_n = stage_ms["gather_hit"]
+    miss_ms, miss_n = stage_ms["gather_miss"]
+    # algorithmic bytes of one hit-copy launch: each hit row read and written once, plus the 8-byte
+    # position of every requested row
+    hit_bytes = (hits_total * 2 * row_bytes + rows_total * 8) / max(hit_n, 1)
+    hit_gbs = hit_bytes / (hit_ms / max(hit_n, 1) * 1e-3) / 1e9 if hit_ms > 0 else 0.0
+    roofline = {"kernel": "k_copy_hits (gather, cache hits)", "bound": "hbm", "achieved": round(hit_gbs, 1),
+                "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(hit_gbs / peak, 4),
+                "traffic": None, "rows_per_launch": rows_total / max(hit_n, 1),
+                "hit_rows_per_launch": hits_total / max(hit_n, 1), "us_per_launch": 1000.0 * hit_ms / max(hit_n, 1)}
+    miss_bytes = miss_total * row_bytes / max(miss_n, 1)
+    miss_gbs = miss_bytes / (miss_ms / max(miss_n, 1) * 1e-3) / 1e9 if miss_ms > 0 else 0.0
+
+    # ---- measured host-link rate (pinned host -> device copy), the miss kernel's ceiling
+    probe_rows = min(w.num_nodes, (1 << 30) // row_bytes)
+    dst = torch.empty((probe_rows, w.feat_dim), dtype=inst.host_feats.dtype, device="cuda")
+    dst.copy_(inst.host_feats[:probe_rows], non_blocking=True)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    dst.copy_(inst.host_feats[:probe_rows], non_blocking=True)
+    e1.record()
+    torch.cuda.synchronize()
+    link_gbs = probe_rows * row_bytes / (e0.elapsed_time(e1) * 1e-3) / 1e9
+    del dst
+    roofline_link = {"kernel": "k_copy_miss (gather, rows from pinned host memory)", "bound": "host_link",
+                     "achieved": round(miss_gbs, 2), "peak": round(link_gbs, 2),
+                     "peak_kind": "pinned host->device copy of 1 GiB measured in this run", "unit": "GB/s",
+                     "frac": round(miss_gbs / link_gbs, 4) if link_gbs else None,
+                     "miss_rows_per_launch": miss_total / max(miss_n, 1),
+                     "us_per_launch": 1000.0 * miss_ms / max(miss_n, 1)}
+
+    # ---- end to end through host buffers --------------------------------------
+    def e2e_step(host_seeds):
+        seeds = host_seeds.to("cuda", non_blocking=True)
+        sample, x = step(seeds)
+        digest = torch.cat([x[0], x[-1]]).float().cpu()      # device -> host read of the step's result
+        return digest
+
+    for b in host_batches[:args.warmup]:
+        e2e_step(b)
+    barrier()
+    ev0.record()
+    for b in host_batches[args.warmup:]:
+        e2e_step(b)
+    ev1.record()
+    barrier()
+    ms_e2e = reduce_max(ev0.elapsed_time(ev1))
+    e2e = {"value": world * args.steps / (ms_e2e / 1000.0), "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
+           "h2d_bytes_per_step": w.batch * 8, "d2h_bytes_per_step": 2 * w.feat_dim * 4 + 64 * 4,
+           "note": "seeds come from pinned host memory; a digest (first and last gathered row) and the per-hop "
+                   "unique counts are read back; the gathered rows stay on the GPU for the model"}
+    ops.check_status()
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int64 ids, " + w.dtype + " rows", "data": "synthetic", "config": config, "clocks": clock_info,
+        "e2e": e2e, "gpu_launches": int(reduce_sum(launches)), "roofline": roofline, "roofline_link": roofline_link,
+        "per_step": {"gathered_rows": rows_total / args.steps, "cache_hit_rate": hits_total / max(rows_total, 1),
+                     "gather_gb": rows_total / args.steps * row_bytes / 1e9,
+                     "stage_ms": {k: round(v[0] / args.steps, 4) for k, v in stage_ms.items()},
+                     "stage_launches": {k: v[1] / args.steps for k, v in stage_ms.items()}},
+    }
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = CpuPath(inst)
+        seeds = [b.cpu().numpy() for b in batches_of(inst.train_ids, w.batch, args.cpu_batches + 1)]
+        rate, dt, rows = cpu.time(seeds, warmup=1)
+        line["cpu_baseline"] = {"value": rate, "unit": UNIT, "cores": cpu.cores, "kind": "port",
+                                "sample": f"{args.cpu_batches} mini-batches of {w.batch} seeds on the full graph "
+                                          f"({dt:.1f} s, about {rows:.0f} gathered rows each), C restatement with "
+                                          "OpenMP over all host threads"}
+    if rank == 0:
+        print(json.dumps(line))
+    synthetic.cleanup(inst)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -299,9 +299,11 @@ size_t apt_sort_u64_temp_bytes(int64_t n);
 int apt_sort_u64(const uint64_t* keys_in, uint64_t* keys_out, int64_t n,
                  void* temp, size_t temp_bytes, int end_bit, void* stream);
 /* Standard-normal rows: element (row, col) from Philox keyed by seed; written
- * as dtype. Fills rows [first_row, first_row + num_rows). */
-int apt_normal_rows(uint64_t seed, int64_t first_row, int64_t num_rows,
-                    int64_t dim, int dtype, void* out, void* stream);
+ * as dtype. Output row r holds node row_ids[r], or first_row + r when row_ids
+ * is NULL, so a cache table and the full table agree row by row. */
+int apt_normal_rows(uint64_t seed, int64_t first_row, const int64_t* row_ids,
+                    int64_t num_rows, int64_t dim, int dtype, void* out,
+                    void* stream);
 
 #ifdef __cplusplus
 }
