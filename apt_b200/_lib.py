@@ -1,7 +1,7 @@
 """ctypes binding of libapt_b200.so (the C ABI declared in include/apt_b200.h).
 
 There is no CPU or PyTorch fallback: if the CUDA library has not been built,
-importing this module raises. Build it with ``python -m apt_b200.build``.
+importing this module raises. Build it with ``python apt_b200/build.py``.
 """
 import ctypes
 import os
@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_PKG, "libapt_b200.so")
 if not os.path.exists(LIB_PATH):
     raise ImportError(
         f"{LIB_PATH} is missing: the sm_100a CUDA library has not been built "
-        "(run `python -m apt_b200.build`). apt_b200 has no fallback path."
+        "(run `python apt_b200/build.py`). apt_b200 has no fallback path."
     )
 
 lib = ctypes.CDLL(LIB_PATH)

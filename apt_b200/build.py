@@ -1,7 +1,9 @@
 """Builds apt_b200/libapt_b200.so from apt_b200/csrc/*.cu with nvcc for sm_100a.
 
-Run as ``python -m apt_b200.build`` (add ``--force`` to rebuild). The library
-is built in-tree; nothing is installed.
+Run as ``python apt_b200/build.py`` (add ``--force`` to rebuild, ``-v`` for
+ptxas register/shared-memory reports). Run as a file, it does not import the
+package, which refuses to load without the library. The library is built
+in-tree; nothing is installed.
 """
 import os
 import shutil
