@@ -11,6 +11,8 @@
 //
 // Rows are opaque bytes. The vector width V is the widest of 16/8/4/2/1 bytes
 // that divides every row size, column offset and base address involved.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace apt {
@@ -272,5 +274,122 @@ extern "C" int apt_gather_rows(const int64_t* index, int64_t num_rows,
 #undef APT_MISS
 #undef APT_HITS
 #undef APT_BY_WIDTH
+  return APT_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Gather without any allocation, for callers that must not allocate.
+//
+// The scratch that apt_gather_rows takes from its caller (decoded positions,
+// miss list, miss counter) lives here in a fixed array inside the library's
+// device image, sized for kStaticGatherMaxRows rows per call. The name
+// g_gather_scratch is a host-side stand-in in host code, not a device address;
+// the address kernels can use is asked for once per device with
+// cudaGetSymbolAddress while that device is current.
+namespace apt {
+
+constexpr int64_t kStaticGatherMaxRows = 1 << 20;
+constexpr size_t kStaticGatherBytes =
+    (size_t)kStaticGatherMaxRows * 8 + (size_t)kStaticGatherMaxRows * 4 + 256;
+
+static __device__ __align__(256) unsigned char g_gather_scratch[kStaticGatherBytes];
+
+static void* g_scratch_addr[64];
+static bool g_scratch_ready[64];
+static std::mutex g_scratch_mu;
+
+static int static_scratch(void** out) {
+  int dev = 0;
+  APT_CUDA(cudaGetDevice(&dev));
+  APT_CHECK_ARG(dev >= 0 && dev < 64, "apt_gather_rows_static: device ordinal %d", dev);
+  std::lock_guard<std::mutex> lk(g_scratch_mu);
+  if (!g_scratch_ready[dev]) {
+    void* p = nullptr;
+    APT_CUDA(cudaGetSymbolAddress(&p, g_gather_scratch));
+    g_scratch_addr[dev] = p;
+    g_scratch_ready[dev] = true;
+  }
+  *out = g_scratch_addr[dev];
+  return APT_OK;
+}
+
+}  // namespace apt
+
+extern "C" int64_t apt_gather_static_max_rows(void) { return apt::kStaticGatherMaxRows; }
+
+extern "C" int apt_gather_rows_static(const int64_t* index, int64_t num_rows,
+                                      const int64_t* feat_pos_map, int64_t num_nodes,
+                                      const void* dev_feats, int64_t num_dev_rows,
+                                      int64_t dev_row_bytes, const void* uva_feats,
+                                      int64_t num_uva_rows, int64_t uva_row_bytes,
+                                      int64_t uva_col_offset_bytes, void* out,
+                                      int32_t* status_word, void* stream) {
+  using namespace apt;
+  APT_CHECK_ARG(num_rows >= 0, "apt_gather_rows_static: negative num_rows");
+  if (num_rows > kStaticGatherMaxRows) {
+    set_error("apt_gather_rows_static: %lld rows exceed the built-in scratch of %lld rows per call; "
+              "split the request or use apt_gather_rows with a caller workspace",
+              (long long)num_rows, (long long)kStaticGatherMaxRows);
+    return APT_ERR_CAPACITY;
+  }
+  APT_CHECK_ARG(dev_row_bytes > 0 && num_dev_rows >= 0 && num_uva_rows >= 0 && num_nodes >= 0,
+                "apt_gather_rows_static: bad table sizes");
+  APT_CHECK_ARG(num_uva_rows == 0 ||
+                    (uva_col_offset_bytes >= 0 && uva_col_offset_bytes + dev_row_bytes <= uva_row_bytes),
+                "apt_gather_rows_static: column window outside the host row");
+  if (num_rows == 0) return APT_OK;
+  APT_CHECK_ARG(index && feat_pos_map && out && status_word, "apt_gather_rows_static: null pointer");
+  APT_CHECK_ARG((num_dev_rows == 0 || dev_feats) && (num_uva_rows == 0 || uva_feats),
+                "apt_gather_rows_static: null feature table");
+  void* base = nullptr;
+  const int rc = static_scratch(&base);
+  if (rc != APT_OK) return rc;
+  GatherWs ws;
+  gather_layout(kStaticGatherMaxRows, (char*)base, &ws);
+  cudaStream_t s = (cudaStream_t)stream;
+
+  uint64_t bits = (uint64_t)dev_row_bytes | (uintptr_t)out;
+  if (num_dev_rows > 0) bits |= (uintptr_t)dev_feats;
+  const int vw_hit = vec_width(bits);
+  if (num_uva_rows > 0)
+    bits |= (uint64_t)uva_row_bytes | (uint64_t)uva_col_offset_bytes | (uintptr_t)uva_feats;
+  const int vw_miss = vec_width(bits);
+
+  // The array keeps the previous call's contents: the miss counter must start at
+  // zero; positions and the miss list are rewritten for every row that is read.
+  APT_CUDA(cudaMemsetAsync(ws.miss_count, 0, sizeof(int32_t), s));
+  {
+    const int grid = wave_grid(ceil_div(num_rows, 256), 8);
+    APT_LAUNCH(k_classify, grid, 256, 0, s, index, num_rows, feat_pos_map, num_nodes,
+               num_dev_rows, num_uva_rows, ws, status_word);
+  }
+  const char* devp = (const char*)dev_feats;
+  const char* uvap = (const char*)uva_feats;
+  char* outp = (char*)out;
+#define APT_SMISS(V)                                                            \
+  APT_LAUNCH(k_copy_miss<V>, kNumSMs, kGatherBlock, 0, s, ws.miss_count,        \
+             ws.miss_rows, ws.src_pos, uvap, uva_row_bytes, uva_col_offset_bytes, \
+             dev_row_bytes, outp)
+#define APT_SHITS(V)                                                            \
+  do {                                                                          \
+    const int grid = wave_grid(ceil_div(num_rows, (kGatherBlock / 32) * kRowsPerWarp), 8, 4); \
+    APT_LAUNCH(k_copy_hits<V>, grid, kGatherBlock, 0, s, num_rows, ws.src_pos,  \
+               devp, dev_row_bytes, outp);                                      \
+  } while (0)
+#define APT_SBY_WIDTH(W, MACRO)                                                 \
+  do {                                                                          \
+    switch (W) {                                                                \
+      case 16: MACRO(uint4); break;                                             \
+      case 8: MACRO(uint2); break;                                              \
+      case 4: MACRO(uint32_t); break;                                           \
+      case 2: MACRO(uint16_t); break;                                           \
+      default: MACRO(uint8_t); break;                                           \
+    }                                                                           \
+  } while (0)
+  if (num_uva_rows > 0) APT_SBY_WIDTH(vw_miss, APT_SMISS);
+  APT_SBY_WIDTH(vw_hit, APT_SHITS);
+#undef APT_SMISS
+#undef APT_SHITS
+#undef APT_SBY_WIDTH
   return APT_OK;
 }

@@ -176,6 +176,41 @@ int apt_gather_rows(const int64_t* index, int64_t num_rows,
                     size_t workspace_bytes, int32_t* status_word, void* stream,
                     void* side_stream);
 
+/* Gather for callers that cannot allocate device memory. No counterpart in the
+ * reference, whose gather allocates its output and keeps no scratch.
+ *
+ * Who needs it: code that runs where cudaMalloc is not an option — inside a
+ * memory pool whose owner has handed out every byte already (an inference
+ * server that pre-plans all device memory at start-up), in a callback or a
+ * real-time loop where an allocator call may block or synchronise the
+ * device, or in a process whose allocator hooks forbid allocation after
+ * initialisation. Such a caller passes its own inputs and output; the scratch
+ * apt_gather_rows would take as `workspace` is a fixed array built into the
+ * library's device image instead (about 12.6 MB, held by every GPU that loads
+ * the library until the process exits).
+ *
+ * Same arguments and result as apt_gather_rows, with these differences:
+ *  - at most apt_gather_static_max_rows() (1 048 576) rows per call; more
+ *    returns APT_ERR_CAPACITY with a message and launches nothing;
+ *  - all three kernels run on `stream` (no side stream, no events);
+ *  - it calls no cudaMalloc, cudaFree or other allocating routine. The first
+ *    call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress) with that device current; make that first call
+ *    before any stream capture begins;
+ *  - every call on a device uses the same array, which still holds the
+ *    previous call's contents (the call clears what has to start at zero).
+ *    Two calls that overlap on the GPU — different streams, or different host
+ *    threads — race on it: issue them on one stream, or order them yourself.
+ */
+int64_t apt_gather_static_max_rows(void);
+int apt_gather_rows_static(const int64_t* index, int64_t num_rows,
+                           const int64_t* feat_pos_map, int64_t num_nodes,
+                           const void* dev_feats, int64_t num_dev_rows,
+                           int64_t dev_row_bytes, const void* uva_feats,
+                           int64_t num_uva_rows, int64_t uva_row_bytes,
+                           int64_t uva_col_offset_bytes, void* out,
+                           int32_t* status_word, void* stream);
+
 /* ------------------------------------------------------------ SpMM / SDDMM
  * Segment-batched COO operators over sampled blocks: edge e of segment k
  * (coo_offset[k] <= e < coo_offset[k+1]) reads input row input_offset[k]+row[e]
