@@ -30,6 +30,7 @@ PROTOTYPES = {
     "apt_version": (c_int, []),
     "apt_launch_count": (c_int64, []),
     "apt_launch_count_reset": (None, []),
+    "apt_set_tunable": (c_int, [c_char_p, c_int64]),
     "apt_profile_enable": (c_int, [c_int]),
     "apt_profile_read": (c_int, [c_char_p, ctypes.POINTER(c_double), ctypes.POINTER(c_int64)]),
     "apt_sample_csc_fanout": (c_int, [P, c_int64, c_int, P, c_int64, P, P, P, P, c_uint64, c_uint32, c_int, P, P, P]),

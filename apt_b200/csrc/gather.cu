@@ -7,10 +7,16 @@
 //                lane one 16-byte vector per row, all loads issued before the
 //                first store, so every warp keeps 4 x 512 B in flight.
 //   k_copy_miss  pinned host memory -> HBM over the host link, same mover over
-//                the miss list, on a side stream so that it overlaps the hits.
+//                the miss list. It runs after the hit copy on the same stream:
+//                measured on B200, running the two at once slows the hit copy
+//                by 2-4x (host-link reads back up the memory pipeline) and the
+//                pair finishes later than when run back to back. The side
+//                stream is kept behind the gather_overlap tunable.
 //
 // Rows are opaque bytes. The vector width V is the widest of 16/8/4/2/1 bytes
 // that divides every row size, column offset and base address involved.
+#include <string.h>
+
 #include <mutex>
 
 #include "common.cuh"
@@ -157,6 +163,118 @@ k_copy_miss(const int32_t* __restrict__ miss_count,
   }
 }
 
+// ---- tunables (set through apt_set_tunable; defaults are the measured best) ----
+static int g_miss_mode = 0;      // 0: ld.global.nc 16 B, 1: plain ld.global 16 B, 2: bulk copy through shared memory
+static int g_miss_blocks = kNumSMs;
+static int g_hit_waves = 4;      // cap on waves of 148 x 8 blocks of the hit copy
+static int g_overlap = 0;        // 1: miss copy on the side stream, under the hit copy
+
+// Plain-load variant of the miss mover (16-byte vectors only).
+__global__ void __launch_bounds__(kGatherBlock)
+k_copy_miss_plain(const int32_t* __restrict__ miss_count, const int32_t* __restrict__ miss_rows,
+                  const int64_t* __restrict__ src_pos, const char* uva_feats, int64_t uva_row_bytes,
+                  int64_t col_offset_bytes, int64_t row_bytes, char* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t n = *miss_count;
+  const int chunks = (int)(row_bytes / 16);
+  for (int64_t m0 = warp * kRowsPerWarp; m0 < n; m0 += warps * kRowsPerWarp) {
+    int64_t r[kRowsPerWarp], p[kRowsPerWarp];
+#pragma unroll
+    for (int k = 0; k < kRowsPerWarp; ++k) {
+      r[k] = m0 + k < n ? (int64_t)miss_rows[m0 + k] : (int64_t)-1;
+      p[k] = r[k] >= 0 ? -src_pos[r[k]] - 2 : (int64_t)0;
+    }
+    for (int c = lane; c < chunks; c += 32) {
+      uint4 v[kRowsPerWarp];
+#pragma unroll
+      for (int k = 0; k < kRowsPerWarp; ++k)
+        if (r[k] >= 0) v[k] = ld_plain_16((const uint4*)(uva_feats + p[k] * uva_row_bytes + col_offset_bytes) + c);
+#pragma unroll
+      for (int k = 0; k < kRowsPerWarp; ++k)
+        if (r[k] >= 0) st_stream_16((uint4*)(out + r[k] * row_bytes) + c, v[k]);
+    }
+  }
+}
+
+// Bulk-copy variant: one lane per warp asks the copy engine of the SM for the
+// whole row (cp.async.bulk global -> shared, completion on an mbarrier), then
+// for the row's way out (shared -> global). Rows must be multiples of 16 bytes
+// on 16-byte boundaries. Waits are bounded: a row that does not arrive sets
+// the status flag and is skipped.
+constexpr int kBulkStages = 4;  // rows in flight per warp
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__global__ void __launch_bounds__(kGatherBlock)
+k_copy_miss_bulk(const int32_t* __restrict__ miss_count, const int32_t* __restrict__ miss_rows,
+                 const int64_t* __restrict__ src_pos, const char* uva_feats, int64_t uva_row_bytes,
+                 int64_t col_offset_bytes, int64_t row_bytes, char* __restrict__ out, int32_t* status) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) uint64_t bars[(kGatherBlock / 32) * kBulkStages];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + wib;
+  const int64_t n = *miss_count;
+  unsigned char* wbuf = smem + (size_t)wib * kBulkStages * row_bytes;
+  uint64_t* wbar = bars + wib * kBulkStages;
+  if (lane == 0) {
+    for (int k = 0; k < kBulkStages; ++k)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(wbar + k)));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  uint32_t phase = 0;
+  for (int64_t m0 = warp * kBulkStages; m0 < n; m0 += warps * kBulkStages) {
+    if (lane == 0) {
+      for (int k = 0; k < kBulkStages; ++k) {
+        if (m0 + k >= n) break;
+        const int64_t r = miss_rows[m0 + k];
+        const int64_t p = -src_pos[r] - 2;
+        const char* src = uva_feats + p * uva_row_bytes + col_offset_bytes;
+        const uint32_t bar = smem_u32(wbar + k), dst = smem_u32(wbuf + (size_t)k * row_bytes);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)row_bytes)
+                     : "memory");
+        asm volatile(
+            "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+            "l"(src), "r"((uint32_t)row_bytes), "r"(bar)
+            : "memory");
+      }
+      bool failed = false;
+      for (int k = 0; k < kBulkStages; ++k) {
+        if (m0 + k >= n) break;
+        const uint32_t bar = smem_u32(wbar + k);
+        uint32_t done = 0;
+        const uint64_t t0 = global_timer_ns();
+        for (int it = 0; it < (1 << 20) && !done; ++it) {
+          asm volatile(
+              "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+              : "=r"(done)
+              : "r"(bar), "r"(phase)
+              : "memory");
+          if (!done && (it & 15) == 15 && global_timer_ns() - t0 > 1000000000ull) break;  // 1 s
+        }
+        if (!done) {
+          failed = true;
+          continue;
+        }
+        const int64_t r = miss_rows[m0 + k];
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(out + r * row_bytes),
+                     "r"(smem_u32(wbuf + (size_t)k * row_bytes)), "r"((uint32_t)row_bytes)
+                     : "memory");
+      }
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      if (failed) atomicOr(status, APT_FLAG_PEER_TIMEOUT);
+    }
+    phase ^= 1;
+    __syncwarp();
+  }
+}
+
 // Two events per device, reused by every call, order the side stream between
 // the classify kernel and the end of the call.
 static cudaEvent_t g_ev[64][2];
@@ -169,6 +287,24 @@ static int vec_width(uint64_t bits) {
 }
 
 }  // namespace apt
+
+extern "C" int apt_set_tunable(const char* name, int64_t value) {
+  using namespace apt;
+  APT_CHECK_ARG(name, "apt_set_tunable: null name");
+  if (!strcmp(name, "gather_miss_mode") && value >= 0 && value <= 2) {
+    g_miss_mode = (int)value;
+  } else if (!strcmp(name, "gather_miss_blocks") && value >= 1 && value <= 65535) {
+    g_miss_blocks = (int)value;
+  } else if (!strcmp(name, "gather_hit_waves") && value >= 1 && value <= 64) {
+    g_hit_waves = (int)value;
+  } else if (!strcmp(name, "gather_overlap") && (value == 0 || value == 1)) {
+    g_overlap = (int)value;
+  } else {
+    set_error("apt_set_tunable: unknown name or bad value: %s = %lld", name, (long long)value);
+    return APT_ERR_BAD_ARG;
+  }
+  return APT_OK;
+}
 
 extern "C" size_t apt_gather_workspace_bytes(int64_t num_rows) {
   if (num_rows < 0) return 0;
@@ -205,7 +341,7 @@ extern "C" int apt_gather_rows(const int64_t* index, int64_t num_rows,
   }
   cudaStream_t s = (cudaStream_t)stream;
   cudaStream_t side = (cudaStream_t)side_stream;
-  const bool overlap = side != nullptr && side != s && num_uva_rows > 0;
+  const bool overlap = g_overlap && side != nullptr && side != s && num_uva_rows > 0;
 
   uint64_t bits = (uint64_t)dev_row_bytes | (uintptr_t)out;
   if (num_dev_rows > 0) bits |= (uintptr_t)dev_feats;
@@ -240,14 +376,14 @@ extern "C" int apt_gather_rows(const int64_t* index, int64_t num_rows,
 #define APT_MISS(V)                                                             \
   do {                                                                          \
     ProfScope prof("gather_miss", ms);                                          \
-    APT_LAUNCH(k_copy_miss<V>, kNumSMs, kGatherBlock, 0, ms, ws.miss_count,     \
+    APT_LAUNCH(k_copy_miss<V>, g_miss_blocks, kGatherBlock, 0, ms, ws.miss_count, \
                ws.miss_rows, ws.src_pos, uvap, uva_row_bytes,                   \
                uva_col_offset_bytes, dev_row_bytes, outp);                      \
   } while (0)
 #define APT_HITS(V)                                                             \
   do {                                                                          \
     ProfScope prof("gather_hit", s);                                            \
-    const int grid = wave_grid(ceil_div(num_rows, (kGatherBlock / 32) * kRowsPerWarp), 8, 4); \
+    const int grid = wave_grid(ceil_div(num_rows, (kGatherBlock / 32) * kRowsPerWarp), 8, g_hit_waves); \
     APT_LAUNCH(k_copy_hits<V>, grid, kGatherBlock, 0, s, num_rows, ws.src_pos,  \
                devp, dev_row_bytes, outp);                                      \
   } while (0)
@@ -264,7 +400,20 @@ extern "C" int apt_gather_rows(const int64_t* index, int64_t num_rows,
 
   if (num_uva_rows > 0) {
     cudaStream_t ms = overlap ? side : s;
-    APT_BY_WIDTH(vw_miss, APT_MISS);
+    if (vw_miss == 16 && g_miss_mode == 1) {
+      ProfScope prof("gather_miss", ms);
+      APT_LAUNCH(k_copy_miss_plain, g_miss_blocks, kGatherBlock, 0, ms, ws.miss_count, ws.miss_rows,
+                 ws.src_pos, uvap, uva_row_bytes, uva_col_offset_bytes, dev_row_bytes, outp);
+    } else if (vw_miss == 16 && g_miss_mode == 2 &&
+               (size_t)dev_row_bytes * kBulkStages * (kGatherBlock / 32) <= 200 * 1024) {
+      const size_t smem = (size_t)dev_row_bytes * kBulkStages * (kGatherBlock / 32);
+      APT_CUDA(cudaFuncSetAttribute(k_copy_miss_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      ProfScope prof("gather_miss", ms);
+      APT_LAUNCH(k_copy_miss_bulk, g_miss_blocks, kGatherBlock, smem, ms, ws.miss_count, ws.miss_rows,
+                 ws.src_pos, uvap, uva_row_bytes, uva_col_offset_bytes, dev_row_bytes, outp, status_word);
+    } else {
+      APT_BY_WIDTH(vw_miss, APT_MISS);
+    }
   }
   APT_BY_WIDTH(vw_hit, APT_HITS);
   if (overlap) {

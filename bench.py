@@ -39,12 +39,19 @@ UNIT = "mini-batches/s"
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="c1_papers_np")
     ap.add_argument("--impl", default="apt_b200", choices=["apt_b200", "reference"])
     ap.add_argument("--cpu-batches", type=int, default=12, help="batches of the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--stage", default="minibatch", choices=["minibatch", "gather"],
+                    help="gather: time the cached feature gather alone on a synthetic table")
+    ap.add_argument("--rows", type=int, default=1_081_344, help="--stage gather: rows per call")
+    ap.add_argument("--table-rows", type=int, default=4_000_000, help="--stage gather: rows of the cached table")
+    ap.add_argument("--feat-dim", type=int, default=128)
+    ap.add_argument("--feat-dtype", default="f32", choices=["f32", "bf16", "f16"])
+    ap.add_argument("--miss-frac", type=float, default=0.0, help="--stage gather: share of rows read from host memory")
     return ap.parse_args()
 
 
@@ -200,9 +207,73 @@ class CpuPath:
         return n / dt, dt, rows / max(n, 1)
 
 
+# ------------------------------------------------------------------ stage: gather
+def stage_gather(args):
+    """The cached feature gather alone: `rows` random rows out of a cache table of
+    `table_rows` rows (larger than L2), a share `miss_frac` of them from pinned
+    host memory instead. One JSON line with the hit-copy kernel's roofline."""
+    import apt_b200  # noqa: F401
+    from apt_b200 import ops
+    from apt_b200._lib import lib
+
+    dt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[args.feat_dtype]
+    torch.cuda.set_device(0)
+    n_dev, dim = args.table_rows, args.feat_dim
+    n_host = max(16, int(n_dev * 0.25)) if args.miss_frac > 0 else 16
+    g = torch.Generator(device="cuda").manual_seed(5)
+    dev_feats = torch.randn((n_dev, dim), generator=g, device="cuda").to(dt)
+    host = torch.randn((n_host, dim)).to(dt).pin_memory()
+    n = n_dev + n_host                       # ids [0, n_dev) cached, [n_dev, n) only in host memory
+    ops.cache_feats_shared(n, host, dev_feats, torch.arange(n_dev), torch.arange(n_host) + n_dev, 0)
+    row_bytes = dim * dev_feats.element_size()
+    n_miss = int(args.rows * args.miss_frac)
+    peak, peak_kind = peaks()
+    lib.apt_profile_enable(1)
+    total_ms = 0.0
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for it in range(args.warmup + args.steps):
+        ids = torch.cat([torch.randint(0, n_dev, (args.rows - n_miss,), generator=g, device="cuda"),
+                         torch.randint(n_dev, n, (n_miss,), generator=g, device="cuda")])
+        ids = ids[torch.randperm(args.rows, generator=g, device="cuda")].contiguous()
+        if it == args.warmup:
+            for tag in (b"gather_hit", b"gather_miss", b"gather_classify"):
+                t, k = ctypes.c_double(), ctypes.c_int64()
+                lib.apt_profile_read(tag, ctypes.byref(t), ctypes.byref(k))
+        torch.cuda.nvtx.range_push("apt_timed")
+        ev0.record()
+        out = ops.load_subtensor(ids)
+        ev1.record()
+        torch.cuda.nvtx.range_pop()
+        torch.cuda.synchronize()
+        if it >= args.warmup:
+            total_ms += ev0.elapsed_time(ev1)
+    ops.check_status()
+    res = {}
+    for tag in ("gather_hit", "gather_miss", "gather_classify"):
+        t, k = ctypes.c_double(), ctypes.c_int64()
+        lib.apt_profile_read(tag.encode(), ctypes.byref(t), ctypes.byref(k))
+        res[tag] = (t.value, k.value)
+    hit_ms, hit_n = res["gather_hit"]
+    hit_bytes = (args.rows - n_miss) * 2 * row_bytes + args.rows * 8
+    gbs = hit_bytes / (hit_ms / hit_n * 1e-3) / 1e9
+    call_gbs = args.rows * (2 * row_bytes + 16) / (total_ms / args.steps * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "cached feature gather GB/s (hit-copy kernel)", "value": gbs, "unit": "GB/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+        "dtype": args.feat_dtype, "data": "synthetic",
+        "config": {"workload": "stage gather", "rows": args.rows, "table_rows": n_dev, "row_bytes": row_bytes,
+                   "miss_frac": args.miss_frac, "l2": "cache table larger than the 126 MB L2, new random ids every call"},
+        "whole_call_gbs": call_gbs,
+        "stage_us": {k: 1000.0 * v[0] / max(v[1], 1) for k, v in res.items()},
+        "roofline": {"kernel": "k_copy_hits", "bound": "hbm", "achieved": round(gbs, 1), "peak": peak,
+                     "peak_kind": peak_kind, "unit": "GB/s", "frac": round(gbs / peak, 4), "traffic": None}}))
+
+
 # ------------------------------------------------------------------------- main
 def main():
     args = parse()
+    if args.stage == "gather":
+        return stage_gather(args)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -287,21 +358,23 @@ def main():
 
     # ---- device-resident run ------------------------------------------------
     ops.set_sampling(key=7777777, call_id=0)
+    clocks = ClockSampler(local_rank)
+    clocks.start()          # sampled from the warm-up on: the timed region alone can be shorter than one sample period
     for b in dev_batches[:args.warmup]:
         step(b)
     ops.check_status()
-    clocks = ClockSampler(local_rank)
-    clocks.start()
     lib.apt_profile_enable(1)
     lib.apt_launch_count_reset()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     kept = []
     barrier()
+    torch.cuda.nvtx.range_push("apt_timed")
     ev0.record()
     for b in dev_batches[args.warmup:]:
         sample, x = step(b)
         kept.append(sample[0])
     ev1.record()
+    torch.cuda.nvtx.range_pop()
     barrier()
     launches = int(lib.apt_launch_count())
     lib.apt_profile_enable(0)

@@ -64,6 +64,15 @@ void apt_launch_count_reset(void);
 int apt_profile_enable(int on);
 int apt_profile_read(const char* tag, double* total_ms, int64_t* launches);
 
+/* Tuning knobs for measurements; the defaults are what the benchmark uses.
+ *   gather_miss_mode   0 16-byte ld.global.nc, 1 plain 16-byte loads,
+ *                      2 bulk copies (cp.async.bulk) staged through shared memory
+ *   gather_miss_blocks blocks of the miss-copy kernel (default 148)
+ *   gather_hit_waves   cap on the hit-copy grid, in waves of 148 x 8 blocks (default 4)
+ *   gather_overlap     1: miss copy on the side stream under the hit copy,
+ *                      0 (default): after it on the main stream */
+int apt_set_tunable(const char* name, int64_t value);
+
 /* ------------------------------------------------------------------ sampling
  * Uniform fanout sampling of in-neighbours from a CSC graph, one dense row of
  * `fanout` ids per seed. Takes the role of LocalSampleNeighbors /
@@ -161,9 +170,10 @@ int apt_unique_sorted(const int64_t* ids, int64_t num_ids, int64_t id_lo,
  *   p == -1: out[r] = 0 and APT_FLAG_FEAT_NOT_EXIST (the reference reads out
  *            of bounds here)
  * Rows are opaque bytes, so fp32/bf16/fp16 tables share the code.
- * Three kernels: classify (decode p, compact the miss list), hit copy on
- * `stream`, miss copy on `side_stream` (may be NULL: then it runs on `stream`
- * after the hit copy). The output is complete in `stream` order on return.
+ * Three kernels on `stream`: classify (decode p, compact the miss list), miss
+ * copy, hit copy. With the gather_overlap tunable set and a non-NULL
+ * `side_stream` the miss copy runs there instead, ordered by events. The
+ * output is complete in `stream` order on return.
  * workspace: apt_gather_workspace_bytes(num_rows) bytes.
  */
 size_t apt_gather_workspace_bytes(int64_t num_rows);

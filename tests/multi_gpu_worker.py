@@ -1,0 +1,150 @@
+"""One rank of the multi-GPU parity check (launched by tests/test_gpu_multi.py
+through torch.distributed.run, one process per GPU).
+
+Every rank builds the same small graph and feature table, the ranks run the
+NP mini-batch (seed shuffle to the owner, outer-hop sampling there, feature
+shuffle back, backward shuffle) with the peer-to-peer exchange, and rank 0
+compares what all ranks got with the CPU oracle replaying all ranks at once.
+The library all-to-all (NCCL) must give the same bytes. A timing of a large
+feature shuffle with both backends is printed for information.
+"""
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import apt_b200  # noqa: E402
+from apt_b200 import ops  # noqa: E402
+from apt_b200.exchange import NcclExchange  # noqa: E402
+from oracle import oracle as orc  # noqa: E402
+from tests.helpers import small_graph  # noqa: E402
+
+I64 = np.int64
+
+
+def gather_objects(obj):
+    out = [None] * dist.get_world_size()
+    dist.all_gather_object(out, obj)
+    return out
+
+
+def host(t):
+    return (t.float() if t.dtype == torch.bfloat16 else t).cpu().numpy()
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ops.init(rank, local, world, ops.nccl_get_unique_id(), world)
+    assert ops.STATE.exchange.name == "p2p"
+    p2p = ops.STATE.exchange
+    nccl = NcclExchange(ops.STATE)
+
+    n, indptr, indices = small_graph(scale=13, edge_factor=8)
+    e = torch.empty(0, dtype=torch.int64)
+    ops.mix_cache_graphs(0, e, e, e, torch.from_numpy(indptr).cuda(), torch.from_numpy(indices).cuda())
+    mv = np.linspace(0, n, world + 1).astype(I64)
+    ops.register_min_vids(torch.from_numpy(mv))
+    graph = (None, None, None, indptr, indices)
+    report = {}
+
+    # --- the reference's all-to-all cases (tests/test_alltoall.cc:24-99) on real links
+    for expand in (1, 16):
+        k, b = 7, 100
+        send = [k * (rank - r) ** 2 + b for r in range(world)]
+        recv = [k * (r - rank) ** 2 + b for r in range(world)]
+        inp = torch.full((sum(send) * expand,), rank, dtype=torch.int64, device="cuda")
+        out = torch.empty(sum(recv) * expand, dtype=torch.int64, device="cuda")
+        ops.alltoall(inp, out, torch.tensor(send).cumsum(0), torch.tensor(recv).cumsum(0), expand, 0)
+        want = np.concatenate([np.full(recv[r] * expand, r, dtype=I64) for r in range(world)])
+        assert np.array_equal(host(out), want), f"alltoall expand {expand}"
+
+    # --- NP outer hop: shuffle + unique + sample at the owner
+    rng = np.random.default_rng(100 + rank)
+    seeds = rng.integers(0, n, 3000 + 101 * rank).astype(I64)
+    for trial in range(3):  # several epochs of the inbox
+        ops.set_sampling(key=555, call_id=7)
+        res = ops.np_sample_and_shuffle(torch.from_numpy(seeds).cuda(), 10)
+        ops.set_sampling(key=555, call_id=7)
+        ops.STATE.exchange = nccl
+        res_nccl = ops.np_sample_and_shuffle(torch.from_numpy(seeds).cuda(), 10)
+        ops.STATE.exchange = p2p
+        for a, b_ in zip(res, res_nccl):
+            assert np.array_equal(host(a), host(b_)), "p2p and nccl disagree"
+    all_seeds = gather_objects(seeds)
+    all_res = gather_objects([host(t) for t in res])
+    if rank == 0:
+        want = orc.np_sample_and_shuffle(all_seeds, 10, mv, graph, key=555, call_id=7)
+        for r in range(world):
+            for got, w in zip(all_res[r], want[r]):
+                assert np.array_equal(got, w), f"rank {r}: np_sample_and_shuffle differs from the oracle"
+    uniq, nbr, perm, send_off, recv_off, inverse_idx = res
+
+    # --- feature shuffle forward/backward (fp32 1 KiB rows, bf16 512 B rows, odd width)
+    for dtype, D in ((torch.float32, 256), (torch.bfloat16, 256), (torch.float32, 3)):
+        g = torch.Generator(device="cuda").manual_seed(7)
+        table = torch.randn((n, D), generator=g, device="cuda").to(dtype)   # same on every rank
+        h = table[uniq]                                                        # "layer-0 output" of owned ids
+        x = ops.rows_gather(h, inverse_idx)
+        y = ops.feat_shuffle(x, send_off, recv_off, perm, D, 1)
+        assert torch.equal(y, table[torch.from_numpy(seeds).cuda()]), "feat_shuffle fwd"
+        ops.STATE.exchange = nccl
+        y2 = ops.feat_shuffle(x, send_off, recv_off, perm, D, 1)
+        ops.STATE.exchange = p2p
+        assert torch.equal(y, y2)
+        grad = torch.randn(y.shape, generator=g, device="cuda").to(dtype)
+        gb = ops.feat_shuffle(grad, recv_off, send_off, perm, D, 0)
+        ops.STATE.exchange = nccl
+        gb2 = ops.feat_shuffle(grad, recv_off, send_off, perm, D, 0)
+        ops.STATE.exchange = p2p
+        assert torch.equal(gb, gb2), "feat_shuffle bwd: p2p vs nccl"
+        all_grad = gather_objects(host(grad))
+        all_gb = gather_objects(host(gb))
+        all_meta = gather_objects((host(perm), send_off.numpy(), recv_off.numpy()))
+        if rank == 0:
+            want = orc.feat_shuffle(all_grad, [m[2] for m in all_meta], [m[1] for m in all_meta],
+                                    [m[0] for m in all_meta], D, fwd=False)
+            for r in range(world):
+                assert np.array_equal(all_gb[r], want[r]), f"rank {r}: feat_shuffle bwd differs from the oracle"
+    ops.check_status()
+
+    # --- timing of a large forward shuffle (2 KiB fp16 rows), both backends
+    rows, D = 200_000, 1024
+    ids = torch.randint(0, n, (rows,), device="cuda")
+    recv_ids, perm2, roff, doff = ops.shuffle_seeds(ids)
+    x = torch.randn((recv_ids.numel(), D), device="cuda").half()
+    for name, ex in (("p2p", p2p), ("nccl", nccl)):
+        ops.STATE.exchange = ex
+        for _ in range(3):
+            ops.feat_shuffle(x, roff, doff, perm2, D, 1)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            ops.feat_shuffle(x, roff, doff, perm2, D, 1)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1) / 10], device="cuda")
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        counts = np.diff(np.concatenate([[0], roff.numpy()]))
+        remote = int(counts.sum() - counts[rank]) * D * 2
+        report[name] = {"ms": float(ms.item()), "remote_gb_per_s_per_gpu": remote / (float(ms.item()) * 1e-3) / 1e9}
+    ops.STATE.exchange = p2p
+    ops.check_status()
+    if rank == 0:
+        print("MULTI_GPU_OK " + json.dumps({"world": world, "shuffle_2KiB_rows": report}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

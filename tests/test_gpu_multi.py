@@ -1,0 +1,27 @@
+"""Multi-GPU parity of the seed and feature shuffle over real peer-to-peer
+links: spawns one process per GPU (2, or 4 when the box has them). Skipped on a
+single-GPU box; the same protocol is covered there by the emulated ranks of
+tests/test_gpu_shuffle.py."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_np_shuffle_across_gpus(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29500 + world),
+           os.path.join(ROOT, "tests", "multi_gpu_worker.py")]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "MULTI_GPU_OK" in res.stdout
+    print(res.stdout[res.stdout.index("MULTI_GPU_OK"):].splitlines()[0])
