@@ -25,12 +25,13 @@ __device__ __forceinline__ int owner_of(int64_t v, const int64_t* mv,
 }
 
 __global__ void __launch_bounds__(kBucketBlock)
-k_bucket_count(const int64_t* __restrict__ ids, int64_t n,
+k_bucket_count(const int64_t* __restrict__ ids, int64_t n, const int64_t* __restrict__ n_dev,
                const int64_t* __restrict__ min_vids, OwnerParams p,
                int32_t* __restrict__ hist /* [world_size][nblocks] */,
                int nblocks) {
   __shared__ int64_t mv[kMaxRanks + 1];
   __shared__ int cnt[kMaxRanks];
+  n = effective_n(n, n_dev);
   if (threadIdx.x <= p.world_size) mv[threadIdx.x] = min_vids[threadIdx.x];
   if (threadIdx.x < kMaxRanks) cnt[threadIdx.x] = 0;
   __syncthreads();
@@ -45,9 +46,10 @@ k_bucket_count(const int64_t* __restrict__ ids, int64_t n,
 // output slot of bucket b's items from block blk. Bucket sizes and inclusive
 // offsets fall out of the same array.
 __global__ void k_bucket_sizes(const int32_t* __restrict__ hist, int nblocks,
-                               int world_size, int64_t n,
+                               int world_size, int64_t n, const int64_t* __restrict__ n_dev,
                                int64_t* __restrict__ sizes,
                                int64_t* __restrict__ offsets) {
+  n = effective_n(n, n_dev);
   const int b = threadIdx.x;
   if (b >= world_size) return;
   const int64_t beg = hist[(int64_t)b * nblocks];
@@ -57,13 +59,14 @@ __global__ void k_bucket_sizes(const int32_t* __restrict__ hist, int nblocks,
 }
 
 __global__ void __launch_bounds__(kBucketBlock)
-k_bucket_scatter(const int64_t* __restrict__ ids, int64_t n,
+k_bucket_scatter(const int64_t* __restrict__ ids, int64_t n, const int64_t* __restrict__ n_dev,
                  const int64_t* __restrict__ min_vids, OwnerParams p,
                  const int32_t* __restrict__ hist, int nblocks,
                  int64_t* __restrict__ sorted, int64_t* __restrict__ perm) {
   __shared__ int64_t mv[kMaxRanks + 1];
   __shared__ int warp_cnt[kBucketBlock / 32][kMaxRanks];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  n = effective_n(n, n_dev);
   if (threadIdx.x <= p.world_size) mv[threadIdx.x] = min_vids[threadIdx.x];
   for (int t = threadIdx.x; t < (kBucketBlock / 32) * kMaxRanks; t += blockDim.x)
     (&warp_cnt[0][0])[t] = 0;
@@ -103,8 +106,9 @@ k_bucket_scatter(const int64_t* __restrict__ ids, int64_t n,
 constexpr int kUniqBlock = 1024;
 
 __global__ void __launch_bounds__(256)
-k_uniq_mark(const int64_t* __restrict__ ids, int64_t n, int64_t lo, int64_t hi,
-            uint32_t* __restrict__ bitmap, int32_t* status) {
+k_uniq_mark(const int64_t* __restrict__ ids, int64_t n, const int64_t* __restrict__ n_dev,
+            int64_t lo, int64_t hi, uint32_t* __restrict__ bitmap, int32_t* status) {
+  n = effective_n(n, n_dev);
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   int flags = 0;
@@ -154,10 +158,11 @@ k_uniq_emit(const uint32_t* __restrict__ bitmap, int64_t nwords, int64_t lo,
 }
 
 __global__ void __launch_bounds__(256)
-k_uniq_inverse(const int64_t* __restrict__ ids, int64_t n, int64_t lo, int64_t hi,
-               const uint32_t* __restrict__ bitmap,
+k_uniq_inverse(const int64_t* __restrict__ ids, int64_t n, const int64_t* __restrict__ n_dev,
+               int64_t lo, int64_t hi, const uint32_t* __restrict__ bitmap,
                const uint32_t* __restrict__ word_prefix,
                int64_t* __restrict__ out_inverse) {
+  n = effective_n(n, n_dev);
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (; i < n; i += stride) {
@@ -182,7 +187,7 @@ extern "C" size_t apt_bucket_workspace_bytes(int64_t num_ids, int world_size) {
 }
 
 extern "C" int apt_bucket_by_owner(const int64_t* ids, int64_t num_ids,
-                                   const int64_t* min_vids, int world_size,
+                                   const int64_t* num_ids_dev, const int64_t* min_vids, int world_size,
                                    int64_t shuffle_id_offset, int rank,
                                    int node_beg, int node_end, void* workspace,
                                    size_t workspace_bytes, int64_t* out_sorted,
@@ -218,11 +223,11 @@ extern "C" int apt_bucket_by_owner(const int64_t* ids, int64_t num_ids,
   const int nblocks = (int)ceil_div(num_ids, kBucketBlock);
   int32_t* hist = (int32_t*)workspace;
   ProfScope prof("bucket", s);
-  APT_LAUNCH(k_bucket_count, nblocks, kBucketBlock, 0, s, ids, num_ids, min_vids, p, hist, nblocks);
+  APT_LAUNCH(k_bucket_count, nblocks, kBucketBlock, 0, s, ids, num_ids, num_ids_dev, min_vids, p, hist, nblocks);
   APT_LAUNCH(k_scan_blocks, 1, 1024, 0, s, hist, nblocks * world_size, (int64_t*)nullptr);
-  APT_LAUNCH(k_bucket_sizes, 1, 32, 0, s, hist, nblocks, world_size, num_ids,
+  APT_LAUNCH(k_bucket_sizes, 1, 32, 0, s, hist, nblocks, world_size, num_ids, num_ids_dev,
              out_bucket_sizes, out_bucket_offsets);
-  APT_LAUNCH(k_bucket_scatter, nblocks, kBucketBlock, 0, s, ids, num_ids, min_vids, p, hist,
+  APT_LAUNCH(k_bucket_scatter, nblocks, kBucketBlock, 0, s, ids, num_ids, num_ids_dev, min_vids, p, hist,
              nblocks, out_sorted, out_perm);
   return APT_OK;
 }
@@ -257,7 +262,8 @@ extern "C" size_t apt_unique_workspace_bytes(int64_t id_range) {
   return apt::uniq_layout(id_range, nullptr, nullptr);
 }
 
-extern "C" int apt_unique_sorted(const int64_t* ids, int64_t num_ids, int64_t id_lo,
+extern "C" int apt_unique_sorted(const int64_t* ids, int64_t num_ids,
+                                 const int64_t* num_ids_dev, int64_t id_lo,
                                  int64_t id_hi, void* workspace, size_t workspace_bytes,
                                  int64_t* out_unique, int64_t* out_inverse,
                                  int64_t* out_num_unique, int32_t* status_word,
@@ -285,12 +291,12 @@ extern "C" int apt_unique_sorted(const int64_t* ids, int64_t num_ids, int64_t id
   ProfScope prof("unique_sorted", s);
   APT_CUDA(cudaMemsetAsync(ws.bitmap, 0, (size_t)ws.nwords * 4, s));
   const int g = wave_grid(ceil_div(num_ids, 256), 8);
-  APT_LAUNCH(k_uniq_mark, g, 256, 0, s, ids, num_ids, id_lo, id_hi, ws.bitmap, status_word);
+  APT_LAUNCH(k_uniq_mark, g, 256, 0, s, ids, num_ids, num_ids_dev, id_lo, id_hi, ws.bitmap, status_word);
   APT_LAUNCH(k_uniq_count, ws.nblocks, kUniqBlock, 0, s, ws.bitmap, ws.nwords, ws.block_sums);
   APT_LAUNCH(k_scan_blocks, 1, 1024, 0, s, ws.block_sums, ws.nblocks, out_num_unique);
   APT_LAUNCH(k_uniq_emit, ws.nblocks, kUniqBlock, 0, s, ws.bitmap, ws.nwords, id_lo,
              ws.block_sums, ws.word_prefix, out_unique);
-  APT_LAUNCH(k_uniq_inverse, g, 256, 0, s, ids, num_ids, id_lo, id_hi, ws.bitmap,
+  APT_LAUNCH(k_uniq_inverse, g, 256, 0, s, ids, num_ids, num_ids_dev, id_lo, id_hi, ws.bitmap,
              ws.word_prefix, out_inverse);
   return APT_OK;
 }

@@ -137,6 +137,16 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
+// Sizes may live on the device: an operator chained behind another one takes
+// its element count from a device word (what the previous kernel produced), so
+// that the host never has to wait for it. `n_host` is then only an upper bound
+// that sized the grid and the buffers.
+__device__ __forceinline__ int64_t effective_n(int64_t n_host, const int64_t* n_dev) {
+  if (!n_dev) return n_host;
+  const int64_t v = *n_dev;
+  return v < 0 ? 0 : (v < n_host ? v : n_host);
+}
+
 // Exclusive scan of one int per thread over a block of up to 1024 threads.
 // Returns the thread's exclusive prefix; *total gets the block sum (all threads).
 // `warp_sums` is a shared array of 33 ints. Ends with a __syncthreads().

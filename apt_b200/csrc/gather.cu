@@ -45,11 +45,12 @@ static size_t gather_layout(int64_t n, char* base, GatherWs* ws) {
 }
 
 __global__ void __launch_bounds__(256)
-k_classify(const int64_t* __restrict__ index, int64_t n,
+k_classify(const int64_t* __restrict__ index, int64_t n, const int64_t* __restrict__ n_dev,
            const int64_t* __restrict__ pos_map, int64_t num_nodes,
            int64_t num_dev_rows, int64_t num_uva_rows, GatherWs ws,
            int32_t* status) {
   const int lane = threadIdx.x & 31;
+  n = effective_n(n, n_dev);
   int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   int flags = 0;
@@ -103,9 +104,10 @@ __device__ __forceinline__ uint2 zero_vec<uint2>() { return make_uint2(0, 0); }
 // (src_pos == -1), or belong to the miss kernel (src_pos < -1).
 template <typename V>
 __global__ void __launch_bounds__(kGatherBlock)
-k_copy_hits(int64_t n, const int64_t* __restrict__ src_pos,
+k_copy_hits(int64_t n, const int64_t* __restrict__ n_dev, const int64_t* __restrict__ src_pos,
             const char* __restrict__ dev_feats, int64_t row_bytes,
             char* __restrict__ out) {
+  n = effective_n(n, n_dev);
   const int lane = threadIdx.x & 31;
   const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
   const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -312,7 +314,7 @@ extern "C" size_t apt_gather_workspace_bytes(int64_t num_rows) {
 }
 
 extern "C" int apt_gather_rows(const int64_t* index, int64_t num_rows,
-                               const int64_t* feat_pos_map, int64_t num_nodes,
+                               const int64_t* num_rows_dev, const int64_t* feat_pos_map, int64_t num_nodes,
                                const void* dev_feats, int64_t num_dev_rows,
                                int64_t dev_row_bytes, const void* uva_feats,
                                int64_t num_uva_rows, int64_t uva_row_bytes,
@@ -354,7 +356,7 @@ extern "C" int apt_gather_rows(const int64_t* index, int64_t num_rows,
   {
     ProfScope prof("gather_classify", s);
     const int grid = wave_grid(ceil_div(num_rows, 256), 8);
-    APT_LAUNCH(k_classify, grid, 256, 0, s, index, num_rows, feat_pos_map, num_nodes,
+    APT_LAUNCH(k_classify, grid, 256, 0, s, index, num_rows, num_rows_dev, feat_pos_map, num_nodes,
                num_dev_rows, num_uva_rows, ws, status_word);
   }
   int dev = 0;
@@ -384,8 +386,8 @@ extern "C" int apt_gather_rows(const int64_t* index, int64_t num_rows,
   do {                                                                          \
     ProfScope prof("gather_hit", s);                                            \
     const int grid = wave_grid(ceil_div(num_rows, (kGatherBlock / 32) * kRowsPerWarp), 8, g_hit_waves); \
-    APT_LAUNCH(k_copy_hits<V>, grid, kGatherBlock, 0, s, num_rows, ws.src_pos,  \
-               devp, dev_row_bytes, outp);                                      \
+    APT_LAUNCH(k_copy_hits<V>, grid, kGatherBlock, 0, s, num_rows, num_rows_dev, \
+               ws.src_pos, devp, dev_row_bytes, outp);                          \
   } while (0)
 #define APT_BY_WIDTH(W, MACRO)                                                  \
   do {                                                                          \
@@ -509,8 +511,8 @@ extern "C" int apt_gather_rows_static(const int64_t* index, int64_t num_rows,
   APT_CUDA(cudaMemsetAsync(ws.miss_count, 0, sizeof(int32_t), s));
   {
     const int grid = wave_grid(ceil_div(num_rows, 256), 8);
-    APT_LAUNCH(k_classify, grid, 256, 0, s, index, num_rows, feat_pos_map, num_nodes,
-               num_dev_rows, num_uva_rows, ws, status_word);
+    APT_LAUNCH(k_classify, grid, 256, 0, s, index, num_rows, (const int64_t*)nullptr, feat_pos_map,
+               num_nodes, num_dev_rows, num_uva_rows, ws, status_word);
   }
   const char* devp = (const char*)dev_feats;
   const char* uvap = (const char*)uva_feats;
@@ -522,8 +524,8 @@ extern "C" int apt_gather_rows_static(const int64_t* index, int64_t num_rows,
 #define APT_SHITS(V)                                                            \
   do {                                                                          \
     const int grid = wave_grid(ceil_div(num_rows, (kGatherBlock / 32) * kRowsPerWarp), 8, 4); \
-    APT_LAUNCH(k_copy_hits<V>, grid, kGatherBlock, 0, s, num_rows, ws.src_pos,  \
-               devp, dev_row_bytes, outp);                                      \
+    APT_LAUNCH(k_copy_hits<V>, grid, kGatherBlock, 0, s, num_rows,              \
+               (const int64_t*)nullptr, ws.src_pos, devp, dev_row_bytes, outp); \
   } while (0)
 #define APT_SBY_WIDTH(W, MACRO)                                                 \
   do {                                                                          \

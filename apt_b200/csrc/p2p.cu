@@ -183,22 +183,28 @@ __global__ void k_p2p_wait(const char* local_base, int world_size, int parity,
                            uint32_t epoch, int64_t timeout_ns,
                            int64_t* __restrict__ out_counts, int32_t* status) {
   const int r = threadIdx.x;
-  if (r >= world_size) return;
-  const uint64_t* flag = (const uint64_t*)local_base + (size_t)parity * kP2pMaxRanks + r;
+  const bool live = r < world_size;
+  const uint64_t* flag = (const uint64_t*)local_base + (size_t)parity * kP2pMaxRanks + (live ? r : 0);
   const uint64_t t0 = global_timer_ns();
-  uint64_t v = ld_acquire_sys(flag);
+  uint64_t v = live ? ld_acquire_sys(flag) : ((uint64_t)epoch << 32);
   // Bounded both by wall time and by an iteration count, in case the timer stalls.
   for (uint64_t it = 0; (uint32_t)(v >> 32) != epoch && it < (1ull << 34); ++it) {
     if ((it & 63) == 63 && (int64_t)(global_timer_ns() - t0) > timeout_ns) break;
     __nanosleep(64);
     v = ld_acquire_sys(flag);
   }
+  if (!live) v = (uint64_t)epoch << 32;  // lanes beyond the world contribute nothing
+  int64_t got = 0;
   if ((uint32_t)(v >> 32) == epoch) {
-    out_counts[r] = (int64_t)(uint32_t)v;
+    got = (int64_t)(uint32_t)v;
   } else {
-    out_counts[r] = 0;
     atomicOr(status, APT_FLAG_PEER_TIMEOUT);
   }
+  if (live) out_counts[r] = got;
+  // total over the peers, for operators chained behind the exchange
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) got += __shfl_down_sync(0xffffffffu, got, d);
+  if (r == 0) out_counts[world_size] = got;
 }
 
 // mode 0: dst row j = concatenation row j; 1: dst row i = concat row index[i];

@@ -8,6 +8,7 @@
 // the first-occurrence flags into new ids, which makes the result independent
 // of the table layout and of thread scheduling.
 //
+//   k_clear    empties the slots this call will use
 //   k_insert   items -> table (CAS on the key, atomicMin on the position),
 //              remembers each item's slot
 //   k_count    per-block number of first occurrences
@@ -23,16 +24,39 @@ constexpr int kRelabelBlock = 1024;
 
 struct RelabelWs {
   int64_t* keys;     // [cap] -1 = empty
-  int32_t* min_pos;  // [cap] initialised to 0x7f7f7f7f by a byte memset
+  int32_t* min_pos;  // [cap] 0x7f7f7f7f = none yet
   int32_t* new_id;   // [cap]
   int32_t* slot_of;  // [n]
   int32_t* block_sums;  // [nblocks + 1]
-  uint32_t cap;
+  uint32_t cap;      // capacity for the host-side (upper bound) item count
   int nblocks;
 };
 
-static inline uint32_t relabel_capacity(int64_t n) {
+// Problem size as the kernels see it. With device-side counts the number of
+// seeds comes from a device word and every seed brings `per_seed` neighbours;
+// the table then only uses the capacity the real item count needs, so clearing
+// and probing cost what the real size costs, not what the upper bound would.
+struct RelabelDims {
+  int64_t S, n;
+  uint32_t cap;
+};
+
+__host__ __device__ inline uint32_t relabel_capacity(int64_t n) {
   return (uint32_t)(n + n / 2 + 64);
+}
+
+__device__ __forceinline__ RelabelDims relabel_dims(int64_t S_host, int64_t M_host,
+                                                    const int64_t* S_dev, int64_t per_seed) {
+  RelabelDims d;
+  if (S_dev) {
+    d.S = effective_n(S_host, S_dev);
+    d.n = d.S + d.S * per_seed;
+  } else {
+    d.S = S_host;
+    d.n = S_host + M_host;
+  }
+  d.cap = relabel_capacity(d.n);
+  return d;
 }
 
 static size_t relabel_layout(int64_t n, char* base, RelabelWs* ws) {
@@ -76,16 +100,32 @@ __device__ __forceinline__ int64_t item_at(const int64_t* seeds, int64_t S,
   return i < S ? seeds[i] : nbrs[i - S];
 }
 
+// Empties the slots the real item count will use (keys = -1, min_pos = none).
+__global__ void __launch_bounds__(256)
+k_clear(int64_t S_host, int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed,
+        RelabelWs ws) {
+  const RelabelDims d = relabel_dims(S_host, M_host, S_dev, per_seed);
+  // two keys per 16-byte store; cap is rounded up to even inside the padded arrays
+  const int64_t pairs = ((int64_t)d.cap + 1) / 2;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < pairs; i += stride) {
+    ((uint4*)ws.keys)[i] = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);
+    ((uint2*)ws.min_pos)[i] = make_uint2(0x7f7f7f7fu, 0x7f7f7f7fu);
+  }
+}
+
 __global__ void __launch_bounds__(kRelabelBlock)
-k_insert(const int64_t* __restrict__ seeds, int64_t S,
-         const int64_t* __restrict__ nbrs, int64_t n, RelabelWs ws,
+k_insert(const int64_t* __restrict__ seeds, int64_t S_host, const int64_t* __restrict__ nbrs,
+         int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed, RelabelWs ws,
          int32_t* status) {
+  const RelabelDims d = relabel_dims(S_host, M_host, S_dev, per_seed);
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
-  const int64_t key = item_at(seeds, S, nbrs, i);
-  uint32_t pos = (uint32_t)(((uint64_t)hash_id(key) * ws.cap) >> 32);
+  if (i >= d.n) return;
+  const int64_t key = item_at(seeds, d.S, nbrs, i);
+  uint32_t pos = (uint32_t)(((uint64_t)hash_id(key) * d.cap) >> 32);
   unsigned long long* keys = (unsigned long long*)ws.keys;
-  for (uint32_t probe = 0; probe < ws.cap; ++probe) {
+  for (uint32_t probe = 0; probe < d.cap; ++probe) {
     unsigned long long prev = keys[pos];
     if (prev == ~0ull) prev = atomicCAS(keys + pos, ~0ull, (unsigned long long)key);
     if (prev == ~0ull || prev == (unsigned long long)key) {
@@ -93,7 +133,7 @@ k_insert(const int64_t* __restrict__ seeds, int64_t S,
       ws.slot_of[i] = (int32_t)pos;
       return;
     }
-    pos = pos + 1 == ws.cap ? 0 : pos + 1;
+    pos = pos + 1 == d.cap ? 0 : pos + 1;
   }
   ws.slot_of[i] = -1;
   atomicOr(status, APT_FLAG_TABLE_FULL);
@@ -106,35 +146,41 @@ __device__ __forceinline__ int is_first(const RelabelWs& ws, int64_t i, int64_t 
 }
 
 __global__ void __launch_bounds__(kRelabelBlock)
-k_count(int64_t n, RelabelWs ws) {
+k_count(int64_t S_host, int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed,
+        RelabelWs ws) {
+  const RelabelDims d = relabel_dims(S_host, M_host, S_dev, per_seed);
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int f = is_first(ws, i, n);
+  const int f = is_first(ws, i, d.n);
   const int c = __syncthreads_count(f);
   if (threadIdx.x == 0) ws.block_sums[blockIdx.x] = c;
 }
 
 __global__ void __launch_bounds__(kRelabelBlock)
-k_assign(const int64_t* __restrict__ seeds, int64_t S,
-         const int64_t* __restrict__ nbrs, int64_t n, RelabelWs ws,
+k_assign(const int64_t* __restrict__ seeds, int64_t S_host, const int64_t* __restrict__ nbrs,
+         int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed, RelabelWs ws,
          int64_t* __restrict__ out_unique) {
   __shared__ int warp_sums[33];
+  const RelabelDims d = relabel_dims(S_host, M_host, S_dev, per_seed);
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int f = is_first(ws, i, n);
+  const int f = is_first(ws, i, d.n);
   int total;
   const int ex = block_exclusive_scan(f, warp_sums, &total);
   if (f) {
     const int32_t id = ws.block_sums[blockIdx.x] + ex;
-    out_unique[id] = item_at(seeds, S, nbrs, i);
+    out_unique[id] = item_at(seeds, d.S, nbrs, i);
     ws.new_id[ws.slot_of[i]] = id;
   }
 }
 
 __global__ void __launch_bounds__(256)
-k_relabel(int64_t S, int64_t M, RelabelWs ws, int64_t* __restrict__ out) {
+k_relabel(int64_t S_host, int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed,
+          RelabelWs ws, int64_t* __restrict__ out) {
+  const RelabelDims d = relabel_dims(S_host, M_host, S_dev, per_seed);
+  const int64_t M = d.n - d.S;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (; i < M; i += stride) {
-    const int32_t slot = ws.slot_of[S + i];
+    const int32_t slot = ws.slot_of[d.S + i];
     out[i] = slot >= 0 ? (int64_t)ws.new_id[slot] : -1;
   }
 }
@@ -147,17 +193,22 @@ extern "C" size_t apt_relabel_workspace_bytes(int64_t num_items) {
 }
 
 extern "C" int apt_relabel_csc(const int64_t* seeds, int64_t num_seeds,
-                               const int64_t* neighbors, int64_t num_neighbors,
-                               void* workspace, size_t workspace_bytes,
+                               const int64_t* num_seeds_dev, const int64_t* neighbors,
+                               int64_t num_neighbors, void* workspace, size_t workspace_bytes,
                                int64_t* out_unique, int64_t* out_relabeled,
-                               int64_t* out_num_unique, int32_t* status_word,
-                               void* stream) {
+                               int64_t* out_num_unique, int32_t* status_word, void* stream) {
   using namespace apt;
   APT_CHECK_ARG(num_seeds >= 0 && num_neighbors >= 0, "apt_relabel_csc: negative size");
   const int64_t n = num_seeds + num_neighbors;
   APT_CHECK_ARG(n < (int64_t)0x7f000000, "apt_relabel_csc: %lld items exceed the 31-bit position range",
                 (long long)n);
   APT_CHECK_ARG(out_num_unique && status_word, "apt_relabel_csc: null output word");
+  int64_t per_seed = 0;
+  if (num_seeds_dev) {
+    APT_CHECK_ARG(num_seeds > 0 && num_neighbors % num_seeds == 0,
+                  "apt_relabel_csc: with a device-side seed count the neighbours must be a fixed number per seed");
+    per_seed = num_neighbors / num_seeds;
+  }
   cudaStream_t s = (cudaStream_t)stream;
   if (n == 0) {
     APT_CUDA(cudaMemsetAsync(out_num_unique, 0, sizeof(int64_t), s));
@@ -174,15 +225,20 @@ extern "C" int apt_relabel_csc(const int64_t* seeds, int64_t num_seeds,
     return APT_ERR_CAPACITY;
   }
   ProfScope prof("relabel", s);
-  APT_CUDA(cudaMemsetAsync(ws.keys, 0xff, (size_t)ws.cap * 8, s));
-  APT_CUDA(cudaMemsetAsync(ws.min_pos, 0x7f, (size_t)ws.cap * 4, s));
-  APT_LAUNCH(k_insert, ws.nblocks, kRelabelBlock, 0, s, seeds, num_seeds, neighbors, n, ws, status_word);
-  APT_LAUNCH(k_count, ws.nblocks, kRelabelBlock, 0, s, n, ws);
+  {
+    const int grid = wave_grid(ceil_div(((int64_t)ws.cap + 1) / 2, 256), 8, 2);
+    APT_LAUNCH(k_clear, grid, 256, 0, s, num_seeds, num_neighbors, num_seeds_dev, per_seed, ws);
+  }
+  APT_LAUNCH(k_insert, ws.nblocks, kRelabelBlock, 0, s, seeds, num_seeds, neighbors, num_neighbors,
+             num_seeds_dev, per_seed, ws, status_word);
+  APT_LAUNCH(k_count, ws.nblocks, kRelabelBlock, 0, s, num_seeds, num_neighbors, num_seeds_dev, per_seed, ws);
   APT_LAUNCH(k_scan_blocks, 1, 1024, 0, s, ws.block_sums, ws.nblocks, out_num_unique);
-  APT_LAUNCH(k_assign, ws.nblocks, kRelabelBlock, 0, s, seeds, num_seeds, neighbors, n, ws, out_unique);
+  APT_LAUNCH(k_assign, ws.nblocks, kRelabelBlock, 0, s, seeds, num_seeds, neighbors, num_neighbors,
+             num_seeds_dev, per_seed, ws, out_unique);
   if (num_neighbors > 0) {
     const int grid = wave_grid(ceil_div(num_neighbors, 256), 8);
-    APT_LAUNCH(k_relabel, grid, 256, 0, s, num_seeds, num_neighbors, ws, out_relabeled);
+    APT_LAUNCH(k_relabel, grid, 256, 0, s, num_seeds, num_neighbors, num_seeds_dev, per_seed, ws,
+               out_relabeled);
   }
   return APT_OK;
 }

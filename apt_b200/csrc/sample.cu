@@ -23,13 +23,14 @@ __device__ __forceinline__ int64_t mod_deg(uint32_t word, int64_t deg) {
 template <int G>
 __global__ void __launch_bounds__(256)
 sample_replace_kernel(const int64_t* __restrict__ seeds, int64_t num_seeds,
-                      int fanout, const int64_t* __restrict__ adj_pos_map,
+                      const int64_t* __restrict__ num_seeds_dev, int fanout, const int64_t* __restrict__ adj_pos_map,
                       int64_t num_nodes, const int64_t* __restrict__ dev_indptr,
                       const int64_t* __restrict__ dev_indices,
                       const int64_t* __restrict__ uva_indptr,
                       const int64_t* __restrict__ uva_indices, uint32_t k0,
                       uint32_t k1, uint32_t call_id,
                       int64_t* __restrict__ out, int32_t* status) {
+  num_seeds = effective_n(num_seeds, num_seeds_dev);
   const int sub = threadIdx.x % G;
   const int64_t groups_per_block = blockDim.x / G;
   int64_t j = (int64_t)blockIdx.x * groups_per_block + threadIdx.x / G;
@@ -77,13 +78,14 @@ sample_replace_kernel(const int64_t* __restrict__ seeds, int64_t num_seeds,
 // vote on the collision.
 __global__ void __launch_bounds__(256)
 sample_floyd_kernel(const int64_t* __restrict__ seeds, int64_t num_seeds,
-                    int fanout, const int64_t* __restrict__ adj_pos_map,
+                    const int64_t* __restrict__ num_seeds_dev, int fanout, const int64_t* __restrict__ adj_pos_map,
                     int64_t num_nodes, const int64_t* __restrict__ dev_indptr,
                     const int64_t* __restrict__ dev_indices,
                     const int64_t* __restrict__ uva_indptr,
                     const int64_t* __restrict__ uva_indices, uint32_t k0,
                     uint32_t k1, uint32_t call_id, int64_t* __restrict__ out,
                     int32_t* status) {
+  num_seeds = effective_n(num_seeds, num_seeds_dev);
   const int lane = threadIdx.x & 31;
   const int64_t warps_per_block = blockDim.x >> 5;
   int64_t j = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
@@ -140,7 +142,7 @@ sample_floyd_kernel(const int64_t* __restrict__ seeds, int64_t num_seeds,
 }  // namespace apt
 
 extern "C" int apt_sample_csc_fanout(
-    const int64_t* seeds, int64_t num_seeds, int fanout,
+    const int64_t* seeds, int64_t num_seeds, const int64_t* num_seeds_dev, int fanout,
     const int64_t* adj_pos_map, int64_t num_nodes, const int64_t* dev_indptr,
     const int64_t* dev_indices, const int64_t* uva_indptr,
     const int64_t* uva_indices, uint64_t key, uint32_t call_id, int replace,
@@ -159,7 +161,7 @@ extern "C" int apt_sample_csc_fanout(
   ProfScope prof("sample", s);
   if (!replace) {
     const int grid = wave_grid(ceil_div(num_seeds, 8), 8);
-    APT_LAUNCH(sample_floyd_kernel, grid, 256, 0, s, seeds, num_seeds, fanout,
+    APT_LAUNCH(sample_floyd_kernel, grid, 256, 0, s, seeds, num_seeds, num_seeds_dev, fanout,
                adj_pos_map, num_nodes, dev_indptr, dev_indices, uva_indptr,
                uva_indices, k0, k1, call_id, out_neighbors, status_word);
     return APT_OK;
@@ -168,7 +170,7 @@ extern "C" int apt_sample_csc_fanout(
   do {                                                                         \
     const int grid = wave_grid(ceil_div(num_seeds, 256 / G), 8);               \
     APT_LAUNCH(sample_replace_kernel<G>, grid, 256, 0, s, seeds, num_seeds,    \
-               fanout, adj_pos_map, num_nodes, dev_indptr, dev_indices,        \
+               num_seeds_dev, fanout, adj_pos_map, num_nodes, dev_indptr, dev_indices,        \
                uva_indptr, uva_indices, k0, k1, call_id, out_neighbors,        \
                status_word);                                                   \
   } while (0)

@@ -47,6 +47,11 @@ class LocalExchange:
         off = offsets.cpu()
         return sorted_ids, off, off.clone()
 
+    def exchange_ids_enqueue(self, sorted_ids, sizes, offsets):
+        """Stream-ordered variant without a host read: (recv buffer, device counts
+        int64[world_size + 1] with the total last)."""
+        return sorted_ids, torch.cat([offsets, offsets])
+
     def exchange_rows(self, inputs, send_offset, recv_offset, permutation, fwd):
         from . import ops
 
@@ -81,6 +86,12 @@ class NcclExchange:
         recv_counts = [int(x) for x in recv_sizes.tolist()]
         recv = self._a2a(sorted_ids.view(-1, 1), send_counts, recv_counts, 1).view(-1)
         return recv, torch.tensor(recv_counts).cumsum(0), offsets.cpu()
+
+    def exchange_ids_enqueue(self, sorted_ids, sizes, offsets):
+        # the library all-to-all needs the sizes on the host: this baseline synchronises
+        recv, recv_offset, _ = self.exchange_ids(sorted_ids, sizes, offsets)
+        counts = torch.cat([torch.tensor(_counts(recv_offset)), recv_offset[-1:]]).to(sorted_ids.device)
+        return recv, counts
 
     def exchange_rows(self, inputs, send_offset, recv_offset, permutation, fwd):
         from . import ops
@@ -171,8 +182,7 @@ class P2PExchange:
         ws = st.world_size
         n = sorted_ids.numel()
         self._check_capacity(n, 8)
-        words = st.words()
-        counts_dev = torch.empty(ws, dtype=torch.int64, device=sorted_ids.device)
+        counts_dev = torch.empty(ws + 1, dtype=torch.int64, device=sorted_ids.device)
         self._push(sorted_ids, None, 0, offsets, n, 8)
         self._wait(counts_dev)
         # one host read brings the received counts, my bucket offsets and the status word
@@ -183,7 +193,22 @@ class P2PExchange:
         total = int(recv_offset[-1])
         recv = torch.empty(total, dtype=torch.int64, device=sorted_ids.device)
         self._pull(counts_dev, None, 0, total, total, 8, recv)
-        return recv, recv_offset, host[ws:].clone()
+        return recv, recv_offset, host[ws + 1:].clone()
+
+    def exchange_ids_enqueue(self, sorted_ids, sizes, offsets):
+        """Stream-ordered seed exchange without a host read. Every rank is taken
+        to send at most sorted_ids.numel() ids (the ranks run the same batch
+        shape), which bounds what this rank can receive."""
+        st = self.state
+        ws = st.world_size
+        n = sorted_ids.numel()
+        self._check_capacity(n, 8)
+        counts_dev = torch.empty(ws + 1, dtype=torch.int64, device=sorted_ids.device)
+        self._push(sorted_ids, None, 0, offsets, n, 8)
+        self._wait(counts_dev)
+        recv = torch.empty(ws * n, dtype=torch.int64, device=sorted_ids.device)
+        self._pull(counts_dev, None, 0, ws * n, ws * n, 8, recv)
+        return recv, counts_dev
 
     def exchange_rows(self, inputs, send_offset, recv_offset, permutation, fwd):
         st = self.state
@@ -191,7 +216,7 @@ class P2PExchange:
         row_bytes = inputs.shape[1] * inputs.element_size()
         self._check_capacity(max(_counts(send_offset)), row_bytes)
         off_dev = self._offsets_to_device(send_offset)
-        counts_dev = torch.empty(ws, dtype=torch.int64, device=inputs.device)
+        counts_dev = torch.empty(ws + 1, dtype=torch.int64, device=inputs.device)
         rows_in = inputs.shape[0]
         total_out = int(recv_offset[-1])
         if fwd:
@@ -211,7 +236,7 @@ class P2PExchange:
         row_bytes = expand * inp.element_size()
         self._check_capacity(max(_counts(send_offset)), row_bytes)
         off_dev = self._offsets_to_device(send_offset)
-        counts_dev = torch.empty(st.world_size, dtype=torch.int64, device=inp.device)
+        counts_dev = torch.empty(st.world_size + 1, dtype=torch.int64, device=inp.device)
         rows_in = int(send_offset[-1])
         total_out = int(recv_offset[-1])
         self._push(inp, None, 0, off_dev, rows_in, row_bytes)

@@ -113,6 +113,7 @@ class NPCState:
         self._words = None
         self._host_words = None
         self._side_stream = None
+        self.prefetched = None  # (input ids, gathered rows) left by a sampler that gathers ahead
         self.exchange = None  # set by apt_b200.exchange.make_exchange at init
         self.shuffle_backend = os.environ.get("APT_SHUFFLE_BACKEND", "p2p")
         self.p2p_region_bytes = int(os.environ.get("APT_P2P_REGION_MB", "256")) << 20
@@ -130,15 +131,22 @@ class NPCState:
             self._ws[key] = buf
         return buf
 
+    NUM_WORDS = 128
+
     def words(self) -> torch.Tensor:
-        """int64[8] device words: [0..6] small results (counts), [7] status flags."""
+        """int64[128] device words: [0..126] small results (counts a kernel leaves for
+        the next kernel and, later, for the host), [127] status flags."""
         if self._words is None or self._words.device != self.device():
-            self._words = torch.zeros(8, dtype=torch.int64, device=self.device())
-            self._host_words = torch.zeros(8, dtype=torch.int64).pin_memory()
+            self._words = torch.zeros(self.NUM_WORDS, dtype=torch.int64, device=self.device())
+            self._host_words = torch.zeros(self.NUM_WORDS, dtype=torch.int64).pin_memory()
         return self._words
 
+    def word(self, k: int) -> torch.Tensor:
+        """One-element view of device word k (a device-side count)."""
+        return self.words()[k:k + 1]
+
     def status_ptr(self):
-        return ctypes.c_void_p(self.words().data_ptr() + 56)
+        return ctypes.c_void_p(self.words().data_ptr() + 8 * (self.NUM_WORDS - 1))
 
     def read_words(self) -> torch.Tensor:
         """Copies the device words to the host (one stream sync) and raises on
@@ -146,9 +154,9 @@ class NPCState:
         w = self.words()
         self._host_words.copy_(w, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-        flags = int(self._host_words[7]) & 0xFFFFFFFF
+        flags = int(self._host_words[self.NUM_WORDS - 1]) & 0xFFFFFFFF
         if flags & ~_lib.FLAG_ZERO_DEGREE:
-            w[7] = 0
+            w[self.NUM_WORDS - 1] = 0
             raise RuntimeError(f"apt_b200 device status flags 0x{flags:x}: " + _flag_text(flags))
         return self._host_words
 
@@ -275,7 +283,8 @@ def set_sampling(key: Optional[int] = None, call_id: Optional[int] = None, repla
 
 
 # -------------------------------------------------------------------- sampling
-def _sample(seeds: torch.Tensor, fanout: int) -> torch.Tensor:
+def _sample(seeds: torch.Tensor, fanout: int, n_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """n_dev: optional one-element device count; seeds.numel() is then an upper bound."""
     g = STATE.graph
     if g.uva_indptr is None:
         raise RuntimeError("mix_cache_graphs has not been called")
@@ -284,7 +293,7 @@ def _sample(seeds: torch.Tensor, fanout: int) -> torch.Tensor:
     call_id = STATE.sample_calls
     STATE.sample_calls += 1
     check(lib.apt_sample_csc_fanout(
-        _ptr(seeds), seeds.numel(), int(fanout), _ptr(g.adj_pos_map), g.num_total_nodes,
+        _ptr(seeds), seeds.numel(), _ptr(n_dev), int(fanout), _ptr(g.adj_pos_map), g.num_total_nodes,
         _ptr(g.dev_indptr), _ptr(g.dev_indices), _ptr(g.uva_indptr), _ptr(g.uva_indices),
         STATE.sample_key, call_id & 0xFFFFFFFF, 1 if STATE.sample_replace else 0,
         _ptr(out), STATE.status_ptr(), _stream()))
@@ -296,25 +305,31 @@ def local_sample_one_layer(seeds: torch.Tensor, fanout: int) -> List[torch.Tenso
     return [seeds, _sample(seeds, fanout)]
 
 
-def relabel_csc(seeds: torch.Tensor, neighbors: torch.Tensor) -> List[torch.Tensor]:
-    """RelabelCSC, src/relabel.cc:9-15: [all_unique, relabeled_neighbors]."""
-    seeds = _need_cuda(seeds, "seeds")
-    neighbors = _need_cuda(neighbors, "neighbors")
+def _relabel_enqueue(seeds, neighbors, n_dev, count_out):
+    """Enqueues the relabelling; the number of unique ids lands in the device
+    word `count_out`. Returns the full-length (upper bound) buffers."""
     n = seeds.numel() + neighbors.numel()
     uniq = torch.empty(n, dtype=torch.int64, device=seeds.device)
     rel = torch.empty(neighbors.numel(), dtype=torch.int64, device=seeds.device)
     nbytes = lib.apt_relabel_workspace_bytes(n)
     ws = STATE.workspace("relabel", nbytes)
-    words = STATE.words()
-    check(lib.apt_relabel_csc(_ptr(seeds), seeds.numel(), _ptr(neighbors), neighbors.numel(),
+    check(lib.apt_relabel_csc(_ptr(seeds), seeds.numel(), _ptr(n_dev), _ptr(neighbors), neighbors.numel(),
                               _ptr(ws), ws.numel(), _ptr(uniq), _ptr(rel),
-                              ctypes.c_void_p(words.data_ptr()), STATE.status_ptr(), _stream()))
+                              _ptr(count_out), STATE.status_ptr(), _stream()))
+    return uniq, rel
+
+
+def relabel_csc(seeds: torch.Tensor, neighbors: torch.Tensor) -> List[torch.Tensor]:
+    """RelabelCSC, src/relabel.cc:9-15: [all_unique, relabeled_neighbors]."""
+    seeds = _need_cuda(seeds, "seeds")
+    neighbors = _need_cuda(neighbors, "neighbors")
+    uniq, rel = _relabel_enqueue(seeds, neighbors, None, STATE.word(0))
     num_unique = int(STATE.read_words()[0])
     return [uniq[:num_unique], rel]
 
 
 # ---------------------------------------------------------------- seed shuffle
-def _bucket(seeds: torch.Tensor):
+def _bucket(seeds: torch.Tensor, n_dev: Optional[torch.Tensor] = None):
     s = STATE
     if s.shuffle_min_vids is None:
         raise RuntimeError("register_min_vids has not been called")
@@ -327,7 +342,8 @@ def _bucket(seeds: torch.Tensor):
     nbytes = lib.apt_bucket_workspace_bytes(n, s.world_size)
     ws = s.workspace("bucket", nbytes)
     node_beg = s.rank - s.rank % s.node_size
-    check(lib.apt_bucket_by_owner(_ptr(seeds), n, _ptr(s.shuffle_min_vids), s.world_size, s.shuffle_id_offset,
+    check(lib.apt_bucket_by_owner(_ptr(seeds), n, _ptr(n_dev), _ptr(s.shuffle_min_vids), s.world_size,
+                                  s.shuffle_id_offset,
                                   s.rank, node_beg, node_beg + s.node_size, _ptr(ws), ws.numel(),
                                   _ptr(sorted_ids), _ptr(perm), _ptr(sizes), _ptr(offsets), _stream()))
     return sorted_ids, perm, sizes, offsets
@@ -347,17 +363,21 @@ def unique_sorted(ids: torch.Tensor, id_lo: int, id_hi: int):
     """Sorted unique + inverse of ids in [id_lo, id_hi): torch::_unique2(sorted,
     return_inverse) of src/sampling.cc:58-59, via a bitmap over the id range."""
     ids = _need_cuda(ids, "ids")
+    uniq, inv = _unique_enqueue(ids, None, id_lo, id_hi, STATE.word(0))
+    num_unique = int(STATE.read_words()[0])
+    return uniq[:num_unique], inv
+
+
+def _unique_enqueue(ids, n_dev, id_lo, id_hi, count_out):
     n = ids.numel()
     rng = int(id_hi) - int(id_lo)
     uniq = torch.empty(min(n, max(rng, 0)), dtype=torch.int64, device=ids.device)
     inv = torch.empty(n, dtype=torch.int64, device=ids.device)
     nbytes = lib.apt_unique_workspace_bytes(rng)
     ws = STATE.workspace("unique", nbytes)
-    words = STATE.words()
-    check(lib.apt_unique_sorted(_ptr(ids), n, int(id_lo), int(id_hi), _ptr(ws), ws.numel(), _ptr(uniq), _ptr(inv),
-                                ctypes.c_void_p(words.data_ptr()), STATE.status_ptr(), _stream()))
-    num_unique = int(STATE.read_words()[0])
-    return uniq[:num_unique], inv
+    check(lib.apt_unique_sorted(_ptr(ids), n, _ptr(n_dev), int(id_lo), int(id_hi), _ptr(ws), ws.numel(), _ptr(uniq),
+                                _ptr(inv), _ptr(count_out), STATE.status_ptr(), _stream()))
+    return uniq, inv
 
 
 def _owned_range():
@@ -400,6 +420,17 @@ def load_subtensor(node_id: torch.Tensor) -> torch.Tensor:
     if f.feat_pos_map is None:
         raise RuntimeError("cache_feats_shared has not been called")
     node_id = _need_cuda(node_id, "node_id")
+    pre = STATE.prefetched
+    if pre is not None:
+        STATE.prefetched = None
+        ids, rows = pre
+        if ids.data_ptr() == node_id.data_ptr() and ids.numel() == node_id.numel():
+            return rows
+    return _gather_enqueue(node_id, None)
+
+
+def _gather_enqueue(node_id: torch.Tensor, n_dev: Optional[torch.Tensor]) -> torch.Tensor:
+    f = STATE.feat
     n = node_id.numel()
     esz = f.dev_feats.element_size()
     out = torch.empty((n, f.rank_feat_dim), dtype=f.dev_feats.dtype, device=node_id.device)
@@ -407,7 +438,7 @@ def load_subtensor(node_id: torch.Tensor) -> torch.Tensor:
     ws = STATE.workspace("gather", nbytes)
     side = STATE.side_stream() if f.uva_feats.shape[0] > 0 else None
     check(lib.apt_gather_rows(
-        _ptr(node_id), n, _ptr(f.feat_pos_map), f.num_total_nodes,
+        _ptr(node_id), n, _ptr(n_dev), _ptr(f.feat_pos_map), f.num_total_nodes,
         _ptr(f.dev_feats), f.dev_feats.shape[0], f.rank_feat_dim * esz,
         _ptr(f.uva_feats), f.uva_feats.shape[0], f.feat_dim * esz, f.feat_dim_offset * esz,
         _ptr(out), _ptr(ws), ws.numel(), STATE.status_ptr(), _stream(),

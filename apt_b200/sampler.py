@@ -3,7 +3,16 @@ MixedNeighborSampler (NP, python/npc/sampler.py:109-156) and of the DP branch
 of MixedPSNeighborSampler (:187-203), returning blocks as plain COO tensors
 instead of DGLBlock objects (DGL builds those from the same COO,
 python/npc/sampler.py:59-91).
+
+By default the whole mini-batch is enqueued without the host ever waiting for
+an intermediate size: each operator takes its element count from the device
+word the previous one wrote, buffers are sized for the no-duplicate upper
+bound, and one read at the end brings every count to the host, where the
+buffers are narrowed to their real lengths. The results are identical to
+calling the operators one by one (``chained=False``), which reads a count
+after every relabelling like the reference does (src/cuda/relabel.cu:119).
 """
+import os
 from dataclasses import dataclass
 from typing import List
 
@@ -26,24 +35,55 @@ class Block:
     fanout: int
 
 
+_COL_CACHE = {}
+
+
+def _coo_col(num_dst_max: int, num_dst: int, fanout: int, device) -> torch.Tensor:
+    """arange(num_dst).repeat_interleave(fanout) (python/npc/sampler.py:78) as a
+    prefix of a cached longer one."""
+    key = (fanout, device)
+    col = _COL_CACHE.get(key)
+    if col is None or col.numel() < num_dst_max * fanout:
+        col = torch.arange(0, num_dst_max, device=device).repeat_interleave(fanout)
+        _COL_CACHE[key] = col
+    return col[:num_dst * fanout]
+
+
 def create_block(seeds: torch.Tensor, neighbors: torch.Tensor, fanout: int) -> Block:
     unique_frontier, indices = ops.relabel_csc(seeds, neighbors)
     coo_col = torch.arange(0, seeds.numel(), device=indices.device).repeat_interleave(fanout)
     return Block(indices, coo_col, unique_frontier.numel(), seeds.numel(), unique_frontier, fanout)
 
 
+# Upper-bound buffers beyond this many bytes of gathered rows are not gathered
+# ahead of the size read; the gather then runs right after it with exact sizes.
+_PREFETCH_LIMIT_BYTES = 3 << 30
+
+
 class MixedNeighborSampler:
     """NP ("NPC") strategy: inner hops are sampled locally, the outermost hop at
     the owner of each frontier node (np_sample_and_shuffle). fanouts[0] is the
-    outermost hop, as in the reference's --fan_out (python/npc/utils/utils.py:428-432)."""
+    outermost hop, as in the reference's --fan_out (python/npc/utils/utils.py:428-432).
 
-    def __init__(self, rank: int, fanouts: List[int]):
+    chained            enqueue the whole mini-batch with device-side sizes (one host
+                       read per batch) instead of one read per operator
+    prefetch_features  also enqueue the feature gather of the input nodes before that
+                       read; the next ops.load_subtensor(input_nodes) returns it
+    """
+
+    def __init__(self, rank: int, fanouts: List[int], chained: bool = None, prefetch_features: bool = True):
         self.rank = rank
         self.fir_fanouts = list(fanouts[1:])
         self.las_fanouts = fanouts[0]
         self.num_layers = len(fanouts)
+        if chained is None:
+            chained = os.environ.get("APT_CHAINED_SAMPLER", "1") != "0"
+        self.chained = chained
+        self.prefetch_features = prefetch_features
 
     def sample(self, graph, seeds: torch.Tensor):
+        if self.chained:
+            return self._sample_chained(seeds)
         output_nodes = seeds
         blocks = []
         for fanout in reversed(self.fir_fanouts):
@@ -57,6 +97,67 @@ class MixedNeighborSampler:
         blocks.insert(0, block)
         seeds = block.src_ids
         return seeds, output_nodes, blocks, perm, send_offset, recv_offset, inverse_idx
+
+    def _sample_chained(self, seeds: torch.Tensor):
+        st = ops.STATE
+        ws = st.world_size
+        if self.num_layers > 14:
+            raise RuntimeError("the chained sampler keeps at most 14 hop counts")
+        seeds = ops._need_cuda(seeds, "seeds")
+        output_nodes = seeds
+        slot = 0
+        cur, cur_n, cur_slot = seeds, None, None
+        layers = []                      # (dst buffer, dst count slot, rel, uniq, uniq count slot, fanout)
+        for fanout in reversed(self.fir_fanouts):
+            nbr = ops._sample(cur, fanout, cur_n)
+            cnt = st.word(slot)
+            uniq, rel = ops._relabel_enqueue(cur, nbr, cur_n, cnt)
+            layers.append((cur, cur_slot, rel, uniq, slot, fanout))
+            cur, cur_n, cur_slot = uniq, cnt, slot
+            slot += 1
+        # outermost hop at the owners (NPSampleAndShuffle, src/sampling.cc:52-69)
+        sorted_ids, perm, sizes, offsets = ops._bucket(cur, cur_n)
+        recv, recv_counts = ops._exchange().exchange_ids_enqueue(sorted_ids, sizes, offsets)
+        total = recv_counts[ws:ws + 1]
+        lo, hi = ops._owned_range()
+        u_slot = slot
+        uniq2, inv = ops._unique_enqueue(recv, total, lo, hi, st.word(u_slot))
+        nbr = ops._sample(uniq2, self.las_fanouts, st.word(u_slot))
+        in_slot = slot + 1
+        uniq3, rel3 = ops._relabel_enqueue(uniq2, nbr, st.word(u_slot), st.word(in_slot))
+        rows = None
+        f = st.feat
+        if self.prefetch_features and f.feat_pos_map is not None and \
+                uniq3.numel() * f.rank_feat_dim * f.dev_feats.element_size() <= _PREFETCH_LIMIT_BYTES:
+            rows = ops._gather_enqueue(uniq3, st.word(in_slot))
+        # counts the host needs: per-peer received ids and my bucket offsets ride along in the word block
+        words = st.words()                          # [0..15] hop counts, [16..48] received, [64..95] bucket offsets
+        words[16:16 + ws + 1].copy_(recv_counts)
+        words[64:64 + ws].copy_(offsets)
+        host = st.read_words()                      # the one host read of the mini-batch
+        count = [int(host[k]) for k in range(in_slot + 1)]
+        recv_cnt = host[16:16 + ws].clone()
+        dev_offset = host[64:64 + ws].clone()
+        recv_offset = recv_cnt.cumsum(0)
+        total_recv = int(recv_offset[-1])
+
+        blocks = []
+        n_dst = seeds.numel()
+        for dst_buf, dst_slot, rel, uniq, u_s, fanout in layers:
+            n_src = count[u_s]
+            blocks.insert(0, Block(rel[:n_dst * fanout], _coo_col(dst_buf.numel(), n_dst, fanout, rel.device),
+                                   n_src, n_dst, uniq[:n_src], fanout))
+            n_dst = n_src
+        n_frontier = n_dst
+        n_owner_dst, n_in = count[u_slot], count[in_slot]
+        f0 = self.las_fanouts
+        blocks.insert(0, Block(rel3[:n_owner_dst * f0], _coo_col(uniq2.numel(), n_owner_dst, f0, rel3.device),
+                               n_in, n_owner_dst, uniq3[:n_in], f0))
+        input_nodes = uniq3[:n_in]
+        if rows is not None:
+            st.prefetched = (input_nodes, rows[:n_in])
+        return (input_nodes, output_nodes, blocks, perm[:n_frontier], recv_offset, dev_offset,
+                inv[:total_recv])
 
 
 class DPNeighborSampler:

@@ -11,6 +11,11 @@
  *  - Ids and offsets are int64_t, like the reference's IdType (src/utils.h:14).
  *  - `stream` is a cudaStream_t passed as void*. Calls are stream-ordered and
  *    never synchronise the host unless the comment says so.
+ *  - Sizes are host integers. Where an entry point also takes a `*_dev`
+ *    pointer, that device word (if not NULL) overrides the host size at run
+ *    time, the host size then being only an upper bound that sized grids and
+ *    buffers: a chain of operators can so run without the host ever reading
+ *    an intermediate count.
  *  - Outputs and workspaces are allocated by the caller. No entry point in
  *    this header allocates device memory except apt_p2p_create.
  *  - Return value: APT_OK or an apt_status; apt_last_error() gives the text.
@@ -92,7 +97,8 @@ int apt_set_tunable(const char* name, int64_t value);
  * adj_pos_map may be NULL: every node then reads (uva_indptr, uva_indices),
  * which may be plain device memory holding the whole graph.
  */
-int apt_sample_csc_fanout(const int64_t* seeds, int64_t num_seeds, int fanout,
+int apt_sample_csc_fanout(const int64_t* seeds, int64_t num_seeds,
+                          const int64_t* num_seeds_dev, int fanout,
                           const int64_t* adj_pos_map, int64_t num_nodes,
                           const int64_t* dev_indptr, const int64_t* dev_indices,
                           const int64_t* uva_indptr, const int64_t* uva_indices,
@@ -111,9 +117,12 @@ int apt_sample_csc_fanout(const int64_t* seeds, int64_t num_seeds, int fanout,
  *   out_num_unique int64[1] device word receiving U
  * workspace: apt_relabel_workspace_bytes(num_seeds + num_neighbors) bytes,
  * 256-byte aligned; contents need no initialisation.
+ * With num_seeds_dev the real seed count S comes from the device and the
+ * neighbours are taken to be S * (num_neighbors / num_seeds) (a fixed fanout).
  */
 size_t apt_relabel_workspace_bytes(int64_t num_items);
 int apt_relabel_csc(const int64_t* seeds, int64_t num_seeds,
+                    const int64_t* num_seeds_dev,
                     const int64_t* neighbors, int64_t num_neighbors,
                     void* workspace, size_t workspace_bytes,
                     int64_t* out_unique, int64_t* out_relabeled,
@@ -134,6 +143,7 @@ int apt_relabel_csc(const int64_t* seeds, int64_t num_seeds,
  */
 size_t apt_bucket_workspace_bytes(int64_t num_ids, int world_size);
 int apt_bucket_by_owner(const int64_t* ids, int64_t num_ids,
+                        const int64_t* num_ids_dev,
                         const int64_t* min_vids, int world_size,
                         int64_t shuffle_id_offset, int rank, int node_beg,
                         int node_end, void* workspace, size_t workspace_bytes,
@@ -152,8 +162,8 @@ int apt_bucket_by_owner(const int64_t* ids, int64_t num_ids,
  * workspace: apt_unique_workspace_bytes(id_hi - id_lo) bytes.
  */
 size_t apt_unique_workspace_bytes(int64_t id_range);
-int apt_unique_sorted(const int64_t* ids, int64_t num_ids, int64_t id_lo,
-                      int64_t id_hi, void* workspace, size_t workspace_bytes,
+int apt_unique_sorted(const int64_t* ids, int64_t num_ids,
+                      const int64_t* num_ids_dev, int64_t id_lo, int64_t id_hi, void* workspace, size_t workspace_bytes,
                       int64_t* out_unique, int64_t* out_inverse,
                       int64_t* out_num_unique, int32_t* status_word,
                       void* stream);
@@ -178,6 +188,7 @@ int apt_unique_sorted(const int64_t* ids, int64_t num_ids, int64_t id_lo,
  */
 size_t apt_gather_workspace_bytes(int64_t num_rows);
 int apt_gather_rows(const int64_t* index, int64_t num_rows,
+                    const int64_t* num_rows_dev,
                     const int64_t* feat_pos_map, int64_t num_nodes,
                     const void* dev_feats, int64_t num_dev_rows,
                     int64_t dev_row_bytes, const void* uva_feats,
@@ -314,8 +325,8 @@ size_t apt_p2p_region_bytes(const apt_p2p* ctx);
 int apt_p2p_push(apt_p2p* ctx, const void* src, const int64_t* src_index,
                  int index_is_dest, const int64_t* send_offsets, int64_t max_rows,
                  int64_t row_bytes, int32_t* status_word, void* stream);
-/* Wait for this epoch's flags; out_recv_counts int64[world_size] (device)
- * receives the rows each peer sent. timeout_ns <= 0 selects 2 s. On timeout
+/* Wait for this epoch's flags; out_recv_counts int64[world_size + 1] (device)
+ * receives the rows each peer sent and, in the last entry, their total. timeout_ns <= 0 selects 2 s. On timeout
  * APT_FLAG_PEER_TIMEOUT is ORed into status_word and counts are set to 0. */
 int apt_p2p_wait(apt_p2p* ctx, int64_t* out_recv_counts, int32_t* status_word,
                  int64_t timeout_ns, void* stream);

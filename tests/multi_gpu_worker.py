@@ -88,6 +88,20 @@ def main():
                 assert np.array_equal(got, w), f"rank {r}: np_sample_and_shuffle differs from the oracle"
     uniq, nbr, perm, send_off, recv_off, inverse_idx = res
 
+    # --- the whole three-hop mini-batch: device-chained sizes against one read per operator
+    batch = torch.from_numpy(seeds[:512]).cuda()
+    outs = []
+    for chained in (False, True):
+        ops.set_sampling(key=99, call_id=0)
+        smp = apt_b200.MixedNeighborSampler(rank, [10, 5, 5], chained=chained, prefetch_features=False)
+        outs.append(smp.sample(None, batch))
+    a, b_ = outs
+    for i in (0, 1, 3, 4, 5, 6):
+        assert np.array_equal(host(a[i]), host(b_[i])), f"chained sampler differs at output {i}"
+    for ba, bb in zip(a[2], b_[2]):
+        assert np.array_equal(host(ba.coo_row), host(bb.coo_row)) and np.array_equal(host(ba.src_ids), host(bb.src_ids))
+        assert np.array_equal(host(ba.coo_col), host(bb.coo_col)) and (ba.num_src, ba.num_dst) == (bb.num_src, bb.num_dst)
+
     # --- feature shuffle forward/backward (fp32 1 KiB rows, bf16 512 B rows, odd width)
     for dtype, D in ((torch.float32, 256), (torch.bfloat16, 256), (torch.float32, 3)):
         g = torch.Generator(device="cuda").manual_seed(7)

@@ -14,7 +14,8 @@ pytestmark = pytest.mark.gpu
 I64 = np.int64
 
 
-def test_np_minibatch_matches_oracle():
+@pytest.mark.parametrize("chained", [False, True])
+def test_np_minibatch_matches_oracle(chained):
     n, indptr, indices = small_graph(scale=13, edge_factor=8)
     install_graph(indptr, indices)
     reset_world(1, 0)
@@ -26,9 +27,11 @@ def test_np_minibatch_matches_oracle():
     fanouts = [15, 10, 5]
     seeds = rng.permutation(n)[:256].astype(I64)
     ops.set_sampling(key=31337, call_id=0)
-    sampler = apt_b200.MixedNeighborSampler(0, fanouts)
+    sampler = apt_b200.MixedNeighborSampler(0, fanouts, chained=chained)
     input_nodes, output_nodes, blocks, perm, send_off, recv_off, inverse_idx = sampler.sample(None, dev(seeds))
+    assert (ops.STATE.prefetched is not None) == chained
     x = ops.load_subtensor(input_nodes)
+    assert ops.STATE.prefetched is None
 
     # oracle: same loop as python/npc/sampler.py:132-156
     graph = (None, None, None, indptr, indices)

@@ -49,9 +49,10 @@ class Ranks:
             check(lib.apt_p2p_push(self.ctx[r], srcs[r].data_ptr() if srcs[r].numel() else None, idx, index_is_dest,
                                    off.data_ptr(), n, row_bytes, self.status.data_ptr(), _stream()))
         for r in range(self.ws):
-            c = torch.empty(self.ws, dtype=torch.int64, device="cuda")
+            c = torch.empty(self.ws + 1, dtype=torch.int64, device="cuda")   # per-peer counts, then their total
             check(lib.apt_p2p_wait(self.ctx[r], c.data_ptr(), self.status.data_ptr(), 0, _stream()))
-            counts.append(c)
+            assert int(c[:self.ws].sum().item()) == int(c[self.ws].item())
+            counts.append(c[:self.ws])
         return counts
 
     def pull(self, r, counts, dst, row_bytes, index=None, index_is_source=0, num_dst_rows=0):
@@ -152,10 +153,10 @@ def test_p2p_wait_times_out_with_a_status_not_a_hang():
         src = torch.arange(8, dtype=torch.int64, device="cuda")
         off = dev(np.array([4, 8], dtype=I64))
         check(lib.apt_p2p_push(ranks.ctx[0], src.data_ptr(), None, 0, off.data_ptr(), 8, 8, ranks.status.data_ptr(), _stream()))
-        c = torch.full((2,), -1, dtype=torch.int64, device="cuda")
+        c = torch.full((3,), -1, dtype=torch.int64, device="cuda")
         check(lib.apt_p2p_wait(ranks.ctx[0], c.data_ptr(), ranks.status.data_ptr(), 50_000_000, _stream()))  # 50 ms
         torch.cuda.synchronize()
-        assert host(c).tolist() == [4, 0]
+        assert host(c).tolist() == [4, 0, 4]
         assert int(ranks.status[0].item()) & _lib.FLAG_PEER_TIMEOUT
         # the context stays usable
         assert int((src + 1).sum().item()) == 36
@@ -169,11 +170,11 @@ def test_p2p_region_overflow_is_flagged():
         src = torch.arange(100, dtype=torch.int64, device="cuda")
         off = dev(np.array([100], dtype=I64))
         check(lib.apt_p2p_push(ranks.ctx[0], src.data_ptr(), None, 0, off.data_ptr(), 100, 8, ranks.status.data_ptr(), _stream()))
-        c = torch.empty(1, dtype=torch.int64, device="cuda")
+        c = torch.empty(2, dtype=torch.int64, device="cuda")
         check(lib.apt_p2p_wait(ranks.ctx[0], c.data_ptr(), ranks.status.data_ptr(), 0, _stream()))
         torch.cuda.synchronize()
         assert int(ranks.status[0].item()) & _lib.FLAG_TABLE_FULL
-        assert host(c).tolist() == [32]
+        assert host(c).tolist() == [32, 32]
     finally:
         ranks.close()
 
