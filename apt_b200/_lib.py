@@ -33,7 +33,7 @@ PROTOTYPES = {
     "apt_set_tunable": (c_int, [c_char_p, c_int64]),
     "apt_profile_enable": (c_int, [c_int]),
     "apt_profile_read": (c_int, [c_char_p, ctypes.POINTER(c_double), ctypes.POINTER(c_int64)]),
-    "apt_sample_csc_fanout": (c_int, [P, c_int64, P, c_int, P, c_int64, P, P, P, P, c_uint64, c_uint32, c_int, P, P, P]),
+    "apt_sample_csc_fanout": (c_int, [P, c_int64, P, c_int, P, c_int64, P, P, P, P, c_uint64, c_uint32, P, c_int, P, P, P]),
     "apt_relabel_workspace_bytes": (c_size_t, [c_int64]),
     "apt_relabel_csc": (c_int, [P, c_int64, P, P, c_int64, P, c_size_t, P, P, P, P, P]),
     "apt_bucket_workspace_bytes": (c_size_t, [c_int64, c_int]),

@@ -28,9 +28,10 @@ sample_replace_kernel(const int64_t* __restrict__ seeds, int64_t num_seeds,
                       const int64_t* __restrict__ dev_indices,
                       const int64_t* __restrict__ uva_indptr,
                       const int64_t* __restrict__ uva_indices, uint32_t k0,
-                      uint32_t k1, uint32_t call_id,
+                      uint32_t k1, uint32_t call_id, const int64_t* __restrict__ call_base_dev,
                       int64_t* __restrict__ out, int32_t* status) {
   num_seeds = effective_n(num_seeds, num_seeds_dev);
+  if (call_base_dev) call_id += (uint32_t)*call_base_dev;
   const int sub = threadIdx.x % G;
   const int64_t groups_per_block = blockDim.x / G;
   int64_t j = (int64_t)blockIdx.x * groups_per_block + threadIdx.x / G;
@@ -83,9 +84,10 @@ sample_floyd_kernel(const int64_t* __restrict__ seeds, int64_t num_seeds,
                     const int64_t* __restrict__ dev_indices,
                     const int64_t* __restrict__ uva_indptr,
                     const int64_t* __restrict__ uva_indices, uint32_t k0,
-                    uint32_t k1, uint32_t call_id, int64_t* __restrict__ out,
-                    int32_t* status) {
+                    uint32_t k1, uint32_t call_id, const int64_t* __restrict__ call_base_dev,
+                    int64_t* __restrict__ out, int32_t* status) {
   num_seeds = effective_n(num_seeds, num_seeds_dev);
+  if (call_base_dev) call_id += (uint32_t)*call_base_dev;
   const int lane = threadIdx.x & 31;
   const int64_t warps_per_block = blockDim.x >> 5;
   int64_t j = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
@@ -145,8 +147,9 @@ extern "C" int apt_sample_csc_fanout(
     const int64_t* seeds, int64_t num_seeds, const int64_t* num_seeds_dev, int fanout,
     const int64_t* adj_pos_map, int64_t num_nodes, const int64_t* dev_indptr,
     const int64_t* dev_indices, const int64_t* uva_indptr,
-    const int64_t* uva_indices, uint64_t key, uint32_t call_id, int replace,
-    int64_t* out_neighbors, int32_t* status_word, void* stream) {
+    const int64_t* uva_indices, uint64_t key, uint32_t call_id,
+    const int64_t* call_id_base_dev, int replace, int64_t* out_neighbors,
+    int32_t* status_word, void* stream) {
   using namespace apt;
   APT_CHECK_ARG(num_seeds >= 0 && fanout > 0 && num_nodes >= 0,
                 "apt_sample_csc_fanout: bad sizes (seeds %lld fanout %d)",
@@ -163,7 +166,7 @@ extern "C" int apt_sample_csc_fanout(
     const int grid = wave_grid(ceil_div(num_seeds, 8), 8);
     APT_LAUNCH(sample_floyd_kernel, grid, 256, 0, s, seeds, num_seeds, num_seeds_dev, fanout,
                adj_pos_map, num_nodes, dev_indptr, dev_indices, uva_indptr,
-               uva_indices, k0, k1, call_id, out_neighbors, status_word);
+               uva_indices, k0, k1, call_id, call_id_base_dev, out_neighbors, status_word);
     return APT_OK;
   }
 #define APT_SAMPLE_G(G)                                                        \
@@ -171,8 +174,8 @@ extern "C" int apt_sample_csc_fanout(
     const int grid = wave_grid(ceil_div(num_seeds, 256 / G), 8);               \
     APT_LAUNCH(sample_replace_kernel<G>, grid, 256, 0, s, seeds, num_seeds,    \
                num_seeds_dev, fanout, adj_pos_map, num_nodes, dev_indptr, dev_indices,        \
-               uva_indptr, uva_indices, k0, k1, call_id, out_neighbors,        \
-               status_word);                                                   \
+               uva_indptr, uva_indices, k0, k1, call_id, call_id_base_dev,     \
+               out_neighbors, status_word);                                    \
   } while (0)
   if (fanout <= 8) {
     APT_SAMPLE_G(8);

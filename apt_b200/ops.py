@@ -19,6 +19,7 @@ from . import _lib
 from ._lib import check, lib
 
 _DTYPE_CODE = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _lib.F16}
+_USE_SIDE_STREAM = os.environ.get("APT_GATHER_SIDE_STREAM", "0") == "1"
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -114,6 +115,8 @@ class NPCState:
         self._host_words = None
         self._side_stream = None
         self.prefetched = None  # (input ids, gathered rows) left by a sampler that gathers ahead
+        self.generation = 0     # bumped whenever installed state changes; captured graphs check it
+        self.profiling = False
         self.exchange = None  # set by apt_b200.exchange.make_exchange at init
         self.shuffle_backend = os.environ.get("APT_SHUFFLE_BACKEND", "p2p")
         self.p2p_region_bytes = int(os.environ.get("APT_P2P_REGION_MB", "256")) << 20
@@ -189,6 +192,13 @@ def _exchange():
     return STATE.exchange
 
 
+def profile_enable(on: bool):
+    """Per-kernel CUDA-event timing (apt_profile_enable). Captured CUDA graphs
+    cannot hold timing events, so samplers run eagerly while this is on."""
+    STATE.profiling = bool(on)
+    check(lib.apt_profile_enable(1 if on else 0))
+
+
 def check_status():
     """Synchronises and raises if any kernel since the last check flagged an error."""
     STATE.read_words()
@@ -211,6 +221,7 @@ def init(rank: int, local_rank: int, world_size: int, nccl_id_tensor_list: torch
     torch.cuda.set_device(s.local_rank)
     s.exchange = make_exchange(s)
     s.initialized = True
+    s.generation += 1
 
 
 def register_min_vids(shuffle_min_vids: torch.Tensor, shuffle_id_offset: int = 0) -> None:
@@ -219,6 +230,7 @@ def register_min_vids(shuffle_min_vids: torch.Tensor, shuffle_id_offset: int = 0
     if mv.numel() != STATE.world_size + 1:
         raise RuntimeError(f"min_vids needs world_size+1 = {STATE.world_size + 1} entries, got {mv.numel()}")
     STATE.shuffle_min_vids = mv
+    STATE.generation += 1
     STATE._min_vids_host = [int(x) for x in shuffle_min_vids.cpu().tolist()]
     STATE.shuffle_id_offset = int(shuffle_id_offset)
 
@@ -229,6 +241,7 @@ def mix_cache_graphs(num_cached_nodes: int, cached_node_idx: torch.Tensor, cache
     host memory (read over the host link, as in the reference) or CUDA memory
     (the whole topology resident in HBM)."""
     g = STATE.graph
+    STATE.generation += 1
     if int(num_cached_nodes) != cached_node_idx.numel():
         raise RuntimeError("num_cached_nodes != cached_node_idx.numel()")
     g.num_cached_nodes = int(num_cached_nodes)
@@ -252,6 +265,7 @@ def cache_feats_shared(num_total_nodes: int, localnode_feats: torch.Tensor, cach
     """CacheFeatsShared, src/cache_feats.cc:14-61."""
     f = STATE.feat
     dev = STATE.device()
+    STATE.generation += 1
     if localnode_feats.dim() != 2 or cached_feats.dim() != 2:
         raise RuntimeError("feature tables must be 2-D")
     if cached_feats.dtype != localnode_feats.dtype or cached_feats.dtype not in _DTYPE_CODE:
@@ -274,6 +288,7 @@ def cache_feats_shared(num_total_nodes: int, localnode_feats: torch.Tensor, cach
 def set_sampling(key: Optional[int] = None, call_id: Optional[int] = None, replace: Optional[bool] = None):
     """Sampler stream control: draws depend only on (key, call_id, seed slot,
     draw slot); call_id advances by one per sampling call."""
+    STATE.generation += 1
     if key is not None:
         STATE.sample_key = int(key)
     if call_id is not None:
@@ -283,19 +298,23 @@ def set_sampling(key: Optional[int] = None, call_id: Optional[int] = None, repla
 
 
 # -------------------------------------------------------------------- sampling
-def _sample(seeds: torch.Tensor, fanout: int, n_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """n_dev: optional one-element device count; seeds.numel() is then an upper bound."""
+def _sample(seeds: torch.Tensor, fanout: int, n_dev: Optional[torch.Tensor] = None,
+            call_id: Optional[int] = None, call_base_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """n_dev: optional one-element device count; seeds.numel() is then an upper bound.
+    call_id / call_base_dev: explicit call id (plus a device-side base) instead of the
+    process-wide counter, for sequences replayed from a CUDA graph."""
     g = STATE.graph
     if g.uva_indptr is None:
         raise RuntimeError("mix_cache_graphs has not been called")
     seeds = _need_cuda(seeds, "seeds")
     out = torch.empty(seeds.numel() * int(fanout), dtype=torch.int64, device=seeds.device)
-    call_id = STATE.sample_calls
-    STATE.sample_calls += 1
+    if call_id is None:
+        call_id = STATE.sample_calls
+        STATE.sample_calls += 1
     check(lib.apt_sample_csc_fanout(
         _ptr(seeds), seeds.numel(), _ptr(n_dev), int(fanout), _ptr(g.adj_pos_map), g.num_total_nodes,
         _ptr(g.dev_indptr), _ptr(g.dev_indices), _ptr(g.uva_indptr), _ptr(g.uva_indices),
-        STATE.sample_key, call_id & 0xFFFFFFFF, 1 if STATE.sample_replace else 0,
+        STATE.sample_key, call_id & 0xFFFFFFFF, _ptr(call_base_dev), 1 if STATE.sample_replace else 0,
         _ptr(out), STATE.status_ptr(), _stream()))
     return out
 
@@ -436,7 +455,8 @@ def _gather_enqueue(node_id: torch.Tensor, n_dev: Optional[torch.Tensor]) -> tor
     out = torch.empty((n, f.rank_feat_dim), dtype=f.dev_feats.dtype, device=node_id.device)
     nbytes = lib.apt_gather_workspace_bytes(n)
     ws = STATE.workspace("gather", nbytes)
-    side = STATE.side_stream() if f.uva_feats.shape[0] > 0 else None
+    # the miss copy runs after the hit copy on the same stream unless a side stream is asked for
+    side = STATE.side_stream() if f.uva_feats.shape[0] > 0 and _USE_SIDE_STREAM else None
     check(lib.apt_gather_rows(
         _ptr(node_id), n, _ptr(n_dev), _ptr(f.feat_pos_map), f.num_total_nodes,
         _ptr(f.dev_feats), f.dev_feats.shape[0], f.rank_feat_dim * esz,

@@ -60,6 +60,21 @@ def create_block(seeds: torch.Tensor, neighbors: torch.Tensor, fanout: int) -> B
 _PREFETCH_LIMIT_BYTES = 3 << 30
 
 
+class _Plan:
+    """Buffers of one enqueued mini-batch and, when captured, the CUDA graph
+    that replays the enqueue."""
+
+    def __init__(self):
+        self.seeds_buf = None
+        self.bufs = None
+        self.graph = None
+        self.generation = -1
+        self.keepalive = None
+
+
+_CALL_BASE_SLOT = 100  # device word holding the sampler's call-id base for graph replays
+
+
 class MixedNeighborSampler:
     """NP ("NPC") strategy: inner hops are sampled locally, the outermost hop at
     the owner of each frontier node (np_sample_and_shuffle). fanouts[0] is the
@@ -69,17 +84,29 @@ class MixedNeighborSampler:
                        read per batch) instead of one read per operator
     prefetch_features  also enqueue the feature gather of the input nodes before that
                        read; the next ops.load_subtensor(input_nodes) returns it
+    use_graph          capture the enqueue once per batch size as a CUDA graph and
+                       replay it (one launch per mini-batch). The results of a batch
+                       live in the graph's buffers: they stay valid until
+                       `graph_buffers` further batches have been sampled.
     """
 
-    def __init__(self, rank: int, fanouts: List[int], chained: bool = None, prefetch_features: bool = True):
+    def __init__(self, rank: int, fanouts: List[int], chained: bool = None, prefetch_features: bool = True,
+                 use_graph: bool = None, graph_buffers: int = 2):
         self.rank = rank
         self.fir_fanouts = list(fanouts[1:])
         self.las_fanouts = fanouts[0]
         self.num_layers = len(fanouts)
         if chained is None:
             chained = os.environ.get("APT_CHAINED_SAMPLER", "1") != "0"
+        if use_graph is None:
+            use_graph = os.environ.get("APT_SAMPLER_GRAPH", "1") != "0"
         self.chained = chained
         self.prefetch_features = prefetch_features
+        self.use_graph = use_graph and chained
+        self.graph_buffers = max(1, int(graph_buffers))
+        self._plans = {}
+        self._turn = 0
+        self._host_base = None
 
     def sample(self, graph, seeds: torch.Tensor):
         if self.chained:
@@ -98,52 +125,60 @@ class MixedNeighborSampler:
         seeds = block.src_ids
         return seeds, output_nodes, blocks, perm, send_offset, recv_offset, inverse_idx
 
-    def _sample_chained(self, seeds: torch.Tensor):
+    # ------------------------------------------------------------ chained path
+    def _enqueue(self, seeds: torch.Tensor, call_base_dev):
+        """Enqueues every kernel of the mini-batch on the current stream; no host
+        read. With call_base_dev the k-th sampling call uses call id base + k."""
         st = ops.STATE
         ws = st.world_size
-        if self.num_layers > 14:
-            raise RuntimeError("the chained sampler keeps at most 14 hop counts")
-        seeds = ops._need_cuda(seeds, "seeds")
-        output_nodes = seeds
+        explicit = call_base_dev is not None
         slot = 0
-        cur, cur_n, cur_slot = seeds, None, None
-        layers = []                      # (dst buffer, dst count slot, rel, uniq, uniq count slot, fanout)
+        call = 0
+        cur, cur_n = seeds, None
+        layers = []                      # (dst buffer, rel, uniq, uniq count slot, fanout)
         for fanout in reversed(self.fir_fanouts):
-            nbr = ops._sample(cur, fanout, cur_n)
+            nbr = ops._sample(cur, fanout, cur_n, call if explicit else None, call_base_dev)
+            call += 1
             cnt = st.word(slot)
             uniq, rel = ops._relabel_enqueue(cur, nbr, cur_n, cnt)
-            layers.append((cur, cur_slot, rel, uniq, slot, fanout))
-            cur, cur_n, cur_slot = uniq, cnt, slot
+            layers.append((cur, rel, uniq, slot, fanout))
+            cur, cur_n = uniq, cnt
             slot += 1
         # outermost hop at the owners (NPSampleAndShuffle, src/sampling.cc:52-69)
         sorted_ids, perm, sizes, offsets = ops._bucket(cur, cur_n)
         recv, recv_counts = ops._exchange().exchange_ids_enqueue(sorted_ids, sizes, offsets)
         total = recv_counts[ws:ws + 1]
         lo, hi = ops._owned_range()
-        u_slot = slot
+        u_slot, in_slot = slot, slot + 1
         uniq2, inv = ops._unique_enqueue(recv, total, lo, hi, st.word(u_slot))
-        nbr = ops._sample(uniq2, self.las_fanouts, st.word(u_slot))
-        in_slot = slot + 1
+        nbr = ops._sample(uniq2, self.las_fanouts, st.word(u_slot), call if explicit else None, call_base_dev)
         uniq3, rel3 = ops._relabel_enqueue(uniq2, nbr, st.word(u_slot), st.word(in_slot))
         rows = None
         f = st.feat
         if self.prefetch_features and f.feat_pos_map is not None and \
                 uniq3.numel() * f.rank_feat_dim * f.dev_feats.element_size() <= _PREFETCH_LIMIT_BYTES:
             rows = ops._gather_enqueue(uniq3, st.word(in_slot))
-        # counts the host needs: per-peer received ids and my bucket offsets ride along in the word block
-        words = st.words()                          # [0..15] hop counts, [16..48] received, [64..95] bucket offsets
+        # counts the host needs ride along in the word block:
+        # [0..15] hop counts, [16..48] ids received per peer, [64..95] my bucket offsets
+        words = st.words()
         words[16:16 + ws + 1].copy_(recv_counts)
         words[64:64 + ws].copy_(offsets)
-        host = st.read_words()                      # the one host read of the mini-batch
-        count = [int(host[k]) for k in range(in_slot + 1)]
-        recv_cnt = host[16:16 + ws].clone()
-        dev_offset = host[64:64 + ws].clone()
-        recv_offset = recv_cnt.cumsum(0)
-        total_recv = int(recv_offset[-1])
+        return dict(layers=layers, perm=perm, inv=inv, uniq2=uniq2, uniq3=uniq3, rel3=rel3, rows=rows,
+                    u_slot=u_slot, in_slot=in_slot)
 
+    def _finish(self, seeds, bufs):
+        """The one host read of the mini-batch, then buffers narrowed to their real sizes."""
+        st = ops.STATE
+        ws = st.world_size
+        host = st.read_words()
+        u_slot, in_slot = bufs["u_slot"], bufs["in_slot"]
+        count = [int(host[k]) for k in range(in_slot + 1)]
+        recv_offset = host[16:16 + ws].clone().cumsum(0)
+        dev_offset = host[64:64 + ws].clone()
+        total_recv = int(recv_offset[-1])
         blocks = []
         n_dst = seeds.numel()
-        for dst_buf, dst_slot, rel, uniq, u_s, fanout in layers:
+        for dst_buf, rel, uniq, u_s, fanout in bufs["layers"]:
             n_src = count[u_s]
             blocks.insert(0, Block(rel[:n_dst * fanout], _coo_col(dst_buf.numel(), n_dst, fanout, rel.device),
                                    n_src, n_dst, uniq[:n_src], fanout))
@@ -151,13 +186,62 @@ class MixedNeighborSampler:
         n_frontier = n_dst
         n_owner_dst, n_in = count[u_slot], count[in_slot]
         f0 = self.las_fanouts
+        uniq2, uniq3, rel3 = bufs["uniq2"], bufs["uniq3"], bufs["rel3"]
         blocks.insert(0, Block(rel3[:n_owner_dst * f0], _coo_col(uniq2.numel(), n_owner_dst, f0, rel3.device),
                                n_in, n_owner_dst, uniq3[:n_in], f0))
         input_nodes = uniq3[:n_in]
-        if rows is not None:
-            st.prefetched = (input_nodes, rows[:n_in])
-        return (input_nodes, output_nodes, blocks, perm[:n_frontier], recv_offset, dev_offset,
-                inv[:total_recv])
+        if bufs["rows"] is not None:
+            st.prefetched = (input_nodes, bufs["rows"][:n_in])
+        return (input_nodes, seeds, blocks, bufs["perm"][:n_frontier], recv_offset, dev_offset,
+                bufs["inv"][:total_recv])
+
+    def _graph_ok(self):
+        st = ops.STATE
+        # the peer-to-peer exchange advances a host-side epoch per call and cannot be replayed
+        return self.use_graph and st.world_size == 1 and not st.profiling
+
+    def _plan_for(self, seeds):
+        st = ops.STATE
+        key = (seeds.numel(), seeds.device)
+        ring = self._plans.setdefault(key, [None] * self.graph_buffers)
+        i = self._turn % self.graph_buffers
+        self._turn += 1
+        plan = ring[i]
+        if plan is not None and plan.generation == st.generation:
+            return plan
+        plan = _Plan()
+        plan.generation = st.generation
+        plan.seeds_buf = torch.empty_like(seeds)
+        plan.seeds_buf.copy_(seeds)
+        base_dev = st.word(_CALL_BASE_SLOT)
+        # one eager run first: it sizes the cached workspaces and surfaces errors outside capture
+        bufs = self._enqueue(plan.seeds_buf, base_dev)
+        st.read_words()
+        st.prefetched = None
+        del bufs
+        plan.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(plan.graph):
+            plan.bufs = self._enqueue(plan.seeds_buf, base_dev)
+        plan.keepalive = list(st._ws.values())
+        ring[i] = plan
+        return plan
+
+    def _sample_chained(self, seeds: torch.Tensor):
+        st = ops.STATE
+        if self.num_layers > 14:
+            raise RuntimeError("the chained sampler keeps at most 14 hop counts")
+        seeds = ops._need_cuda(seeds, "seeds")
+        if not self._graph_ok():
+            return self._finish(seeds, self._enqueue(seeds, None))
+        if self._host_base is None:
+            self._host_base = torch.zeros(1, dtype=torch.int64).pin_memory()
+        self._host_base[0] = st.sample_calls
+        st.word(_CALL_BASE_SLOT).copy_(self._host_base, non_blocking=True)
+        plan = self._plan_for(seeds)
+        plan.seeds_buf.copy_(seeds)
+        plan.graph.replay()
+        st.sample_calls += self.num_layers
+        return self._finish(seeds, plan.bufs)
 
 
 class DPNeighborSampler:

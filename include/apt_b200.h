@@ -96,13 +96,16 @@ int apt_set_tunable(const char* name, int64_t value);
  *               counter (j & 0xffffffff, j >> 32, i >> 2, call_id).
  * adj_pos_map may be NULL: every node then reads (uva_indptr, uva_indices),
  * which may be plain device memory holding the whole graph.
+ * call_id_base_dev (may be NULL) is a device word added to call_id at run time,
+ * so that a captured CUDA graph draws a fresh stream at every replay.
  */
 int apt_sample_csc_fanout(const int64_t* seeds, int64_t num_seeds,
                           const int64_t* num_seeds_dev, int fanout,
                           const int64_t* adj_pos_map, int64_t num_nodes,
                           const int64_t* dev_indptr, const int64_t* dev_indices,
                           const int64_t* uva_indptr, const int64_t* uva_indices,
-                          uint64_t key, uint32_t call_id, int replace,
+                          uint64_t key, uint32_t call_id,
+                          const int64_t* call_id_base_dev, int replace,
                           int64_t* out_neighbors, int32_t* status_word,
                           void* stream);
 

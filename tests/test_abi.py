@@ -37,7 +37,7 @@ def test_argument_errors_without_gpu():
     assert lib.apt_gather_workspace_bytes(0) > 0
     assert lib.apt_bucket_workspace_bytes(5000, 8) >= 8 * 5 * 4
     # argument checks fire before any CUDA call
-    st = lib.apt_sample_csc_fanout(None, 5, None, 0, None, 10, None, None, None, None, 1, 0, 1, None, None, None)
+    st = lib.apt_sample_csc_fanout(None, 5, None, 0, None, 10, None, None, None, None, 1, 0, None, 1, None, None, None)
     assert st == _lib.APT_ERR_BAD_ARG and b"apt_sample_csc_fanout" in lib.apt_last_error()
     st = lib.apt_bucket_by_owner(None, 5, None, None, 64, 0, 0, 0, 1, None, 0, None, None, None, None, None)
     assert st == _lib.APT_ERR_BAD_ARG

@@ -68,6 +68,41 @@ def test_np_minibatch_matches_oracle(chained):
     ops.check_status()
 
 
+def test_graph_replay_equals_eager_over_several_batches():
+    """Three consecutive mini-batches: CUDA-graph replay, device-chained eager and one
+    host read per operator give the same tensors; with two graph buffers a batch's
+    results survive the next batch."""
+    n, indptr, indices = small_graph(scale=12, edge_factor=8)
+    install_graph(indptr, indices)
+    reset_world(1, 0)
+    ops.register_min_vids(torch.tensor([0, n]))
+    rng = np.random.default_rng(8)
+    feats, uva, devf, cached_idx, local_idx, pos_map, cpu_map = feature_setup(n, 32, 0.5, rng)
+    ops.cache_feats_shared(n, torch.from_numpy(uva).pin_memory(), dev(devf), torch.from_numpy(cached_idx),
+                           torch.from_numpy(local_idx), 0)
+    batches = [dev(rng.permutation(n)[:200].astype(I64)) for _ in range(3)]
+    results = {}
+    for mode, kw in (("plain", dict(chained=False)), ("eager", dict(chained=True, use_graph=False)),
+                     ("graph", dict(chained=True, use_graph=True, graph_buffers=2))):
+        ops.set_sampling(key=4242, call_id=5)
+        smp = apt_b200.MixedNeighborSampler(0, [10, 5], **kw)
+        outs = []
+        for b in batches:
+            res = smp.sample(None, b)
+            x = ops.load_subtensor(res[0])
+            outs.append((res, x))
+        # with two buffers the previous batch is still intact after the next one was sampled
+        keep = [(host(r[0]), host(r[2][0].coo_row), host(x_)) for r, x_ in outs[-2:]]
+        results[mode] = ([(host(r[0]), host(r[2][0].coo_row), host(r[2][1].coo_row), host(r[3]), host(r[6]),
+                           host(x_), r[2][0].num_src) for r, x_ in outs[-2:]], keep)
+    for mode in ("eager", "graph"):
+        for got, want in zip(results[mode][0], results["plain"][0]):
+            for g_, w_ in zip(got, want):
+                assert np.array_equal(g_, w_), mode
+    assert apt_b200.STATE.sample_calls == 5 + 2 * 3
+    ops.check_status()
+
+
 @pytest.mark.parametrize("row_elems,dtype", [(256, torch.float32), (1024, torch.float16), (3, torch.float32), (1, torch.bfloat16)])
 def test_row_movers(row_elems, dtype):
     g = torch.Generator(device="cuda").manual_seed(row_elems)
