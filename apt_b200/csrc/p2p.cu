@@ -3,12 +3,16 @@
 //
 // Inbox layout of every rank (one cudaMalloc, exported by CUDA IPC):
 //   [0, 4096)             header: flags[2][32] (uint64: epoch << 32 | rows),
-//                         then the push kernel's block counter
+//                         the push kernel's block counter, and the two
+//                         sequence numbers (pushes and waits completed)
 //   [4096, ...)           data[parity][source rank][region_bytes]
 // A push writes rows for peer r into data[parity][me] of r's inbox; when the
 // last block of the push kernel has finished (block counter) it publishes
 // flags[parity][me] on every peer. The wait kernel polls the local flags with
 // a time bound; the pull kernel reads the rows out of the local inbox.
+// The epoch of an all-to-all is not a kernel argument: push and wait kernels
+// derive it from the sequence numbers in the local header and advance them,
+// so an enqueued sequence can be captured in a CUDA graph and replayed.
 #include <string.h>
 
 #include "common.cuh"
@@ -20,6 +24,8 @@ constexpr int kMoveBlock = 256;
 constexpr int kP2pMaxRanks = 32;
 constexpr size_t kHeaderBytes = 4096;
 constexpr size_t kCounterOffset = 2048;
+constexpr size_t kPushSeqOffset = 2112;  // uint32: all-to-alls this rank has pushed
+constexpr size_t kWaitSeqOffset = 2120;  // uint32: all-to-alls this rank has waited for
 
 template <typename V>
 __device__ __forceinline__ V mv_load(const V* p) { return *p; }
@@ -104,10 +110,14 @@ template <typename V>
 __global__ void __launch_bounds__(kMoveBlock)
 k_p2p_push(const char* __restrict__ src, const int64_t* __restrict__ src_index,
            int index_is_dest, const int64_t* __restrict__ send_offsets, int world_size,
-           int me, int64_t row_bytes, size_t region_bytes, PeerTable peers, int parity,
-           uint32_t epoch, int32_t* status) {
+           int me, int64_t row_bytes, size_t region_bytes, PeerTable peers, int32_t* status) {
   __shared__ int64_t soff[kP2pMaxRanks + 1];
   __shared__ bool is_last;
+  // Every block reads the sequence number before it takes its ticket below, and
+  // the number only moves after the last ticket, so all blocks see the same epoch.
+  uint32_t* push_seq = (uint32_t*)(peers.base[me] + kPushSeqOffset);
+  const uint32_t epoch = *(volatile uint32_t*)push_seq + 1u;
+  const int parity = (int)(epoch & 1u);
   if (threadIdx.x == 0) soff[0] = 0;
   if (threadIdx.x < world_size) soff[threadIdx.x + 1] = send_offsets[threadIdx.x];
   __syncthreads();
@@ -176,12 +186,15 @@ k_p2p_push(const char* __restrict__ src, const int64_t* __restrict__ src_index,
     if (rows > cap_rows) rows = cap_rows;
     uint64_t* flag = (uint64_t*)peers.base[r] + (size_t)parity * kP2pMaxRanks + me;
     st_release_sys(flag, ((uint64_t)epoch << 32) | (uint64_t)(uint32_t)rows);
+    if (r == 0) *(volatile uint32_t*)push_seq = epoch;
   }
 }
 
-__global__ void k_p2p_wait(const char* local_base, int world_size, int parity,
-                           uint32_t epoch, int64_t timeout_ns,
+__global__ void k_p2p_wait(char* local_base, int world_size, int64_t timeout_ns,
                            int64_t* __restrict__ out_counts, int32_t* status) {
+  uint32_t* wait_seq = (uint32_t*)(local_base + kWaitSeqOffset);
+  const uint32_t epoch = *(volatile uint32_t*)wait_seq + 1u;
+  const int parity = (int)(epoch & 1u);
   const int r = threadIdx.x;
   const bool live = r < world_size;
   const uint64_t* flag = (const uint64_t*)local_base + (size_t)parity * kP2pMaxRanks + (live ? r : 0);
@@ -204,7 +217,10 @@ __global__ void k_p2p_wait(const char* local_base, int world_size, int parity,
   // total over the peers, for operators chained behind the exchange
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) got += __shfl_down_sync(0xffffffffu, got, d);
-  if (r == 0) out_counts[world_size] = got;
+  if (r == 0) {
+    out_counts[world_size] = got;
+    *(volatile uint32_t*)wait_seq = epoch;
+  }
 }
 
 // mode 0: dst row j = concatenation row j; 1: dst row i = concat row index[i];
@@ -212,10 +228,12 @@ __global__ void k_p2p_wait(const char* local_base, int world_size, int parity,
 template <typename V, int MODE>
 __global__ void __launch_bounds__(kMoveBlock)
 k_p2p_pull(const char* __restrict__ local_base, const int64_t* __restrict__ recv_counts,
-           int world_size, int parity, size_t region_bytes,
+           int world_size, size_t region_bytes,
            const int64_t* __restrict__ index, int64_t num_dst_rows, int64_t row_bytes,
            char* __restrict__ dst) {
   __shared__ int64_t roff[kP2pMaxRanks + 1];
+  // the all-to-all being read is the last one waited for
+  const int parity = (int)(*(const volatile uint32_t*)(local_base + kWaitSeqOffset) & 1u);
   if (threadIdx.x == 0) {
     int64_t run = 0;
     roff[0] = 0;
@@ -271,7 +289,6 @@ struct apt_p2p {
   char* local_base;
   char* peer_base[apt::kP2pMaxRanks];
   bool peer_is_ipc[apt::kP2pMaxRanks];
-  uint32_t epoch;
 };
 
 extern "C" int apt_rows_gather(const void* in, const int64_t* index, int64_t num_out_rows,
@@ -294,7 +311,6 @@ extern "C" int apt_p2p_create(int rank, int world_size, size_t region_bytes, apt
   c->world_size = world_size;
   c->region_bytes = align_up(region_bytes, 256);
   c->alloc_bytes = kHeaderBytes + 2 * (size_t)world_size * c->region_bytes;
-  c->epoch = 0;
   for (int r = 0; r < kP2pMaxRanks; ++r) {
     c->peer_base[r] = nullptr;
     c->peer_is_ipc[r] = false;
@@ -363,8 +379,6 @@ extern "C" int apt_p2p_push(apt_p2p* ctx, const void* src, const int64_t* src_in
   for (int r = 0; r < ctx->world_size; ++r)
     APT_CHECK_ARG(ctx->peer_base[r], "apt_p2p_push: peer %d is not attached", r);
   cudaStream_t s = (cudaStream_t)stream;
-  ctx->epoch += 1;
-  const int parity = (int)(ctx->epoch & 1u);
   PeerTable pt;
   for (int r = 0; r < kP2pMaxRanks; ++r) pt.base[r] = ctx->peer_base[r];
   const int w = vec_width_of((uint64_t)row_bytes | (uintptr_t)src | (uint64_t)ctx->region_bytes);
@@ -373,8 +387,7 @@ extern "C" int apt_p2p_push(apt_p2p* ctx, const void* src, const int64_t* src_in
   const char* sp = (const char*)src;
 #define APT_PUSH(V)                                                                       \
   APT_LAUNCH(k_p2p_push<V>, grid, kMoveBlock, 0, s, sp, src_index, index_is_dest, send_offsets,          \
-             ctx->world_size, ctx->rank, row_bytes, ctx->region_bytes, pt, parity,        \
-             ctx->epoch, status_word)
+             ctx->world_size, ctx->rank, row_bytes, ctx->region_bytes, pt, status_word)
   switch (w) {
     case 16: APT_PUSH(uint4); break;
     case 8: APT_PUSH(uint2); break;
@@ -390,12 +403,11 @@ extern "C" int apt_p2p_wait(apt_p2p* ctx, int64_t* out_recv_counts, int32_t* sta
                             int64_t timeout_ns, void* stream) {
   using namespace apt;
   APT_CHECK_ARG(ctx && out_recv_counts && status_word, "apt_p2p_wait: bad argument");
-  APT_CHECK_ARG(ctx->epoch > 0, "apt_p2p_wait: no push has been issued");
   if (timeout_ns <= 0) timeout_ns = 2000000000ll;
   cudaStream_t s = (cudaStream_t)stream;
   ProfScope prof("p2p_wait", s);
-  APT_LAUNCH(k_p2p_wait, 1, 32, 0, s, ctx->local_base, ctx->world_size, (int)(ctx->epoch & 1u),
-             ctx->epoch, timeout_ns, out_recv_counts, status_word);
+  APT_LAUNCH(k_p2p_wait, 1, 32, 0, s, ctx->local_base, ctx->world_size, timeout_ns, out_recv_counts,
+             status_word);
   return APT_OK;
 }
 
@@ -407,7 +419,6 @@ extern "C" int apt_p2p_pull(apt_p2p* ctx, const int64_t* recv_counts, const int6
   if (max_rows == 0) return APT_OK;
   APT_CHECK_ARG(dst, "apt_p2p_pull: null destination");
   cudaStream_t s = (cudaStream_t)stream;
-  const int parity = (int)(ctx->epoch & 1u);
   const int w = vec_width_of((uint64_t)row_bytes | (uintptr_t)dst | (uint64_t)ctx->region_bytes);
   const int grid = wave_grid(ceil_div(max_rows, (kMoveBlock / 32) * kMoveRows), 8, 4);
   const int mode = !dst_index ? 0 : (index_is_source ? 1 : 2);
@@ -415,7 +426,7 @@ extern "C" int apt_p2p_pull(apt_p2p* ctx, const int64_t* recv_counts, const int6
   char* dp = (char*)dst;
 #define APT_PULL(V, M)                                                                     \
   APT_LAUNCH((k_p2p_pull<V, M>), grid, kMoveBlock, 0, s, ctx->local_base, recv_counts,     \
-             ctx->world_size, parity, ctx->region_bytes, dst_index, num_dst_rows,          \
+             ctx->world_size, ctx->region_bytes, dst_index, num_dst_rows,                  \
              row_bytes, dp)
 #define APT_PULL_W(V)                                   \
   do {                                                  \

@@ -197,8 +197,8 @@ class MixedNeighborSampler:
 
     def _graph_ok(self):
         st = ops.STATE
-        # the peer-to-peer exchange advances a host-side epoch per call and cannot be replayed
-        return self.use_graph and st.world_size == 1 and not st.profiling
+        # the library all-to-all (baseline backend) reads sizes on the host and cannot be captured
+        return self.use_graph and not st.profiling and ops._exchange().name in ("local", "p2p")
 
     def _plan_for(self, seeds):
         st = ops.STATE

@@ -300,6 +300,8 @@ int apt_rows_scatter(const void* in, const int64_t* index, int64_t num_in_rows,
  *                  counts to a device array;
  *   apt_p2p_pull   copies / permutes the received rows out of the inbox.
  * All ranks must issue the same sequence of all-to-alls on one stream each.
+ * The epoch is kept in the inbox header and advanced by the kernels, so the
+ * three calls carry no per-call host state and may be captured in a CUDA graph.
  * Waiting for all flags of epoch e before any store of epoch e+1, together
  * with the parity double buffer, keeps an inbox region from being overwritten
  * before its owner has consumed it.
