@@ -103,11 +103,17 @@ k_bucket_scatter(const int64_t* __restrict__ ids, int64_t n, const int64_t* __re
 }
 
 // ------------------------------------------------------------ sorted unique
+// A two-level bitmap over the id range stands in for the sort: level 0 has one
+// bit per id, level 1 one bit per level-0 word that is not zero. Counting,
+// ranking and emitting walk level 1 only (range/1024 words), so the cost of a
+// call follows the number of ids, not the width of the range. Both levels are
+// all-zero between calls: the call clears exactly the words it set.
 constexpr int kUniqBlock = 1024;
 
 __global__ void __launch_bounds__(256)
 k_uniq_mark(const int64_t* __restrict__ ids, int64_t n, const int64_t* __restrict__ n_dev,
-            int64_t lo, int64_t hi, uint32_t* __restrict__ bitmap, int32_t* status) {
+            int64_t lo, int64_t hi, uint32_t* __restrict__ l0, uint32_t* __restrict__ l1,
+            int32_t* status) {
   n = effective_n(n, n_dev);
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -120,46 +126,64 @@ k_uniq_mark(const int64_t* __restrict__ ids, int64_t n, const int64_t* __restric
     }
     const int64_t r = v - lo;
     const uint32_t bit = 1u << (r & 31);
-    uint32_t* w = bitmap + (r >> 5);
-    if (!(*(volatile uint32_t*)w & bit)) atomicOr(w, bit);
+    const int64_t w = r >> 5;
+    if (*(volatile uint32_t*)(l0 + w) & bit) continue;
+    const uint32_t old = atomicOr(l0 + w, bit);
+    if (old == 0) atomicOr(l1 + (w >> 5), 1u << (w & 31));  // first bit of this word
   }
   if (flags) atomicOr(status, flags);
 }
 
+// Ids under one level-1 word (up to 1024 of them).
+__device__ __forceinline__ int l1_word_count(const uint32_t* __restrict__ l0, int64_t w1, uint32_t bits) {
+  int c = 0;
+  while (bits) {
+    const int b = __ffs(bits) - 1;
+    bits &= bits - 1;
+    c += __popc(l0[(w1 << 5) + b]);
+  }
+  return c;
+}
+
 __global__ void __launch_bounds__(kUniqBlock)
-k_uniq_count(const uint32_t* __restrict__ bitmap, int64_t nwords,
+k_uniq_count(const uint32_t* __restrict__ l0, const uint32_t* __restrict__ l1, int64_t nwords1,
              int32_t* __restrict__ block_sums) {
   __shared__ int warp_sums[33];
-  const int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int c = w < nwords ? __popc(bitmap[w]) : 0;
+  const int64_t w1 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint32_t bits = w1 < nwords1 ? l1[w1] : 0u;
   int total;
-  block_exclusive_scan(c, warp_sums, &total);
+  block_exclusive_scan(l1_word_count(l0, w1, bits), warp_sums, &total);
   if (threadIdx.x == 0) block_sums[blockIdx.x] = total;
 }
 
 __global__ void __launch_bounds__(kUniqBlock)
-k_uniq_emit(const uint32_t* __restrict__ bitmap, int64_t nwords, int64_t lo,
-            const int32_t* __restrict__ block_sums,
+k_uniq_emit(const uint32_t* __restrict__ l0, const uint32_t* __restrict__ l1, int64_t nwords1,
+            int64_t lo, const int32_t* __restrict__ block_sums,
             uint32_t* __restrict__ word_prefix, int64_t* __restrict__ out_unique) {
   __shared__ int warp_sums[33];
-  const int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  uint32_t bits = w < nwords ? bitmap[w] : 0u;
+  const int64_t w1 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  uint32_t bits1 = w1 < nwords1 ? l1[w1] : 0u;
   int total;
-  const int ex = block_exclusive_scan(__popc(bits), warp_sums, &total);
-  if (w >= nwords) return;
+  const int ex = block_exclusive_scan(l1_word_count(l0, w1, bits1), warp_sums, &total);
   int64_t at = (int64_t)block_sums[blockIdx.x] + ex;
-  word_prefix[w] = (uint32_t)at;
-  const int64_t base = lo + (w << 5);
-  while (bits) {
-    const int b = __ffs(bits) - 1;
-    out_unique[at++] = base + b;
-    bits &= bits - 1;
+  while (bits1) {
+    const int b1 = __ffs(bits1) - 1;
+    bits1 &= bits1 - 1;
+    const int64_t w = (w1 << 5) + b1;
+    uint32_t bits = l0[w];
+    word_prefix[w] = (uint32_t)at;      // rank of the word's first id; only non-zero words are ever looked up
+    const int64_t base = lo + (w << 5);
+    while (bits) {
+      const int b = __ffs(bits) - 1;
+      bits &= bits - 1;
+      out_unique[at++] = base + b;
+    }
   }
 }
 
 __global__ void __launch_bounds__(256)
 k_uniq_inverse(const int64_t* __restrict__ ids, int64_t n, const int64_t* __restrict__ n_dev,
-               int64_t lo, int64_t hi, const uint32_t* __restrict__ bitmap,
+               int64_t lo, int64_t hi, const uint32_t* __restrict__ l0,
                const uint32_t* __restrict__ word_prefix,
                int64_t* __restrict__ out_inverse) {
   n = effective_n(n, n_dev);
@@ -172,9 +196,25 @@ k_uniq_inverse(const int64_t* __restrict__ ids, int64_t n, const int64_t* __rest
       continue;
     }
     const int64_t r = v - lo;
-    const uint32_t bits = bitmap[r >> 5];
+    const uint32_t bits = l0[r >> 5];
     out_inverse[i] = (int64_t)word_prefix[r >> 5] +
                      __popc(bits & ((1u << (r & 31)) - 1u));
+  }
+}
+
+// Puts both levels back to zero by revisiting the ids that set them.
+__global__ void __launch_bounds__(256)
+k_uniq_clear(const int64_t* __restrict__ ids, int64_t n, const int64_t* __restrict__ n_dev,
+             int64_t lo, int64_t hi, uint32_t* __restrict__ l0, uint32_t* __restrict__ l1) {
+  n = effective_n(n, n_dev);
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    const int64_t v = ids[i];
+    if (v < lo || v >= hi) continue;
+    const int64_t w = (v - lo) >> 5;
+    l0[w] = 0u;
+    l1[w >> 5] = 0u;
   }
 }
 
@@ -234,32 +274,46 @@ extern "C" int apt_bucket_by_owner(const int64_t* ids, int64_t num_ids,
 
 namespace apt {
 struct UniqWs {
-  uint32_t* bitmap;
-  uint32_t* word_prefix;
-  int32_t* block_sums;
-  int64_t nwords;
+  uint32_t* l0;           // [nwords0] one bit per id
+  uint32_t* l1;           // [nwords1] one bit per level-0 word
+  uint32_t* word_prefix;  // [nwords0]
+  int32_t* block_sums;    // [nblocks + 1]
+  int64_t nwords0, nwords1;
   int nblocks;
+  size_t bitmap_bytes;    // l0 + l1: the part that has to be zero between calls
 };
 static size_t uniq_layout(int64_t range, char* base, UniqWs* ws) {
-  const int64_t nwords = ceil_div(range > 0 ? range : 1, 32);
-  const int nblocks = (int)ceil_div(nwords, kUniqBlock);
-  const size_t b0 = align_up((size_t)nwords * 4, 256);
-  const size_t b1 = align_up((size_t)nwords * 4, 256);
-  const size_t b2 = align_up((size_t)(nblocks + 1) * 4, 256);
+  const int64_t nwords0 = ceil_div(range > 0 ? range : 1, 32);
+  const int64_t nwords1 = ceil_div(nwords0, 32);
+  const int nblocks = (int)ceil_div(nwords1, kUniqBlock);
+  const size_t b0 = align_up((size_t)nwords1 * 32 * 4, 256);  // level 0, padded to whole level-1 words
+  const size_t b1 = align_up((size_t)nwords1 * 4, 256);
+  const size_t b2 = align_up((size_t)nwords0 * 4, 256);
+  const size_t b3 = align_up((size_t)(nblocks + 1) * 4, 256);
   if (ws) {
-    ws->bitmap = (uint32_t*)base;
-    ws->word_prefix = (uint32_t*)(base + b0);
-    ws->block_sums = (int32_t*)(base + b0 + b1);
-    ws->nwords = nwords;
+    ws->l0 = (uint32_t*)base;
+    ws->l1 = (uint32_t*)(base + b0);
+    ws->word_prefix = (uint32_t*)(base + b0 + b1);
+    ws->block_sums = (int32_t*)(base + b0 + b1 + b2);
+    ws->nwords0 = nwords0;
+    ws->nwords1 = nwords1;
     ws->nblocks = nblocks;
+    ws->bitmap_bytes = b0 + b1;
   }
-  return b0 + b1 + b2;
+  return b0 + b1 + b2 + b3;
 }
 }  // namespace apt
 
 extern "C" size_t apt_unique_workspace_bytes(int64_t id_range) {
   if (id_range < 0) return 0;
   return apt::uniq_layout(id_range, nullptr, nullptr);
+}
+
+extern "C" int apt_unique_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace apt;
+  APT_CHECK_ARG(workspace && workspace_bytes > 0, "apt_unique_workspace_init: null workspace");
+  APT_CUDA(cudaMemsetAsync(workspace, 0, workspace_bytes, (cudaStream_t)stream));
+  return APT_OK;
 }
 
 extern "C" int apt_unique_sorted(const int64_t* ids, int64_t num_ids,
@@ -289,14 +343,14 @@ extern "C" int apt_unique_sorted(const int64_t* ids, int64_t num_ids,
     return APT_ERR_CAPACITY;
   }
   ProfScope prof("unique_sorted", s);
-  APT_CUDA(cudaMemsetAsync(ws.bitmap, 0, (size_t)ws.nwords * 4, s));
   const int g = wave_grid(ceil_div(num_ids, 256), 8);
-  APT_LAUNCH(k_uniq_mark, g, 256, 0, s, ids, num_ids, num_ids_dev, id_lo, id_hi, ws.bitmap, status_word);
-  APT_LAUNCH(k_uniq_count, ws.nblocks, kUniqBlock, 0, s, ws.bitmap, ws.nwords, ws.block_sums);
+  APT_LAUNCH(k_uniq_mark, g, 256, 0, s, ids, num_ids, num_ids_dev, id_lo, id_hi, ws.l0, ws.l1, status_word);
+  APT_LAUNCH(k_uniq_count, ws.nblocks, kUniqBlock, 0, s, ws.l0, ws.l1, ws.nwords1, ws.block_sums);
   APT_LAUNCH(k_scan_blocks, 1, 1024, 0, s, ws.block_sums, ws.nblocks, out_num_unique);
-  APT_LAUNCH(k_uniq_emit, ws.nblocks, kUniqBlock, 0, s, ws.bitmap, ws.nwords, id_lo,
-             ws.block_sums, ws.word_prefix, out_unique);
-  APT_LAUNCH(k_uniq_inverse, g, 256, 0, s, ids, num_ids, num_ids_dev, id_lo, id_hi, ws.bitmap,
+  APT_LAUNCH(k_uniq_emit, ws.nblocks, kUniqBlock, 0, s, ws.l0, ws.l1, ws.nwords1, id_lo, ws.block_sums,
+             ws.word_prefix, out_unique);
+  APT_LAUNCH(k_uniq_inverse, g, 256, 0, s, ids, num_ids, num_ids_dev, id_lo, id_hi, ws.l0,
              ws.word_prefix, out_inverse);
+  APT_LAUNCH(k_uniq_clear, g, 256, 0, s, ids, num_ids, num_ids_dev, id_lo, id_hi, ws.l0, ws.l1);
   return APT_OK;
 }

@@ -49,9 +49,9 @@ def _device_visible(t: torch.Tensor, name: str) -> torch.Tensor:
     if not t.is_contiguous():
         raise RuntimeError(f"{name} must be contiguous")
     if t.numel() > 0 and not t.is_pinned():
-        err = torch.cuda.cudart().cudaHostRegister(t.data_ptr(), t.numel() * t.element_size(), 0)
-        if int(err) != 0:
-            raise RuntimeError(f"cudaHostRegister({name}) failed with {err}")
+        from . import hostmem
+
+        hostmem.register(t.data_ptr(), t.numel() * t.element_size())
     return t
 
 
@@ -394,6 +394,10 @@ def _unique_enqueue(ids, n_dev, id_lo, id_hi, count_out):
     inv = torch.empty(n, dtype=torch.int64, device=ids.device)
     nbytes = lib.apt_unique_workspace_bytes(rng)
     ws = STATE.workspace("unique", nbytes)
+    if getattr(ws, "_apt_clean", False) is not True:
+        # the bitmap has to be zero once; every call then leaves it zero again
+        check(lib.apt_unique_workspace_init(_ptr(ws), ws.numel(), _stream()))
+        ws._apt_clean = True
     check(lib.apt_unique_sorted(_ptr(ids), n, _ptr(n_dev), int(id_lo), int(id_hi), _ptr(ws), ws.numel(), _ptr(uniq),
                                 _ptr(inv), _ptr(count_out), STATE.status_ptr(), _stream()))
     return uniq, inv

@@ -20,7 +20,7 @@ from typing import List, Optional
 
 import torch
 
-from . import _lib, ops
+from . import _lib, hostmem, ops
 from ._lib import check, lib
 
 _TORCH_DT = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}
@@ -147,7 +147,7 @@ def _shared_host_table(w: Workload, rank: int, world_size: int, tag: str):
     rows, dim = w.num_nodes, w.feat_dim
     dt = _TORCH_DT[w.dtype]
     if world_size == 1:
-        return torch.empty((rows, dim), dtype=dt).pin_memory(), None
+        return hostmem.alloc_table(rows, dim, dt), None
     import torch.distributed as dist
 
     path = f"/dev/shm/apt_b200_{tag}_{w.name}.bin"
@@ -157,6 +157,7 @@ def _shared_host_table(w: Workload, rank: int, world_size: int, tag: str):
             f.truncate(nbytes)
     dist.barrier()
     t = torch.from_file(path, shared=True, size=rows * dim, dtype=dt).view(rows, dim)
+    hostmem.register(t.data_ptr(), nbytes)   # page-locked before the fill, so the fill runs at link speed
     return t, path
 
 

@@ -157,14 +157,17 @@ int apt_bucket_by_owner(const int64_t* ids, int64_t num_ids,
 /* ------------------------------------------------------- sorted unique + inverse
  * Ascending unique of ids within [id_lo, id_hi) and, per input, its position
  * in that unique list. Takes the role of torch::_unique2(sorted, inverse) in
- * NPSampleAndShuffle (src/sampling.cc:58-59). A bitmap over the id range
- * replaces the sort. Ids outside the range set APT_FLAG_ID_OUT_OF_RANGE and
- * get inverse -1.
+ * NPSampleAndShuffle (src/sampling.cc:58-59). A two-level bitmap over the id
+ * range replaces the sort. Ids outside the range set APT_FLAG_ID_OUT_OF_RANGE
+ * and get inverse -1.
  *   out_unique int64[min(num_ids, id_hi-id_lo)], out_inverse int64[num_ids],
  *   out_num_unique int64[1] device word.
- * workspace: apt_unique_workspace_bytes(id_hi - id_lo) bytes.
+ * workspace: apt_unique_workspace_bytes(id_hi - id_lo) bytes, zeroed ONCE with
+ * apt_unique_workspace_init after allocation; every call leaves it zeroed
+ * again (it clears the bits it set), so a call costs O(num_ids + range/1024).
  */
 size_t apt_unique_workspace_bytes(int64_t id_range);
+int apt_unique_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
 int apt_unique_sorted(const int64_t* ids, int64_t num_ids,
                       const int64_t* num_ids_dev, int64_t id_lo, int64_t id_hi, void* workspace, size_t workspace_bytes,
                       int64_t* out_unique, int64_t* out_inverse,
