@@ -35,6 +35,7 @@ PROTOTYPES = {
     "apt_profile_read": (c_int, [c_char_p, ctypes.POINTER(c_double), ctypes.POINTER(c_int64)]),
     "apt_sample_csc_fanout": (c_int, [P, c_int64, P, c_int, P, c_int64, P, P, P, P, c_uint64, c_uint32, P, c_int, P, P, P]),
     "apt_relabel_workspace_bytes": (c_size_t, [c_int64]),
+    "apt_relabel_workspace_init": (c_int, [P, c_size_t, P]),
     "apt_relabel_csc": (c_int, [P, c_int64, P, P, c_int64, P, c_size_t, P, P, P, P, P]),
     "apt_bucket_workspace_bytes": (c_size_t, [c_int64, c_int]),
     "apt_bucket_by_owner": (c_int, [P, c_int64, P, P, c_int, c_int64, c_int, c_int, c_int, P, c_size_t, P, P, P, P, P]),

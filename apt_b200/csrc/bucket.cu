@@ -36,41 +36,66 @@ k_bucket_count(const int64_t* __restrict__ ids, int64_t n, const int64_t* __rest
   if (threadIdx.x < kMaxRanks) cnt[threadIdx.x] = 0;
   __syncthreads();
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) atomicAdd(&cnt[owner_of(ids[i], mv, p)], 1);
+  // one shared-memory add per bucket and warp instead of one per id
+  const int b = i < n ? owner_of(ids[i], mv, p) : -1;
+  const unsigned peers = __match_any_sync(0xffffffffu, b);
+  if (b >= 0 && (threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&cnt[b], __popc(peers));
   __syncthreads();
   if (threadIdx.x < p.world_size)
     hist[(int64_t)threadIdx.x * nblocks + blockIdx.x] = cnt[threadIdx.x];
 }
 
-// After the scan of hist (bucket-major), hist[b*nblocks + blk] is the first
-// output slot of bucket b's items from block blk. Bucket sizes and inclusive
-// offsets fall out of the same array.
-__global__ void k_bucket_sizes(const int32_t* __restrict__ hist, int nblocks,
-                               int world_size, int64_t n, const int64_t* __restrict__ n_dev,
-                               int64_t* __restrict__ sizes,
-                               int64_t* __restrict__ offsets) {
-  n = effective_n(n, n_dev);
-  const int b = threadIdx.x;
-  if (b >= world_size) return;
-  const int64_t beg = hist[(int64_t)b * nblocks];
-  const int64_t end = b + 1 < world_size ? hist[(int64_t)(b + 1) * nblocks] : n;
-  sizes[b] = end - beg;
-  offsets[b] = end;
-}
-
+// Scatter. hist[k*nblocks + blk] (written by k_bucket_count) is the number of
+// ids of block blk owned by rank k. The first output slot of bucket k's ids from
+// this block is (ids of all lower buckets) + (ids of bucket k in lower blocks):
+// warp k of the block sums row k of hist for that, so no scan kernel sits between
+// the two passes. Block 0 also writes the bucket sizes (+ their total) and the
+// inclusive offsets.
 __global__ void __launch_bounds__(kBucketBlock)
 k_bucket_scatter(const int64_t* __restrict__ ids, int64_t n, const int64_t* __restrict__ n_dev,
                  const int64_t* __restrict__ min_vids, OwnerParams p,
                  const int32_t* __restrict__ hist, int nblocks,
-                 int64_t* __restrict__ sorted, int64_t* __restrict__ perm) {
+                 int64_t* __restrict__ sorted, int64_t* __restrict__ perm,
+                 int64_t* __restrict__ sizes, int64_t* __restrict__ offsets) {
   __shared__ int64_t mv[kMaxRanks + 1];
   __shared__ int warp_cnt[kBucketBlock / 32][kMaxRanks];
+  __shared__ int row_total[kMaxRanks], row_before[kMaxRanks], bucket_base[kMaxRanks];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   n = effective_n(n, n_dev);
   if (threadIdx.x <= p.world_size) mv[threadIdx.x] = min_vids[threadIdx.x];
   for (int t = threadIdx.x; t < (kBucketBlock / 32) * kMaxRanks; t += blockDim.x)
     (&warp_cnt[0][0])[t] = 0;
+  if (warp < p.world_size) {
+    const int32_t* row = hist + (int64_t)warp * nblocks;
+    int tot = 0, before = 0;
+    for (int t = lane; t < nblocks; t += 32) {
+      const int c = row[t];
+      tot += c;
+      if (t < (int)blockIdx.x) before += c;
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+      tot += __shfl_down_sync(0xffffffffu, tot, d);
+      before += __shfl_down_sync(0xffffffffu, before, d);
+    }
+    if (lane == 0) {
+      row_total[warp] = tot;
+      row_before[warp] = before;
+    }
+  }
   __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int k = 0; k < p.world_size; ++k) {
+      bucket_base[k] = run + row_before[k];
+      run += row_total[k];
+      if (blockIdx.x == 0) {
+        sizes[k] = row_total[k];
+        offsets[k] = run;
+      }
+    }
+    if (blockIdx.x == 0) sizes[p.world_size] = run;
+  }
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const bool live = i < n;
   int64_t v = 0;
@@ -95,8 +120,7 @@ k_bucket_scatter(const int64_t* __restrict__ ids, int64_t n, const int64_t* __re
   }
   __syncthreads();
   if (live) {
-    const int64_t slot = (int64_t)hist[(int64_t)b * nblocks + blockIdx.x] +
-                         warp_cnt[warp][b] + rank_in_warp;
+    const int64_t slot = (int64_t)bucket_base[b] + warp_cnt[warp][b] + rank_in_warp;
     sorted[slot] = v;
     perm[i] = slot;
   }
@@ -159,13 +183,16 @@ k_uniq_count(const uint32_t* __restrict__ l0, const uint32_t* __restrict__ l1, i
 __global__ void __launch_bounds__(kUniqBlock)
 k_uniq_emit(const uint32_t* __restrict__ l0, const uint32_t* __restrict__ l1, int64_t nwords1,
             int64_t lo, const int32_t* __restrict__ block_sums,
-            uint32_t* __restrict__ word_prefix, int64_t* __restrict__ out_unique) {
+            uint32_t* __restrict__ word_prefix, int64_t* __restrict__ out_unique,
+            int64_t* __restrict__ out_num_unique) {
   __shared__ int warp_sums[33];
+  const int before = block_sum_of(block_sums, blockIdx.x, warp_sums);
   const int64_t w1 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   uint32_t bits1 = w1 < nwords1 ? l1[w1] : 0u;
   int total;
   const int ex = block_exclusive_scan(l1_word_count(l0, w1, bits1), warp_sums, &total);
-  int64_t at = (int64_t)block_sums[blockIdx.x] + ex;
+  if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) *out_num_unique = before + total;
+  int64_t at = (int64_t)before + ex;
   while (bits1) {
     const int b1 = __ffs(bits1) - 1;
     bits1 &= bits1 - 1;
@@ -244,7 +271,7 @@ extern "C" int apt_bucket_by_owner(const int64_t* ids, int64_t num_ids,
                 "apt_bucket_by_owner: rank/offset outside the world");
   cudaStream_t s = (cudaStream_t)stream;
   if (num_ids == 0) {
-    APT_CUDA(cudaMemsetAsync(out_bucket_sizes, 0, sizeof(int64_t) * world_size, s));
+    APT_CUDA(cudaMemsetAsync(out_bucket_sizes, 0, sizeof(int64_t) * (world_size + 1), s));
     APT_CUDA(cudaMemsetAsync(out_bucket_offsets, 0, sizeof(int64_t) * world_size, s));
     return APT_OK;
   }
@@ -264,11 +291,8 @@ extern "C" int apt_bucket_by_owner(const int64_t* ids, int64_t num_ids,
   int32_t* hist = (int32_t*)workspace;
   ProfScope prof("bucket", s);
   APT_LAUNCH(k_bucket_count, nblocks, kBucketBlock, 0, s, ids, num_ids, num_ids_dev, min_vids, p, hist, nblocks);
-  APT_LAUNCH(k_scan_blocks, 1, 1024, 0, s, hist, nblocks * world_size, (int64_t*)nullptr);
-  APT_LAUNCH(k_bucket_sizes, 1, 32, 0, s, hist, nblocks, world_size, num_ids, num_ids_dev,
-             out_bucket_sizes, out_bucket_offsets);
   APT_LAUNCH(k_bucket_scatter, nblocks, kBucketBlock, 0, s, ids, num_ids, num_ids_dev, min_vids, p, hist,
-             nblocks, out_sorted, out_perm);
+             nblocks, out_sorted, out_perm, out_bucket_sizes, out_bucket_offsets);
   return APT_OK;
 }
 
@@ -346,9 +370,8 @@ extern "C" int apt_unique_sorted(const int64_t* ids, int64_t num_ids,
   const int g = wave_grid(ceil_div(num_ids, 256), 8);
   APT_LAUNCH(k_uniq_mark, g, 256, 0, s, ids, num_ids, num_ids_dev, id_lo, id_hi, ws.l0, ws.l1, status_word);
   APT_LAUNCH(k_uniq_count, ws.nblocks, kUniqBlock, 0, s, ws.l0, ws.l1, ws.nwords1, ws.block_sums);
-  APT_LAUNCH(k_scan_blocks, 1, 1024, 0, s, ws.block_sums, ws.nblocks, out_num_unique);
   APT_LAUNCH(k_uniq_emit, ws.nblocks, kUniqBlock, 0, s, ws.l0, ws.l1, ws.nwords1, id_lo, ws.block_sums,
-             ws.word_prefix, out_unique);
+             ws.word_prefix, out_unique, out_num_unique);
   APT_LAUNCH(k_uniq_inverse, g, 256, 0, s, ids, num_ids, num_ids_dev, id_lo, id_hi, ws.l0,
              ws.word_prefix, out_inverse);
   APT_LAUNCH(k_uniq_clear, g, 256, 0, s, ids, num_ids, num_ids_dev, id_lo, id_hi, ws.l0, ws.l1);

@@ -180,24 +180,29 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums,
   return res;
 }
 
-// One block: in-place exclusive scan of sums[0..nblocks); the total goes to
-// sums[nblocks] and, if given, to *out_total.
-static __global__ void __launch_bounds__(1024)
-k_scan_blocks(int32_t* sums, int nblocks, int64_t* out_total) {
-  __shared__ int warp_sums[33];
-  int carry = 0;
-  for (int base = 0; base < nblocks; base += blockDim.x) {
-    const int idx = base + threadIdx.x;
-    const int v = idx < nblocks ? sums[idx] : 0;
-    int total;
-    const int ex = block_exclusive_scan(v, warp_sums, &total);
-    if (idx < nblocks) sums[idx] = carry + ex;
-    carry += total;
+// Sum of sums[0..count) computed by the whole block (every thread must call it
+// and gets the result). Lets the block that owns tile `b` find the offset of its
+// tile from the per-tile counts of an earlier kernel without a scan kernel in
+// between. `scratch` is a shared array of 33 ints. Ends with a __syncthreads().
+__device__ __forceinline__ int block_sum_of(const int32_t* __restrict__ sums, int count, int* scratch) {
+  int acc = 0;
+  for (int t = threadIdx.x; t < count; t += blockDim.x) acc += sums[t];
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, d);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) scratch[warp] = acc;
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    int v = lane < nw ? scratch[lane] : 0;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v += __shfl_down_sync(0xffffffffu, v, d);
+    if (lane == 0) scratch[32] = v;
   }
-  if (threadIdx.x == 0) {
-    sums[nblocks] = carry;
-    if (out_total) *out_total = carry;
-  }
+  __syncthreads();
+  const int total = scratch[32];
+  __syncthreads();
+  return total;
 }
 
 #endif  // __CUDACC__

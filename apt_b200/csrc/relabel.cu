@@ -4,38 +4,47 @@
 // One open-addressing table (linear probing, load <= 2/3) in the caller's
 // workspace holds, per distinct id, the smallest position at which it occurs.
 // An item is a "first occurrence" iff that minimum equals its own position;
-// an ordered compaction (block counts -> one-block scan -> in-block scan) turns
-// the first-occurrence flags into new ids, which makes the result independent
-// of the table layout and of thread scheduling.
+// an ordered compaction (per-tile counts, then each tile sums the counts of the
+// tiles before it) turns the first-occurrence flags into new ids, which makes
+// the result independent of the table layout and of thread scheduling.
 //
-//   k_clear    empties the slots this call will use
 //   k_insert   items -> table (CAS on the key, atomicMin on the position),
 //              remembers each item's slot
-//   k_count    per-block number of first occurrences
-//   k_scan     exclusive scan of the block counts, writes U
-//   k_assign   new id = block offset + in-block rank; writes unique[] and the
-//              slot's new id
-//   k_relabel  neighbours -> new id through the remembered slot
+//   k_count    per-tile number of first occurrences
+//   k_assign   new id = offset of the tile + rank inside it; writes unique[],
+//              the slot's new id and (last tile) the number of unique ids
+//   k_relabel  neighbours -> new id through the remembered slot; every item
+//              also empties its slot again
+//
+// The table is empty between calls (apt_relabel_workspace_init empties it once,
+// each call empties the slots it used), so a call costs what its own item count
+// costs and no clearing pass is needed.
 #include "common.cuh"
 
 namespace apt {
 
 constexpr int kRelabelBlock = 1024;
+constexpr unsigned long long kEmptyKey = ~0ull;
+constexpr uint32_t kNoPos = 0xffffffffu;
+
+// key, smallest position and new id of one distinct id: 16 bytes, one sector.
+struct Slot {
+  unsigned long long key;
+  uint32_t min_pos;
+  uint32_t new_id;
+};
 
 struct RelabelWs {
-  int64_t* keys;     // [cap] -1 = empty
-  int32_t* min_pos;  // [cap] 0x7f7f7f7f = none yet
-  int32_t* new_id;   // [cap]
-  int32_t* slot_of;  // [n]
-  int32_t* block_sums;  // [nblocks + 1]
-  uint32_t cap;      // capacity for the host-side (upper bound) item count
-  int nblocks;
+  Slot* slots;          // [cap_ws] all-0xff between calls
+  int32_t* slot_of;     // [items_ws]
+  int32_t* tile_count;  // [tiles_ws]
+  int64_t items_ws;     // items this workspace was sized for
+  int tiles;            // tiles of the host-side (upper bound) item count of this call
 };
 
 // Problem size as the kernels see it. With device-side counts the number of
 // seeds comes from a device word and every seed brings `per_seed` neighbours;
-// the table then only uses the capacity the real item count needs, so clearing
-// and probing cost what the real size costs, not what the upper bound would.
+// the table then uses the capacity the real item count needs.
 struct RelabelDims {
   int64_t S, n;
   uint32_t cap;
@@ -59,30 +68,25 @@ __device__ __forceinline__ RelabelDims relabel_dims(int64_t S_host, int64_t M_ho
   return d;
 }
 
-static size_t relabel_layout(int64_t n, char* base, RelabelWs* ws) {
-  const uint32_t cap = relabel_capacity(n);
-  const int nblocks = (int)ceil_div(n > 0 ? n : 1, kRelabelBlock);
-  size_t off = 0;
-  auto take = [&](size_t bytes) {
-    size_t o = off;
-    off = align_up(off + bytes, 256);
-    return o;
-  };
-  const size_t o_keys = take((size_t)cap * 8);
-  const size_t o_min = take((size_t)cap * 4);
-  const size_t o_new = take((size_t)cap * 4);
-  const size_t o_slot = take((size_t)(n > 0 ? n : 1) * 4);
-  const size_t o_sums = take((size_t)(nblocks + 1) * 4);
-  if (ws) {
-    ws->keys = (int64_t*)(base + o_keys);
-    ws->min_pos = (int32_t*)(base + o_min);
-    ws->new_id = (int32_t*)(base + o_new);
-    ws->slot_of = (int32_t*)(base + o_slot);
-    ws->block_sums = (int32_t*)(base + o_sums);
-    ws->cap = cap;
-    ws->nblocks = nblocks;
-  }
-  return off;
+static size_t relabel_bytes_for(int64_t items) {
+  const int64_t n = items > 0 ? items : 1;
+  return align_up((size_t)relabel_capacity(n) * sizeof(Slot), 256) + align_up((size_t)n * 4, 256) +
+         align_up((size_t)(ceil_div(n, kRelabelBlock) + 1) * 4, 256);
+}
+
+// The layout depends only on the size of the workspace, not on the call, so
+// that "empty between calls" holds for one fixed slot region.
+static bool relabel_layout(char* base, size_t bytes, RelabelWs* ws) {
+  // 16 * 1.5 + 4 bytes per item plus a little: first guess, then shrink until it fits
+  int64_t items = bytes > 4096 ? (int64_t)((bytes - 4096) / 281 * 10) : 0;
+  while (items > 0 && relabel_bytes_for(items) > bytes) items -= 1 + items / 4096;
+  ws->items_ws = items;
+  if (items <= 0) return false;
+  const size_t o_slot_of = align_up((size_t)relabel_capacity(items) * sizeof(Slot), 256);
+  ws->slots = (Slot*)base;
+  ws->slot_of = (int32_t*)(base + o_slot_of);
+  ws->tile_count = (int32_t*)(base + o_slot_of + align_up((size_t)items * 4, 256));
+  return true;
 }
 
 __device__ __forceinline__ uint32_t hash_id(int64_t key) {
@@ -100,21 +104,6 @@ __device__ __forceinline__ int64_t item_at(const int64_t* seeds, int64_t S,
   return i < S ? seeds[i] : nbrs[i - S];
 }
 
-// Empties the slots the real item count will use (keys = -1, min_pos = none).
-__global__ void __launch_bounds__(256)
-k_clear(int64_t S_host, int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed,
-        RelabelWs ws) {
-  const RelabelDims d = relabel_dims(S_host, M_host, S_dev, per_seed);
-  // two keys per 16-byte store; cap is rounded up to even inside the padded arrays
-  const int64_t pairs = ((int64_t)d.cap + 1) / 2;
-  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (; i < pairs; i += stride) {
-    ((uint4*)ws.keys)[i] = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);
-    ((uint2*)ws.min_pos)[i] = make_uint2(0x7f7f7f7fu, 0x7f7f7f7fu);
-  }
-}
-
 __global__ void __launch_bounds__(kRelabelBlock)
 k_insert(const int64_t* __restrict__ seeds, int64_t S_host, const int64_t* __restrict__ nbrs,
          int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed, RelabelWs ws,
@@ -122,14 +111,14 @@ k_insert(const int64_t* __restrict__ seeds, int64_t S_host, const int64_t* __res
   const RelabelDims d = relabel_dims(S_host, M_host, S_dev, per_seed);
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= d.n) return;
-  const int64_t key = item_at(seeds, d.S, nbrs, i);
-  uint32_t pos = (uint32_t)(((uint64_t)hash_id(key) * d.cap) >> 32);
-  unsigned long long* keys = (unsigned long long*)ws.keys;
+  const unsigned long long key = (unsigned long long)item_at(seeds, d.S, nbrs, i);
+  uint32_t pos = (uint32_t)(((uint64_t)hash_id((int64_t)key) * d.cap) >> 32);
   for (uint32_t probe = 0; probe < d.cap; ++probe) {
-    unsigned long long prev = keys[pos];
-    if (prev == ~0ull) prev = atomicCAS(keys + pos, ~0ull, (unsigned long long)key);
-    if (prev == ~0ull || prev == (unsigned long long)key) {
-      atomicMin(ws.min_pos + pos, (int32_t)i);
+    Slot* s = ws.slots + pos;
+    unsigned long long prev = *(volatile unsigned long long*)&s->key;
+    if (prev == kEmptyKey) prev = atomicCAS(&s->key, kEmptyKey, key);
+    if (prev == kEmptyKey || prev == key) {
+      atomicMin(&s->min_pos, (uint32_t)i);
       ws.slot_of[i] = (int32_t)pos;
       return;
     }
@@ -142,7 +131,7 @@ k_insert(const int64_t* __restrict__ seeds, int64_t S_host, const int64_t* __res
 __device__ __forceinline__ int is_first(const RelabelWs& ws, int64_t i, int64_t n) {
   if (i >= n) return 0;
   const int32_t slot = ws.slot_of[i];
-  return slot >= 0 && ws.min_pos[slot] == (int32_t)i;
+  return slot >= 0 && ws.slots[slot].min_pos == (uint32_t)i;
 }
 
 __global__ void __launch_bounds__(kRelabelBlock)
@@ -152,36 +141,43 @@ k_count(int64_t S_host, int64_t M_host, const int64_t* __restrict__ S_dev, int64
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int f = is_first(ws, i, d.n);
   const int c = __syncthreads_count(f);
-  if (threadIdx.x == 0) ws.block_sums[blockIdx.x] = c;
+  if (threadIdx.x == 0) ws.tile_count[blockIdx.x] = c;
 }
 
 __global__ void __launch_bounds__(kRelabelBlock)
 k_assign(const int64_t* __restrict__ seeds, int64_t S_host, const int64_t* __restrict__ nbrs,
          int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed, RelabelWs ws,
-         int64_t* __restrict__ out_unique) {
-  __shared__ int warp_sums[33];
+         int64_t* __restrict__ out_unique, int64_t* __restrict__ out_num_unique) {
+  __shared__ int scratch[33];
   const RelabelDims d = relabel_dims(S_host, M_host, S_dev, per_seed);
+  const int before = block_sum_of(ws.tile_count, blockIdx.x, scratch);
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int f = is_first(ws, i, d.n);
   int total;
-  const int ex = block_exclusive_scan(f, warp_sums, &total);
+  const int ex = block_exclusive_scan(f, scratch, &total);
   if (f) {
-    const int32_t id = ws.block_sums[blockIdx.x] + ex;
+    const int32_t id = before + ex;
     out_unique[id] = item_at(seeds, d.S, nbrs, i);
-    ws.new_id[ws.slot_of[i]] = id;
+    ws.slots[ws.slot_of[i]].new_id = (uint32_t)id;
   }
+  if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) *out_num_unique = before + total;
 }
 
 __global__ void __launch_bounds__(256)
 k_relabel(int64_t S_host, int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed,
           RelabelWs ws, int64_t* __restrict__ out) {
   const RelabelDims d = relabel_dims(S_host, M_host, S_dev, per_seed);
-  const int64_t M = d.n - d.S;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (; i < M; i += stride) {
-    const int32_t slot = ws.slot_of[d.S + i];
-    out[i] = slot >= 0 ? (int64_t)ws.new_id[slot] : -1;
+  for (; i < d.n; i += stride) {
+    const int32_t slot = ws.slot_of[i];
+    if (i >= d.S) out[i - d.S] = slot >= 0 ? (int64_t)ws.slots[slot].new_id : -1;
+    // Nothing reads keys or positions any more (this kernel only reads new_id):
+    // every item empties the slot it used; items of one id write the same values.
+    if (slot >= 0) {
+      ws.slots[slot].key = kEmptyKey;
+      ws.slots[slot].min_pos = kNoPos;
+    }
   }
 }
 
@@ -189,7 +185,15 @@ k_relabel(int64_t S_host, int64_t M_host, const int64_t* __restrict__ S_dev, int
 
 extern "C" size_t apt_relabel_workspace_bytes(int64_t num_items) {
   if (num_items < 0) return 0;
-  return apt::relabel_layout(num_items, nullptr, nullptr);
+  // a little headroom so that the size-only layout always fits num_items
+  return apt::relabel_bytes_for(num_items + num_items / 256 + 4096);
+}
+
+extern "C" int apt_relabel_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace apt;
+  APT_CHECK_ARG(workspace && workspace_bytes > 0, "apt_relabel_workspace_init: null workspace");
+  APT_CUDA(cudaMemsetAsync(workspace, 0xff, workspace_bytes, (cudaStream_t)stream));
+  return APT_OK;
 }
 
 extern "C" int apt_relabel_csc(const int64_t* seeds, int64_t num_seeds,
@@ -219,26 +223,20 @@ extern "C" int apt_relabel_csc(const int64_t* seeds, int64_t num_seeds,
                 "apt_relabel_csc: null pointer");
   APT_CHECK_ARG(((uintptr_t)workspace & 255) == 0, "apt_relabel_csc: workspace must be 256-byte aligned");
   RelabelWs ws;
-  const size_t need = relabel_layout(n, (char*)workspace, &ws);
-  if (workspace_bytes < need) {
-    set_error("apt_relabel_csc: workspace %zu < %zu bytes", workspace_bytes, need);
+  if (!relabel_layout((char*)workspace, workspace_bytes, &ws) || ws.items_ws < n) {
+    set_error("apt_relabel_csc: workspace of %zu bytes holds %lld items, %lld needed (apt_relabel_workspace_bytes)",
+              workspace_bytes, (long long)ws.items_ws, (long long)n);
     return APT_ERR_CAPACITY;
   }
+  ws.tiles = (int)ceil_div(n, kRelabelBlock);
   ProfScope prof("relabel", s);
-  {
-    const int grid = wave_grid(ceil_div(((int64_t)ws.cap + 1) / 2, 256), 8, 2);
-    APT_LAUNCH(k_clear, grid, 256, 0, s, num_seeds, num_neighbors, num_seeds_dev, per_seed, ws);
-  }
-  APT_LAUNCH(k_insert, ws.nblocks, kRelabelBlock, 0, s, seeds, num_seeds, neighbors, num_neighbors,
+  APT_LAUNCH(k_insert, ws.tiles, kRelabelBlock, 0, s, seeds, num_seeds, neighbors, num_neighbors,
              num_seeds_dev, per_seed, ws, status_word);
-  APT_LAUNCH(k_count, ws.nblocks, kRelabelBlock, 0, s, num_seeds, num_neighbors, num_seeds_dev, per_seed, ws);
-  APT_LAUNCH(k_scan_blocks, 1, 1024, 0, s, ws.block_sums, ws.nblocks, out_num_unique);
-  APT_LAUNCH(k_assign, ws.nblocks, kRelabelBlock, 0, s, seeds, num_seeds, neighbors, num_neighbors,
-             num_seeds_dev, per_seed, ws, out_unique);
-  if (num_neighbors > 0) {
-    const int grid = wave_grid(ceil_div(num_neighbors, 256), 8);
-    APT_LAUNCH(k_relabel, grid, 256, 0, s, num_seeds, num_neighbors, num_seeds_dev, per_seed, ws,
-               out_relabeled);
-  }
+  APT_LAUNCH(k_count, ws.tiles, kRelabelBlock, 0, s, num_seeds, num_neighbors, num_seeds_dev, per_seed, ws);
+  APT_LAUNCH(k_assign, ws.tiles, kRelabelBlock, 0, s, seeds, num_seeds, neighbors, num_neighbors,
+             num_seeds_dev, per_seed, ws, out_unique, out_num_unique);
+  const int grid = wave_grid(ceil_div(n, 256), 8);
+  APT_LAUNCH(k_relabel, grid, 256, 0, s, num_seeds, num_neighbors, num_seeds_dev, per_seed, ws,
+             out_relabeled);
   return APT_OK;
 }

@@ -47,10 +47,14 @@ class LocalExchange:
         off = offsets.cpu()
         return sorted_ids, off, off.clone()
 
-    def exchange_ids_enqueue(self, sorted_ids, sizes, offsets):
+    def exchange_ids_enqueue(self, sorted_ids, sizes, offsets, counts_out=None):
         """Stream-ordered variant without a host read: (recv buffer, device counts
-        int64[world_size + 1] with the total last)."""
-        return sorted_ids, torch.cat([offsets, offsets])
+        int64[world_size + 1] with the total last). With one rank what is
+        received is what was bucketed, so the bucket sizes are the counts."""
+        if counts_out is not None and counts_out.data_ptr() != sizes.data_ptr():
+            counts_out.copy_(sizes)
+            return sorted_ids, counts_out
+        return sorted_ids, sizes
 
     def exchange_rows(self, inputs, send_offset, recv_offset, permutation, fwd):
         from . import ops
@@ -80,6 +84,7 @@ class NcclExchange:
         return out
 
     def exchange_ids(self, sorted_ids, sizes, offsets):
+        sizes = sizes[:self.state.world_size].contiguous()
         recv_sizes = torch.empty_like(sizes)
         dist.all_to_all_single(recv_sizes, sizes, group=self.group)
         send_counts = [int(x) for x in sizes.tolist()]
@@ -87,10 +92,13 @@ class NcclExchange:
         recv = self._a2a(sorted_ids.view(-1, 1), send_counts, recv_counts, 1).view(-1)
         return recv, torch.tensor(recv_counts).cumsum(0), offsets.cpu()
 
-    def exchange_ids_enqueue(self, sorted_ids, sizes, offsets):
+    def exchange_ids_enqueue(self, sorted_ids, sizes, offsets, counts_out=None):
         # the library all-to-all needs the sizes on the host: this baseline synchronises
         recv, recv_offset, _ = self.exchange_ids(sorted_ids, sizes, offsets)
         counts = torch.cat([torch.tensor(_counts(recv_offset)), recv_offset[-1:]]).to(sorted_ids.device)
+        if counts_out is not None:
+            counts_out.copy_(counts)
+            counts = counts_out
         return recv, counts
 
     def exchange_rows(self, inputs, send_offset, recv_offset, permutation, fwd):
@@ -195,7 +203,7 @@ class P2PExchange:
         self._pull(counts_dev, None, 0, total, total, 8, recv)
         return recv, recv_offset, host[ws + 1:].clone()
 
-    def exchange_ids_enqueue(self, sorted_ids, sizes, offsets):
+    def exchange_ids_enqueue(self, sorted_ids, sizes, offsets, counts_out=None):
         """Stream-ordered seed exchange without a host read. Every rank is taken
         to send at most sorted_ids.numel() ids (the ranks run the same batch
         shape), which bounds what this rank can receive."""
@@ -203,7 +211,8 @@ class P2PExchange:
         ws = st.world_size
         n = sorted_ids.numel()
         self._check_capacity(n, 8)
-        counts_dev = torch.empty(ws + 1, dtype=torch.int64, device=sorted_ids.device)
+        counts_dev = counts_out if counts_out is not None else \
+            torch.empty(ws + 1, dtype=torch.int64, device=sorted_ids.device)
         self._push(sorted_ids, None, 0, offsets, n, 8)
         self._wait(counts_dev)
         recv = torch.empty(ws * n, dtype=torch.int64, device=sorted_ids.device)

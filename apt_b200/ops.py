@@ -134,11 +134,11 @@ class NPCState:
             self._ws[key] = buf
         return buf
 
-    NUM_WORDS = 128
+    NUM_WORDS = 256
 
     def words(self) -> torch.Tensor:
-        """int64[128] device words: [0..126] small results (counts a kernel leaves for
-        the next kernel and, later, for the host), [127] status flags."""
+        """int64[256] device words: [0..254] small results (counts a kernel leaves for
+        the next kernel and, later, for the host), [255] status flags."""
         if self._words is None or self._words.device != self.device():
             self._words = torch.zeros(self.NUM_WORDS, dtype=torch.int64, device=self.device())
             self._host_words = torch.zeros(self.NUM_WORDS, dtype=torch.int64).pin_memory()
@@ -332,6 +332,10 @@ def _relabel_enqueue(seeds, neighbors, n_dev, count_out):
     rel = torch.empty(neighbors.numel(), dtype=torch.int64, device=seeds.device)
     nbytes = lib.apt_relabel_workspace_bytes(n)
     ws = STATE.workspace("relabel", nbytes)
+    if getattr(ws, "_apt_clean", False) is not True:
+        # the table has to be empty once; every call then releases the slots it used
+        check(lib.apt_relabel_workspace_init(_ptr(ws), ws.numel(), _stream()))
+        ws._apt_clean = True
     check(lib.apt_relabel_csc(_ptr(seeds), seeds.numel(), _ptr(n_dev), _ptr(neighbors), neighbors.numel(),
                               _ptr(ws), ws.numel(), _ptr(uniq), _ptr(rel),
                               _ptr(count_out), STATE.status_ptr(), _stream()))
@@ -348,7 +352,11 @@ def relabel_csc(seeds: torch.Tensor, neighbors: torch.Tensor) -> List[torch.Tens
 
 
 # ---------------------------------------------------------------- seed shuffle
-def _bucket(seeds: torch.Tensor, n_dev: Optional[torch.Tensor] = None):
+def _bucket(seeds: torch.Tensor, n_dev: Optional[torch.Tensor] = None, sizes: Optional[torch.Tensor] = None,
+            offsets: Optional[torch.Tensor] = None):
+    """Stable partition by owner: (sorted ids, permutation, sizes[world_size + 1]
+    with their total last, inclusive offsets[world_size]). `sizes` / `offsets`
+    may be given as preallocated device views."""
     s = STATE
     if s.shuffle_min_vids is None:
         raise RuntimeError("register_min_vids has not been called")
@@ -356,8 +364,10 @@ def _bucket(seeds: torch.Tensor, n_dev: Optional[torch.Tensor] = None):
     dev = seeds.device
     sorted_ids = torch.empty(n, dtype=torch.int64, device=dev)
     perm = torch.empty(n, dtype=torch.int64, device=dev)
-    sizes = torch.empty(s.world_size, dtype=torch.int64, device=dev)
-    offsets = torch.empty(s.world_size, dtype=torch.int64, device=dev)
+    if sizes is None:
+        sizes = torch.empty(s.world_size + 1, dtype=torch.int64, device=dev)
+    if offsets is None:
+        offsets = torch.empty(s.world_size, dtype=torch.int64, device=dev)
     nbytes = lib.apt_bucket_workspace_bytes(n, s.world_size)
     ws = s.workspace("bucket", nbytes)
     node_beg = s.rank - s.rank % s.node_size

@@ -145,8 +145,14 @@ class MixedNeighborSampler:
             cur, cur_n = uniq, cnt
             slot += 1
         # outermost hop at the owners (NPSampleAndShuffle, src/sampling.cc:52-69)
-        sorted_ids, perm, sizes, offsets = ops._bucket(cur, cur_n)
-        recv, recv_counts = ops._exchange().exchange_ids_enqueue(sorted_ids, sizes, offsets)
+        # counts the host needs are written straight into the word block by the kernels:
+        # [0..15] hop counts, [16..48] ids received per peer (+ total), [64..95] my bucket offsets,
+        # [100] call-id base of graph replays, [128..160] bucket sizes when they are not what is received
+        words = st.words()
+        recv_view = words[16:16 + ws + 1]
+        sizes_view = recv_view if ws == 1 else words[128:128 + ws + 1]
+        sorted_ids, perm, sizes, offsets = ops._bucket(cur, cur_n, sizes_view, words[64:64 + ws])
+        recv, recv_counts = ops._exchange().exchange_ids_enqueue(sorted_ids, sizes, offsets, recv_view)
         total = recv_counts[ws:ws + 1]
         lo, hi = ops._owned_range()
         u_slot, in_slot = slot, slot + 1
@@ -158,11 +164,6 @@ class MixedNeighborSampler:
         if self.prefetch_features and f.feat_pos_map is not None and \
                 uniq3.numel() * f.rank_feat_dim * f.dev_feats.element_size() <= _PREFETCH_LIMIT_BYTES:
             rows = ops._gather_enqueue(uniq3, st.word(in_slot))
-        # counts the host needs ride along in the word block:
-        # [0..15] hop counts, [16..48] ids received per peer, [64..95] my bucket offsets
-        words = st.words()
-        words[16:16 + ws + 1].copy_(recv_counts)
-        words[64:64 + ws].copy_(offsets)
         return dict(layers=layers, perm=perm, inv=inv, uniq2=uniq2, uniq3=uniq3, rel3=rel3, rows=rows,
                     u_slot=u_slot, in_slot=in_slot)
 

@@ -156,8 +156,9 @@ def _shared_host_table(w: Workload, rank: int, world_size: int, tag: str):
         with open(path, "wb") as f:
             f.truncate(nbytes)
     dist.barrier()
+    # registered with CUDA after the fill (cache_feats_shared does it): registering the still
+    # unpopulated shared mapping fails with an operating-system error
     t = torch.from_file(path, shared=True, size=rows * dim, dtype=dt).view(rows, dim)
-    hostmem.register(t.data_ptr(), nbytes)   # page-locked before the fill, so the fill runs at link speed
     return t, path
 
 

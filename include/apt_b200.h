@@ -118,12 +118,16 @@ int apt_sample_csc_fanout(const int64_t* seeds, int64_t num_seeds,
  *   out_unique     int64[num_seeds + num_neighbors] (only the first U written)
  *   out_relabeled  int64[num_neighbors]
  *   out_num_unique int64[1] device word receiving U
- * workspace: apt_relabel_workspace_bytes(num_seeds + num_neighbors) bytes,
- * 256-byte aligned; contents need no initialisation.
+ * workspace: apt_relabel_workspace_bytes(num_seeds + num_neighbors) bytes or
+ * more, 256-byte aligned, emptied ONCE with apt_relabel_workspace_init after
+ * allocation; every call leaves it empty again (it releases the table slots it
+ * used), so no clearing pass runs per call. Always pass the same size for the
+ * same workspace: the layout is derived from it.
  * With num_seeds_dev the real seed count S comes from the device and the
  * neighbours are taken to be S * (num_neighbors / num_seeds) (a fixed fanout).
  */
 size_t apt_relabel_workspace_bytes(int64_t num_items);
+int apt_relabel_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
 int apt_relabel_csc(const int64_t* seeds, int64_t num_seeds,
                     const int64_t* num_seeds_dev,
                     const int64_t* neighbors, int64_t num_neighbors,
@@ -140,7 +144,8 @@ int apt_relabel_csc(const int64_t* seeds, int64_t num_seeds,
  *   owner(v): d = shuffle_id_offset; while d+1 < world_size and
  *             min_vids[d+1] <= v: ++d;  if d outside [node_beg,node_end): d = rank
  *   out_sorted[ out_perm[i] ] = ids[i]; ids of one owner keep their input order
- *   out_bucket_sizes int64[world_size]; out_bucket_offsets = inclusive cumsum.
+ *   out_bucket_sizes int64[world_size + 1] (sizes, then their total);
+ *   out_bucket_offsets int64[world_size] = inclusive cumsum.
  * min_vids is a device array of world_size+1 entries; world_size <= 32.
  * workspace: apt_bucket_workspace_bytes(num_ids, world_size) bytes.
  */

@@ -161,7 +161,8 @@ def test_bucket_matches_oracle(ws, n_ids):
     finally:
         reset_world()
     wsz, wof, wsorted, wperm = orc.bucket_by_owner(ids, mv, ws, rank=rank)
-    assert np.array_equal(host(sizes), wsz) and np.array_equal(host(offsets), wof)
+    assert np.array_equal(host(sizes)[:ws], wsz) and np.array_equal(host(offsets), wof)
+    assert int(host(sizes)[ws]) == n_ids              # the total follows the sizes
     assert np.array_equal(host(sorted_ids), wsorted) and np.array_equal(host(perm), wperm)
 
 
@@ -179,7 +180,7 @@ def test_bucket_machine_window_remap():
         reset_world()
     wsz, wof, wsorted, wperm = orc.bucket_by_owner(ids, mv, ws, rank=rank, node_beg=4, node_end=8)
     assert host(sizes)[:4].sum() == 0
-    assert np.array_equal(host(sizes), wsz) and np.array_equal(host(sorted_ids), wsorted)
+    assert np.array_equal(host(sizes)[:ws], wsz) and np.array_equal(host(sorted_ids), wsorted)
     assert np.array_equal(host(perm), wperm)
 
 
