@@ -389,11 +389,13 @@ def main():
     lib.apt_launch_count_reset()
     kept = []
     barrier()
+    torch.cuda.nvtx.range_push("apt_profiled")
     ev0.record()
     for b in dev_batches[args.warmup:]:
         sample, x = step(b)
         kept.append(sample[0].clone())
     ev1.record()
+    torch.cuda.nvtx.range_pop()
     barrier()
     launches = int(lib.apt_launch_count())
     ops.profile_enable(False)
