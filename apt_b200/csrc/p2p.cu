@@ -129,7 +129,19 @@ k_p2p_push(const char* __restrict__ src, const int64_t* __restrict__ src_index,
   const size_t slot_off = kHeaderBytes + ((size_t)parity * world_size + me) * region_bytes;
   const int64_t cap_rows = (int64_t)(region_bytes / (size_t)row_bytes);
   bool overflow = false;
-  for (int64_t j0 = warp * kMoveRows; j0 < n; j0 += warps * kMoveRows) {
+  // Walking the stream in order would have every sender write to peer 0 first,
+  // then peer 1, ...: all senders on one receiver's links at a time. Unless the
+  // index names destinations (then the source order already mixes the peers),
+  // work item t is row t / N of the bucket of peer (me + 1 + t % N) % N, so that
+  // neighbouring warps feed different peers and senders start at different ones.
+  const bool interleave = !(src_index && index_is_dest);
+  int64_t work = n;
+  if (interleave) {
+    int64_t longest = 0;
+    for (int r = 0; r < world_size; ++r) longest = max(longest, soff[r + 1] - soff[r]);
+    work = longest * world_size;
+  }
+  for (int64_t j0 = warp * kMoveRows; j0 < work; j0 += warps * kMoveRows) {
     const char* sp[kMoveRows];
     char* dp[kMoveRows];
 #pragma unroll
@@ -139,15 +151,23 @@ k_p2p_push(const char* __restrict__ src, const int64_t* __restrict__ src_index,
       const int64_t t = j0 + k;
       sp[k] = nullptr;
       dp[k] = nullptr;
-      if (t < n) {
-        const int64_t j = (src_index && index_is_dest) ? src_index[t] : t;
-        const int64_t srow = (src_index && !index_is_dest) ? src_index[t] : t;
-        if (j < 0 || j >= n) {
-          overflow = true;
-          continue;
-        }
+      if (t < work) {
+        int64_t j;
         int r = 0;
-        while (soff[r + 1] <= j) ++r;
+        if (interleave) {
+          r = (int)((me + 1 + t % world_size) % world_size);
+          const int64_t l = t / world_size;
+          if (l >= soff[r + 1] - soff[r]) continue;   // this peer's bucket is shorter
+          j = soff[r] + l;
+        } else {
+          j = src_index[t];
+          if (j < 0 || j >= n) {
+            overflow = true;
+            continue;
+          }
+          while (soff[r + 1] <= j) ++r;
+        }
+        const int64_t srow = (src_index && !index_is_dest) ? src_index[j] : (interleave ? j : t);
         const int64_t local = j - soff[r];
         if (local >= cap_rows) {
           overflow = true;

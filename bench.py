@@ -45,8 +45,9 @@ def parse():
     ap.add_argument("--impl", default="apt_b200", choices=["apt_b200", "reference"])
     ap.add_argument("--cpu-batches", type=int, default=12, help="batches of the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--stage", default="minibatch", choices=["minibatch", "gather"],
-                    help="gather: time the cached feature gather alone on a synthetic table")
+    ap.add_argument("--stage", default="minibatch", choices=["minibatch", "gather", "shuffle"],
+                    help="gather: the cached feature gather alone on a synthetic table; "
+                         "shuffle: the NPC feature shuffle alone (needs --gpus >= 2 under torchrun)")
     ap.add_argument("--rows", type=int, default=1_081_344, help="--stage gather: rows per call")
     ap.add_argument("--table-rows", type=int, default=4_000_000, help="--stage gather: rows of the cached table")
     ap.add_argument("--feat-dim", type=int, default=128)
@@ -269,11 +270,106 @@ def stage_gather(args):
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": round(gbs / peak, 4), "traffic": None}}))
 
 
+# ------------------------------------------------------------------ stage: shuffle
+def stage_shuffle(args):
+    """The NPC feature shuffle alone (FeatShuffle forward and backward): every rank asks
+    for `rows` rows owned uniformly at random by all ranks, the owners send them back.
+    Reports GB/s per GPU and direction over NVLink for the peer-to-peer path, split into
+    its kernels, next to the library all-to-all on the same rows."""
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world < 2:
+        raise SystemExit("--stage shuffle needs at least 2 ranks (torchrun)")
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    import apt_b200  # noqa: F401
+    from apt_b200 import ops
+    from apt_b200._lib import lib
+    from apt_b200.exchange import NcclExchange
+
+    dt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[args.feat_dtype]
+    dim = args.feat_dim
+    row_bytes = dim * torch.empty(0, dtype=dt).element_size()
+    rows = args.rows
+    ops.STATE.p2p_region_bytes = max(64 << 20, int(2.0 * rows / world * row_bytes) + (8 << 20))
+    ops.init(rank, local, world, ops.nccl_get_unique_id(), world)
+    p2p, nccl = ops.STATE.exchange, NcclExchange(ops.STATE)
+    n = 1 << 24
+    ops.register_min_vids(torch.tensor([n * r // world for r in range(world)] + [n]))
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    ids = torch.randint(0, n, (rows,), generator=g, device="cuda")
+    recv_ids, perm, send_off, recv_off = ops.shuffle_seeds(ids)   # python names: send_offset = C++ recv_offset
+    x = torch.randn((recv_ids.numel(), dim), generator=g, device="cuda").to(dt)
+    grad = torch.randn((rows, dim), generator=g, device="cuda").to(dt)
+    counts = [int(c) for c in (send_off - torch.cat([torch.zeros(1, dtype=torch.int64), send_off[:-1]])).tolist()]
+    remote_out = (sum(counts) - counts[rank]) * row_bytes          # bytes this rank sends to other GPUs (fwd)
+
+    def run(ex, fwd, profiled):
+        ops.STATE.exchange = ex
+        fn = (lambda: ops.feat_shuffle(x, send_off, recv_off, perm, dim, 1)) if fwd else \
+             (lambda: ops.feat_shuffle(grad, recv_off, send_off, perm, dim, 0))
+        for _ in range(args.warmup):
+            fn()
+        ops.profile_enable(profiled)
+        for tag in (b"p2p_push", b"p2p_wait", b"p2p_pull"):
+            t_, k_ = ctypes.c_double(), ctypes.c_int64()
+            lib.apt_profile_read(tag, ctypes.byref(t_), ctypes.byref(k_))
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ops.profile_enable(False)
+        ms = torch.tensor([e0.elapsed_time(e1) / args.steps], device="cuda")
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        stages = {}
+        for tag in ("p2p_push", "p2p_wait", "p2p_pull"):
+            t_, k_ = ctypes.c_double(), ctypes.c_int64()
+            lib.apt_profile_read(tag.encode(), ctypes.byref(t_), ctypes.byref(k_))
+            stages[tag] = 1000.0 * t_.value / max(k_.value, 1)
+        return float(ms.item()), stages
+
+    res = {}
+    for name, ex in (("p2p", p2p), ("nccl", nccl)):
+        for fwd in (True, False):
+            ms, _ = run(ex, fwd, False)
+            res[f"{name}_{'fwd' if fwd else 'bwd'}_ms"] = ms
+    _, stages = run(p2p, True, True)
+    ops.STATE.exchange = p2p
+    ops.check_status()
+    link_peak = 770.0      # GB/s per direction per GPU, measured peer copy on this pool (900 nominal)
+    rem = torch.tensor([float(remote_out)], device="cuda")
+    dist.all_reduce(rem, op=dist.ReduceOp.MAX)
+    remote = float(rem.item())
+    gbs = {k: remote / (v * 1e-3) / 1e9 for k, v in res.items()}
+    push_gbs = remote / (stages["p2p_push"] * 1e-6) / 1e9
+    if rank == 0:
+        print(json.dumps({
+            "metric": "NPC feature shuffle GB/s per GPU and direction over NVLink", "value": gbs["p2p_fwd_ms"],
+            "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": res["p2p_fwd_ms"], "higher_is_better": True, "dtype": args.feat_dtype, "data": "synthetic",
+            "config": {"workload": "stage shuffle", "rows_per_gpu": rows, "row_bytes": row_bytes,
+                       "remote_bytes_per_gpu": remote, "owners": "uniform over ranks"},
+            "ms": res, "gbs": gbs, "p2p_stage_us": stages,
+            "roofline": {"kernel": "k_p2p_push", "bound": "nvlink", "achieved": round(push_gbs, 1), "peak": link_peak,
+                         "peak_kind": "measured peer copy per direction (900 nominal)", "unit": "GB/s",
+                         "frac": round(push_gbs / link_peak, 4), "traffic": None},
+            "whole_op_frac_of_link": round(gbs["p2p_fwd_ms"] / link_peak, 4),
+            "nccl_baseline_gbs": gbs["nccl_fwd_ms"]}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 # ------------------------------------------------------------------------- main
 def main():
     args = parse()
     if args.stage == "gather":
         return stage_gather(args)
+    if args.stage == "shuffle":
+        return stage_shuffle(args)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
