@@ -16,9 +16,17 @@
 
 #include "common.cuh"
 
+#include <math.h>
+
 namespace apt {
 
 constexpr int kMaxSegments = 64;
+
+static int pow2_at_least_fwd(int64_t x) {
+  int g = 1;
+  while (g < x && g < 32) g <<= 1;
+  return g;
+}
 
 struct SegTable {
   // Copied into shared memory by each block: first edge and row bases per segment.
@@ -96,6 +104,26 @@ k_edge_ranges(const int64_t* __restrict__ col, int64_t E, SegTable st,
   for (; e < E; e += stride) {
     const int64_t d = ooff[seg_of(coo, st.nseg, e)] + col[e];
     const int64_t prev = e > 0 ? ooff[seg_of(coo, st.nseg, e - 1)] + col[e - 1] : (int64_t)-1;
+    if (d < prev || d < 0 || d >= num_out_rows) {
+      bad = true;
+      continue;
+    }
+    for (int64_t t = prev + 1; t <= d; ++t) ws.range[t] = e;
+    if (e == E - 1)
+      for (int64_t t = d + 1; t <= num_out_rows; ++t) ws.range[t] = E;
+  }
+  if (bad) atomicOr(ws.flags, 1);
+}
+
+// Single-block variant: col already holds output rows.
+__global__ void __launch_bounds__(256)
+k_edge_ranges_single(const int64_t* __restrict__ col, int64_t E, int64_t num_out_rows, SpmmWs ws) {
+  int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  bool bad = false;
+  for (; e < E; e += stride) {
+    const int64_t d = col[e];
+    const int64_t prev = e > 0 ? col[e - 1] : (int64_t)-1;
     if (d < prev || d < 0 || d >= num_out_rows) {
       bad = true;
       continue;
@@ -274,6 +302,90 @@ k_sddmm(const int64_t* __restrict__ row, const int64_t* __restrict__ col, int64_
   }
 }
 
+// ---- fused GAT edge pipeline ---------------------------------------------------------
+// For every destination row d with its edges e (src_e -> d) and every head h:
+//   s_e = leaky_relu(el[src_e, h] + er[d, h]);  a_e = softmax over the edges of d;
+//   out[d, h, :] = sum_e a_e * ft[src_e, h, :]
+// which is u_add_v -> leaky_relu -> edge_softmax -> u_mul_e + sum in one pass
+// over a grouped block (python/npc/model/gatconv.py:113-124). One lane group per
+// destination row as in k_spmm_rows; scores are recomputed per lane (a block has
+// at most a few dozen edges per row), sums stay in fp32 registers.
+template <typename T, int VE>
+__global__ void __launch_bounds__(256)
+k_gat_rows(const int64_t* __restrict__ row, const T* __restrict__ ft, const T* __restrict__ el,
+           const T* __restrict__ er, int num_heads, int64_t head_dim, float slope,
+           int64_t num_dst, SpmmWs ws, T* __restrict__ out, T* __restrict__ attn,
+           int group, int32_t* status) {
+  const bool unsorted = *ws.flags != 0;
+  if (unsorted && blockIdx.x == 0 && threadIdx.x == 0) atomicOr(status, APT_FLAG_NOT_GROUPED);
+  const int sub = threadIdx.x % group;
+  const int64_t rows_per_block = blockDim.x / group;
+  const int64_t feat_dim = (int64_t)num_heads * head_dim;
+  const int64_t nvec = feat_dim / VE;
+  int64_t d = (int64_t)blockIdx.x * rows_per_block + threadIdx.x / group;
+  const int64_t stride = (int64_t)gridDim.x * rows_per_block;
+  for (; d < num_dst; d += stride) {
+    const int64_t e0 = unsorted ? 0 : ws.range[d];
+    const int64_t e1 = unsorted ? 0 : ws.range[d + 1];
+    for (int64_t c = sub; c < nvec; c += group) {
+      const int h = (int)((c * VE) / head_dim);
+      const float r = Elem<T>::to_f(er[d * num_heads + h]);
+      float m = -INFINITY;
+      for (int64_t e = e0; e < e1; ++e) {
+        float s = Elem<T>::to_f(el[row[e] * num_heads + h]) + r;
+        s = s > 0.f ? s : s * slope;
+        m = fmaxf(m, s);
+      }
+      float denom = 0.f;
+      for (int64_t e = e0; e < e1; ++e) {
+        float s = Elem<T>::to_f(el[row[e] * num_heads + h]) + r;
+        s = s > 0.f ? s : s * slope;
+        denom += expf(s - m);
+      }
+      const float inv = denom > 0.f ? 1.f / denom : 0.f;
+      float acc[VE];
+#pragma unroll
+      for (int t = 0; t < VE; ++t) acc[t] = 0.f;
+      const bool writes_attn = attn != nullptr && (c * VE) % head_dim == 0;
+      for (int64_t e = e0; e < e1; ++e) {
+        const int64_t src = row[e];
+        float s = Elem<T>::to_f(el[src * num_heads + h]) + r;
+        s = s > 0.f ? s : s * slope;
+        const float a = expf(s - m) * inv;
+        if (writes_attn) attn[e * num_heads + h] = Elem<T>::from_f(a);
+        const Pack<T, VE> p = load_pack<T, VE>(ft + src * feat_dim + c * VE);
+#pragma unroll
+        for (int t = 0; t < VE; ++t) acc[t] += a * Elem<T>::to_f(p.v[t]);
+      }
+      Pack<T, VE> o;
+#pragma unroll
+      for (int t = 0; t < VE; ++t) o.v[t] = Elem<T>::from_f(acc[t]);
+      store_pack<T, VE>(out + d * feat_dim + c * VE, o);
+    }
+  }
+}
+
+template <typename T>
+static int launch_gat(bool vec, const int64_t* row, const void* ft, const void* el, const void* er,
+                      int num_heads, int64_t head_dim, float slope, int64_t num_dst, SpmmWs ws, void* out,
+                      void* attn, int32_t* status, cudaStream_t s) {
+  constexpr int VE = 16 / sizeof(T);
+  const int64_t feat_dim = (int64_t)num_heads * head_dim;
+  ProfScope prof("gat_rows", s);
+  if (vec) {
+    const int group = pow2_at_least_fwd(feat_dim / VE);
+    const int grid = wave_grid(ceil_div(num_dst, 256 / group), 8);
+    APT_LAUNCH((k_gat_rows<T, VE>), grid, 256, 0, s, row, (const T*)ft, (const T*)el, (const T*)er, num_heads,
+               head_dim, slope, num_dst, ws, (T*)out, (T*)attn, group, status);
+  } else {
+    const int group = pow2_at_least_fwd(feat_dim);
+    const int grid = wave_grid(ceil_div(num_dst, 256 / group), 8);
+    APT_LAUNCH((k_gat_rows<T, 1>), grid, 256, 0, s, row, (const T*)ft, (const T*)el, (const T*)er, num_heads,
+               head_dim, slope, num_dst, ws, (T*)out, (T*)attn, group, status);
+  }
+  return APT_OK;
+}
+
 static int pow2_at_least(int64_t x) {
   int g = 1;
   while (g < x && g < 32) g <<= 1;
@@ -446,5 +558,54 @@ extern "C" int apt_sddmm(int op, int dtype, const int64_t* coo_row, const int64_
       return dispatch_sddmm<__nv_bfloat16>(op, vec, coo_row, coo_col, num_edges, lhs, rhs, feat_dim, st, rhs_offset, out, s);
     default:
       return dispatch_sddmm<__half>(op, vec, coo_row, coo_col, num_edges, lhs, rhs, feat_dim, st, rhs_offset, out, s);
+  }
+}
+
+extern "C" int apt_gat_edge_softmax_sum(int dtype, const int64_t* coo_row, const int64_t* coo_col,
+                                        int64_t num_edges, const void* ft, const void* el, const void* er,
+                                        int num_heads, int64_t head_dim, float negative_slope,
+                                        int64_t num_dst, void* out, void* out_attn, void* workspace,
+                                        size_t workspace_bytes, int32_t* status_word, void* stream) {
+  using namespace apt;
+  APT_CHECK_ARG(dtype >= APT_F32 && dtype <= APT_F16, "apt_gat_edge_softmax_sum: dtype %d", dtype);
+  APT_CHECK_ARG(num_edges >= 0 && num_heads >= 1 && head_dim >= 1 && num_dst >= 0,
+                "apt_gat_edge_softmax_sum: bad sizes");
+  if (num_dst == 0) return APT_OK;
+  const size_t esz = elem_size(dtype);
+  const int64_t feat_dim = (int64_t)num_heads * head_dim;
+  cudaStream_t s = (cudaStream_t)stream;
+  APT_CHECK_ARG(out && status_word, "apt_gat_edge_softmax_sum: null output");
+  if (num_edges == 0) {
+    APT_CUDA(cudaMemsetAsync(out, 0, (size_t)num_dst * feat_dim * esz, s));
+    return APT_OK;
+  }
+  APT_CHECK_ARG(coo_row && coo_col && ft && el && er && workspace, "apt_gat_edge_softmax_sum: null pointer");
+  APT_CHECK_ARG(((uintptr_t)workspace & 255) == 0, "apt_gat_edge_softmax_sum: workspace must be 256-byte aligned");
+  const size_t need = apt_spmm_workspace_bytes(num_dst);
+  if (workspace_bytes < need) {
+    set_error("apt_gat_edge_softmax_sum: workspace %zu < %zu bytes", workspace_bytes, need);
+    return APT_ERR_CAPACITY;
+  }
+  SpmmWs ws;
+  ws.range = (int64_t*)workspace;
+  ws.flags = (int32_t*)((char*)workspace + need - 256);
+  APT_CUDA(cudaMemsetAsync(ws.flags, 0, 4, s));
+  {
+    ProfScope prof("spmm_ranges", s);
+    const int grid = wave_grid(ceil_div(num_edges, 256), 8);
+    APT_LAUNCH(k_edge_ranges_single, grid, 256, 0, s, coo_col, num_edges, num_dst, ws);
+  }
+  const int ve = 16 / (int)esz;
+  const bool vec = (((uint64_t)(feat_dim * esz) | (uintptr_t)ft | (uintptr_t)out) & 15) == 0 && head_dim % ve == 0;
+  switch (dtype) {
+    case APT_F32:
+      return launch_gat<float>(vec, coo_row, ft, el, er, num_heads, head_dim, negative_slope, num_dst, ws, out,
+                               out_attn, status_word, s);
+    case APT_BF16:
+      return launch_gat<__nv_bfloat16>(vec, coo_row, ft, el, er, num_heads, head_dim, negative_slope, num_dst, ws,
+                                       out, out_attn, status_word, s);
+    default:
+      return launch_gat<__half>(vec, coo_row, ft, el, er, num_heads, head_dim, negative_slope, num_dst, ws, out,
+                                out_attn, status_word, s);
   }
 }

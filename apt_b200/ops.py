@@ -176,6 +176,7 @@ def _flag_text(flags):
         _lib.FLAG_ZERO_DEGREE: "node without in-neighbours sampled",
         _lib.FLAG_TABLE_FULL: "workspace or inbox region too small",
         _lib.FLAG_PEER_TIMEOUT: "a peer's data did not arrive in time",
+        _lib.FLAG_NOT_GROUPED: "edges of a block are not grouped by destination",
     }
     return ", ".join(v for k, v in names.items() if flags & k)
 
@@ -404,10 +405,11 @@ def _unique_enqueue(ids, n_dev, id_lo, id_hi, count_out):
     inv = torch.empty(n, dtype=torch.int64, device=ids.device)
     nbytes = lib.apt_unique_workspace_bytes(rng)
     ws = STATE.workspace("unique", nbytes)
-    if getattr(ws, "_apt_clean", False) is not True:
-        # the bitmap has to be zero once; every call then leaves it zero again
+    if getattr(ws, "_apt_clean_range", None) != rng:
+        # the bitmap has to be zero once per id range (the layout follows the range);
+        # every call then leaves it zero again
         check(lib.apt_unique_workspace_init(_ptr(ws), ws.numel(), _stream()))
-        ws._apt_clean = True
+        ws._apt_clean_range = rng
     check(lib.apt_unique_sorted(_ptr(ids), n, _ptr(n_dev), int(id_lo), int(id_hi), _ptr(ws), ws.numel(), _ptr(uniq),
                                 _ptr(inv), _ptr(count_out), STATE.status_ptr(), _stream()))
     return uniq, inv
@@ -589,6 +591,34 @@ def sddmm_u_add_v(coo_row, coo_col, lhs, rhs, coo_offset, lhs_offset, rhs_offset
 def sddmm_u_mul_v(coo_row, coo_col, lhs, rhs, coo_offset, lhs_offset, rhs_offset):
     """UMulV, src/sddmm.cc:21-31."""
     return _sddmm(1, coo_row, coo_col, lhs, rhs, coo_offset, lhs_offset, rhs_offset)
+
+
+def gat_edge_softmax_sum(coo_row, coo_col, ft, el, er, num_dst: int, negative_slope: float = 0.2,
+                         return_attention: bool = False):
+    """One sampled block of a GAT layer in one kernel: u_add_v(el, er) -> leaky_relu ->
+    edge_softmax -> u_mul_e(ft, a) summed per destination (the DGL calls of
+    python/npc/model/gatconv.py:113-124). ft [num_src, H, Dh] or [num_src, H*Dh],
+    el [num_src, H(,1)], er [num_dst, H(,1)]; edges grouped by destination.
+    Returns out [num_dst, H, Dh] (and the attention [E, H, 1])."""
+    if ft.dtype not in _DTYPE_CODE or el.dtype != ft.dtype or er.dtype != ft.dtype:
+        raise RuntimeError(f"gat_edge_softmax_sum: unsupported dtypes {ft.dtype}/{el.dtype}/{er.dtype}")
+    coo_row = _need_cuda(coo_row, "coo_row")
+    coo_col = _need_cuda(coo_col, "coo_col")
+    ft = _need_cuda(ft, "ft", dtype=None)
+    el = _need_cuda(el, "el", dtype=None)
+    er = _need_cuda(er, "er", dtype=None)
+    num_src = ft.shape[0]
+    heads = el.numel() // max(num_src, 1) if num_src else er.numel() // max(num_dst, 1)
+    head_dim = ft.numel() // max(num_src * heads, 1)
+    out = torch.empty((num_dst, heads, head_dim), dtype=ft.dtype, device=ft.device)
+    attn = torch.empty((coo_row.numel(), heads, 1), dtype=ft.dtype, device=ft.device) if return_attention else None
+    nbytes = lib.apt_spmm_workspace_bytes(num_dst)
+    ws = STATE.workspace("spmm", nbytes)
+    check(lib.apt_gat_edge_softmax_sum(_DTYPE_CODE[ft.dtype], _ptr(coo_row), _ptr(coo_col), coo_row.numel(),
+                                       _ptr(ft), _ptr(el), _ptr(er), int(heads), int(head_dim),
+                                       float(negative_slope), int(num_dst), _ptr(out), _ptr(attn), _ptr(ws),
+                                       ws.numel(), STATE.status_ptr(), _stream()))
+    return (out, attn) if return_attention else out
 
 
 # ------------------------------------------------------------------ row movers

@@ -245,6 +245,40 @@ class MixedNeighborSampler:
         return self._finish(seeds, plan.bufs)
 
 
+class SPGATSampler:
+    """SNP strategy with a GAT model (MixedPSNeighborSampler with system "SP",
+    model "GAT", shuffle_with_dst False, python/npc/sampler.py:187-238 and
+    :358-364): inner hops as in GDP; in the outermost hop the block keeps the
+    local dst nodes, its sources are the sorted unique neighbours, and those
+    ids travel to their owners, which load and project their features; the
+    feature shuffle brings the projected rows back in unique-neighbour order.
+    Returns (input_nodes, output_nodes, blocks, perm, send_offset, recv_offset)
+    with input_nodes = cat(dst nodes, ids received from the other ranks)."""
+
+    def __init__(self, rank: int, fanouts: List[int]):
+        self.rank = rank
+        self.fanouts = list(fanouts)
+
+    def sample(self, graph, seeds: torch.Tensor):
+        output_nodes = seeds
+        blocks = []
+        n_total = ops.STATE.graph.num_total_nodes
+        for layer_id, fanout in enumerate(reversed(self.fanouts)):
+            seeds, neighbors = ops.local_sample_one_layer(seeds, fanout)
+            if layer_id != len(self.fanouts) - 1:
+                block = create_block(seeds, neighbors, fanout)
+                seeds = block.src_ids
+                blocks.insert(0, block)
+                continue
+            num_dst = seeds.numel()
+            unique_neigh, arange_src = ops.unique_sorted(neighbors, 0, n_total)
+            arange_dst = torch.arange(num_dst, device=seeds.device).repeat_interleave(fanout)
+            blocks.insert(0, Block(arange_src, arange_dst, unique_neigh.numel(), num_dst, unique_neigh, fanout))
+            shuffled_neigh, perm, send_offset, recv_offset = ops.sp_sample_shuffle_src(unique_neigh)
+            seeds = torch.cat((seeds, shuffled_neigh))
+        return seeds, output_nodes, blocks, perm, send_offset, recv_offset
+
+
 class DPNeighborSampler:
     """GDP strategy: every hop local (python/npc/sampler.py:202-203 with the
     common block construction)."""

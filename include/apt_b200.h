@@ -52,6 +52,7 @@ typedef enum apt_dtype { APT_F32 = 0, APT_BF16 = 1, APT_F16 = 2 } apt_dtype;
 #define APT_FLAG_ZERO_DEGREE     4  /* sampled a node with no in-neighbour */
 #define APT_FLAG_TABLE_FULL      8  /* relabel hash table overflow (workspace too small) */
 #define APT_FLAG_PEER_TIMEOUT    16 /* a peer's flag did not arrive in time */
+#define APT_FLAG_NOT_GROUPED     32 /* a block operator got edges not grouped by destination */
 
 const char* apt_last_error(void);
 int apt_version(void);
@@ -167,9 +168,10 @@ int apt_bucket_by_owner(const int64_t* ids, int64_t num_ids,
  * and get inverse -1.
  *   out_unique int64[min(num_ids, id_hi-id_lo)], out_inverse int64[num_ids],
  *   out_num_unique int64[1] device word.
- * workspace: apt_unique_workspace_bytes(id_hi - id_lo) bytes, zeroed ONCE with
- * apt_unique_workspace_init after allocation; every call leaves it zeroed
- * again (it clears the bits it set), so a call costs O(num_ids + range/1024).
+ * workspace: apt_unique_workspace_bytes(id_hi - id_lo) bytes, zeroed with
+ * apt_unique_workspace_init after allocation and again whenever it is used with
+ * another range width (the layout follows the width); every call leaves it
+ * zeroed again (it clears the bits it set), so a call costs O(num_ids + range/1024).
  */
 size_t apt_unique_workspace_bytes(int64_t id_range);
 int apt_unique_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
@@ -277,6 +279,26 @@ int apt_sddmm(int op, int dtype, const int64_t* coo_row,
               const void* rhs, int64_t feat_dim, const int64_t* coo_offset,
               const int64_t* lhs_offset, const int64_t* rhs_offset,
               int num_segments, void* out, void* stream);
+
+/* Fused GAT edge pipeline over one sampled block whose edges are grouped by
+ * destination (col non-decreasing): per destination d and head h,
+ *   s_e = leaky_relu(el[row[e], h] + er[d, h]),  a = softmax of s over d's edges,
+ *   out[d, h, :] = sum_e a_e * ft[row[e], h, :].
+ * It stands for the DGL calls of the reference's SNP-GAT layer
+ * (python/npc/model/gatconv.py:113-124: u_add_v, leaky_relu, edge_softmax,
+ * u_mul_e + sum), which the reference leaves to DGL. ft is [num_src,
+ * num_heads*head_dim], el [num_src, num_heads], er [num_dst, num_heads];
+ * out_attn ([num_edges, num_heads], may be NULL) receives a. Rows without
+ * edges become 0. Edges that are not grouped set APT_FLAG_NOT_GROUPED and give
+ * zeros. workspace: apt_spmm_workspace_bytes(num_dst) bytes. */
+int apt_gat_edge_softmax_sum(int dtype, const int64_t* coo_row,
+                             const int64_t* coo_col, int64_t num_edges,
+                             const void* ft, const void* el, const void* er,
+                             int num_heads, int64_t head_dim,
+                             float negative_slope, int64_t num_dst, void* out,
+                             void* out_attn, void* workspace,
+                             size_t workspace_bytes, int32_t* status_word,
+                             void* stream);
 
 /* ------------------------------------------------------- local row movers
  * out[i] = in[index[i]] and out[index[i]] = in[i] over rows of row_bytes

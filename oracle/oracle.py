@@ -374,6 +374,51 @@ def sddmm(op, row, col, lhs, rhs, coo_offset, lhs_offset, rhs_offset, acc=np.flo
     return a + b if op == "u_add_v" else a * b
 
 
+def gat_edge_softmax_sum(row, col, ft, el, er, num_dst, negative_slope=0.2):
+    """The DGL calls of the reference's SNP-GAT layer, python/npc/model/gatconv.py:113-124,
+    restated from the public operator definitions (DGL itself is not available, so
+    this stage is parity-unpinned): e = leaky_relu(el[src] + er[dst]) (fn.u_add_v +
+    LeakyReLU), a = softmax of e over the incoming edges of each dst per head
+    (dgl.ops.edge_softmax), out[dst] = sum_e a * ft[src] (fn.u_mul_e + fn.sum).
+    ft [Ns, H, D], el [Ns, H], er [Nd, H]. Returns (out [Nd, H, D], a [E, H]) in fp64."""
+    row = np.asarray(row, dtype=I64)
+    col = np.asarray(col, dtype=I64)
+    ft = np.asarray(ft, dtype=np.float64)
+    el = np.asarray(el, dtype=np.float64).reshape(ft.shape[0], -1)
+    er = np.asarray(er, dtype=np.float64).reshape(num_dst, -1)
+    s = el[row] + er[col]
+    s = np.where(s > 0, s, s * negative_slope)
+    m = np.full((num_dst, s.shape[1]), -np.inf)
+    np.maximum.at(m, col, s)
+    ex = np.exp(s - m[col])
+    den = np.zeros((num_dst, s.shape[1]))
+    np.add.at(den, col, ex)
+    a = ex / den[col]
+    out = np.zeros((num_dst,) + ft.shape[1:])
+    np.add.at(out, col, a[:, :, None] * ft[row])
+    return out, a
+
+
+def sp_gat_sample(seeds_per_rank, fanout, min_vids, graph, key, call_id):
+    """Outermost hop of the SNP-GAT sampler, python/npc/sampler.py:215-238, for all
+    ranks at once: local sampling, sorted unique of the neighbours as block sources,
+    shuffle of those ids to their owners (SPSampleShuffleSrc, src/sampling.cc:151-157).
+    Per rank: dict(neighbors, unique_neigh, arange_src, shuffled, perm, send_offset,
+    recv_offset, input_nodes)."""
+    res = []
+    uniq = []
+    for seeds in seeds_per_rank:
+        nbr = sample_csc_fanout(seeds, fanout, *graph, key=key, call_id=call_id)
+        u, inv = unique_sorted(nbr)
+        uniq.append(u)
+        res.append(dict(neighbors=nbr, unique_neigh=u, arange_src=inv))
+    shuffled = shuffle_seeds(uniq, min_vids)
+    for r, (recv, perm, recv_off, dev_off) in enumerate(shuffled):
+        res[r].update(shuffled=recv, perm=perm, send_offset=recv_off, recv_offset=dev_off,
+                      input_nodes=np.concatenate([np.asarray(seeds_per_rank[r], dtype=I64), recv]))
+    return res
+
+
 # ------------------------------------------------------- synthetic generators
 def rmat_edges(seed, first_edge, num_edges, scale, num_nodes, a=0.57, b=0.19, c=0.19):
     """The benchmark's R-MAT generator (counter-based; same stream as the GPU

@@ -102,6 +102,30 @@ def main():
         assert np.array_equal(host(ba.coo_row), host(bb.coo_row)) and np.array_equal(host(ba.src_ids), host(bb.src_ids))
         assert np.array_equal(host(ba.coo_col), host(bb.coo_col)) and (ba.num_src, ba.num_dst) == (bb.num_src, bb.num_dst)
 
+    # --- SNP-GAT outermost hop (python/npc/sampler.py:215-238): unique sources go to their owners,
+    # their projected rows come back in unique-source order (python/npc/model/gatconv.py:98-105)
+    ops.set_sampling(key=321, call_id=0)
+    sp = apt_b200.SPGATSampler(rank, [10])
+    sp_seeds = seeds[:700]
+    in_nodes, _, sp_blocks, sp_perm, sp_send, sp_recv = sp.sample(None, torch.from_numpy(sp_seeds).cuda())
+    all_sp_seeds = gather_objects(sp_seeds)
+    all_sp = gather_objects((host(in_nodes), host(sp_blocks[0].coo_row), host(sp_blocks[0].src_ids), host(sp_perm),
+                             sp_send.numpy(), sp_recv.numpy()))
+    if rank == 0:
+        want = orc.sp_gat_sample(all_sp_seeds, 10, mv, graph, key=321, call_id=0)
+        for r in range(world):
+            got = all_sp[r]
+            w = want[r]
+            names = ("input_nodes", "arange_src", "unique_neigh", "perm", "send_offset", "recv_offset")
+            for name, a_ in zip(names, got):
+                assert np.array_equal(a_, w[name]), \
+                    f"rank {r}: SNP-GAT sampler output {name} differs from the oracle ({a_.shape} vs {w[name].shape})"
+    g0 = torch.Generator(device="cuda").manual_seed(11)
+    table_sp = torch.randn((n, 256), generator=g0, device="cuda").bfloat16()       # 4 heads x 64, bf16
+    projected = table_sp[in_nodes][sp_blocks[0].num_dst:]
+    back = ops.feat_shuffle(projected, sp_send, sp_recv, sp_perm, 256, 1)
+    assert torch.equal(back, table_sp[sp_blocks[0].src_ids]), "SNP-GAT feature shuffle"
+
     # --- feature shuffle forward/backward (fp32 1 KiB rows, bf16 512 B rows, odd width)
     for dtype, D in ((torch.float32, 256), (torch.bfloat16, 256), (torch.float32, 3)):
         g = torch.Generator(device="cuda").manual_seed(7)

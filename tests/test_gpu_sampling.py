@@ -193,6 +193,15 @@ def test_unique_sorted_matches_oracle(n_ids, lo, hi):
     assert np.array_equal(host(uniq), wu) and np.array_equal(host(inv), wi)
 
 
+def test_unique_sorted_alternating_ranges_share_one_workspace():
+    rng = np.random.default_rng(77)
+    for lo, hi in ((0, 5000), (0, 9000), (100, 4100), (0, 9000), (0, 5000)):
+        ids = rng.integers(lo, hi, 3000).astype(I64)
+        uniq, inv = ops.unique_sorted(dev(ids), lo, hi)
+        wu, wi = orc.unique_sorted(ids)
+        assert np.array_equal(host(uniq), wu) and np.array_equal(host(inv), wi)
+
+
 def test_committed_fixture_on_gpu():
     z = np.load(os.path.join(GOLDEN, "path_small.npz"))
     install_graph(z["indptr"], z["indices"])
