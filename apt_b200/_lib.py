@@ -44,7 +44,7 @@ PROTOTYPES = {
     "apt_unique_workspace_init": (c_int, [P, c_size_t, P]),
     "apt_unique_sorted": (c_int, [P, c_int64, P, c_int64, c_int64, P, c_size_t, P, P, P, P, P]),
     "apt_gather_workspace_bytes": (c_size_t, [c_int64]),
-    "apt_gather_rows": (c_int, [P, c_int64, P, P, c_int64, P, c_int64, c_int64, P, c_int64, c_int64, c_int64, P, P, c_size_t, P, P, P]),
+    "apt_gather_rows": (c_int, [P, c_int64, P, P, c_int64, P, c_int64, c_int64, P, c_int64, c_int64, c_int64, P, P, c_size_t, P, P]),
     "apt_gather_static_max_rows": (c_int64, []),
     "apt_gather_rows_static": (c_int, [P, c_int64, P, c_int64, P, c_int64, c_int64, P, c_int64, c_int64, c_int64, P, P, P]),
     "apt_spmm_workspace_bytes": (c_size_t, [c_int64]),

@@ -1,17 +1,22 @@
 // Cache-aware feature-row gather.
 //
-//   k_classify   one thread per requested row: id -> feat_pos_map entry, kept
-//                in a dense scratch array; rows that live in host memory are
-//                also appended (warp-aggregated) to a miss list.
-//   k_copy_hits  HBM -> HBM. One warp moves kRowsPerWarp rows at a time, each
-//                lane one 16-byte vector per row, all loads issued before the
-//                first store, so every warp keeps 4 x 512 B in flight.
-//   k_copy_miss  pinned host memory -> HBM over the host link, same mover over
-//                the miss list. It runs after the hit copy on the same stream:
-//                measured on B200, running the two at once slows the hit copy
-//                by 2-4x (host-link reads back up the memory pipeline) and the
-//                pair finishes later than when run back to back. The side
-//                stream is kept behind the gather_overlap tunable.
+//   k_classify     one thread per requested row: id -> feat_pos_map entry, kept
+//                  in a dense scratch array; rows that live in host memory are
+//                  also appended (warp-aggregated) to a miss list.
+//   k_copy_hits    HBM -> HBM. One warp moves four rows at a time, each lane one
+//                  16-byte vector per row, all loads issued before the first
+//                  store. (A variant that decoded the ids inside the copy kernel,
+//                  32 rows per warp, reached 4.3 TB/s on 1 M rows where this pair
+//                  reaches 6.2 TB/s: the two dependent lookups in front of the
+//                  row loads leave the warp with nothing in flight.)
+//   k_copy_miss    pinned host memory -> HBM over the host link, same mover over
+//                  the miss list. It runs after the hit copy on the same stream:
+//                  measured on B200, running the two at once (second stream, any
+//                  grid size) slows the hit copy by 2-4x and the pair finishes
+//                  later than back to back.
+//   k_copy_miss_bulk  variant of the miss copy that stages rows through shared
+//                  memory with cp.async.bulk (gather_miss_mode = 1); measured
+//                  equal or slower than the vector loads, kept for comparison.
 //
 // Rows are opaque bytes. The vector width V is the widest of 16/8/4/2/1 bytes
 // that divides every row size, column offset and base address involved.
@@ -23,7 +28,7 @@
 
 namespace apt {
 
-constexpr int kRowsPerWarp = 4;
+constexpr int kRowsPerGroup = 4;   // rows whose loads are in flight together
 constexpr int kGatherBlock = 256;
 
 struct GatherWs {
@@ -44,11 +49,27 @@ static size_t gather_layout(int64_t n, char* base, GatherWs* ws) {
   return b0 + b1 + 256;
 }
 
+template <typename V>
+__device__ __forceinline__ V ld_vec(const V* p) { return __ldg(p); }
+template <>
+__device__ __forceinline__ uint4 ld_vec<uint4>(const uint4* p) { return ld_stream_16(p); }
+template <typename V>
+__device__ __forceinline__ void st_vec(V* p, V v) { *p = v; }
+template <>
+__device__ __forceinline__ void st_vec<uint4>(uint4* p, uint4 v) { st_stream_16(p, v); }
+template <typename V>
+__device__ __forceinline__ V zero_vec() { return V(0); }
+template <>
+__device__ __forceinline__ uint4 zero_vec<uint4>() { return make_uint4(0, 0, 0, 0); }
+template <>
+__device__ __forceinline__ uint2 zero_vec<uint2>() { return make_uint2(0, 0); }
+
+// p = feat_pos_map[index[r]]: p >= 0 cache row, p < -1 host row -(p)-2 (queued for
+// the miss copy), p == -1 no such row (zeros + flag).
 __global__ void __launch_bounds__(256)
 k_classify(const int64_t* __restrict__ index, int64_t n, const int64_t* __restrict__ n_dev,
-           const int64_t* __restrict__ pos_map, int64_t num_nodes,
-           int64_t num_dev_rows, int64_t num_uva_rows, GatherWs ws,
-           int32_t* status) {
+           const int64_t* __restrict__ pos_map, int64_t num_nodes, int64_t num_dev_rows,
+           int64_t num_uva_rows, GatherWs ws, int32_t* status) {
   const int lane = threadIdx.x & 31;
   n = effective_n(n, n_dev);
   int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -85,47 +106,30 @@ k_classify(const int64_t* __restrict__ index, int64_t n, const int64_t* __restri
   if (flags) atomicOr(status, flags);
 }
 
-template <typename V>
-__device__ __forceinline__ V ld_vec(const V* p) { return __ldg(p); }
-template <>
-__device__ __forceinline__ uint4 ld_vec<uint4>(const uint4* p) { return ld_stream_16(p); }
-template <typename V>
-__device__ __forceinline__ void st_vec(V* p, V v) { *p = v; }
-template <>
-__device__ __forceinline__ void st_vec<uint4>(uint4* p, uint4 v) { st_stream_16(p, v); }
-template <typename V>
-__device__ __forceinline__ V zero_vec() { return V(0); }
-template <>
-__device__ __forceinline__ uint4 zero_vec<uint4>() { return make_uint4(0, 0, 0, 0); }
-template <>
-__device__ __forceinline__ uint2 zero_vec<uint2>() { return make_uint2(0, 0); }
-
-// Rows r0..r0+3 of the output come from dev row src_pos[r] (>= 0), are zero
-// (src_pos == -1), or belong to the miss kernel (src_pos < -1).
+// Rows r0..r0+3 of the output come from cache row src_pos[r] (>= 0), are zero
+// (src_pos == -1), or belong to the miss copy (src_pos < -1).
 template <typename V>
 __global__ void __launch_bounds__(kGatherBlock)
 k_copy_hits(int64_t n, const int64_t* __restrict__ n_dev, const int64_t* __restrict__ src_pos,
-            const char* __restrict__ dev_feats, int64_t row_bytes,
-            char* __restrict__ out) {
+            const char* __restrict__ dev_feats, int64_t row_bytes, char* __restrict__ out) {
   n = effective_n(n, n_dev);
   const int lane = threadIdx.x & 31;
   const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
   const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int chunks = (int)(row_bytes / (int64_t)sizeof(V));
-  for (int64_t r0 = warp * kRowsPerWarp; r0 < n; r0 += warps * kRowsPerWarp) {
-    int64_t p[kRowsPerWarp];
+  for (int64_t r0 = warp * kRowsPerGroup; r0 < n; r0 += warps * kRowsPerGroup) {
+    int64_t p[kRowsPerGroup];
 #pragma unroll
-    for (int k = 0; k < kRowsPerWarp; ++k)
-      p[k] = r0 + k < n ? src_pos[r0 + k] : (int64_t)-2;
+    for (int k = 0; k < kRowsPerGroup; ++k) p[k] = r0 + k < n ? src_pos[r0 + k] : (int64_t)-2;
     for (int c = lane; c < chunks; c += 32) {
-      V v[kRowsPerWarp];
+      V v[kRowsPerGroup];
 #pragma unroll
-      for (int k = 0; k < kRowsPerWarp; ++k) {
+      for (int k = 0; k < kRowsPerGroup; ++k) {
         v[k] = zero_vec<V>();
         if (p[k] >= 0) v[k] = ld_vec<V>((const V*)(dev_feats + p[k] * row_bytes) + c);
       }
 #pragma unroll
-      for (int k = 0; k < kRowsPerWarp; ++k)
+      for (int k = 0; k < kRowsPerGroup; ++k)
         if (p[k] >= -1) st_vec<V>((V*)(out + (r0 + k) * row_bytes) + c, v[k]);
     }
   }
@@ -133,72 +137,39 @@ k_copy_hits(int64_t n, const int64_t* __restrict__ n_dev, const int64_t* __restr
 
 template <typename V>
 __global__ void __launch_bounds__(kGatherBlock)
-k_copy_miss(const int32_t* __restrict__ miss_count,
-            const int32_t* __restrict__ miss_rows,
-            const int64_t* __restrict__ src_pos,
-            const char* __restrict__ uva_feats, int64_t uva_row_bytes,
+k_copy_miss(GatherWs ws, const char* __restrict__ uva_feats, int64_t uva_row_bytes,
             int64_t col_offset_bytes, int64_t row_bytes, char* __restrict__ out) {
   const int lane = threadIdx.x & 31;
   const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
   const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int64_t n = *miss_count;
+  const int64_t n = *ws.miss_count;
   const int chunks = (int)(row_bytes / (int64_t)sizeof(V));
-  for (int64_t m0 = warp * kRowsPerWarp; m0 < n; m0 += warps * kRowsPerWarp) {
-    int64_t r[kRowsPerWarp], p[kRowsPerWarp];
+  for (int64_t m0 = warp * kRowsPerGroup; m0 < n; m0 += warps * kRowsPerGroup) {
+    int64_t r[kRowsPerGroup], p[kRowsPerGroup];
 #pragma unroll
-    for (int k = 0; k < kRowsPerWarp; ++k) {
-      r[k] = m0 + k < n ? (int64_t)miss_rows[m0 + k] : (int64_t)-1;
-      p[k] = r[k] >= 0 ? -src_pos[r[k]] - 2 : (int64_t)0;
+    for (int k = 0; k < kRowsPerGroup; ++k) {
+      r[k] = m0 + k < n ? (int64_t)ws.miss_rows[m0 + k] : (int64_t)-1;
+      p[k] = r[k] >= 0 ? -ws.src_pos[r[k]] - 2 : (int64_t)0;
     }
     for (int c = lane; c < chunks; c += 32) {
-      V v[kRowsPerWarp];
+      V v[kRowsPerGroup];
 #pragma unroll
-      for (int k = 0; k < kRowsPerWarp; ++k) {
+      for (int k = 0; k < kRowsPerGroup; ++k) {
         v[k] = zero_vec<V>();
         if (r[k] >= 0)
           v[k] = ld_vec<V>((const V*)(uva_feats + p[k] * uva_row_bytes + col_offset_bytes) + c);
       }
 #pragma unroll
-      for (int k = 0; k < kRowsPerWarp; ++k)
+      for (int k = 0; k < kRowsPerGroup; ++k)
         if (r[k] >= 0) st_vec<V>((V*)(out + r[k] * row_bytes) + c, v[k]);
     }
   }
 }
 
 // ---- tunables (set through apt_set_tunable; defaults are the measured best) ----
-static int g_miss_mode = 0;      // 0: ld.global.nc 16 B, 1: plain ld.global 16 B, 2: bulk copy through shared memory
+static int g_miss_mode = 0;      // 0: 16-byte ld.global.nc, 1: bulk copy staged through shared memory
 static int g_miss_blocks = kNumSMs;
 static int g_hit_waves = 4;      // cap on waves of 148 x 8 blocks of the hit copy
-static int g_overlap = 0;        // 1: miss copy on the side stream, under the hit copy
-
-// Plain-load variant of the miss mover (16-byte vectors only).
-__global__ void __launch_bounds__(kGatherBlock)
-k_copy_miss_plain(const int32_t* __restrict__ miss_count, const int32_t* __restrict__ miss_rows,
-                  const int64_t* __restrict__ src_pos, const char* uva_feats, int64_t uva_row_bytes,
-                  int64_t col_offset_bytes, int64_t row_bytes, char* __restrict__ out) {
-  const int lane = threadIdx.x & 31;
-  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
-  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int64_t n = *miss_count;
-  const int chunks = (int)(row_bytes / 16);
-  for (int64_t m0 = warp * kRowsPerWarp; m0 < n; m0 += warps * kRowsPerWarp) {
-    int64_t r[kRowsPerWarp], p[kRowsPerWarp];
-#pragma unroll
-    for (int k = 0; k < kRowsPerWarp; ++k) {
-      r[k] = m0 + k < n ? (int64_t)miss_rows[m0 + k] : (int64_t)-1;
-      p[k] = r[k] >= 0 ? -src_pos[r[k]] - 2 : (int64_t)0;
-    }
-    for (int c = lane; c < chunks; c += 32) {
-      uint4 v[kRowsPerWarp];
-#pragma unroll
-      for (int k = 0; k < kRowsPerWarp; ++k)
-        if (r[k] >= 0) v[k] = ld_plain_16((const uint4*)(uva_feats + p[k] * uva_row_bytes + col_offset_bytes) + c);
-#pragma unroll
-      for (int k = 0; k < kRowsPerWarp; ++k)
-        if (r[k] >= 0) st_stream_16((uint4*)(out + r[k] * row_bytes) + c, v[k]);
-    }
-  }
-}
 
 // Bulk-copy variant: one lane per warp asks the copy engine of the SM for the
 // whole row (cp.async.bulk global -> shared, completion on an mbarrier), then
@@ -212,15 +183,14 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 }
 
 __global__ void __launch_bounds__(kGatherBlock)
-k_copy_miss_bulk(const int32_t* __restrict__ miss_count, const int32_t* __restrict__ miss_rows,
-                 const int64_t* __restrict__ src_pos, const char* uva_feats, int64_t uva_row_bytes,
-                 int64_t col_offset_bytes, int64_t row_bytes, char* __restrict__ out, int32_t* status) {
+k_copy_miss_bulk(GatherWs ws, const char* uva_feats, int64_t uva_row_bytes, int64_t col_offset_bytes,
+                 int64_t row_bytes, char* __restrict__ out, int32_t* status) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t bars[(kGatherBlock / 32) * kBulkStages];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
   const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + wib;
-  const int64_t n = *miss_count;
+  const int64_t n = *ws.miss_count;
   unsigned char* wbuf = smem + (size_t)wib * kBulkStages * row_bytes;
   uint64_t* wbar = bars + wib * kBulkStages;
   if (lane == 0) {
@@ -234,9 +204,7 @@ k_copy_miss_bulk(const int32_t* __restrict__ miss_count, const int32_t* __restri
     if (lane == 0) {
       for (int k = 0; k < kBulkStages; ++k) {
         if (m0 + k >= n) break;
-        const int64_t r = miss_rows[m0 + k];
-        const int64_t p = -src_pos[r] - 2;
-        const char* src = uva_feats + p * uva_row_bytes + col_offset_bytes;
+        const char* src = uva_feats + (-ws.src_pos[ws.miss_rows[m0 + k]] - 2) * uva_row_bytes + col_offset_bytes;
         const uint32_t bar = smem_u32(wbar + k), dst = smem_u32(wbuf + (size_t)k * row_bytes);
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)row_bytes)
                      : "memory");
@@ -263,7 +231,7 @@ k_copy_miss_bulk(const int32_t* __restrict__ miss_count, const int32_t* __restri
           failed = true;
           continue;
         }
-        const int64_t r = miss_rows[m0 + k];
+        const int64_t r = ws.miss_rows[m0 + k];
         asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(out + r * row_bytes),
                      "r"(smem_u32(wbuf + (size_t)k * row_bytes)), "r"((uint32_t)row_bytes)
                      : "memory");
@@ -277,15 +245,98 @@ k_copy_miss_bulk(const int32_t* __restrict__ miss_count, const int32_t* __restri
   }
 }
 
-// Two events per device, reused by every call, order the side stream between
-// the classify kernel and the end of the call.
-static cudaEvent_t g_ev[64][2];
-static bool g_ev_ready[64];
-
 static int vec_width(uint64_t bits) {
   for (int w = 16; w > 1; w >>= 1)
     if ((bits & (uint64_t)(w - 1)) == 0) return w;
   return 1;
+}
+
+struct GatherArgs {
+  const int64_t* index;
+  int64_t num_rows;
+  const int64_t* num_rows_dev;
+  const int64_t* feat_pos_map;
+  int64_t num_nodes;
+  const char* dev_feats;
+  int64_t num_dev_rows, dev_row_bytes;
+  const char* uva_feats;
+  int64_t num_uva_rows, uva_row_bytes, uva_col_offset_bytes;
+  char* out;
+  int32_t* status_word;
+};
+
+// The three launches shared by the workspace-taking and the allocation-free entry points.
+static int gather_launch(const GatherArgs& a, GatherWs ws, cudaStream_t s) {
+  uint64_t bits = (uint64_t)a.dev_row_bytes | (uintptr_t)a.out;
+  if (a.num_dev_rows > 0) bits |= (uintptr_t)a.dev_feats;
+  const int vw_hit = vec_width(bits);
+  if (a.num_uva_rows > 0)
+    bits |= (uint64_t)a.uva_row_bytes | (uint64_t)a.uva_col_offset_bytes | (uintptr_t)a.uva_feats;
+  const int vw_miss = vec_width(bits);
+  // the miss counter is the one word that has to start at zero
+  APT_CUDA(cudaMemsetAsync(ws.miss_count, 0, sizeof(int32_t), s));
+
+  {
+    ProfScope prof("gather_classify", s);
+    const int grid = wave_grid(ceil_div(a.num_rows, 256), 8);
+    APT_LAUNCH(k_classify, grid, 256, 0, s, a.index, a.num_rows, a.num_rows_dev, a.feat_pos_map,
+               a.num_nodes, a.num_dev_rows, a.num_uva_rows, ws, a.status_word);
+  }
+#define APT_HITS(V)                                                                        \
+  do {                                                                                     \
+    ProfScope prof("gather_hit", s);                                                       \
+    const int grid =                                                                       \
+        wave_grid(ceil_div(a.num_rows, (kGatherBlock / 32) * kRowsPerGroup), 8, g_hit_waves); \
+    APT_LAUNCH(k_copy_hits<V>, grid, kGatherBlock, 0, s, a.num_rows, a.num_rows_dev,       \
+               ws.src_pos, a.dev_feats, a.dev_row_bytes, a.out);                           \
+  } while (0)
+#define APT_MISS(V)                                                                        \
+  do {                                                                                     \
+    ProfScope prof("gather_miss", s);                                                      \
+    APT_LAUNCH(k_copy_miss<V>, g_miss_blocks, kGatherBlock, 0, s, ws, a.uva_feats,         \
+               a.uva_row_bytes, a.uva_col_offset_bytes, a.dev_row_bytes, a.out);           \
+  } while (0)
+#define APT_BY_WIDTH(W, MACRO)                                                             \
+  do {                                                                                     \
+    switch (W) {                                                                           \
+      case 16: MACRO(uint4); break;                                                        \
+      case 8: MACRO(uint2); break;                                                         \
+      case 4: MACRO(uint32_t); break;                                                      \
+      case 2: MACRO(uint16_t); break;                                                      \
+      default: MACRO(uint8_t); break;                                                      \
+    }                                                                                      \
+  } while (0)
+  APT_BY_WIDTH(vw_hit, APT_HITS);
+  if (a.num_uva_rows > 0) {
+    const size_t smem = (size_t)a.dev_row_bytes * kBulkStages * (kGatherBlock / 32);
+    if (vw_miss == 16 && g_miss_mode == 1 && smem <= 200 * 1024) {
+      APT_CUDA(cudaFuncSetAttribute(k_copy_miss_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      ProfScope prof("gather_miss", s);
+      APT_LAUNCH(k_copy_miss_bulk, g_miss_blocks, kGatherBlock, smem, s, ws, a.uva_feats, a.uva_row_bytes,
+                 a.uva_col_offset_bytes, a.dev_row_bytes, a.out, a.status_word);
+    } else {
+      APT_BY_WIDTH(vw_miss, APT_MISS);
+    }
+  }
+#undef APT_HITS
+#undef APT_MISS
+#undef APT_BY_WIDTH
+  return APT_OK;
+}
+
+static int gather_check(const char* who, const GatherArgs& a) {
+  APT_CHECK_ARG(a.num_rows >= 0 && a.num_rows < (int64_t)0x7fffffff, "%s: bad num_rows", who);
+  APT_CHECK_ARG(a.dev_row_bytes > 0 && a.num_dev_rows >= 0 && a.num_uva_rows >= 0 && a.num_nodes >= 0,
+                "%s: bad table sizes", who);
+  APT_CHECK_ARG(a.num_uva_rows == 0 || (a.uva_col_offset_bytes >= 0 &&
+                                         a.uva_col_offset_bytes + a.dev_row_bytes <= a.uva_row_bytes),
+                "%s: column window [%lld,+%lld) outside a %lld-byte host row", who,
+                (long long)a.uva_col_offset_bytes, (long long)a.dev_row_bytes, (long long)a.uva_row_bytes);
+  if (a.num_rows == 0) return APT_OK;
+  APT_CHECK_ARG(a.index && a.feat_pos_map && a.out && a.status_word, "%s: null pointer", who);
+  APT_CHECK_ARG((a.num_dev_rows == 0 || a.dev_feats) && (a.num_uva_rows == 0 || a.uva_feats),
+                "%s: null feature table", who);
+  return APT_OK;
 }
 
 }  // namespace apt
@@ -293,14 +344,12 @@ static int vec_width(uint64_t bits) {
 extern "C" int apt_set_tunable(const char* name, int64_t value) {
   using namespace apt;
   APT_CHECK_ARG(name, "apt_set_tunable: null name");
-  if (!strcmp(name, "gather_miss_mode") && value >= 0 && value <= 2) {
+  if (!strcmp(name, "gather_miss_mode") && value >= 0 && value <= 1) {
     g_miss_mode = (int)value;
   } else if (!strcmp(name, "gather_miss_blocks") && value >= 1 && value <= 65535) {
     g_miss_blocks = (int)value;
   } else if (!strcmp(name, "gather_hit_waves") && value >= 1 && value <= 64) {
     g_hit_waves = (int)value;
-  } else if (!strcmp(name, "gather_overlap") && (value == 0 || value == 1)) {
-    g_overlap = (int)value;
   } else {
     set_error("apt_set_tunable: unknown name or bad value: %s = %lld", name, (long long)value);
     return APT_ERR_BAD_ARG;
@@ -314,129 +363,38 @@ extern "C" size_t apt_gather_workspace_bytes(int64_t num_rows) {
 }
 
 extern "C" int apt_gather_rows(const int64_t* index, int64_t num_rows,
-                               const int64_t* num_rows_dev, const int64_t* feat_pos_map, int64_t num_nodes,
-                               const void* dev_feats, int64_t num_dev_rows,
+                               const int64_t* num_rows_dev, const int64_t* feat_pos_map,
+                               int64_t num_nodes, const void* dev_feats, int64_t num_dev_rows,
                                int64_t dev_row_bytes, const void* uva_feats,
                                int64_t num_uva_rows, int64_t uva_row_bytes,
-                               int64_t uva_col_offset_bytes, void* out,
-                               void* workspace, size_t workspace_bytes,
-                               int32_t* status_word, void* stream,
-                               void* side_stream) {
+                               int64_t uva_col_offset_bytes, void* out, void* workspace,
+                               size_t workspace_bytes, int32_t* status_word, void* stream) {
   using namespace apt;
-  APT_CHECK_ARG(num_rows >= 0 && num_rows < (int64_t)0x7fffffff, "apt_gather_rows: bad num_rows");
-  APT_CHECK_ARG(dev_row_bytes > 0 && num_dev_rows >= 0 && num_uva_rows >= 0 && num_nodes >= 0,
-                "apt_gather_rows: bad table sizes");
-  APT_CHECK_ARG(num_uva_rows == 0 ||
-                    (uva_col_offset_bytes >= 0 && uva_col_offset_bytes + dev_row_bytes <= uva_row_bytes),
-                "apt_gather_rows: column window [%lld,+%lld) outside a %lld-byte host row",
-                (long long)uva_col_offset_bytes, (long long)dev_row_bytes, (long long)uva_row_bytes);
-  if (num_rows == 0) return APT_OK;
-  APT_CHECK_ARG(index && feat_pos_map && out && workspace && status_word, "apt_gather_rows: null pointer");
-  APT_CHECK_ARG((num_dev_rows == 0 || dev_feats) && (num_uva_rows == 0 || uva_feats),
-                "apt_gather_rows: null feature table");
-  APT_CHECK_ARG(((uintptr_t)workspace & 255) == 0, "apt_gather_rows: workspace must be 256-byte aligned");
+  const GatherArgs a{index, num_rows, num_rows_dev, feat_pos_map, num_nodes, (const char*)dev_feats,
+                     num_dev_rows, dev_row_bytes, (const char*)uva_feats, num_uva_rows, uva_row_bytes,
+                     uva_col_offset_bytes, (char*)out, status_word};
+  const int rc = gather_check("apt_gather_rows", a);
+  if (rc != APT_OK || num_rows == 0) return rc;
+  APT_CHECK_ARG(workspace && ((uintptr_t)workspace & 255) == 0,
+                "apt_gather_rows: workspace must be non-null and 256-byte aligned");
   GatherWs ws;
   const size_t need = gather_layout(num_rows, (char*)workspace, &ws);
   if (workspace_bytes < need) {
     set_error("apt_gather_rows: workspace %zu < %zu bytes", workspace_bytes, need);
     return APT_ERR_CAPACITY;
   }
-  cudaStream_t s = (cudaStream_t)stream;
-  cudaStream_t side = (cudaStream_t)side_stream;
-  const bool overlap = g_overlap && side != nullptr && side != s && num_uva_rows > 0;
-
-  uint64_t bits = (uint64_t)dev_row_bytes | (uintptr_t)out;
-  if (num_dev_rows > 0) bits |= (uintptr_t)dev_feats;
-  const int vw_hit = vec_width(bits);
-  if (num_uva_rows > 0)
-    bits |= (uint64_t)uva_row_bytes | (uint64_t)uva_col_offset_bytes | (uintptr_t)uva_feats;
-  const int vw_miss = vec_width(bits);
-
-  APT_CUDA(cudaMemsetAsync(ws.miss_count, 0, sizeof(int32_t), s));
-  {
-    ProfScope prof("gather_classify", s);
-    const int grid = wave_grid(ceil_div(num_rows, 256), 8);
-    APT_LAUNCH(k_classify, grid, 256, 0, s, index, num_rows, num_rows_dev, feat_pos_map, num_nodes,
-               num_dev_rows, num_uva_rows, ws, status_word);
-  }
-  int dev = 0;
-  if (overlap) {
-    APT_CUDA(cudaGetDevice(&dev));
-    APT_CHECK_ARG(dev >= 0 && dev < 64, "apt_gather_rows: device ordinal %d", dev);
-    if (!g_ev_ready[dev]) {
-      APT_CUDA(cudaEventCreateWithFlags(&g_ev[dev][0], cudaEventDisableTiming));
-      APT_CUDA(cudaEventCreateWithFlags(&g_ev[dev][1], cudaEventDisableTiming));
-      g_ev_ready[dev] = true;
-    }
-    APT_CUDA(cudaEventRecord(g_ev[dev][0], s));
-    APT_CUDA(cudaStreamWaitEvent(side, g_ev[dev][0], 0));
-  }
-  const char* devp = (const char*)dev_feats;
-  const char* uvap = (const char*)uva_feats;
-  char* outp = (char*)out;
-
-#define APT_MISS(V)                                                             \
-  do {                                                                          \
-    ProfScope prof("gather_miss", ms);                                          \
-    APT_LAUNCH(k_copy_miss<V>, g_miss_blocks, kGatherBlock, 0, ms, ws.miss_count, \
-               ws.miss_rows, ws.src_pos, uvap, uva_row_bytes,                   \
-               uva_col_offset_bytes, dev_row_bytes, outp);                      \
-  } while (0)
-#define APT_HITS(V)                                                             \
-  do {                                                                          \
-    ProfScope prof("gather_hit", s);                                            \
-    const int grid = wave_grid(ceil_div(num_rows, (kGatherBlock / 32) * kRowsPerWarp), 8, g_hit_waves); \
-    APT_LAUNCH(k_copy_hits<V>, grid, kGatherBlock, 0, s, num_rows, num_rows_dev, \
-               ws.src_pos, devp, dev_row_bytes, outp);                          \
-  } while (0)
-#define APT_BY_WIDTH(W, MACRO)                                                  \
-  do {                                                                          \
-    switch (W) {                                                                \
-      case 16: MACRO(uint4); break;                                             \
-      case 8: MACRO(uint2); break;                                              \
-      case 4: MACRO(uint32_t); break;                                           \
-      case 2: MACRO(uint16_t); break;                                           \
-      default: MACRO(uint8_t); break;                                           \
-    }                                                                           \
-  } while (0)
-
-  if (num_uva_rows > 0) {
-    cudaStream_t ms = overlap ? side : s;
-    if (vw_miss == 16 && g_miss_mode == 1) {
-      ProfScope prof("gather_miss", ms);
-      APT_LAUNCH(k_copy_miss_plain, g_miss_blocks, kGatherBlock, 0, ms, ws.miss_count, ws.miss_rows,
-                 ws.src_pos, uvap, uva_row_bytes, uva_col_offset_bytes, dev_row_bytes, outp);
-    } else if (vw_miss == 16 && g_miss_mode == 2 &&
-               (size_t)dev_row_bytes * kBulkStages * (kGatherBlock / 32) <= 200 * 1024) {
-      const size_t smem = (size_t)dev_row_bytes * kBulkStages * (kGatherBlock / 32);
-      APT_CUDA(cudaFuncSetAttribute(k_copy_miss_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      ProfScope prof("gather_miss", ms);
-      APT_LAUNCH(k_copy_miss_bulk, g_miss_blocks, kGatherBlock, smem, ms, ws.miss_count, ws.miss_rows,
-                 ws.src_pos, uvap, uva_row_bytes, uva_col_offset_bytes, dev_row_bytes, outp, status_word);
-    } else {
-      APT_BY_WIDTH(vw_miss, APT_MISS);
-    }
-  }
-  APT_BY_WIDTH(vw_hit, APT_HITS);
-  if (overlap) {
-    APT_CUDA(cudaEventRecord(g_ev[dev][1], side));
-    APT_CUDA(cudaStreamWaitEvent(s, g_ev[dev][1], 0));
-  }
-#undef APT_MISS
-#undef APT_HITS
-#undef APT_BY_WIDTH
-  return APT_OK;
+  return gather_launch(a, ws, (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------
 // Gather without any allocation, for callers that must not allocate.
 //
 // The scratch that apt_gather_rows takes from its caller (decoded positions,
-// miss list, miss counter) lives here in a fixed array inside the library's
-// device image, sized for kStaticGatherMaxRows rows per call. The name
-// g_gather_scratch is a host-side stand-in in host code, not a device address;
-// the address kernels can use is asked for once per device with
-// cudaGetSymbolAddress while that device is current.
+// miss list and miss counter) lives here in a fixed array inside the library's device image,
+// sized for kStaticGatherMaxRows rows per call. The name g_gather_scratch is a
+// host-side stand-in in host code, not a device address; the address kernels can
+// use is asked for once per device with cudaGetSymbolAddress while that device
+// is current.
 namespace apt {
 
 constexpr int64_t kStaticGatherMaxRows = 1 << 20;
@@ -483,64 +441,17 @@ extern "C" int apt_gather_rows_static(const int64_t* index, int64_t num_rows,
               (long long)num_rows, (long long)kStaticGatherMaxRows);
     return APT_ERR_CAPACITY;
   }
-  APT_CHECK_ARG(dev_row_bytes > 0 && num_dev_rows >= 0 && num_uva_rows >= 0 && num_nodes >= 0,
-                "apt_gather_rows_static: bad table sizes");
-  APT_CHECK_ARG(num_uva_rows == 0 ||
-                    (uva_col_offset_bytes >= 0 && uva_col_offset_bytes + dev_row_bytes <= uva_row_bytes),
-                "apt_gather_rows_static: column window outside the host row");
-  if (num_rows == 0) return APT_OK;
-  APT_CHECK_ARG(index && feat_pos_map && out && status_word, "apt_gather_rows_static: null pointer");
-  APT_CHECK_ARG((num_dev_rows == 0 || dev_feats) && (num_uva_rows == 0 || uva_feats),
-                "apt_gather_rows_static: null feature table");
+  const GatherArgs a{index, num_rows, nullptr, feat_pos_map, num_nodes, (const char*)dev_feats,
+                     num_dev_rows, dev_row_bytes, (const char*)uva_feats, num_uva_rows, uva_row_bytes,
+                     uva_col_offset_bytes, (char*)out, status_word};
+  int rc = gather_check("apt_gather_rows_static", a);
+  if (rc != APT_OK || num_rows == 0) return rc;
   void* base = nullptr;
-  const int rc = static_scratch(&base);
+  rc = static_scratch(&base);
   if (rc != APT_OK) return rc;
   GatherWs ws;
   gather_layout(kStaticGatherMaxRows, (char*)base, &ws);
-  cudaStream_t s = (cudaStream_t)stream;
-
-  uint64_t bits = (uint64_t)dev_row_bytes | (uintptr_t)out;
-  if (num_dev_rows > 0) bits |= (uintptr_t)dev_feats;
-  const int vw_hit = vec_width(bits);
-  if (num_uva_rows > 0)
-    bits |= (uint64_t)uva_row_bytes | (uint64_t)uva_col_offset_bytes | (uintptr_t)uva_feats;
-  const int vw_miss = vec_width(bits);
-
-  // The array keeps the previous call's contents: the miss counter must start at
-  // zero; positions and the miss list are rewritten for every row that is read.
-  APT_CUDA(cudaMemsetAsync(ws.miss_count, 0, sizeof(int32_t), s));
-  {
-    const int grid = wave_grid(ceil_div(num_rows, 256), 8);
-    APT_LAUNCH(k_classify, grid, 256, 0, s, index, num_rows, (const int64_t*)nullptr, feat_pos_map,
-               num_nodes, num_dev_rows, num_uva_rows, ws, status_word);
-  }
-  const char* devp = (const char*)dev_feats;
-  const char* uvap = (const char*)uva_feats;
-  char* outp = (char*)out;
-#define APT_SMISS(V)                                                            \
-  APT_LAUNCH(k_copy_miss<V>, kNumSMs, kGatherBlock, 0, s, ws.miss_count,        \
-             ws.miss_rows, ws.src_pos, uvap, uva_row_bytes, uva_col_offset_bytes, \
-             dev_row_bytes, outp)
-#define APT_SHITS(V)                                                            \
-  do {                                                                          \
-    const int grid = wave_grid(ceil_div(num_rows, (kGatherBlock / 32) * kRowsPerWarp), 8, 4); \
-    APT_LAUNCH(k_copy_hits<V>, grid, kGatherBlock, 0, s, num_rows,              \
-               (const int64_t*)nullptr, ws.src_pos, devp, dev_row_bytes, outp); \
-  } while (0)
-#define APT_SBY_WIDTH(W, MACRO)                                                 \
-  do {                                                                          \
-    switch (W) {                                                                \
-      case 16: MACRO(uint4); break;                                             \
-      case 8: MACRO(uint2); break;                                              \
-      case 4: MACRO(uint32_t); break;                                           \
-      case 2: MACRO(uint16_t); break;                                           \
-      default: MACRO(uint8_t); break;                                           \
-    }                                                                           \
-  } while (0)
-  if (num_uva_rows > 0) APT_SBY_WIDTH(vw_miss, APT_SMISS);
-  APT_SBY_WIDTH(vw_hit, APT_SHITS);
-#undef APT_SMISS
-#undef APT_SHITS
-#undef APT_SBY_WIDTH
-  return APT_OK;
+  // The array keeps the previous call's contents: gather_launch zeroes the miss
+  // counter; positions and the miss list are rewritten for every row that is read.
+  return gather_launch(a, ws, (cudaStream_t)stream);
 }

@@ -138,6 +138,9 @@ __global__ void __launch_bounds__(kRelabelBlock)
 k_count(int64_t S_host, int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed,
         RelabelWs ws) {
   const RelabelDims d = relabel_dims(S_host, M_host, S_dev, per_seed);
+  // tiles past the real item count (the grid covers the upper bound) have nothing to count,
+  // and no tile before them ever reads their count
+  if ((int64_t)blockIdx.x * blockDim.x >= d.n) return;
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int f = is_first(ws, i, d.n);
   const int c = __syncthreads_count(f);
@@ -150,8 +153,14 @@ k_assign(const int64_t* __restrict__ seeds, int64_t S_host, const int64_t* __res
          int64_t* __restrict__ out_unique, int64_t* __restrict__ out_num_unique) {
   __shared__ int scratch[33];
   const RelabelDims d = relabel_dims(S_host, M_host, S_dev, per_seed);
+  const int64_t tile_first = (int64_t)blockIdx.x * blockDim.x;
+  if (tile_first >= d.n) {
+    // past the real item count; with no item at all the first tile reports zero unique ids
+    if (d.n == 0 && blockIdx.x == 0 && threadIdx.x == 0) *out_num_unique = 0;
+    return;
+  }
   const int before = block_sum_of(ws.tile_count, blockIdx.x, scratch);
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t i = tile_first + threadIdx.x;
   const int f = is_first(ws, i, d.n);
   int total;
   const int ex = block_exclusive_scan(f, scratch, &total);
@@ -160,7 +169,8 @@ k_assign(const int64_t* __restrict__ seeds, int64_t S_host, const int64_t* __res
     out_unique[id] = item_at(seeds, d.S, nbrs, i);
     ws.slots[ws.slot_of[i]].new_id = (uint32_t)id;
   }
-  if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) *out_num_unique = before + total;
+  // the tile that holds the last real item knows the number of unique ids
+  if (tile_first + blockDim.x >= d.n && threadIdx.x == 0) *out_num_unique = before + total;
 }
 
 __global__ void __launch_bounds__(256)

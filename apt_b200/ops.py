@@ -19,7 +19,6 @@ from . import _lib
 from ._lib import check, lib
 
 _DTYPE_CODE = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _lib.F16}
-_USE_SIDE_STREAM = os.environ.get("APT_GATHER_SIDE_STREAM", "0") == "1"
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -113,7 +112,6 @@ class NPCState:
         self._ws = {}
         self._words = None
         self._host_words = None
-        self._side_stream = None
         self.prefetched = None  # (input ids, gathered rows) left by a sampler that gathers ahead
         self.generation = 0     # bumped whenever installed state changes; captured graphs check it
         self.profiling = False
@@ -162,11 +160,6 @@ class NPCState:
             w[self.NUM_WORDS - 1] = 0
             raise RuntimeError(f"apt_b200 device status flags 0x{flags:x}: " + _flag_text(flags))
         return self._host_words
-
-    def side_stream(self):
-        if self._side_stream is None:
-            self._side_stream = torch.cuda.Stream()
-        return self._side_stream
 
 
 def _flag_text(flags):
@@ -471,18 +464,11 @@ def _gather_enqueue(node_id: torch.Tensor, n_dev: Optional[torch.Tensor]) -> tor
     out = torch.empty((n, f.rank_feat_dim), dtype=f.dev_feats.dtype, device=node_id.device)
     nbytes = lib.apt_gather_workspace_bytes(n)
     ws = STATE.workspace("gather", nbytes)
-    # the miss copy runs after the hit copy on the same stream unless a side stream is asked for
-    side = STATE.side_stream() if f.uva_feats.shape[0] > 0 and _USE_SIDE_STREAM else None
     check(lib.apt_gather_rows(
         _ptr(node_id), n, _ptr(n_dev), _ptr(f.feat_pos_map), f.num_total_nodes,
         _ptr(f.dev_feats), f.dev_feats.shape[0], f.rank_feat_dim * esz,
         _ptr(f.uva_feats), f.uva_feats.shape[0], f.feat_dim * esz, f.feat_dim_offset * esz,
-        _ptr(out), _ptr(ws), ws.numel(), STATE.status_ptr(), _stream(),
-        ctypes.c_void_p(side.cuda_stream) if side is not None else None))
-    if side is not None:
-        # the workspace and output are also in use on the side stream
-        ws.record_stream(side)
-        out.record_stream(side)
+        _ptr(out), _ptr(ws), ws.numel(), STATE.status_ptr(), _stream()))
     return out
 
 

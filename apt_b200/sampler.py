@@ -57,7 +57,7 @@ def create_block(seeds: torch.Tensor, neighbors: torch.Tensor, fanout: int) -> B
 
 # Upper-bound buffers beyond this many bytes of gathered rows are not gathered
 # ahead of the size read; the gather then runs right after it with exact sizes.
-_PREFETCH_LIMIT_BYTES = 3 << 30
+_PREFETCH_LIMIT_BYTES = 6 << 30
 
 
 class _Plan:

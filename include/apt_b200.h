@@ -71,12 +71,10 @@ int apt_profile_enable(int on);
 int apt_profile_read(const char* tag, double* total_ms, int64_t* launches);
 
 /* Tuning knobs for measurements; the defaults are what the benchmark uses.
- *   gather_miss_mode   0 16-byte ld.global.nc, 1 plain 16-byte loads,
- *                      2 bulk copies (cp.async.bulk) staged through shared memory
+ *   gather_miss_mode   0 16-byte ld.global.nc loads (default),
+ *                      1 bulk copies (cp.async.bulk) staged through shared memory
  *   gather_miss_blocks blocks of the miss-copy kernel (default 148)
- *   gather_hit_waves   cap on the hit-copy grid, in waves of 148 x 8 blocks (default 4)
- *   gather_overlap     1: miss copy on the side stream under the hit copy,
- *                      0 (default): after it on the main stream */
+ *   gather_hit_waves   cap on the hit-copy grid, in waves of 148 x 8 blocks (default 4) */
 int apt_set_tunable(const char* name, int64_t value);
 
 /* ------------------------------------------------------------------ sampling
@@ -193,11 +191,9 @@ int apt_unique_sorted(const int64_t* ids, int64_t num_ids,
  *   p == -1: out[r] = 0 and APT_FLAG_FEAT_NOT_EXIST (the reference reads out
  *            of bounds here)
  * Rows are opaque bytes, so fp32/bf16/fp16 tables share the code.
- * Three kernels on `stream`: classify (decode p, compact the miss list), miss
- * copy, hit copy. With the gather_overlap tunable set and a non-NULL
- * `side_stream` the miss copy runs there instead, ordered by events. The
- * output is complete in `stream` order on return.
- * workspace: apt_gather_workspace_bytes(num_rows) bytes.
+ * Three kernels on `stream`: classify (decode p, compact the miss list), the
+ * hit copy out of the HBM cache and the miss copy over the host link.
+ * workspace: apt_gather_workspace_bytes(num_rows) bytes; needs no initialisation.
  */
 size_t apt_gather_workspace_bytes(int64_t num_rows);
 int apt_gather_rows(const int64_t* index, int64_t num_rows,
@@ -207,8 +203,7 @@ int apt_gather_rows(const int64_t* index, int64_t num_rows,
                     int64_t dev_row_bytes, const void* uva_feats,
                     int64_t num_uva_rows, int64_t uva_row_bytes,
                     int64_t uva_col_offset_bytes, void* out, void* workspace,
-                    size_t workspace_bytes, int32_t* status_word, void* stream,
-                    void* side_stream);
+                    size_t workspace_bytes, int32_t* status_word, void* stream);
 
 /* Gather for callers that cannot allocate device memory. No counterpart in the
  * reference, whose gather allocates its output and keeps no scratch.
@@ -223,10 +218,9 @@ int apt_gather_rows(const int64_t* index, int64_t num_rows,
  * library's device image instead (about 12.6 MB, held by every GPU that loads
  * the library until the process exits).
  *
- * Same arguments and result as apt_gather_rows, with these differences:
+ * Same arguments (minus the workspace) and result as apt_gather_rows, with these differences:
  *  - at most apt_gather_static_max_rows() (1 048 576) rows per call; more
  *    returns APT_ERR_CAPACITY with a message and launches nothing;
- *  - all three kernels run on `stream` (no side stream, no events);
  *  - it calls no cudaMalloc, cudaFree or other allocating routine. The first
  *    call on each device looks up the array's device address
  *    (cudaGetSymbolAddress) with that device current; make that first call

@@ -122,5 +122,5 @@ def test_gather_direct_abi_call_capacity_error():
     ws = torch.empty(64, dtype=torch.uint8, device="cuda")
     st = _lib.lib.apt_gather_rows(ids.data_ptr(), 50, None, f.feat_pos_map.data_ptr(), 100, f.dev_feats.data_ptr(),
                                   f.dev_feats.shape[0], 32, f.uva_feats.data_ptr(), 100, 32, 0, out.data_ptr(),
-                                  ws.data_ptr(), 64, ops.STATE.status_ptr(), None, None)
+                                  ws.data_ptr(), 64, ops.STATE.status_ptr(), None)
     assert st == _lib.APT_ERR_CAPACITY

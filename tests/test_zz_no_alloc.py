@@ -37,7 +37,7 @@ def _with_workspace(ids, pos, dev_t, uva_t, status):
     ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
     check(lib.apt_gather_rows(ids.data_ptr(), n, None, pos.data_ptr(), pos.numel(), dev_t.data_ptr(), dev_t.shape[0], rb,
                               uva_t.data_ptr(), uva_t.shape[0], rb, 0, out.data_ptr(), ws.data_ptr(), nbytes,
-                              status.data_ptr(), None, None))
+                              status.data_ptr(), None))
     return out
 
 
