@@ -154,6 +154,44 @@ def main():
                 assert np.array_equal(all_gb[r], want[r]), f"rank {r}: feat_shuffle bwd differs from the oracle"
     ops.check_status()
 
+    # --- the small NP configuration of the benchmark list (2^20 nodes, 16 M R-MAT edges, fanout [25, 10],
+    # 1024 seeds per rank): graph built on every GPU, whole mini-batch against the oracle replaying all ranks
+    from apt_b200 import synthetic
+    w0 = synthetic.WORKLOADS["c0_small_np"]
+    ip0, ix0 = synthetic.build_csc(w0)
+    e0_ = torch.empty(0, dtype=torch.int64)
+    ops.mix_cache_graphs(0, e0_, e0_, e0_, ip0, ix0)
+    mv0 = synthetic.partition_min_vids(w0.num_nodes, world)
+    ops.register_min_vids(mv0)
+    gsd = torch.Generator(device="cuda").manual_seed(1000 + rank)
+    batch0 = torch.randperm(w0.num_nodes, generator=gsd, device="cuda")[:w0.batch]
+    ops.set_sampling(key=2026, call_id=0)
+    smp0 = apt_b200.MixedNeighborSampler(rank, w0.fanouts, prefetch_features=False)
+    out0 = smp0.sample(None, batch0)
+    all_b0 = gather_objects(host(batch0))
+    all_o0 = gather_objects((host(out0[0]), host(out0[2][0].coo_row), host(out0[2][1].coo_row), host(out0[3]),
+                             out0[4].numpy(), out0[5].numpy(), host(out0[6])))
+    if rank == 0:
+        cip, cix = host(ip0), host(ix0)
+        g0 = (None, None, None, cip, cix)
+        frontier, inner = [], []
+        for r in range(world):
+            nb = orc.sample_csc_fanout(all_b0[r], w0.fanouts[1], *g0, key=2026, call_id=0)
+            u, rel = orc.relabel_csc(all_b0[r], nb)
+            frontier.append(u)
+            inner.append(rel)
+        outer = orc.np_sample_and_shuffle(frontier, w0.fanouts[0], mv0.numpy(), g0, key=2026, call_id=1)
+        for r in range(world):
+            uq, nb, pm, so, ro, inv = outer[r]
+            u3, rel3 = orc.relabel_csc(uq, nb)
+            want0 = (u3, rel3, inner[r], pm, so, ro, inv)
+            for name, a_, b_ in zip(("input_nodes", "outer coo_row", "inner coo_row", "perm", "send_offset",
+                                     "recv_offset", "inverse_idx"), all_o0[r], want0):
+                assert np.array_equal(a_, b_), f"rank {r}: small NP configuration: {name} differs from the oracle"
+    # put the small test graph back for the timing below
+    ops.mix_cache_graphs(0, e, e, e, torch.from_numpy(indptr).cuda(), torch.from_numpy(indices).cuda())
+    ops.register_min_vids(torch.from_numpy(mv))
+
     # --- timing of a large forward shuffle (2 KiB fp16 rows), both backends
     rows, D = 200_000, 1024
     ids = torch.randint(0, n, (rows,), device="cuda")
