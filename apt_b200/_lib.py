@@ -62,6 +62,7 @@ PROTOTYPES = {
     "apt_p2p_push": (c_int, [P, P, P, c_int, P, c_int64, c_int64, P, P]),
     "apt_p2p_wait": (c_int, [P, P, P, c_int64, P]),
     "apt_p2p_pull": (c_int, [P, P, P, c_int, c_int64, c_int64, c_int64, P, P]),
+    "apt_p2p_alltoall_fused": (c_int, [P, P, P, c_int, P, P, P, c_int64, c_int64, c_int, P, P, c_int64, P]),
     "apt_rmat_edges": (c_int, [c_uint64, c_int64, c_int64, c_int, c_int64, c_float, c_float, c_float, P, P, P]),
     "apt_sort_u64_temp_bytes": (c_size_t, [c_int64]),
     "apt_sort_u64": (c_int, [P, P, c_int64, P, c_size_t, c_int, P]),

@@ -22,10 +22,15 @@ namespace apt {
 constexpr int kMoveRows = 4;   // rows in flight per warp
 constexpr int kMoveBlock = 256;
 constexpr int kP2pMaxRanks = 32;
-constexpr size_t kHeaderBytes = 4096;
+constexpr size_t kHeaderBytes = 16384;
 constexpr size_t kCounterOffset = 2048;
 constexpr size_t kPushSeqOffset = 2112;  // uint32: all-to-alls this rank has pushed
 constexpr size_t kWaitSeqOffset = 2120;  // uint32: all-to-alls this rank has waited for
+// fused (chunked) all-to-all: flags[parity][source][chunk], one ticket counter per chunk, one for the end
+constexpr int kMaxChunks = 8;
+constexpr size_t kChunkFlagOffset = 4096;
+constexpr size_t kChunkCounterOffset = 8192;
+constexpr size_t kDoneCounterOffset = 8192 + 64;
 
 template <typename V>
 __device__ __forceinline__ V mv_load(const V* p) { return *p; }
@@ -301,6 +306,244 @@ k_p2p_pull(const char* __restrict__ local_base, const int64_t* __restrict__ recv
   }
 }
 
+
+// ------------------------------------------------------------ fused all-to-all
+// Push, wait and pull in ONE cooperative kernel, so that the local pass that
+// permutes received rows to their final place overlaps the NVLink transfer
+// instead of following it. Every (sender, receiver) bucket is cut into C chunks
+// of rows. All blocks are co-resident (cooperative launch) and run
+//     push(0); push(1), pull(0); push(2), pull(1); ... ; pull(C-1)
+// where push(c) stores this rank's chunk c into every peer's inbox and the last
+// block to finish it releases flag (epoch, rows) for chunk c on every peer, and
+// pull(c) waits (bounded) for chunk c of every source and moves those rows from
+// the local inbox to `dst`. A flag for chunk k depends only on pushes <= k and
+// pulls <= k-2 of its sender, so no wait can close a cycle between GPUs.
+struct FusedA2A {
+  const char* src;
+  const int64_t* src_index;     // as in k_p2p_push
+  int index_is_dest;
+  const int64_t* send_offsets;  // inclusive, world_size entries (device)
+  const int64_t* recv_offsets;  // inclusive, world_size entries (device): rows each source will send
+  const int64_t* pull_index;    // NULL: dst row j = concatenation row j; else dst row i = row pull_index[i]
+  int64_t num_dst_rows;
+  char* dst;
+  int64_t row_bytes;
+  int chunks, world_size, me;
+  size_t region_bytes;
+  PeerTable peers;
+  int64_t timeout_ns;
+  int32_t* status;
+};
+
+__device__ __forceinline__ int64_t chunk_lo(int64_t len, int c, int chunks) { return len * c / chunks; }
+
+__global__ void __launch_bounds__(kMoveBlock)
+k_p2p_fused(FusedA2A a) {
+  __shared__ int64_t soff[kP2pMaxRanks + 1], roff[kP2pMaxRanks + 1];
+  __shared__ int flag_ok;
+  const int ws = a.world_size, me = a.me;
+  if (threadIdx.x == 0) soff[0] = roff[0] = 0;
+  if (threadIdx.x < ws) {
+    soff[threadIdx.x + 1] = a.send_offsets[threadIdx.x];
+    roff[threadIdx.x + 1] = a.recv_offsets[threadIdx.x];
+  }
+  char* local = a.peers.base[me];
+  uint32_t* push_seq = (uint32_t*)(local + kPushSeqOffset);
+  const uint32_t epoch = *(volatile uint32_t*)push_seq + 1u;   // moves only after every block has finished
+  const int parity = (int)(epoch & 1u);
+  __syncthreads();
+  const int64_t n_send = soff[ws], n_recv = roff[ws];
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int chunks_per_row = (int)(a.row_bytes / 16);
+  const size_t my_slot = kHeaderBytes + ((size_t)parity * ws + me) * a.region_bytes;
+  const char* inbox = local + kHeaderBytes + (size_t)parity * ws * a.region_bytes;
+  const int64_t cap_rows = (int64_t)(a.region_bytes / (size_t)a.row_bytes);
+  const bool by_dest = a.src_index && a.index_is_dest;
+  bool overflow = false, timed_out = false;
+
+  for (int step = 0; step <= a.chunks; ++step) {
+    // ---------------------------------------------------------------- push(step)
+    if (step < a.chunks) {
+      const int c = step;
+      int64_t work = n_send;
+      if (!by_dest) {
+        int64_t longest = 0;
+        for (int r = 0; r < ws; ++r) {
+          const int64_t len = soff[r + 1] - soff[r];
+          longest = max(longest, chunk_lo(len, c + 1, a.chunks) - chunk_lo(len, c, a.chunks));
+        }
+        work = longest * ws;
+      }
+      for (int64_t t0 = warp * kMoveRows; t0 < work; t0 += warps * kMoveRows) {
+        const char* sp[kMoveRows];
+        char* dp[kMoveRows];
+#pragma unroll
+        for (int k = 0; k < kMoveRows; ++k) {
+          const int64_t t = t0 + k;
+          sp[k] = nullptr;
+          dp[k] = nullptr;
+          if (t >= work) continue;
+          int r;
+          int64_t l, srow;
+          if (!by_dest) {
+            r = (int)((me + 1 + t % ws) % ws);
+            const int64_t len = soff[r + 1] - soff[r];
+            l = chunk_lo(len, c, a.chunks) + t / ws;
+            if (l >= chunk_lo(len, c + 1, a.chunks)) continue;
+            const int64_t j = soff[r] + l;
+            srow = a.src_index ? a.src_index[j] : j;
+          } else {
+            const int64_t j = a.src_index[t];
+            if (j < 0 || j >= n_send) {
+              overflow = true;
+              continue;
+            }
+            r = 0;
+            while (soff[r + 1] <= j) ++r;
+            l = j - soff[r];
+            const int64_t len = soff[r + 1] - soff[r];
+            if (l < chunk_lo(len, c, a.chunks) || l >= chunk_lo(len, c + 1, a.chunks)) continue;
+            srow = t;
+          }
+          if (l >= cap_rows) {
+            overflow = true;
+            continue;
+          }
+          sp[k] = a.src + srow * a.row_bytes;
+          dp[k] = a.peers.base[r] + my_slot + l * a.row_bytes;
+        }
+        for (int q = lane; q < chunks_per_row; q += 32) {
+          uint4 v[kMoveRows];
+#pragma unroll
+          for (int k = 0; k < kMoveRows; ++k)
+            if (sp[k]) v[k] = ld_plain_16((const uint4*)sp[k] + q);
+#pragma unroll
+          for (int k = 0; k < kMoveRows; ++k)
+            if (sp[k]) st_plain_16((uint4*)dp[k] + q, v[k]);
+        }
+      }
+      // chunk c of this rank is complete on every peer once all blocks have passed here
+      __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        int32_t* counter = (int32_t*)(local + kChunkCounterOffset) + c;
+        if (atomicAdd(counter, 1) == (int)gridDim.x - 1) {
+          *counter = 0;
+          __threadfence_system();
+          for (int r = 0; r < ws; ++r) {
+            const int64_t len = soff[r + 1] - soff[r];
+            int64_t rows = chunk_lo(len, c + 1, a.chunks) - chunk_lo(len, c, a.chunks);
+            uint64_t* flag = (uint64_t*)(a.peers.base[r] + kChunkFlagOffset) +
+                             ((size_t)parity * kP2pMaxRanks + me) * kMaxChunks + c;
+            st_release_sys(flag, ((uint64_t)epoch << 32) | (uint64_t)(uint32_t)rows);
+          }
+        }
+      }
+    }
+    // ---------------------------------------------------------------- pull(step - 1)
+    if (step >= 1) {
+      const int c = step - 1;
+      if (threadIdx.x == 0) {
+        int ok = 1;
+        const uint64_t t0 = global_timer_ns();
+        for (int s = 0; s < ws && ok; ++s) {
+          const uint64_t* flag = (const uint64_t*)(local + kChunkFlagOffset) +
+                                 ((size_t)parity * kP2pMaxRanks + s) * kMaxChunks + c;
+          uint64_t v = ld_acquire_sys(flag);
+          for (uint64_t it = 0; (uint32_t)(v >> 32) != epoch && it < (1ull << 34); ++it) {
+            if ((it & 63) == 63 && (int64_t)(global_timer_ns() - t0) > a.timeout_ns) break;
+            __nanosleep(64);
+            v = ld_acquire_sys(flag);
+          }
+          if ((uint32_t)(v >> 32) != epoch) ok = 0;
+        }
+        flag_ok = ok;
+      }
+      __syncthreads();
+      if (!flag_ok) {
+        timed_out = true;      // keep going: the other phases must still be signalled
+      } else if (a.pull_index) {
+        // gather: dst row i takes concatenation row pull_index[i] if that row lies in chunk c
+        for (int64_t i0 = warp * kMoveRows; i0 < a.num_dst_rows; i0 += warps * kMoveRows) {
+          const char* sp[kMoveRows];
+#pragma unroll
+          for (int k = 0; k < kMoveRows; ++k) {
+            sp[k] = nullptr;
+            const int64_t i = i0 + k;
+            if (i >= a.num_dst_rows) continue;
+            const int64_t j = a.pull_index[i];
+            if (j < 0 || j >= n_recv) continue;
+            int s = 0;
+            while (roff[s + 1] <= j) ++s;
+            const int64_t l = j - roff[s], len = roff[s + 1] - roff[s];
+            if (l < chunk_lo(len, c, a.chunks) || l >= chunk_lo(len, c + 1, a.chunks) || l >= cap_rows) continue;
+            sp[k] = inbox + (size_t)s * a.region_bytes + l * a.row_bytes;
+          }
+          for (int q = lane; q < chunks_per_row; q += 32) {
+            uint4 v[kMoveRows];
+#pragma unroll
+            for (int k = 0; k < kMoveRows; ++k)
+              if (sp[k]) v[k] = ld_plain_16((const uint4*)sp[k] + q);
+#pragma unroll
+            for (int k = 0; k < kMoveRows; ++k)
+              if (sp[k]) st_plain_16((uint4*)(a.dst + (i0 + k) * a.row_bytes) + q, v[k]);
+          }
+        }
+      } else {
+        // contiguous: concatenation row roff[s] + l lands at the same dst row
+        int64_t longest = 0;
+        for (int s = 0; s < ws; ++s) {
+          const int64_t len = roff[s + 1] - roff[s];
+          longest = max(longest, chunk_lo(len, c + 1, a.chunks) - chunk_lo(len, c, a.chunks));
+        }
+        const int64_t work = longest * ws;
+        for (int64_t t0 = warp * kMoveRows; t0 < work; t0 += warps * kMoveRows) {
+          const char* sp[kMoveRows];
+          char* dp[kMoveRows];
+#pragma unroll
+          for (int k = 0; k < kMoveRows; ++k) {
+            sp[k] = nullptr;
+            dp[k] = nullptr;
+            const int64_t t = t0 + k;
+            if (t >= work) continue;
+            const int s = (int)(t % ws);
+            const int64_t len = roff[s + 1] - roff[s];
+            const int64_t l = chunk_lo(len, c, a.chunks) + t / ws;
+            if (l >= chunk_lo(len, c + 1, a.chunks) || l >= cap_rows) continue;
+            sp[k] = inbox + (size_t)s * a.region_bytes + l * a.row_bytes;
+            dp[k] = a.dst + (roff[s] + l) * a.row_bytes;
+          }
+          for (int q = lane; q < chunks_per_row; q += 32) {
+            uint4 v[kMoveRows];
+#pragma unroll
+            for (int k = 0; k < kMoveRows; ++k)
+              if (sp[k]) v[k] = ld_plain_16((const uint4*)sp[k] + q);
+#pragma unroll
+            for (int k = 0; k < kMoveRows; ++k)
+              if (sp[k]) st_plain_16((uint4*)dp[k] + q, v[k]);
+          }
+        }
+      }
+      __syncthreads();   // flag_ok is rewritten in the next step
+    }
+  }
+  if (overflow) atomicOr(a.status, APT_FLAG_TABLE_FULL);
+  if (timed_out && threadIdx.x == 0) atomicOr(a.status, APT_FLAG_PEER_TIMEOUT);
+  // the last block to finish advances both sequence numbers: the next all-to-all, fused or not,
+  // then uses the other half of the inbox
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int32_t* done = (int32_t*)(local + kDoneCounterOffset);
+    if (atomicAdd(done, 1) == (int)gridDim.x - 1) {
+      *done = 0;
+      *(volatile uint32_t*)push_seq = epoch;
+      *(volatile uint32_t*)(local + kWaitSeqOffset) = epoch;
+    }
+  }
+}
+
 }  // namespace apt
 
 struct apt_p2p {
@@ -463,5 +706,56 @@ extern "C" int apt_p2p_pull(apt_p2p* ctx, const int64_t* recv_counts, const int6
   }
 #undef APT_PULL_W
 #undef APT_PULL
+  return APT_OK;
+}
+
+extern "C" int apt_p2p_alltoall_fused(apt_p2p* ctx, const void* src, const int64_t* src_index,
+                                      int index_is_dest, const int64_t* send_offsets,
+                                      const int64_t* recv_offsets, const int64_t* pull_index,
+                                      int64_t num_dst_rows, int64_t row_bytes, int chunks, void* dst,
+                                      int32_t* status_word, int64_t timeout_ns, void* stream) {
+  using namespace apt;
+  APT_CHECK_ARG(ctx && send_offsets && recv_offsets && status_word && row_bytes > 0 && num_dst_rows >= 0,
+                "apt_p2p_alltoall_fused: bad argument");
+  APT_CHECK_ARG(chunks >= 1 && chunks <= kMaxChunks, "apt_p2p_alltoall_fused: chunks %d outside [1,%d]", chunks,
+                kMaxChunks);
+  // src / dst may be NULL on a rank that sends / receives nothing; it still takes part
+  APT_CHECK_ARG(row_bytes % 16 == 0 && ((uintptr_t)src & 15) == 0 && ((uintptr_t)dst & 15) == 0 &&
+                    (ctx->region_bytes & 15) == 0,
+                "apt_p2p_alltoall_fused: rows must be multiples of 16 bytes on 16-byte boundaries");
+  APT_CHECK_ARG((size_t)row_bytes <= ctx->region_bytes, "apt_p2p_alltoall_fused: row larger than an inbox region");
+  for (int r = 0; r < ctx->world_size; ++r)
+    APT_CHECK_ARG(ctx->peer_base[r], "apt_p2p_alltoall_fused: peer %d is not attached", r);
+  if (timeout_ns <= 0) timeout_ns = 2000000000ll;
+  FusedA2A a;
+  a.src = (const char*)src;
+  a.src_index = src_index;
+  a.index_is_dest = index_is_dest;
+  a.send_offsets = send_offsets;
+  a.recv_offsets = recv_offsets;
+  a.pull_index = pull_index;
+  a.num_dst_rows = num_dst_rows;
+  a.dst = (char*)dst;
+  a.row_bytes = row_bytes;
+  a.chunks = chunks;
+  a.world_size = ctx->world_size;
+  a.me = ctx->rank;
+  a.region_bytes = ctx->region_bytes;
+  for (int r = 0; r < kP2pMaxRanks; ++r) a.peers.base[r] = ctx->peer_base[r];
+  a.timeout_ns = timeout_ns;
+  a.status = status_word;
+  // every block has to be resident at once (blocks wait for each other's chunks): cooperative launch
+  int per_sm = 0;
+  APT_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_p2p_fused, kMoveBlock, 0));
+  APT_CHECK_ARG(per_sm >= 1, "apt_p2p_alltoall_fused: kernel does not fit an SM");
+  int dev = 0, sms = 0;
+  APT_CUDA(cudaGetDevice(&dev));
+  APT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int grid = sms * (per_sm < 4 ? per_sm : 4);
+  void* args[] = {&a};
+  cudaStream_t s = (cudaStream_t)stream;
+  ProfScope prof("p2p_fused", s);
+  APT_CUDA(cudaLaunchCooperativeKernel((const void*)k_p2p_fused, dim3(grid), dim3(kMoveBlock), args, 0, s));
+  count_launch();
   return APT_OK;
 }

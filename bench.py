@@ -45,9 +45,10 @@ def parse():
     ap.add_argument("--impl", default="apt_b200", choices=["apt_b200", "reference"])
     ap.add_argument("--cpu-batches", type=int, default=12, help="batches of the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--stage", default="minibatch", choices=["minibatch", "gather", "shuffle"],
+    ap.add_argument("--stage", default="minibatch", choices=["minibatch", "gather", "shuffle", "ops"],
                     help="gather: the cached feature gather alone on a synthetic table; "
-                         "shuffle: the NPC feature shuffle alone (needs --gpus >= 2 under torchrun)")
+                         "shuffle: the NPC feature shuffle alone (needs --gpus >= 2 under torchrun); "
+                         "ops: sampling, relabelling, SpMM, SDDMM and the fused GAT block one by one")
     ap.add_argument("--rows", type=int, default=1_081_344, help="--stage gather: rows per call")
     ap.add_argument("--table-rows", type=int, default=4_000_000, help="--stage gather: rows of the cached table")
     ap.add_argument("--feat-dim", type=int, default=128)
@@ -270,6 +271,91 @@ def stage_gather(args):
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": round(gbs / peak, 4), "traffic": None}}))
 
 
+# ------------------------------------------------------------------ stage: ops
+def stage_ops(args):
+    """Every remaining operator of the path alone, at the size of the papers-shaped outermost hop
+    (67 584 destination nodes x fanout 15) on the small R-MAT graph (CSC larger than L2):
+    time per call (CUDA events) and algorithmic GB/s against the measured HBM peak."""
+    import apt_b200  # noqa: F401
+    from apt_b200 import ops, synthetic
+
+    torch.cuda.set_device(0)
+    w = synthetic.WORKLOADS["c0_small_np"]
+    indptr, indices = synthetic.build_csc(w)
+    e = torch.empty(0, dtype=torch.int64)
+    ops.mix_cache_graphs(0, e, e, e, indptr, indices)
+    S, f, n = 67_584, 15, w.num_nodes
+    g = torch.Generator(device="cuda").manual_seed(9)
+    peak, peak_kind = peaks()
+    results = {}
+
+    def timed(name, fn, algo_bytes, fresh=None):
+        for _ in range(args.warmup):
+            fn(fresh() if fresh else None)
+        inputs = [fresh() if fresh else None for _ in range(args.steps)]
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.nvtx.range_push("apt_timed")
+        e0.record()
+        for x in inputs:
+            fn(x)
+        e1.record()
+        torch.cuda.nvtx.range_pop()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        gbs = algo_bytes / (ms * 1e-3) / 1e9
+        results[name] = {"us": round(1000 * ms, 2), "algorithmic_mb": round(algo_bytes / 1e6, 2),
+                         "gbs": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4)}
+
+    def seeds():
+        return torch.randint(0, n, (S,), generator=g, device="cuda")
+
+    # sampling: 32 + 16 f bytes per seed
+    timed("sample_csc_fanout (67 584 seeds x 15)", lambda s: ops._sample(s, f), S * (32 + 16 * f), seeds)
+    nbr_pool = [ops._sample(seeds(), f) for _ in range(4)]
+    seed_pool = [torch.randperm(n, generator=g, device="cuda")[:S].contiguous() for _ in range(4)]
+    k = [0]
+
+    def relabel(_):
+        k[0] += 1
+        ops._relabel_enqueue(seed_pool[k[0] % 4], nbr_pool[k[0] % 4], None, ops.STATE.word(0))
+
+    items = S * (1 + f)
+    timed("relabel_csc (1.08 M items, no host read)", relabel, 16 * items)
+    uniq, rel = ops.relabel_csc(seed_pool[0], nbr_pool[0])
+    n_src, E = uniq.numel(), rel.numel()
+    col = torch.arange(S, device="cuda").repeat_interleave(f)
+    off = [torch.tensor(v, device="cuda") for v in ([0, E], [0, n_src], [0, S])]
+    for dt, name in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
+        D = 256
+        x = torch.randn((n_src, D), generator=g, device="cuda").to(dt)
+        esz = x.element_size()
+        ws = ops.STATE.workspace("spmm", 1)
+        timed(f"spmm_copy_u_sum {name} D=256 (1.01 M edges, grouped)",
+              lambda _: ops._spmm(0, rel, col, x, None, off[0], off[1], off[2]), E * (16 + D * esz) + S * D * esz)
+        gsd = torch.randn((S, D), generator=g, device="cuda").to(dt)
+        timed(f"spmm_copy_u_sum {name} D=256 backward shape (scattered)",
+              lambda _: ops._spmm(0, col, rel, gsd, None, off[0], off[2], off[1]), E * (16 + D * esz) + n_src * D * esz)
+    el = torch.randn((n_src, 4), generator=g, device="cuda")
+    er = torch.randn((S, 4), generator=g, device="cuda")
+    timed("sddmm_u_add_v f32 D=4 (GAT scores)", lambda _: ops.sddmm_u_add_v(rel, col, el, er, *off), E * (16 + 3 * 4 * 4))
+    ft = torch.randn((n_src, 4, 64), generator=g, device="cuda").bfloat16()
+    elb, erb = el.bfloat16(), er.bfloat16()
+    timed("gat_edge_softmax_sum bf16 4 heads x 64",
+          lambda _: ops.gat_edge_softmax_sum(rel, col, ft, elb, erb, S), E * (8 + 4 * 2 + 256 * 2) + S * 256 * 2)
+    ids = torch.randint(0, n, (S,), generator=g, device="cuda")
+    ops.register_min_vids(torch.tensor([0, n]))
+    timed("unique_sorted (67 584 ids over 2^20)", lambda _: ops._unique_enqueue(ids, None, 0, n, ops.STATE.word(1)),
+          16 * S + n // 1024 * 4)
+    timed("bucket_by_owner (67 584 ids)", lambda _: ops._bucket(ids), 24 * S)
+    ops.check_status()
+    print(json.dumps({"metric": "operators of the mini-batch path, one by one", "unit": "us per call", "n_gpus": 1,
+                      "steps": args.steps, "warmup": args.warmup, "data": "synthetic",
+                      "config": {"workload": "stage ops", "graph": w.name, "dst_nodes": S, "fanout": f,
+                                 "block_src_nodes": n_src, "edges": E},
+                      "peak": {"hbm_gbs": peak, "kind": peak_kind}, "ops": results}))
+
+
 # ------------------------------------------------------------------ stage: shuffle
 def stage_shuffle(args):
     """The NPC feature shuffle alone (FeatShuffle forward and backward): every rank asks
@@ -311,7 +397,7 @@ def stage_shuffle(args):
         for _ in range(args.warmup):
             fn()
         ops.profile_enable(profiled)
-        for tag in (b"p2p_push", b"p2p_wait", b"p2p_pull"):
+        for tag in (b"p2p_push", b"p2p_wait", b"p2p_pull", b"p2p_fused"):
             t_, k_ = ctypes.c_double(), ctypes.c_int64()
             lib.apt_profile_read(tag, ctypes.byref(t_), ctypes.byref(k_))
         torch.cuda.synchronize()
@@ -326,7 +412,7 @@ def stage_shuffle(args):
         ms = torch.tensor([e0.elapsed_time(e1) / args.steps], device="cuda")
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         stages = {}
-        for tag in ("p2p_push", "p2p_wait", "p2p_pull"):
+        for tag in ("p2p_push", "p2p_wait", "p2p_pull", "p2p_fused"):
             t_, k_ = ctypes.c_double(), ctypes.c_int64()
             lib.apt_profile_read(tag.encode(), ctypes.byref(t_), ctypes.byref(k_))
             stages[tag] = 1000.0 * t_.value / max(k_.value, 1)
@@ -337,7 +423,11 @@ def stage_shuffle(args):
         for fwd in (True, False):
             ms, _ = run(ex, fwd, False)
             res[f"{name}_{'fwd' if fwd else 'bwd'}_ms"] = ms
-    _, stages = run(p2p, True, True)
+    # the three separate kernels (push, wait, pull), to show what each part costs
+    fused_was = p2p.use_fused
+    p2p.use_fused = False
+    res["p2p_unfused_fwd_ms"], stages = run(p2p, True, True)
+    p2p.use_fused = fused_was
     ops.STATE.exchange = p2p
     ops.check_status()
     link_peak = 770.0      # GB/s per direction per GPU, measured peer copy on this pool (900 nominal)
@@ -352,7 +442,8 @@ def stage_shuffle(args):
             "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": res["p2p_fwd_ms"], "higher_is_better": True, "dtype": args.feat_dtype, "data": "synthetic",
             "config": {"workload": "stage shuffle", "rows_per_gpu": rows, "row_bytes": row_bytes,
-                       "remote_bytes_per_gpu": remote, "owners": "uniform over ranks"},
+                       "remote_bytes_per_gpu": remote, "owners": "uniform over ranks",
+                       "fused_kernel": bool(p2p.use_fused), "chunks": p2p.chunks},
             "ms": res, "gbs": gbs, "p2p_stage_us": stages,
             "roofline": {"kernel": "k_p2p_push", "bound": "nvlink", "achieved": round(push_gbs, 1), "peak": link_peak,
                          "peak_kind": "measured peer copy per direction (900 nominal)", "unit": "GB/s",
@@ -370,6 +461,8 @@ def main():
         return stage_gather(args)
     if args.stage == "shuffle":
         return stage_shuffle(args)
+    if args.stage == "ops":
+        return stage_ops(args)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -369,6 +369,21 @@ int apt_p2p_pull(apt_p2p* ctx, const int64_t* recv_counts,
                  int64_t num_dst_rows, int64_t max_rows, int64_t row_bytes,
                  void* dst, void* stream);
 
+/* The same all-to-all as push + wait + pull, as ONE cooperative kernel in which
+ * the local pass (moving received rows to their final place) overlaps the
+ * NVLink transfer: buckets are cut into `chunks` (1..8) row ranges, each with
+ * its own flag; blocks push chunk c+1 while they pull chunk c. The receiver has
+ * to know how many rows every source sends (recv_offsets, device, inclusive),
+ * which FeatShuffle and AlltoAll do (their offsets come from the host). Rows
+ * must be multiples of 16 bytes. pull_index NULL: dst row j = concatenation row
+ * j; else dst row i = concatenation row pull_index[i] (num_dst_rows rows). */
+int apt_p2p_alltoall_fused(apt_p2p* ctx, const void* src, const int64_t* src_index,
+                           int index_is_dest, const int64_t* send_offsets,
+                           const int64_t* recv_offsets, const int64_t* pull_index,
+                           int64_t num_dst_rows, int64_t row_bytes, int chunks,
+                           void* dst, int32_t* status_word, int64_t timeout_ns,
+                           void* stream);
+
 /* --------------------------------------------------------- setup utilities
  * Not on the timed path; they prepare the synthetic graphs of the benchmark
  * on the GPU so that a 1.6 G-edge graph is built in seconds. */

@@ -144,6 +144,12 @@ def main():
         gb2 = ops.feat_shuffle(grad, recv_off, send_off, perm, D, 0)
         ops.STATE.exchange = p2p
         assert torch.equal(gb, gb2), "feat_shuffle bwd: p2p vs nccl"
+        # the same two calls through the single cooperative kernel, buckets cut into 3 chunks
+        p2p.use_fused, p2p.chunks = True, 3
+        y3 = ops.feat_shuffle(x, send_off, recv_off, perm, D, 1)
+        gb3 = ops.feat_shuffle(grad, recv_off, send_off, perm, D, 0)
+        p2p.use_fused, p2p.chunks = False, 1
+        assert torch.equal(y3, y) and torch.equal(gb3, gb), "fused all-to-all"
         all_grad = gather_objects(host(grad))
         all_gb = gather_objects(host(gb))
         all_meta = gather_objects((host(perm), send_off.numpy(), recv_off.numpy()))
