@@ -47,7 +47,7 @@ PROTOTYPES = {
     "apt_gather_rows": (c_int, [P, c_int64, P, P, c_int64, P, c_int64, c_int64, P, c_int64, c_int64, c_int64, P, P, c_size_t, P, P]),
     "apt_gather_static_max_rows": (c_int64, []),
     "apt_gather_rows_static": (c_int, [P, c_int64, P, c_int64, P, c_int64, c_int64, P, c_int64, c_int64, c_int64, P, P, P]),
-    "apt_spmm_workspace_bytes": (c_size_t, [c_int64]),
+    "apt_spmm_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "apt_spmm_sum": (c_int, [c_int, c_int, P, P, c_int64, P, P, c_int64, c_int64, P, P, P, c_int, c_int64, P, P, c_size_t, P]),
     "apt_sddmm": (c_int, [c_int, c_int, P, P, c_int64, P, P, c_int64, P, P, P, c_int, P, P]),
     "apt_gat_edge_softmax_sum": (c_int, [c_int, P, P, c_int64, P, P, P, c_int, c_int64, c_float, c_int64, P, P, P, c_size_t, P, P]),

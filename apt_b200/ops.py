@@ -526,7 +526,7 @@ def _spmm(op, coo_row, coo_col, inp, edata, coo_offset, input_offset, output_off
     # edata may be [E, D], [E, H] or [E, H, 1]: one value per column or per head
     edim = edata.numel() // num_edges if edata is not None and num_edges else feat_dim
     out = torch.empty((out_num, feat_dim), dtype=ref.dtype, device=ref.device)
-    nbytes = lib.apt_spmm_workspace_bytes(out_num)
+    nbytes = lib.apt_spmm_workspace_bytes(out_num, num_edges)
     ws = STATE.workspace("spmm", nbytes)
     check(lib.apt_spmm_sum(op, _DTYPE_CODE[ref.dtype], _ptr(coo_row), _ptr(coo_col), coo_row.numel(),
                            _ptr(inp), _ptr(edata), int(edim), int(feat_dim), _ptr(coo_offset),
@@ -598,7 +598,7 @@ def gat_edge_softmax_sum(coo_row, coo_col, ft, el, er, num_dst: int, negative_sl
     head_dim = ft.numel() // max(num_src * heads, 1)
     out = torch.empty((num_dst, heads, head_dim), dtype=ft.dtype, device=ft.device)
     attn = torch.empty((coo_row.numel(), heads, 1), dtype=ft.dtype, device=ft.device) if return_attention else None
-    nbytes = lib.apt_spmm_workspace_bytes(num_dst)
+    nbytes = lib.apt_spmm_workspace_bytes(num_dst, 0)
     ws = STATE.workspace("spmm", nbytes)
     check(lib.apt_gat_edge_softmax_sum(_DTYPE_CODE[ft.dtype], _ptr(coo_row), _ptr(coo_col), coo_row.numel(),
                                        _ptr(ft), _ptr(el), _ptr(er), int(heads), int(head_dim),

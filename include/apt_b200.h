@@ -250,15 +250,17 @@ int apt_gather_rows_static(const int64_t* index, int64_t num_rows,
  * The output is fully written (rows without edges become 0); it needs no
  * zero-fill. When col is non-decreasing inside every segment (a sampled
  * block), each output row is reduced by one warp in edge order: no atomics,
- * deterministic. Otherwise edges are scattered with vector red.add.
+ * deterministic. Otherwise the edges are first grouped by output row with a
+ * counting sort on the device and reduced by the same kernel (no float atomics;
+ * the order of the terms inside a row then depends on scheduling).
  * op: 0 copy_u, 1 copy_e, 2 u_mul_e, 3 u_add_e (the arithmetic the reference's
  *     UMulESum kernel actually performs, src/cuda/spmm.cu:78).
  * edata (copy_e, u_mul_e, u_add_e) has num_edges rows of edata_dim columns,
  * edata_dim == feat_dim, or a divisor of feat_dim (one scalar per head,
  * broadcast over feat_dim/edata_dim columns).
- * workspace: apt_spmm_workspace_bytes(num_out_rows) bytes.
+ * workspace: apt_spmm_workspace_bytes(num_out_rows, num_edges) bytes.
  */
-size_t apt_spmm_workspace_bytes(int64_t num_out_rows);
+size_t apt_spmm_workspace_bytes(int64_t num_out_rows, int64_t num_edges);
 int apt_spmm_sum(int op, int dtype, const int64_t* coo_row,
                  const int64_t* coo_col, int64_t num_edges, const void* input,
                  const void* edata, int64_t edata_dim, int64_t feat_dim,
@@ -284,7 +286,7 @@ int apt_sddmm(int op, int dtype, const int64_t* coo_row,
  * num_heads*head_dim], el [num_src, num_heads], er [num_dst, num_heads];
  * out_attn ([num_edges, num_heads], may be NULL) receives a. Rows without
  * edges become 0. Edges that are not grouped set APT_FLAG_NOT_GROUPED and give
- * zeros. workspace: apt_spmm_workspace_bytes(num_dst) bytes. */
+ * zeros. workspace: apt_spmm_workspace_bytes(num_dst, 0) bytes. */
 int apt_gat_edge_softmax_sum(int dtype, const int64_t* coo_row,
                              const int64_t* coo_col, int64_t num_edges,
                              const void* ft, const void* el, const void* er,

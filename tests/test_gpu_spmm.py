@@ -65,6 +65,28 @@ def test_copy_u_sum_unsorted_backward_shape(dtype):
         assert np.abs(got - want).max() <= 0.05 * max(1.0, np.abs(want).max())
 
 
+@pytest.mark.parametrize("grouped", [True, False])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_hub_rows_with_thousands_of_edges(grouped, dtype):
+    # power-law destinations (the backward call): a few output rows own most of the edges
+    rng = np.random.default_rng(12)
+    n_in, n_out, E, D = 3000, 500, 60000, 128
+    col = np.minimum((rng.zipf(1.4, E) - 1), n_out - 1).astype(I64)
+    if grouped:
+        col = np.sort(col)
+    row = rng.integers(0, n_in, E).astype(I64)
+    x = _round(rng.standard_normal((n_in, D)).astype(np.float32), dtype)
+    off = (np.array([0, E], dtype=I64), np.array([0, n_in], dtype=I64), np.array([0, n_out], dtype=I64))
+    assert np.bincount(col).max() > 5000
+    out = ops.spmm_copy_u_sum(dev(row), dev(col), dev(x, dtype), dev(off[0]), dev(off[1]), dev(off[2]))
+    want = orc.spmm_sum("copy_u", row, col, x, None, *off)
+    got = host(out).astype(np.float64)
+    # sums of thousands of terms: the bound is relative to the sum of magnitudes (fp32 accumulation)
+    scale = np.maximum(orc.spmm_sum("copy_u", row, col, np.abs(x), None, *off), 1.0)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert (np.abs(got - want) / scale).max() <= tol
+
+
 def test_empty_rows_and_empty_edges():
     D = 16
     x = np.ones((10, D), dtype=np.float32)
