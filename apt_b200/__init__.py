@@ -10,8 +10,10 @@ from . import npc_ops  # noqa: F401  (registers torch.ops.npc.*)
 from . import ops
 from .ops import (  # noqa: F401
     STATE, alltoall, cache_feats_shared, check_status, cpu_load_subtensor, feat_shuffle, init,
-    load_subtensor, local_sample_one_layer, mix_cache_graphs, nccl_get_unique_id, np_sample_and_shuffle,
+    load_subtensor, local_sample_one_layer, mix_cache_graphs, mp_feat_shuffle_bwd, mp_feat_shuffle_fwd,
+    mp_sample_shuffle, nccl_get_unique_id, np_sample_and_shuffle,
     register_min_vids, relabel_csc, rows_gather, rows_scatter, sddmm_u_add_v, sddmm_u_mul_v, set_sampling,
-    gat_edge_softmax_sum, shuffle_seeds, sp_sample_shuffle_src, spmm_copy_e_sum, spmm_copy_u_sum, spmm_u_mul_e_sum, unique_sorted,
+    gat_edge_softmax_sum, shuffle_seeds, sp_feat_shuffle, sp_sample_and_shuffle, sp_sample_shuffle_src, spmm_copy_e_sum, spmm_copy_u_sum, spmm_u_mul_e_sum, src_to_vir,
+    srcdst_to_vir, unique_sorted,
 )
-from .sampler import Block, DPNeighborSampler, MixedNeighborSampler, SPGATSampler, create_block  # noqa: F401
+from .sampler import Block, DPNeighborSampler, MPSampler, MixedNeighborSampler, SPGATSampler, SPVirtualSampler, create_block  # noqa: F401

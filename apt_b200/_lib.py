@@ -21,6 +21,7 @@ lib = ctypes.CDLL(LIB_PATH)
 APT_OK, APT_ERR_BAD_ARG, APT_ERR_CUDA, APT_ERR_TIMEOUT, APT_ERR_OOB, APT_ERR_CAPACITY = range(6)
 FLAG_ID_OUT_OF_RANGE, FLAG_FEAT_NOT_EXIST, FLAG_ZERO_DEGREE, FLAG_TABLE_FULL, FLAG_PEER_TIMEOUT = 1, 2, 4, 8, 16
 FLAG_NOT_GROUPED = 32
+FLAG_SIZE_MISMATCH = 64
 F32, BF16, F16 = 0, 1, 2
 IPC_HANDLE_BYTES = 64
 
@@ -51,6 +52,11 @@ PROTOTYPES = {
     "apt_spmm_sum": (c_int, [c_int, c_int, P, P, c_int64, P, P, c_int64, c_int64, P, P, P, c_int, c_int64, P, P, c_size_t, P]),
     "apt_sddmm": (c_int, [c_int, c_int, P, P, c_int64, P, P, c_int64, P, P, P, c_int, P, P]),
     "apt_gat_edge_softmax_sum": (c_int, [c_int, P, P, c_int64, P, P, P, c_int, c_int64, c_float, c_int64, P, P, P, c_size_t, P, P]),
+    "apt_src_to_vir": (c_int, [P, c_int64, c_int64, c_int64, P, c_int, c_int, c_int, c_int, c_int, P, P]),
+    "apt_srcdst_to_vir": (c_int, [P, c_int64, P, c_int64, c_int64, P, c_int, c_int, c_int, c_int, c_int, P, P]),
+    "apt_vir_send_sizes": (c_int, [P, c_int64, P, c_int64, P, c_int, c_int64, c_int, P, P, P]),
+    "apt_sp_pack_frontier": (c_int, [P, P, c_int64, c_int64, c_int, c_int64, c_int64, P, P]),
+    "apt_sp_unpack_frontier": (c_int, [P, c_int64, P, c_int64, P, P, P]),
     "apt_rows_gather": (c_int, [P, P, c_int64, c_int64, P, P]),
     "apt_rows_scatter": (c_int, [P, P, c_int64, c_int64, P, P]),
     "apt_p2p_create": (c_int, [c_int, c_int, c_size_t, ctypes.POINTER(P), P]),
@@ -62,6 +68,7 @@ PROTOTYPES = {
     "apt_p2p_push": (c_int, [P, P, P, c_int, P, c_int64, c_int64, P, P]),
     "apt_p2p_wait": (c_int, [P, P, P, c_int64, P]),
     "apt_p2p_pull": (c_int, [P, P, P, c_int, c_int64, c_int64, c_int64, P, P]),
+    "apt_p2p_pull_sum": (c_int, [P, P, c_int, c_int64, c_int64, P, P, P]),
     "apt_p2p_alltoall_fused": (c_int, [P, P, P, c_int, P, P, P, c_int64, c_int64, c_int, P, P, c_int64, P]),
     "apt_rmat_edges": (c_int, [c_uint64, c_int64, c_int64, c_int, c_int64, c_float, c_float, c_float, P, P, P]),
     "apt_sort_u64_temp_bytes": (c_size_t, [c_int64]),

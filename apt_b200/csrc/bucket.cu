@@ -4,25 +4,7 @@
 
 namespace apt {
 
-constexpr int kMaxRanks = 32;
 constexpr int kBucketBlock = 1024;
-
-struct OwnerParams {
-  int world_size;
-  int shuffle_id_offset;
-  int rank, node_beg, node_end;
-};
-
-// Owner of id v: the last rank d with min_vids[d] <= v, starting from
-// shuffle_id_offset; owners outside this machine's rank window fall back to
-// the calling rank.
-__device__ __forceinline__ int owner_of(int64_t v, const int64_t* mv,
-                                        const OwnerParams& p) {
-  int d = p.shuffle_id_offset;
-  while (d + 1 < p.world_size && mv[d + 1] <= v) ++d;
-  if (d < p.node_beg || d >= p.node_end) d = p.rank;
-  return d;
-}
 
 __global__ void __launch_bounds__(kBucketBlock)
 k_bucket_count(const int64_t* __restrict__ ids, int64_t n, const int64_t* __restrict__ n_dev,

@@ -137,6 +137,24 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
+constexpr int kMaxRanks = 32;
+
+struct OwnerParams {
+  int world_size;
+  int shuffle_id_offset;
+  int rank, node_beg, node_end;
+};
+
+// Owner of id v: the last rank d with min_vids[d] <= v, starting from
+// shuffle_id_offset; owners outside this machine's rank window fall back to
+// the calling rank.
+__device__ __forceinline__ int owner_of(int64_t v, const int64_t* mv, const OwnerParams& p) {
+  int d = p.shuffle_id_offset;
+  while (d + 1 < p.world_size && mv[d + 1] <= v) ++d;
+  if (d < p.node_beg || d >= p.node_end) d = p.rank;
+  return d;
+}
+
 // Sizes may live on the device: an operator chained behind another one takes
 // its element count from a device word (what the previous kernel produced), so
 // that the host never has to wait for it. `n_host` is then only an upper bound

@@ -13,6 +13,8 @@
 // The epoch of an all-to-all is not a kernel argument: push and wait kernels
 // derive it from the sequence numbers in the local header and advance them,
 // so an enqueued sequence can be captured in a CUDA graph and replayed.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -306,6 +308,53 @@ k_p2p_pull(const char* __restrict__ local_base, const int64_t* __restrict__ recv
   }
 }
 
+
+// Reduce-scatter epilogue. Every source has pushed the same number of rows (its
+// partial results for this rank's segment) into its region of the local inbox;
+// element i of dst is their sum, taken in rank order with an fp32 accumulator,
+// so the result does not depend on which peer arrived first. A source whose
+// count differs from num_rows is left out and APT_FLAG_SIZE_MISMATCH is set.
+template <typename T> __device__ __forceinline__ float elem_to_f(T x);
+template <> __device__ __forceinline__ float elem_to_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ float elem_to_f<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <> __device__ __forceinline__ float elem_to_f<__half>(__half x) { return __half2float(x); }
+template <typename T> __device__ __forceinline__ T elem_from_f(float x);
+template <> __device__ __forceinline__ float elem_from_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 elem_from_f<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+template <> __device__ __forceinline__ __half elem_from_f<__half>(float x) { return __float2half_rn(x); }
+
+template <typename T, int VE>
+__global__ void __launch_bounds__(256)
+k_p2p_pull_sum(const char* __restrict__ local_base, const int64_t* __restrict__ recv_counts,
+               int world_size, size_t region_bytes, int64_t num_rows, int64_t row_elems,
+               T* __restrict__ dst, int32_t* status) {
+  __shared__ int ok[kP2pMaxRanks];
+  const int parity = (int)(*(const volatile uint32_t*)(local_base + kWaitSeqOffset) & 1u);
+  const char* data = local_base + kHeaderBytes + (size_t)parity * world_size * region_bytes;
+  if (threadIdx.x < world_size) {
+    ok[threadIdx.x] = recv_counts[threadIdx.x] == num_rows;
+    if (!ok[threadIdx.x] && blockIdx.x == 0) atomicOr(status, APT_FLAG_SIZE_MISMATCH);
+  }
+  __syncthreads();
+  struct alignas(sizeof(T) * VE) Vec { T v[VE]; };
+  const int64_t nvec = num_rows * row_elems / VE;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    float acc[VE];
+#pragma unroll
+    for (int t = 0; t < VE; ++t) acc[t] = 0.f;
+    for (int s = 0; s < world_size; ++s) {
+      if (!ok[s]) continue;
+      const Vec x = *((const Vec*)(data + (size_t)s * region_bytes) + i);
+#pragma unroll
+      for (int t = 0; t < VE; ++t) acc[t] += elem_to_f<T>(x.v[t]);
+    }
+    Vec o;
+#pragma unroll
+    for (int t = 0; t < VE; ++t) o.v[t] = elem_from_f<T>(acc[t]);
+    *((Vec*)dst + i) = o;
+  }
+}
 
 // ------------------------------------------------------------ fused all-to-all
 // Push, wait and pull in ONE cooperative kernel, so that the local pass that
@@ -706,6 +755,37 @@ extern "C" int apt_p2p_pull(apt_p2p* ctx, const int64_t* recv_counts, const int6
   }
 #undef APT_PULL_W
 #undef APT_PULL
+  return APT_OK;
+}
+
+extern "C" int apt_p2p_pull_sum(apt_p2p* ctx, const int64_t* recv_counts, int dtype, int64_t num_rows,
+                                int64_t row_elems, void* dst, int32_t* status_word, void* stream) {
+  using namespace apt;
+  APT_CHECK_ARG(ctx && recv_counts && status_word && num_rows >= 0 && row_elems > 0, "apt_p2p_pull_sum: bad argument");
+  APT_CHECK_ARG(dtype >= APT_F32 && dtype <= APT_F16, "apt_p2p_pull_sum: dtype %d", dtype);
+  if (num_rows == 0) return APT_OK;
+  APT_CHECK_ARG(dst, "apt_p2p_pull_sum: null destination");
+  const size_t esz = dtype == APT_F32 ? 4 : 2;
+  APT_CHECK_ARG((size_t)num_rows * row_elems * esz <= ctx->region_bytes,
+                "apt_p2p_pull_sum: %lld rows of %lld elements exceed the %zu-byte region", (long long)num_rows,
+                (long long)row_elems, ctx->region_bytes);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int64_t total = num_rows * row_elems;
+  const bool vec = (((uint64_t)(total * esz) | (uintptr_t)dst) & 15) == 0;
+  const int ve = vec ? (int)(16 / esz) : 1;
+  const int grid = wave_grid(ceil_div(total / ve, 256), 8, 4);
+  ProfScope prof("p2p_pull_sum", s);
+#define APT_PULL_SUM(T, VE)                                                                              \
+  APT_LAUNCH((k_p2p_pull_sum<T, VE>), grid, 256, 0, s, ctx->local_base, recv_counts, ctx->world_size,    \
+             ctx->region_bytes, num_rows, row_elems, (T*)dst, status_word)
+  if (dtype == APT_F32) {
+    if (vec) { APT_PULL_SUM(float, 4); } else { APT_PULL_SUM(float, 1); }
+  } else if (dtype == APT_BF16) {
+    if (vec) { APT_PULL_SUM(__nv_bfloat16, 8); } else { APT_PULL_SUM(__nv_bfloat16, 1); }
+  } else {
+    if (vec) { APT_PULL_SUM(__half, 8); } else { APT_PULL_SUM(__half, 1); }
+  }
+#undef APT_PULL_SUM
   return APT_OK;
 }
 

@@ -304,7 +304,11 @@ k_spmm_rows(const int64_t* __restrict__ row, int64_t E, const T* __restrict__ in
   }
   __syncthreads();
   const bool unsorted = *ws.flags != 0;
-  const int sub = threadIdx.x % group;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane % group;
+  // lanes of this group inside the warp: the shuffles below name only them, so groups
+  // whose rows differ in length do not wait for each other
+  const unsigned gmask = group == 32 ? 0xffffffffu : (((1u << group) - 1u) << (lane - sub));
   const int64_t rows_per_block = blockDim.x / group;
   const int64_t nvec = feat_dim / VE;
   const int64_t per = feat_dim / edata_dim;
@@ -314,23 +318,40 @@ k_spmm_rows(const int64_t* __restrict__ row, int64_t E, const T* __restrict__ in
     const int64_t e0 = ws.range[d];
     const int64_t e1 = ws.range[d + 1];
     if (e1 - e0 > kLongRow) {
-      // one lane group would walk this row for milliseconds: queue it for k_spmm_long
+      // one lane group would walk this row for too long: queue it for k_spmm_long
       if (sub == 0) ws.long_rows[atomicAdd(ws.flags + 2, 1)] = d;
       continue;
     }
-    for (int64_t c = sub; c < nvec; c += group) {
+    for (int64_t c0 = 0; c0 < nvec; c0 += group) {
+      const int64_t c = c0 + sub;
       float acc[VE];
 #pragma unroll
       for (int t = 0; t < VE; ++t) acc[t] = 0.f;
-      for (int64_t k = e0; k < e1; ++k) {
-        const int64_t e = unsorted ? (int64_t)ws.order[k] : k;
-        const int64_t src = OP == kCopyE ? 0 : ioff[st.nseg > 1 ? seg_of(coo, st.nseg, e) : 0] + row[e];
-        edge_value<T, VE, OP>(acc, in, edata, src, e, feat_dim, edata_dim, per, c * VE);
+      // The group resolves `group` edges at a time, one per lane (edge id through the
+      // order array when the edges are not grouped, then its source row): two dependent
+      // loads for the whole batch instead of two per edge. The values are then handed
+      // round by shuffles, and the row loads of one batch do not depend on each other.
+      for (int64_t k0 = e0; k0 < e1; k0 += group) {
+        int my_e = 0;
+        int64_t my_src = 0;
+        if (k0 + sub < e1) {
+          my_e = unsorted ? ws.order[k0 + sub] : (int)(k0 + sub);
+          my_src = OP == kCopyE ? 0 : ioff[st.nseg > 1 ? seg_of(coo, st.nseg, my_e) : 0] + row[my_e];
+        }
+        const int cnt = (int)min((int64_t)group, e1 - k0);
+#pragma unroll 4
+        for (int j = 0; j < cnt; ++j) {
+          const int e = __shfl_sync(gmask, my_e, j, group);
+          const int64_t src = __shfl_sync(gmask, my_src, j, group);
+          if (c < nvec) edge_value<T, VE, OP>(acc, in, edata, src, e, feat_dim, edata_dim, per, c * VE);
+        }
       }
-      Pack<T, VE> o;
+      if (c < nvec) {
+        Pack<T, VE> o;
 #pragma unroll
-      for (int t = 0; t < VE; ++t) o.v[t] = Elem<T>::from_f(acc[t]);
-      store_pack<T, VE>(out + d * feat_dim + c * VE, o);
+        for (int t = 0; t < VE; ++t) o.v[t] = Elem<T>::from_f(acc[t]);
+        store_pack<T, VE>(out + d * feat_dim + c * VE, o);
+      }
     }
   }
 }
@@ -457,15 +478,17 @@ static int pow2_at_least(int64_t x) {
   return g;
 }
 
-// One block per long row: the eight warps take the row's edges in turn, each keeps
+constexpr int kLongWarps = 32;
+
+// One block per long row: its kLongWarps warps take the row's edges in turn, each keeps
 // its partial sums in fp32 registers, the partials meet in shared memory and the
 // row is written once. Columns are covered 32 vectors at a time.
 template <typename T, int VE, int OP>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kLongWarps * 32)
 k_spmm_long(const int64_t* __restrict__ row, const T* __restrict__ in, const T* __restrict__ edata,
             int64_t edata_dim, int64_t feat_dim, SegTable st, SpmmWs ws, T* __restrict__ out) {
   __shared__ int64_t coo[kMaxSegments + 1], ioff[kMaxSegments + 1];
-  __shared__ float part[8][32][VE];
+  __shared__ float part[kLongWarps][32][VE];
   for (int t = threadIdx.x; t <= st.nseg; t += blockDim.x) {
     coo[t] = st.coo_off[t];
     ioff[t] = OP == kCopyE ? 0 : st.in_off[t];
@@ -484,11 +507,20 @@ k_spmm_long(const int64_t* __restrict__ row, const T* __restrict__ in, const T* 
       float acc[VE];
 #pragma unroll
       for (int t = 0; t < VE; ++t) acc[t] = 0.f;
-      if (c < nvec) {
-        for (int64_t k = e0 + warp; k < e1; k += 8) {
-          const int64_t e = unsorted ? (int64_t)ws.order[k] : k;
-          const int64_t src = OP == kCopyE ? 0 : ioff[st.nseg > 1 ? seg_of(coo, st.nseg, e) : 0] + row[e];
-          edge_value<T, VE, OP>(acc, in, edata, src, e, feat_dim, edata_dim, per, c * VE);
+      // each warp takes every kLongWarps-th batch of 32 edges, resolved one per lane as in k_spmm_rows
+      for (int64_t k0 = e0 + warp * 32; k0 < e1; k0 += kLongWarps * 32) {
+        int my_e = 0;
+        int64_t my_src = 0;
+        if (k0 + lane < e1) {
+          my_e = unsorted ? ws.order[k0 + lane] : (int)(k0 + lane);
+          my_src = OP == kCopyE ? 0 : ioff[st.nseg > 1 ? seg_of(coo, st.nseg, my_e) : 0] + row[my_e];
+        }
+        const int cnt = (int)min((int64_t)32, e1 - k0);
+#pragma unroll 4
+        for (int j = 0; j < cnt; ++j) {
+          const int e = __shfl_sync(0xffffffffu, my_e, j);
+          const int64_t src = __shfl_sync(0xffffffffu, my_src, j);
+          if (c < nvec) edge_value<T, VE, OP>(acc, in, edata, src, e, feat_dim, edata_dim, per, c * VE);
         }
       }
 #pragma unroll
@@ -500,7 +532,7 @@ k_spmm_long(const int64_t* __restrict__ row, const T* __restrict__ in, const T* 
         for (int t = 0; t < VE; ++t) {
           float v = 0.f;
 #pragma unroll
-          for (int w = 0; w < 8; ++w) v += part[w][lane][t];
+          for (int w = 0; w < kLongWarps; ++w) v += part[w][lane][t];
           o.v[t] = Elem<T>::from_f(v);
         }
         store_pack<T, VE>(out + d * feat_dim + c * VE, o);
@@ -525,7 +557,7 @@ static int launch_spmm(const int64_t* row, const int64_t* col, int64_t E, const 
   {
     ProfScope prof("spmm_long", s);
     const int grid = (int)std::min<int64_t>(E / kLongRow + 1, (int64_t)kNumSMs * 8);
-    APT_LAUNCH((k_spmm_long<T, VE, OP>), grid, 256, 0, s, row, in, edata, edata_dim, feat_dim, st, ws, out);
+    APT_LAUNCH((k_spmm_long<T, VE, OP>), grid, kLongWarps * 32, 0, s, row, in, edata, edata_dim, feat_dim, st, ws, out);
   }
   return APT_OK;
 }

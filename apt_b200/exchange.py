@@ -68,6 +68,12 @@ class LocalExchange:
         n = int(send_offset[-1]) * expand
         out.view(-1)[:n].copy_(inp.view(-1)[:n])
 
+    def allbroadcast(self, inp, recv_counts):
+        return inp.clone()
+
+    def reduce_scatter(self, inp, seg_sizes, my_rows):
+        return inp.clone()
+
 
 class NcclExchange:
     """Baseline: the collective library's all-to-all-v."""
@@ -116,6 +122,20 @@ class NcclExchange:
         send_counts, recv_counts = _counts(send_offset), _counts(recv_offset)
         res = self._a2a(inp.view(-1, expand)[: sum(send_counts)], send_counts, recv_counts, expand)
         out.view(-1)[: res.numel()].copy_(res.view(-1))
+
+    def allbroadcast(self, inp, recv_counts):
+        """Every rank's rows to every rank, in rank order (all-gather of blocks of
+        different lengths)."""
+        ws = self.state.world_size
+        n = inp.shape[0]
+        return self._a2a(inp.repeat(ws, 1), [n] * ws, [int(c) for c in recv_counts], inp.shape[1])
+
+    def reduce_scatter(self, inp, seg_sizes, my_rows):
+        """Segment r of every rank's rows summed on rank r."""
+        ws = self.state.world_size
+        counts = [int(c) for c in seg_sizes.tolist()]
+        buf = self._a2a(inp, counts, [int(my_rows)] * ws, inp.shape[1])
+        return buf.view(ws, int(my_rows), inp.shape[1]).float().sum(0).to(inp.dtype)
 
 
 class P2PExchange:
@@ -288,6 +308,44 @@ class P2PExchange:
         self._push(inp, None, 0, off_dev, rows_in, row_bytes)
         self._wait(counts_dev)
         self._pull(counts_dev, None, 0, total_out, total_out, row_bytes, out)
+
+    def allbroadcast(self, inp, recv_counts):
+        """Every rank's rows to every rank, in rank order: one push whose source
+        index repeats this rank's rows once per peer."""
+        st = self.state
+        ws = st.world_size
+        n, width = inp.shape
+        row_bytes = width * inp.element_size()
+        self._check_capacity(max([n] + [int(c) for c in recv_counts]), row_bytes)
+        index = torch.arange(n, device=inp.device).repeat(ws)
+        off_dev, _ = self._offsets_to_device(torch.arange(1, ws + 1, dtype=torch.int64) * n)
+        counts_dev = torch.empty(ws + 1, dtype=torch.int64, device=inp.device)
+        self._push(inp, index, 0, off_dev, n * ws, row_bytes)
+        self._wait(counts_dev)
+        total = int(sum(int(c) for c in recv_counts))
+        out = torch.empty((total, width), dtype=inp.dtype, device=inp.device)
+        self._pull(counts_dev, None, 0, total, total, row_bytes, out)
+        return out
+
+    def reduce_scatter(self, inp, seg_sizes, my_rows):
+        """Segment r of every rank's rows summed on rank r: the segments are pushed
+        into the owners' inboxes and one kernel there adds the world_size copies
+        in rank order."""
+        from .ops import _DTYPE_CODE
+
+        st = self.state
+        ws = st.world_size
+        width = inp.shape[1]
+        row_bytes = width * inp.element_size()
+        self._check_capacity(max(int(c) for c in seg_sizes.tolist()), row_bytes)
+        off_dev, _ = self._offsets_to_device(seg_sizes.cumsum(0))
+        counts_dev = torch.empty(ws + 1, dtype=torch.int64, device=inp.device)
+        self._push(inp, None, 0, off_dev, inp.shape[0], row_bytes)
+        self._wait(counts_dev)
+        out = torch.empty((int(my_rows), width), dtype=inp.dtype, device=inp.device)
+        check(lib.apt_p2p_pull_sum(self.ctx, _ptr(counts_dev), _DTYPE_CODE[inp.dtype], int(my_rows), width, _ptr(out),
+                                   st.status_ptr(), _stream()))
+        return out
 
     def close(self):
         if self.ctx is not None:

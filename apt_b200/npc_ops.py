@@ -22,6 +22,13 @@ _SCHEMAS = {
     "load_subtensor": "(Tensor node_id) -> Tensor",
     "local_sample_one_layer": "(Tensor seeds, int fanout) -> Tensor[]",
     "np_sample_and_shuffle": "(Tensor seeds, int fanout) -> Tensor[]",
+    "srcdst_to_vir": "(int fanout, Tensor dst, Tensor src) -> Tensor",
+    "src_to_vir": "(int fanout, int num_dst, Tensor src) -> Tensor",
+    "sp_sample_and_shuffle": "(int num_dst, Tensor send_frontier, Tensor sorted_allnodes, Tensor unique_frontier, int shuffle_with_dst) -> Tensor[]",
+    "sp_feat_shuffle": "(Tensor inputs, Tensor send_sizes, Tensor recv_sizes, int total_recv_size, int expand, int shuffle_with_dst) -> Tensor",
+    "mp_sample_shuffle": "(Tensor seeds, Tensor unique_frontier, Tensor coo_row) -> Tensor[]",
+    "mp_feat_shuffle_fwd": "(Tensor inputs, Tensor send_size, Tensor recv_size, int feat_dim) -> Tensor",
+    "mp_feat_shuffle_bwd": "(Tensor inputs, Tensor send_size, Tensor recv_size, int feat_dim) -> Tensor",
     "sp_sample_shuffle_src": "(Tensor unique_src) -> Tensor[]",
     "feat_shuffle": "(Tensor inputs, Tensor send_offset, Tensor recv_offset, Tensor permutation, int feat_dim, int fwd_flag) -> Tensor",
     "shuffle_seeds": "(Tensor seeds) -> (Tensor, Tensor, Tensor, Tensor)",
@@ -33,19 +40,12 @@ _SCHEMAS = {
     "sddmm_u_mul_v": "(Tensor coo_row, Tensor coo_col, Tensor lhs, Tensor rhs, Tensor coo_offset, Tensor lhs_offset, Tensor rhs_offset) -> Tensor",
 }
 
-# Registered by the reference for the SNP virtual-node, NFP and multi-machine
-# strategies (src/pybind.cc:25,28-29,31-32,34,36,38-40); not part of this path.
+# Registered by the reference for several machines (src/pybind.cc:25,28-29);
+# not part of this path.
 _NOT_BUILT = {
     "register_multi_machines_scheme": "(Tensor remote_worker_map, Tensor remote_worker_id) -> ()",
     "crossmachine_load_subtensor": "(Tensor node_id) -> Tensor",
     "cluster_reqs": "(Tensor node_id) -> (Tensor, Tensor, Tensor)",
-    "srcdst_to_vir": "(int fanout, Tensor dst, Tensor src) -> Tensor",
-    "src_to_vir": "(int fanout, int num_dst, Tensor src) -> Tensor",
-    "sp_sample_and_shuffle": "(int num_dst, Tensor send_frontier, Tensor sorted_allnodes, Tensor unique_frontier, int shuffle_with_dst) -> Tensor[]",
-    "mp_sample_shuffle": "(Tensor seeds, Tensor unique_frontier, Tensor coo_row) -> Tensor[]",
-    "sp_feat_shuffle": "(Tensor inputs, Tensor send_sizes, Tensor recv_sizes, int total_recv_size, int expand, int shuffle_with_dst) -> Tensor",
-    "mp_feat_shuffle_fwd": "(Tensor inputs, Tensor send_size, Tensor recv_size, int feat_dim) -> Tensor",
-    "mp_feat_shuffle_bwd": "(Tensor inputs, Tensor send_size, Tensor recv_size, int feat_dim) -> Tensor",
 }
 
 _LIB = torch.library.Library("npc", "DEF")

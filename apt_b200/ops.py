@@ -170,6 +170,7 @@ def _flag_text(flags):
         _lib.FLAG_TABLE_FULL: "workspace or inbox region too small",
         _lib.FLAG_PEER_TIMEOUT: "a peer's data did not arrive in time",
         _lib.FLAG_NOT_GROUPED: "edges of a block are not grouped by destination",
+        _lib.FLAG_SIZE_MISMATCH: "a peer sent another number of rows than the reduction expects",
     }
     return ", ".join(v for k, v in names.items() if flags & k)
 
@@ -438,6 +439,187 @@ def np_sample_and_shuffle(seeds: torch.Tensor, fanout: int) -> List[torch.Tensor
 def sp_sample_shuffle_src(unique_src: torch.Tensor) -> List[torch.Tensor]:
     """SPSampleShuffleSrc, src/sampling.cc:151-157."""
     return list(shuffle_seeds(unique_src))
+
+
+# ------------------------------------------------- SNP virtual nodes (SAGE / GCN)
+SP_BASE = 10_000_000   # python/npc/sampler.py:181: virtual node = sender * SP_BASE + destination index
+
+
+def _owner_args():
+    s = STATE
+    if s.shuffle_min_vids is None:
+        raise RuntimeError("register_min_vids has not been called")
+    node_beg = s.rank - s.rank % s.node_size
+    return _ptr(s.shuffle_min_vids), s.world_size, int(s.shuffle_id_offset), s.rank, node_beg, node_beg + s.node_size
+
+
+def src_to_vir(fanout: int, num_dst: int, src: torch.Tensor) -> torch.Tensor:
+    """SrcToVir, src/sampling.cc:19-34: owner(src[i]) * num_dst + i // fanout."""
+    src = _need_cuda(src, "src")
+    out = torch.empty_like(src)
+    check(lib.apt_src_to_vir(_ptr(src), src.numel(), int(fanout), int(num_dst), *_owner_args(), _ptr(out), _stream()))
+    return out
+
+
+def srcdst_to_vir(fanout: int, dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
+    """SrcDsttoVir, src/sampling.cc:36-50: destinations first, then the
+    neighbours shifted by world_size * num_dst."""
+    dst = _need_cuda(dst, "dst")
+    src = _need_cuda(src, "src")
+    out = torch.empty(dst.numel() + src.numel(), dtype=torch.int64, device=src.device)
+    check(lib.apt_srcdst_to_vir(_ptr(dst), dst.numel(), _ptr(src), src.numel(), int(fanout), *_owner_args(),
+                                _ptr(out), _stream()))
+    return out
+
+
+def vir_send_sizes(num_seeds: int, sorted_allnodes: torch.Tensor, unique_frontier: torch.Tensor,
+                   shuffle_with_dst: int, with_offsets: bool = False):
+    """Device tensor of the k = 2 (3 with destinations) sizes per receiver that
+    SPSampleAndShuffle exchanges (src/sampling.cc:86-106)."""
+    ws = STATE.world_size
+    k = 3 if shuffle_with_dst else 2
+    sizes = torch.empty(k * ws, dtype=torch.int64, device=sorted_allnodes.device)
+    offs = torch.empty(k * ws + 1, dtype=torch.int64, device=sorted_allnodes.device) if with_offsets else None
+    check(lib.apt_vir_send_sizes(_ptr(sorted_allnodes), sorted_allnodes.numel(), _ptr(unique_frontier),
+                                 unique_frontier.numel(), None, ws, int(num_seeds), int(bool(shuffle_with_dst)),
+                                 _ptr(offs), _ptr(sizes), _stream()))
+    return (sizes, offs) if with_offsets else sizes
+
+
+def sp_pack_frontier(sorted_vir: torch.Tensor, sorted_ids: torch.Tensor, num_dst: int) -> torch.Tensor:
+    """rank * SP_BASE * N + (sorted_vir % num_dst) * N + sorted_ids, the packed
+    (sender, destination index, neighbour id) of python/npc/sampler.py:296-300."""
+    out = torch.empty_like(sorted_ids)
+    check(lib.apt_sp_pack_frontier(_ptr(sorted_vir), _ptr(sorted_ids), sorted_ids.numel(), int(num_dst), STATE.rank,
+                                   SP_BASE, int(STATE.graph.num_total_nodes), _ptr(out), _stream()))
+    return out
+
+
+def _cumsum_cpu(sizes: torch.Tensor) -> torch.Tensor:
+    return sizes.cumsum(0) if sizes.numel() else sizes
+
+
+def sp_sample_and_shuffle(num_dst: int, send_frontier: torch.Tensor, sorted_allnodes: torch.Tensor,
+                          unique_frontier: torch.Tensor, shuffle_with_dst: int) -> List[torch.Tensor]:
+    """SPSampleAndShuffle, src/sampling.cc:71-149: [vir_src, ori_src, send_sizes,
+    recv_sizes] or, with destinations, [recv_dst, vir_src, ori_src, send_sizes,
+    recv_sizes]; the size vectors are CPU int64 as in the reference."""
+    send_frontier = _need_cuda(send_frontier, "send_frontier")
+    sorted_allnodes = _need_cuda(sorted_allnodes, "sorted_allnodes")
+    unique_frontier = _need_cuda(unique_frontier, "unique_frontier")
+    s = STATE
+    ws = s.world_size
+    with_dst = int(bool(shuffle_with_dst))
+    k = 3 if with_dst else 2
+    ex = _exchange()
+    send_sizes_dev = vir_send_sizes(num_dst, sorted_allnodes, unique_frontier, with_dst)
+    recv_sizes_dev = torch.empty_like(send_sizes_dev)
+    steps = torch.arange(1, ws + 1, dtype=torch.int64) * k
+    ex.alltoall(send_sizes_dev, recv_sizes_dev, steps, steps, 1)
+    both = torch.stack([send_sizes_dev, recv_sizes_dev]).cpu()
+    send_sizes, recv_sizes = both[0].contiguous(), both[1].contiguous()
+    n_total = int(s.graph.num_total_nodes)
+    dev = send_frontier.device
+    if with_dst:
+        sd, rd = send_sizes[0::3], recv_sizes[0::3]
+        ss, rs = send_sizes[1::3], recv_sizes[1::3]
+        n_sd, n_rd, n_rs = int(sd.sum()), int(rd.sum()), int(rs.sum())
+        recv_all = torch.empty(n_rd + n_rs, dtype=torch.int64, device=dev)
+        ex.alltoall(send_frontier[:n_sd], recv_all[:n_rd], _cumsum_cpu(sd), _cumsum_cpu(rd), 1)
+        ex.alltoall(send_frontier[n_sd:], recv_all[n_rd:], _cumsum_cpu(ss), _cumsum_cpu(rs), 1)
+        recv_src = recv_all[n_rd:]
+    else:
+        ss, rs = send_sizes[0::2], recv_sizes[0::2]
+        n_rs = int(rs.sum())
+        recv_src = torch.empty(n_rs, dtype=torch.int64, device=dev)
+        ex.alltoall(send_frontier, recv_src, _cumsum_cpu(ss), _cumsum_cpu(rs), 1)
+    vir_src = torch.empty(n_rs, dtype=torch.int64, device=dev)
+    ori_src = torch.empty(n_rs, dtype=torch.int64, device=dev)
+    check(lib.apt_sp_unpack_frontier(_ptr(recv_src), n_rs, None, n_total, _ptr(vir_src), _ptr(ori_src), _stream()))
+    if with_dst:
+        return [recv_all[:n_rd], vir_src, ori_src, send_sizes, recv_sizes]
+    return [vir_src, ori_src, send_sizes, recv_sizes]
+
+
+def sp_feat_shuffle(inputs: torch.Tensor, send_sizes: torch.Tensor, recv_sizes: torch.Tensor, total_recv_size: int,
+                    expand: int, shuffle_with_dst: int) -> torch.Tensor:
+    """SPFeatShuffle, src/feat_shuffle.cc:32-52: rows of `expand` elements; per
+    peer q the last of its k sizes (partial sums per virtual node), preceded,
+    with destinations, by sizes[3 q] destination rows for every q."""
+    if inputs.dtype not in _DTYPE_CODE:
+        raise RuntimeError(f"sp_feat_shuffle: unsupported dtype {inputs.dtype}")
+    inputs = _need_cuda(inputs, "inputs", dtype=None)
+    expand = int(expand)
+    rows = inputs.numel() // expand
+    flat = inputs.view(rows, expand)
+    out = torch.empty((int(total_recv_size), expand), dtype=inputs.dtype, device=inputs.device)
+    send_sizes, recv_sizes = send_sizes.cpu(), recv_sizes.cpu()
+    ex = _exchange()
+    if shuffle_with_dst:
+        sd, rd = send_sizes[0::3], recv_sizes[0::3]
+        sv, rv = send_sizes[2::3], recv_sizes[2::3]
+        n_sd, n_rd = int(sd.sum()), int(rd.sum())
+        if n_sd + int(sv.sum()) != rows or n_rd + int(rv.sum()) != int(total_recv_size):
+            raise RuntimeError("sp_feat_shuffle: sizes do not add up to the rows given")
+        ex.alltoall(flat[:n_sd], out[:n_rd], _cumsum_cpu(sd), _cumsum_cpu(rd), expand)
+        ex.alltoall(flat[n_sd:], out[n_rd:], _cumsum_cpu(sv), _cumsum_cpu(rv), expand)
+    else:
+        sv, rv = send_sizes[1::2], recv_sizes[1::2]
+        if int(sv.sum()) != rows or int(rv.sum()) != int(total_recv_size):
+            raise RuntimeError("sp_feat_shuffle: sizes do not add up to the rows given")
+        ex.alltoall(flat, out, _cumsum_cpu(sv), _cumsum_cpu(rv), expand)
+    return out
+
+
+# ------------------------------------------- NFP (feature dimension partitioned)
+def mp_sample_shuffle(seeds: torch.Tensor, unique_frontier: torch.Tensor, coo_row: torch.Tensor) -> List[torch.Tensor]:
+    """MPSampleShuffle, src/sampling.cc:195-239: every rank receives every
+    rank's frontier and relabelled rows. [recv_frontier, recv_coo_row,
+    [seeds_size] (cpu), recv_seeds_size (cpu), recv_frontier_size (cpu),
+    recv_coo_size (cpu)]."""
+    unique_frontier = _need_cuda(unique_frontier, "unique_frontier")
+    coo_row = _need_cuda(coo_row, "coo_row")
+    ws = STATE.world_size
+    ex = _exchange()
+    mine = torch.tensor([[seeds.numel(), unique_frontier.numel(), coo_row.numel()]], dtype=torch.int64,
+                        device=unique_frontier.device)
+    sizes = ex.allbroadcast(mine, [1] * ws).cpu()                       # [ws, 3]
+    recv_seeds_size = sizes[:, 0].contiguous()
+    recv_frontier_size = sizes[:, 1].contiguous()
+    recv_coo_size = sizes[:, 2].contiguous()
+    recv_frontier = ex.allbroadcast(unique_frontier.view(-1, 1), recv_frontier_size.tolist()).view(-1)
+    recv_coo_row = ex.allbroadcast(coo_row.view(-1, 1), recv_coo_size.tolist()).view(-1)
+    return [recv_frontier, recv_coo_row, torch.tensor([seeds.numel()]), recv_seeds_size, recv_frontier_size,
+            recv_coo_size]
+
+
+def mp_feat_shuffle_fwd(inputs: torch.Tensor, send_size: torch.Tensor, recv_size: torch.Tensor,
+                        feat_dim: int) -> torch.Tensor:
+    """MPFeatShuffleFwd, src/feat_shuffle.cc:54-64 (a reduce-scatter): rows
+    [off[r], off[r] + send_size[r]) of every rank's inputs are summed on rank r,
+    which gets recv_size rows. The sum runs over the ranks in rank order in fp32."""
+    if inputs.dtype not in _DTYPE_CODE:
+        raise RuntimeError(f"mp_feat_shuffle_fwd: unsupported dtype {inputs.dtype}")
+    inputs = _need_cuda(inputs, "inputs", dtype=None)
+    feat_dim = int(feat_dim)
+    flat = inputs.view(inputs.numel() // feat_dim, feat_dim)
+    send_size = send_size.cpu().to(torch.int64).view(-1)
+    mine = int(recv_size.view(-1)[0])
+    if int(send_size.sum()) != flat.shape[0] or int(send_size[STATE.rank]) != mine:
+        raise RuntimeError("mp_feat_shuffle_fwd: sizes do not match the rows given")
+    return _exchange().reduce_scatter(flat, send_size, mine)
+
+
+def mp_feat_shuffle_bwd(inputs: torch.Tensor, send_size: torch.Tensor, recv_size: torch.Tensor,
+                        feat_dim: int) -> torch.Tensor:
+    """MPFeatShuffleBwd, src/feat_shuffle.cc:66-79 (an all-gather of blocks of
+    different lengths): every rank receives every rank's rows in rank order."""
+    inputs = _need_cuda(inputs, "inputs", dtype=None)
+    feat_dim = int(feat_dim)
+    flat = inputs.view(inputs.numel() // feat_dim, feat_dim)
+    if int(send_size.view(-1)[0]) != flat.shape[0]:
+        raise RuntimeError("mp_feat_shuffle_bwd: send_size does not match the rows given")
+    return _exchange().allbroadcast(flat, [int(x) for x in recv_size.view(-1).tolist()])
 
 
 # ---------------------------------------------------------------------- gather

@@ -279,6 +279,132 @@ class SPGATSampler:
         return seeds, output_nodes, blocks, perm, send_offset, recv_offset
 
 
+class SPVirtualSampler:
+    """SNP strategy with a SAGE or GCN model (MixedPSNeighborSampler with system
+    "SP", python/npc/sampler.py:240-330). Inner hops as in GDP. In the outermost
+    hop each sampled neighbour becomes a virtual node (owner, local destination):
+    block1 joins the sorted unique virtual nodes to the local destinations, the
+    packed triples (sender, destination index, neighbour id) travel to the
+    neighbour's owner, and block2 there joins the received neighbours to the
+    received virtual nodes, so that the owner sums its rows per virtual node
+    before anything crosses a link (sp_feat_shuffle carries the partial sums).
+
+    The reference sorts the virtual ids with torch.sort, which leaves equal keys
+    in any order; here the order is the stable one, given by the owner bucketing
+    (virtual ids rise with the position inside one owner's bucket).
+
+    Returns (input_nodes, output_nodes, blocks, send_sizes, recv_sizes); blocks =
+    [block2, block1, inner blocks...]. block2.src_ids are the unique received
+    neighbours, its destinations the sorted unique received virtual nodes
+    (`self.last["unique_dst"]`)."""
+
+    def __init__(self, rank: int, fanouts: List[int], model: str = "SAGE", shuffle_with_dst: bool = False):
+        if model not in ("SAGE", "GCN"):
+            raise ValueError("SPVirtualSampler serves SAGE and GCN; GAT uses SPGATSampler")
+        self.rank = rank
+        self.fanouts = list(fanouts)
+        self.model = model
+        self.shuffle_with_dst = bool(shuffle_with_dst)
+        self.last = {}
+
+    def _outer(self, seeds, neighbors, fanout):
+        st = ops.STATE
+        ws = st.world_size
+        num_dst = seeds.numel()
+        dev = seeds.device
+        n_total = st.graph.num_total_nodes
+        nbr_sorted, nbr_pos, _, _ = ops._bucket(neighbors)        # neighbours grouped by owner, input order kept
+        if self.shuffle_with_dst:
+            map_all = ops.srcdst_to_vir(fanout, seeds, neighbors)
+            dst_sorted, dst_pos, _, _ = ops._bucket(seeds)
+            pos = torch.cat((dst_pos, nbr_pos + num_dst))
+            sorted_all = ops.rows_scatter(map_all.view(-1, 1), pos, pos.numel()).view(-1)
+            map_src = sorted_all[num_dst:]
+            lo = ws * num_dst
+        else:
+            map_all = ops.src_to_vir(fanout, num_dst, neighbors)
+            sorted_all = ops.rows_scatter(map_all.view(-1, 1), nbr_pos, nbr_pos.numel()).view(-1)
+            map_src = sorted_all
+            lo = 0
+        unique_frontier, _ = ops.unique_sorted(map_src, lo, lo + ws * max(num_dst, 1))
+        arange_dst = unique_frontier % max(num_dst, 1)
+        arange_src = torch.arange(unique_frontier.numel(), device=dev)
+        block1 = Block(arange_src, arange_dst, unique_frontier.numel(), num_dst, unique_frontier, fanout)
+        packed = ops.sp_pack_frontier(map_src, nbr_sorted, num_dst)
+        if self.shuffle_with_dst:
+            send_frontier = torch.cat((dst_sorted, packed))
+            recv_dst, recv_seeds, recv_neighbors, send_sizes, recv_sizes = ops.sp_sample_and_shuffle(
+                num_dst, send_frontier, sorted_all, unique_frontier, 1)
+        else:
+            recv_dst = None
+            recv_seeds, recv_neighbors, send_sizes, recv_sizes = ops.sp_sample_and_shuffle(
+                num_dst, packed, sorted_all, unique_frontier, 0)
+        own_lo, own_hi = ops._owned_range()
+        unique_src, a_src = ops.unique_sorted(recv_neighbors, own_lo, own_hi)
+        unique_dst, a_dst = ops.unique_sorted(recv_seeds, 0, ws * ops.SP_BASE)
+        block2 = Block(a_src, a_dst, unique_src.numel(), unique_dst.numel(), unique_src, fanout)
+        self.last = dict(neighbors=neighbors, sorted_allnodes=sorted_all, unique_frontier=unique_frontier,
+                         send_frontier=send_frontier if self.shuffle_with_dst else packed, recv_dst=recv_dst,
+                         vir_src=recv_seeds, ori_src=recv_neighbors, unique_dst=unique_dst)
+        if self.shuffle_with_dst:
+            nxt = torch.cat((recv_dst, unique_src))
+        elif self.model == "GCN":
+            nxt = unique_src
+        else:
+            nxt = torch.cat((seeds, unique_src))
+        return nxt, block1, block2, send_sizes, recv_sizes
+
+    def sample(self, graph, seeds: torch.Tensor):
+        output_nodes = seeds
+        blocks = []
+        for layer_id, fanout in enumerate(reversed(self.fanouts)):
+            seeds, neighbors = ops.local_sample_one_layer(seeds, fanout)
+            if layer_id != len(self.fanouts) - 1:
+                block = create_block(seeds, neighbors, fanout)
+                seeds = block.src_ids
+                blocks.insert(0, block)
+                continue
+            seeds, block1, block2, send_sizes, recv_sizes = self._outer(seeds, neighbors, fanout)
+            blocks.insert(0, block1)
+            blocks.insert(0, block2)
+        return seeds, output_nodes, blocks, send_sizes, recv_sizes
+
+
+class MPSampler:
+    """NFP strategy with a SAGE or GCN model (MixedPSNeighborSampler with system
+    "MP", python/npc/sampler.py:332-356): every rank holds a slice of the feature
+    columns of all nodes. Inner hops as in GDP; in the outermost hop every rank
+    relabels its own block and then receives every rank's frontier and relabelled
+    rows, so that it can aggregate its column slice for all ranks' destinations
+    (multi-segment spmm_copy_u_sum) before mp_feat_shuffle_fwd sums the slices.
+
+    Returns (input_nodes, output_nodes, blocks, send_size, recv_size); blocks[0] =
+    (all_coo_row, all_coo_col, recv_frontier_size, recv_coo_size, recv_size) as in
+    the reference, input_nodes = the concatenation of all ranks' frontiers."""
+
+    def __init__(self, rank: int, fanouts: List[int]):
+        self.rank = rank
+        self.fanouts = list(fanouts)
+
+    def sample(self, graph, seeds: torch.Tensor):
+        output_nodes = seeds
+        blocks = []
+        for layer_id, fanout in enumerate(reversed(self.fanouts)):
+            seeds, neighbors = ops.local_sample_one_layer(seeds, fanout)
+            if layer_id != len(self.fanouts) - 1:
+                block = create_block(seeds, neighbors, fanout)
+                seeds = block.src_ids
+                blocks.insert(0, block)
+                continue
+            unique_frontier, coo_row = ops.relabel_csc(seeds, neighbors)
+            all_frontier, all_coo_row, send_size, recv_size, recv_frontier_size, recv_coo_size = \
+                ops.mp_sample_shuffle(seeds, unique_frontier, coo_row)
+            all_coo_col = torch.cat([_coo_col(int(i), int(i), fanout, all_coo_row.device) for i in recv_size])
+            blocks.insert(0, (all_coo_row, all_coo_col, recv_frontier_size, recv_coo_size, recv_size))
+            seeds = all_frontier
+        return seeds, output_nodes, blocks, send_size, recv_size
+
+
 class DPNeighborSampler:
     """GDP strategy: every hop local (python/npc/sampler.py:202-203 with the
     common block construction)."""

@@ -278,6 +278,7 @@ def stage_ops(args):
     time per call (CUDA events) and algorithmic GB/s against the measured HBM peak."""
     import apt_b200  # noqa: F401
     from apt_b200 import ops, synthetic
+    from apt_b200._lib import lib
 
     torch.cuda.set_device(0)
     w = synthetic.WORKLOADS["c0_small_np"]
@@ -289,7 +290,15 @@ def stage_ops(args):
     peak, peak_kind = peaks()
     results = {}
 
-    def timed(name, fn, algo_bytes, fresh=None):
+    def read_tags(tags):
+        out = {}
+        for tag in tags:
+            t_, k_ = ctypes.c_double(), ctypes.c_int64()
+            lib.apt_profile_read(tag.encode(), ctypes.byref(t_), ctypes.byref(k_))
+            out[tag] = round(1e6 * t_.value / max(k_.value, 1), 2)
+        return out
+
+    def timed(name, fn, algo_bytes, fresh=None, tags=()):
         for _ in range(args.warmup):
             fn(fresh() if fresh else None)
         inputs = [fresh() if fresh else None for _ in range(args.steps)]
@@ -306,6 +315,14 @@ def stage_ops(args):
         gbs = algo_bytes / (ms * 1e-3) / 1e9
         results[name] = {"us": round(1000 * ms, 2), "algorithmic_mb": round(algo_bytes / 1e6, 2),
                          "gbs": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4)}
+        if tags:   # a second, untimed pass with an event pair around each launch group
+            ops.profile_enable(True)
+            read_tags(tags)
+            for x in inputs[:5]:
+                fn(x)
+            torch.cuda.synchronize()
+            ops.profile_enable(False)
+            results[name]["launch_groups_us"] = read_tags(tags)
 
     def seeds():
         return torch.randint(0, n, (S,), generator=g, device="cuda")
@@ -326,16 +343,19 @@ def stage_ops(args):
     n_src, E = uniq.numel(), rel.numel()
     col = torch.arange(S, device="cuda").repeat_interleave(f)
     off = [torch.tensor(v, device="cuda") for v in ([0, E], [0, n_src], [0, S])]
+    spmm_tags = ("spmm_ranges", "spmm_group", "spmm_rows", "spmm_long")
     for dt, name in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
         D = 256
         x = torch.randn((n_src, D), generator=g, device="cuda").to(dt)
         esz = x.element_size()
         ws = ops.STATE.workspace("spmm", 1)
         timed(f"spmm_copy_u_sum {name} D=256 (1.01 M edges, grouped)",
-              lambda _: ops._spmm(0, rel, col, x, None, off[0], off[1], off[2]), E * (16 + D * esz) + S * D * esz)
+              lambda _: ops._spmm(0, rel, col, x, None, off[0], off[1], off[2]), E * (16 + D * esz) + S * D * esz,
+              tags=spmm_tags)
         gsd = torch.randn((S, D), generator=g, device="cuda").to(dt)
         timed(f"spmm_copy_u_sum {name} D=256 backward shape (scattered)",
-              lambda _: ops._spmm(0, col, rel, gsd, None, off[0], off[2], off[1]), E * (16 + D * esz) + n_src * D * esz)
+              lambda _: ops._spmm(0, col, rel, gsd, None, off[0], off[2], off[1]), E * (16 + D * esz) + n_src * D * esz,
+              tags=spmm_tags)
     el = torch.randn((n_src, 4), generator=g, device="cuda")
     er = torch.randn((S, 4), generator=g, device="cuda")
     timed("sddmm_u_add_v f32 D=4 (GAT scores)", lambda _: ops.sddmm_u_add_v(rel, col, el, er, *off), E * (16 + 3 * 4 * 4))

@@ -53,6 +53,7 @@ typedef enum apt_dtype { APT_F32 = 0, APT_BF16 = 1, APT_F16 = 2 } apt_dtype;
 #define APT_FLAG_TABLE_FULL      8  /* relabel hash table overflow (workspace too small) */
 #define APT_FLAG_PEER_TIMEOUT    16 /* a peer's flag did not arrive in time */
 #define APT_FLAG_NOT_GROUPED     32 /* a block operator got edges not grouped by destination */
+#define APT_FLAG_SIZE_MISMATCH   64 /* a peer sent another number of rows than the reduction expects */
 
 const char* apt_last_error(void);
 int apt_version(void);
@@ -296,6 +297,52 @@ int apt_gat_edge_softmax_sum(int dtype, const int64_t* coo_row,
                              size_t workspace_bytes, int32_t* status_word,
                              void* stream);
 
+/* ------------------------------------------- SNP virtual nodes (SAGE / GCN)
+ * The id arithmetic of the SNP strategy with virtual nodes: neighbour i of
+ * local destination i / fanout, owned by rank o, becomes the virtual node
+ * o * num_dst + i / fanout.
+ *
+ * apt_src_to_vir      MapSrctoVir (src/cuda/npc_kernel.cu:71-117; SrcToVir,
+ *                     src/sampling.cc:19-34): out_vir[num_src].
+ * apt_srcdst_to_vir   MapSrcDsttoVir (src/cuda/npc_kernel.cu:15-70; SrcDsttoVir,
+ *                     src/sampling.cc:36-50): out_vir[num_dst + num_src],
+ *                     destinations first (owner * num_dst + index), neighbours
+ *                     shifted by world_size * num_dst.
+ * apt_vir_send_sizes  GetVirSendOffset / GetVirSendOffsetWithDst
+ *                     (src/cuda/npc_kernel.cu:119-183) and the size vector
+ *                     SPSampleAndShuffle derives from them (src/sampling.cc:86-106,
+ *                     permutations of src/core.cc:80-95). out_send_offset (may be
+ *                     null): int64[(with_dst ? 3 : 2) * world_size + 1] lower bounds;
+ *                     out_send_sizes: per receiver r (ids, unique virtual nodes) or
+ *                     (destinations, ids, unique virtual nodes) bound for r.
+ *                     num_unique_dev (may be null) overrides num_unique on the device.
+ * apt_sp_pack_frontier   out[i] = rank * sp_base * num_total_nodes
+ *                     + (sorted_vir[i] % num_dst) * num_total_nodes + sorted_ids[i],
+ *                     the packed triple of python/npc/sampler.py:296-300.
+ * apt_sp_unpack_frontier out_vir = packed / num_total_nodes, out_ori = packed %
+ *                     num_total_nodes (src/sampling.cc:128-129, :141-142).
+ * The owner function and its arguments are those of apt_bucket_by_owner.
+ */
+int apt_src_to_vir(const int64_t* src, int64_t num_src, int64_t fanout,
+                   int64_t num_dst, const int64_t* min_vids, int world_size,
+                   int shuffle_id_offset, int rank, int node_beg, int node_end,
+                   int64_t* out_vir, void* stream);
+int apt_srcdst_to_vir(const int64_t* dst, int64_t num_dst, const int64_t* src,
+                      int64_t num_src, int64_t fanout, const int64_t* min_vids,
+                      int world_size, int shuffle_id_offset, int rank,
+                      int node_beg, int node_end, int64_t* out_vir, void* stream);
+int apt_vir_send_sizes(const int64_t* sorted_nodes, int64_t num_sorted,
+                       const int64_t* unique_nodes, int64_t num_unique,
+                       const int64_t* num_unique_dev, int world_size,
+                       int64_t base, int with_dst, int64_t* out_send_offset,
+                       int64_t* out_send_sizes, void* stream);
+int apt_sp_pack_frontier(const int64_t* sorted_vir, const int64_t* sorted_ids,
+                         int64_t n, int64_t num_dst, int rank, int64_t sp_base,
+                         int64_t num_total_nodes, int64_t* out, void* stream);
+int apt_sp_unpack_frontier(const int64_t* packed, int64_t n, const int64_t* n_dev,
+                           int64_t num_total_nodes, int64_t* out_vir,
+                           int64_t* out_ori, void* stream);
+
 /* ------------------------------------------------------- local row movers
  * out[i] = in[index[i]] and out[index[i]] = in[i] over rows of row_bytes
  * bytes (16-byte vectors when alignment allows). These are the index_select /
@@ -370,6 +417,15 @@ int apt_p2p_pull(apt_p2p* ctx, const int64_t* recv_counts,
                  const int64_t* dst_index, int index_is_source,
                  int64_t num_dst_rows, int64_t max_rows, int64_t row_bytes,
                  void* dst, void* stream);
+/* Reduce-scatter epilogue, the receiving half of _AllReduce (one ncclReduce per
+ * root, src/ops/collective.cc:404-436) behind MPFeatShuffleFwd
+ * (src/feat_shuffle.cc:54-64): after a push in which every rank sent its partial
+ * rows for this rank's segment, dst[num_rows x row_elems] = the sum over the
+ * peers in rank order (fp32 accumulator; dtype APT_F32 / APT_BF16 / APT_F16).
+ * A peer that sent another row count is left out and APT_FLAG_SIZE_MISMATCH set. */
+int apt_p2p_pull_sum(apt_p2p* ctx, const int64_t* recv_counts, int dtype,
+                     int64_t num_rows, int64_t row_elems, void* dst,
+                     int32_t* status_word, void* stream);
 
 /* The same all-to-all as push + wait + pull, as ONE cooperative kernel in which
  * the local pass (moving received rows to their final place) overlaps the

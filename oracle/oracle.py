@@ -419,6 +419,219 @@ def sp_gat_sample(seeds_per_rank, fanout, min_vids, graph, key, call_id):
     return res
 
 
+# --------------------------------------- SNP with virtual nodes (SAGE / GCN)
+def src_to_vir(src, fanout, num_dst, min_vids, world_size, shuffle_id_offset=0, rank=0, node_beg=0, node_end=None):
+    """MapSrctoVir, src/cuda/npc_kernel.cu:71-117 (SrcToVir, src/sampling.cc:19-34):
+    neighbour i of destination i // fanout becomes owner * num_dst + i // fanout."""
+    src = np.asarray(src, dtype=I64)
+    own = owner_of(src, min_vids, world_size, shuffle_id_offset, rank, node_beg, node_end)
+    return own * I64(num_dst) + np.arange(len(src), dtype=I64) // I64(fanout)
+
+
+def srcdst_to_vir(dst, src, fanout, min_vids, world_size, shuffle_id_offset=0, rank=0, node_beg=0, node_end=None):
+    """MapSrcDsttoVir, src/cuda/npc_kernel.cu:15-70 (SrcDsttoVir, src/sampling.cc:36-50):
+    destinations first (owner * num_dst + index), then the neighbours shifted by
+    world_size * num_dst."""
+    dst = np.asarray(dst, dtype=I64)
+    src = np.asarray(src, dtype=I64)
+    num_dst = I64(len(dst))
+    od = owner_of(dst, min_vids, world_size, shuffle_id_offset, rank, node_beg, node_end)
+    os_ = owner_of(src, min_vids, world_size, shuffle_id_offset, rank, node_beg, node_end)
+    return np.concatenate([od * num_dst + np.arange(len(dst), dtype=I64),
+                           os_ * num_dst + I64(world_size) * num_dst + np.arange(len(src), dtype=I64) // I64(fanout)])
+
+
+def vir_send_offset(world_size, base, sorted_nodes, unique_nodes, with_dst):
+    """GetVirSendOffset / GetVirSendOffsetWithDst, src/cuda/npc_kernel.cu:119-183:
+    lower bounds of base * i in the sorted virtual ids (i in [0, k ws], k = 2 with
+    destinations else 1), then in their sorted unique values for the last ws of
+    those search values."""
+    k = 2 if with_dst else 1
+    vals = I64(base) * np.arange(k * world_size + 1, dtype=I64)
+    first = np.searchsorted(np.asarray(sorted_nodes, dtype=I64), vals, side="left")
+    second = np.searchsorted(np.asarray(unique_nodes, dtype=I64), vals[(k - 1) * world_size + 1:], side="left")
+    return np.concatenate([first, second]).astype(I64)
+
+
+def vir_send_sizes(world_size, base, sorted_nodes, unique_nodes, with_dst):
+    """The size vector SPSampleAndShuffle derives from those offsets,
+    src/sampling.cc:86-106 with the permutations of src/core.cc:80-95: per
+    receiver r, (ids, unique virtual nodes) or (destinations, ids, unique
+    virtual nodes) bound for r."""
+    k = 3 if with_dst else 2
+    off = vir_send_offset(world_size, base, sorted_nodes, unique_nodes, with_dst)
+    fir_uni = off[(k - 1) * world_size + 1]
+    sizes = np.diff(off)
+    sizes[(k - 1) * world_size] = fir_uni
+    permute = np.array([i * world_size + r for r in range(world_size) for i in range(k)], dtype=I64)
+    return sizes[permute].astype(I64)
+
+
+def sp_sample_and_shuffle(num_seeds_pr, send_frontier_pr, sorted_pr, unique_pr, with_dst, num_total_nodes):
+    """SPSampleAndShuffle, src/sampling.cc:71-149, with the size exchange
+    (AlltoAll of k values per peer) and SPSampleAlltoAll(WithDst),
+    src/ops/collective.cc:38-133, for all ranks at once. Per rank: dict(recv_dst
+    (with destinations only), vir_src, ori_src, send_sizes, recv_sizes)."""
+    ws = len(send_frontier_pr)
+    k = 3 if with_dst else 2
+    send_sizes = [vir_send_sizes(ws, num_seeds_pr[r], sorted_pr[r], unique_pr[r], with_dst) for r in range(ws)]
+    recv_sizes = [np.concatenate([send_sizes[q][k * r:k * r + k] for q in range(ws)]) for r in range(ws)]
+    out = []
+    for r in range(ws):
+        parts_dst, parts_src = [], []
+        for q in range(ws):
+            sz = send_sizes[q]
+            fr = np.asarray(send_frontier_pr[q], dtype=I64)
+            if with_dst:
+                d0 = int(sz[0:3 * r:3].sum())
+                parts_dst.append(fr[d0:d0 + int(sz[3 * r])])
+                s0 = int(sz[0::3].sum()) + int(sz[1:3 * r:3].sum())
+                parts_src.append(fr[s0:s0 + int(sz[3 * r + 1])])
+            else:
+                s0 = int(sz[0:2 * r:2].sum())
+                parts_src.append(fr[s0:s0 + int(sz[2 * r])])
+        recv_src = np.concatenate(parts_src) if parts_src else np.zeros(0, dtype=I64)
+        res = dict(vir_src=recv_src // I64(num_total_nodes), ori_src=recv_src % I64(num_total_nodes),
+                   send_sizes=send_sizes[r], recv_sizes=recv_sizes[r])
+        if with_dst:
+            res["recv_dst"] = np.concatenate(parts_dst)
+        out.append(res)
+    return out
+
+
+def sp_feat_shuffle(inputs_pr, send_sizes_pr, recv_sizes_pr, with_dst):
+    """SPFeatShuffle, src/feat_shuffle.cc:32-52 over SPFeatureAlltoAll(WithDst),
+    src/ops/collective.cc:135-212: rank r sends send_sizes[k q + k - 1] rows to q
+    (after, with destinations, send_sizes[3 q] destination rows to every q) and
+    receives in sender order. Returns the received rows per rank."""
+    ws = len(inputs_pr)
+    k = 3 if with_dst else 2
+    out = []
+    for r in range(ws):
+        parts = []
+        passes = (0, 2) if with_dst else (1,)
+        for i in passes:
+            for q in range(ws):
+                sz = np.asarray(send_sizes_pr[q], dtype=I64)
+                start = 0
+                for j in passes:
+                    if j == i:
+                        break
+                    start += int(sz[j::k].sum())
+                start += int(sz[i:k * r:k].sum()) if r > 0 else 0
+                n = int(sz[k * r + i])
+                assert n == int(recv_sizes_pr[r][k * q + i])
+                parts.append(np.asarray(inputs_pr[q])[start:start + n])
+        out.append(np.concatenate(parts) if parts else np.zeros((0,) + np.asarray(inputs_pr[r]).shape[1:]))
+    return out
+
+
+def sp_virtual_sample(seeds_pr, fanout, min_vids, graph, key, call_id, num_total_nodes, with_dst=False,
+                      model="SAGE", sp_base=10_000_000):
+    """Outermost hop of the SNP sampler for SAGE / GCN, python/npc/sampler.py:240-330,
+    for all ranks at once. Neighbours are mapped to virtual nodes (owner, local
+    destination), sorted (the reference's torch.sort leaves ties in any order; the
+    stable order is taken here), block1 joins the unique virtual nodes to the local
+    destinations, the packed triples (sender, destination index, neighbour id) go to
+    the neighbour's owner, and block2 there joins the received neighbours to the
+    received virtual nodes. Per rank a dict of every intermediate."""
+    ws = len(seeds_pr)
+    pre = []
+    for r, seeds in enumerate(seeds_pr):
+        seeds = np.asarray(seeds, dtype=I64)
+        num_dst = len(seeds)
+        nbr = sample_csc_fanout(seeds, fanout, *graph, key=key, call_id=call_id)
+        if with_dst:
+            m = srcdst_to_vir(seeds, nbr, fanout, min_vids, ws, rank=r)
+            perm = np.argsort(m, kind="stable")
+            sorted_all = m[perm]
+            map_src = sorted_all[num_dst:]
+            send = np.concatenate([seeds[perm[:num_dst]],
+                                   I64(r) * I64(sp_base) * I64(num_total_nodes) + (map_src % num_dst) * I64(num_total_nodes)
+                                   + nbr[perm[num_dst:] - num_dst]])
+        else:
+            m = src_to_vir(nbr, fanout, num_dst, min_vids, ws, rank=r)
+            perm = np.argsort(m, kind="stable")
+            sorted_all = m[perm]
+            map_src = m
+            send = I64(r) * I64(sp_base) * I64(num_total_nodes) + (sorted_all % num_dst) * I64(num_total_nodes) + nbr[perm]
+        uniq = np.unique(map_src)
+        pre.append(dict(seeds=seeds, neighbors=nbr, sorted_allnodes=sorted_all, perm=perm, unique_frontier=uniq,
+                        block1_src=np.arange(len(uniq), dtype=I64), block1_dst=uniq % max(num_dst, 1),
+                        send_frontier=send))
+    sh = sp_sample_and_shuffle([len(p["seeds"]) for p in pre], [p["send_frontier"] for p in pre],
+                               [p["sorted_allnodes"] for p in pre], [p["unique_frontier"] for p in pre],
+                               with_dst, num_total_nodes)
+    for r, p in enumerate(pre):
+        p.update(sh[r])
+        usrc, asrc = np.unique(p["ori_src"], return_inverse=True)
+        udst, adst = np.unique(p["vir_src"], return_inverse=True)
+        p.update(unique_src=usrc, block2_src=asrc.astype(I64), unique_dst=udst, block2_dst=adst.astype(I64))
+        if with_dst:
+            p["input_nodes"] = np.concatenate([p["recv_dst"], usrc])
+        elif model == "GCN":
+            p["input_nodes"] = usrc
+        else:
+            p["input_nodes"] = np.concatenate([p["seeds"], usrc])
+    return pre
+
+
+# ------------------------------------------------ NFP (feature dimension split)
+def allbroadcast_v2(inputs, expand=1):
+    """AllBroadcastV2, src/ops/collective.cc:367-402: every rank sends its whole
+    (variable-length) input to every rank; received in rank order."""
+    cat = np.concatenate([np.asarray(x).reshape(-1, expand) for x in inputs]) if inputs else np.zeros((0, expand))
+    return [cat.copy() for _ in inputs]
+
+
+def mp_sample_shuffle(seeds_pr, unique_frontier_pr, coo_row_pr):
+    """MPSampleShuffle, src/sampling.cc:195-239, for all ranks at once: sizes
+    all-gathered, frontiers and relabelled rows all-broadcast. Per rank:
+    (recv_frontier, recv_coo_row, [seeds_size], recv_seeds_size,
+    recv_frontier_size, recv_coo_size)."""
+    ws = len(seeds_pr)
+    seeds_size = np.array([len(x) for x in seeds_pr], dtype=I64)
+    frontier_size = np.array([len(x) for x in unique_frontier_pr], dtype=I64)
+    coo_size = np.array([len(x) for x in coo_row_pr], dtype=I64)
+    fr = np.concatenate([np.asarray(x, dtype=I64) for x in unique_frontier_pr])
+    co = np.concatenate([np.asarray(x, dtype=I64) for x in coo_row_pr])
+    return [(fr.copy(), co.copy(), np.array([seeds_size[r]], dtype=I64), seeds_size.copy(), frontier_size.copy(),
+             coo_size.copy()) for r in range(ws)]
+
+
+def mp_feat_shuffle_fwd(inputs_pr, seg_sizes, feat_dim, acc=np.float64):
+    """MPFeatShuffleFwd, src/feat_shuffle.cc:54-64 over _AllReduce,
+    src/ops/collective.cc:404-436: rank r receives the sum over all ranks of
+    their rows [off[r], off[r + 1]) (seg_sizes[r] rows of feat_dim)."""
+    xs = [np.asarray(x).reshape(-1, feat_dim).astype(acc) for x in inputs_pr]
+    return allreduce_scatter_v(xs, seg_sizes)
+
+
+def mp_feat_shuffle_bwd(inputs_pr, feat_dim):
+    """MPFeatShuffleBwd, src/feat_shuffle.cc:66-79: all-broadcast of every
+    rank's rows."""
+    return allbroadcast_v2(inputs_pr, feat_dim)
+
+
+def mp_sample(seeds_pr, fanout, graph, key, call_id):
+    """Outermost hop of the NFP sampler for SAGE / GCN, python/npc/sampler.py:332-356:
+    local sampling and relabelling, then every rank gets every rank's frontier
+    and relabelled rows; all_coo_col restarts at 0 for every sender's block."""
+    pre = []
+    for seeds in seeds_pr:
+        seeds = np.asarray(seeds, dtype=I64)
+        nbr = sample_csc_fanout(seeds, fanout, *graph, key=key, call_id=call_id)
+        u, rel = relabel_csc(seeds, nbr)
+        pre.append((seeds, nbr, u, rel))
+    sh = mp_sample_shuffle([p[0] for p in pre], [p[2] for p in pre], [p[3] for p in pre])
+    out = []
+    for r, (fr, co, send_size, recv_size, recv_frontier_size, recv_coo_size) in enumerate(sh):
+        col = np.concatenate([np.repeat(np.arange(int(i), dtype=I64), fanout) for i in recv_size])
+        out.append(dict(neighbors=pre[r][1], all_frontier=fr, all_coo_row=co, all_coo_col=col, send_size=send_size,
+                        recv_size=recv_size, recv_frontier_size=recv_frontier_size, recv_coo_size=recv_coo_size))
+    return out
+
+
 # ------------------------------------------------------- synthetic generators
 def rmat_edges(seed, first_edge, num_edges, scale, num_nodes, a=0.57, b=0.19, c=0.19):
     """The benchmark's R-MAT generator (counter-based; same stream as the GPU

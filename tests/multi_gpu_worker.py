@@ -126,6 +126,113 @@ def main():
     back = ops.feat_shuffle(projected, sp_send, sp_recv, sp_perm, 256, 1)
     assert torch.equal(back, table_sp[sp_blocks[0].src_ids]), "SNP-GAT feature shuffle"
 
+    # --- SNP with virtual nodes for SAGE / GCN (python/npc/sampler.py:240-330), without and with
+    # destinations: every intermediate against the oracle replaying all ranks, then the partial sums
+    # per virtual node travel back (SPFeatShuffle) and must add up to the direct neighbour sums
+    g1 = torch.Generator(device="cuda").manual_seed(13)
+    table_v = torch.randn((n, 32), generator=g1, device="cuda")                     # same on every rank
+    vseeds = seeds[:500 + 37 * rank]
+    all_vseeds = gather_objects(vseeds)
+    one = lambda a_, b_: torch.tensor([a_, b_], device="cuda")
+    for with_dst in (False, True):
+        ops.set_sampling(key=555, call_id=0)
+        vs = apt_b200.SPVirtualSampler(rank, [6], model="SAGE", shuffle_with_dst=with_dst)
+        v_in, _, (vb2, vb1), v_send, v_recv = vs.sample(None, torch.from_numpy(vseeds).cuda())
+        last = vs.last
+        names = ["neighbors", "sorted_allnodes", "unique_frontier", "send_frontier", "vir_src", "ori_src", "unique_dst"]
+        got_v = {k_: host(last[k_]) for k_ in names}
+        got_v.update(send_sizes=v_send.numpy(), recv_sizes=v_recv.numpy(), input_nodes=host(v_in),
+                     block1_dst=host(vb1.coo_col), block2_src=host(vb2.coo_row), block2_dst=host(vb2.coo_col),
+                     unique_src=host(vb2.src_ids))
+        if with_dst:
+            got_v["recv_dst"] = host(last["recv_dst"])
+        all_v = gather_objects(got_v)
+        if rank == 0:
+            want_v = orc.sp_virtual_sample(all_vseeds, 6, mv, graph, key=555, call_id=0, num_total_nodes=n,
+                                           with_dst=with_dst, model="SAGE")
+            for r in range(world):
+                for name, a_ in all_v[r].items():
+                    assert np.array_equal(a_, want_v[r][name]), \
+                        f"rank {r}: SNP virtual-node sampler (with_dst={with_dst}): {name} differs from the oracle"
+        h_vir = ops.spmm_copy_u_sum(vb2.coo_row, vb2.coo_col, table_v[vb2.src_ids], one(0, vb2.coo_row.numel()),
+                                    one(0, vb2.num_src), one(0, vb2.num_dst))
+        if with_dst:
+            h_in = torch.cat((table_v[last["recv_dst"]], h_vir))
+            total = int(v_send[0::3].sum() + v_send[2::3].sum())
+        else:
+            h_in = h_vir
+            total = int(v_send[1::2].sum())
+        part = ops.sp_feat_shuffle(h_in, v_recv, v_send, total, 32, int(with_dst))
+        ops.STATE.exchange = nccl
+        part_nccl = ops.sp_feat_shuffle(h_in, v_recv, v_send, total, 32, int(with_dst))
+        ops.STATE.exchange = p2p
+        assert torch.equal(part, part_nccl), "SNP virtual-node feature shuffle: p2p and library all-to-all differ"
+        if with_dst:
+            h_self, part = part[:len(vseeds)], part[len(vseeds):].contiguous()
+            dst_sorted = ops._bucket(torch.from_numpy(vseeds).cuda())[0]
+            assert torch.equal(h_self, table_v[dst_sorted]), "SNP virtual nodes: destination rows"
+        out_v = ops.spmm_copy_u_sum(vb1.coo_row, vb1.coo_col, part, one(0, vb1.coo_row.numel()), one(0, vb1.num_src),
+                                    one(0, vb1.num_dst))
+        direct = table_v[last["neighbors"]].view(len(vseeds), 6, 32).double().sum(1)
+        assert (out_v.double() - direct).abs().max().item() <= 1e-4, "SNP virtual nodes: sums differ from direct sums"
+        # backward direction: gradients of the partial sums travel to the owners
+        gpart = torch.randn((total, 32), generator=g1, device="cuda")
+        n_back = int(v_recv[0::3].sum() + v_recv[2::3].sum()) if with_dst else int(v_recv[1::2].sum())
+        gback = ops.sp_feat_shuffle(gpart, v_send, v_recv, n_back, 32, int(with_dst))
+        all_g = gather_objects((host(gpart), host(gback), v_send.numpy(), v_recv.numpy()))
+        if rank == 0:
+            want_g = orc.sp_feat_shuffle([a_[0] for a_ in all_g], [a_[2] for a_ in all_g], [a_[3] for a_ in all_g],
+                                         with_dst)
+            for r in range(world):
+                assert np.array_equal(all_g[r][1], want_g[r]), f"rank {r}: sp_feat_shuffle backward differs"
+    ops.check_status()
+
+    # --- NFP (python/npc/sampler.py:332-356, model/sageconv.py:117-188): every rank holds a slice of the
+    # columns, aggregates it for all ranks' blocks (multi-segment SpMM) and the reduce-scatter sums the slices
+    ops.set_sampling(key=777, call_id=0)
+    mseeds = seeds[:300 + 41 * rank]
+    all_mseeds = gather_objects(mseeds)
+    m_in, _, m_blocks, m_send, m_recv = apt_b200.MPSampler(rank, [5]).sample(None, torch.from_numpy(mseeds).cuda())
+    m_row, m_col, m_fsz, m_csz, m_ssz = m_blocks[0]
+    all_m = gather_objects(dict(all_frontier=host(m_in), all_coo_row=host(m_row), all_coo_col=host(m_col),
+                                send_size=m_send.numpy(), recv_size=m_recv.numpy(), recv_frontier_size=m_fsz.numpy(),
+                                recv_coo_size=m_csz.numpy()))
+    if rank == 0:
+        want_m = orc.mp_sample(all_mseeds, 5, graph, key=777, call_id=0)
+        for r in range(world):
+            for name, a_ in all_m[r].items():
+                assert np.array_equal(a_, want_m[r][name]), f"rank {r}: NFP sampler: {name} differs from the oracle"
+    width = 8
+    g2 = torch.Generator(device="cuda").manual_seed(17)
+    table_m = torch.randn((n, world * width), generator=g2, device="cuda")          # same on every rank
+    weight = torch.randn((world * width, 16), generator=g2, device="cuda")
+    cum = lambda t: torch.cat([torch.zeros(1, dtype=torch.int64), t.cumsum(0)]).cuda()
+    xs_m = table_m[m_in][:, rank * width:(rank + 1) * width] @ weight[rank * width:(rank + 1) * width]
+    part_m = ops.spmm_copy_u_sum(m_row, m_col, xs_m.contiguous(), cum(m_csz), cum(m_fsz), cum(m_ssz))
+    summed = ops.mp_feat_shuffle_fwd(part_m, m_recv, m_send, 16)
+    ops.STATE.exchange = nccl
+    summed_nccl = ops.mp_feat_shuffle_fwd(part_m, m_recv, m_send, 16)
+    ops.STATE.exchange = p2p
+    nb_m = torch.from_numpy(orc.sample_csc_fanout(mseeds, 5, *graph, key=777, call_id=0)).cuda()
+    direct_m = (table_m[nb_m].double() @ weight.double()).view(len(mseeds), 5, 16).sum(1)
+    assert (summed.double() - direct_m).abs().max().item() <= 1e-3, "NFP: reduce-scatter differs from the direct sums"
+    assert (summed - summed_nccl).abs().max().item() <= 1e-4, "NFP: p2p and library reduce-scatter differ"
+    all_part = gather_objects(host(part_m))
+    all_sum = gather_objects(host(summed))
+    back_m = ops.mp_feat_shuffle_bwd(summed, m_send, m_recv, 16)
+    ops.STATE.exchange = nccl
+    back_nccl = ops.mp_feat_shuffle_bwd(summed, m_send, m_recv, 16)
+    ops.STATE.exchange = p2p
+    assert torch.equal(back_m, back_nccl), "NFP: p2p and library all-broadcast differ"
+    all_back = gather_objects(host(back_m))
+    if rank == 0:
+        want_sum = orc.mp_feat_shuffle_fwd(all_part, m_recv.numpy(), 16)
+        for r in range(world):
+            err = np.abs(all_sum[r] - want_sum[r]).max() if len(all_sum[r]) else 0.0
+            assert err <= 1e-4, f"rank {r}: mp_feat_shuffle_fwd differs from the oracle by {err}"
+            assert np.array_equal(all_back[r], np.concatenate(all_sum)), f"rank {r}: mp_feat_shuffle_bwd"
+    ops.check_status()
+
     # --- feature shuffle forward/backward (fp32 1 KiB rows, bf16 512 B rows, odd width)
     for dtype, D in ((torch.float32, 256), (torch.bfloat16, 256), (torch.float32, 3)):
         g = torch.Generator(device="cuda").manual_seed(7)

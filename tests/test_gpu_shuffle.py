@@ -225,3 +225,98 @@ def test_operator_layer_single_rank(backend):
         if backend == "p2p":
             ex.close()
         reset_world()
+
+
+@pytest.mark.parametrize("ws", [2, 4, 8])
+@pytest.mark.parametrize("dtype,D", [(torch.float32, 256), (torch.bfloat16, 64), (torch.float16, 40), (torch.float32, 3)])
+def test_p2p_reduce_scatter_and_allbroadcast(ws, dtype, D):
+    """The NFP exchanges over emulated ranks: segment r of every rank's rows summed
+    on rank r (receiving half of _AllReduce, src/ops/collective.cc:404-436), and
+    every rank's rows to every rank (AllBroadcastV2, :367-402)."""
+    rng = np.random.default_rng(ws * 100 + D)
+    seg = rng.integers(0, 300, ws).astype(I64)
+    seg[rng.integers(0, ws)] = 0                                  # one rank owns no destination
+    rows = int(seg.sum())
+    esz = torch.empty(0, dtype=dtype).element_size()
+    xs = [torch.from_numpy(rng.standard_normal((rows, D)).astype(np.float32)).to(dtype).cuda() for _ in range(ws)]
+    ranks = Ranks(ws, region_bytes=4 << 20)
+    code = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _lib.F16}[dtype]
+    try:
+        counts = ranks.alltoall(xs, [np.cumsum(seg)] * ws, D * esz)
+        want = orc.mp_feat_shuffle_fwd([host(x) for x in xs], seg, D)
+        for r in range(ws):
+            c = torch.cat([counts[r], counts[r].sum()[None]])
+            out = torch.full((int(seg[r]), D), 7, dtype=dtype, device="cuda")
+            check(lib.apt_p2p_pull_sum(ranks.ctx[r], c.data_ptr(), code, int(seg[r]), D,
+                                       out.data_ptr() if out.numel() else None, ranks.status.data_ptr(), _stream()))
+            tol = 1e-5 if dtype == torch.float32 else 1e-2
+            err = np.abs(host(out).astype(np.float64) - want[r]) / np.maximum(np.abs(want[r]), 1.0)
+            assert err.size == 0 or err.max() <= tol
+        assert int(ranks.status[0].item()) == 0
+        # a peer that sent another row count is reported, not summed
+        r = int(np.argmax(seg))
+        c = torch.cat([counts[r], counts[r].sum()[None]]).clone()
+        c[(r + 1) % ws] += 1
+        out = torch.empty((int(seg[r]), D), dtype=dtype, device="cuda")
+        check(lib.apt_p2p_pull_sum(ranks.ctx[r], c.data_ptr(), code, int(seg[r]), D, out.data_ptr(),
+                                   ranks.status.data_ptr(), _stream()))
+        assert int(ranks.status[0].item()) & _lib.FLAG_SIZE_MISMATCH
+        ranks.status.zero_()
+
+        # all-broadcast: the push index repeats every rank's rows once per peer
+        lens = rng.integers(0, 200, ws).astype(I64)
+        ys = [torch.from_numpy(rng.standard_normal((int(n_), D)).astype(np.float32)).to(dtype).cuda() for n_ in lens]
+        idx = [torch.arange(int(n_), device="cuda").repeat(ws) for n_ in lens]
+        counts = ranks.alltoall(ys, [np.arange(1, ws + 1, dtype=I64) * int(n_) for n_ in lens], D * esz,
+                                src_index=[i if i.numel() else torch.zeros(1, dtype=torch.int64, device="cuda")
+                                           for i in idx], index_is_dest=0)
+        cat = np.concatenate([host(y) for y in ys])
+        for r in range(ws):
+            assert np.array_equal(host(counts[r]), lens)
+            out = torch.empty((int(lens.sum()), D), dtype=dtype, device="cuda")
+            ranks.pull(r, counts[r], out, D * esz)
+            assert np.array_equal(host(out), cat)
+        assert int(ranks.status[0].item()) == 0
+    finally:
+        ranks.close()
+
+
+@pytest.mark.parametrize("backend", ["local", "p2p"])
+def test_nfp_operators_single_rank(backend):
+    """mp_sample_shuffle / mp_feat_shuffle_fwd / _bwd and the NFP sampler with one rank."""
+    from apt_b200.exchange import LocalExchange, P2PExchange
+    from apt_b200.sampler import MPSampler
+
+    n, indptr, indices = small_graph(scale=11)
+    install_graph(indptr, indices)
+    reset_world(1, 0)
+    s = apt_b200.STATE
+    ex = LocalExchange(s) if backend == "local" else P2PExchange.__new__(P2PExchange)
+    if backend == "p2p":
+        c = ctypes.c_void_p()
+        check(lib.apt_p2p_create(0, 1, 8 << 20, ctypes.byref(c), None))
+        P2PExchange.__init__(ex, s, 0, ctx=c)
+    s.exchange = ex
+    try:
+        rng = np.random.default_rng(3)
+        seeds = rng.permutation(n)[:400].astype(I64)
+        ops.set_sampling(key=4, call_id=0)
+        in_nodes, out_nodes, blocks, send_size, recv_size = MPSampler(0, [6]).sample(None, dev(seeds))
+        want = orc.mp_sample([seeds], 6, (None, None, None, indptr, indices), key=4, call_id=0)[0]
+        all_coo_row, all_coo_col, recv_frontier_size, recv_coo_size, recv_seed_size = blocks[0]
+        assert np.array_equal(host(in_nodes), want["all_frontier"])
+        assert np.array_equal(host(all_coo_row), want["all_coo_row"])
+        assert np.array_equal(host(all_coo_col), want["all_coo_col"])
+        for got, name in ((send_size, "send_size"), (recv_size, "recv_size"), (recv_frontier_size, "recv_frontier_size"),
+                          (recv_coo_size, "recv_coo_size"), (recv_seed_size, "recv_size")):
+            assert not got.is_cuda and np.array_equal(got.numpy(), want[name])
+        x = torch.randn((400, 48), device="cuda")
+        y = ops.mp_feat_shuffle_fwd(x, recv_size, send_size, 48)
+        assert torch.equal(y, x)
+        z = ops.mp_feat_shuffle_bwd(y, send_size, recv_size, 48)
+        assert torch.equal(z, x)
+        ops.check_status()
+    finally:
+        if backend == "p2p":
+            ex.close()
+        reset_world()

@@ -300,6 +300,91 @@ def test_spmm_segments():
 
 
 # ------------------------------------------------------------ committed fixtures
+@pytest.mark.parametrize("ws", [1, 2, 3, 8])
+@pytest.mark.parametrize("with_dst", [False, True])
+def test_virtual_node_path_adds_up(ws, with_dst):
+    # SNP with virtual nodes: the partial sums per virtual node, sent back, add up to the direct
+    # neighbour sums; sizes are consistent between the ranks; every received virtual node names
+    # its sender (python/npc/sampler.py:240-330, src/sampling.cc:71-149)
+    n, indptr, indices = small_graph(scale=10, edge_factor=8)
+    graph = (None, None, None, indptr, indices)
+    mv = np.linspace(0, n, ws + 1).astype(I64)
+    rng = np.random.default_rng(ws)
+    seeds = [rng.integers(0, n, 40 + 9 * r).astype(I64) for r in range(ws)]
+    f, k = 5, (3 if with_dst else 2)
+    res = orc.sp_virtual_sample(seeds, f, mv, graph, key=1, call_id=2, num_total_nodes=n, with_dst=with_dst)
+    x = rng.standard_normal((n, 4))
+    inputs = []
+    for r, p in enumerate(res):
+        assert np.array_equal(orc.owner_of(p["ori_src"], mv, ws), np.full(len(p["ori_src"]), r))
+        assert np.array_equal(np.sort(p["vir_src"] // 10_000_000, kind="stable"), p["vir_src"] // 10_000_000)
+        for q in range(ws):
+            assert np.array_equal(p["recv_sizes"][k * q:k * q + k], res[q]["send_sizes"][k * r:k * r + k])
+        assert p["send_sizes"][k - 2::k].sum() == len(seeds[r]) * f
+        assert p["send_sizes"][k - 1::k].sum() == len(p["unique_frontier"])
+        assert p["recv_sizes"][k - 1::k].sum() == len(p["unique_dst"])
+        h = np.zeros((len(p["unique_dst"]), 4))
+        np.add.at(h, p["block2_dst"], x[p["unique_src"]][p["block2_src"]])
+        inputs.append(np.concatenate([x[p["recv_dst"]], h]) if with_dst else h)
+    got = orc.sp_feat_shuffle(inputs, [p["recv_sizes"] for p in res], [p["send_sizes"] for p in res], with_dst)
+    for r, p in enumerate(res):
+        g, nd = got[r], len(seeds[r])
+        if with_dst:
+            assert np.allclose(g[:nd], x[seeds[r][p["perm"][:nd]]])
+            g = g[nd:]
+        out = np.zeros((nd, 4))
+        np.add.at(out, p["block1_dst"], g)
+        assert np.allclose(out, x[p["neighbors"]].reshape(nd, f, 4).sum(1))
+
+
+def test_virtual_send_offsets_closed_form():
+    # 2 ranks, 3 destinations, fanout 2: owners of the neighbours 0 1 | 1 1 | 0 0
+    mv = np.array([0, 10, 20], dtype=I64)
+    src = np.array([1, 11, 12, 13, 2, 3], dtype=I64)
+    m = orc.src_to_vir(src, 2, 3, mv, 2)
+    assert m.tolist() == [0, 3, 4, 4, 2, 2]
+    s, u = np.sort(m), np.unique(m)
+    assert orc.vir_send_offset(2, 3, s, u, False).tolist() == [0, 3, 6, 2, 4]
+    assert orc.vir_send_sizes(2, 3, s, u, False).tolist() == [3, 2, 3, 2]
+    dst = np.array([15, 5, 6], dtype=I64)
+    md = orc.srcdst_to_vir(dst, src, 2, mv, 2)
+    assert md.tolist() == [3, 1, 2, 6, 9, 10, 10, 8, 8]
+    sd = np.sort(md)
+    ud = np.unique(sd[3:])
+    assert orc.vir_send_offset(2, 3, sd, ud, True).tolist() == [0, 2, 3, 6, 9, 2, 4]
+    assert orc.vir_send_sizes(2, 3, sd, ud, True).tolist() == [2, 3, 2, 1, 3, 2]
+
+
+@pytest.mark.parametrize("ws", [1, 2, 4])
+def test_nfp_path_adds_up(ws):
+    # NFP: every rank holds a slice of the columns; the multi-segment aggregation of all ranks'
+    # blocks followed by the reduce-scatter gives every rank the full-width neighbour sums of its
+    # own seeds (python/npc/sampler.py:332-356, python/npc/model/sageconv.py:117-188)
+    n, indptr, indices = small_graph(scale=10, edge_factor=8)
+    graph = (None, None, None, indptr, indices)
+    rng = np.random.default_rng(40 + ws)
+    seeds = [rng.permutation(n)[:30 + 11 * r].astype(I64) for r in range(ws)]
+    f, width = 4, 3
+    res = orc.mp_sample(seeds, f, graph, key=9, call_id=1)
+    x = rng.standard_normal((n, ws * width))
+    w = rng.standard_normal((ws * width, 5))                # the layer's weight, rows split like the columns
+    partial = []
+    for r, p in enumerate(res):
+        fo = np.concatenate([[0], np.cumsum(p["recv_frontier_size"])])
+        co = np.concatenate([[0], np.cumsum(p["recv_coo_size"])])
+        so = np.concatenate([[0], np.cumsum(p["recv_size"])])
+        assert p["send_size"][0] == len(seeds[r]) and co[-1] == len(p["all_coo_row"]) == len(p["all_coo_col"])
+        xs = x[p["all_frontier"], r * width:(r + 1) * width] @ w[r * width:(r + 1) * width]
+        partial.append(orc.spmm_sum("copy_u", p["all_coo_row"], p["all_coo_col"], xs, None, co, fo, so))
+    got = orc.mp_feat_shuffle_fwd(partial, res[0]["recv_size"], 5)
+    for r in range(ws):
+        want = (x[res[r]["neighbors"]] @ w).reshape(len(seeds[r]), f, 5).sum(1)
+        assert np.allclose(got[r], want)
+    back = orc.mp_feat_shuffle_bwd([g.astype(np.float32) for g in got], 5)
+    for r in range(ws):
+        assert np.array_equal(back[r], np.concatenate(got).astype(np.float32))
+
+
 def test_committed_fixture_matches_oracle():
     z = np.load(os.path.join(GOLDEN, "path_small.npz"))
     indptr, indices = z["indptr"], z["indices"]
