@@ -45,10 +45,13 @@ def parse():
     ap.add_argument("--impl", default="apt_b200", choices=["apt_b200", "reference"])
     ap.add_argument("--cpu-batches", type=int, default=12, help="batches of the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--stage", default="minibatch", choices=["minibatch", "gather", "shuffle", "ops"],
+    ap.add_argument("--stage", default="minibatch", choices=["minibatch", "gather", "shuffle", "ops", "strategies"],
                     help="gather: the cached feature gather alone on a synthetic table; "
                          "shuffle: the NPC feature shuffle alone (needs --gpus >= 2 under torchrun); "
-                         "ops: sampling, relabelling, SpMM, SDDMM and the fused GAT block one by one")
+                         "ops: sampling, relabelling, SpMM, SDDMM and the fused GAT block one by one; "
+                         "strategies: the outermost hop and its first-layer exchange under NP, SNP with virtual "
+                         "nodes and NFP, side by side (needs --gpus >= 2 under torchrun)")
+    ap.add_argument("--hidden", type=int, default=256, help="--stage strategies: width of the exchanged rows")
     ap.add_argument("--rows", type=int, default=1_081_344, help="--stage gather: rows per call")
     ap.add_argument("--table-rows", type=int, default=4_000_000, help="--stage gather: rows of the cached table")
     ap.add_argument("--feat-dim", type=int, default=128)
@@ -474,6 +477,111 @@ def stage_shuffle(args):
     dist.destroy_process_group()
 
 
+# -------------------------------------------------------------- stage: strategies
+def stage_strategies(args):
+    """One mini-batch of the small graph (2^20 nodes, fanout [25, 10], 1024 seeds per GPU) through the
+    sampler and the first-layer exchange of three strategies of the reference: NP (seeds to the owner,
+    hidden rows back), SNP with virtual nodes (packed neighbour ids to the owner, partial sums per
+    virtual node back) and NFP (frontiers and blocks to everyone, column slices summed by a
+    reduce-scatter). Reports ms per mini-batch (max over ranks) and the bytes each strategy puts on
+    NVLink per GPU, which is what the reference's planner trades off."""
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world < 2:
+        raise SystemExit("--stage strategies needs at least 2 ranks (torchrun)")
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    import apt_b200
+    from apt_b200 import ops, synthetic
+
+    ops.STATE.p2p_region_bytes = 256 << 20
+    ops.init(rank, local, world, ops.nccl_get_unique_id(), world)
+    w = synthetic.WORKLOADS["c0_small_np"]
+    indptr, indices = synthetic.build_csc(w)
+    e = torch.empty(0, dtype=torch.int64)
+    ops.mix_cache_graphs(0, e, e, e, indptr, indices)
+    ops.register_min_vids(synthetic.partition_min_vids(w.num_nodes, world))
+    H = args.hidden
+    g = torch.Generator(device="cuda").manual_seed(500 + rank)
+    steps = args.warmup + args.steps
+    batches = [torch.randperm(w.num_nodes, generator=g, device="cuda")[:w.batch] for _ in range(steps)]
+    table = torch.randn((w.num_nodes, H), generator=g, device="cuda")       # stands for the projected rows
+    table_slice = table[:, :H // world].contiguous()
+    one = lambda a, b: torch.tensor([a, b], device="cuda")
+    cum = lambda t: torch.cat([torch.zeros(1, dtype=torch.int64), t.cumsum(0)]).cuda()
+    volume = {}
+
+    def np_step(seeds):
+        smp = np_step.sampler
+        in_nodes, _, blocks, perm, send_off, recv_off, inv = smp.sample(None, seeds)
+        h = table[in_nodes[:blocks[0].num_dst]]                         # layer output of the owned frontier
+        x = ops.rows_gather(h, inv)
+        y = ops.feat_shuffle(x, send_off, recv_off, perm, H, 1)
+        sent = int(send_off[-1]) - int(send_off[rank] - (send_off[rank - 1] if rank else 0))
+        got = int(recv_off[-1]) - int(recv_off[rank] - (recv_off[rank - 1] if rank else 0))
+        volume["NP"] = (got * 8, sent * H * 4)                          # ids out = rows this rank asked for
+        return y
+
+    np_step.sampler = apt_b200.MixedNeighborSampler(rank, w.fanouts, prefetch_features=False)
+
+    def sp_step(seeds):
+        smp = sp_step.sampler
+        in_nodes, _, (b2, b1, *_), send_sizes, recv_sizes = smp.sample(None, seeds)
+        h_vir = ops.spmm_copy_u_sum(b2.coo_row, b2.coo_col, table[b2.src_ids], one(0, b2.coo_row.numel()),
+                                    one(0, b2.num_src), one(0, b2.num_dst))
+        part = ops.sp_feat_shuffle(h_vir, recv_sizes, send_sizes, int(send_sizes[1::2].sum()), H, 0)
+        out = ops.spmm_copy_u_sum(b1.coo_row, b1.coo_col, part, one(0, b1.coo_row.numel()), one(0, b1.num_src),
+                                  one(0, b1.num_dst))
+        ids = int(send_sizes[0::2].sum() - send_sizes[2 * rank])
+        rows = int(recv_sizes[1::2].sum() - recv_sizes[2 * rank + 1])
+        volume["SNP"] = (ids * 8, rows * H * 4)
+        return out
+
+    sp_step.sampler = apt_b200.SPVirtualSampler(rank, w.fanouts, model="SAGE")
+
+    def mp_step(seeds):
+        smp = mp_step.sampler
+        in_nodes, _, blocks, send_size, recv_size = smp.sample(None, seeds)
+        row, col, fsz, csz, ssz = blocks[0]
+        xs = table_slice[in_nodes]                                       # this rank's column slice, projected
+        part = ops.spmm_copy_u_sum(row, col, xs, cum(csz), cum(fsz), cum(ssz))
+        out = ops.mp_feat_shuffle_fwd(part, recv_size, send_size, H // world)
+        mine = int(fsz[rank] + csz[rank])
+        volume["NFP"] = ((world - 1) * mine * 8, int(ssz.sum() - ssz[rank]) * (H // world) * 4)
+        return out
+
+    mp_step.sampler = apt_b200.MPSampler(rank, w.fanouts)
+
+    res = {}
+    for name, fn in (("NP", np_step), ("SNP", sp_step), ("NFP", mp_step)):
+        ops.set_sampling(key=2026, call_id=0)
+        for b in batches[:args.warmup]:
+            fn(b)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for b in batches[args.warmup:]:
+            fn(b)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1) / args.steps], device="cuda")
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        vol = torch.tensor(volume[name], dtype=torch.float64, device="cuda")
+        dist.all_reduce(vol, op=dist.ReduceOp.MAX)
+        res[name] = {"ms_per_minibatch": round(float(ms.item()), 4),
+                     "id_bytes_out_per_gpu": int(vol[0].item()), "row_bytes_out_per_gpu": int(vol[1].item())}
+    ops.check_status()
+    if rank == 0:
+        print(json.dumps({"metric": "outermost hop + first-layer exchange per strategy", "unit": "ms per mini-batch",
+                          "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "data": "synthetic",
+                          "config": {"workload": "stage strategies", "graph": w.name, "fanouts": list(w.fanouts),
+                                     "seeds_per_gpu": w.batch, "hidden": H, "rows": "f32"},
+                          "strategies": res}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 # ------------------------------------------------------------------------- main
 def main():
     args = parse()
@@ -483,6 +591,8 @@ def main():
         return stage_shuffle(args)
     if args.stage == "ops":
         return stage_ops(args)
+    if args.stage == "strategies":
+        return stage_strategies(args)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
