@@ -57,6 +57,10 @@ PROTOTYPES = {
     "apt_vir_send_sizes": (c_int, [P, c_int64, P, c_int64, P, c_int, c_int64, c_int, P, P, P]),
     "apt_sp_pack_frontier": (c_int, [P, P, c_int64, c_int64, c_int, c_int64, c_int64, P, P]),
     "apt_sp_unpack_frontier": (c_int, [P, c_int64, P, c_int64, P, P, P]),
+    "apt_hotness_add": (c_int, [P, c_int64, P, P, c_int64, P, P]),
+    "apt_hot_order_workspace_bytes": (c_size_t, [c_int64]),
+    "apt_hot_order": (c_int, [P, c_int64, P, c_size_t, P, P]),
+    "apt_cached_access": (c_int, [P, c_int64, P, c_int64, P, P]),
     "apt_rows_gather": (c_int, [P, P, c_int64, c_int64, P, P]),
     "apt_rows_scatter": (c_int, [P, P, c_int64, c_int64, P, P]),
     "apt_p2p_create": (c_int, [c_int, c_int, c_size_t, ctypes.POINTER(P), P]),

@@ -13,7 +13,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libapt_b200.so")
-SOURCES = ["core.cu", "sample.cu", "relabel.cu", "bucket.cu", "gather.cu", "spmm.cu", "virt.cu", "p2p.cu", "util.cu"]
+SOURCES = ["core.cu", "sample.cu", "relabel.cu", "bucket.cu", "gather.cu", "spmm.cu", "virt.cu", "hotness.cu", "p2p.cu", "util.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",

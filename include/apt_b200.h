@@ -343,6 +343,30 @@ int apt_sp_unpack_frontier(const int64_t* packed, int64_t n, const int64_t* n_de
                            int64_t num_total_nodes, int64_t* out_vir,
                            int64_t* out_ori, void* stream);
 
+/* ------------------------------------------- dry run: hotness and cache policy
+ * The access counters the reference keeps on the host during a dry run
+ * (counter[input_nodes.cpu()] += 1, examples/dryrun.py:86-93,
+ * python/npc/cost_model/estimator.py:433-436), the order the cache policy sorts
+ * them into (torch.sort(freq, descending=True)[1], python/npc/ops.py:189-231,
+ * estimator.py:208-209) and the hit volume of a cache of the hottest nodes
+ * (get_cache_miss, estimator.py:22-30), kept on the device.
+ *
+ * apt_hotness_add    counters[ids[i]] += 1 (int32 counters of num_nodes entries).
+ * apt_hot_order      out_sorted_idx[num_nodes] = node ids by falling counter; equal
+ *                    counters by rising id (the reference's sort leaves ties open).
+ * apt_cached_access  out[0] = sum of all counters, out[1] = sum over the first
+ *                    num_cache entries of sorted_idx (device int64[2]).
+ */
+int apt_hotness_add(const int64_t* ids, int64_t n, const int64_t* n_dev,
+                    int32_t* counters, int64_t num_nodes, int32_t* status_word,
+                    void* stream);
+size_t apt_hot_order_workspace_bytes(int64_t num_nodes);
+int apt_hot_order(const int32_t* counters, int64_t num_nodes, void* workspace,
+                  size_t workspace_bytes, int64_t* out_sorted_idx, void* stream);
+int apt_cached_access(const int32_t* counters, int64_t num_nodes,
+                      const int64_t* sorted_idx, int64_t num_cache,
+                      int64_t* out_total_and_cached, void* stream);
+
 /* ------------------------------------------------------- local row movers
  * out[i] = in[index[i]] and out[index[i]] = in[i] over rows of row_bytes
  * bytes (16-byte vectors when alignment allows). These are the index_select /

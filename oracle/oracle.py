@@ -632,6 +632,87 @@ def mp_sample(seeds_pr, fanout, graph, key, call_id):
     return out
 
 
+# ------------------------------------------- dry run, cache policy, cost model
+def hot_order(freq):
+    """torch.sort(freq, descending=True)[1] (python/npc/cost_model/estimator.py:26,
+    :208-209) with equal frequencies by rising id."""
+    freq = np.asarray(freq)
+    return np.lexsort((np.arange(len(freq)), -freq.astype(np.int64))).astype(I64)
+
+
+def get_cache_miss(seeds_freq, num_cache_nodes, input_dim, made_seeds_freq=None):
+    """get_cache_miss, estimator.py:22-30."""
+    seeds_freq = np.asarray(seeds_freq).astype(np.int64)
+    order = hot_order(seeds_freq if made_seeds_freq is None else made_seeds_freq)
+    k = min(int(num_cache_nodes), len(seeds_freq))
+    return int(seeds_freq.sum() - seeds_freq[order[:k]].sum()) * int(input_dim)
+
+
+def np_reshuffle_vol(world_size, rank, send_offset, recv_offset, dim):
+    """get_np_reshuffle_vol, estimator.py:129-144."""
+    so, ro = [int(x) for x in send_offset], [int(x) for x in recv_offset]
+    total_send = so[world_size - 1] - so[rank] + (so[rank - 1] if rank > 0 else 0)
+    total_recv = ro[world_size - 1] - ro[rank] + (ro[rank - 1] if rank > 0 else 0)
+    return 2 * dim * (total_send + total_recv)
+
+
+def sp_reshuffle_vol(world_size, rank, send_sizes, recv_sizes, dim, with_dst=False):
+    """get_sp_reshuffle_vol for SAGE / GCN, estimator.py:147-178."""
+    k = 3 if with_dst else 2
+    vol = 0
+    for r in range(world_size):
+        if r == rank:
+            continue
+        vol += 2 * dim * int(send_sizes[k * r + k - 1] + recv_sizes[k * r + k - 1])
+        if with_dst:
+            vol += 2 * dim * int(send_sizes[3 * r] + recv_sizes[3 * r])
+    return vol
+
+
+def mp_reshuffle_vol(world_size, send_size, recv_size, dim):
+    """get_mp_reshuffle_vol, estimator.py:181-188."""
+    return 2 * dim * (int(send_size[0]) * (world_size - 2) + int(np.sum(recv_size)))
+
+
+def vol_to_seconds(vol, mib_per_s, bytes_per_element=4):
+    """cachemiss_vol_to_time / reshuffle_vol_to_time, estimator.py:112-118."""
+    return vol * bytes_per_element / (1024 * 1024 * mib_per_s)
+
+
+def all_strategy_sample(seeds_pr, fanouts, min_vids, graph, key, first_call_id, num_total_nodes, model="SAGE",
+                        with_dst=False):
+    """AllPSNeighborSampler.sample, python/npc/sampler.py:403-600, for all ranks at
+    once: inner hops, then the outermost hop under GDP, NP, SNP (virtual nodes) and
+    NFP. The outermost NP draw comes before the local one (:408-416), which fixes
+    the call ids. Per rank: dict(dp_seeds, np=(seeds, send_offset, recv_offset),
+    sp=(seeds, send_sizes, recv_sizes), mp=(seeds, send_size, recv_size))."""
+    ws = len(seeds_pr)
+    cur = [np.asarray(s_, dtype=I64) for s_ in seeds_pr]
+    call = first_call_id
+    rev = list(reversed(list(fanouts)))
+    for f in rev[:-1]:
+        nxt = []
+        for s_ in cur:
+            nb = sample_csc_fanout(s_, f, *graph, key=key, call_id=call)
+            nxt.append(relabel_csc(s_, nb)[0])
+        cur = nxt
+        call += 1
+    f = rev[-1]
+    npo = np_sample_and_shuffle(cur, f, min_vids, graph, key=key, call_id=call)
+    call += 1
+    sp = sp_virtual_sample(cur, f, min_vids, graph, key=key, call_id=call, num_total_nodes=num_total_nodes,
+                           with_dst=with_dst, model=model)
+    mp = mp_sample(cur, f, graph, key=key, call_id=call)
+    out = []
+    for r in range(ws):
+        uq, nb, _, so, ro, _ = npo[r]
+        out.append(dict(dp_seeds=relabel_csc(cur[r], sp[r]["neighbors"])[0],
+                        np=(relabel_csc(uq, nb)[0], so, ro),
+                        sp=(sp[r]["input_nodes"], sp[r]["send_sizes"], sp[r]["recv_sizes"]),
+                        mp=(mp[r]["all_frontier"], mp[r]["send_size"], mp[r]["recv_size"])))
+    return out
+
+
 # ------------------------------------------------------- synthetic generators
 def rmat_edges(seed, first_edge, num_edges, scale, num_nodes, a=0.57, b=0.19, c=0.19):
     """The benchmark's R-MAT generator (counter-based; same stream as the GPU

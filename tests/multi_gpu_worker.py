@@ -233,6 +233,31 @@ def main():
             assert np.array_equal(all_back[r], np.concatenate(all_sum)), f"rank {r}: mp_feat_shuffle_bwd"
     ops.check_status()
 
+    # --- dry run and cost model (python/npc/cost_model/estimator.py:283-697): all four strategies in one pass,
+    # counters on the device; exchange volumes and input-node frequencies against the oracle replaying all ranks
+    from apt_b200 import planner
+    rng_p = np.random.default_rng(900 + rank)
+    p_batches = [rng_p.permutation(n)[:96].astype(I64) for _ in range(2)]
+    ops.set_sampling(key=4242, call_id=0)
+    all_sampler = planner.AllStrategySampler(rank, [4, 3], model="SAGE")
+    cm = planner.run_costmodel(all_sampler, [[torch.from_numpy(b).cuda() for b in p_batches]], n,
+                               cache_memory=500 * 32 * 4, input_dim=32, num_hidden=16)
+    all_pb = gather_objects(p_batches)
+    all_cm = gather_objects((cm.volumes, cm.best, cm.records))
+    if rank == 0:
+        want_vol = [dict.fromkeys(("DP", "NP", "SP", "MP"), 0.0) for _ in range(world)]
+        for step in range(2):
+            o = orc.all_strategy_sample([all_pb[r][step] for r in range(world)], [4, 3], mv, graph, key=4242,
+                                        first_call_id=3 * step, num_total_nodes=n)
+            for r in range(world):
+                want_vol[r]["NP"] += orc.np_reshuffle_vol(world, r, o[r]["np"][1], o[r]["np"][2], 16)
+                want_vol[r]["SP"] += orc.sp_reshuffle_vol(world, r, o[r]["sp"][1], o[r]["sp"][2], 16)
+                want_vol[r]["MP"] += orc.mp_reshuffle_vol(world, o[r]["mp"][1], o[r]["mp"][2], 16)
+        for r in range(world):
+            assert all_cm[r][0] == want_vol[r], f"rank {r}: cost model volumes {all_cm[r][0]} != {want_vol[r]}"
+            assert all_cm[r][1] == all_cm[0][1] and all_cm[r][2] == all_cm[0][2], "ranks disagree on the best strategy"
+    ops.check_status()
+
     # --- feature shuffle forward/backward (fp32 1 KiB rows, bf16 512 B rows, odd width)
     for dtype, D in ((torch.float32, 256), (torch.bfloat16, 256), (torch.float32, 3)):
         g = torch.Generator(device="cuda").manual_seed(7)

@@ -385,6 +385,21 @@ def test_nfp_path_adds_up(ws):
         assert np.array_equal(back[r], np.concatenate(got).astype(np.float32))
 
 
+def test_cost_model_arithmetic_closed_form():
+    # get_cache_miss (python/npc/cost_model/estimator.py:22-30) and the volume formulas (:129-188)
+    freq = np.array([5, 0, 9, 9, 1], dtype=np.int32)
+    assert orc.hot_order(freq).tolist() == [2, 3, 0, 4, 1]
+    assert orc.get_cache_miss(freq, 0, 10) == 240 and orc.get_cache_miss(freq, 2, 10) == 60
+    assert orc.get_cache_miss(freq, 99, 10) == 0
+    assert orc.get_cache_miss(freq, 1, 10, made_seeds_freq=np.array([0, 7, 0, 0, 0])) == 240
+    # rank 1 of 3: sends 4 + 6 rows to the others, receives 1 + 2
+    assert orc.np_reshuffle_vol(3, 1, [4, 9, 15], [1, 8, 10], 256) == 2 * 256 * (10 + 3)
+    assert orc.sp_reshuffle_vol(2, 0, [7, 3, 9, 4], [1, 2, 5, 6], 8) == 2 * 8 * (4 + 6)
+    assert orc.sp_reshuffle_vol(2, 1, [1, 7, 3, 2, 9, 4], [1, 1, 2, 3, 5, 6], 8, with_dst=True) == 2 * 8 * (1 + 3 + 1 + 2)
+    assert orc.mp_reshuffle_vol(4, [10], [10, 20, 30, 40], 16) == 2 * 16 * (10 * 2 + 100)
+    assert orc.vol_to_seconds(1024 * 1024, 4.0) == 1.0
+
+
 def test_committed_fixture_matches_oracle():
     z = np.load(os.path.join(GOLDEN, "path_small.npz"))
     indptr, indices = z["indptr"], z["indices"]
