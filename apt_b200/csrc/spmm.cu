@@ -258,12 +258,12 @@ enum { kCopyU = 0, kCopyE = 1, kUMulE = 2, kUAddE = 3 };
 
 template <typename T, int VE, int OP>
 __device__ __forceinline__ void edge_value(float* acc, const T* __restrict__ in,
-                                           const T* __restrict__ edata, int64_t src_row,
+                                           const T* __restrict__ edata, int64_t src_off /* row * feat_dim */,
                                            int64_t e, int64_t feat_dim, int64_t edata_dim,
                                            int64_t per, int64_t col0) {
   float x[VE];
   if constexpr (OP != kCopyE) {
-    const Pack<T, VE> p = load_pack<T, VE>(in + src_row * feat_dim + col0);
+    const Pack<T, VE> p = load_pack<T, VE>(in + src_off + col0);
 #pragma unroll
     for (int t = 0; t < VE; ++t) x[t] = Elem<T>::to_f(p.v[t]);
   }
@@ -336,12 +336,13 @@ k_spmm_rows(const int64_t* __restrict__ row, int64_t E, const T* __restrict__ in
         int64_t my_src = 0;
         if (k0 + sub < e1) {
           my_e = unsorted ? ws.order[k0 + sub] : (int)(k0 + sub);
-          my_src = OP == kCopyE ? 0 : ioff[st.nseg > 1 ? seg_of(coo, st.nseg, my_e) : 0] + row[my_e];
+          // element offset of the source row, so that the walk below only adds
+          my_src = OP == kCopyE ? 0 : (ioff[st.nseg > 1 ? seg_of(coo, st.nseg, my_e) : 0] + row[my_e]) * feat_dim;
         }
         const int cnt = (int)min((int64_t)group, e1 - k0);
 #pragma unroll 4
         for (int j = 0; j < cnt; ++j) {
-          const int e = __shfl_sync(gmask, my_e, j, group);
+          const int e = OP == kCopyU ? 0 : __shfl_sync(gmask, my_e, j, group);   // copy_u never looks at the edge id
           const int64_t src = __shfl_sync(gmask, my_src, j, group);
           if (c < nvec) edge_value<T, VE, OP>(acc, in, edata, src, e, feat_dim, edata_dim, per, c * VE);
         }
@@ -513,12 +514,12 @@ k_spmm_long(const int64_t* __restrict__ row, const T* __restrict__ in, const T* 
         int64_t my_src = 0;
         if (k0 + lane < e1) {
           my_e = unsorted ? ws.order[k0 + lane] : (int)(k0 + lane);
-          my_src = OP == kCopyE ? 0 : ioff[st.nseg > 1 ? seg_of(coo, st.nseg, my_e) : 0] + row[my_e];
+          my_src = OP == kCopyE ? 0 : (ioff[st.nseg > 1 ? seg_of(coo, st.nseg, my_e) : 0] + row[my_e]) * feat_dim;
         }
         const int cnt = (int)min((int64_t)32, e1 - k0);
 #pragma unroll 4
         for (int j = 0; j < cnt; ++j) {
-          const int e = __shfl_sync(0xffffffffu, my_e, j);
+          const int e = OP == kCopyU ? 0 : __shfl_sync(0xffffffffu, my_e, j);
           const int64_t src = __shfl_sync(0xffffffffu, my_src, j);
           if (c < nvec) edge_value<T, VE, OP>(acc, in, edata, src, e, feat_dim, edata_dim, per, c * VE);
         }
