@@ -13,7 +13,7 @@ from .ops import (  # noqa: F401
     load_subtensor, local_sample_one_layer, mix_cache_graphs, mp_feat_shuffle_bwd, mp_feat_shuffle_fwd,
     mp_sample_shuffle, nccl_get_unique_id, np_sample_and_shuffle,
     register_min_vids, relabel_csc, rows_gather, rows_scatter, sddmm_u_add_v, sddmm_u_mul_v, set_sampling,
-    gat_edge_softmax_sum, shuffle_seeds, sp_feat_shuffle, sp_sample_and_shuffle, sp_sample_shuffle_src, spmm_copy_e_sum, spmm_copy_u_sum, spmm_u_mul_e_sum, src_to_vir,
+    gat_edge_softmax_sum, gat_edge_softmax_sum_backward, GATEdgeSoftmaxSum, shuffle_seeds, sp_feat_shuffle, sp_sample_and_shuffle, sp_sample_shuffle_src, spmm_copy_e_sum, spmm_copy_u_sum, spmm_u_mul_e_sum, src_to_vir,
     srcdst_to_vir, unique_sorted,
 )
 from .sampler import Block, DPNeighborSampler, MPSampler, MixedNeighborSampler, SPGATSampler, SPVirtualSampler, create_block  # noqa: F401

@@ -52,6 +52,7 @@ PROTOTYPES = {
     "apt_spmm_sum": (c_int, [c_int, c_int, P, P, c_int64, P, P, c_int64, c_int64, P, P, P, c_int, c_int64, P, P, c_size_t, P]),
     "apt_sddmm": (c_int, [c_int, c_int, P, P, c_int64, P, P, c_int64, P, P, P, c_int, P, P]),
     "apt_gat_edge_softmax_sum": (c_int, [c_int, P, P, c_int64, P, P, P, c_int, c_int64, c_float, c_int64, P, P, P, c_size_t, P, P]),
+    "apt_gat_edge_backward": (c_int, [c_int, P, P, c_int64, P, P, P, P, c_int, c_int64, c_float, c_int64, P, P, P, P, c_size_t, P, P]),
     "apt_src_to_vir": (c_int, [P, c_int64, c_int64, c_int64, P, c_int, c_int, c_int, c_int, c_int, P, P]),
     "apt_srcdst_to_vir": (c_int, [P, c_int64, P, c_int64, c_int64, P, c_int, c_int, c_int, c_int, c_int, P, P]),
     "apt_vir_send_sizes": (c_int, [P, c_int64, P, c_int64, P, c_int, c_int64, c_int, P, P, P]),

@@ -473,6 +473,174 @@ static int launch_gat(bool vec, const int64_t* row, const void* ft, const void* 
   return APT_OK;
 }
 
+// ---- backward of the fused GAT edge pipeline: the edge part ---------------------------
+// Per destination row d and head h (s_e, a_e as in k_gat_rows, g = grad_out[d, h, :]):
+//   dot_e = <g, ft[src_e, h, :]>;  t = sum_e a_e dot_e;
+//   grad_s_e = a_e (dot_e - t) * (s_e > 0 ? 1 : slope);  grad_er[d, h] = sum_e grad_s_e
+// attn[e, h] = a_e and grad_score[e, h] = grad_s_e go out per edge; the sums over the
+// source side (grad_ft = sum a_e g, grad_el = sum grad_s_e) are SpMM calls in the
+// reverse direction. The lanes of one head (lanes_per_head of them, a power of two
+// inside the lane group) each hold a slice of g and of the ft row and meet in a
+// butterfly of shuffles for the dot product.
+template <typename T, int VE>
+__global__ void __launch_bounds__(256)
+k_gat_bwd_rows(const int64_t* __restrict__ row, const T* __restrict__ ft, const T* __restrict__ el,
+               const T* __restrict__ er, const T* __restrict__ grad_out, int num_heads, int64_t head_dim,
+               float slope, int64_t num_dst, SpmmWs ws, T* __restrict__ attn, T* __restrict__ grad_score,
+               T* __restrict__ grad_er, int group, int lanes_per_head, int32_t* status) {
+  const bool unsorted = *ws.flags != 0;
+  if (unsorted && blockIdx.x == 0 && threadIdx.x == 0) atomicOr(status, APT_FLAG_NOT_GROUPED);
+  const int lane = threadIdx.x & 31;
+  const int sub = lane % group;
+  const unsigned gmask = group == 32 ? 0xffffffffu : (((1u << group) - 1u) << (lane - sub));
+  const int64_t rows_per_block = blockDim.x / group;
+  const int64_t feat_dim = (int64_t)num_heads * head_dim;
+  const int64_t nvec = feat_dim / VE;
+  int64_t d = (int64_t)blockIdx.x * rows_per_block + threadIdx.x / group;
+  const int64_t stride = (int64_t)gridDim.x * rows_per_block;
+  for (; d < num_dst; d += stride) {
+    const int64_t e0 = unsorted ? 0 : ws.range[d];
+    const int64_t e1 = unsorted ? 0 : ws.range[d + 1];
+    for (int64_t c0 = 0; c0 < nvec; c0 += group) {
+      const int64_t c = c0 + sub;
+      const bool live = c < nvec;
+      const int h = live ? (int)((c * VE) / head_dim) : 0;
+      const bool leader = live && (c * VE) % head_dim == 0;
+      const float r = Elem<T>::to_f(er[d * num_heads + h]);
+      float m = -INFINITY;
+      for (int64_t e = e0; e < e1; ++e) {
+        float s = Elem<T>::to_f(el[row[e] * num_heads + h]) + r;
+        s = s > 0.f ? s : s * slope;
+        m = fmaxf(m, s);
+      }
+      float denom = 0.f;
+      for (int64_t e = e0; e < e1; ++e) {
+        float s = Elem<T>::to_f(el[row[e] * num_heads + h]) + r;
+        s = s > 0.f ? s : s * slope;
+        denom += expf(s - m);
+      }
+      const float inv = denom > 0.f ? 1.f / denom : 0.f;
+      float g[VE];
+#pragma unroll
+      for (int t = 0; t < VE; ++t) g[t] = 0.f;
+      if (live) {
+        const Pack<T, VE> p = load_pack<T, VE>(grad_out + d * feat_dim + c * VE);
+#pragma unroll
+        for (int t = 0; t < VE; ++t) g[t] = Elem<T>::to_f(p.v[t]);
+      }
+      // first walk: t = sum_e a_e dot_e; second walk: the per-edge results
+      float tsum = 0.f, ger = 0.f;
+      for (int pass = 0; pass < 2; ++pass) {
+        for (int64_t e = e0; e < e1; ++e) {
+          const int64_t src = row[e];
+          const float raw = Elem<T>::to_f(el[src * num_heads + h]) + r;
+          const float s = raw > 0.f ? raw : raw * slope;
+          const float a = expf(s - m) * inv;
+          float dot = 0.f;
+          if (live) {
+            const Pack<T, VE> p = load_pack<T, VE>(ft + src * feat_dim + c * VE);
+#pragma unroll
+            for (int t = 0; t < VE; ++t) dot += g[t] * Elem<T>::to_f(p.v[t]);
+          }
+          for (int o = lanes_per_head >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(gmask, dot, o, group);
+          if (pass == 0) {
+            tsum += a * dot;
+          } else {
+            const float gs = a * (dot - tsum) * (raw > 0.f ? 1.f : slope);
+            ger += gs;
+            if (leader) {
+              attn[e * num_heads + h] = Elem<T>::from_f(a);
+              grad_score[e * num_heads + h] = Elem<T>::from_f(gs);
+            }
+          }
+        }
+      }
+      if (leader) grad_er[d * num_heads + h] = Elem<T>::from_f(ger);
+    }
+  }
+}
+
+// Any head width: one thread per (destination, head), everything in turn.
+template <typename T>
+__global__ void __launch_bounds__(256)
+k_gat_bwd_generic(const int64_t* __restrict__ row, const T* __restrict__ ft, const T* __restrict__ el,
+                  const T* __restrict__ er, const T* __restrict__ grad_out, int num_heads, int64_t head_dim,
+                  float slope, int64_t num_dst, SpmmWs ws, T* __restrict__ attn, T* __restrict__ grad_score,
+                  T* __restrict__ grad_er, int32_t* status) {
+  const bool unsorted = *ws.flags != 0;
+  if (unsorted && blockIdx.x == 0 && threadIdx.x == 0) atomicOr(status, APT_FLAG_NOT_GROUPED);
+  const int64_t feat_dim = (int64_t)num_heads * head_dim;
+  const int64_t total = num_dst * num_heads;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t d = i / num_heads;
+    const int h = (int)(i - d * num_heads);
+    const int64_t e0 = unsorted ? 0 : ws.range[d];
+    const int64_t e1 = unsorted ? 0 : ws.range[d + 1];
+    const float r = Elem<T>::to_f(er[d * num_heads + h]);
+    float m = -INFINITY;
+    for (int64_t e = e0; e < e1; ++e) {
+      float s = Elem<T>::to_f(el[row[e] * num_heads + h]) + r;
+      s = s > 0.f ? s : s * slope;
+      m = fmaxf(m, s);
+    }
+    float denom = 0.f;
+    for (int64_t e = e0; e < e1; ++e) {
+      float s = Elem<T>::to_f(el[row[e] * num_heads + h]) + r;
+      s = s > 0.f ? s : s * slope;
+      denom += expf(s - m);
+    }
+    const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    const T* g = grad_out + d * feat_dim + (int64_t)h * head_dim;
+    float tsum = 0.f, ger = 0.f;
+    for (int pass = 0; pass < 2; ++pass) {
+      for (int64_t e = e0; e < e1; ++e) {
+        const int64_t src = row[e];
+        const float raw = Elem<T>::to_f(el[src * num_heads + h]) + r;
+        const float s = raw > 0.f ? raw : raw * slope;
+        const float a = expf(s - m) * inv;
+        const T* f = ft + src * feat_dim + (int64_t)h * head_dim;
+        float dot = 0.f;
+        for (int64_t k = 0; k < head_dim; ++k) dot += Elem<T>::to_f(g[k]) * Elem<T>::to_f(f[k]);
+        if (pass == 0) {
+          tsum += a * dot;
+        } else {
+          const float gs = a * (dot - tsum) * (raw > 0.f ? 1.f : slope);
+          ger += gs;
+          attn[e * num_heads + h] = Elem<T>::from_f(a);
+          grad_score[e * num_heads + h] = Elem<T>::from_f(gs);
+        }
+      }
+    }
+    grad_er[d * num_heads + h] = Elem<T>::from_f(ger);
+  }
+}
+
+template <typename T>
+static int launch_gat_bwd(bool vec, const int64_t* row, const void* ft, const void* el, const void* er,
+                          const void* grad_out, int num_heads, int64_t head_dim, float slope, int64_t num_dst,
+                          SpmmWs ws, void* attn, void* grad_score, void* grad_er, int32_t* status, cudaStream_t s) {
+  constexpr int VE = 16 / sizeof(T);
+  const int64_t feat_dim = (int64_t)num_heads * head_dim;
+  ProfScope prof("gat_bwd_rows", s);
+  const int64_t lph = head_dim / VE;                   // lanes per head when rows are read as 16-byte vectors
+  const bool pow2 = lph >= 1 && lph <= 32 && (lph & (lph - 1)) == 0;
+  if (vec && pow2) {
+    const int group = pow2_at_least_fwd(feat_dim / VE);
+    if (group % lph == 0) {
+      const int grid = wave_grid(ceil_div(num_dst, 256 / group), 8);
+      APT_LAUNCH((k_gat_bwd_rows<T, VE>), grid, 256, 0, s, row, (const T*)ft, (const T*)el, (const T*)er,
+                 (const T*)grad_out, num_heads, head_dim, slope, num_dst, ws, (T*)attn, (T*)grad_score, (T*)grad_er,
+                 group, (int)lph, status);
+      return APT_OK;
+    }
+  }
+  const int grid = wave_grid(ceil_div(num_dst * num_heads, 256), 8);
+  APT_LAUNCH((k_gat_bwd_generic<T>), grid, 256, 0, s, row, (const T*)ft, (const T*)el, (const T*)er,
+             (const T*)grad_out, num_heads, head_dim, slope, num_dst, ws, (T*)attn, (T*)grad_score, (T*)grad_er, status);
+  return APT_OK;
+}
+
 static int pow2_at_least(int64_t x) {
   int g = 1;
   while (g < x && g < 32) g <<= 1;
@@ -766,5 +934,55 @@ extern "C" int apt_gat_edge_softmax_sum(int dtype, const int64_t* coo_row, const
     default:
       return launch_gat<__half>(vec, coo_row, ft, el, er, num_heads, head_dim, negative_slope, num_dst, ws, out,
                                 out_attn, status_word, s);
+  }
+}
+
+extern "C" int apt_gat_edge_backward(int dtype, const int64_t* coo_row, const int64_t* coo_col, int64_t num_edges,
+                                     const void* ft, const void* el, const void* er, const void* grad_out,
+                                     int num_heads, int64_t head_dim, float negative_slope, int64_t num_dst,
+                                     void* out_attn, void* out_grad_score, void* out_grad_er, void* workspace,
+                                     size_t workspace_bytes, int32_t* status_word, void* stream) {
+  using namespace apt;
+  APT_CHECK_ARG(dtype >= APT_F32 && dtype <= APT_F16, "apt_gat_edge_backward: dtype %d", dtype);
+  APT_CHECK_ARG(num_edges >= 0 && num_heads >= 1 && head_dim >= 1 && num_dst >= 0, "apt_gat_edge_backward: bad sizes");
+  if (num_dst == 0) return APT_OK;
+  const size_t esz = elem_size(dtype);
+  const int64_t feat_dim = (int64_t)num_heads * head_dim;
+  cudaStream_t s = (cudaStream_t)stream;
+  APT_CHECK_ARG(out_grad_er && status_word, "apt_gat_edge_backward: null output");
+  if (num_edges == 0) {
+    APT_CUDA(cudaMemsetAsync(out_grad_er, 0, (size_t)num_dst * num_heads * esz, s));
+    return APT_OK;
+  }
+  APT_CHECK_ARG(coo_row && coo_col && ft && el && er && grad_out && out_attn && out_grad_score && workspace,
+                "apt_gat_edge_backward: null pointer");
+  APT_CHECK_ARG(((uintptr_t)workspace & 255) == 0, "apt_gat_edge_backward: workspace must be 256-byte aligned");
+  SpmmWs ws;
+  const size_t need = spmm_layout(num_dst, 0, (char*)workspace, &ws);
+  if (workspace_bytes < need) {
+    set_error("apt_gat_edge_backward: workspace %zu < %zu bytes", workspace_bytes, need);
+    return APT_ERR_CAPACITY;
+  }
+  APT_CUDA(cudaMemsetAsync(ws.flags, 0, 4, s));
+  // edges that name no valid destination keep zeros
+  APT_CUDA(cudaMemsetAsync(out_attn, 0, (size_t)num_edges * num_heads * esz, s));
+  APT_CUDA(cudaMemsetAsync(out_grad_score, 0, (size_t)num_edges * num_heads * esz, s));
+  {
+    ProfScope prof("spmm_ranges", s);
+    const int grid = wave_grid(ceil_div(num_edges, 256), 8);
+    APT_LAUNCH(k_edge_ranges_single, grid, 256, 0, s, coo_col, num_edges, num_dst, ws);
+  }
+  const int ve = 16 / (int)esz;
+  const bool vec = (((uint64_t)(feat_dim * esz) | (uintptr_t)ft | (uintptr_t)grad_out) & 15) == 0 && head_dim % ve == 0;
+  switch (dtype) {
+    case APT_F32:
+      return launch_gat_bwd<float>(vec, coo_row, ft, el, er, grad_out, num_heads, head_dim, negative_slope, num_dst,
+                                   ws, out_attn, out_grad_score, out_grad_er, status_word, s);
+    case APT_BF16:
+      return launch_gat_bwd<__nv_bfloat16>(vec, coo_row, ft, el, er, grad_out, num_heads, head_dim, negative_slope,
+                                           num_dst, ws, out_attn, out_grad_score, out_grad_er, status_word, s);
+    default:
+      return launch_gat_bwd<__half>(vec, coo_row, ft, el, er, grad_out, num_heads, head_dim, negative_slope,
+                                    num_dst, ws, out_attn, out_grad_score, out_grad_er, status_word, s);
   }
 }

@@ -789,6 +789,71 @@ def gat_edge_softmax_sum(coo_row, coo_col, ft, el, er, num_dst: int, negative_sl
     return (out, attn) if return_attention else out
 
 
+def _spmm_single(op, in_index, out_index, inp, edata, edim, feat_dim, num_in, num_out):
+    """apt_spmm_sum over one segment with the sizes known on the host (no read of an
+    offset tensor): out[out_index[e]] += f(inp[in_index[e]], edata[e])."""
+    ref = inp if inp is not None else edata
+    E = in_index.numel()
+    off = torch.tensor([0, E, 0, num_in, 0, num_out], dtype=torch.int64).to(ref.device, non_blocking=True)
+    out = torch.empty((num_out, feat_dim), dtype=ref.dtype, device=ref.device)
+    ws = STATE.workspace("spmm", lib.apt_spmm_workspace_bytes(num_out, E))
+    check(lib.apt_spmm_sum(op, _DTYPE_CODE[ref.dtype], _ptr(in_index), _ptr(out_index), E, _ptr(inp), _ptr(edata),
+                           int(edim), int(feat_dim), _ptr(off[0:2]), _ptr(off[2:4]), _ptr(off[4:6]), 1, int(num_out),
+                           _ptr(out), _ptr(ws), ws.numel(), _stream()))
+    return out
+
+
+def gat_edge_softmax_sum_backward(coo_row, coo_col, ft, el, er, grad_out, negative_slope: float = 0.2):
+    """Gradients of gat_edge_softmax_sum with respect to ft, el and er for
+    grad_out [num_dst, H, Dh]: one kernel over the destinations (softmax and
+    leaky_relu backward per edge, grad_er), then the two sums over the source side
+    as SpMM calls in the reverse direction. Returns (grad_ft, grad_el, grad_er)
+    shaped like ft, el, er."""
+    if ft.dtype not in _DTYPE_CODE or any(t.dtype != ft.dtype for t in (el, er, grad_out)):
+        raise RuntimeError("gat_edge_softmax_sum_backward: unsupported or mixed dtypes")
+    coo_row = _need_cuda(coo_row, "coo_row")
+    coo_col = _need_cuda(coo_col, "coo_col")
+    ft = _need_cuda(ft, "ft", dtype=None)
+    el = _need_cuda(el, "el", dtype=None)
+    er = _need_cuda(er, "er", dtype=None)
+    grad_out = _need_cuda(grad_out, "grad_out", dtype=None)
+    num_src, num_dst, E = ft.shape[0], grad_out.shape[0], coo_row.numel()
+    heads = el.numel() // max(num_src, 1) if num_src else er.numel() // max(num_dst, 1)
+    head_dim = ft.numel() // max(num_src * heads, 1)
+    dev, dt = ft.device, ft.dtype
+    attn = torch.empty((E, heads), dtype=dt, device=dev)
+    gscore = torch.empty((E, heads), dtype=dt, device=dev)
+    grad_er = torch.empty((num_dst, heads), dtype=dt, device=dev)
+    ws = STATE.workspace("spmm", lib.apt_spmm_workspace_bytes(num_dst, 0))
+    check(lib.apt_gat_edge_backward(_DTYPE_CODE[dt], _ptr(coo_row), _ptr(coo_col), E, _ptr(ft), _ptr(el), _ptr(er),
+                                    _ptr(grad_out), int(heads), int(head_dim), float(negative_slope), int(num_dst),
+                                    _ptr(attn), _ptr(gscore), _ptr(grad_er), _ptr(ws), ws.numel(),
+                                    STATE.status_ptr(), _stream()))
+    if E == 0 or num_src == 0:
+        return torch.zeros_like(ft), torch.zeros_like(el), grad_er.view(er.shape)
+    width = heads * head_dim
+    grad_ft = _spmm_single(2, coo_col, coo_row, grad_out.view(num_dst, width), attn, heads, width, num_dst, num_src)
+    grad_el = _spmm_single(1, coo_col, coo_row, None, gscore, heads, heads, num_dst, num_src)
+    return grad_ft.view(ft.shape), grad_el.view(el.shape), grad_er.view(er.shape)
+
+
+class GATEdgeSoftmaxSum(torch.autograd.Function):
+    """gat_edge_softmax_sum with its backward, for use inside a model:
+    ``out = GATEdgeSoftmaxSum.apply(coo_row, coo_col, ft, el, er, num_dst, slope)``."""
+
+    @staticmethod
+    def forward(ctx, coo_row, coo_col, ft, el, er, num_dst, negative_slope=0.2):
+        ctx.save_for_backward(coo_row, coo_col, ft, el, er)
+        ctx.slope = float(negative_slope)
+        return gat_edge_softmax_sum(coo_row, coo_col, ft, el, er, int(num_dst), float(negative_slope))
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        coo_row, coo_col, ft, el, er = ctx.saved_tensors
+        g_ft, g_el, g_er = gat_edge_softmax_sum_backward(coo_row, coo_col, ft, el, er, grad_out.contiguous(), ctx.slope)
+        return None, None, g_ft, g_el, g_er, None, None
+
+
 # ------------------------------------------------------------------ row movers
 def rows_gather(inp: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
     """out[i] = inp[index[i]] for 2-D inp (the model's h[inverse_idx],

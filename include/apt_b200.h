@@ -297,6 +297,23 @@ int apt_gat_edge_softmax_sum(int dtype, const int64_t* coo_row,
                              size_t workspace_bytes, int32_t* status_word,
                              void* stream);
 
+/* Edge part of the backward pass of apt_gat_edge_softmax_sum (what DGL's autograd
+ * runs for python/npc/model/gatconv.py:113-124), same block and layouts. With
+ * g = grad_out[d, h, :] ([num_dst, num_heads*head_dim]):
+ *   dot_e = <g, ft[row[e], h, :]>,  t = sum over d's edges of a_e dot_e,
+ *   grad_s_e = a_e (dot_e - t) * (el[row[e],h] + er[d,h] > 0 ? 1 : negative_slope)
+ * out_attn[e, h] = a_e, out_grad_score[e, h] = grad_s_e (both [num_edges, num_heads]),
+ * out_grad_er[d, h] = sum_e grad_s_e. The sums over the source side follow as
+ * apt_spmm_sum calls with row and col swapped: grad_ft = u_mul_e(grad_out, out_attn),
+ * grad_el = copy_e(out_grad_score). workspace: apt_spmm_workspace_bytes(num_dst, 0). */
+int apt_gat_edge_backward(int dtype, const int64_t* coo_row, const int64_t* coo_col,
+                          int64_t num_edges, const void* ft, const void* el,
+                          const void* er, const void* grad_out, int num_heads,
+                          int64_t head_dim, float negative_slope, int64_t num_dst,
+                          void* out_attn, void* out_grad_score, void* out_grad_er,
+                          void* workspace, size_t workspace_bytes,
+                          int32_t* status_word, void* stream);
+
 /* ------------------------------------------- SNP virtual nodes (SAGE / GCN)
  * The id arithmetic of the SNP strategy with virtual nodes: neighbour i of
  * local destination i / fanout, owned by rank o, becomes the virtual node

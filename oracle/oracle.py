@@ -399,6 +399,35 @@ def gat_edge_softmax_sum(row, col, ft, el, er, num_dst, negative_slope=0.2):
     return out, a
 
 
+def gat_edge_softmax_sum_backward(row, col, ft, el, er, grad_out, num_dst, negative_slope=0.2):
+    """Gradients of gat_edge_softmax_sum (the chain DGL's autograd runs for
+    python/npc/model/gatconv.py:113-124) in float64: with s = el[row] + er[col],
+    a = edge_softmax(leaky_relu(s)), out[col] += a * ft[row]:
+      grad_ft[row] += a * grad_out[col];   grad_a = <grad_out[col], ft[row]> per head;
+      grad_z = a * (grad_a - sum over the destination's edges of a * grad_a);
+      grad_s = grad_z * (1 if s > 0 else slope); grad_el[row] += grad_s; grad_er[col] += grad_s.
+    Returns (grad_ft, grad_el, grad_er, a, grad_s)."""
+    row = np.asarray(row, dtype=I64)
+    col = np.asarray(col, dtype=I64)
+    ft = np.asarray(ft, dtype=np.float64)
+    el = np.asarray(el, dtype=np.float64)
+    er = np.asarray(er, dtype=np.float64)
+    go = np.asarray(grad_out, dtype=np.float64)
+    _, a = gat_edge_softmax_sum(row, col, ft, el, er, num_dst, negative_slope)
+    s = el[row] + er[col]
+    grad_ft = np.zeros_like(ft)
+    np.add.at(grad_ft, row, a[:, :, None] * go[col])
+    grad_a = (go[col] * ft[row]).sum(-1)
+    t = np.zeros((num_dst, a.shape[1]))
+    np.add.at(t, col, a * grad_a)
+    grad_s = a * (grad_a - t[col]) * np.where(s > 0, 1.0, negative_slope)
+    grad_el = np.zeros_like(el)
+    np.add.at(grad_el, row, grad_s)
+    grad_er = np.zeros_like(er)
+    np.add.at(grad_er, col, grad_s)
+    return grad_ft, grad_el, grad_er, a, grad_s
+
+
 def sp_gat_sample(seeds_per_rank, fanout, min_vids, graph, key, call_id):
     """Outermost hop of the SNP-GAT sampler, python/npc/sampler.py:215-238, for all
     ranks at once: local sampling, sorted unique of the neighbours as block sources,
