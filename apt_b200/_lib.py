@@ -74,6 +74,10 @@ PROTOTYPES = {
     "apt_p2p_wait": (c_int, [P, P, P, c_int64, P]),
     "apt_p2p_pull": (c_int, [P, P, P, c_int, c_int64, c_int64, c_int64, P, P]),
     "apt_p2p_pull_sum": (c_int, [P, P, c_int, c_int64, c_int64, P, P, P]),
+    "apt_p2p_create_landing": (c_int, [c_int, c_int, c_size_t, c_size_t, c_int, ctypes.POINTER(P), P]),
+    "apt_p2p_landing_bytes": (c_size_t, [P]),
+    "apt_p2p_landing": (P, [P, c_int]),
+    "apt_p2p_push_direct": (c_int, [P, P, P, c_int, P, c_int64, c_int64, c_int, P, P]),
     "apt_p2p_alltoall_fused": (c_int, [P, P, P, c_int, P, P, P, c_int64, c_int64, c_int, P, P, c_int64, P]),
     "apt_rmat_edges": (c_int, [c_uint64, c_int64, c_int64, c_int, c_int64, c_float, c_float, c_float, P, P, P]),
     "apt_sort_u64_temp_bytes": (c_size_t, [c_int64]),

@@ -117,7 +117,8 @@ template <typename V>
 __global__ void __launch_bounds__(kMoveBlock)
 k_p2p_push(const char* __restrict__ src, const int64_t* __restrict__ src_index,
            int index_is_dest, const int64_t* __restrict__ send_offsets, int world_size,
-           int me, int64_t row_bytes, size_t region_bytes, PeerTable peers, int32_t* status) {
+           int me, int64_t row_bytes, size_t region_bytes, PeerTable peers, int32_t* status,
+           size_t landing_off /* 0: rows go to the inbox region */, size_t landing_bytes) {
   __shared__ int64_t soff[kP2pMaxRanks + 1];
   __shared__ bool is_last;
   // Every block reads the sequence number before it takes its ticket below, and
@@ -134,7 +135,16 @@ k_p2p_push(const char* __restrict__ src, const int64_t* __restrict__ src_index,
   const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int chunks = (int)(row_bytes / (int64_t)sizeof(V));
   const size_t slot_off = kHeaderBytes + ((size_t)parity * world_size + me) * region_bytes;
-  const int64_t cap_rows = (int64_t)(region_bytes / (size_t)row_bytes);
+  // Direct placement: the receiver has told this rank, in the all-to-all waited for last, the
+  // final row slot of every row it is about to get (8 bytes per row, in the inbox region of that
+  // receiver here). Rows then go straight to that slot of the receiver's landing buffer and no
+  // pull pass follows.
+  const bool direct = landing_off != 0;
+  const int64_t cap_rows = direct ? (int64_t)(region_bytes / 8) : (int64_t)(region_bytes / (size_t)row_bytes);
+  const int64_t landing_rows = direct ? (int64_t)(landing_bytes / (size_t)row_bytes) : 0;
+  const char* slot_lists = peers.base[me] + kHeaderBytes +
+                           (size_t)(*(const volatile uint32_t*)(peers.base[me] + kWaitSeqOffset) & 1u) *
+                               world_size * region_bytes;
   bool overflow = false;
   // Walking the stream in order would have every sender write to peer 0 first,
   // then peer 1, ...: all senders on one receiver's links at a time. Unless the
@@ -178,6 +188,14 @@ k_p2p_push(const char* __restrict__ src, const int64_t* __restrict__ src_index,
         const int64_t local = j - soff[r];
         if (local >= cap_rows) {
           overflow = true;
+        } else if (direct) {
+          const int64_t slot = ((const int64_t*)(slot_lists + (size_t)r * region_bytes))[local];
+          if (slot < 0 || slot >= landing_rows) {
+            overflow = true;
+          } else {
+            sp[k] = src + srow * row_bytes;
+            dp[k] = peers.base[r] + landing_off + slot * row_bytes;
+          }
         } else {
           sp[k] = src + srow * row_bytes;
           dp[k] = peers.base[r] + slot_off + local * row_bytes;
@@ -598,6 +616,8 @@ k_p2p_fused(FusedA2A a) {
 struct apt_p2p {
   int rank, world_size, device;
   size_t region_bytes, alloc_bytes;
+  size_t landing_bytes;   // bytes of one landing buffer (0: none)
+  int landing_slots;      // landing buffers behind the inbox, used in turn
   char* local_base;
   char* peer_base[apt::kP2pMaxRanks];
   bool peer_is_ipc[apt::kP2pMaxRanks];
@@ -614,15 +634,24 @@ extern "C" int apt_rows_scatter(const void* in, const int64_t* index, int64_t nu
 
 extern "C" int apt_p2p_create(int rank, int world_size, size_t region_bytes, apt_p2p** out_ctx,
                               void* out_handle) {
+  return apt_p2p_create_landing(rank, world_size, region_bytes, 0, 0, out_ctx, out_handle);
+}
+
+extern "C" int apt_p2p_create_landing(int rank, int world_size, size_t region_bytes, size_t landing_bytes,
+                                      int landing_slots, apt_p2p** out_ctx, void* out_handle) {
   using namespace apt;
   APT_CHECK_ARG(out_ctx && world_size >= 1 && world_size <= kP2pMaxRanks && rank >= 0 &&
                     rank < world_size && region_bytes > 0,
                 "apt_p2p_create: bad argument (rank %d of %d)", rank, world_size);
+  APT_CHECK_ARG(landing_slots >= 0 && landing_slots <= 64 && (landing_slots == 0) == (landing_bytes == 0),
+                "apt_p2p_create_landing: %d landing buffers of %zu bytes", landing_slots, landing_bytes);
   apt_p2p* c = new apt_p2p();
   c->rank = rank;
   c->world_size = world_size;
   c->region_bytes = align_up(region_bytes, 256);
-  c->alloc_bytes = kHeaderBytes + 2 * (size_t)world_size * c->region_bytes;
+  c->landing_bytes = align_up(landing_bytes, 256);
+  c->landing_slots = landing_slots;
+  c->alloc_bytes = kHeaderBytes + 2 * (size_t)world_size * c->region_bytes + (size_t)landing_slots * c->landing_bytes;
   for (int r = 0; r < kP2pMaxRanks; ++r) {
     c->peer_base[r] = nullptr;
     c->peer_is_ipc[r] = false;
@@ -670,6 +699,12 @@ extern "C" int apt_p2p_attach_ptr(apt_p2p* ctx, int peer, void* base) {
 
 extern "C" void* apt_p2p_local_base(apt_p2p* ctx) { return ctx ? ctx->local_base : nullptr; }
 extern "C" size_t apt_p2p_region_bytes(const apt_p2p* ctx) { return ctx ? ctx->region_bytes : 0; }
+extern "C" size_t apt_p2p_landing_bytes(const apt_p2p* ctx) { return ctx ? ctx->landing_bytes : 0; }
+extern "C" void* apt_p2p_landing(apt_p2p* ctx, int slot) {
+  if (!ctx || slot < 0 || slot >= ctx->landing_slots) return nullptr;
+  return ctx->local_base + apt::kHeaderBytes + 2 * (size_t)ctx->world_size * ctx->region_bytes +
+         (size_t)slot * ctx->landing_bytes;
+}
 
 extern "C" int apt_p2p_destroy(apt_p2p* ctx) {
   if (!ctx) return APT_OK;
@@ -680,9 +715,9 @@ extern "C" int apt_p2p_destroy(apt_p2p* ctx) {
   return APT_OK;
 }
 
-extern "C" int apt_p2p_push(apt_p2p* ctx, const void* src, const int64_t* src_index,
-                            int index_is_dest, const int64_t* send_offsets, int64_t max_rows, int64_t row_bytes,
-                            int32_t* status_word, void* stream) {
+static int p2p_push_launch(apt_p2p* ctx, const void* src, const int64_t* src_index, int index_is_dest,
+                           const int64_t* send_offsets, int64_t max_rows, int64_t row_bytes, size_t landing_off,
+                           int32_t* status_word, void* stream) {
   using namespace apt;
   APT_CHECK_ARG(ctx && send_offsets && status_word && row_bytes > 0 && max_rows >= 0, "apt_p2p_push: bad argument");
   APT_CHECK_ARG(max_rows == 0 || src, "apt_p2p_push: null source");
@@ -699,7 +734,8 @@ extern "C" int apt_p2p_push(apt_p2p* ctx, const void* src, const int64_t* src_in
   const char* sp = (const char*)src;
 #define APT_PUSH(V)                                                                       \
   APT_LAUNCH(k_p2p_push<V>, grid, kMoveBlock, 0, s, sp, src_index, index_is_dest, send_offsets,          \
-             ctx->world_size, ctx->rank, row_bytes, ctx->region_bytes, pt, status_word)
+             ctx->world_size, ctx->rank, row_bytes, ctx->region_bytes, pt, status_word, landing_off,     \
+             ctx->landing_bytes)
   switch (w) {
     case 16: APT_PUSH(uint4); break;
     case 8: APT_PUSH(uint2); break;
@@ -709,6 +745,25 @@ extern "C" int apt_p2p_push(apt_p2p* ctx, const void* src, const int64_t* src_in
   }
 #undef APT_PUSH
   return APT_OK;
+}
+
+extern "C" int apt_p2p_push(apt_p2p* ctx, const void* src, const int64_t* src_index,
+                            int index_is_dest, const int64_t* send_offsets, int64_t max_rows, int64_t row_bytes,
+                            int32_t* status_word, void* stream) {
+  return p2p_push_launch(ctx, src, src_index, index_is_dest, send_offsets, max_rows, row_bytes, 0, status_word,
+                         stream);
+}
+
+extern "C" int apt_p2p_push_direct(apt_p2p* ctx, const void* src, const int64_t* src_index, int index_is_dest,
+                                   const int64_t* send_offsets, int64_t max_rows, int64_t row_bytes,
+                                   int landing_slot, int32_t* status_word, void* stream) {
+  using namespace apt;
+  APT_CHECK_ARG(ctx && landing_slot >= 0 && landing_slot < ctx->landing_slots,
+                "apt_p2p_push_direct: landing buffer %d of %d", landing_slot, ctx ? ctx->landing_slots : 0);
+  const size_t off = kHeaderBytes + 2 * (size_t)ctx->world_size * ctx->region_bytes +
+                     (size_t)landing_slot * ctx->landing_bytes;
+  return p2p_push_launch(ctx, src, src_index, index_is_dest, send_offsets, max_rows, row_bytes, off, status_word,
+                         stream);
 }
 
 extern "C" int apt_p2p_wait(apt_p2p* ctx, int64_t* out_recv_counts, int32_t* status_word,

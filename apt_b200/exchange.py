@@ -156,12 +156,24 @@ class P2PExchange:
         self.chunks = max(1, min(8, int(os.environ.get("APT_P2P_CHUNKS", "1"))))
         self._off_dev = None
         self._off_host = None
+        # Direct placement (opt-in, APT_P2P_DIRECT=1): the feature shuffle writes every row to its
+        # final slot of a landing buffer on the receiving GPU, and the tensor it returns is a view of
+        # that buffer, valid until APT_P2P_DIRECT_SLOTS (default 4) further feature shuffles have run.
+        self.direct = os.environ.get("APT_P2P_DIRECT", "0") == "1"
+        self._landing_turn = 0
+        self._landing_views = {}
+        self._landing_slots = max(1, int(os.environ.get("APT_P2P_DIRECT_SLOTS", "4")))
         if ctx is not None:  # same-process ranks (tests): contexts are wired by the caller
             self.ctx = ctx
+            self.direct = self.direct and lib.apt_p2p_landing_bytes(ctx) > 0
             return
         handle = ctypes.create_string_buffer(_lib.IPC_HANDLE_BYTES)
         ctx_p = ctypes.c_void_p()
-        check(lib.apt_p2p_create(state.rank, state.world_size, int(region_bytes), ctypes.byref(ctx_p), handle))
+        landing_slots = self._landing_slots if self.direct else 0
+        landing_bytes = (int(os.environ.get("APT_P2P_LANDING_MB", "0")) << 20) or int(region_bytes)
+        check(lib.apt_p2p_create_landing(state.rank, state.world_size, int(region_bytes),
+                                         landing_bytes if landing_slots else 0, landing_slots,
+                                         ctypes.byref(ctx_p), handle))
         self.ctx = ctx_p
         handles = exchange_blobs(bytes(handle.raw), group)
         for r, h in enumerate(handles):
@@ -265,10 +277,61 @@ class P2PExchange:
         self._pull(counts_dev, None, 0, ws * n, ws * n, 8, recv)
         return recv, counts_dev
 
+    def _landing_view(self, slot, rows, width, dtype):
+        """The first rows x width elements of landing buffer `slot` as a tensor (no copy)."""
+        base = self._landing_views.get(slot)
+        if base is None:
+            nbytes = int(lib.apt_p2p_landing_bytes(self.ctx))
+            ptr = lib.apt_p2p_landing(self.ctx, slot)
+
+            class _Raw:
+                __cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (int(ptr), False),
+                                            "version": 2}
+
+            base = torch.as_tensor(_Raw(), device=self.state.device())
+            self._landing_views[slot] = base
+        esz = torch.empty(0, dtype=dtype).element_size()
+        return base[:rows * width * esz].view(dtype).view(rows, width)
+
+    def _exchange_rows_direct(self, inputs, send_offset, recv_offset, permutation, fwd):
+        """Two all-to-alls and no pull: the receiver sends each sender the final slot of every
+        row it will get (8 bytes per row), the senders then store the rows at those slots of the
+        receiver's landing buffer."""
+        st = self.state
+        ws = st.world_size
+        width = inputs.shape[1]
+        row_bytes = width * inputs.element_size()
+        total_recv = int(recv_offset[-1])
+        out_rows = permutation.numel() if fwd else total_recv
+        if out_rows * row_bytes > int(lib.apt_p2p_landing_bytes(self.ctx)):
+            raise RuntimeError(f"direct feature shuffle: {out_rows} rows of {row_bytes} bytes do not fit the landing "
+                               "buffer; raise APT_P2P_LANDING_MB (every rank must take the same path)")
+        self._check_capacity(max(_counts(recv_offset) + _counts(send_offset)), 8)
+        dev = inputs.device
+        if fwd:   # concatenation row p ends at the row i with permutation[i] == p
+            slots = torch.empty(total_recv, dtype=torch.int64, device=dev)
+            slots[permutation] = torch.arange(permutation.numel(), device=dev)
+        else:     # rows arrive in concatenation order
+            slots = torch.arange(total_recv, dtype=torch.int64, device=dev)
+        counts_dev = torch.empty(ws + 1, dtype=torch.int64, device=dev)
+        ask_off, _ = self._offsets_to_device(recv_offset)
+        self._push(slots, None, 0, ask_off, total_recv, 8)
+        self._wait(counts_dev)
+        slot = self._landing_turn
+        self._landing_turn = (slot + 1) % self._landing_slots
+        off_dev, _ = self._offsets_to_device(send_offset)
+        index, by_dest = (None, 0) if fwd else (permutation, 1)
+        check(lib.apt_p2p_push_direct(self.ctx, _ptr(inputs), _ptr(index), by_dest, _ptr(off_dev), inputs.shape[0],
+                                      int(row_bytes), slot, st.status_ptr(), _stream()))
+        self._wait(counts_dev)
+        return self._landing_view(slot, out_rows, width, inputs.dtype)
+
     def exchange_rows(self, inputs, send_offset, recv_offset, permutation, fwd):
         st = self.state
         ws = st.world_size
         row_bytes = inputs.shape[1] * inputs.element_size()
+        if self.direct and row_bytes % 16 == 0:
+            return self._exchange_rows_direct(inputs, send_offset, recv_offset, permutation, fwd)
         self._check_capacity(max(_counts(send_offset)), row_bytes)
         rows_in = inputs.shape[0]
         total_out = int(recv_offset[-1])

@@ -468,6 +468,26 @@ int apt_p2p_pull_sum(apt_p2p* ctx, const int64_t* recv_counts, int dtype,
                      int64_t num_rows, int64_t row_elems, void* dst,
                      int32_t* status_word, void* stream);
 
+/* Direct placement (opt-in): an inbox with landing_slots landing buffers of
+ * landing_bytes each behind it. The receiver first sends every sender, with an
+ * ordinary apt_p2p_push of 8-byte rows + apt_p2p_wait, the final row slot of each
+ * row it is about to get; apt_p2p_push_direct then stores row l for peer r at
+ * slot list[r][l] of r's landing buffer `landing_slot`, so that FeatShuffle's
+ * index_select / index_select_backward pass over the received rows
+ * (src/feat_shuffle.cc:13-28) needs no second kernel. After the apt_p2p_wait
+ * that follows, apt_p2p_landing(ctx, landing_slot) holds the result; it stays
+ * valid until that landing buffer is named again. All ranks must create their
+ * inboxes with the same sizes. Slots outside the buffer set APT_FLAG_TABLE_FULL. */
+int apt_p2p_create_landing(int rank, int world_size, size_t region_bytes,
+                           size_t landing_bytes, int landing_slots,
+                           apt_p2p** out_ctx, void* out_ipc_handle);
+size_t apt_p2p_landing_bytes(const apt_p2p* ctx);
+void* apt_p2p_landing(apt_p2p* ctx, int landing_slot);
+int apt_p2p_push_direct(apt_p2p* ctx, const void* src, const int64_t* src_index,
+                        int index_is_dest, const int64_t* send_offsets,
+                        int64_t max_rows, int64_t row_bytes, int landing_slot,
+                        int32_t* status_word, void* stream);
+
 /* The same all-to-all as push + wait + pull, as ONE cooperative kernel in which
  * the local pass (moving received rows to their final place) overlaps the
  * NVLink transfer: buckets are cut into `chunks` (1..8) row ranges, each with

@@ -292,6 +292,31 @@ def main():
                 assert np.array_equal(all_gb[r], want[r]), f"rank {r}: feat_shuffle bwd differs from the oracle"
     ops.check_status()
 
+    # --- opt-in direct placement: rows stored at their final slots of a landing buffer on the receiver,
+    # no pull pass; same bytes as the three-kernel path, forward and backward
+    from apt_b200.exchange import P2PExchange
+    os.environ.update(APT_P2P_DIRECT="1", APT_P2P_DIRECT_SLOTS="2", APT_P2P_LANDING_MB="64")
+    direct = P2PExchange(ops.STATE, 64 << 20)
+    os.environ.pop("APT_P2P_DIRECT")
+    assert direct.direct
+    for dtype, D in ((torch.float32, 256), (torch.bfloat16, 256)):
+        g = torch.Generator(device="cuda").manual_seed(7)
+        table = torch.randn((n, D), generator=g, device="cuda").to(dtype)
+        x = ops.rows_gather(table[uniq], inverse_idx)
+        grad = torch.randn((len(seeds), D), generator=g, device="cuda").to(dtype)
+        ops.STATE.exchange = p2p
+        want_y = ops.feat_shuffle(x, send_off, recv_off, perm, D, 1)
+        want_g = ops.feat_shuffle(grad, recv_off, send_off, perm, D, 0)
+        ops.STATE.exchange = direct
+        got_y = ops.feat_shuffle(x, send_off, recv_off, perm, D, 1)
+        got_g = ops.feat_shuffle(grad, recv_off, send_off, perm, D, 0)
+        assert torch.equal(got_y, want_y), "direct placement: forward shuffle differs"
+        assert torch.equal(got_g, want_g), "direct placement: backward shuffle differs"
+    ops.STATE.exchange = p2p
+    ops.check_status()
+    dist.barrier()
+    direct.close()
+
     # --- the small NP configuration of the benchmark list (2^20 nodes, 16 M R-MAT edges, fanout [25, 10],
     # 1024 seeds per rank): graph built on every GPU, whole mini-batch against the oracle replaying all ranks
     from apt_b200 import synthetic

@@ -320,3 +320,48 @@ def test_nfp_operators_single_rank(backend):
         if backend == "p2p":
             ex.close()
         reset_world()
+
+
+@pytest.mark.parametrize("dtype,D", [(torch.float32, 64), (torch.bfloat16, 256), (torch.float16, 1024)])
+def test_direct_placement_single_rank(dtype, D):
+    """Opt-in direct placement: the rows land at their final slots of a landing buffer and the
+    result is a view of it; same bytes as the push / wait / pull path, forward and backward."""
+    from apt_b200.exchange import P2PExchange
+
+    reset_world(1, 0)
+    s = apt_b200.STATE
+    c = ctypes.c_void_p()
+    check(lib.apt_p2p_create_landing(0, 1, 8 << 20, 8 << 20, 2, ctypes.byref(c), None))
+    ex = P2PExchange.__new__(P2PExchange)
+    P2PExchange.__init__(ex, s, 0, ctx=c)
+    ex._landing_slots = 2
+    s.exchange = ex
+    try:
+        g = torch.Generator(device="cuda").manual_seed(D)
+        n = 3000
+        x = torch.randn((n, D), generator=g, device="cuda").to(dtype)
+        perm = torch.randperm(n, generator=g, device="cuda")
+        off = torch.tensor([n])
+        ex.direct = False
+        want_f = ops.feat_shuffle(x, off, off, perm, D, 1)
+        want_b = ops.feat_shuffle(x, off, off, perm, D, 0)
+        ex.direct = True
+        got_f = ops.feat_shuffle(x, off, off, perm, D, 1)
+        assert torch.equal(got_f, want_f) and torch.equal(got_f, x[perm])
+        got_b = ops.feat_shuffle(x, off, off, perm, D, 0)
+        assert torch.equal(got_b, want_b)
+        # two landing buffers: the first result is still intact after the second call, and is
+        # overwritten by the third
+        assert torch.equal(got_f, x[perm])
+        y = torch.randn((n, D), generator=g, device="cuda").to(dtype)
+        got_f2 = ops.feat_shuffle(y, off, off, perm, D, 1)
+        assert got_f2.data_ptr() == got_f.data_ptr() and torch.equal(got_f, y[perm])
+        # a result that does not fit the landing buffer is refused on the host
+        big = torch.zeros((9 << 20) // (D * x.element_size()) + 1, D, dtype=dtype, device="cuda")
+        p2 = torch.arange(big.shape[0], device="cuda")
+        with pytest.raises(RuntimeError):
+            ops.feat_shuffle(big, torch.tensor([big.shape[0]]), torch.tensor([big.shape[0]]), p2, D, 1)
+        ops.check_status()
+    finally:
+        ex.close()
+        reset_world()
