@@ -55,7 +55,8 @@ PROTOTYPES = {
     "apt_gat_edge_backward": (c_int, [c_int, P, P, c_int64, P, P, P, P, c_int, c_int64, c_float, c_int64, P, P, P, P, c_size_t, P, P]),
     "apt_src_to_vir": (c_int, [P, c_int64, c_int64, c_int64, P, c_int, c_int, c_int, c_int, c_int, P, P]),
     "apt_srcdst_to_vir": (c_int, [P, c_int64, P, c_int64, c_int64, P, c_int, c_int, c_int, c_int, c_int, P, P]),
-    "apt_vir_send_sizes": (c_int, [P, c_int64, P, c_int64, P, c_int, c_int64, c_int, P, P, P]),
+    "apt_vir_send_sizes": (c_int, [P, c_int64, P, P, c_int64, P, c_int, c_int64, P, c_int, P, P, P]),
+    "apt_sp_map_place_pack": (c_int, [P, P, c_int64, P, c_int64, P, c_int, c_int, c_int, c_int, c_int, c_int64, c_int64, P, P, P, P]),
     "apt_sp_pack_frontier": (c_int, [P, P, c_int64, c_int64, c_int, c_int64, c_int64, P, P]),
     "apt_sp_unpack_frontier": (c_int, [P, c_int64, P, c_int64, P, P, P]),
     "apt_hotness_add": (c_int, [P, c_int64, P, P, c_int64, P, P]),

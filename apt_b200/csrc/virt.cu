@@ -45,13 +45,17 @@ __device__ __forceinline__ int64_t lower_bound_of(const int64_t* __restrict__ a,
 // (destinations, ids, uniques) per receiver.
 __global__ void __launch_bounds__(128)
 k_vir_send_sizes(const int64_t* __restrict__ sorted_nodes, int64_t num_sorted,
+                 const int64_t* __restrict__ num_sorted_dev,
                  const int64_t* __restrict__ unique_nodes, int64_t num_unique,
-                 const int64_t* __restrict__ num_unique_dev, int ws, int64_t base, int with_dst,
+                 const int64_t* __restrict__ num_unique_dev, int ws, int64_t base,
+                 const int64_t* __restrict__ base_dev, int with_dst,
                  int64_t* __restrict__ out_offset, int64_t* __restrict__ out_sizes) {
   __shared__ int64_t off[3 * kMaxRanks + 1];
   const int K = with_dst ? 2 * ws : ws;
   const int total = K + 1 + ws;
+  num_sorted = effective_n(num_sorted, num_sorted_dev);
   num_unique = effective_n(num_unique, num_unique_dev);
+  if (base_dev) base = *base_dev;
   for (int t = threadIdx.x; t < total; t += blockDim.x) {
     if (t <= K) off[t] = lower_bound_of(sorted_nodes, num_sorted, base * t);
     else off[t] = lower_bound_of(unique_nodes, num_unique, base * (int64_t)(K - ws + (t - K)));
@@ -87,6 +91,35 @@ k_sp_unpack(const int64_t* __restrict__ packed, int64_t n, const int64_t* __rest
     const int64_t q = v / num_total_nodes;
     out_vir[i] = q;
     out_ori[i] = v - q * num_total_nodes;
+  }
+}
+
+// The whole sender side of the virtual-node hop in one pass over the neighbours:
+// neighbour i (of destination i / fanout) has been given slot pos[i] by the stable owner
+// bucketing; its virtual id owner * num_dst + i / fanout and its packed triple
+// (sender, destination index, neighbour id) are written to that slot, which is the
+// order a stable sort of the virtual ids yields. num_dst may come from a device word
+// (what the previous relabelling produced); the number of neighbours is then
+// num_dst * fanout and is left in out_count for the kernels that follow.
+__global__ void __launch_bounds__(256)
+k_sp_map_place_pack(const int64_t* __restrict__ nbr, const int64_t* __restrict__ pos, int64_t num_dst,
+                    const int64_t* __restrict__ num_dst_dev, int64_t fanout,
+                    const int64_t* __restrict__ min_vids, OwnerParams p, int64_t rank_term,
+                    int64_t num_total_nodes, int64_t* __restrict__ sorted_vir,
+                    int64_t* __restrict__ packed, int64_t* __restrict__ out_count) {
+  __shared__ int64_t mv[kMaxRanks + 1];
+  if (threadIdx.x <= p.world_size) mv[threadIdx.x] = min_vids[threadIdx.x];
+  __syncthreads();
+  num_dst = effective_n(num_dst, num_dst_dev);
+  const int64_t n = num_dst * fanout;
+  if (out_count && blockIdx.x == 0 && threadIdx.x == 0) *out_count = n;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const int64_t v = nbr[i];
+    const int64_t d = i / fanout;
+    const int64_t slot = pos[i];
+    sorted_vir[slot] = (int64_t)owner_of(v, mv, p) * num_dst + d;
+    packed[slot] = rank_term + d * num_total_nodes + v;
   }
 }
 
@@ -138,10 +171,10 @@ extern "C" int apt_srcdst_to_vir(const int64_t* dst, int64_t num_dst, const int6
 }
 
 extern "C" int apt_vir_send_sizes(const int64_t* sorted_nodes, int64_t num_sorted,
-                                  const int64_t* unique_nodes, int64_t num_unique,
-                                  const int64_t* num_unique_dev, int world_size, int64_t base,
-                                  int with_dst, int64_t* out_send_offset, int64_t* out_send_sizes,
-                                  void* stream) {
+                                  const int64_t* num_sorted_dev, const int64_t* unique_nodes,
+                                  int64_t num_unique, const int64_t* num_unique_dev, int world_size,
+                                  int64_t base, const int64_t* base_dev, int with_dst,
+                                  int64_t* out_send_offset, int64_t* out_send_sizes, void* stream) {
   using namespace apt;
   APT_CHECK_ARG(world_size >= 1 && world_size <= kMaxRanks, "apt_vir_send_sizes: world_size %d outside [1,%d]",
                 world_size, kMaxRanks);
@@ -150,8 +183,8 @@ extern "C" int apt_vir_send_sizes(const int64_t* sorted_nodes, int64_t num_sorte
                 "apt_vir_send_sizes: null pointer");
   cudaStream_t s = (cudaStream_t)stream;
   ProfScope prof("vir_send_sizes", s);
-  APT_LAUNCH(k_vir_send_sizes, 1, 128, 0, s, sorted_nodes, num_sorted, unique_nodes, num_unique, num_unique_dev,
-             world_size, base, with_dst ? 1 : 0, out_send_offset, out_send_sizes);
+  APT_LAUNCH(k_vir_send_sizes, 1, 128, 0, s, sorted_nodes, num_sorted, num_sorted_dev, unique_nodes, num_unique,
+             num_unique_dev, world_size, base, base_dev, with_dst ? 1 : 0, out_send_offset, out_send_sizes);
   return APT_OK;
 }
 
@@ -186,5 +219,33 @@ extern "C" int apt_sp_unpack_frontier(const int64_t* packed, int64_t n, const in
   ProfScope prof("sp_unpack", s);
   APT_LAUNCH(k_sp_unpack, wave_grid(ceil_div(n, 256), 8), 256, 0, s, packed, n, n_dev, num_total_nodes, out_vir,
              out_ori);
+  return APT_OK;
+}
+
+extern "C" int apt_sp_map_place_pack(const int64_t* neighbors, const int64_t* positions, int64_t num_dst,
+                                     const int64_t* num_dst_dev, int64_t fanout, const int64_t* min_vids,
+                                     int world_size, int shuffle_id_offset, int rank, int node_beg, int node_end,
+                                     int64_t sp_base, int64_t num_total_nodes, int64_t* out_sorted_vir,
+                                     int64_t* out_packed, int64_t* out_count, void* stream) {
+  using namespace apt;
+  if (int rc = check_owner_args("apt_sp_map_place_pack", world_size, shuffle_id_offset, rank, node_beg, node_end))
+    return rc;
+  APT_CHECK_ARG(num_dst >= 0 && fanout >= 1 && sp_base > 0 && num_total_nodes > 0, "apt_sp_map_place_pack: bad sizes");
+  APT_CHECK_ARG(num_dst <= sp_base, "apt_sp_map_place_pack: %lld destinations exceed sp_base %lld",
+                (long long)num_dst, (long long)sp_base);
+  APT_CHECK_ARG((double)(rank + 1) * (double)sp_base * (double)num_total_nodes < 9.2e18,
+                "apt_sp_map_place_pack: packed id overflows 63 bits");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (num_dst == 0) {
+    if (out_count) APT_CUDA(cudaMemsetAsync(out_count, 0, 8, s));
+    return APT_OK;
+  }
+  APT_CHECK_ARG(neighbors && positions && min_vids && out_sorted_vir && out_packed,
+                "apt_sp_map_place_pack: null pointer");
+  ProfScope prof("sp_map_place_pack", s);
+  OwnerParams p{world_size, shuffle_id_offset, rank, node_beg, node_end};
+  APT_LAUNCH(k_sp_map_place_pack, wave_grid(ceil_div(num_dst * fanout, 256), 8), 256, 0, s, neighbors, positions,
+             num_dst, num_dst_dev, fanout, min_vids, p, (int64_t)rank * sp_base * num_total_nodes, num_total_nodes,
+             out_sorted_vir, out_packed, out_count);
   return APT_OK;
 }

@@ -74,6 +74,10 @@ class LocalExchange:
     def reduce_scatter(self, inp, seg_sizes, my_rows):
         return inp.clone()
 
+    def exchange_fixed(self, send, recv):
+        """All-to-all of one row of send[world_size, k] per peer into recv, stream-ordered."""
+        recv.copy_(send)
+
 
 class NcclExchange:
     """Baseline: the collective library's all-to-all-v."""
@@ -136,6 +140,9 @@ class NcclExchange:
         counts = [int(c) for c in seg_sizes.tolist()]
         buf = self._a2a(inp, counts, [int(my_rows)] * ws, inp.shape[1])
         return buf.view(ws, int(my_rows), inp.shape[1]).float().sum(0).to(inp.dtype)
+
+    def exchange_fixed(self, send, recv):
+        dist.all_to_all_single(recv, send.contiguous(), group=self.group)
 
 
 class P2PExchange:
@@ -409,6 +416,18 @@ class P2PExchange:
         check(lib.apt_p2p_pull_sum(self.ctx, _ptr(counts_dev), _DTYPE_CODE[inp.dtype], int(my_rows), width, _ptr(out),
                                    st.status_ptr(), _stream()))
         return out
+
+    def exchange_fixed(self, send, recv):
+        """All-to-all of one row of send[world_size, k] per peer into recv[world_size, k]; sizes
+        are the same everywhere, so nothing is read on the host."""
+        ws = self.state.world_size
+        if getattr(self, "_steps_dev", None) is None:
+            self._steps_dev = torch.arange(1, ws + 1, dtype=torch.int64, device=send.device)
+            self._fixed_counts = torch.empty(ws + 1, dtype=torch.int64, device=send.device)
+        row_bytes = send.shape[1] * send.element_size()
+        self._push(send, None, 0, self._steps_dev, ws, row_bytes)
+        self._wait(self._fixed_counts)
+        self._pull(self._fixed_counts, None, 0, ws, ws, row_bytes, recv)
 
     def close(self):
         if self.ctx is not None:

@@ -392,13 +392,19 @@ def unique_sorted(ids: torch.Tensor, id_lo: int, id_hi: int):
     return uniq[:num_unique], inv
 
 
-def _unique_enqueue(ids, n_dev, id_lo, id_hi, count_out):
+def _unique_enqueue(ids, n_dev, id_lo, id_hi, count_out, ws_name="unique"):
+    """`ws_name` picks the cached bitmap: callers that alternate between id ranges give
+    each range its own, so that none is cleared again on every call."""
     n = ids.numel()
     rng = int(id_hi) - int(id_lo)
     uniq = torch.empty(min(n, max(rng, 0)), dtype=torch.int64, device=ids.device)
     inv = torch.empty(n, dtype=torch.int64, device=ids.device)
     nbytes = lib.apt_unique_workspace_bytes(rng)
-    ws = STATE.workspace("unique", nbytes)
+    if ws_name != "unique":
+        # a bitmap of its own per id range: a captured graph that replays this call must find
+        # the layout it was captured with, whatever ran on the shared bitmap in between
+        ws_name = f"{ws_name}:{rng}"
+    ws = STATE.workspace(ws_name, nbytes)
     if getattr(ws, "_apt_clean_range", None) != rng:
         # the bitmap has to be zero once per id range (the layout follows the range);
         # every call then leaves it zero again
@@ -480,8 +486,8 @@ def vir_send_sizes(num_seeds: int, sorted_allnodes: torch.Tensor, unique_frontie
     k = 3 if shuffle_with_dst else 2
     sizes = torch.empty(k * ws, dtype=torch.int64, device=sorted_allnodes.device)
     offs = torch.empty(k * ws + 1, dtype=torch.int64, device=sorted_allnodes.device) if with_offsets else None
-    check(lib.apt_vir_send_sizes(_ptr(sorted_allnodes), sorted_allnodes.numel(), _ptr(unique_frontier),
-                                 unique_frontier.numel(), None, ws, int(num_seeds), int(bool(shuffle_with_dst)),
+    check(lib.apt_vir_send_sizes(_ptr(sorted_allnodes), sorted_allnodes.numel(), None, _ptr(unique_frontier),
+                                 unique_frontier.numel(), None, ws, int(num_seeds), None, int(bool(shuffle_with_dst)),
                                  _ptr(offs), _ptr(sizes), _stream()))
     return (sizes, offs) if with_offsets else sizes
 

@@ -19,6 +19,7 @@ from typing import List
 import torch
 
 from . import ops
+from ._lib import check, lib
 
 
 @dataclass
@@ -156,7 +157,7 @@ class MixedNeighborSampler:
         total = recv_counts[ws:ws + 1]
         lo, hi = ops._owned_range()
         u_slot, in_slot = slot, slot + 1
-        uniq2, inv = ops._unique_enqueue(recv, total, lo, hi, st.word(u_slot))
+        uniq2, inv = ops._unique_enqueue(recv, total, lo, hi, st.word(u_slot), "unique_np")
         nbr = ops._sample(uniq2, self.las_fanouts, st.word(u_slot), call if explicit else None, call_base_dev)
         uniq3, rel3 = ops._relabel_enqueue(uniq2, nbr, st.word(u_slot), st.word(in_slot))
         rows = None
@@ -298,14 +299,171 @@ class SPVirtualSampler:
     neighbours, its destinations the sorted unique received virtual nodes
     (`self.last["unique_dst"]`)."""
 
-    def __init__(self, rank: int, fanouts: List[int], model: str = "SAGE", shuffle_with_dst: bool = False):
+    def __init__(self, rank: int, fanouts: List[int], model: str = "SAGE", shuffle_with_dst: bool = False,
+                 chained: bool = None, use_graph: bool = None):
         if model not in ("SAGE", "GCN"):
             raise ValueError("SPVirtualSampler serves SAGE and GCN; GAT uses SPGATSampler")
         self.rank = rank
         self.fanouts = list(fanouts)
         self.model = model
         self.shuffle_with_dst = bool(shuffle_with_dst)
+        if chained is None:
+            chained = os.environ.get("APT_CHAINED_SAMPLER", "1") != "0"
+        # the chained form (no host read before the end of the mini-batch) covers the variant
+        # without destinations
+        self.chained = bool(chained) and not self.shuffle_with_dst
+        if use_graph is None:
+            use_graph = os.environ.get("APT_SAMPLER_GRAPH", "1") != "0"
+        self.use_graph = bool(use_graph) and self.chained
+        self._plans = {}
+        self._turn = 0
+        self._host_base = None
         self.last = {}
+
+    # word slots of the chained form: [0..13] hop counts, [16..48] ids received per peer (+ total),
+    # [50] neighbours, [51] unique virtual nodes, [52] unique received neighbours, [53] unique received
+    # virtual nodes, [128..191] send sizes, [192..253] receive sizes
+    _N, _UF, _US, _UD, _SEND, _RECV = 50, 51, 52, 53, 128, 192
+
+    def _enqueue(self, seeds: torch.Tensor, call_base_dev):
+        """Every kernel of the mini-batch on the current stream, no host read."""
+        st = ops.STATE
+        ws = st.world_size
+        dev = seeds.device
+        words = st.words()
+        explicit = call_base_dev is not None
+        slot = 0
+        call = 0
+        cur, cur_n = seeds, None
+        layers = []
+        for fanout in list(reversed(self.fanouts))[:-1]:
+            nbr = ops._sample(cur, fanout, cur_n, call if explicit else None, call_base_dev)
+            call += 1
+            cnt = st.word(slot)
+            uniq, rel = ops._relabel_enqueue(cur, nbr, cur_n, cnt)
+            layers.append((cur, rel, uniq, slot, fanout))
+            cur, cur_n = uniq, cnt
+            slot += 1
+        f = self.fanouts[0]
+        s_max = cur.numel()
+        n_max = s_max * f
+        nbr = ops._sample(cur, f, cur_n, call if explicit else None, call_base_dev)
+        n_word = None
+        if cur_n is not None:
+            n_word = st.word(self._N)
+            torch.mul(cur_n, f, out=n_word)
+        _, pos, _, _ = ops._bucket(nbr, n_word)
+        sorted_vir = torch.empty(n_max, dtype=torch.int64, device=dev)
+        packed = torch.empty(n_max, dtype=torch.int64, device=dev)
+        owner = ops._owner_args()
+        check(lib.apt_sp_map_place_pack(ops._ptr(nbr), ops._ptr(pos), s_max, ops._ptr(cur_n), f, *owner, ops.SP_BASE,
+                                        int(st.graph.num_total_nodes), ops._ptr(sorted_vir), ops._ptr(packed), None,
+                                        ops._stream()))
+        uf_word = st.word(self._UF)
+        unique_frontier, _ = ops._unique_enqueue(sorted_vir, n_word, 0, ws * max(s_max, 1), uf_word, "unique_vir")
+        send_sizes = words[self._SEND:self._SEND + 2 * ws]
+        recv_sizes = words[self._RECV:self._RECV + 2 * ws]
+        check(lib.apt_vir_send_sizes(ops._ptr(sorted_vir), n_max, ops._ptr(n_word), ops._ptr(unique_frontier),
+                                     unique_frontier.numel(), ops._ptr(uf_word), ws, s_max, ops._ptr(cur_n), 0, None,
+                                     ops._ptr(send_sizes), ops._stream()))
+        ex = ops._exchange()
+        ex.exchange_fixed(send_sizes.view(ws, 2), recv_sizes.view(ws, 2))
+        counts = words[16:16 + ws + 1]
+        if ws == 1:
+            recv = packed
+            counts[0:1].copy_(send_sizes[0:1])
+            counts[1:2].copy_(send_sizes[0:1])
+        else:
+            send_off = torch.cumsum(send_sizes[0::2], 0)
+            recv, _ = ex.exchange_ids_enqueue(packed, None, send_off, counts)
+        total = counts[ws:ws + 1]
+        vir_src = torch.empty(recv.numel(), dtype=torch.int64, device=dev)
+        ori_src = torch.empty(recv.numel(), dtype=torch.int64, device=dev)
+        check(lib.apt_sp_unpack_frontier(ops._ptr(recv), recv.numel(), ops._ptr(total), int(st.graph.num_total_nodes),
+                                         ops._ptr(vir_src), ops._ptr(ori_src), ops._stream()))
+        lo, hi = ops._owned_range()
+        unique_src, a_src = ops._unique_enqueue(ori_src, total, lo, hi, st.word(self._US), "unique_sp_src")
+        unique_dst, a_dst = ops._unique_enqueue(vir_src, total, 0, ws * ops.SP_BASE, st.word(self._UD), "unique_vdst")
+        div = cur_n if cur_n is not None else max(s_max, 1)
+        arange_dst = torch.remainder(unique_frontier, div)
+        return dict(layers=layers, slot=slot, cur=cur, nbr=nbr, sorted_vir=sorted_vir, packed=packed,
+                    unique_frontier=unique_frontier, arange_dst=arange_dst, vir_src=vir_src, ori_src=ori_src,
+                    unique_src=unique_src, a_src=a_src, unique_dst=unique_dst, a_dst=a_dst)
+
+    def _finish(self, seeds, b):
+        """The one host read of the mini-batch, then everything is narrowed to its real size."""
+        st = ops.STATE
+        ws = st.world_size
+        dev = seeds.device
+        f = self.fanouts[0]
+        host = st.read_words()
+        count = [int(host[k]) for k in range(b["slot"])]
+        blocks = []
+        n_dst = seeds.numel()
+        for dst_buf, rel, uniq, u_s, fanout in b["layers"]:
+            n_src = count[u_s]
+            blocks.insert(0, Block(rel[:n_dst * fanout], _coo_col(dst_buf.numel(), n_dst, fanout, dev), n_src, n_dst,
+                                   uniq[:n_src], fanout))
+            n_dst = n_src
+        num_dst = n_dst
+        n_uf, n_us, n_ud = int(host[self._UF]), int(host[self._US]), int(host[self._UD])
+        n_recv = int(host[16 + ws])
+        send_sizes_cpu = host[self._SEND:self._SEND + 2 * ws].clone()
+        recv_sizes_cpu = host[self._RECV:self._RECV + 2 * ws].clone()
+        unique_frontier, unique_src = b["unique_frontier"], b["unique_src"]
+        block1 = Block(torch.arange(n_uf, device=dev), b["arange_dst"][:n_uf], n_uf, num_dst, unique_frontier[:n_uf], f)
+        block2 = Block(b["a_src"][:n_recv], b["a_dst"][:n_recv], n_us, n_ud, unique_src[:n_us], f)
+        blocks.insert(0, block1)
+        blocks.insert(0, block2)
+        dst_nodes = b["cur"][:num_dst]
+        self.last = dict(neighbors=b["nbr"][:num_dst * f], sorted_allnodes=b["sorted_vir"][:num_dst * f],
+                         unique_frontier=unique_frontier[:n_uf], send_frontier=b["packed"][:num_dst * f], recv_dst=None,
+                         vir_src=b["vir_src"][:n_recv], ori_src=b["ori_src"][:n_recv],
+                         unique_dst=b["unique_dst"][:n_ud])
+        nxt = unique_src[:n_us] if self.model == "GCN" else torch.cat((dst_nodes, unique_src[:n_us]))
+        return nxt, seeds, blocks, send_sizes_cpu, recv_sizes_cpu
+
+    def _plan_for(self, seeds):
+        st = ops.STATE
+        key = (seeds.numel(), seeds.device)
+        ring = self._plans.setdefault(key, [None] * 2)
+        i = self._turn % 2
+        self._turn += 1
+        plan = ring[i]
+        if plan is not None and plan.generation == st.generation:
+            return plan
+        plan = _Plan()
+        plan.generation = st.generation
+        plan.seeds_buf = torch.empty_like(seeds)
+        plan.seeds_buf.copy_(seeds)
+        base_dev = st.word(_CALL_BASE_SLOT)
+        # one eager run first: it sizes the cached workspaces and surfaces errors outside capture
+        bufs = self._enqueue(plan.seeds_buf, base_dev)
+        st.read_words()
+        del bufs
+        plan.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(plan.graph):
+            plan.bufs = self._enqueue(plan.seeds_buf, base_dev)
+        plan.keepalive = list(st._ws.values())
+        ring[i] = plan
+        return plan
+
+    def _sample_chained(self, seeds: torch.Tensor):
+        st = ops.STATE
+        if st.world_size > 31 or len(self.fanouts) > 14:
+            raise RuntimeError("the chained SNP sampler serves at most 31 ranks and 14 hops")
+        seeds = ops._need_cuda(seeds, "seeds")
+        if not self.use_graph or st.profiling:
+            return self._finish(seeds, self._enqueue(seeds, None))
+        if self._host_base is None:
+            self._host_base = torch.zeros(1, dtype=torch.int64).pin_memory()
+        self._host_base[0] = st.sample_calls
+        st.word(_CALL_BASE_SLOT).copy_(self._host_base, non_blocking=True)
+        plan = self._plan_for(seeds)
+        plan.seeds_buf.copy_(seeds)
+        plan.graph.replay()
+        st.sample_calls += len(self.fanouts)
+        return self._finish(seeds, plan.bufs)
 
     def _outer(self, seeds, neighbors, fanout):
         st = ops.STATE
@@ -355,6 +513,8 @@ class SPVirtualSampler:
         return nxt, block1, block2, send_sizes, recv_sizes
 
     def sample(self, graph, seeds: torch.Tensor):
+        if self.chained and ops._exchange().name in ("local", "p2p"):
+            return self._sample_chained(seeds)
         output_nodes = seeds
         blocks = []
         for layer_id, fanout in enumerate(reversed(self.fanouts)):

@@ -332,7 +332,8 @@ int apt_gat_edge_backward(int dtype, const int64_t* coo_row, const int64_t* coo_
  *                     null): int64[(with_dst ? 3 : 2) * world_size + 1] lower bounds;
  *                     out_send_sizes: per receiver r (ids, unique virtual nodes) or
  *                     (destinations, ids, unique virtual nodes) bound for r.
- *                     num_unique_dev (may be null) overrides num_unique on the device.
+ *                     num_sorted_dev, num_unique_dev and base_dev (each may be null)
+ *                     override num_sorted, num_unique and base on the device.
  * apt_sp_pack_frontier   out[i] = rank * sp_base * num_total_nodes
  *                     + (sorted_vir[i] % num_dst) * num_total_nodes + sorted_ids[i],
  *                     the packed triple of python/npc/sampler.py:296-300.
@@ -349,10 +350,25 @@ int apt_srcdst_to_vir(const int64_t* dst, int64_t num_dst, const int64_t* src,
                       int world_size, int shuffle_id_offset, int rank,
                       int node_beg, int node_end, int64_t* out_vir, void* stream);
 int apt_vir_send_sizes(const int64_t* sorted_nodes, int64_t num_sorted,
+                       const int64_t* num_sorted_dev,
                        const int64_t* unique_nodes, int64_t num_unique,
                        const int64_t* num_unique_dev, int world_size,
-                       int64_t base, int with_dst, int64_t* out_send_offset,
-                       int64_t* out_send_sizes, void* stream);
+                       int64_t base, const int64_t* base_dev, int with_dst,
+                       int64_t* out_send_offset, int64_t* out_send_sizes,
+                       void* stream);
+/* The sender side of the hop in one pass (python/npc/sampler.py:255-300 without
+ * destinations): with positions = out_perm of apt_bucket_by_owner over the
+ * neighbours, out_sorted_vir[positions[i]] = owner(neighbors[i]) * num_dst +
+ * i / fanout (the stably sorted virtual ids) and out_packed[positions[i]] = the
+ * packed triple of apt_sp_pack_frontier. num_dst_dev (may be null) overrides
+ * num_dst on the device; out_count (may be null) receives num_dst * fanout. */
+int apt_sp_map_place_pack(const int64_t* neighbors, const int64_t* positions,
+                          int64_t num_dst, const int64_t* num_dst_dev,
+                          int64_t fanout, const int64_t* min_vids, int world_size,
+                          int shuffle_id_offset, int rank, int node_beg,
+                          int node_end, int64_t sp_base, int64_t num_total_nodes,
+                          int64_t* out_sorted_vir, int64_t* out_packed,
+                          int64_t* out_count, void* stream);
 int apt_sp_pack_frontier(const int64_t* sorted_vir, const int64_t* sorted_ids,
                          int64_t n, int64_t num_dst, int rank, int64_t sp_base,
                          int64_t num_total_nodes, int64_t* out, void* stream);

@@ -99,9 +99,9 @@ def test_pack_and_unpack_round_trip():
         reset_world()
 
 
-@pytest.mark.parametrize("with_dst", [False, True])
+@pytest.mark.parametrize("with_dst,chained", [(False, True), (False, False), (True, False)])
 @pytest.mark.parametrize("model", ["SAGE", "GCN"])
-def test_outermost_hop_with_one_rank(with_dst, model):
+def test_outermost_hop_with_one_rank(with_dst, chained, model):
     n, indptr, indices = small_graph(scale=11, edge_factor=6)
     reset_world()
     install_graph(indptr, indices)
@@ -110,7 +110,8 @@ def test_outermost_hop_with_one_rank(with_dst, model):
     rng = np.random.default_rng(11)
     seeds = rng.permutation(n)[:300].astype(I64)
     fanout = 7
-    sampler = SPVirtualSampler(0, [fanout], model=model, shuffle_with_dst=with_dst)
+    sampler = SPVirtualSampler(0, [fanout], model=model, shuffle_with_dst=with_dst, chained=chained)
+    assert sampler.chained == chained
     input_nodes, output_nodes, blocks, send_sizes, recv_sizes = sampler.sample(None, dev(seeds))
     want = orc.sp_virtual_sample([seeds], fanout, mv, (None, None, None, indptr, indices), key=77, call_id=5,
                                  num_total_nodes=n, with_dst=with_dst, model=model)[0]
@@ -156,5 +157,40 @@ def test_outermost_hop_with_one_rank(with_dst, model):
                               one(0, block1.num_dst))
     direct = x[want["neighbors"]].reshape(len(seeds), fanout, 16).astype(np.float64).sum(1)
     assert np.abs(host(out) - direct).max() <= 1e-4
+    ops.check_status()
+    reset_world()
+
+
+def test_chained_sampler_equals_operator_by_operator_form():
+    # three hops, three mini-batches: the chained form (sizes stay on the device, one host read per
+    # mini-batch), replayed from a CUDA graph or enqueued kernel by kernel, gives what the
+    # operator-by-operator form gives
+    n, indptr, indices = small_graph(scale=12, edge_factor=8)
+    reset_world()
+    install_graph(indptr, indices)
+    _world(1, 0, n)
+    rng = np.random.default_rng(21)
+    batches = [dev(rng.permutation(n)[:128].astype(I64)) for _ in range(3)]
+    outs = []
+    for chained, use_graph in ((True, True), (True, False), (False, False)):
+        ops.set_sampling(key=5, call_id=0)
+        smp = SPVirtualSampler(0, [6, 4, 3], model="SAGE", chained=chained, use_graph=use_graph)
+        assert smp.use_graph == use_graph
+        res = []
+        for seeds in batches:
+            out = smp.sample(None, seeds)
+            res.append((out, {k: (v.clone() if v is not None else None) for k, v in smp.last.items()},
+                        [(b.coo_row.clone(), b.coo_col.clone(), b.src_ids.clone(), b.num_src, b.num_dst) for b in out[2]],
+                        out[0].clone()))
+        outs.append(res)
+    for other in outs[1:]:
+        for (a, la, ba, ia), (b, lb, bb, ib) in zip(outs[0], other):
+            assert torch.equal(ia, ib) and torch.equal(a[3], b[3]) and torch.equal(a[4], b[4])
+            assert len(ba) == len(bb) == 4
+            for x, y in zip(ba, bb):
+                assert x[3:] == y[3:] and all(torch.equal(p, q) for p, q in zip(x[:3], y[:3]))
+            for k in ("neighbors", "sorted_allnodes", "unique_frontier", "send_frontier", "vir_src", "ori_src",
+                      "unique_dst"):
+                assert torch.equal(la[k], lb[k]), k
     ops.check_status()
     reset_world()
