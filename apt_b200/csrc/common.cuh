@@ -55,6 +55,8 @@ struct ProfScope {
     }                                                                         \
   } while (0)
 
+void set_relabel_small(bool on);   // relabel.cu: one-block shared-memory path for small layers
+
 constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }

@@ -350,6 +350,8 @@ extern "C" int apt_set_tunable(const char* name, int64_t value) {
     g_miss_blocks = (int)value;
   } else if (!strcmp(name, "gather_hit_waves") && value >= 1 && value <= 64) {
     g_hit_waves = (int)value;
+  } else if (!strcmp(name, "relabel_small") && value >= 0 && value <= 1) {
+    set_relabel_small(value != 0);
   } else {
     set_error("apt_set_tunable: unknown name or bad value: %s = %lld", name, (long long)value);
     return APT_ERR_BAD_ARG;

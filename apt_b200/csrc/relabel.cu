@@ -16,6 +16,9 @@
 //   k_relabel  neighbours -> new id through the remembered slot; every item
 //              also empties its slot again
 //
+// Layers of up to 8192 items run in one block with the table in shared memory
+// (k_relabel_small below).
+//
 // The table is empty between calls (apt_relabel_workspace_init empties it once,
 // each call empties the slots it used), so a call costs what its own item count
 // costs and no clearing pass is needed.
@@ -191,6 +194,73 @@ k_relabel(int64_t S_host, int64_t M_host, const int64_t* __restrict__ S_dev, int
   }
 }
 
+// ---- small layers: the whole relabelling in one block, table in shared memory ----------
+// Up to kSmallItems items (the innermost hops of a mini-batch: 1024 seeds x (1 + 5)) fit a
+// table of kSmallCap 16-byte slots in the 227 KB of shared memory of one SM together with
+// each item's slot number. One block of 1024 threads then runs the three phases (insert,
+// ordered compaction, relabel) with block barriers between them: no global table traffic,
+// no clearing, one launch instead of four. The order of first occurrence is decided by
+// the minimum position per id exactly as in the multi-block path, so both give the same
+// arrays.
+static bool g_relabel_small = true;   // apt_set_tunable("relabel_small", 0) forces the multi-block path
+void set_relabel_small(bool on) { g_relabel_small = on; }
+
+constexpr int kSmallItems = 8192;
+constexpr uint32_t kSmallCap = 12288;
+constexpr size_t kSmallSmem = (size_t)kSmallCap * sizeof(Slot) + (size_t)kSmallItems * sizeof(uint16_t);
+
+__global__ void __launch_bounds__(kRelabelBlock)
+k_relabel_small(const int64_t* __restrict__ seeds, int64_t S_host, const int64_t* __restrict__ nbrs,
+                int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed,
+                int64_t* __restrict__ out_unique, int64_t* __restrict__ out_relabeled,
+                int64_t* __restrict__ out_num_unique) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  __shared__ int scratch[33];
+  Slot* slots = (Slot*)smem;
+  uint16_t* slot_of = (uint16_t*)(smem + (size_t)kSmallCap * sizeof(Slot));
+  const RelabelDims d = relabel_dims(S_host, M_host, S_dev, per_seed);
+  const int n = (int)d.n;
+  for (uint32_t t = threadIdx.x; t < kSmallCap; t += blockDim.x) {
+    slots[t].key = kEmptyKey;
+    slots[t].min_pos = kNoPos;
+    slots[t].new_id = 0;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const unsigned long long key = (unsigned long long)item_at(seeds, d.S, nbrs, i);
+    uint32_t pos = (uint32_t)(((uint64_t)hash_id((int64_t)key) * kSmallCap) >> 32);
+    for (;;) {   // at most kSmallItems of the kSmallCap slots are ever taken: an empty one is found
+      Slot* s = slots + pos;
+      unsigned long long prev = *(volatile unsigned long long*)&s->key;
+      if (prev == kEmptyKey) prev = atomicCAS(&s->key, kEmptyKey, key);
+      if (prev == kEmptyKey || prev == key) {
+        atomicMin(&s->min_pos, (uint32_t)i);
+        slot_of[i] = (uint16_t)pos;
+        break;
+      }
+      pos = pos + 1 == kSmallCap ? 0 : pos + 1;
+    }
+  }
+  __syncthreads();
+  int running = 0;
+  for (int base = 0; base < n; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    const int f = i < n && slots[slot_of[i]].min_pos == (uint32_t)i;
+    int total;
+    const int ex = block_exclusive_scan(f, scratch, &total);
+    if (f) {
+      const int id = running + ex;
+      out_unique[id] = item_at(seeds, d.S, nbrs, i);
+      slots[slot_of[i]].new_id = (uint32_t)id;
+    }
+    running += total;
+  }
+  if (threadIdx.x == 0) *out_num_unique = running;
+  __syncthreads();
+  for (int i = (int)d.S + threadIdx.x; i < n; i += blockDim.x)
+    out_relabeled[i - d.S] = (int64_t)slots[slot_of[i]].new_id;
+}
+
 }  // namespace apt
 
 extern "C" size_t apt_relabel_workspace_bytes(int64_t num_items) {
@@ -232,6 +302,19 @@ extern "C" int apt_relabel_csc(const int64_t* seeds, int64_t num_seeds,
                     out_unique && workspace,
                 "apt_relabel_csc: null pointer");
   APT_CHECK_ARG(((uintptr_t)workspace & 255) == 0, "apt_relabel_csc: workspace must be 256-byte aligned");
+  if (n <= kSmallItems && g_relabel_small) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    APT_CUDA(cudaGetDevice(&dev));
+    if (dev < 64 && !attr_set[dev]) {
+      APT_CUDA(cudaFuncSetAttribute(k_relabel_small, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmallSmem));
+      attr_set[dev] = true;
+    }
+    ProfScope prof("relabel", s);
+    APT_LAUNCH(k_relabel_small, 1, kRelabelBlock, kSmallSmem, s, seeds, num_seeds, neighbors, num_neighbors,
+               num_seeds_dev, per_seed, out_unique, out_relabeled, out_num_unique);
+    return APT_OK;
+  }
   RelabelWs ws;
   if (!relabel_layout((char*)workspace, workspace_bytes, &ws) || ws.items_ws < n) {
     set_error("apt_relabel_csc: workspace of %zu bytes holds %lld items, %lld needed (apt_relabel_workspace_bytes)",

@@ -692,7 +692,22 @@ def main():
     torch.cuda.nvtx.range_pop()
     barrier()
     ms = reduce_max(ev0.elapsed_time(ev1))
+    graph_mode = bool(sampler._graph_ok())
     value = world * args.steps / (ms / 1000.0)
+    ops.check_status()
+
+    # ---- spread of the single steps: an event pair around each of up to 100 of the same steps
+    n_spread = min(args.steps, 100)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(n_spread + 1)]
+    barrier()
+    marks[0].record()
+    for k, b in enumerate(dev_batches[args.warmup:args.warmup + n_spread]):
+        step(b)
+        marks[k + 1].record()
+    barrier()
+    per_step = sorted(marks[k].elapsed_time(marks[k + 1]) for k in range(n_spread))
+    spread = {"steps": n_spread, "median": per_step[n_spread // 2], "p10": per_step[n_spread // 10],
+              "p90": per_step[min(n_spread - 1, (9 * n_spread) // 10)]}
     ops.check_status()
 
     # ---- the same steps once more with per-kernel CUDA events (for the roofline and the
@@ -793,8 +808,9 @@ def main():
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int64 ids, " + w.dtype + " rows", "data": "synthetic", "config": config, "clocks": clock_info,
         "e2e": e2e, "gpu_launches": int(reduce_sum(launches)),
-        "launch_mode": "one CUDA graph replay per mini-batch" if (world == 1 and sampler.use_graph) else
+        "launch_mode": "one CUDA graph replay per mini-batch" if graph_mode else
                        "kernels enqueued one by one, sizes chained on the device",
+        "step_ms_spread": spread,
         "profiled_value": world * args.steps / (ms_prof / 1000.0),
         "roofline": roofline, "roofline_link": roofline_link,
         "per_step": {"gathered_rows": rows_total / args.steps, "cache_hit_rate": hits_total / max(rows_total, 1),

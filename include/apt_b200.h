@@ -75,7 +75,9 @@ int apt_profile_read(const char* tag, double* total_ms, int64_t* launches);
  *   gather_miss_mode   0 16-byte ld.global.nc loads (default),
  *                      1 bulk copies (cp.async.bulk) staged through shared memory
  *   gather_miss_blocks blocks of the miss-copy kernel (default 148)
- *   gather_hit_waves   cap on the hit-copy grid, in waves of 148 x 8 blocks (default 4) */
+ *   gather_hit_waves   cap on the hit-copy grid, in waves of 148 x 8 blocks (default 4)
+ *   relabel_small      1 (default): layers of up to 8192 items are relabelled by one block with
+ *                      the hash table in shared memory; 0: always the multi-block path */
 int apt_set_tunable(const char* name, int64_t value);
 
 /* ------------------------------------------------------------------ sampling

@@ -1,5 +1,5 @@
 """Multi-GPU parity of the seed and feature shuffle over real peer-to-peer
-links: spawns one process per GPU (2, or 4 when the box has them). Skipped on a
+links: spawns one process per GPU (2, then 4 and 8 when the box has them). Skipped on a
 single-GPU box; the same protocol is covered there by the emulated ranks of
 tests/test_gpu_shuffle.py."""
 import os
@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_np_shuffle_across_gpus(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")

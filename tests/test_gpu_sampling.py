@@ -8,6 +8,7 @@ import torch
 
 import apt_b200
 from apt_b200 import ops
+from apt_b200._lib import check, lib
 from oracle import oracle as orc
 from tests.gpu_util import dev, host, install_graph, reset_world
 from tests.helpers import small_graph
@@ -115,6 +116,26 @@ def test_relabel_matches_oracle(S, f, hi):
     uniq, rel = ops.relabel_csc(dev(seeds), dev(nbrs))
     wu, wr = orc.relabel_csc(seeds, nbrs)
     assert np.array_equal(host(uniq), wu) and np.array_equal(host(rel), wr)
+
+
+@pytest.mark.parametrize("S,f", [(1, 1), (1024, 5), (1024, 7), (1170, 6), (1171, 6), (3000, 1)])
+def test_relabel_one_block_path_equals_multi_block_path(S, f):
+    # layers of up to 8192 items run in one block with the table in shared memory; the same
+    # call with that path switched off must give the same arrays (8190 and 8197 items straddle the limit)
+    rng = np.random.default_rng(S * 31 + f)
+    seeds = dev(rng.integers(0, 4000, S).astype(I64))
+    nbrs = dev(rng.integers(0, 4000, S * f).astype(I64))
+    outs = []
+    for small in (1, 0):
+        check(lib.apt_set_tunable(b"relabel_small", small))
+        try:
+            outs.append(ops.relabel_csc(seeds, nbrs))
+        finally:
+            check(lib.apt_set_tunable(b"relabel_small", 1))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    wu, wr = orc.relabel_csc(host(seeds), host(nbrs))
+    assert np.array_equal(host(outs[0][0]), wu) and np.array_equal(host(outs[0][1]), wr)
+    ops.check_status()
 
 
 def test_relabel_edge_cases():
