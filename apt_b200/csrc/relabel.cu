@@ -184,13 +184,16 @@ k_relabel(int64_t S_host, int64_t M_host, const int64_t* __restrict__ S_dev, int
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (; i < d.n; i += stride) {
     const int32_t slot = ws.slot_of[i];
-    if (i >= d.S) out[i - d.S] = slot >= 0 ? (int64_t)ws.slots[slot].new_id : -1;
-    // Nothing reads keys or positions any more (this kernel only reads new_id):
-    // every item empties the slot it used; items of one id write the same values.
-    if (slot >= 0) {
-      ws.slots[slot].key = kEmptyKey;
-      ws.slots[slot].min_pos = kNoPos;
+    if (slot < 0) {
+      if (i >= d.S) out[i - d.S] = -1;
+      continue;
     }
+    // one 16-byte load brings the new id and the position of the id's first occurrence
+    const uint4 v = ld_plain_16((const uint4*)(ws.slots + slot));
+    if (i >= d.S) out[i - d.S] = (int64_t)v.w;
+    // Nothing reads keys any more and only the first occurrence itself compares positions:
+    // that item empties the slot with one 16-byte store (the new id stays for the others).
+    if (v.z == (uint32_t)i) st_plain_16((uint4*)(ws.slots + slot), make_uint4(0xffffffffu, 0xffffffffu, kNoPos, v.w));
   }
 }
 
