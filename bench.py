@@ -154,7 +154,9 @@ class CpuPath:
         n = self.w.num_nodes
         self.pos_map = -np.arange(n, dtype=np.int64) - 2      # every row in the host table
         self.min_vids = inst.min_vids.numpy().astype(np.int64)
-        self.cores = os.cpu_count()
+        # torchrun hands its workers OMP_NUM_THREADS=1: the baseline takes the host's threads explicitly
+        self.lib.oracle_set_threads.restype = ctypes.c_int
+        self.cores = int(self.lib.oracle_set_threads(os.cpu_count() or 1))
 
     @staticmethod
     def _p(a):

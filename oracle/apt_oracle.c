@@ -12,6 +12,9 @@
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 typedef int64_t i64;
 typedef uint32_t u32;
@@ -26,6 +29,18 @@ static void philox(u32 c[4], u32 k0, u32 k1) {
     c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
     k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
   }
+}
+
+/* Threads of the `omp parallel for` loops: a launcher may have set OMP_NUM_THREADS=1 for its
+ * workers; the timed baseline asks for the host's threads explicitly. Returns what is in force. */
+int oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
 }
 
 void oracle_philox(const u32* ctr, const u32* key, u32* out) {
