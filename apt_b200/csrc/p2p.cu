@@ -184,8 +184,10 @@ k_p2p_push(const char* __restrict__ src, const int64_t* __restrict__ src_index,
           }
           while (soff[r + 1] <= j) ++r;
         }
-        const int64_t srow = (src_index && !index_is_dest) ? src_index[j] : (interleave ? j : t);
         const int64_t local = j - soff[r];
+        // index_is_dest == 2 (no index): every peer gets the same rows, bucket row l is source row l
+        const int64_t srow = index_is_dest == 2 ? local
+                             : (src_index && !index_is_dest) ? src_index[j] : (interleave ? j : t);
         if (local >= cap_rows) {
           overflow = true;
         } else if (direct) {
@@ -289,7 +291,9 @@ k_p2p_pull(const char* __restrict__ local_base, const int64_t* __restrict__ recv
   }
   __syncthreads();
   const int64_t total = roff[world_size];
-  const int64_t n = MODE == 1 ? num_dst_rows : total;
+  // never more rows than the destination holds: a caller that sized it by an upper bound of what
+  // the peers send loses the excess (and can see it in the counts) instead of writing past the end
+  const int64_t n = MODE == 1 ? num_dst_rows : (total < num_dst_rows ? total : num_dst_rows);
   const int lane = threadIdx.x & 31;
   const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
   const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);

@@ -78,6 +78,13 @@ class LocalExchange:
         """All-to-all of one row of send[world_size, k] per peer into recv, stream-ordered."""
         recv.copy_(send)
 
+    def allbroadcast_enqueue(self, inp, n_dev, counts_out):
+        """Stream-ordered all-broadcast of the first n_dev rows of inp (device count): (buffer of
+        world_size x inp.shape[0] rows holding the received rows in rank order, counts)."""
+        counts_out[0:1].copy_(n_dev)
+        counts_out[1:2].copy_(n_dev)
+        return inp, counts_out
+
 
 class NcclExchange:
     """Baseline: the collective library's all-to-all-v."""
@@ -416,6 +423,25 @@ class P2PExchange:
         check(lib.apt_p2p_pull_sum(self.ctx, _ptr(counts_dev), _DTYPE_CODE[inp.dtype], int(my_rows), width, _ptr(out),
                                    st.status_ptr(), _stream()))
         return out
+
+    def allbroadcast_enqueue(self, inp, n_dev, counts_out):
+        """Stream-ordered all-broadcast of the first n_dev rows of inp (a device count) without a
+        host read: one push in which every peer's bucket is the same source rows. Every rank is
+        taken to send at most inp.shape[0] rows. Returns (buffer of world_size x inp.shape[0] rows
+        with the received rows in rank order, counts_out[world_size + 1])."""
+        ws = self.state.world_size
+        n_max, width = inp.shape
+        row_bytes = width * inp.element_size()
+        self._check_capacity(n_max, row_bytes)
+        if getattr(self, "_steps_dev", None) is None:
+            self._steps_dev = torch.arange(1, ws + 1, dtype=torch.int64, device=inp.device)
+            self._fixed_counts = torch.empty(ws + 1, dtype=torch.int64, device=inp.device)
+        offsets = self._steps_dev * n_dev
+        self._push(inp, None, 2, offsets, n_max * ws, row_bytes)
+        self._wait(counts_out)
+        recv = torch.empty((ws * n_max, width), dtype=inp.dtype, device=inp.device)
+        self._pull(counts_out, None, 0, ws * n_max, ws * n_max, row_bytes, recv)
+        return recv, counts_out
 
     def exchange_fixed(self, send, recv):
         """All-to-all of one row of send[world_size, k] per peer into recv[world_size, k]; sizes

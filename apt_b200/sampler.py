@@ -408,6 +408,9 @@ class SPVirtualSampler:
         num_dst = n_dst
         n_uf, n_us, n_ud = int(host[self._UF]), int(host[self._US]), int(host[self._UD])
         n_recv = int(host[16 + ws])
+        if n_recv > b["vir_src"].numel():
+            raise RuntimeError("chained SNP sampler: more ids received than the buffer sized from this rank's own "
+                               "batch holds; use chained=False for batches that differ this much between the ranks")
         send_sizes_cpu = host[self._SEND:self._SEND + 2 * ws].clone()
         recv_sizes_cpu = host[self._RECV:self._RECV + 2 * ws].clone()
         unique_frontier, unique_src = b["unique_frontier"], b["unique_src"]
@@ -542,11 +545,86 @@ class MPSampler:
     (all_coo_row, all_coo_col, recv_frontier_size, recv_coo_size, recv_size) as in
     the reference, input_nodes = the concatenation of all ranks' frontiers."""
 
-    def __init__(self, rank: int, fanouts: List[int]):
+    def __init__(self, rank: int, fanouts: List[int], chained: bool = None):
         self.rank = rank
         self.fanouts = list(fanouts)
+        if chained is None:
+            chained = os.environ.get("APT_CHAINED_SAMPLER", "1") != "0"
+        self.chained = bool(chained)
+
+    # word slots of the chained form: [0..13] hop counts (the last one is the frontier of the outermost
+    # hop), [54..56] this rank's (seeds, frontier, rows) sizes, [16..48] / [64..96] rows received per peer
+    # for the two broadcasts, [128..223] every rank's three sizes
+    _MINE, _ALL = 54, 128
+
+    def _sample_chained(self, seeds: torch.Tensor):
+        """Every kernel of the mini-batch enqueued without a host read (sizes stay in the device
+        word block, buffers are upper bounds, the broadcasts take device-side counts), then one
+        read and everything is narrowed."""
+        st = ops.STATE
+        ws = st.world_size
+        if ws > 31 or len(self.fanouts) > 13:
+            raise RuntimeError("the chained NFP sampler serves at most 31 ranks and 13 hops")
+        seeds = ops._need_cuda(seeds, "seeds")
+        dev = seeds.device
+        words = st.words()
+        slot = 0
+        cur, cur_n = seeds, None
+        layers = []
+        for fanout in list(reversed(self.fanouts))[:-1]:
+            nbr = ops._sample(cur, fanout, cur_n)
+            cnt = st.word(slot)
+            uniq, rel = ops._relabel_enqueue(cur, nbr, cur_n, cnt)
+            layers.append((cur, rel, uniq, slot, fanout))
+            cur, cur_n = uniq, cnt
+            slot += 1
+        f = self.fanouts[0]
+        nbr = ops._sample(cur, f, cur_n)
+        uf_word = st.word(slot)
+        unique_frontier, coo_row = ops._relabel_enqueue(cur, nbr, cur_n, uf_word)
+        mine = words[self._MINE:self._MINE + 3]
+        if cur_n is None:
+            mine[0:1].fill_(cur.numel())
+        else:
+            mine[0:1].copy_(cur_n)
+        mine[1:2].copy_(uf_word)
+        torch.mul(mine[0:1], f, out=mine[2:3])
+        ex = ops._exchange()
+        all_sizes = words[self._ALL:self._ALL + 3 * ws].view(ws, 3)
+        if ws == 1:
+            all_sizes.copy_(mine.view(1, 3))
+        else:
+            got, _ = ex.allbroadcast_enqueue(mine.view(1, 3), words[self._MINE + 3:self._MINE + 4].fill_(1),
+                                             torch.empty(ws + 1, dtype=torch.int64, device=dev))
+            all_sizes.copy_(got[:ws])
+        recv_frontier, _ = ex.allbroadcast_enqueue(unique_frontier.view(-1, 1), mine[1:2], words[16:16 + ws + 1])
+        recv_coo, _ = ex.allbroadcast_enqueue(coo_row.view(-1, 1), mine[2:3], words[64:64 + ws + 1])
+
+        host = st.read_words()
+        count = [int(host[k]) for k in range(slot)]
+        blocks = []
+        n_dst = seeds.numel()
+        for dst_buf, rel, uniq, u_s, fanout in layers:
+            n_src = count[u_s]
+            blocks.insert(0, Block(rel[:n_dst * fanout], _coo_col(dst_buf.numel(), n_dst, fanout, dev), n_src, n_dst,
+                                   uniq[:n_src], fanout))
+            n_dst = n_src
+        sizes = host[self._ALL:self._ALL + 3 * ws].view(ws, 3)
+        recv_size = sizes[:, 0].clone()
+        recv_frontier_size = sizes[:, 1].clone()
+        recv_coo_size = sizes[:, 2].clone()
+        if int(recv_frontier_size.sum()) > recv_frontier.shape[0] or int(recv_coo_size.sum()) > recv_coo.shape[0]:
+            raise RuntimeError("chained NFP sampler: the ranks sent more rows than the buffers sized from this rank's "
+                               "own batch hold; it needs the same number of seeds on every rank (or chained=False)")
+        all_frontier = recv_frontier.view(-1)[:int(recv_frontier_size.sum())]
+        all_coo_row = recv_coo.view(-1)[:int(recv_coo_size.sum())]
+        all_coo_col = torch.cat([_coo_col(int(i), int(i), f, dev) for i in recv_size])
+        blocks.insert(0, (all_coo_row, all_coo_col, recv_frontier_size, recv_coo_size, recv_size))
+        return all_frontier, seeds, blocks, torch.tensor([n_dst]), recv_size
 
     def sample(self, graph, seeds: torch.Tensor):
+        if self.chained and ops._exchange().name in ("local", "p2p"):
+            return self._sample_chained(seeds)
         output_nodes = seeds
         blocks = []
         for layer_id, fanout in enumerate(reversed(self.fanouts)):

@@ -458,7 +458,10 @@ size_t apt_p2p_region_bytes(const apt_p2p* ctx);
  * [send_offsets[r-1], send_offsets[r]) go to peer r. send_offsets is a DEVICE
  * array of world_size inclusive row offsets; max_rows is a host-side upper
  * bound of send_offsets[world_size-1] that sizes the grid. Rows that do not
- * fit a region are dropped and APT_FLAG_TABLE_FULL is set. Advances the epoch. */
+ * fit a region are dropped and APT_FLAG_TABLE_FULL is set. Advances the epoch.
+ * With src_index NULL and index_is_dest == 2 every peer gets the same rows: row l
+ * of each peer's bucket is src row l (the all-broadcast of AllBroadcastV2,
+ * src/ops/collective.cc:367-402, without the world_size-fold copy of the input). */
 int apt_p2p_push(apt_p2p* ctx, const void* src, const int64_t* src_index,
                  int index_is_dest, const int64_t* send_offsets, int64_t max_rows,
                  int64_t row_bytes, int32_t* status_word, void* stream);
@@ -471,7 +474,9 @@ int apt_p2p_wait(apt_p2p* ctx, int64_t* out_recv_counts, int32_t* status_word,
  * If dst_index is NULL row j of the concatenation lands at dst row j; else if
  * index_is_source it is a gather: dst row i = concatenation row dst_index[i]
  * (num_dst_rows rows); else a scatter: concatenation row j lands at
- * dst_index[j]. recv_counts is the device array apt_p2p_wait filled. */
+ * dst_index[j]. recv_counts is the device array apt_p2p_wait filled. Without an
+ * index, or with a scatter index, at most num_dst_rows rows of the concatenation
+ * are copied (the capacity of dst). */
 int apt_p2p_pull(apt_p2p* ctx, const int64_t* recv_counts,
                  const int64_t* dst_index, int index_is_source,
                  int64_t num_dst_rows, int64_t max_rows, int64_t row_bytes,

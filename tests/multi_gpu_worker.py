@@ -192,7 +192,10 @@ def main():
     ops.set_sampling(key=777, call_id=0)
     mseeds = seeds[:300 + 41 * rank]
     all_mseeds = gather_objects(mseeds)
-    m_in, _, m_blocks, m_send, m_recv = apt_b200.MPSampler(rank, [5]).sample(None, torch.from_numpy(mseeds).cuda())
+    # seed counts differ between the ranks here: the operator-by-operator form sizes its buffers from the
+    # gathered sizes; the chained form (buffers sized from the own batch) is checked below on equal counts
+    m_in, _, m_blocks, m_send, m_recv = apt_b200.MPSampler(rank, [5], chained=False).sample(
+        None, torch.from_numpy(mseeds).cuda())
     m_row, m_col, m_fsz, m_csz, m_ssz = m_blocks[0]
     all_m = gather_objects(dict(all_frontier=host(m_in), all_coo_row=host(m_row), all_coo_col=host(m_col),
                                 send_size=m_send.numpy(), recv_size=m_recv.numpy(), recv_frontier_size=m_fsz.numpy(),
@@ -202,6 +205,23 @@ def main():
         for r in range(world):
             for name, a_ in all_m[r].items():
                 assert np.array_equal(a_, want_m[r][name]), f"rank {r}: NFP sampler: {name} differs from the oracle"
+    ops.set_sampling(key=778, call_id=0)
+    eq_seeds = seeds[:256]
+    all_eq = gather_objects(eq_seeds)
+    c_in, _, c_blocks, c_send, c_recv = apt_b200.MPSampler(rank, [4, 3]).sample(None, torch.from_numpy(eq_seeds).cuda())
+    c_row, c_col, c_fsz, c_csz, c_ssz = c_blocks[0]
+    all_c = gather_objects(dict(all_frontier=host(c_in), all_coo_row=host(c_row), all_coo_col=host(c_col),
+                                send_size=c_send.numpy(), recv_size=c_recv.numpy(), recv_frontier_size=c_fsz.numpy(),
+                                recv_coo_size=c_csz.numpy()))
+    if rank == 0:
+        inner = []
+        for r in range(world):
+            nb_ = orc.sample_csc_fanout(all_eq[r], 3, *graph, key=778, call_id=0)
+            inner.append(orc.relabel_csc(all_eq[r], nb_)[0])
+        want_c = orc.mp_sample(inner, 4, graph, key=778, call_id=1)
+        for r in range(world):
+            for name, a_ in all_c[r].items():
+                assert np.array_equal(a_, want_c[r][name]), f"rank {r}: chained NFP sampler: {name} differs from the oracle"
     width = 8
     g2 = torch.Generator(device="cuda").manual_seed(17)
     table_m = torch.randn((n, world * width), generator=g2, device="cuda")          # same on every rank

@@ -310,6 +310,21 @@ def test_nfp_operators_single_rank(backend):
         for got, name in ((send_size, "send_size"), (recv_size, "recv_size"), (recv_frontier_size, "recv_frontier_size"),
                           (recv_coo_size, "recv_coo_size"), (recv_seed_size, "recv_size")):
             assert not got.is_cuda and np.array_equal(got.numpy(), want[name])
+        # three hops: the chained form (one host read per mini-batch) and the operator-by-operator form agree
+        seeds3 = dev(rng.permutation(n)[:100].astype(I64))
+        res3 = []
+        for chained in (True, False):
+            ops.set_sampling(key=4, call_id=10)
+            smp = MPSampler(0, [5, 4, 3], chained=chained)
+            assert smp.chained == chained
+            res3.append(smp.sample(None, seeds3))
+        a, b = res3
+        assert torch.equal(a[0], b[0]) and torch.equal(a[3], b[3]) and torch.equal(a[4], b[4])
+        for x_, y_ in zip(a[2][0], b[2][0]):
+            assert torch.equal(x_, y_)
+        for x_, y_ in zip(a[2][1:], b[2][1:]):
+            assert torch.equal(x_.coo_row, y_.coo_row) and torch.equal(x_.src_ids, y_.src_ids)
+            assert (x_.num_src, x_.num_dst) == (y_.num_src, y_.num_dst)
         x = torch.randn((400, 48), device="cuda")
         y = ops.mp_feat_shuffle_fwd(x, recv_size, send_size, 48)
         assert torch.equal(y, x)
