@@ -178,6 +178,9 @@ class MixedNeighborSampler:
         recv_offset = host[16:16 + ws].clone().cumsum(0)
         dev_offset = host[64:64 + ws].clone()
         total_recv = int(recv_offset[-1])
+        if total_recv > bufs["inv"].numel():
+            raise RuntimeError("chained NP sampler: more ids received than the buffer sized from this rank's own "
+                               "batch holds; use chained=False for batches that differ this much between the ranks")
         blocks = []
         n_dst = seeds.numel()
         for dst_buf, rel, uniq, u_s, fanout in bufs["layers"]:
