@@ -452,6 +452,115 @@ k_gat_rows(const int64_t* __restrict__ row, const T* __restrict__ ft, const T* _
   }
 }
 
+// Fast path of the same operator for wide rows (one warp per destination row), up to
+// kGatHeads heads and up to 32 edges per row (fixed-fanout blocks): lane j computes the scores
+// of edge j for all heads once (one exp per edge and head instead of two per edge and lane),
+// the softmax statistics are warp reductions, the attention values and source ids wait in
+// shared memory, and the weighted sum then walks the edges with one shared-memory read each.
+// Rows with more than 32 edges take the recomputing walk of k_gat_rows.
+constexpr int kGatHeads = 8;
+
+template <typename T, int VE>
+__global__ void __launch_bounds__(256)
+k_gat_rows_warp(const int64_t* __restrict__ row, const T* __restrict__ ft, const T* __restrict__ el,
+                const T* __restrict__ er, int num_heads, int64_t head_dim, float slope,
+                int64_t num_dst, SpmmWs ws, T* __restrict__ out, T* __restrict__ attn, int32_t* status) {
+  __shared__ float a_sh[8][32][kGatHeads];
+  __shared__ int64_t src_sh[8][32];
+  const bool unsorted = *ws.flags != 0;
+  if (unsorted && blockIdx.x == 0 && threadIdx.x == 0) atomicOr(status, APT_FLAG_NOT_GROUPED);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t feat_dim = (int64_t)num_heads * head_dim;
+  const int64_t nvec = feat_dim / VE;
+  int64_t d = (int64_t)blockIdx.x * 8 + warp;
+  const int64_t stride = (int64_t)gridDim.x * 8;
+  for (; d < num_dst; d += stride) {
+    const int64_t e0 = unsorted ? 0 : ws.range[d];
+    const int64_t e1 = unsorted ? 0 : ws.range[d + 1];
+    const int deg = (int)(e1 - e0);
+    if (deg <= 32) {
+      const bool has = lane < deg;
+      const int64_t src = has ? row[e0 + lane] : 0;
+      src_sh[warp][lane] = src;
+#pragma unroll
+      for (int h = 0; h < kGatHeads; ++h) {
+        if (h < num_heads) {
+          float sc = -INFINITY;
+          if (has) {
+            sc = Elem<T>::to_f(el[src * num_heads + h]) + Elem<T>::to_f(er[d * num_heads + h]);
+            sc = sc > 0.f ? sc : sc * slope;
+          }
+          float m = sc;
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+          const float p = has ? expf(sc - m) : 0.f;
+          float sum = p;
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+          const float a = sum > 0.f ? p / sum : 0.f;
+          a_sh[warp][lane][h] = a;
+          if (has && attn) attn[(e0 + lane) * num_heads + h] = Elem<T>::from_f(a);
+        }
+      }
+      __syncwarp();
+      for (int64_t c = lane; c < nvec; c += 32) {
+        const int h = (int)((c * VE) / head_dim);
+        float acc[VE];
+#pragma unroll
+        for (int t = 0; t < VE; ++t) acc[t] = 0.f;
+#pragma unroll 4
+        for (int j = 0; j < deg; ++j) {
+          const float a = a_sh[warp][j][h];
+          const Pack<T, VE> p = load_pack<T, VE>(ft + src_sh[warp][j] * feat_dim + c * VE);
+#pragma unroll
+          for (int t = 0; t < VE; ++t) acc[t] += a * Elem<T>::to_f(p.v[t]);
+        }
+        Pack<T, VE> o;
+#pragma unroll
+        for (int t = 0; t < VE; ++t) o.v[t] = Elem<T>::from_f(acc[t]);
+        store_pack<T, VE>(out + d * feat_dim + c * VE, o);
+      }
+      __syncwarp();
+      continue;
+    }
+    for (int64_t c = lane; c < nvec; c += 32) {
+      const int h = (int)((c * VE) / head_dim);
+      const float r = Elem<T>::to_f(er[d * num_heads + h]);
+      float m = -INFINITY;
+      for (int64_t e = e0; e < e1; ++e) {
+        float sc = Elem<T>::to_f(el[row[e] * num_heads + h]) + r;
+        sc = sc > 0.f ? sc : sc * slope;
+        m = fmaxf(m, sc);
+      }
+      float denom = 0.f;
+      for (int64_t e = e0; e < e1; ++e) {
+        float sc = Elem<T>::to_f(el[row[e] * num_heads + h]) + r;
+        sc = sc > 0.f ? sc : sc * slope;
+        denom += expf(sc - m);
+      }
+      const float inv = denom > 0.f ? 1.f / denom : 0.f;
+      float acc[VE];
+#pragma unroll
+      for (int t = 0; t < VE; ++t) acc[t] = 0.f;
+      const bool writes_attn = attn != nullptr && (c * VE) % head_dim == 0;
+      for (int64_t e = e0; e < e1; ++e) {
+        const int64_t src = row[e];
+        float sc = Elem<T>::to_f(el[src * num_heads + h]) + r;
+        sc = sc > 0.f ? sc : sc * slope;
+        const float a = expf(sc - m) * inv;
+        if (writes_attn) attn[e * num_heads + h] = Elem<T>::from_f(a);
+        const Pack<T, VE> p = load_pack<T, VE>(ft + src * feat_dim + c * VE);
+#pragma unroll
+        for (int t = 0; t < VE; ++t) acc[t] += a * Elem<T>::to_f(p.v[t]);
+      }
+      Pack<T, VE> o;
+#pragma unroll
+      for (int t = 0; t < VE; ++t) o.v[t] = Elem<T>::from_f(acc[t]);
+      store_pack<T, VE>(out + d * feat_dim + c * VE, o);
+    }
+  }
+}
+
 template <typename T>
 static int launch_gat(bool vec, const int64_t* row, const void* ft, const void* el, const void* er,
                       int num_heads, int64_t head_dim, float slope, int64_t num_dst, SpmmWs ws, void* out,
@@ -459,7 +568,11 @@ static int launch_gat(bool vec, const int64_t* row, const void* ft, const void* 
   constexpr int VE = 16 / sizeof(T);
   const int64_t feat_dim = (int64_t)num_heads * head_dim;
   ProfScope prof("gat_rows", s);
-  if (vec) {
+  if (vec && feat_dim / VE > 16 && num_heads <= kGatHeads) {
+    const int grid = wave_grid(ceil_div(num_dst, 8), 8);
+    APT_LAUNCH((k_gat_rows_warp<T, VE>), grid, 256, 0, s, row, (const T*)ft, (const T*)el, (const T*)er, num_heads,
+               head_dim, slope, num_dst, ws, (T*)out, (T*)attn, status);
+  } else if (vec) {
     const int group = pow2_at_least_fwd(feat_dim / VE);
     const int grid = wave_grid(ceil_div(num_dst, 256 / group), 8);
     APT_LAUNCH((k_gat_rows<T, VE>), grid, 256, 0, s, row, (const T*)ft, (const T*)el, (const T*)er, num_heads,
