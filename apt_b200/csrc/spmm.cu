@@ -260,7 +260,7 @@ template <typename T, int VE, int OP>
 __device__ __forceinline__ void edge_value(float* acc, const T* __restrict__ in,
                                            const T* __restrict__ edata, int64_t src_off /* row * feat_dim */,
                                            int64_t e, int64_t feat_dim, int64_t edata_dim,
-                                           int64_t per, int64_t col0) {
+                                           int64_t per, int64_t col0, int64_t ecol = -1) {
   float x[VE];
   if constexpr (OP != kCopyE) {
     const Pack<T, VE> p = load_pack<T, VE>(in + src_off + col0);
@@ -279,6 +279,11 @@ __device__ __forceinline__ void edge_value(float* acc, const T* __restrict__ in,
         const float w = Elem<T>::to_f(p.v[t]);
         x[t] = OP == kUMulE ? x[t] * w : x[t] + w;
       }
+    } else if (ecol >= 0) {
+      // one value per head and the whole slice inside one head: a single load, column found by the caller
+      const float w = Elem<T>::to_f(edata[e * edata_dim + ecol]);
+#pragma unroll
+      for (int t = 0; t < VE; ++t) x[t] = OP == kUMulE ? x[t] * w : x[t] + w;
     } else {
 #pragma unroll
       for (int t = 0; t < VE; ++t) {
@@ -324,6 +329,7 @@ k_spmm_rows(const int64_t* __restrict__ row, int64_t E, const T* __restrict__ in
     }
     for (int64_t c0 = 0; c0 < nvec; c0 += group) {
       const int64_t c = c0 + sub;
+      const int64_t ecol = (per > 1 && per % VE == 0) ? (c * VE) / per : -1;
       float acc[VE];
 #pragma unroll
       for (int t = 0; t < VE; ++t) acc[t] = 0.f;
@@ -344,7 +350,7 @@ k_spmm_rows(const int64_t* __restrict__ row, int64_t E, const T* __restrict__ in
         for (int j = 0; j < cnt; ++j) {
           const int e = OP == kCopyU ? 0 : __shfl_sync(gmask, my_e, j, group);   // copy_u never looks at the edge id
           const int64_t src = __shfl_sync(gmask, my_src, j, group);
-          if (c < nvec) edge_value<T, VE, OP>(acc, in, edata, src, e, feat_dim, edata_dim, per, c * VE);
+          if (c < nvec) edge_value<T, VE, OP>(acc, in, edata, src, e, feat_dim, edata_dim, per, c * VE, ecol);
         }
       }
       if (c < nvec) {
@@ -600,7 +606,8 @@ __global__ void __launch_bounds__(256)
 k_gat_bwd_rows(const int64_t* __restrict__ row, const T* __restrict__ ft, const T* __restrict__ el,
                const T* __restrict__ er, const T* __restrict__ grad_out, int num_heads, int64_t head_dim,
                float slope, int64_t num_dst, SpmmWs ws, T* __restrict__ attn, T* __restrict__ grad_score,
-               T* __restrict__ grad_er, int group, int lanes_per_head, int32_t* status) {
+               T* __restrict__ grad_er, int group, int lanes_per_head, int32_t* status,
+               int64_t skip_up_to /* rows with at most this many edges belong to k_gat_bwd_warp */) {
   const bool unsorted = *ws.flags != 0;
   if (unsorted && blockIdx.x == 0 && threadIdx.x == 0) atomicOr(status, APT_FLAG_NOT_GROUPED);
   const int lane = threadIdx.x & 31;
@@ -614,6 +621,7 @@ k_gat_bwd_rows(const int64_t* __restrict__ row, const T* __restrict__ ft, const 
   for (; d < num_dst; d += stride) {
     const int64_t e0 = unsorted ? 0 : ws.range[d];
     const int64_t e1 = unsorted ? 0 : ws.range[d + 1];
+    if (e1 - e0 <= skip_up_to) continue;
     for (int64_t c0 = 0; c0 < nvec; c0 += group) {
       const int64_t c = c0 + sub;
       const bool live = c < nvec;
@@ -670,6 +678,101 @@ k_gat_bwd_rows(const int64_t* __restrict__ row, const T* __restrict__ ft, const 
       }
       if (leader) grad_er[d * num_heads + h] = Elem<T>::from_f(ger);
     }
+  }
+}
+
+// Wide rows with at most 32 edges (fixed-fanout blocks), one warp per destination: lane j
+// scores edge j for all heads once, the lanes then walk the edges ONCE over ft (each lane its
+// slice of grad_out and of the row, the lanes of a head meeting in a shuffle butterfly) and
+// leave <grad_out, ft> per edge and head in shared memory, and lane j finishes edge j.
+template <typename T, int VE>
+__global__ void __launch_bounds__(256)
+k_gat_bwd_warp(const int64_t* __restrict__ row, const T* __restrict__ ft, const T* __restrict__ el,
+               const T* __restrict__ er, const T* __restrict__ grad_out, int num_heads, int64_t head_dim,
+               float slope, int64_t num_dst, SpmmWs ws, T* __restrict__ attn, T* __restrict__ grad_score,
+               T* __restrict__ grad_er, int lanes_per_head, int32_t* status) {
+  __shared__ float a_sh[8][32][kGatHeads], fac_sh[8][32][kGatHeads], dot_sh[8][32][kGatHeads];
+  __shared__ int64_t src_sh[8][32];
+  const bool unsorted = *ws.flags != 0;
+  if (unsorted && blockIdx.x == 0 && threadIdx.x == 0) atomicOr(status, APT_FLAG_NOT_GROUPED);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t feat_dim = (int64_t)num_heads * head_dim;
+  const int64_t nvec = feat_dim / VE;
+  int64_t d = (int64_t)blockIdx.x * 8 + warp;
+  const int64_t stride = (int64_t)gridDim.x * 8;
+  for (; d < num_dst; d += stride) {
+    const int64_t e0 = unsorted ? 0 : ws.range[d];
+    const int64_t e1 = unsorted ? 0 : ws.range[d + 1];
+    const int deg = (int)(e1 - e0);
+    if (deg > 32) continue;            // left to k_gat_bwd_rows
+    const bool has = lane < deg;
+    const int64_t src = has ? row[e0 + lane] : 0;
+    src_sh[warp][lane] = src;
+#pragma unroll
+    for (int h = 0; h < kGatHeads; ++h) {
+      if (h < num_heads) {
+        float raw = 0.f, sc = -INFINITY;
+        if (has) {
+          raw = Elem<T>::to_f(el[src * num_heads + h]) + Elem<T>::to_f(er[d * num_heads + h]);
+          sc = raw > 0.f ? raw : raw * slope;
+        }
+        float m = sc;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        const float p = has ? expf(sc - m) : 0.f;
+        float sum = p;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        a_sh[warp][lane][h] = sum > 0.f ? p / sum : 0.f;
+        fac_sh[warp][lane][h] = raw > 0.f ? 1.f : slope;
+      }
+    }
+    __syncwarp();
+    for (int64_t c0 = 0; c0 < nvec; c0 += 32) {
+      const int64_t c = c0 + lane;
+      const bool live = c < nvec;
+      const int h = live ? (int)((c * VE) / head_dim) : 0;
+      const bool leader = live && (c * VE) % head_dim == 0;
+      float g[VE];
+#pragma unroll
+      for (int t = 0; t < VE; ++t) g[t] = 0.f;
+      if (live) {
+        const Pack<T, VE> p = load_pack<T, VE>(grad_out + d * feat_dim + c * VE);
+#pragma unroll
+        for (int t = 0; t < VE; ++t) g[t] = Elem<T>::to_f(p.v[t]);
+      }
+      for (int j = 0; j < deg; ++j) {
+        float dot = 0.f;
+        if (live) {
+          const Pack<T, VE> p = load_pack<T, VE>(ft + src_sh[warp][j] * feat_dim + c * VE);
+#pragma unroll
+          for (int t = 0; t < VE; ++t) dot += g[t] * Elem<T>::to_f(p.v[t]);
+        }
+        for (int o = lanes_per_head >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (leader) dot_sh[warp][j][h] = dot;
+      }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int h = 0; h < kGatHeads; ++h) {
+      if (h < num_heads) {
+        const float a = has ? a_sh[warp][lane][h] : 0.f;
+        const float dot = has ? dot_sh[warp][lane][h] : 0.f;
+        float t = a * dot;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        const float gs = has ? a * (dot - t) * fac_sh[warp][lane][h] : 0.f;
+        if (has) {
+          attn[(e0 + lane) * num_heads + h] = Elem<T>::from_f(a);
+          grad_score[(e0 + lane) * num_heads + h] = Elem<T>::from_f(gs);
+        }
+        float ger = gs;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ger += __shfl_xor_sync(0xffffffffu, ger, o);
+        if (lane == 0) grad_er[d * num_heads + h] = Elem<T>::from_f(ger);
+      }
+    }
+    __syncwarp();
   }
 }
 
@@ -741,10 +844,19 @@ static int launch_gat_bwd(bool vec, const int64_t* row, const void* ft, const vo
   if (vec && pow2) {
     const int group = pow2_at_least_fwd(feat_dim / VE);
     if (group % lph == 0) {
+      int64_t skip = -1;
+      if (group == 32 && num_heads <= kGatHeads) {
+        // rows of up to 32 edges: one warp per row; the kernel after it takes the longer rows
+        const int grid_w = wave_grid(ceil_div(num_dst, 8), 8);
+        APT_LAUNCH((k_gat_bwd_warp<T, VE>), grid_w, 256, 0, s, row, (const T*)ft, (const T*)el, (const T*)er,
+                   (const T*)grad_out, num_heads, head_dim, slope, num_dst, ws, (T*)attn, (T*)grad_score,
+                   (T*)grad_er, (int)lph, status);
+        skip = 32;
+      }
       const int grid = wave_grid(ceil_div(num_dst, 256 / group), 8);
       APT_LAUNCH((k_gat_bwd_rows<T, VE>), grid, 256, 0, s, row, (const T*)ft, (const T*)el, (const T*)er,
                  (const T*)grad_out, num_heads, head_dim, slope, num_dst, ws, (T*)attn, (T*)grad_score, (T*)grad_er,
-                 group, (int)lph, status);
+                 group, (int)lph, status, skip);
       return APT_OK;
     }
   }
@@ -786,6 +898,7 @@ k_spmm_long(const int64_t* __restrict__ row, const T* __restrict__ in, const T* 
     const int64_t e0 = ws.range[d], e1 = ws.range[d + 1];
     for (int64_t c0 = 0; c0 < nvec; c0 += 32) {
       const int64_t c = c0 + lane;
+      const int64_t ecol = (per > 1 && per % VE == 0) ? (c * VE) / per : -1;
       float acc[VE];
 #pragma unroll
       for (int t = 0; t < VE; ++t) acc[t] = 0.f;
@@ -802,7 +915,7 @@ k_spmm_long(const int64_t* __restrict__ row, const T* __restrict__ in, const T* 
         for (int j = 0; j < cnt; ++j) {
           const int e = OP == kCopyU ? 0 : __shfl_sync(0xffffffffu, my_e, j);
           const int64_t src = __shfl_sync(0xffffffffu, my_src, j);
-          if (c < nvec) edge_value<T, VE, OP>(acc, in, edata, src, e, feat_dim, edata_dim, per, c * VE);
+          if (c < nvec) edge_value<T, VE, OP>(acc, in, edata, src, e, feat_dim, edata_dim, per, c * VE, ecol);
         }
       }
 #pragma unroll

@@ -368,6 +368,12 @@ def stage_ops(args):
     elb, erb = el.bfloat16(), er.bfloat16()
     timed("gat_edge_softmax_sum bf16 4 heads x 64",
           lambda _: ops.gat_edge_softmax_sum(rel, col, ft, elb, erb, S), E * (8 + 4 * 2 + 256 * 2) + S * 256 * 2)
+    gob = torch.randn((S, 4, 64), generator=g, device="cuda").bfloat16()
+    # backward: the edge kernel reads ft twice, then two reverse SpMM calls (u_mul_e over 256 columns, copy_e over 4)
+    timed("gat_edge_softmax_sum backward bf16 4 heads x 64 (edge kernel + 2 reverse SpMM)",
+          lambda _: ops.gat_edge_softmax_sum_backward(rel, col, ft, elb, erb, gob),
+          E * (8 + 4 * 2 * 2 + 2 * 256 * 2) + S * 256 * 2 + E * (16 + 256 * 2 + 4 * 2) + n_src * 256 * 2,
+          tags=("gat_bwd_rows",) + spmm_tags)
     ids = torch.randint(0, n, (S,), generator=g, device="cuda")
     ops.register_min_vids(torch.tensor([0, n]))
     timed("unique_sorted (67 584 ids over 2^20)", lambda _: ops._unique_enqueue(ids, None, 0, n, ops.STATE.word(1)),
