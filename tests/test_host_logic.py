@@ -61,3 +61,50 @@ def test_handle_exchange_two_gloo_ranks(tmp_path):
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, MASTER_ADDR="127.0.0.1"))
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     assert res.stdout.count("HOST_OK") == 2
+
+
+def test_library_backend_collectives_two_gloo_ranks(tmp_path):
+    """The NFP and SNP collectives of the library back end (all-broadcast, reduce-scatter, fixed-shape
+    all-to-all, all-to-all with offsets) over 2 gloo ranks on CPU tensors, against the oracle."""
+    script = tmp_path / "worker.py"
+    script.write_text(textwrap.dedent(f"""
+        import sys
+        sys.path.insert(0, {ROOT!r})
+        import numpy as np, torch
+        import torch.distributed as dist
+        from apt_b200.exchange import NcclExchange
+        from apt_b200.ops import NPCState
+        from oracle import oracle as orc
+        dist.init_process_group("gloo")
+        r, ws = dist.get_rank(), dist.get_world_size()
+        s = NPCState(); s.world_size = ws; s.rank = r
+        ex = NcclExchange(s)
+        rng = np.random.default_rng(5)
+        lens = [3, 5]
+        xs = [rng.standard_normal((n, 4)).astype(np.float32) for n in lens]
+        got = ex.allbroadcast(torch.from_numpy(xs[r]), lens)
+        assert np.array_equal(got.numpy(), orc.allbroadcast_v2(xs, 4)[r])
+        seg = np.array([2, 4])
+        ys = [rng.standard_normal((6, 3)).astype(np.float32) for _ in range(ws)]
+        got = ex.reduce_scatter(torch.from_numpy(ys[r]), torch.from_numpy(seg), int(seg[r]))
+        assert np.allclose(got.numpy(), orc.mp_feat_shuffle_fwd(ys, seg, 3)[r], atol=1e-6)
+        send = torch.arange(4).view(2, 2) + 10 * r
+        recv = torch.empty_like(send)
+        ex.exchange_fixed(send, recv)
+        assert recv.tolist() == [[2 * r, 2 * r + 1], [10 + 2 * r, 11 + 2 * r]], recv
+        # the closed-form all-to-all case of the reference's tests/test_alltoall.cc:24-60 (k = 7, b = 100)
+        sizes = [[7 * (q - p) ** 2 + 100 for p in range(ws)] for q in range(ws)]
+        inp = torch.cat([torch.full((sizes[r][p],), 10 * r + p, dtype=torch.int64) for p in range(ws)])
+        recv_sizes = [sizes[q][r] for q in range(ws)]
+        out = torch.empty(sum(recv_sizes), dtype=torch.int64)
+        ex.alltoall(inp, out, torch.tensor(sizes[r]).cumsum(0), torch.tensor(recv_sizes).cumsum(0), 1)
+        want = torch.cat([torch.full((recv_sizes[q],), 10 * q + r, dtype=torch.int64) for q in range(ws)])
+        assert torch.equal(out, want)
+        dist.barrier()
+        print("COLL_OK", r)
+    """))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29432", str(script)]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, MASTER_ADDR="127.0.0.1"))
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    assert res.stdout.count("COLL_OK") == 2
