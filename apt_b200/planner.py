@@ -17,7 +17,7 @@ import torch.distributed as dist
 
 from . import ops
 from ._lib import check, lib
-from .sampler import MPSampler, SPVirtualSampler, create_block
+from .sampler import SPVirtualSampler, create_block
 
 BYTES_PER_ELEMENT = 4
 # MiB/s, python/npc/cost_model/estimator.py:16-20 (measured by its authors on their machines)
