@@ -278,6 +278,36 @@ def main():
             assert all_cm[r][1] == all_cm[0][1] and all_cm[r][2] == all_cm[0][2], "ranks disagree on the best strategy"
     ops.check_status()
 
+    # --- the committed two-rank fixture (tests/golden/strategies_small.npz): SNP with virtual nodes and NFP
+    if world == 2:
+        gdir = os.path.join(ROOT, "tests", "golden")
+        zf = np.load(os.path.join(gdir, "path_small.npz"))
+        fx = np.load(os.path.join(gdir, "strategies_small.npz"))
+        nf = int(zf["num_nodes"])
+        ops.mix_cache_graphs(0, e, e, e, torch.from_numpy(zf["indptr"]).cuda(), torch.from_numpy(zf["indices"]).cuda())
+        ops.register_min_vids(torch.from_numpy(np.linspace(0, nf, 3).astype(I64)))
+        fseeds = torch.from_numpy(fx[f"ws2/{rank}/seeds"]).cuda()
+        for with_dst in (False, True):
+            ops.set_sampling(key=99, call_id=4)
+            fs = apt_b200.SPVirtualSampler(rank, [5], model="SAGE", shuffle_with_dst=with_dst)
+            f_in, _, (fb2, fb1), f_send, f_recv = fs.sample(None, fseeds)
+            got_f = dict(fs.last, input_nodes=f_in, unique_src=fb2.src_ids, block1_dst=fb1.coo_col,
+                         block2_src=fb2.coo_row, block2_dst=fb2.coo_col, send_sizes=f_send, recv_sizes=f_recv)
+            for name in ("neighbors", "sorted_allnodes", "unique_frontier", "send_frontier", "vir_src", "ori_src",
+                         "send_sizes", "recv_sizes", "unique_src", "unique_dst", "block1_dst", "block2_src",
+                         "block2_dst", "input_nodes"):
+                assert np.array_equal(host(got_f[name]), fx[f"ws2/{rank}/snp{int(with_dst)}/{name}"]), \
+                    f"rank {rank}: fixture, SNP with_dst={with_dst}: {name}"
+        ops.set_sampling(key=99, call_id=4)
+        f_in, _, f_blocks, f_send, f_recv = apt_b200.MPSampler(rank, [5], chained=False).sample(None, fseeds)
+        f_row, f_col, f_fsz, f_csz, f_ssz = f_blocks[0]
+        for name, v in dict(all_frontier=f_in, all_coo_row=f_row, all_coo_col=f_col, send_size=f_send, recv_size=f_recv,
+                            recv_frontier_size=f_fsz, recv_coo_size=f_csz).items():
+            assert np.array_equal(host(v), fx[f"ws2/{rank}/nfp/{name}"]), f"rank {rank}: fixture, NFP: {name}"
+        ops.check_status()
+        ops.mix_cache_graphs(0, e, e, e, torch.from_numpy(indptr).cuda(), torch.from_numpy(indices).cuda())
+        ops.register_min_vids(torch.from_numpy(mv))
+
     # --- feature shuffle forward/backward (fp32 1 KiB rows, bf16 512 B rows, odd width)
     for dtype, D in ((torch.float32, 256), (torch.bfloat16, 256), (torch.float32, 3)):
         g = torch.Generator(device="cuda").manual_seed(7)

@@ -194,3 +194,38 @@ def test_chained_sampler_equals_operator_by_operator_form():
                 assert torch.equal(la[k], lb[k]), k
     ops.check_status()
     reset_world()
+
+
+def test_committed_strategy_fixture_one_rank():
+    # tests/golden/strategies_small.npz, one-rank cases: SNP with virtual nodes (both variants) and NFP
+    import os
+
+    from apt_b200.sampler import MPSampler
+
+    golden = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    z = np.load(os.path.join(golden, "path_small.npz"))
+    want = np.load(os.path.join(golden, "strategies_small.npz"))
+    n = int(z["num_nodes"])
+    reset_world()
+    install_graph(z["indptr"], z["indices"])
+    _world(1, 0, n)
+    seeds = dev(want["ws1/0/seeds"])
+    for with_dst in (False, True):
+        ops.set_sampling(key=99, call_id=4)
+        smp = SPVirtualSampler(0, [5], model="SAGE", shuffle_with_dst=with_dst)
+        input_nodes, _, (block2, block1), send_sizes, recv_sizes = smp.sample(None, seeds)
+        got = dict(smp.last, input_nodes=input_nodes, unique_src=block2.src_ids, block1_dst=block1.coo_col,
+                   block2_src=block2.coo_row, block2_dst=block2.coo_col, send_sizes=send_sizes, recv_sizes=recv_sizes)
+        for name in ("neighbors", "sorted_allnodes", "unique_frontier", "send_frontier", "vir_src", "ori_src",
+                     "send_sizes", "recv_sizes", "unique_src", "unique_dst", "block1_dst", "block2_src", "block2_dst",
+                     "input_nodes"):
+            assert np.array_equal(host(got[name]), want[f"ws1/0/snp{int(with_dst)}/{name}"]), (with_dst, name)
+    ops.set_sampling(key=99, call_id=4)
+    in_nodes, _, blocks, send_size, recv_size = MPSampler(0, [5]).sample(None, seeds)
+    row, col, fsz, csz, ssz = blocks[0]
+    got = dict(all_frontier=in_nodes, all_coo_row=row, all_coo_col=col, send_size=send_size, recv_size=recv_size,
+               recv_frontier_size=fsz, recv_coo_size=csz)
+    for name, v in got.items():
+        assert np.array_equal(host(v), want[f"ws1/0/nfp/{name}"]), name
+    ops.check_status()
+    reset_world()

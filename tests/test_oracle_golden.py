@@ -414,3 +414,18 @@ def test_committed_fixture_matches_oracle():
     src, dst = orc.rmat_edges(int(z["graph_seed"]), 0, int(z["num_edges"]), int(z["scale"]), int(z["num_nodes"]))
     ip, ix = orc.csc_from_edges(src, dst, int(z["num_nodes"]))
     assert np.array_equal(ip, indptr) and np.array_equal(ix, indices)
+
+
+def test_committed_strategy_fixture_matches_oracle():
+    # tests/golden/strategies_small.npz (tests/golden/make_golden.py): SNP with virtual nodes and NFP
+    # on the fixture graph for one and two ranks; the oracle must still produce every array
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(GOLDEN, "make_golden.py"))
+    mg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mg)
+    z = np.load(os.path.join(GOLDEN, "path_small.npz"))
+    want = np.load(os.path.join(GOLDEN, "strategies_small.npz"))
+    got = mg.strategy_cases(z["indptr"], z["indices"], int(z["num_nodes"]))
+    assert sorted(got) == sorted(want.files)
+    for k in want.files:
+        assert np.array_equal(got[k], want[k]), k
