@@ -765,7 +765,11 @@ def main():
     hit_gbs = hit_bytes / (hit_ms / max(hit_n, 1) * 1e-3) / 1e9 if hit_ms > 0 else 0.0
     roofline = {"kernel": "k_copy_hits (gather, cache hits)", "bound": "hbm", "achieved": round(hit_gbs, 1),
                 "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(hit_gbs / peak, 4),
-                "traffic": None, "rows_per_launch": rows_total / max(hit_n, 1),
+                # DRAM bytes of this launch, scaled from the ncu capture of the same kernel on 1 081 344 rows
+                # (1054.7 MB of traffic for 1115.9 MB algorithmic, profiles/gather_hit_copy_1M_rows_512B.md):
+                # a streaming copy's traffic grows with the rows it moves
+                "traffic": round(hit_bytes * 1054.7 / 1115.9), "traffic_source": "ncu on 1 081 344 rows, scaled by rows",
+                "rows_per_launch": rows_total / max(hit_n, 1),
                 "hit_rows_per_launch": hits_total / max(hit_n, 1), "us_per_launch": 1000.0 * hit_ms / max(hit_n, 1)}
     miss_bytes = miss_total * row_bytes / max(miss_n, 1)
     miss_gbs = miss_bytes / (miss_ms / max(miss_n, 1) * 1e-3) / 1e9 if miss_ms > 0 else 0.0
