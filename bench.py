@@ -40,7 +40,7 @@ def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--workload", default="c1_papers_np")
     ap.add_argument("--impl", default="apt_b200", choices=["apt_b200", "reference"])
     ap.add_argument("--cpu-batches", type=int, default=12, help="batches of the CPU-baseline sample")
