@@ -108,3 +108,34 @@ def test_library_backend_collectives_two_gloo_ranks(tmp_path):
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, MASTER_ADDR="127.0.0.1"))
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     assert res.stdout.count("COLL_OK") == 2
+
+
+def test_cost_model_host_arithmetic_matches_oracle():
+    """The volume and time formulas of the cost model (python/npc/cost_model/estimator.py:112-188) need no GPU."""
+    import numpy as np
+
+    from apt_b200 import planner
+    from oracle import oracle as orc
+
+    rng = np.random.default_rng(12)
+    for ws in (2, 3, 8):
+        for rank in range(ws):
+            so, ro = np.cumsum(rng.integers(0, 50, ws)), np.cumsum(rng.integers(0, 50, ws))
+            assert planner.get_np_reshuffle_vol(ws, rank, torch.from_numpy(so), torch.from_numpy(ro), 128) == \
+                orc.np_reshuffle_vol(ws, rank, so, ro, 128)
+            for with_dst in (False, True):
+                k = 3 if with_dst else 2
+                ss, rs = rng.integers(0, 50, k * ws), rng.integers(0, 50, k * ws)
+                assert planner.get_sp_reshuffle_vol(ws, rank, torch.from_numpy(ss), torch.from_numpy(rs), 32, "GCN",
+                                                    with_dst) == orc.sp_reshuffle_vol(ws, rank, ss, rs, 32, with_dst)
+            sizes = rng.integers(1, 50, ws)
+            assert planner.get_mp_reshuffle_vol(ws, torch.tensor([int(sizes[rank])]), torch.from_numpy(sizes), 64) == \
+                orc.mp_reshuffle_vol(ws, [int(sizes[rank])], sizes, 64)
+    # a GAT layer exchanges hidden x heads columns, through the NP formula (estimator.py:121-122, :149-150)
+    assert planner.get_reshuffle_dim("GAT", 64, 4) == 256 and planner.get_reshuffle_dim("SAGE", 64, 4) == 64
+    so = torch.tensor([4, 9, 15])
+    assert planner.get_sp_reshuffle_vol(3, 1, so, so, 256, "GAT") == planner.get_np_reshuffle_vol(3, 1, so, so, 256)
+    vol = 3 * 1024 * 1024
+    assert planner.cachemiss_vol_to_time(vol) == orc.vol_to_seconds(vol, planner.REFERENCE_BW["pcie"])
+    assert planner.reshuffle_vol_to_time(vol) == orc.vol_to_seconds(vol, planner.REFERENCE_BW["network"])
+    assert planner.reshuffle_vol_to_time(vol, planner.B200_BW) < planner.reshuffle_vol_to_time(vol)
