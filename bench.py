@@ -43,7 +43,8 @@ def parse():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--workload", default="c1_papers_np")
     ap.add_argument("--impl", default="apt_b200", choices=["apt_b200", "reference"])
-    ap.add_argument("--cpu-batches", type=int, default=12, help="batches of the CPU-baseline sample")
+    ap.add_argument("--cpu-batches", type=int, default=1000,
+                    help="batches of the CPU-baseline sample (about 10 s of work on 16 host threads)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--stage", default="minibatch", choices=["minibatch", "gather", "shuffle", "ops", "strategies"],
                     help="gather: the cached feature gather alone on a synthetic table; "
