@@ -73,6 +73,8 @@ PROTOTYPES = {
     "apt_p2p_region_bytes": (c_size_t, [P]),
     "apt_p2p_push": (c_int, [P, P, P, c_int, P, c_int64, c_int64, P, P]),
     "apt_p2p_wait": (c_int, [P, P, P, c_int64, P]),
+    "apt_p2p_default_timeout_ns": (c_int64, []),
+    "apt_p2p_poisoned": (c_int, [P, ctypes.POINTER(c_int)]),
     "apt_p2p_pull": (c_int, [P, P, P, c_int, c_int64, c_int64, c_int64, P, P]),
     "apt_p2p_pull_sum": (c_int, [P, P, c_int, c_int64, c_int64, P, P, P]),
     "apt_p2p_create_landing": (c_int, [c_int, c_int, c_size_t, c_size_t, c_int, ctypes.POINTER(P), P]),

@@ -15,6 +15,7 @@
 // so an enqueued sequence can be captured in a CUDA graph and replayed.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -28,6 +29,10 @@ constexpr size_t kHeaderBytes = 16384;
 constexpr size_t kCounterOffset = 2048;
 constexpr size_t kPushSeqOffset = 2112;  // uint32: all-to-alls this rank has pushed
 constexpr size_t kWaitSeqOffset = 2120;  // uint32: all-to-alls this rank has waited for
+// uint32, sticky: a wait of this rank ran out of time. From then on the two-region rotation no longer
+// proves that a peer has read a region before it is written again, so every later push, wait and fused
+// all-to-all of this rank refuses to run (status APT_FLAG_PEER_TIMEOUT) until the inbox is created anew.
+constexpr size_t kPoisonOffset = 2128;
 // fused (chunked) all-to-all: flags[parity][source][chunk], one ticket counter per chunk, one for the end
 constexpr int kMaxChunks = 8;
 constexpr size_t kChunkFlagOffset = 4096;
@@ -121,6 +126,11 @@ k_p2p_push(const char* __restrict__ src, const int64_t* __restrict__ src_index,
            size_t landing_off /* 0: rows go to the inbox region */, size_t landing_bytes) {
   __shared__ int64_t soff[kP2pMaxRanks + 1];
   __shared__ bool is_last;
+  if (*(const volatile uint32_t*)(peers.base[me] + kPoisonOffset)) {
+    // an earlier wait of this rank timed out: nothing is stored on any peer and no flag is published
+    if (blockIdx.x == 0 && threadIdx.x == 0) atomicOr(status, APT_FLAG_PEER_TIMEOUT);
+    return;
+  }
   // Every block reads the sequence number before it takes its ticket below, and
   // the number only moves after the last ticket, so all blocks see the same epoch.
   uint32_t* push_seq = (uint32_t*)(peers.base[me] + kPushSeqOffset);
@@ -240,10 +250,19 @@ k_p2p_push(const char* __restrict__ src, const int64_t* __restrict__ src_index,
 __global__ void k_p2p_wait(char* local_base, int world_size, int64_t timeout_ns,
                            int64_t* __restrict__ out_counts, int32_t* status) {
   uint32_t* wait_seq = (uint32_t*)(local_base + kWaitSeqOffset);
-  const uint32_t epoch = *(volatile uint32_t*)wait_seq + 1u;
-  const int parity = (int)(epoch & 1u);
+  volatile uint32_t* poison = (volatile uint32_t*)(local_base + kPoisonOffset);
   const int r = threadIdx.x;
   const bool live = r < world_size;
+  if (*poison) {   // refused: see kPoisonOffset
+    if (live) out_counts[r] = 0;
+    if (r == 0) {
+      out_counts[world_size] = 0;
+      atomicOr(status, APT_FLAG_PEER_TIMEOUT);
+    }
+    return;
+  }
+  const uint32_t epoch = *(volatile uint32_t*)wait_seq + 1u;
+  const int parity = (int)(epoch & 1u);
   const uint64_t* flag = (const uint64_t*)local_base + (size_t)parity * kP2pMaxRanks + (live ? r : 0);
   const uint64_t t0 = global_timer_ns();
   uint64_t v = live ? ld_acquire_sys(flag) : ((uint64_t)epoch << 32);
@@ -259,6 +278,7 @@ __global__ void k_p2p_wait(char* local_base, int world_size, int64_t timeout_ns,
     got = (int64_t)(uint32_t)v;
   } else {
     atomicOr(status, APT_FLAG_PEER_TIMEOUT);
+    *poison = 1u;
   }
   if (live) out_counts[r] = got;
   // total over the peers, for operators chained behind the exchange
@@ -293,7 +313,8 @@ k_p2p_pull(const char* __restrict__ local_base, const int64_t* __restrict__ recv
   const int64_t total = roff[world_size];
   // never more rows than the destination holds: a caller that sized it by an upper bound of what
   // the peers send loses the excess (and can see it in the counts) instead of writing past the end
-  const int64_t n = MODE == 1 ? num_dst_rows : (total < num_dst_rows ? total : num_dst_rows);
+  // (with a scatter index every concatenation row is visited; its destination row is checked instead)
+  const int64_t n = MODE == 1 ? num_dst_rows : MODE == 2 ? total : (total < num_dst_rows ? total : num_dst_rows);
   const int lane = threadIdx.x & 31;
   const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
   const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -310,7 +331,7 @@ k_p2p_pull(const char* __restrict__ local_base, const int64_t* __restrict__ recv
       if (i < n) {
         const int64_t j = MODE == 1 ? index[i] : i;          // concatenation row
         const int64_t d = MODE == 2 ? index[i] : i;          // destination row
-        if (j >= 0 && j < total && d >= 0) {
+        if (j >= 0 && j < total && d >= 0 && d < num_dst_rows) {
           int r = 0;
           while (roff[r + 1] <= j) ++r;
           sp[k] = data + (size_t)r * region_bytes + (j - roff[r]) * row_bytes;
@@ -419,6 +440,10 @@ k_p2p_fused(FusedA2A a) {
     roff[threadIdx.x + 1] = a.recv_offsets[threadIdx.x];
   }
   char* local = a.peers.base[me];
+  if (*(const volatile uint32_t*)(local + kPoisonOffset)) {   // refused: see kPoisonOffset
+    if (blockIdx.x == 0 && threadIdx.x == 0) atomicOr(a.status, APT_FLAG_PEER_TIMEOUT);
+    return;
+  }
   uint32_t* push_seq = (uint32_t*)(local + kPushSeqOffset);
   const uint32_t epoch = *(volatile uint32_t*)push_seq + 1u;   // moves only after every block has finished
   const int parity = (int)(epoch & 1u);
@@ -602,13 +627,18 @@ k_p2p_fused(FusedA2A a) {
   }
   if (overflow) atomicOr(a.status, APT_FLAG_TABLE_FULL);
   if (timed_out && threadIdx.x == 0) atomicOr(a.status, APT_FLAG_PEER_TIMEOUT);
+  // the poison word is written by the last block below, after every block has read it above
   // the last block to finish advances both sequence numbers: the next all-to-all, fused or not,
   // then uses the other half of the inbox
   __syncthreads();
   if (threadIdx.x == 0) {
     int32_t* done = (int32_t*)(local + kDoneCounterOffset);
+    int32_t* tflag = (int32_t*)(local + kDoneCounterOffset) + 1;   // some block of this launch timed out
+    if (timed_out) atomicOr(tflag, 1);
+    __threadfence();
     if (atomicAdd(done, 1) == (int)gridDim.x - 1) {
       *done = 0;
+      if (atomicExch(tflag, 0)) *(volatile uint32_t*)(local + kPoisonOffset) = 1u;
       *(volatile uint32_t*)push_seq = epoch;
       *(volatile uint32_t*)(local + kWaitSeqOffset) = epoch;
     }
@@ -770,11 +800,36 @@ extern "C" int apt_p2p_push_direct(apt_p2p* ctx, const void* src, const int64_t*
                          stream);
 }
 
+// Bound of a device-side wait when the caller passes none: APT_P2P_TIMEOUT_MS (read once), default
+// 30 s. It has to exceed the largest skew between ranks that is not a failure (a rank that is still
+// registering host memory, loading data or compiling while its peers already wait).
+static int64_t default_timeout_ns() {
+  static const int64_t ns = [] {
+    const char* e = getenv("APT_P2P_TIMEOUT_MS");
+    long long ms = e ? atoll(e) : 0;
+    if (ms <= 0) ms = 30000;
+    if (ms > 600000) ms = 600000;
+    return (int64_t)ms * 1000000ll;
+  }();
+  return ns;
+}
+
+extern "C" int64_t apt_p2p_default_timeout_ns(void) { return default_timeout_ns(); }
+
+extern "C" int apt_p2p_poisoned(apt_p2p* ctx, int* out_poisoned) {
+  using namespace apt;
+  APT_CHECK_ARG(ctx && out_poisoned, "apt_p2p_poisoned: bad argument");
+  uint32_t v = 0;
+  APT_CUDA(cudaMemcpy(&v, ctx->local_base + kPoisonOffset, sizeof(v), cudaMemcpyDeviceToHost));
+  *out_poisoned = v != 0;
+  return APT_OK;
+}
+
 extern "C" int apt_p2p_wait(apt_p2p* ctx, int64_t* out_recv_counts, int32_t* status_word,
                             int64_t timeout_ns, void* stream) {
   using namespace apt;
   APT_CHECK_ARG(ctx && out_recv_counts && status_word, "apt_p2p_wait: bad argument");
-  if (timeout_ns <= 0) timeout_ns = 2000000000ll;
+  if (timeout_ns <= 0) timeout_ns = default_timeout_ns();
   cudaStream_t s = (cudaStream_t)stream;
   ProfScope prof("p2p_wait", s);
   APT_LAUNCH(k_p2p_wait, 1, 32, 0, s, ctx->local_base, ctx->world_size, timeout_ns, out_recv_counts,
@@ -865,7 +920,7 @@ extern "C" int apt_p2p_alltoall_fused(apt_p2p* ctx, const void* src, const int64
   APT_CHECK_ARG((size_t)row_bytes <= ctx->region_bytes, "apt_p2p_alltoall_fused: row larger than an inbox region");
   for (int r = 0; r < ctx->world_size; ++r)
     APT_CHECK_ARG(ctx->peer_base[r], "apt_p2p_alltoall_fused: peer %d is not attached", r);
-  if (timeout_ns <= 0) timeout_ns = 2000000000ll;
+  if (timeout_ns <= 0) timeout_ns = default_timeout_ns();
   FusedA2A a;
   a.src = (const char*)src;
   a.src_index = src_index;

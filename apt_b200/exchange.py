@@ -199,6 +199,14 @@ class P2PExchange:
     def region_bytes(self):
         return int(lib.apt_p2p_region_bytes(self.ctx))
 
+    def poisoned(self) -> bool:
+        """True once a wait of this rank ran out of time. The inbox then refuses every further
+        exchange (the kernels set the peer-timeout flag and store nothing): all ranks have to
+        build new exchanges (ops.init) behind a host barrier."""
+        out = ctypes.c_int(0)
+        check(lib.apt_p2p_poisoned(self.ctx, ctypes.byref(out)))
+        return bool(out.value)
+
     def _offsets_to_device(self, send_cpu, recv_cpu=None):
         """CPU offsets -> device, through a pinned staging block so the copy does
         not stall the stream. Four alternating slots let back-to-back calls keep

@@ -168,7 +168,8 @@ def _flag_text(flags):
         _lib.FLAG_FEAT_NOT_EXIST: "feature row neither cached nor in host memory",
         _lib.FLAG_ZERO_DEGREE: "node without in-neighbours sampled",
         _lib.FLAG_TABLE_FULL: "workspace or inbox region too small",
-        _lib.FLAG_PEER_TIMEOUT: "a peer's data did not arrive in time",
+        _lib.FLAG_PEER_TIMEOUT: "a peer's data did not arrive within the wait bound (APT_P2P_TIMEOUT_MS); the "
+                                "exchange refuses further use: call init() again on every rank, behind a barrier",
         _lib.FLAG_NOT_GROUPED: "edges of a block are not grouped by destination",
         _lib.FLAG_SIZE_MISMATCH: "a peer sent another number of rows than the reduction expects",
     }

@@ -592,7 +592,29 @@ def stage_strategies(args):
 
 
 # ------------------------------------------------------------------------- main
+PHASE = ["setup"]     # the part of the run an exception came from
+
+
 def main():
+    """Runs the benchmark; a failing rank prints its traceback as its last lines on stderr and a
+    one-line JSON record of the error on stdout before it exits non-zero, so that the cause
+    survives the launcher's own summary."""
+    try:
+        run()
+    except BaseException as exc:   # noqa: BLE001  (SystemExit included: say why the rank left)
+        if isinstance(exc, SystemExit) and exc.code in (0, None):
+            raise
+        import traceback
+
+        rank = os.environ.get("RANK", "0")
+        text = traceback.format_exc()
+        print(json.dumps({"error": f"{type(exc).__name__}: {exc}", "phase": PHASE[0], "rank": int(rank)}), flush=True)
+        sys.stderr.write(f"\n[bench.py rank {rank}] failed in phase '{PHASE[0]}':\n{text}")
+        sys.stderr.flush()
+        os._exit(1)      # do not wait in a collective's destructor for peers that are still running
+
+
+def run():
     args = parse()
     if args.stage == "gather":
         return stage_gather(args)
@@ -634,8 +656,8 @@ def main():
         "strategy": "NP (outermost hop sampled at the owner, random contiguous partition)",
         "topology": "int64 CSC resident in HBM", "host_features": "pinned host memory read by the gather kernel",
         "l2": "inputs (CSC 13.7 GB, feature tables) exceed the 126 MB L2; every step touches other rows",
-        "shuffle_backend": ops.STATE.shuffle_backend if ws_eff > 1 else "local", "setup_s": round(setup_s, 1),
     }
+    run_info = {"setup_s": round(setup_s, 1), "shuffle_backend": ops.STATE.shuffle_backend if ws_eff > 1 else "local"}
 
     if args.impl == "reference":
         cpu = CpuPath(inst)
@@ -645,7 +667,7 @@ def main():
             "impl": "reference", "metric": METRIC, "value": rate, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 / rate, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "int64 ids, " + w.dtype + " rows", "data": "synthetic",
-            "config": config,
+            "config": config, "run_info": run_info,
             "cpu_baseline": {"value": rate, "unit": UNIT, "cores": cpu.cores, "kind": "port",
                              "sample": f"{args.steps} mini-batches of {w.batch} seeds on the full graph, "
                                        f"about {rows:.0f} gathered rows each, OpenMP over all host threads"},
@@ -670,6 +692,9 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def phase(name):
+        PHASE[0] = name
+
     def reduce_max(x):
         if world == 1:
             return x
@@ -688,9 +713,14 @@ def main():
     ops.set_sampling(key=7777777, call_id=0)
     clocks = ClockSampler(local_rank)
     clocks.start()          # sampled from the warm-up on: the timed region alone can be shorter than one sample period
+    # every phase that exchanges between the ranks starts behind a barrier: host-side work of different
+    # length (registering the host table, stopping the clock sampler) must not eat into the wait bound
+    phase("warmup")
+    barrier()
     for b in dev_batches[:args.warmup]:
         step(b)
     ops.check_status()
+    phase("timed")
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     torch.cuda.nvtx.range_push("apt_timed")
@@ -706,6 +736,7 @@ def main():
     ops.check_status()
 
     # ---- spread of the single steps: an event pair around each of up to 100 of the same steps
+    phase("spread")
     n_spread = min(args.steps, 100)
     marks = [torch.cuda.Event(enable_timing=True) for _ in range(n_spread + 1)]
     barrier()
@@ -722,7 +753,9 @@ def main():
     # ---- the same steps once more with per-kernel CUDA events (for the roofline and the
     # launch count). Timing events cannot live inside a captured graph, so this pass
     # enqueues the kernels one by one; its own rate is reported as profiled_value.
+    phase("profiled")
     ops.profile_enable(True)
+    barrier()
     for b in dev_batches[:args.warmup]:
         step(b)
     for tag in ("sample", "relabel", "bucket", "unique_sorted", "gather_classify", "gather_hit", "gather_miss",
@@ -776,6 +809,7 @@ def main():
     miss_gbs = miss_bytes / (miss_ms / max(miss_n, 1) * 1e-3) / 1e9 if miss_ms > 0 else 0.0
 
     # ---- measured host-link rate (pinned host -> device copy), the miss kernel's ceiling
+    phase("host_link_probe")
     probe_rows = min(w.num_nodes, (1 << 30) // row_bytes)
     dst = torch.empty((probe_rows, w.feat_dim), dtype=inst.host_feats.dtype, device="cuda")
     dst.copy_(inst.host_feats[:probe_rows], non_blocking=True)
@@ -801,6 +835,8 @@ def main():
         digest = torch.cat([x[0], x[-1]]).float().cpu()      # device -> host read of the step's result
         return digest
 
+    phase("e2e")
+    barrier()
     for b in host_batches[:args.warmup]:
         e2e_step(b)
     barrier()
@@ -819,7 +855,8 @@ def main():
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int64 ids, " + w.dtype + " rows", "data": "synthetic", "config": config, "clocks": clock_info,
+        "dtype": "int64 ids, " + w.dtype + " rows", "data": "synthetic", "config": config, "run_info": run_info,
+        "clocks": clock_info,
         "e2e": e2e, "gpu_launches": int(reduce_sum(launches)),
         "launch_mode": "one CUDA graph replay per mini-batch" if graph_mode else
                        "kernels enqueued one by one, sizes chained on the device",

@@ -466,17 +466,32 @@ int apt_p2p_push(apt_p2p* ctx, const void* src, const int64_t* src_index,
                  int index_is_dest, const int64_t* send_offsets, int64_t max_rows,
                  int64_t row_bytes, int32_t* status_word, void* stream);
 /* Wait for this epoch's flags; out_recv_counts int64[world_size + 1] (device)
- * receives the rows each peer sent and, in the last entry, their total. timeout_ns <= 0 selects 2 s. On timeout
- * APT_FLAG_PEER_TIMEOUT is ORed into status_word and counts are set to 0. */
+ * receives the rows each peer sent and, in the last entry, their total.
+ * timeout_ns <= 0 selects the default bound: the environment variable
+ * APT_P2P_TIMEOUT_MS (read once per process), else 30 s; it must exceed any skew
+ * between the ranks that is not a failure. On timeout APT_FLAG_PEER_TIMEOUT is
+ * ORed into status_word, the counts of the missing peers are 0, and the inbox is
+ * marked unusable: the two-region rotation no longer proves that a peer has read
+ * a region before it is written again, so every later apt_p2p_push,
+ * apt_p2p_push_direct, apt_p2p_wait and apt_p2p_alltoall_fused on this context
+ * stores nothing on any peer and sets APT_FLAG_PEER_TIMEOUT again. Recovery:
+ * destroy the contexts of all ranks and create new ones behind a host barrier.
+ * (The reference has no counterpart: a lost peer blocks its ncclGroupEnd for good,
+ * src/ops/collective.cc:234-249.) */
 int apt_p2p_wait(apt_p2p* ctx, int64_t* out_recv_counts, int32_t* status_word,
                  int64_t timeout_ns, void* stream);
+/* The default bound above in nanoseconds, and whether a wait of this context
+ * has timed out (synchronous 4-byte read of the inbox header). */
+int64_t apt_p2p_default_timeout_ns(void);
+int apt_p2p_poisoned(apt_p2p* ctx, int* out_poisoned);
 /* Copy received rows out of the inbox in peer order (peer 0's rows first).
  * If dst_index is NULL row j of the concatenation lands at dst row j; else if
  * index_is_source it is a gather: dst row i = concatenation row dst_index[i]
  * (num_dst_rows rows); else a scatter: concatenation row j lands at
  * dst_index[j]. recv_counts is the device array apt_p2p_wait filled. Without an
- * index, or with a scatter index, at most num_dst_rows rows of the concatenation
- * are copied (the capacity of dst). */
+ * index at most num_dst_rows rows of the concatenation are copied (the capacity
+ * of dst); with a scatter index every row of the concatenation is visited and a
+ * row whose destination lies outside [0, num_dst_rows) is dropped. */
 int apt_p2p_pull(apt_p2p* ctx, const int64_t* recv_counts,
                  const int64_t* dst_index, int index_is_source,
                  int64_t num_dst_rows, int64_t max_rows, int64_t row_bytes,

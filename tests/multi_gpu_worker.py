@@ -67,6 +67,23 @@ def main():
         want = np.concatenate([np.full(recv[r] * expand, r, dtype=I64) for r in range(world)])
         assert np.array_equal(host(out), want), f"alltoall expand {expand}"
 
+    # --- a rank that arrives late but inside the wait bound (APT_P2P_TIMEOUT_MS, default 30 s): the wait
+    # kernels of the others spin until its flags arrive; the result is complete and no status flag is set
+    import time
+    torch.cuda.synchronize()
+    dist.barrier()
+    if rank == world - 1:
+        time.sleep(3.0)
+    send = [50 + rank] * world
+    recv = [50 + r for r in range(world)]
+    inp = torch.full((sum(send),), rank, dtype=torch.int64, device="cuda")
+    out = torch.empty(sum(recv), dtype=torch.int64, device="cuda")
+    ops.alltoall(inp, out, torch.tensor(send).cumsum(0), torch.tensor(recv).cumsum(0), 1, 0)
+    assert np.array_equal(host(out), np.concatenate([np.full(recv[r], r, dtype=I64) for r in range(world)])), \
+        "all-to-all with a late rank"
+    ops.check_status()
+    assert not p2p.poisoned()
+
     # --- NP outer hop: shuffle + unique + sample at the owner
     rng = np.random.default_rng(100 + rank)
     seeds = rng.integers(0, n, 3000 + 101 * rank).astype(I64)

@@ -59,6 +59,25 @@ def test_npc_operator_schemas_match_reference_registry():
     assert len(names) == 29
     for n in names:
         assert hasattr(torch.ops.npc, n)
+    # Argument and return TYPES against what the reference's own library registers:
+    # tests/golden/ref_op_schemas.json holds the schema strings the dispatcher reports after
+    # loading the compiled reference (tests/golden/make_ref_schemas.py). The reference's arguments
+    # are unnamed (_0, _1, ...) because TORCH_LIBRARY infers them from C++ signatures; the names
+    # given here are documentation, so only the types are compared.
+    import json
+
+    with open(os.path.join(ROOT, "tests", "golden", "ref_op_schemas.json")) as f:
+        ref = json.load(f)
+    assert sorted(ref) == sorted(names)
+
+    def types_of(schema_text):
+        sch = torch._C.parse_schema("npc::" + schema_text if not schema_text.startswith("npc::") else schema_text)
+        return [str(a.type) for a in sch.arguments], [str(r.type) for r in sch.returns]
+
+    for n in names:
+        ours = torch._C._get_schema("npc::" + n, "")
+        got = ([str(a.type) for a in ours.arguments], [str(r.type) for r in ours.returns])
+        assert got == types_of(ref[n]), f"npc::{n}: {ours} differs from the reference's {ref[n]}"
     ident = torch.ops.npc.nccl_get_unique_id()
     assert ident.dtype == torch.int64 and ident.numel() == 16 and not ident.is_cuda
 

@@ -23,6 +23,15 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+def _raw_bytes(ptr, nbytes):
+    """A uint8 tensor over device memory the library owns (no copy)."""
+
+    class _Raw:
+        __cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1", "data": (int(ptr), False), "version": 2}
+
+    return torch.as_tensor(_Raw(), device="cuda")
+
+
 class Ranks:
     """N inbox contexts in one process, each attached to the others by pointer."""
 
@@ -158,8 +167,53 @@ def test_p2p_wait_times_out_with_a_status_not_a_hang():
         torch.cuda.synchronize()
         assert host(c).tolist() == [4, 0, 4]
         assert int(ranks.status[0].item()) & _lib.FLAG_PEER_TIMEOUT
-        # the context stays usable
+        # the GPU context stays usable ...
         assert int((src + 1).sum().item()) == 36
+        # ... but the inbox does not: after a wait that ran out, a region could be overwritten before its
+        # owner has read it, so the next push stores nothing on any peer and reports the time-out again
+        poisoned = ctypes.c_int(0)
+        check(lib.apt_p2p_poisoned(ranks.ctx[0], ctypes.byref(poisoned)))
+        assert poisoned.value == 1
+        check(lib.apt_p2p_poisoned(ranks.ctx[1], ctypes.byref(poisoned)))
+        assert poisoned.value == 0
+        ranks.status.zero_()
+        region = int(lib.apt_p2p_region_bytes(ranks.ctx[1]))
+        header = 16384
+        peer_inbox = _raw_bytes(lib.apt_p2p_local_base(ranks.ctx[1]), header + 4 * region)
+        before = peer_inbox[header:].clone()
+        src2 = torch.full((8,), 77, dtype=torch.int64, device="cuda")
+        check(lib.apt_p2p_push(ranks.ctx[0], src2.data_ptr(), None, 0, off.data_ptr(), 8, 8, ranks.status.data_ptr(), _stream()))
+        check(lib.apt_p2p_wait(ranks.ctx[0], c.data_ptr(), ranks.status.data_ptr(), 50_000_000, _stream()))
+        torch.cuda.synchronize()
+        assert int(ranks.status[0].item()) & _lib.FLAG_PEER_TIMEOUT
+        assert host(c).tolist() == [0, 0, 0]
+        assert torch.equal(peer_inbox[header:], before)       # nothing reached the peer
+    finally:
+        ranks.close()
+    # inboxes created anew (behind a host barrier when the ranks are processes) work again
+    ranks = Ranks(2)
+    try:
+        srcs = [torch.arange(6, dtype=torch.int64, device="cuda") + 10 * r for r in range(2)]
+        counts = ranks.alltoall(srcs, [[2, 6], [5, 6]], 8)
+        out = torch.empty(7, dtype=torch.int64, device="cuda")
+        ranks.pull(0, counts[0], out, 8)
+        assert host(out).tolist() == [0, 1, 10, 11, 12, 13, 14]
+        assert int(ranks.status[0].item()) == 0
+    finally:
+        ranks.close()
+
+
+def test_p2p_pull_scatter_index_is_bounded():
+    # a scatter index that names a row outside the destination drops that row instead of writing past the end
+    ranks = Ranks(1)
+    try:
+        src = torch.arange(6, dtype=torch.int64, device="cuda") + 100
+        counts = ranks.alltoall([src], [[6]], 8)
+        dst = torch.full((8,), -1, dtype=torch.int64, device="cuda")   # 4 rows belong to the call, 4 are a guard
+        index = dev(np.array([3, 0, 9, 1, -2, 2], dtype=I64))
+        check(lib.apt_p2p_pull(ranks.ctx[0], counts[0].data_ptr(), index.data_ptr(), 0, 4, 6, 8, dst.data_ptr(), _stream()))
+        torch.cuda.synchronize()
+        assert host(dst).tolist() == [101, 103, 105, 100, -1, -1, -1, -1]
     finally:
         ranks.close()
 
