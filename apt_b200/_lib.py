@@ -39,6 +39,8 @@ PROTOTYPES = {
     "apt_relabel_workspace_bytes": (c_size_t, [c_int64]),
     "apt_relabel_workspace_init": (c_int, [P, c_size_t, P]),
     "apt_relabel_csc": (c_int, [P, c_int64, P, P, c_int64, P, c_size_t, P, P, P, P, P]),
+    "apt_sample_relabel_csc": (c_int, [P, c_int64, P, c_int, P, c_int64, P, P, P, P, c_uint64, c_uint32, P, P, c_size_t,
+                                       P, P, P, P, P, P]),
     "apt_bucket_workspace_bytes": (c_size_t, [c_int64, c_int]),
     "apt_bucket_by_owner": (c_int, [P, c_int64, P, P, c_int, c_int64, c_int, c_int, c_int, P, c_size_t, P, P, P, P, P]),
     "apt_unique_workspace_bytes": (c_size_t, [c_int64]),
@@ -46,6 +48,8 @@ PROTOTYPES = {
     "apt_unique_sorted": (c_int, [P, c_int64, P, c_int64, c_int64, P, c_size_t, P, P, P, P, P]),
     "apt_gather_workspace_bytes": (c_size_t, [c_int64]),
     "apt_gather_rows": (c_int, [P, c_int64, P, P, c_int64, P, c_int64, c_int64, P, c_int64, c_int64, c_int64, P, P, c_size_t, P, P]),
+    "apt_gather_rows_from": (c_int, [P, c_int64, P, P, P, c_int64, P, c_int64, c_int64, P, c_int64, c_int64, c_int64, P, P,
+                                     c_size_t, P, P]),
     "apt_gather_static_max_rows": (c_int64, []),
     "apt_gather_rows_static": (c_int, [P, c_int64, P, c_int64, P, c_int64, c_int64, P, c_int64, c_int64, c_int64, P, P, P]),
     "apt_spmm_workspace_bytes": (c_size_t, [c_int64, c_int64]),
@@ -92,6 +96,13 @@ for _name, (_res, _args) in PROTOTYPES.items():
     _fn = getattr(lib, _name)  # AttributeError here means header and library disagree
     _fn.restype = _res
     _fn.argtypes = _args
+
+
+# APT_TUNABLES="name=value,name=value": measurement knobs of apt_set_tunable applied at import.
+for _kv in filter(None, os.environ.get("APT_TUNABLES", "").split(",")):
+    _k, _, _v = _kv.partition("=")
+    if lib.apt_set_tunable(_k.strip().encode(), int(_v)) != APT_OK:
+        raise ValueError("APT_TUNABLES: " + lib.apt_last_error().decode("utf-8", "replace"))
 
 
 class AptError(RuntimeError):

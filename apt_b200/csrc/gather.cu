@@ -1,39 +1,36 @@
 // Cache-aware feature-row gather.
 //
-//   k_classify     one thread per requested row: id -> feat_pos_map entry, kept
-//                  in a dense scratch array; rows that live in host memory are
-//                  also appended (warp-aggregated) to a miss list.
-//   k_copy_hits    HBM -> HBM. One warp moves four rows at a time, each lane one
-//                  16-byte vector per row, all loads issued before the first
-//                  store. (A variant that decoded the ids inside the copy kernel,
-//                  32 rows per warp, reached 4.3 TB/s on 1 M rows where this pair
-//                  reaches 6.2 TB/s: the two dependent lookups in front of the
-//                  row loads leave the warp with nothing in flight.)
-//   k_copy_miss    pinned host memory -> HBM over the host link, same mover over
-//                  the miss list. It runs after the hit copy on the same stream:
-//                  measured on B200, running the two at once (second stream, any
-//                  grid size) slows the hit copy by 2-4x and the pair finishes
-//                  later than back to back.
+//   k_gather_hits  decodes and copies in one launch. Every warp owns one contiguous
+//                  share of the requested rows. For 32 rows at a time lane k looks up
+//                  id -> feat_pos_map entry of row k (the two dependent loads happen
+//                  once per 32 rows and for all warps of the SM at the same time), rows
+//                  that live in host memory are appended (warp-aggregated) to a miss
+//                  list, rows in the cache are copied HBM -> HBM, R of them in flight
+//                  per warp, each lane one 16-byte vector per row, all loads issued
+//                  before the first store. The grid is one resident wave and the rows
+//                  are split evenly over its warps, so there is no partial last wave.
+//   k_copy_miss    pinned host memory -> HBM over the host link, over the miss list.
+//                  It runs after the hit copy on the same stream: measured on B200,
+//                  running the two at once (second stream, any grid size) slows the
+//                  hit copy by 2-4x and the pair finishes later than back to back.
 //   k_copy_miss_bulk  variant of the miss copy that stages rows through shared
-//                  memory with cp.async.bulk (gather_miss_mode = 1); measured
-//                  equal or slower than the vector loads, kept for comparison.
+//                  memory with cp.async.bulk (gather_miss_mode = 1); measured equal
+//                  or slower than the vector loads, kept for comparison.
 //
 // Rows are opaque bytes. The vector width V is the widest of 16/8/4/2/1 bytes
 // that divides every row size, column offset and base address involved.
 #include <string.h>
 
-#include <mutex>
-
 #include "common.cuh"
 
 namespace apt {
 
-constexpr int kRowsPerGroup = 4;   // rows whose loads are in flight together
+constexpr int kRowsPerGroup = 4;   // rows whose loads are in flight together (miss copy)
 constexpr int kGatherBlock = 256;
 
 struct GatherWs {
-  int64_t* src_pos;    // [n]  feat_pos_map[index[r]], -1 = no such row
-  int32_t* miss_rows;  // [n]  output rows whose source is host memory
+  int64_t* miss_pos;   // [n]  host-table row of every miss
+  int32_t* miss_rows;  // [n]  output row of every miss
   int32_t* miss_count; // [1]
 };
 
@@ -42,7 +39,7 @@ static size_t gather_layout(int64_t n, char* base, GatherWs* ws) {
   const size_t b0 = align_up(rows * 8, 256);
   const size_t b1 = align_up(rows * 4, 256);
   if (ws) {
-    ws->src_pos = (int64_t*)base;
+    ws->miss_pos = (int64_t*)base;
     ws->miss_rows = (int32_t*)(base + b0);
     ws->miss_count = (int32_t*)(base + b0 + b1);
   }
@@ -64,22 +61,32 @@ __device__ __forceinline__ uint4 zero_vec<uint4>() { return make_uint4(0, 0, 0, 
 template <>
 __device__ __forceinline__ uint2 zero_vec<uint2>() { return make_uint2(0, 0); }
 
-// p = feat_pos_map[index[r]]: p >= 0 cache row, p < -1 host row -(p)-2 (queued for
-// the miss copy), p == -1 no such row (zeros + flag).
-__global__ void __launch_bounds__(256)
-k_classify(const int64_t* __restrict__ index, int64_t n, const int64_t* __restrict__ n_dev,
-           const int64_t* __restrict__ pos_map, int64_t num_nodes, int64_t num_dev_rows,
-           int64_t num_uva_rows, GatherWs ws, int32_t* status) {
-  const int lane = threadIdx.x & 31;
+// Output rows [first, n) (first from a device word when first_dev is given, else 0):
+// p = feat_pos_map[index[r]]: p >= 0 cache row (copied here), p < -1 host row -(p)-2
+// (queued for the miss copy), p == -1 no such row (zeros + flag).
+template <typename V, int R>
+__global__ void __launch_bounds__(kGatherBlock, R >= 8 ? 2 : 4)
+k_gather_hits(const int64_t* __restrict__ index, int64_t n, const int64_t* __restrict__ n_dev,
+              const int64_t* __restrict__ first_dev, const int64_t* __restrict__ pos_map,
+              int64_t num_nodes, int64_t num_dev_rows, int64_t num_uva_rows,
+              const char* __restrict__ dev_feats, int64_t row_bytes, char* __restrict__ out,
+              GatherWs ws, int32_t* status) {
   n = effective_n(n, n_dev);
-  int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t first = first_dev ? *first_dev : 0;
+  first = first < 0 ? 0 : (first > n ? n : first);
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t m = n - first;
+  const int64_t lo = first + m * warp / warps, hi = first + m * (warp + 1) / warps;
+  const int chunks = (int)(row_bytes / (int64_t)sizeof(V));
   int flags = 0;
-  // Whole warps iterate together so that the ballot below is convergent.
-  for (int64_t r0 = r - lane; r0 < n; r0 += stride, r += stride) {
-    int64_t p = -1;
-    if (r < n) {
-      const int64_t id = index[r];
+  for (int64_t base = lo; base < hi; base += 32) {
+    const int cnt = hi - base < 32 ? (int)(hi - base) : 32;
+    int64_t p = -2;   // lanes past the share: nothing to do (any p < -1 is skipped by the copy below)
+    if (lane < cnt) {
+      const int64_t id = index[base + lane];
+      p = -1;
       if (id < 0 || id >= num_nodes) {
         flags |= APT_FLAG_ID_OUT_OF_RANGE;
       } else {
@@ -91,48 +98,40 @@ k_classify(const int64_t* __restrict__ index, int64_t n, const int64_t* __restri
           p = -1;
         }
       }
-      ws.src_pos[r] = p;
     }
-    const bool miss = p < -1;
-    const unsigned m = __ballot_sync(0xffffffffu, miss);
-    if (m) {
-      int base = 0;
-      const int leader = __ffs(m) - 1;
-      if (lane == leader) base = atomicAdd(ws.miss_count, __popc(m));
-      base = __shfl_sync(0xffffffffu, base, leader);
-      if (miss) ws.miss_rows[base + __popc(m & ((1u << lane) - 1u))] = (int32_t)r;
+    const bool miss = lane < cnt && p < -1;
+    const unsigned mm = __ballot_sync(0xffffffffu, miss);
+    if (mm) {
+      int at = 0;
+      const int leader = __ffs(mm) - 1;
+      if (lane == leader) at = atomicAdd(ws.miss_count, __popc(mm));
+      at = __shfl_sync(0xffffffffu, at, leader) + __popc(mm & ((1u << lane) - 1u));
+      if (miss) {
+        ws.miss_rows[at] = (int32_t)(base + lane);
+        ws.miss_pos[at] = -p - 2;
+      }
+    }
+    for (int k0 = 0; k0 < cnt; k0 += R) {
+      // the trip count is the same for all lanes, so that the shuffles below are convergent
+      for (int c0 = 0; c0 < chunks; c0 += 32) {
+        const int c = c0 + lane;
+        const bool live = c < chunks;
+        V v[R];
+#pragma unroll
+        for (int k = 0; k < R; ++k) {
+          const int64_t pk = __shfl_sync(0xffffffffu, p, (k0 + k) & 31);
+          v[k] = zero_vec<V>();
+          if (live && k0 + k < cnt && pk >= 0) v[k] = ld_vec<V>((const V*)(dev_feats + pk * row_bytes) + c);
+        }
+#pragma unroll
+        for (int k = 0; k < R; ++k) {
+          const int64_t pk = __shfl_sync(0xffffffffu, p, (k0 + k) & 31);
+          if (live && k0 + k < cnt && pk >= -1) st_vec<V>((V*)(out + (base + k0 + k) * row_bytes) + c, v[k]);
+        }
+      }
     }
   }
   if (flags) atomicOr(status, flags);
-}
-
-// Rows r0..r0+3 of the output come from cache row src_pos[r] (>= 0), are zero
-// (src_pos == -1), or belong to the miss copy (src_pos < -1).
-template <typename V>
-__global__ void __launch_bounds__(kGatherBlock)
-k_copy_hits(int64_t n, const int64_t* __restrict__ n_dev, const int64_t* __restrict__ src_pos,
-            const char* __restrict__ dev_feats, int64_t row_bytes, char* __restrict__ out) {
-  n = effective_n(n, n_dev);
-  const int lane = threadIdx.x & 31;
-  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
-  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int chunks = (int)(row_bytes / (int64_t)sizeof(V));
-  for (int64_t r0 = warp * kRowsPerGroup; r0 < n; r0 += warps * kRowsPerGroup) {
-    int64_t p[kRowsPerGroup];
-#pragma unroll
-    for (int k = 0; k < kRowsPerGroup; ++k) p[k] = r0 + k < n ? src_pos[r0 + k] : (int64_t)-2;
-    for (int c = lane; c < chunks; c += 32) {
-      V v[kRowsPerGroup];
-#pragma unroll
-      for (int k = 0; k < kRowsPerGroup; ++k) {
-        v[k] = zero_vec<V>();
-        if (p[k] >= 0) v[k] = ld_vec<V>((const V*)(dev_feats + p[k] * row_bytes) + c);
-      }
-#pragma unroll
-      for (int k = 0; k < kRowsPerGroup; ++k)
-        if (p[k] >= -1) st_vec<V>((V*)(out + (r0 + k) * row_bytes) + c, v[k]);
-    }
-  }
 }
 
 template <typename V>
@@ -149,7 +148,7 @@ k_copy_miss(GatherWs ws, const char* __restrict__ uva_feats, int64_t uva_row_byt
 #pragma unroll
     for (int k = 0; k < kRowsPerGroup; ++k) {
       r[k] = m0 + k < n ? (int64_t)ws.miss_rows[m0 + k] : (int64_t)-1;
-      p[k] = r[k] >= 0 ? -ws.src_pos[r[k]] - 2 : (int64_t)0;
+      p[k] = m0 + k < n ? ws.miss_pos[m0 + k] : (int64_t)0;
     }
     for (int c = lane; c < chunks; c += 32) {
       V v[kRowsPerGroup];
@@ -169,17 +168,34 @@ k_copy_miss(GatherWs ws, const char* __restrict__ uva_feats, int64_t uva_row_byt
 // ---- tunables (set through apt_set_tunable; defaults are the measured best) ----
 static int g_miss_mode = 0;      // 0: 16-byte ld.global.nc, 1: bulk copy staged through shared memory
 static int g_miss_blocks = kNumSMs;
-static int g_hit_waves = 4;      // cap on waves of 148 x 8 blocks of the hit copy
+static int g_hit_rows = 8;       // rows in flight per warp of the hit copy (4 or 8)
 
 // Bulk-copy variant: one lane per warp asks the copy engine of the SM for the
 // whole row (cp.async.bulk global -> shared, completion on an mbarrier), then
 // for the row's way out (shared -> global). Rows must be multiples of 16 bytes
-// on 16-byte boundaries. Waits are bounded: a row that does not arrive sets
-// the status flag and is skipped.
+// on 16-byte boundaries. Waits are bounded. A row that does not arrive sets the
+// status flag and ends the warp's work: its barrier never completed the phase and
+// its copy may still be in flight, so neither the barrier nor the shared-memory
+// stage may be used again; the warp gives every outstanding copy one more bounded
+// wait and leaves its remaining rows untouched (the flag tells the caller).
 constexpr int kBulkStages = 4;  // rows in flight per warp
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t phase) {
+  uint32_t done = 0;
+  const uint64_t t0 = global_timer_ns();
+  for (int it = 0; it < (1 << 20) && !done; ++it) {
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(done)
+        : "r"(bar), "r"(phase)
+        : "memory");
+    if (!done && (it & 15) == 15 && global_timer_ns() - t0 > 1000000000ull) break;  // 1 s
+  }
+  return done != 0;
 }
 
 __global__ void __launch_bounds__(kGatherBlock)
@@ -199,49 +215,38 @@ k_copy_miss_bulk(GatherWs ws, const char* uva_feats, int64_t uva_row_bytes, int6
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncwarp();
+  if (lane != 0) return;   // one lane drives the copies of its warp
   uint32_t phase = 0;
   for (int64_t m0 = warp * kBulkStages; m0 < n; m0 += warps * kBulkStages) {
-    if (lane == 0) {
-      for (int k = 0; k < kBulkStages; ++k) {
-        if (m0 + k >= n) break;
-        const char* src = uva_feats + (-ws.src_pos[ws.miss_rows[m0 + k]] - 2) * uva_row_bytes + col_offset_bytes;
-        const uint32_t bar = smem_u32(wbar + k), dst = smem_u32(wbuf + (size_t)k * row_bytes);
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)row_bytes)
-                     : "memory");
-        asm volatile(
-            "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-            "l"(src), "r"((uint32_t)row_bytes), "r"(bar)
-            : "memory");
-      }
-      bool failed = false;
-      for (int k = 0; k < kBulkStages; ++k) {
-        if (m0 + k >= n) break;
-        const uint32_t bar = smem_u32(wbar + k);
-        uint32_t done = 0;
-        const uint64_t t0 = global_timer_ns();
-        for (int it = 0; it < (1 << 20) && !done; ++it) {
-          asm volatile(
-              "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-              : "=r"(done)
-              : "r"(bar), "r"(phase)
-              : "memory");
-          if (!done && (it & 15) == 15 && global_timer_ns() - t0 > 1000000000ull) break;  // 1 s
-        }
-        if (!done) {
-          failed = true;
-          continue;
-        }
-        const int64_t r = ws.miss_rows[m0 + k];
-        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(out + r * row_bytes),
-                     "r"(smem_u32(wbuf + (size_t)k * row_bytes)), "r"((uint32_t)row_bytes)
-                     : "memory");
-      }
-      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-      if (failed) atomicOr(status, APT_FLAG_PEER_TIMEOUT);
+    const int cnt = n - m0 < kBulkStages ? (int)(n - m0) : kBulkStages;
+    for (int k = 0; k < cnt; ++k) {
+      const char* src = uva_feats + ws.miss_pos[m0 + k] * uva_row_bytes + col_offset_bytes;
+      const uint32_t bar = smem_u32(wbar + k), dst = smem_u32(wbuf + (size_t)k * row_bytes);
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)row_bytes)
+                   : "memory");
+      asm volatile(
+          "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+          "l"(src), "r"((uint32_t)row_bytes), "r"(bar)
+          : "memory");
+    }
+    unsigned arrived = 0;
+    for (int k = 0; k < cnt; ++k) {
+      if (!mbar_wait_bounded(smem_u32(wbar + k), phase)) continue;
+      arrived |= 1u << k;
+      const int64_t r = ws.miss_rows[m0 + k];
+      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(out + r * row_bytes),
+                   "r"(smem_u32(wbuf + (size_t)k * row_bytes)), "r"((uint32_t)row_bytes)
+                   : "memory");
+    }
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    if (arrived != (1u << cnt) - 1u) {
+      atomicOr(status, APT_FLAG_PEER_TIMEOUT);
+      for (int k = 0; k < cnt; ++k)   // one more bounded wait per copy that may still be in flight, then stop
+        if (!(arrived & (1u << k))) mbar_wait_bounded(smem_u32(wbar + k), phase);
+      return;
     }
     phase ^= 1;
-    __syncwarp();
   }
 }
 
@@ -255,6 +260,7 @@ struct GatherArgs {
   const int64_t* index;
   int64_t num_rows;
   const int64_t* num_rows_dev;
+  const int64_t* first_row_dev;
   const int64_t* feat_pos_map;
   int64_t num_nodes;
   const char* dev_feats;
@@ -265,7 +271,28 @@ struct GatherArgs {
   int32_t* status_word;
 };
 
-// The three launches shared by the workspace-taking and the allocation-free entry points.
+// One resident wave of the hit copy for vector type V and R rows in flight.
+template <typename V, int R>
+static int hit_wave_blocks(int* out) {
+  static int cached[64] = {};
+  int dev = 0;
+  APT_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || cached[dev] == 0) {
+    int per_sm = 0, sms = 0;
+    APT_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_gather_hits<V, R>, kGatherBlock, 0));
+    APT_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int wave = (per_sm > 0 ? per_sm : 1) * (sms > 0 ? sms : kNumSMs);
+    if (dev < 0 || dev >= 64) {
+      *out = wave;
+      return APT_OK;
+    }
+    cached[dev] = wave;
+  }
+  *out = cached[dev];
+  return APT_OK;
+}
+
+// The launches shared by the workspace-taking and the allocation-free entry points.
 static int gather_launch(const GatherArgs& a, GatherWs ws, cudaStream_t s) {
   uint64_t bits = (uint64_t)a.dev_row_bytes | (uintptr_t)a.out;
   if (a.num_dev_rows > 0) bits |= (uintptr_t)a.dev_feats;
@@ -276,19 +303,24 @@ static int gather_launch(const GatherArgs& a, GatherWs ws, cudaStream_t s) {
   // the miss counter is the one word that has to start at zero
   APT_CUDA(cudaMemsetAsync(ws.miss_count, 0, sizeof(int32_t), s));
 
-  {
-    ProfScope prof("gather_classify", s);
-    const int grid = wave_grid(ceil_div(a.num_rows, 256), 8);
-    APT_LAUNCH(k_classify, grid, 256, 0, s, a.index, a.num_rows, a.num_rows_dev, a.feat_pos_map,
-               a.num_nodes, a.num_dev_rows, a.num_uva_rows, ws, a.status_word);
-  }
+#define APT_HITS_R(V, R)                                                                   \
+  do {                                                                                     \
+    int wave = 0;                                                                          \
+    const int rc = hit_wave_blocks<V, R>(&wave);                                           \
+    if (rc != APT_OK) return rc;                                                           \
+    /* at least 2 R rows per warp, at most one resident wave */                            \
+    const int64_t want = ceil_div(a.num_rows, (int64_t)(kGatherBlock / 32) * 2 * R);       \
+    const int grid = (int)(want < wave ? (want < 1 ? 1 : want) : wave);                    \
+    ProfScope prof("gather_hit", s);                                                       \
+    APT_LAUNCH((k_gather_hits<V, R>), grid, kGatherBlock, 0, s, a.index, a.num_rows,       \
+               a.num_rows_dev, a.first_row_dev, a.feat_pos_map, a.num_nodes,               \
+               a.num_dev_rows, a.num_uva_rows, a.dev_feats, a.dev_row_bytes, a.out, ws,    \
+               a.status_word);                                                             \
+  } while (0)
 #define APT_HITS(V)                                                                        \
   do {                                                                                     \
-    ProfScope prof("gather_hit", s);                                                       \
-    const int grid =                                                                       \
-        wave_grid(ceil_div(a.num_rows, (kGatherBlock / 32) * kRowsPerGroup), 8, g_hit_waves); \
-    APT_LAUNCH(k_copy_hits<V>, grid, kGatherBlock, 0, s, a.num_rows, a.num_rows_dev,       \
-               ws.src_pos, a.dev_feats, a.dev_row_bytes, a.out);                           \
+    if (g_hit_rows >= 8 && a.dev_row_bytes <= 1024) APT_HITS_R(V, 8);                      \
+    else APT_HITS_R(V, 4);                                                                 \
   } while (0)
 #define APT_MISS(V)                                                                        \
   do {                                                                                     \
@@ -319,6 +351,7 @@ static int gather_launch(const GatherArgs& a, GatherWs ws, cudaStream_t s) {
     }
   }
 #undef APT_HITS
+#undef APT_HITS_R
 #undef APT_MISS
 #undef APT_BY_WIDTH
   return APT_OK;
@@ -348,8 +381,8 @@ extern "C" int apt_set_tunable(const char* name, int64_t value) {
     g_miss_mode = (int)value;
   } else if (!strcmp(name, "gather_miss_blocks") && value >= 1 && value <= 65535) {
     g_miss_blocks = (int)value;
-  } else if (!strcmp(name, "gather_hit_waves") && value >= 1 && value <= 64) {
-    g_hit_waves = (int)value;
+  } else if (!strcmp(name, "gather_hit_rows") && (value == 4 || value == 8)) {
+    g_hit_rows = (int)value;
   } else if (!strcmp(name, "relabel_small") && value >= 0 && value <= 1) {
     set_relabel_small(value != 0);
   } else {
@@ -371,8 +404,21 @@ extern "C" int apt_gather_rows(const int64_t* index, int64_t num_rows,
                                int64_t num_uva_rows, int64_t uva_row_bytes,
                                int64_t uva_col_offset_bytes, void* out, void* workspace,
                                size_t workspace_bytes, int32_t* status_word, void* stream) {
+  return apt_gather_rows_from(index, num_rows, num_rows_dev, nullptr, feat_pos_map, num_nodes, dev_feats,
+                              num_dev_rows, dev_row_bytes, uva_feats, num_uva_rows, uva_row_bytes,
+                              uva_col_offset_bytes, out, workspace, workspace_bytes, status_word, stream);
+}
+
+extern "C" int apt_gather_rows_from(const int64_t* index, int64_t num_rows,
+                                    const int64_t* num_rows_dev, const int64_t* first_row_dev,
+                                    const int64_t* feat_pos_map,
+                                    int64_t num_nodes, const void* dev_feats, int64_t num_dev_rows,
+                                    int64_t dev_row_bytes, const void* uva_feats,
+                                    int64_t num_uva_rows, int64_t uva_row_bytes,
+                                    int64_t uva_col_offset_bytes, void* out, void* workspace,
+                                    size_t workspace_bytes, int32_t* status_word, void* stream) {
   using namespace apt;
-  const GatherArgs a{index, num_rows, num_rows_dev, feat_pos_map, num_nodes, (const char*)dev_feats,
+  const GatherArgs a{index, num_rows, num_rows_dev, first_row_dev, feat_pos_map, num_nodes, (const char*)dev_feats,
                      num_dev_rows, dev_row_bytes, (const char*)uva_feats, num_uva_rows, uva_row_bytes,
                      uva_col_offset_bytes, (char*)out, status_word};
   const int rc = gather_check("apt_gather_rows", a);
@@ -391,12 +437,11 @@ extern "C" int apt_gather_rows(const int64_t* index, int64_t num_rows,
 // ---------------------------------------------------------------------------
 // Gather without any allocation, for callers that must not allocate.
 //
-// The scratch that apt_gather_rows takes from its caller (decoded positions,
-// miss list and miss counter) lives here in a fixed array inside the library's device image,
+// The scratch that apt_gather_rows takes from its caller (the miss list: host-table
+// row and output row of every miss, and the miss counter) lives here in a fixed array inside the library's device image,
 // sized for kStaticGatherMaxRows rows per call. The name g_gather_scratch is a
 // host-side stand-in in host code, not a device address; the address kernels can
-// use is asked for once per device with cudaGetSymbolAddress while that device
-// is current.
+// use is asked for with cudaGetSymbolAddress while the caller's device is current.
 namespace apt {
 
 constexpr int64_t kStaticGatherMaxRows = 1 << 20;
@@ -405,22 +450,13 @@ constexpr size_t kStaticGatherBytes =
 
 static __device__ __align__(256) unsigned char g_gather_scratch[kStaticGatherBytes];
 
-static void* g_scratch_addr[64];
-static bool g_scratch_ready[64];
-static std::mutex g_scratch_mu;
-
+// Asked for on every call (a host-side lookup, no allocation): an address cached per device
+// ordinal would go stale when that device's context is torn down and created again.
 static int static_scratch(void** out) {
-  int dev = 0;
-  APT_CUDA(cudaGetDevice(&dev));
-  APT_CHECK_ARG(dev >= 0 && dev < 64, "apt_gather_rows_static: device ordinal %d", dev);
-  std::lock_guard<std::mutex> lk(g_scratch_mu);
-  if (!g_scratch_ready[dev]) {
-    void* p = nullptr;
-    APT_CUDA(cudaGetSymbolAddress(&p, g_gather_scratch));
-    g_scratch_addr[dev] = p;
-    g_scratch_ready[dev] = true;
-  }
-  *out = g_scratch_addr[dev];
+  void* p = nullptr;
+  APT_CUDA(cudaGetSymbolAddress(&p, g_gather_scratch));
+  APT_CHECK_ARG(p && ((uintptr_t)p & 255) == 0, "apt_gather_rows_static: scratch address %p", p);
+  *out = p;
   return APT_OK;
 }
 
@@ -443,7 +479,7 @@ extern "C" int apt_gather_rows_static(const int64_t* index, int64_t num_rows,
               (long long)num_rows, (long long)kStaticGatherMaxRows);
     return APT_ERR_CAPACITY;
   }
-  const GatherArgs a{index, num_rows, nullptr, feat_pos_map, num_nodes, (const char*)dev_feats,
+  const GatherArgs a{index, num_rows, nullptr, nullptr, feat_pos_map, num_nodes, (const char*)dev_feats,
                      num_dev_rows, dev_row_bytes, (const char*)uva_feats, num_uva_rows, uva_row_bytes,
                      uva_col_offset_bytes, (char*)out, status_word};
   int rc = gather_check("apt_gather_rows_static", a);
@@ -454,6 +490,6 @@ extern "C" int apt_gather_rows_static(const int64_t* index, int64_t num_rows,
   GatherWs ws;
   gather_layout(kStaticGatherMaxRows, (char*)base, &ws);
   // The array keeps the previous call's contents: gather_launch zeroes the miss
-  // counter; positions and the miss list are rewritten for every row that is read.
+  // counter, and only the list entries below the new count are ever read.
   return gather_launch(a, ws, (cudaStream_t)stream);
 }

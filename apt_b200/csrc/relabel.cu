@@ -4,17 +4,21 @@
 // One open-addressing table (linear probing, load <= 2/3) in the caller's
 // workspace holds, per distinct id, the smallest position at which it occurs.
 // An item is a "first occurrence" iff that minimum equals its own position;
-// an ordered compaction (per-tile counts, then each tile sums the counts of the
-// tiles before it) turns the first-occurrence flags into new ids, which makes
-// the result independent of the table layout and of thread scheduling.
+// an ordered compaction turns the first-occurrence flags into new ids, which
+// makes the result independent of the table layout and of thread scheduling.
+// Three launches:
 //
-//   k_insert   items -> table (CAS on the key, atomicMin on the position),
-//              remembers each item's slot
-//   k_count    per-tile number of first occurrences
-//   k_assign   new id = offset of the tile + rank inside it; writes unique[],
-//              the slot's new id and (last tile) the number of unique ids
-//   k_relabel  neighbours -> new id through the remembered slot; every item
-//              also empties its slot again
+//   k_insert        items -> table (CAS on the key, atomicMin on the position),
+//                   remembers each item's slot. When the layer is sampled by this
+//                   library the sampling kernel does this itself
+//                   (sample_replace_kernel<G, true>, apt_sample_relabel_csc) and the
+//                   neighbour list is never read back.
+//   k_scan_assign   single-pass ordered compaction (tile counts chained by a
+//                   look-back over the tiles before): new id = first occurrences
+//                   before the item; writes unique[], the slot's new id and the
+//                   number of unique ids
+//   k_relabel       neighbours -> new id through the remembered slot; the first
+//                   occurrence of every id also empties its slot again
 //
 // Layers of up to 8192 items run in one block with the table in shared memory
 // (k_relabel_small below).
@@ -22,59 +26,16 @@
 // The table is empty between calls (apt_relabel_workspace_init empties it once,
 // each call empties the slots it used), so a call costs what its own item count
 // costs and no clearing pass is needed.
-#include "common.cuh"
+#include "sample_kernels.cuh"
 
 namespace apt {
 
 constexpr int kRelabelBlock = 1024;
-constexpr unsigned long long kEmptyKey = ~0ull;
-constexpr uint32_t kNoPos = 0xffffffffu;
-
-// key, smallest position and new id of one distinct id: 16 bytes, one sector.
-struct Slot {
-  unsigned long long key;
-  uint32_t min_pos;
-  uint32_t new_id;
-};
-
-struct RelabelWs {
-  Slot* slots;          // [cap_ws] all-0xff between calls
-  int32_t* slot_of;     // [items_ws]
-  int32_t* tile_count;  // [tiles_ws]
-  int64_t items_ws;     // items this workspace was sized for
-  int tiles;            // tiles of the host-side (upper bound) item count of this call
-};
-
-// Problem size as the kernels see it. With device-side counts the number of
-// seeds comes from a device word and every seed brings `per_seed` neighbours;
-// the table then uses the capacity the real item count needs.
-struct RelabelDims {
-  int64_t S, n;
-  uint32_t cap;
-};
-
-__host__ __device__ inline uint32_t relabel_capacity(int64_t n) {
-  return (uint32_t)(n + n / 2 + 64);
-}
-
-__device__ __forceinline__ RelabelDims relabel_dims(int64_t S_host, int64_t M_host,
-                                                    const int64_t* S_dev, int64_t per_seed) {
-  RelabelDims d;
-  if (S_dev) {
-    d.S = effective_n(S_host, S_dev);
-    d.n = d.S + d.S * per_seed;
-  } else {
-    d.S = S_host;
-    d.n = S_host + M_host;
-  }
-  d.cap = relabel_capacity(d.n);
-  return d;
-}
 
 static size_t relabel_bytes_for(int64_t items) {
   const int64_t n = items > 0 ? items : 1;
   return align_up((size_t)relabel_capacity(n) * sizeof(Slot), 256) + align_up((size_t)n * 4, 256) +
-         align_up((size_t)(ceil_div(n, kRelabelBlock) + 1) * 4, 256);
+         align_up(sizeof(ScanCtrl) + (size_t)(ceil_div(n, kScanTile) + 1) * 8, 256);
 }
 
 // The layout depends only on the size of the workspace, not on the call, so
@@ -86,20 +47,12 @@ static bool relabel_layout(char* base, size_t bytes, RelabelWs* ws) {
   ws->items_ws = items;
   if (items <= 0) return false;
   const size_t o_slot_of = align_up((size_t)relabel_capacity(items) * sizeof(Slot), 256);
+  const size_t o_ctrl = o_slot_of + align_up((size_t)items * 4, 256);
   ws->slots = (Slot*)base;
   ws->slot_of = (int32_t*)(base + o_slot_of);
-  ws->tile_count = (int32_t*)(base + o_slot_of + align_up((size_t)items * 4, 256));
+  ws->ctrl = (ScanCtrl*)(base + o_ctrl);
+  ws->tile_state = (uint64_t*)(base + o_ctrl + sizeof(ScanCtrl));
   return true;
-}
-
-__device__ __forceinline__ uint32_t hash_id(int64_t key) {
-  // 64 -> 32 bit finaliser (splitmix64 constants); ids are often dense, so the
-  // low bits alone would cluster under linear probing.
-  uint64_t x = (uint64_t)key;
-  x ^= x >> 30; x *= 0xbf58476d1ce4e5b9ull;
-  x ^= x >> 27; x *= 0x94d049bb133111ebull;
-  x ^= x >> 31;
-  return (uint32_t)x;
 }
 
 __device__ __forceinline__ int64_t item_at(const int64_t* seeds, int64_t S,
@@ -107,93 +60,170 @@ __device__ __forceinline__ int64_t item_at(const int64_t* seeds, int64_t S,
   return i < S ? seeds[i] : nbrs[i - S];
 }
 
-__global__ void __launch_bounds__(kRelabelBlock)
+// Pass 1 when the ids come from memory (apt_relabel_csc).
+__global__ void __launch_bounds__(256)
 k_insert(const int64_t* __restrict__ seeds, int64_t S_host, const int64_t* __restrict__ nbrs,
          int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed, RelabelWs ws,
          int32_t* status) {
   const RelabelDims d = relabel_dims(S_host, M_host, S_dev, per_seed);
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= d.n) return;
-  const unsigned long long key = (unsigned long long)item_at(seeds, d.S, nbrs, i);
-  uint32_t pos = (uint32_t)(((uint64_t)hash_id((int64_t)key) * d.cap) >> 32);
-  for (uint32_t probe = 0; probe < d.cap; ++probe) {
-    Slot* s = ws.slots + pos;
-    unsigned long long prev = *(volatile unsigned long long*)&s->key;
-    if (prev == kEmptyKey) prev = atomicCAS(&s->key, kEmptyKey, key);
-    if (prev == kEmptyKey || prev == key) {
-      atomicMin(&s->min_pos, (uint32_t)i);
-      ws.slot_of[i] = (int32_t)pos;
-      return;
-    }
-    pos = pos + 1 == d.cap ? 0 : pos + 1;
-  }
-  ws.slot_of[i] = -1;
-  atomicOr(status, APT_FLAG_TABLE_FULL);
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int flags = 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < d.n; i += stride)
+    ws.slot_of[i] = table_insert(ws.slots, d.cap, item_at(seeds, d.S, nbrs, i), (uint32_t)i, &flags);
+  if (flags) atomicOr(status, flags);
 }
 
-__device__ __forceinline__ int is_first(const RelabelWs& ws, int64_t i, int64_t n) {
-  if (i >= n) return 0;
-  const int32_t slot = ws.slot_of[i];
-  return slot >= 0 && ws.slots[slot].min_pos == (uint32_t)i;
+// ---- pass 2: ordered compaction in one launch ----------------------------------------
+// An item is a first occurrence iff its slot's smallest position is its own. Tiles of
+// kScanTile consecutive items are handed out in launch order by a ticket, so every tile
+// before a running tile is running or finished. A tile publishes its count as soon as it
+// has it, then looks back over the tiles before it (32 at a time, nearest first) until it
+// meets one that has published its inclusive prefix; its own inclusive prefix follows.
+// State words carry the epoch of the call, so nothing has to be cleared between calls.
+constexpr uint32_t kTileAggregate = 1u, kTileInclusive = 2u;
+constexpr int kLookbackSpinLimit = 1 << 22;   // about a second of polling; never reached unless a block died
+
+__device__ __forceinline__ uint64_t ld_state(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_state(uint64_t* p, uint64_t v) {
+  asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
-__global__ void __launch_bounds__(kRelabelBlock)
-k_count(int64_t S_host, int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed,
-        RelabelWs ws) {
-  const RelabelDims d = relabel_dims(S_host, M_host, S_dev, per_seed);
-  // tiles past the real item count (the grid covers the upper bound) have nothing to count,
-  // and no tile before them ever reads their count
-  if ((int64_t)blockIdx.x * blockDim.x >= d.n) return;
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int f = is_first(ws, i, d.n);
-  const int c = __syncthreads_count(f);
-  if (threadIdx.x == 0) ws.tile_count[blockIdx.x] = c;
-}
-
-__global__ void __launch_bounds__(kRelabelBlock)
-k_assign(const int64_t* __restrict__ seeds, int64_t S_host, const int64_t* __restrict__ nbrs,
-         int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed, RelabelWs ws,
-         int64_t* __restrict__ out_unique, int64_t* __restrict__ out_num_unique) {
+__global__ void __launch_bounds__(kScanThreads)
+k_scan_assign(int64_t S_host, int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed,
+              RelabelWs ws, int64_t* __restrict__ out_unique, int64_t* __restrict__ out_num_unique,
+              int32_t* status) {
   __shared__ int scratch[33];
+  __shared__ uint32_t s_tile, s_epoch, s_before;
   const RelabelDims d = relabel_dims(S_host, M_host, S_dev, per_seed);
-  const int64_t tile_first = (int64_t)blockIdx.x * blockDim.x;
-  if (tile_first >= d.n) {
-    // past the real item count; with no item at all the first tile reports zero unique ids
-    if (d.n == 0 && blockIdx.x == 0 && threadIdx.x == 0) *out_num_unique = 0;
-    return;
+  if (threadIdx.x == 0) {
+    s_epoch = *(volatile uint32_t*)&ws.ctrl->epoch + 1u;   // moves only after the last block is done
+    s_tile = atomicAdd(&ws.ctrl->ticket, 1u);
   }
-  const int before = block_sum_of(ws.tile_count, blockIdx.x, scratch);
-  const int64_t i = tile_first + threadIdx.x;
-  const int f = is_first(ws, i, d.n);
-  int total;
-  const int ex = block_exclusive_scan(f, scratch, &total);
-  if (f) {
-    const int32_t id = before + ex;
-    out_unique[id] = item_at(seeds, d.S, nbrs, i);
-    ws.slots[ws.slot_of[i]].new_id = (uint32_t)id;
+  __syncthreads();
+  const uint32_t tile = s_tile, epoch = s_epoch & 0x3fffffffu;
+  const int64_t first = (int64_t)tile * kScanTile;
+  if (first < d.n || tile == 0) {
+    // consecutive items of one thread: the block scan over thread sums keeps item order
+    const int64_t i0 = first + (int64_t)threadIdx.x * kScanItems;
+    int32_t slot[kScanItems];
+    uint4 sv[kScanItems];
+    int f[kScanItems];
+    int mine = 0;
+#pragma unroll
+    for (int k = 0; k < kScanItems; ++k) slot[k] = i0 + k < d.n ? ws.slot_of[i0 + k] : -1;
+#pragma unroll
+    for (int k = 0; k < kScanItems; ++k)
+      if (slot[k] >= 0) sv[k] = ld_plain_16((const uint4*)(ws.slots + slot[k]));
+#pragma unroll
+    for (int k = 0; k < kScanItems; ++k) {
+      f[k] = slot[k] >= 0 && sv[k].z == (uint32_t)(i0 + k);
+      mine += f[k];
+    }
+    int total;
+    const int ex = block_exclusive_scan(mine, scratch, &total);
+    if (threadIdx.x < 32) {
+      const int lane = threadIdx.x;
+      uint32_t before = 0;
+      if (lane == 0)
+        st_state(ws.tile_state + tile,
+                 ((uint64_t)epoch << 34) | ((uint64_t)(tile == 0 ? kTileInclusive : kTileAggregate) << 32) |
+                     (uint32_t)total);
+      if (tile > 0) {
+        int64_t look = (int64_t)tile - 1;
+        int spins = 0;
+        for (;;) {
+          const int64_t idx = look - lane;
+          uint64_t w = idx >= 0 ? ld_state(ws.tile_state + idx) : 0ull;
+          const bool ready = idx < 0 || (uint32_t)(w >> 34) == epoch;
+          const bool incl = idx < 0 || (ready && ((uint32_t)(w >> 32) & 3u) == kTileInclusive);
+          const unsigned ready_mask = __ballot_sync(0xffffffffu, ready);
+          const unsigned incl_mask = __ballot_sync(0xffffffffu, incl);
+          const int stop = incl_mask ? __ffs(incl_mask) - 1 : 31;          // nearest tile with a full prefix
+          const unsigned need = stop == 31 ? 0xffffffffu : ((2u << stop) - 1u);
+          if ((ready_mask & need) == need) {
+            uint32_t v = (lane <= stop && idx >= 0) ? (uint32_t)w : 0u;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            before += v;
+            if (incl_mask) break;
+            look -= 32;
+            spins = 0;
+          } else if (++spins > kLookbackSpinLimit) {
+            if (lane == 0) atomicOr(status, APT_FLAG_TABLE_FULL);   // gave up: ids of this tile are wrong
+            break;
+          } else {
+            __nanosleep(40);
+          }
+        }
+        if (lane == 0)
+          st_state(ws.tile_state + tile,
+                   ((uint64_t)epoch << 34) | ((uint64_t)kTileInclusive << 32) | (uint32_t)(before + total));
+      }
+      if (lane == 0) s_before = before;
+    }
+    __syncthreads();
+    uint32_t id = s_before + (uint32_t)ex;
+#pragma unroll
+    for (int k = 0; k < kScanItems; ++k) {
+      if (f[k]) {
+        out_unique[id] = (int64_t)(((uint64_t)sv[k].y << 32) | sv[k].x);   // the slot's key is the id
+        ws.slots[slot[k]].new_id = id;
+        ++id;
+      }
+    }
+    // the tile that holds the last item (or the only, empty tile) knows the number of unique ids
+    if (threadIdx.x == 0 && first + kScanTile >= d.n) *out_num_unique = (int64_t)s_before + total;
   }
-  // the tile that holds the last real item knows the number of unique ids
-  if (tile_first + blockDim.x >= d.n && threadIdx.x == 0) *out_num_unique = before + total;
+  // the last block to finish puts the ticket back and advances the epoch
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(&ws.ctrl->done, 1u) == gridDim.x - 1) {
+      ws.ctrl->done = 0;
+      ws.ctrl->ticket = 0;
+      __threadfence();
+      *(volatile uint32_t*)&ws.ctrl->epoch = s_epoch;
+    }
+  }
 }
 
+// ---- pass 3: neighbours -> new id through the remembered slot; the first occurrence
+// of every id also empties its slot again with one 16-byte store.
 __global__ void __launch_bounds__(256)
 k_relabel(int64_t S_host, int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed,
           RelabelWs ws, int64_t* __restrict__ out) {
   const RelabelDims d = relabel_dims(S_host, M_host, S_dev, per_seed);
-  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (; i < d.n; i += stride) {
-    const int32_t slot = ws.slot_of[i];
-    if (slot < 0) {
-      if (i >= d.S) out[i - d.S] = -1;
-      continue;
+  constexpr int K = 4;
+  for (int64_t base = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; base < d.n; base += stride * K) {
+    int32_t slot[K];
+    uint4 v[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int64_t i = base + k * stride;
+      slot[k] = i < d.n ? ws.slot_of[i] : -2;
     }
-    // one 16-byte load brings the new id and the position of the id's first occurrence
-    const uint4 v = ld_plain_16((const uint4*)(ws.slots + slot));
-    if (i >= d.S) out[i - d.S] = (int64_t)v.w;
-    // Nothing reads keys any more and only the first occurrence itself compares positions:
-    // that item empties the slot with one 16-byte store (the new id stays for the others).
-    if (v.z == (uint32_t)i) st_plain_16((uint4*)(ws.slots + slot), make_uint4(0xffffffffu, 0xffffffffu, kNoPos, v.w));
+#pragma unroll
+    for (int k = 0; k < K; ++k)
+      if (slot[k] >= 0) v[k] = ld_plain_16((const uint4*)(ws.slots + slot[k]));
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int64_t i = base + k * stride;
+      if (slot[k] == -2) continue;
+      if (slot[k] < 0) {
+        if (i >= d.S) out[i - d.S] = -1;
+        continue;
+      }
+      if (i >= d.S) out[i - d.S] = (int64_t)v[k].w;
+      // Nothing reads keys any more and only the first occurrence itself compares positions:
+      // that item empties the slot (the new id stays for the items that have not read it yet).
+      if (v[k].z == (uint32_t)i)
+        st_plain_16((uint4*)(ws.slots + slot[k]), make_uint4(0xffffffffu, 0xffffffffu, kNoPos, v[k].w));
+    }
   }
 }
 
@@ -202,21 +232,33 @@ k_relabel(int64_t S_host, int64_t M_host, const int64_t* __restrict__ S_dev, int
 // table of kSmallCap 16-byte slots in the 227 KB of shared memory of one SM together with
 // each item's slot number. One block of 1024 threads then runs the three phases (insert,
 // ordered compaction, relabel) with block barriers between them: no global table traffic,
-// no clearing, one launch instead of four. The order of first occurrence is decided by
-// the minimum position per id exactly as in the multi-block path, so both give the same
-// arrays.
+// no clearing, one launch. With SAMPLE the block also draws the neighbours itself (the same
+// draws as sample_replace_kernel: they depend on the seed slot and the draw slot only), so
+// that a whole innermost hop, sampling and relabelling, is one launch. The order of first
+// occurrence is decided by the minimum position per id exactly as in the multi-block path,
+// so both give the same arrays.
 static bool g_relabel_small = true;   // apt_set_tunable("relabel_small", 0) forces the multi-block path
 void set_relabel_small(bool on) { g_relabel_small = on; }
 
 constexpr int kSmallItems = 8192;
 constexpr uint32_t kSmallCap = 12288;
+constexpr uint16_t kSmallNoSlot = 0xffffu;
 constexpr size_t kSmallSmem = (size_t)kSmallCap * sizeof(Slot) + (size_t)kSmallItems * sizeof(uint16_t);
 
+struct SmallSample {     // SAMPLE only
+  CscView g;
+  int fanout;
+  uint32_t k0, k1, call_id;
+  const int64_t* call_base_dev;
+  int64_t* out_neighbors;   // may be NULL
+};
+
+template <bool SAMPLE>
 __global__ void __launch_bounds__(kRelabelBlock)
 k_relabel_small(const int64_t* __restrict__ seeds, int64_t S_host, const int64_t* __restrict__ nbrs,
                 int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed,
                 int64_t* __restrict__ out_unique, int64_t* __restrict__ out_relabeled,
-                int64_t* __restrict__ out_num_unique) {
+                int64_t* __restrict__ out_num_unique, int32_t* status, SmallSample sp) {
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ int scratch[33];
   Slot* slots = (Slot*)smem;
@@ -228,10 +270,30 @@ k_relabel_small(const int64_t* __restrict__ seeds, int64_t S_host, const int64_t
     slots[t].min_pos = kNoPos;
     slots[t].new_id = 0;
   }
+  uint32_t call_id = 0;
+  if (SAMPLE) call_id = sp.call_id + (sp.call_base_dev ? (uint32_t)*sp.call_base_dev : 0u);
   __syncthreads();
+  int flags = 0;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const unsigned long long key = (unsigned long long)item_at(seeds, d.S, nbrs, i);
-    uint32_t pos = (uint32_t)(((uint64_t)hash_id((int64_t)key) * kSmallCap) >> 32);
+    int64_t id;
+    if (!SAMPLE || i < d.S) {
+      id = item_at(seeds, d.S, nbrs, i);
+    } else {
+      const int64_t j = (i - d.S) / sp.fanout;
+      const int slot_i = (int)((i - d.S) % sp.fanout);
+      const int64_t v = seeds[j];
+      const int64_t* row = nullptr;
+      const int64_t deg = csc_row(sp.g, v, &row, &flags);
+      id = deg > 0 ? row[mod_deg(draw_word((uint64_t)j, (uint32_t)slot_i, call_id, sp.k0, sp.k1), deg)] : v;
+      if (sp.out_neighbors) sp.out_neighbors[i - d.S] = id;
+    }
+    if (id < 0) {   // not an id (see table_insert): no slot, relabelled to -1
+      flags |= APT_FLAG_ID_OUT_OF_RANGE;
+      slot_of[i] = kSmallNoSlot;
+      continue;
+    }
+    const unsigned long long key = (unsigned long long)id;
+    uint32_t pos = (uint32_t)(((uint64_t)hash_id(id) * kSmallCap) >> 32);
     for (;;) {   // at most kSmallItems of the kSmallCap slots are ever taken: an empty one is found
       Slot* s = slots + pos;
       unsigned long long prev = *(volatile unsigned long long*)&s->key;
@@ -244,16 +306,17 @@ k_relabel_small(const int64_t* __restrict__ seeds, int64_t S_host, const int64_t
       pos = pos + 1 == kSmallCap ? 0 : pos + 1;
     }
   }
+  if (flags) atomicOr(status, flags);
   __syncthreads();
   int running = 0;
   for (int base = 0; base < n; base += blockDim.x) {
     const int i = base + threadIdx.x;
-    const int f = i < n && slots[slot_of[i]].min_pos == (uint32_t)i;
+    const int f = i < n && slot_of[i] != kSmallNoSlot && slots[slot_of[i]].min_pos == (uint32_t)i;
     int total;
     const int ex = block_exclusive_scan(f, scratch, &total);
     if (f) {
       const int id = running + ex;
-      out_unique[id] = item_at(seeds, d.S, nbrs, i);
+      out_unique[id] = (int64_t)slots[slot_of[i]].key;
       slots[slot_of[i]].new_id = (uint32_t)id;
     }
     running += total;
@@ -261,7 +324,32 @@ k_relabel_small(const int64_t* __restrict__ seeds, int64_t S_host, const int64_t
   if (threadIdx.x == 0) *out_num_unique = running;
   __syncthreads();
   for (int i = (int)d.S + threadIdx.x; i < n; i += blockDim.x)
-    out_relabeled[i - d.S] = (int64_t)slots[slot_of[i]].new_id;
+    out_relabeled[i - d.S] = slot_of[i] == kSmallNoSlot ? (int64_t)-1 : (int64_t)slots[slot_of[i]].new_id;
+}
+
+template <bool SAMPLE>
+static int set_small_smem() {
+  static bool attr_set[64] = {};
+  int dev = 0;
+  APT_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    APT_CUDA(cudaFuncSetAttribute(k_relabel_small<SAMPLE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)kSmallSmem));
+    attr_set[dev] = true;
+  }
+  return APT_OK;
+}
+
+// Passes 2 and 3 of the multi-block path (the table already holds every item).
+static int scan_and_relabel(int64_t num_seeds, int64_t num_neighbors, const int64_t* num_seeds_dev,
+                            int64_t per_seed, const RelabelWs& ws, int64_t* out_unique, int64_t* out_relabeled,
+                            int64_t* out_num_unique, int32_t* status_word, cudaStream_t s) {
+  const int64_t n = num_seeds + num_neighbors;
+  APT_LAUNCH(k_scan_assign, (int)ceil_div(n, kScanTile), kScanThreads, 0, s, num_seeds, num_neighbors,
+             num_seeds_dev, per_seed, ws, out_unique, out_num_unique, status_word);
+  const int grid = wave_grid(ceil_div(n, 256 * 4), 8, 1);
+  APT_LAUNCH(k_relabel, grid, 256, 0, s, num_seeds, num_neighbors, num_seeds_dev, per_seed, ws, out_relabeled);
+  return APT_OK;
 }
 
 }  // namespace apt
@@ -276,6 +364,12 @@ extern "C" int apt_relabel_workspace_init(void* workspace, size_t workspace_byte
   using namespace apt;
   APT_CHECK_ARG(workspace && workspace_bytes > 0, "apt_relabel_workspace_init: null workspace");
   APT_CUDA(cudaMemsetAsync(workspace, 0xff, workspace_bytes, (cudaStream_t)stream));
+  // the control words and tile states of the ordered compaction start at zero
+  RelabelWs ws;
+  if (relabel_layout((char*)workspace, workspace_bytes, &ws)) {
+    const size_t off = (size_t)((char*)ws.ctrl - (char*)workspace);
+    APT_CUDA(cudaMemsetAsync(ws.ctrl, 0, workspace_bytes - off, (cudaStream_t)stream));
+  }
   return APT_OK;
 }
 
@@ -306,16 +400,11 @@ extern "C" int apt_relabel_csc(const int64_t* seeds, int64_t num_seeds,
                 "apt_relabel_csc: null pointer");
   APT_CHECK_ARG(((uintptr_t)workspace & 255) == 0, "apt_relabel_csc: workspace must be 256-byte aligned");
   if (n <= kSmallItems && g_relabel_small) {
-    static bool attr_set[64] = {};
-    int dev = 0;
-    APT_CUDA(cudaGetDevice(&dev));
-    if (dev < 64 && !attr_set[dev]) {
-      APT_CUDA(cudaFuncSetAttribute(k_relabel_small, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmallSmem));
-      attr_set[dev] = true;
-    }
+    const int rc = set_small_smem<false>();
+    if (rc != APT_OK) return rc;
     ProfScope prof("relabel", s);
-    APT_LAUNCH(k_relabel_small, 1, kRelabelBlock, kSmallSmem, s, seeds, num_seeds, neighbors, num_neighbors,
-               num_seeds_dev, per_seed, out_unique, out_relabeled, out_num_unique);
+    APT_LAUNCH(k_relabel_small<false>, 1, kRelabelBlock, kSmallSmem, s, seeds, num_seeds, neighbors, num_neighbors,
+               num_seeds_dev, per_seed, out_unique, out_relabeled, out_num_unique, status_word, SmallSample{});
     return APT_OK;
   }
   RelabelWs ws;
@@ -324,15 +413,72 @@ extern "C" int apt_relabel_csc(const int64_t* seeds, int64_t num_seeds,
               workspace_bytes, (long long)ws.items_ws, (long long)n);
     return APT_ERR_CAPACITY;
   }
-  ws.tiles = (int)ceil_div(n, kRelabelBlock);
   ProfScope prof("relabel", s);
-  APT_LAUNCH(k_insert, ws.tiles, kRelabelBlock, 0, s, seeds, num_seeds, neighbors, num_neighbors,
+  APT_LAUNCH(k_insert, wave_grid(ceil_div(n, 256 * 2), 8, 2), 256, 0, s, seeds, num_seeds, neighbors, num_neighbors,
              num_seeds_dev, per_seed, ws, status_word);
-  APT_LAUNCH(k_count, ws.tiles, kRelabelBlock, 0, s, num_seeds, num_neighbors, num_seeds_dev, per_seed, ws);
-  APT_LAUNCH(k_assign, ws.tiles, kRelabelBlock, 0, s, seeds, num_seeds, neighbors, num_neighbors,
-             num_seeds_dev, per_seed, ws, out_unique, out_num_unique);
-  const int grid = wave_grid(ceil_div(n, 256), 8);
-  APT_LAUNCH(k_relabel, grid, 256, 0, s, num_seeds, num_neighbors, num_seeds_dev, per_seed, ws,
-             out_relabeled);
-  return APT_OK;
+  return scan_and_relabel(num_seeds, num_neighbors, num_seeds_dev, per_seed, ws, out_unique, out_relabeled,
+                          out_num_unique, status_word, s);
+}
+
+extern "C" int apt_sample_relabel_csc(const int64_t* seeds, int64_t num_seeds, const int64_t* num_seeds_dev,
+                                      int fanout, const int64_t* adj_pos_map, int64_t num_nodes,
+                                      const int64_t* dev_indptr, const int64_t* dev_indices,
+                                      const int64_t* uva_indptr, const int64_t* uva_indices, uint64_t key,
+                                      uint32_t call_id, const int64_t* call_id_base_dev, void* workspace,
+                                      size_t workspace_bytes, int64_t* out_neighbors, int64_t* out_unique,
+                                      int64_t* out_relabeled, int64_t* out_num_unique, int32_t* status_word,
+                                      void* stream) {
+  using namespace apt;
+  APT_CHECK_ARG(num_seeds >= 0 && fanout > 0 && num_nodes >= 0,
+                "apt_sample_relabel_csc: bad sizes (seeds %lld fanout %d)", (long long)num_seeds, fanout);
+  const int64_t num_neighbors = num_seeds * fanout, n = num_seeds + num_neighbors;
+  APT_CHECK_ARG(n < (int64_t)0x7f000000, "apt_sample_relabel_csc: %lld items exceed the 31-bit position range",
+                (long long)n);
+  APT_CHECK_ARG(out_num_unique && status_word, "apt_sample_relabel_csc: null output word");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (n == 0) {
+    APT_CUDA(cudaMemsetAsync(out_num_unique, 0, sizeof(int64_t), s));
+    return APT_OK;
+  }
+  APT_CHECK_ARG(seeds && out_unique && out_relabeled && workspace && uva_indptr && uva_indices,
+                "apt_sample_relabel_csc: null pointer");
+  APT_CHECK_ARG(((uintptr_t)workspace & 255) == 0, "apt_sample_relabel_csc: workspace must be 256-byte aligned");
+  const uint32_t k0 = (uint32_t)key, k1 = (uint32_t)(key >> 32);
+  const CscView g{adj_pos_map, num_nodes, dev_indptr, dev_indices, uva_indptr, uva_indices};
+  if (n <= kSmallItems && g_relabel_small) {
+    const int rc = set_small_smem<true>();
+    if (rc != APT_OK) return rc;
+    ProfScope prof("sample_relabel", s);
+    APT_LAUNCH(k_relabel_small<true>, 1, kRelabelBlock, kSmallSmem, s, seeds, num_seeds, (const int64_t*)nullptr,
+               num_neighbors, num_seeds_dev, (int64_t)fanout, out_unique, out_relabeled, out_num_unique, status_word,
+               SmallSample{g, fanout, k0, k1, call_id, call_id_base_dev, out_neighbors});
+    return APT_OK;
+  }
+  RelabelWs ws;
+  if (!relabel_layout((char*)workspace, workspace_bytes, &ws) || ws.items_ws < n) {
+    set_error("apt_sample_relabel_csc: workspace of %zu bytes holds %lld items, %lld needed "
+              "(apt_relabel_workspace_bytes)", workspace_bytes, (long long)ws.items_ws, (long long)n);
+    return APT_ERR_CAPACITY;
+  }
+  const SampleInsert ins{ws.slots, ws.slot_of};
+  {
+    ProfScope prof("sample", s);
+#define APT_SAMPLE_INSERT(G)                                                                         \
+  do {                                                                                               \
+    const int grid = wave_grid(ceil_div(num_seeds, 256 / G), 8);                                     \
+    APT_LAUNCH((sample_replace_kernel<G, true>), grid, 256, 0, s, seeds, num_seeds, num_seeds_dev,   \
+               fanout, g, k0, k1, call_id, call_id_base_dev, out_neighbors, status_word, ins);       \
+  } while (0)
+    if (fanout <= 8) {
+      APT_SAMPLE_INSERT(8);
+    } else if (fanout <= 16) {
+      APT_SAMPLE_INSERT(16);
+    } else {
+      APT_SAMPLE_INSERT(32);
+    }
+#undef APT_SAMPLE_INSERT
+  }
+  ProfScope prof("relabel", s);
+  return scan_and_relabel(num_seeds, num_neighbors, num_seeds_dev, (int64_t)fanout, ws, out_unique, out_relabeled,
+                          out_num_unique, status_word, s);
 }

@@ -27,6 +27,45 @@ __device__ __forceinline__ int64_t mod_deg(uint32_t word, int64_t deg) {
   return deg <= 0xffffffffll ? (int64_t)(word % (uint32_t)deg) : (int64_t)word;
 }
 
+// The CSC as the sampler sees it: rows of the cached part (dev_*) or of the global graph (uva_*),
+// chosen per node by adj_pos_map (NULL: every node reads the global graph).
+struct CscView {
+  const int64_t* adj_pos_map;
+  int64_t num_nodes;
+  const int64_t* dev_indptr;
+  const int64_t* dev_indices;
+  const int64_t* uva_indptr;
+  const int64_t* uva_indices;
+};
+
+// In-neighbour list of node v: returns its length (0 with a flag for a seed that is no node or
+// has no in-neighbour) and points *nbr at it.
+__device__ __forceinline__ int64_t csc_row(const CscView& g, int64_t v, const int64_t** nbr, int* flags) {
+  if (v < 0 || v >= g.num_nodes) {
+    *flags |= APT_FLAG_ID_OUT_OF_RANGE;
+    return 0;
+  }
+  int64_t pos = g.adj_pos_map ? g.adj_pos_map[v] : (int64_t)(-v - 2);
+  const int64_t* indptr;
+  const int64_t* indices;
+  if (pos >= 0) {
+    indptr = g.dev_indptr;
+    indices = g.dev_indices;
+  } else {
+    pos = -pos - 2;
+    indptr = g.uva_indptr;
+    indices = g.uva_indices;
+  }
+  const int64_t start = indptr[pos];
+  const int64_t deg = indptr[pos + 1] - start;
+  if (deg <= 0) {
+    *flags |= APT_FLAG_ZERO_DEGREE;
+    return 0;
+  }
+  *nbr = indices + start;
+  return deg;
+}
+
 struct SampleInsert {
   Slot* slots;        // relabel table (INSERT only)
   int32_t* slot_of;   // [S + S * fanout] slot of every item
@@ -35,11 +74,7 @@ struct SampleInsert {
 template <int G, bool INSERT>
 __global__ void __launch_bounds__(256)
 sample_replace_kernel(const int64_t* __restrict__ seeds, int64_t num_seeds,
-                      const int64_t* __restrict__ num_seeds_dev, int fanout, const int64_t* __restrict__ adj_pos_map,
-                      int64_t num_nodes, const int64_t* __restrict__ dev_indptr,
-                      const int64_t* __restrict__ dev_indices,
-                      const int64_t* __restrict__ uva_indptr,
-                      const int64_t* __restrict__ uva_indices, uint32_t k0,
+                      const int64_t* __restrict__ num_seeds_dev, int fanout, CscView g, uint32_t k0,
                       uint32_t k1, uint32_t call_id, const int64_t* __restrict__ call_base_dev,
                       int64_t* __restrict__ out, int32_t* status, SampleInsert ins) {
   num_seeds = effective_n(num_seeds, num_seeds_dev);
@@ -54,26 +89,7 @@ sample_replace_kernel(const int64_t* __restrict__ seeds, int64_t num_seeds,
     const int64_t v = seeds[j];
     int64_t* orow = out ? out + j * fanout : nullptr;
     const int64_t* nbr = nullptr;
-    int64_t deg = 0;
-    if (v < 0 || v >= num_nodes) {
-      flags |= APT_FLAG_ID_OUT_OF_RANGE;
-    } else {
-      int64_t pos = adj_pos_map ? adj_pos_map[v] : (int64_t)(-v - 2);
-      const int64_t* indptr;
-      const int64_t* indices;
-      if (pos >= 0) {
-        indptr = dev_indptr;
-        indices = dev_indices;
-      } else {
-        pos = -pos - 2;
-        indptr = uva_indptr;
-        indices = uva_indices;
-      }
-      const int64_t start = indptr[pos];
-      deg = indptr[pos + 1] - start;
-      if (deg <= 0) flags |= APT_FLAG_ZERO_DEGREE;
-      nbr = indices + start;
-    }
+    const int64_t deg = csc_row(g, v, &nbr, &flags);
     if (INSERT && sub == 0) ins.slot_of[j] = table_insert(ins.slots, cap, v, (uint32_t)j, &flags);
     for (int i = sub; i < fanout; i += G) {
       int64_t u = v;   // a seed that is no node, or has no in-neighbour, fills its row with itself
@@ -84,75 +100,6 @@ sample_replace_kernel(const int64_t* __restrict__ seeds, int64_t num_seeds,
         ins.slot_of[item] = table_insert(ins.slots, cap, u, (uint32_t)item, &flags);
       }
     }
-  }
-  if (flags) atomicOr(status, flags);
-}
-
-// Without replacement (fanout <= 32): one warp per seed. Lane i ends up holding
-// the edge slot of output i. Floyd's selection: for step i, t = deg-fanout+i,
-// r = draw(j,i) % (t+1); take r unless an earlier step already took it, then
-// take t. Every lane evaluates the same r, the lanes that own earlier picks
-// vote on the collision.
-__global__ void __launch_bounds__(256)
-sample_floyd_kernel(const int64_t* __restrict__ seeds, int64_t num_seeds,
-                    const int64_t* __restrict__ num_seeds_dev, int fanout, const int64_t* __restrict__ adj_pos_map,
-                    int64_t num_nodes, const int64_t* __restrict__ dev_indptr,
-                    const int64_t* __restrict__ dev_indices,
-                    const int64_t* __restrict__ uva_indptr,
-                    const int64_t* __restrict__ uva_indices, uint32_t k0,
-                    uint32_t k1, uint32_t call_id, const int64_t* __restrict__ call_base_dev,
-                    int64_t* __restrict__ out, int32_t* status) {
-  num_seeds = effective_n(num_seeds, num_seeds_dev);
-  if (call_base_dev) call_id += (uint32_t)*call_base_dev;
-  const int lane = threadIdx.x & 31;
-  const int64_t warps_per_block = blockDim.x >> 5;
-  int64_t j = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
-  const int64_t stride = (int64_t)gridDim.x * warps_per_block;
-  int flags = 0;
-  for (; j < num_seeds; j += stride) {
-    const int64_t v = seeds[j];
-    int64_t* orow = out + j * fanout;
-    if (v < 0 || v >= num_nodes) {
-      flags |= APT_FLAG_ID_OUT_OF_RANGE;
-      if (lane < fanout) orow[lane] = v;
-      continue;
-    }
-    int64_t pos = adj_pos_map ? adj_pos_map[v] : (int64_t)(-v - 2);
-    const int64_t* indptr;
-    const int64_t* indices;
-    if (pos >= 0) {
-      indptr = dev_indptr;
-      indices = dev_indices;
-    } else {
-      pos = -pos - 2;
-      indptr = uva_indptr;
-      indices = uva_indices;
-    }
-    const int64_t start = indptr[pos];
-    const int64_t deg = indptr[pos + 1] - start;
-    if (deg <= 0) {
-      flags |= APT_FLAG_ZERO_DEGREE;
-      if (lane < fanout) orow[lane] = v;
-      continue;
-    }
-    const int64_t* nbr = indices + start;
-    int64_t pick = -1;
-    if (deg <= fanout) {
-      if (lane < deg) {
-        pick = lane;
-      } else if (lane < fanout) {
-        pick = mod_deg(draw_word((uint64_t)j, (uint32_t)lane, call_id, k0, k1), deg);
-      }
-    } else {
-      for (int i = 0; i < fanout; ++i) {
-        const int64_t t = deg - fanout + i;
-        const int64_t r =
-            mod_deg(draw_word((uint64_t)j, (uint32_t)i, call_id, k0, k1), t + 1);
-        const unsigned taken = __ballot_sync(0xffffffffu, lane < i && pick == r);
-        if (lane == i) pick = taken ? t : r;
-      }
-    }
-    if (lane < fanout) orow[lane] = nbr[pick];
   }
   if (flags) atomicOr(status, flags);
 }

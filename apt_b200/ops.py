@@ -116,6 +116,7 @@ class NPCState:
         self.generation = 0     # bumped whenever installed state changes; captured graphs check it
         self.profiling = False
         self.exchange = None  # set by apt_b200.exchange.make_exchange at init
+        self._side_stream = None
         self.shuffle_backend = os.environ.get("APT_SHUFFLE_BACKEND", "p2p")
         self.p2p_region_bytes = int(os.environ.get("APT_P2P_REGION_MB", "256")) << 20
 
@@ -131,6 +132,12 @@ class NPCState:
             buf = torch.empty(max(int(nbytes * 1.25), 1 << 16), dtype=torch.uint8, device=self.device())
             self._ws[key] = buf
         return buf
+
+    def side_stream(self) -> torch.cuda.Stream:
+        """A second stream of this device for work that runs beside the main chain of a mini-batch."""
+        if self._side_stream is None or self._side_stream.device != self.device():
+            self._side_stream = torch.cuda.Stream(device=self.device())
+        return self._side_stream
 
     NUM_WORDS = 256
 
@@ -326,16 +333,48 @@ def _relabel_enqueue(seeds, neighbors, n_dev, count_out):
     n = seeds.numel() + neighbors.numel()
     uniq = torch.empty(n, dtype=torch.int64, device=seeds.device)
     rel = torch.empty(neighbors.numel(), dtype=torch.int64, device=seeds.device)
-    nbytes = lib.apt_relabel_workspace_bytes(n)
-    ws = STATE.workspace("relabel", nbytes)
-    if getattr(ws, "_apt_clean", False) is not True:
-        # the table has to be empty once; every call then releases the slots it used
-        check(lib.apt_relabel_workspace_init(_ptr(ws), ws.numel(), _stream()))
-        ws._apt_clean = True
+    ws = _relabel_workspace(n)
     check(lib.apt_relabel_csc(_ptr(seeds), seeds.numel(), _ptr(n_dev), _ptr(neighbors), neighbors.numel(),
                               _ptr(ws), ws.numel(), _ptr(uniq), _ptr(rel),
                               _ptr(count_out), STATE.status_ptr(), _stream()))
     return uniq, rel
+
+
+def _relabel_workspace(n):
+    ws = STATE.workspace("relabel", lib.apt_relabel_workspace_bytes(n))
+    if getattr(ws, "_apt_clean", False) is not True:
+        # the table has to be empty once; every call then releases the slots it used
+        check(lib.apt_relabel_workspace_init(_ptr(ws), ws.numel(), _stream()))
+        ws._apt_clean = True
+    return ws
+
+
+def _sample_relabel_enqueue(seeds, fanout, n_dev, count_out, call_id=None, call_base_dev=None, want_neighbors=False):
+    """One sampled layer, sampling and relabelling together (apt_sample_relabel_csc): returns the
+    upper-bound buffers (unique ids, relabelled neighbours, neighbours or None); the number of
+    unique ids lands in the device word `count_out`."""
+    g = STATE.graph
+    if g.uva_indptr is None:
+        raise RuntimeError("mix_cache_graphs has not been called")
+    if not STATE.sample_replace:
+        nbr = _sample(seeds, fanout, n_dev, call_id, call_base_dev)
+        uniq, rel = _relabel_enqueue(seeds, nbr, n_dev, count_out)
+        return uniq, rel, nbr
+    seeds = _need_cuda(seeds, "seeds")
+    S, f = seeds.numel(), int(fanout)
+    uniq = torch.empty(S * (1 + f), dtype=torch.int64, device=seeds.device)
+    rel = torch.empty(S * f, dtype=torch.int64, device=seeds.device)
+    nbr = torch.empty(S * f, dtype=torch.int64, device=seeds.device) if want_neighbors else None
+    ws = _relabel_workspace(S * (1 + f))
+    if call_id is None:
+        call_id = STATE.sample_calls
+        STATE.sample_calls += 1
+    check(lib.apt_sample_relabel_csc(
+        _ptr(seeds), S, _ptr(n_dev), f, _ptr(g.adj_pos_map), g.num_total_nodes, _ptr(g.dev_indptr),
+        _ptr(g.dev_indices), _ptr(g.uva_indptr), _ptr(g.uva_indices), STATE.sample_key, call_id & 0xFFFFFFFF,
+        _ptr(call_base_dev), _ptr(ws), ws.numel(), _ptr(nbr), _ptr(uniq), _ptr(rel), _ptr(count_out),
+        STATE.status_ptr(), _stream()))
+    return uniq, rel, nbr
 
 
 def relabel_csc(seeds: torch.Tensor, neighbors: torch.Tensor) -> List[torch.Tensor]:
@@ -646,15 +685,20 @@ def load_subtensor(node_id: torch.Tensor) -> torch.Tensor:
     return _gather_enqueue(node_id, None)
 
 
-def _gather_enqueue(node_id: torch.Tensor, n_dev: Optional[torch.Tensor]) -> torch.Tensor:
+def _gather_enqueue(node_id: torch.Tensor, n_dev: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
+                    first_dev: Optional[torch.Tensor] = None, ws_name: str = "gather") -> torch.Tensor:
+    """Enqueues the gather of rows [first_dev, n_dev) of node_id (device words; None: 0 and
+    node_id.numel()) into `out` (allocated here when None). Calls that may overlap on the GPU
+    need workspaces of their own (`ws_name`)."""
     f = STATE.feat
     n = node_id.numel()
     esz = f.dev_feats.element_size()
-    out = torch.empty((n, f.rank_feat_dim), dtype=f.dev_feats.dtype, device=node_id.device)
+    if out is None:
+        out = torch.empty((n, f.rank_feat_dim), dtype=f.dev_feats.dtype, device=node_id.device)
     nbytes = lib.apt_gather_workspace_bytes(n)
-    ws = STATE.workspace("gather", nbytes)
-    check(lib.apt_gather_rows(
-        _ptr(node_id), n, _ptr(n_dev), _ptr(f.feat_pos_map), f.num_total_nodes,
+    ws = STATE.workspace(ws_name, nbytes)
+    check(lib.apt_gather_rows_from(
+        _ptr(node_id), n, _ptr(n_dev), _ptr(first_dev), _ptr(f.feat_pos_map), f.num_total_nodes,
         _ptr(f.dev_feats), f.dev_feats.shape[0], f.rank_feat_dim * esz,
         _ptr(f.uva_feats), f.uva_feats.shape[0], f.feat_dim * esz, f.feat_dim_offset * esz,
         _ptr(out), _ptr(ws), ws.numel(), STATE.status_ptr(), _stream()))

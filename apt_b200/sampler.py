@@ -105,6 +105,9 @@ class MixedNeighborSampler:
         self.prefetch_features = prefetch_features
         self.use_graph = use_graph and chained
         self.graph_buffers = max(1, int(graph_buffers))
+        # 0: one gather after the outermost hop; 1: the frontier's rows are gathered beside the
+        # outermost hop and the two meet before the remaining rows are gathered; 2: they meet at the end
+        self.gather_split = int(os.environ.get("APT_GATHER_SPLIT", "1"))
         self._plans = {}
         self._turn = 0
         self._host_base = None
@@ -138,10 +141,10 @@ class MixedNeighborSampler:
         cur, cur_n = seeds, None
         layers = []                      # (dst buffer, rel, uniq, uniq count slot, fanout)
         for fanout in reversed(self.fir_fanouts):
-            nbr = ops._sample(cur, fanout, cur_n, call if explicit else None, call_base_dev)
-            call += 1
             cnt = st.word(slot)
-            uniq, rel = ops._relabel_enqueue(cur, nbr, cur_n, cnt)
+            uniq, rel, _ = ops._sample_relabel_enqueue(cur, fanout, cur_n, cnt, call if explicit else None,
+                                                       call_base_dev)
+            call += 1
             layers.append((cur, rel, uniq, slot, fanout))
             cur, cur_n = uniq, cnt
             slot += 1
@@ -158,13 +161,33 @@ class MixedNeighborSampler:
         lo, hi = ops._owned_range()
         u_slot, in_slot = slot, slot + 1
         uniq2, inv = ops._unique_enqueue(recv, total, lo, hi, st.word(u_slot), "unique_np")
-        nbr = ops._sample(uniq2, self.las_fanouts, st.word(u_slot), call if explicit else None, call_base_dev)
-        uniq3, rel3 = ops._relabel_enqueue(uniq2, nbr, st.word(u_slot), st.word(in_slot))
-        rows = None
+        # The block of the outermost hop lists its destination nodes (the frontier uniq2, sorted and
+        # distinct) first, so input row j is the row of uniq2[j] for j below the frontier's size: those
+        # rows are fetched on a second stream while the hop is still being sampled and relabelled,
+        # and only the rows of the newly met nodes wait for the relabelling.
         f = st.feat
-        if self.prefetch_features and f.feat_pos_map is not None and \
-                uniq3.numel() * f.rank_feat_dim * f.dev_feats.element_size() <= _PREFETCH_LIMIT_BYTES:
-            rows = ops._gather_enqueue(uniq3, st.word(in_slot))
+        prefetch = self.prefetch_features and f.feat_pos_map is not None and \
+            uniq2.numel() * (1 + self.las_fanouts) * f.rank_feat_dim * f.dev_feats.element_size() <= _PREFETCH_LIMIT_BYTES
+        split = self.gather_split if prefetch and not st.profiling else 0
+        rows = None
+        side = None
+        if prefetch:
+            rows = torch.empty((uniq2.numel() * (1 + self.las_fanouts), f.rank_feat_dim), dtype=f.dev_feats.dtype,
+                               device=uniq2.device)
+        if split:
+            main = torch.cuda.current_stream()
+            side = st.side_stream()
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                ops._gather_enqueue(uniq2, st.word(u_slot), out=rows, ws_name="gather_frontier")
+        uniq3, rel3, _ = ops._sample_relabel_enqueue(uniq2, self.las_fanouts, st.word(u_slot), st.word(in_slot),
+                                                     call if explicit else None, call_base_dev)
+        if split == 1:
+            main.wait_stream(side)
+        if prefetch:
+            ops._gather_enqueue(uniq3, st.word(in_slot), out=rows, first_dev=st.word(u_slot) if split else None)
+        if split == 2:
+            main.wait_stream(side)
         return dict(layers=layers, perm=perm, inv=inv, uniq2=uniq2, uniq3=uniq3, rel3=rel3, rows=rows,
                     u_slot=u_slot, in_slot=in_slot)
 
@@ -340,10 +363,10 @@ class SPVirtualSampler:
         cur, cur_n = seeds, None
         layers = []
         for fanout in list(reversed(self.fanouts))[:-1]:
-            nbr = ops._sample(cur, fanout, cur_n, call if explicit else None, call_base_dev)
-            call += 1
             cnt = st.word(slot)
-            uniq, rel = ops._relabel_enqueue(cur, nbr, cur_n, cnt)
+            uniq, rel, _ = ops._sample_relabel_enqueue(cur, fanout, cur_n, cnt, call if explicit else None,
+                                                       call_base_dev)
+            call += 1
             layers.append((cur, rel, uniq, slot, fanout))
             cur, cur_n = uniq, cnt
             slot += 1
@@ -575,16 +598,14 @@ class MPSampler:
         cur, cur_n = seeds, None
         layers = []
         for fanout in list(reversed(self.fanouts))[:-1]:
-            nbr = ops._sample(cur, fanout, cur_n)
             cnt = st.word(slot)
-            uniq, rel = ops._relabel_enqueue(cur, nbr, cur_n, cnt)
+            uniq, rel, _ = ops._sample_relabel_enqueue(cur, fanout, cur_n, cnt)
             layers.append((cur, rel, uniq, slot, fanout))
             cur, cur_n = uniq, cnt
             slot += 1
         f = self.fanouts[0]
-        nbr = ops._sample(cur, f, cur_n)
         uf_word = st.word(slot)
-        unique_frontier, coo_row = ops._relabel_enqueue(cur, nbr, cur_n, uf_word)
+        unique_frontier, coo_row, _ = ops._sample_relabel_enqueue(cur, f, cur_n, uf_word)
         mine = words[self._MINE:self._MINE + 3]
         if cur_n is None:
             mine[0:1].fill_(cur.numel())

@@ -32,6 +32,13 @@ import torch.distributed as dist
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+STAGE_TAGS = ("sample_relabel", "sample", "relabel", "bucket", "unique_sorted", "gather_hit", "gather_miss",
+              "p2p_push", "p2p_wait", "p2p_pull")
+# DRAM bytes (read + written) per algorithmic byte of the hit kernel, from an ncu capture of that kernel
+# alone at the mini-batch's size (143 000 rows of 512 bytes out of a 27.8 M-row cache table); None until
+# such a capture exists for the current kernel.
+HIT_DRAM_BYTES_PER_ALGORITHMIC_BYTE = None
+HIT_TRAFFIC_SOURCE = "not captured for this kernel yet"
 METRIC = "sampled+gathered mini-batches/sec (whole box)"
 UNIT = "mini-batches/s"
 
@@ -244,7 +251,7 @@ def stage_gather(args):
                          torch.randint(n_dev, n, (n_miss,), generator=g, device="cuda")])
         ids = ids[torch.randperm(args.rows, generator=g, device="cuda")].contiguous()
         if it == args.warmup:
-            for tag in (b"gather_hit", b"gather_miss", b"gather_classify"):
+            for tag in (b"gather_hit", b"gather_miss"):
                 t, k = ctypes.c_double(), ctypes.c_int64()
                 lib.apt_profile_read(tag, ctypes.byref(t), ctypes.byref(k))
         torch.cuda.nvtx.range_push("apt_timed")
@@ -257,12 +264,14 @@ def stage_gather(args):
             total_ms += ev0.elapsed_time(ev1)
     ops.check_status()
     res = {}
-    for tag in ("gather_hit", "gather_miss", "gather_classify"):
+    for tag in ("gather_hit", "gather_miss"):
         t, k = ctypes.c_double(), ctypes.c_int64()
         lib.apt_profile_read(tag.encode(), ctypes.byref(t), ctypes.byref(k))
         res[tag] = (t.value, k.value)
     hit_ms, hit_n = res["gather_hit"]
-    hit_bytes = (args.rows - n_miss) * 2 * row_bytes + args.rows * 8
+    # the hit kernel reads an id and a position-map entry for every requested row (16 bytes) and moves
+    # every cached row once in and once out
+    hit_bytes = (args.rows - n_miss) * 2 * row_bytes + args.rows * 16
     gbs = hit_bytes / (hit_ms / hit_n * 1e-3) / 1e9
     call_gbs = args.rows * (2 * row_bytes + 16) / (total_ms / args.steps * 1e-3) / 1e9
     print(json.dumps({
@@ -273,7 +282,7 @@ def stage_gather(args):
                    "miss_frac": args.miss_frac, "l2": "cache table larger than the 126 MB L2, new random ids every call"},
         "whole_call_gbs": call_gbs,
         "stage_us": {k: 1000.0 * v[0] / max(v[1], 1) for k, v in res.items()},
-        "roofline": {"kernel": "k_copy_hits", "bound": "hbm", "achieved": round(gbs, 1), "peak": peak,
+        "roofline": {"kernel": "k_gather_hits", "bound": "hbm", "achieved": round(gbs, 1), "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": round(gbs / peak, 4), "traffic": None}}))
 
 
@@ -758,8 +767,7 @@ def run():
     barrier()
     for b in dev_batches[:args.warmup]:
         step(b)
-    for tag in ("sample", "relabel", "bucket", "unique_sorted", "gather_classify", "gather_hit", "gather_miss",
-                "p2p_push", "p2p_wait", "p2p_pull"):
+    for tag in STAGE_TAGS:
         t_, n_ = ctypes.c_double(), ctypes.c_int64()
         lib.apt_profile_read(tag.encode(), ctypes.byref(t_), ctypes.byref(n_))
     lib.apt_launch_count_reset()
@@ -784,8 +792,7 @@ def run():
         lib.apt_profile_read(tag.encode(), ctypes.byref(t), ctypes.byref(n))
         return t.value, n.value
 
-    stage_ms = {tag: prof(tag) for tag in ("sample", "relabel", "bucket", "unique_sorted", "gather_classify",
-                                           "gather_hit", "gather_miss", "p2p_push", "p2p_wait", "p2p_pull")}
+    stage_ms = {tag: prof(tag) for tag in STAGE_TAGS}
     pos_map = ops.STATE.feat.feat_pos_map
     rows_total = sum(int(k.numel()) for k in kept)
     hits_total = sum(int((pos_map[k] >= 0).sum().item()) for k in kept)
@@ -793,16 +800,19 @@ def run():
     peak, peak_kind = peaks()
     hit_ms, hit_n = stage_ms["gather_hit"]
     miss_ms, miss_n = stage_ms["gather_miss"]
-    # algorithmic bytes of one hit-copy launch: each hit row read and written once, plus the 8-byte
-    # position of every requested row
-    hit_bytes = (hits_total * 2 * row_bytes + rows_total * 8) / max(hit_n, 1)
+    # algorithmic bytes of one launch of the hit kernel: an id and a position-map entry per requested row
+    # (16 bytes), and every cached row once in and once out
+    hit_bytes = (hits_total * 2 * row_bytes + rows_total * 16) / max(hit_n, 1)
     hit_gbs = hit_bytes / (hit_ms / max(hit_n, 1) * 1e-3) / 1e9 if hit_ms > 0 else 0.0
-    roofline = {"kernel": "k_copy_hits (gather, cache hits)", "bound": "hbm", "achieved": round(hit_gbs, 1),
-                "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(hit_gbs / peak, 4),
-                # DRAM bytes of this launch, scaled from the ncu capture of the same kernel on 1 081 344 rows
-                # (1054.7 MB of traffic for 1115.9 MB algorithmic, profiles/gather_hit_copy_1M_rows_512B.md):
-                # a streaming copy's traffic grows with the rows it moves
-                "traffic": round(hit_bytes * 1054.7 / 1115.9), "traffic_source": "ncu on 1 081 344 rows, scaled by rows",
+    roofline = {"kernel": "k_gather_hits (gather: decode + copy of the cache hits)", "bound": "hbm",
+                "achieved": round(hit_gbs, 1), "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                "frac": round(hit_gbs / peak, 4),
+                "traffic": round(hit_bytes * HIT_DRAM_BYTES_PER_ALGORITHMIC_BYTE)
+                if HIT_DRAM_BYTES_PER_ALGORITHMIC_BYTE else None,
+                "traffic_source": HIT_TRAFFIC_SOURCE,
+                "measured_in": "the pass that enqueues the kernels one by one with an event pair around each "
+                               "(one launch over all input rows of the mini-batch; the graph replay of the headline "
+                               "splits the same rows into two launches of this kernel)",
                 "rows_per_launch": rows_total / max(hit_n, 1),
                 "hit_rows_per_launch": hits_total / max(hit_n, 1), "us_per_launch": 1000.0 * hit_ms / max(hit_n, 1)}
     miss_bytes = miss_total * row_bytes / max(miss_n, 1)

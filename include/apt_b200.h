@@ -75,7 +75,7 @@ int apt_profile_read(const char* tag, double* total_ms, int64_t* launches);
  *   gather_miss_mode   0 16-byte ld.global.nc loads (default),
  *                      1 bulk copies (cp.async.bulk) staged through shared memory
  *   gather_miss_blocks blocks of the miss-copy kernel (default 148)
- *   gather_hit_waves   cap on the hit-copy grid, in waves of 148 x 8 blocks (default 4)
+ *   gather_hit_rows    rows in flight per warp of the hit copy, 8 (default, rows of up to 1 KiB) or 4
  *   relabel_small      1 (default): layers of up to 8192 items are relabelled by one block with
  *                      the hash table in shared memory; 0: always the multi-block path */
 int apt_set_tunable(const char* name, int64_t value);
@@ -127,6 +127,10 @@ int apt_sample_csc_fanout(const int64_t* seeds, int64_t num_seeds,
  * same workspace: the layout is derived from it.
  * With num_seeds_dev the real seed count S comes from the device and the
  * neighbours are taken to be S * (num_neighbors / num_seeds) (a fixed fanout).
+ * A negative id is not an id (-1 is what an operator upstream leaves for an id it
+ * could not resolve): it is left out of out_unique, relabelled to -1, and
+ * APT_FLAG_ID_OUT_OF_RANGE is set. (The reference would take -1 for its
+ * empty-slot mark, src/cuda/relabel.cu:70.)
  */
 size_t apt_relabel_workspace_bytes(int64_t num_items);
 int apt_relabel_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
@@ -137,6 +141,27 @@ int apt_relabel_csc(const int64_t* seeds, int64_t num_seeds,
                     int64_t* out_unique, int64_t* out_relabeled,
                     int64_t* out_num_unique, int32_t* status_word,
                     void* stream);
+
+/* Sampling and relabelling of one layer in one call: what
+ * LocalSamplingNeibhorsOneLayer followed by RelabelCSC compute (src/sampling.cc:13-17,
+ * src/relabel.cc:9-15; python/npc/sampler.py:117-121 calls them back to back),
+ * with the draws of apt_sample_csc_fanout (replace != 0) and the outputs of
+ * apt_relabel_csc on those neighbours. The sampling kernel enters every id into
+ * the relabel table while it holds it, so the neighbour list is not read back;
+ * out_neighbors (int64[num_seeds * fanout]) may be NULL when the caller only needs
+ * the block. Layers of up to 8192 items are one launch. Workspace as for
+ * apt_relabel_csc with num_seeds * (1 + fanout) items. */
+int apt_sample_relabel_csc(const int64_t* seeds, int64_t num_seeds,
+                           const int64_t* num_seeds_dev, int fanout,
+                           const int64_t* adj_pos_map, int64_t num_nodes,
+                           const int64_t* dev_indptr, const int64_t* dev_indices,
+                           const int64_t* uva_indptr, const int64_t* uva_indices,
+                           uint64_t key, uint32_t call_id,
+                           const int64_t* call_id_base_dev,
+                           void* workspace, size_t workspace_bytes,
+                           int64_t* out_neighbors, int64_t* out_unique,
+                           int64_t* out_relabeled, int64_t* out_num_unique,
+                           int32_t* status_word, void* stream);
 
 /* ----------------------------------------------------------- owner bucketing
  * Stable partition of ids by owning rank. Takes the role of ClusterAndPermute
@@ -194,11 +219,23 @@ int apt_unique_sorted(const int64_t* ids, int64_t num_ids,
  *   p == -1: out[r] = 0 and APT_FLAG_FEAT_NOT_EXIST (the reference reads out
  *            of bounds here)
  * Rows are opaque bytes, so fp32/bf16/fp16 tables share the code.
- * Three kernels on `stream`: classify (decode p, compact the miss list), the
- * hit copy out of the HBM cache and the miss copy over the host link.
+ * Two kernels on `stream`: one that decodes p, queues the misses and copies the
+ * hits out of the HBM cache, and the miss copy over the host link.
  * workspace: apt_gather_workspace_bytes(num_rows) bytes; needs no initialisation.
+ * apt_gather_rows_from only produces output rows [*first_row_dev, num_rows) (a
+ * device word; NULL: 0): a caller that already holds the leading rows, e.g. the
+ * destination nodes of a block whose rows it fetched while the block was still
+ * being built, gathers the rest with the same index and output arrays.
  */
 size_t apt_gather_workspace_bytes(int64_t num_rows);
+int apt_gather_rows_from(const int64_t* index, int64_t num_rows,
+                         const int64_t* num_rows_dev, const int64_t* first_row_dev,
+                         const int64_t* feat_pos_map, int64_t num_nodes,
+                         const void* dev_feats, int64_t num_dev_rows,
+                         int64_t dev_row_bytes, const void* uva_feats,
+                         int64_t num_uva_rows, int64_t uva_row_bytes,
+                         int64_t uva_col_offset_bytes, void* out, void* workspace,
+                         size_t workspace_bytes, int32_t* status_word, void* stream);
 int apt_gather_rows(const int64_t* index, int64_t num_rows,
                     const int64_t* num_rows_dev,
                     const int64_t* feat_pos_map, int64_t num_nodes,
@@ -224,10 +261,13 @@ int apt_gather_rows(const int64_t* index, int64_t num_rows,
  * Same arguments (minus the workspace) and result as apt_gather_rows, with these differences:
  *  - at most apt_gather_static_max_rows() (1 048 576) rows per call; more
  *    returns APT_ERR_CAPACITY with a message and launches nothing;
- *  - it calls no cudaMalloc, cudaFree or other allocating routine. The first
- *    call on each device looks up the array's device address
- *    (cudaGetSymbolAddress) with that device current; make that first call
- *    before any stream capture begins;
+ *  - it calls no cudaMalloc, cudaFree or other allocating routine. Every call
+ *    looks up the array's device address (cudaGetSymbolAddress) with the
+ *    calling thread's device current, so the address is never stale, not even
+ *    after the device's context has been torn down and made anew. The first
+ *    call on each device makes the CUDA runtime load the library's device
+ *    image if it has not yet: make that first call before any stream capture
+ *    begins;
  *  - every call on a device uses the same array, which still holds the
  *    previous call's contents (the call clears what has to start at zero).
  *    Two calls that overlap on the GPU — different streams, or different host

@@ -103,6 +103,57 @@ def test_graph_replay_equals_eager_over_several_batches():
     ops.check_status()
 
 
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_frontier_rows_gathered_beside_the_outermost_hop(use_graph):
+    """The rows of the frontier (the destination nodes of the outermost block) are fetched on a
+    second stream while that hop is sampled and relabelled, the other rows afterwards: every way of
+    joining the two streams gives the rows of one plain gather."""
+    n, indptr, indices = small_graph(scale=12, edge_factor=8)
+    install_graph(indptr, indices)
+    reset_world(1, 0)
+    ops.register_min_vids(torch.tensor([0, n]))
+    rng = np.random.default_rng(21)
+    feats, uva, devf, cached_idx, local_idx, pos_map, cpu_map = feature_setup(n, 48, 0.4, rng)
+    ops.cache_feats_shared(n, torch.from_numpy(uva).pin_memory(), dev(devf), torch.from_numpy(cached_idx),
+                           torch.from_numpy(local_idx), 0)
+    batches = [dev(rng.permutation(n)[:300].astype(I64)) for _ in range(3)]
+    got = {}
+    for split in (0, 1, 2):
+        ops.set_sampling(key=77, call_id=0)
+        smp = apt_b200.MixedNeighborSampler(0, [8, 4], chained=True, use_graph=use_graph)
+        smp.gather_split = split
+        outs = []
+        for b in batches:
+            res = smp.sample(None, b)
+            x = ops.load_subtensor(res[0])
+            outs.append((host(res[0]), host(x)))
+        got[split] = outs
+    for split in (1, 2):
+        for (ids_a, x_a), (ids_b, x_b) in zip(got[split], got[0]):
+            assert np.array_equal(ids_a, ids_b) and np.array_equal(x_a, x_b), split
+    for ids_a, x_a in got[1]:
+        assert np.array_equal(x_a, orc.load_subtensor(ids_a, pos_map, devf, uva))
+    ops.check_status()
+
+
+def test_gather_rows_from_a_device_side_first_row():
+    rng = np.random.default_rng(4)
+    n = 3000
+    feats, uva, devf, cached_idx, local_idx, pos_map, cpu_map = feature_setup(n, 32, 0.5, rng)
+    ops.cache_feats_shared(n, torch.from_numpy(uva).pin_memory(), dev(devf), torch.from_numpy(cached_idx),
+                           torch.from_numpy(local_idx), 0)
+    ids = rng.integers(0, n, 5000).astype(I64)
+    want = orc.load_subtensor(ids, pos_map, devf, uva)
+    for first, count in ((0, 5000), (1234, 5000), (4999, 5000), (5000, 5000), (100, 3100), (7000, 5000)):
+        out = torch.full((5000, 32), -7.0, device="cuda")
+        ops._gather_enqueue(dev(ids), torch.tensor([count], device="cuda"), out=out,
+                            first_dev=torch.tensor([first], device="cuda"))
+        ops.check_status()
+        lo = min(first, count)
+        assert np.array_equal(host(out)[lo:count], want[lo:count])
+        assert (host(out)[:lo] == -7.0).all() and (host(out)[count:] == -7.0).all()   # rows outside stay untouched
+
+
 @pytest.mark.parametrize("row_elems,dtype", [(256, torch.float32), (1024, torch.float16), (3, torch.float32), (1, torch.bfloat16)])
 def test_row_movers(row_elems, dtype):
     g = torch.Generator(device="cuda").manual_seed(row_elems)

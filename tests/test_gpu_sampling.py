@@ -166,6 +166,75 @@ def test_relabel_full_size_properties():
     assert np.all(np.diff(fp) > 0)
 
 
+@pytest.mark.parametrize("n_items", [2048, 2049, 10_000, 300_000])
+def test_relabel_many_tiles_repeated_calls(n_items):
+    # the ordered compaction hands tiles of 2048 items out by ticket and chains their counts;
+    # repeated calls on one workspace reuse the tile states (tagged by call) without clearing
+    rng = np.random.default_rng(n_items)
+    lib.apt_set_tunable(b"relabel_small", 0)
+    try:
+        for rep in range(4):
+            S = max(1, n_items // 11)
+            seeds = rng.choice(10 * n_items, S, replace=False).astype(I64)
+            nbrs = rng.integers(0, 3 * n_items, n_items - S).astype(I64)
+            uniq, rel = ops.relabel_csc(dev(seeds), dev(nbrs))
+            wu, wr = orc.relabel_csc(seeds, nbrs)
+            assert np.array_equal(host(uniq), wu) and np.array_equal(host(rel), wr)
+    finally:
+        lib.apt_set_tunable(b"relabel_small", 1)
+
+
+@pytest.mark.parametrize("small", [1, 0])
+def test_relabel_negative_id_is_not_an_id(small):
+    # -1 is what an operator upstream leaves for an id it could not resolve (and the bit pattern of an
+    # empty table slot): it gets no new id, is relabelled to -1 and raises the out-of-range flag
+    seeds = np.array([7, 3, 9], dtype=I64)
+    nbrs = np.array([3, -1, 11, 7, -5, 11, -1, 2], dtype=I64)
+    lib.apt_set_tunable(b"relabel_small", small)
+    try:
+        uniq, rel = ops._relabel_enqueue(dev(seeds), dev(nbrs), None, ops.STATE.word(0))
+        with pytest.raises(RuntimeError, match="id outside"):
+            ops.check_status()
+        n = int(ops.STATE.words()[0].item())
+    finally:
+        lib.apt_set_tunable(b"relabel_small", 1)
+    assert host(uniq)[:n].tolist() == [7, 3, 9, 11, 2]
+    assert host(rel).tolist() == [1, -1, 3, 0, -1, 3, -1, 4]
+    # the table is empty again: the next call is not disturbed
+    u2, r2 = ops.relabel_csc(dev(seeds), dev(np.array([9, 2, 2], dtype=I64)))
+    assert host(u2).tolist() == [7, 3, 9, 2] and host(r2).tolist() == [2, 3, 3]
+
+
+@pytest.mark.parametrize("S,fanout", [(64, 5), (1024, 5), (1200, 10), (6000, 10), (40000, 15)])
+@pytest.mark.parametrize("dev_count", [False, True])
+def test_sample_and_relabel_in_one_call_equals_the_two_calls(graph, S, fanout, dev_count):
+    # apt_sample_relabel_csc (the sampling kernel enters its ids into the relabel table itself; layers of
+    # up to 8192 items are one launch) against sampling, then relabelling, then the oracle
+    n, indptr, indices = graph
+    install_graph(indptr, indices)
+    rng = np.random.default_rng(S + fanout)
+    seeds = rng.choice(n, min(S, n), replace=False).astype(I64)
+    S = len(seeds)
+    buf = np.concatenate([seeds, rng.integers(0, n, 50).astype(I64)])    # the buffer is an upper bound
+    n_dev = torch.tensor([S], dtype=torch.int64, device="cuda") if dev_count else None
+    src = dev(buf) if dev_count else dev(seeds)
+    ops.set_sampling(key=31337, call_id=5)
+    uniq, rel, nbr = ops._sample_relabel_enqueue(src, fanout, n_dev, ops.STATE.word(3), want_neighbors=True)
+    ops.check_status()
+    nu = int(ops.STATE.words()[3].item())
+    want_nbr = orc.sample_csc_fanout(seeds, fanout, None, None, None, indptr, indices, key=31337, call_id=5)
+    wu, wr = orc.relabel_csc(seeds, want_nbr)
+    assert np.array_equal(host(nbr)[:S * fanout], want_nbr)
+    assert nu == len(wu) and np.array_equal(host(uniq)[:nu], wu)
+    assert np.array_equal(host(rel)[:S * fanout], wr)
+    # without the neighbour list (what the chained samplers ask for)
+    ops.set_sampling(key=31337, call_id=5)
+    uniq2, rel2, none = ops._sample_relabel_enqueue(src, fanout, n_dev, ops.STATE.word(4))
+    ops.check_status()
+    assert none is None and int(ops.STATE.words()[4].item()) == nu
+    assert torch.equal(uniq2[:nu], uniq[:nu]) and torch.equal(rel2[:S * fanout], rel[:S * fanout])
+
+
 @pytest.mark.parametrize("ws", [1, 2, 8, 32])
 @pytest.mark.parametrize("n_ids", [0, 1, 1000, 70000])
 def test_bucket_matches_oracle(ws, n_ids):

@@ -65,6 +65,33 @@ def test_static_gather_matches_workspace_gather_twice():
     assert int(status.item()) == 0
 
 
+def test_static_gather_allocates_nothing():
+    # the point of the entry point: once the library's device image is loaded (first call), a call
+    # changes neither the free device memory nor what PyTorch's allocator holds
+    rng = np.random.default_rng(5)
+    n, dim, rows = 5000, 64, 30000
+    uva_t, dev_t, pos = _tables(n, dim, rng)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ids = torch.from_numpy(rng.integers(0, n, rows).astype(np.int64)).cuda()
+    out = torch.empty((rows, dim), device="cuda")
+    rb = dim * 4
+
+    def call():
+        check(lib.apt_gather_rows_static(ids.data_ptr(), rows, pos.data_ptr(), pos.numel(), dev_t.data_ptr(),
+                                         dev_t.shape[0], rb, uva_t.data_ptr(), uva_t.shape[0], rb, 0, out.data_ptr(),
+                                         status.data_ptr(), None))
+        torch.cuda.synchronize()
+
+    call()                                   # loads the device image if this process has not yet
+    free_before, _ = torch.cuda.mem_get_info()
+    reserved_before = torch.cuda.memory_reserved()
+    for _ in range(3):
+        call()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before and torch.cuda.memory_reserved() == reserved_before
+    assert torch.equal(out.cpu(), uva_t[ids.cpu()]) and int(status.item()) == 0
+
+
 def test_static_gather_refuses_more_rows_than_its_scratch_holds():
     limit = lib.apt_gather_static_max_rows()
     assert limit == 1 << 20
