@@ -78,6 +78,7 @@ PROTOTYPES = {
     "apt_p2p_push": (c_int, [P, P, P, c_int, P, c_int64, c_int64, P, P]),
     "apt_p2p_wait": (c_int, [P, P, P, c_int64, P]),
     "apt_p2p_default_timeout_ns": (c_int64, []),
+    "apt_p2p_probe_copy": (c_int, [P, c_int, c_size_t, P]),
     "apt_p2p_poisoned": (c_int, [P, ctypes.POINTER(c_int)]),
     "apt_p2p_pull": (c_int, [P, P, P, c_int, c_int64, c_int64, c_int64, P, P]),
     "apt_p2p_pull_sum": (c_int, [P, P, c_int, c_int64, c_int64, P, P, P]),
@@ -87,6 +88,7 @@ PROTOTYPES = {
     "apt_p2p_push_direct": (c_int, [P, P, P, c_int, P, c_int64, c_int64, c_int, P, P]),
     "apt_p2p_alltoall_fused": (c_int, [P, P, P, c_int, P, P, P, c_int64, c_int64, c_int, P, P, c_int64, P]),
     "apt_rmat_edges": (c_int, [c_uint64, c_int64, c_int64, c_int, c_int64, c_float, c_float, c_float, P, P, P]),
+    "apt_zipf_ranks": (c_int, [c_uint64, c_int64, c_int64, c_int64, c_double, P, P]),
     "apt_sort_u64_temp_bytes": (c_size_t, [c_int64]),
     "apt_sort_u64": (c_int, [P, P, c_int64, P, c_size_t, c_int, P]),
     "apt_normal_rows": (c_int, [c_uint64, c_int64, P, c_int64, c_int64, c_int, P, P]),

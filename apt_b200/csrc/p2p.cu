@@ -48,6 +48,20 @@ __device__ __forceinline__ void mv_store(V* p, V v) { *p = v; }
 template <>
 __device__ __forceinline__ void mv_store<uint4>(uint4* p, uint4 v) { st_plain_16(p, v); }
 
+// Rows narrower than a warp of vectors are moved by a group of G lanes (the power of two covering
+// the row's vectors), so that a warp moves 32 / G x kMoveRows rows at a time: an 8-byte id takes one
+// lane, not a warp.
+__device__ __forceinline__ int lane_group(int chunks) {
+  int g = 1;
+  while (g < chunks && g < 32) g <<= 1;
+  return g;
+}
+static int lane_group_host(int64_t chunks) {
+  int g = 1;
+  while (g < chunks && g < 32) g <<= 1;
+  return g;
+}
+
 // mode 0: out[i] = in[index[i]]   (i < n rows of out)
 // mode 1: out[index[i]] = in[i]   (i < n rows of in)
 template <typename V, int MODE>
@@ -58,20 +72,22 @@ k_rows_move(const char* __restrict__ in, const int64_t* __restrict__ index, int6
   const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
   const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int chunks = (int)(row_bytes / (int64_t)sizeof(V));
-  for (int64_t r0 = warp * kMoveRows; r0 < n; r0 += warps * kMoveRows) {
+  const int G = lane_group(chunks), sub = lane % G, per = 32 / G;      // `per` rows side by side in a warp
+  const int64_t step = (int64_t)per * kMoveRows;
+  for (int64_t r0 = warp * step + lane / G; r0 < n; r0 += warps * step) {
     int64_t ix[kMoveRows];
 #pragma unroll
-    for (int k = 0; k < kMoveRows; ++k) ix[k] = r0 + k < n ? index[r0 + k] : (int64_t)-1;
-    for (int c = lane; c < chunks; c += 32) {
+    for (int k = 0; k < kMoveRows; ++k) ix[k] = r0 + (int64_t)k * per < n ? index[r0 + (int64_t)k * per] : (int64_t)-1;
+    for (int c = sub; c < chunks; c += G) {
       V v[kMoveRows];
 #pragma unroll
       for (int k = 0; k < kMoveRows; ++k) {
-        const int64_t src = MODE == 0 ? ix[k] : r0 + k;
+        const int64_t src = MODE == 0 ? ix[k] : r0 + (int64_t)k * per;
         if (ix[k] >= 0) v[k] = mv_load<V>((const V*)(in + src * row_bytes) + c);
       }
 #pragma unroll
       for (int k = 0; k < kMoveRows; ++k) {
-        const int64_t dst = MODE == 0 ? r0 + k : ix[k];
+        const int64_t dst = MODE == 0 ? r0 + (int64_t)k * per : ix[k];
         if (ix[k] >= 0) mv_store<V>((V*)(out + dst * row_bytes) + c, v[k]);
       }
     }
@@ -90,7 +106,8 @@ static int rows_move(const void* in, const int64_t* index, int64_t n, int64_t ro
   if (n == 0) return APT_OK;
   APT_CHECK_ARG(in && index && out && row_bytes > 0 && n > 0, "%s: bad argument", tag);
   const int w = vec_width_of((uint64_t)row_bytes | (uintptr_t)in | (uintptr_t)out);
-  const int grid = wave_grid(ceil_div(n, (kMoveBlock / 32) * kMoveRows), 8, 4);
+  const int64_t rows_per_warp = (int64_t)(32 / lane_group_host(row_bytes / w)) * kMoveRows;
+  const int grid = wave_grid(ceil_div(n, (kMoveBlock / 32) * rows_per_warp), 8, 4);
   ProfScope prof(tag, s);
   const char* ip = (const char*)in;
   char* op = (char*)out;
@@ -168,14 +185,16 @@ k_p2p_push(const char* __restrict__ src, const int64_t* __restrict__ src_index,
     for (int r = 0; r < world_size; ++r) longest = max(longest, soff[r + 1] - soff[r]);
     work = longest * world_size;
   }
-  for (int64_t j0 = warp * kMoveRows; j0 < work; j0 += warps * kMoveRows) {
+  const int G = lane_group(chunks), sub = lane % G, per = 32 / G;      // `per` rows side by side in a warp
+  const int64_t step = (int64_t)per * kMoveRows;
+  for (int64_t j0 = warp * step + lane / G; j0 < work; j0 += warps * step) {
     const char* sp[kMoveRows];
     char* dp[kMoveRows];
 #pragma unroll
     for (int k = 0; k < kMoveRows; ++k) {
       // t walks the source rows when the index names destinations
       // (stream position j = index[t]) and the stream otherwise.
-      const int64_t t = j0 + k;
+      const int64_t t = j0 + (int64_t)k * per;
       sp[k] = nullptr;
       dp[k] = nullptr;
       if (t < work) {
@@ -214,7 +233,7 @@ k_p2p_push(const char* __restrict__ src, const int64_t* __restrict__ src_index,
         }
       }
     }
-    for (int c = lane; c < chunks; c += 32) {
+    for (int c = sub; c < chunks; c += G) {
       V v[kMoveRows];
 #pragma unroll
       for (int k = 0; k < kMoveRows; ++k)
@@ -320,12 +339,14 @@ k_p2p_pull(const char* __restrict__ local_base, const int64_t* __restrict__ recv
   const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int chunks = (int)(row_bytes / (int64_t)sizeof(V));
   const char* data = local_base + kHeaderBytes + (size_t)parity * world_size * region_bytes;
-  for (int64_t i0 = warp * kMoveRows; i0 < n; i0 += warps * kMoveRows) {
+  const int G = lane_group(chunks), sub = lane % G, per = 32 / G;      // `per` rows side by side in a warp
+  const int64_t step = (int64_t)per * kMoveRows;
+  for (int64_t i0 = warp * step + lane / G; i0 < n; i0 += warps * step) {
     const char* sp[kMoveRows];
     char* dp[kMoveRows];
 #pragma unroll
     for (int k = 0; k < kMoveRows; ++k) {
-      const int64_t i = i0 + k;
+      const int64_t i = i0 + (int64_t)k * per;
       sp[k] = nullptr;
       dp[k] = nullptr;
       if (i < n) {
@@ -339,7 +360,7 @@ k_p2p_pull(const char* __restrict__ local_base, const int64_t* __restrict__ recv
         }
       }
     }
-    for (int c = lane; c < chunks; c += 32) {
+    for (int c = sub; c < chunks; c += G) {
       V v[kMoveRows];
 #pragma unroll
       for (int k = 0; k < kMoveRows; ++k)
@@ -763,7 +784,8 @@ static int p2p_push_launch(apt_p2p* ctx, const void* src, const int64_t* src_ind
   PeerTable pt;
   for (int r = 0; r < kP2pMaxRanks; ++r) pt.base[r] = ctx->peer_base[r];
   const int w = vec_width_of((uint64_t)row_bytes | (uintptr_t)src | (uint64_t)ctx->region_bytes);
-  const int grid = wave_grid(ceil_div(max_rows > 0 ? max_rows : 1, (kMoveBlock / 32) * kMoveRows), 8, 2);
+  const int64_t rows_per_warp = (int64_t)(32 / lane_group_host(row_bytes / w)) * kMoveRows;
+  const int grid = wave_grid(ceil_div(max_rows > 0 ? max_rows : 1, (kMoveBlock / 32) * rows_per_warp), 8, 2);
   ProfScope prof("p2p_push", s);
   const char* sp = (const char*)src;
 #define APT_PUSH(V)                                                                       \
@@ -816,6 +838,18 @@ static int64_t default_timeout_ns() {
 
 extern "C" int64_t apt_p2p_default_timeout_ns(void) { return default_timeout_ns(); }
 
+extern "C" int apt_p2p_probe_copy(apt_p2p* ctx, int peer, size_t nbytes, void* stream) {
+  using namespace apt;
+  APT_CHECK_ARG(ctx && peer >= 0 && peer < ctx->world_size && ctx->peer_base[peer], "apt_p2p_probe_copy: bad peer");
+  APT_CHECK_ARG(nbytes > 0 && nbytes <= ctx->region_bytes, "apt_p2p_probe_copy: %zu bytes exceed a %zu-byte region",
+                nbytes, ctx->region_bytes);
+  // region [0][me] of the peer's inbox is written by this rank only; the source is the same region here
+  const size_t off = kHeaderBytes + (size_t)ctx->rank * ctx->region_bytes;
+  APT_CUDA(cudaMemcpyAsync(ctx->peer_base[peer] + off, ctx->local_base + off, nbytes, cudaMemcpyDeviceToDevice,
+                           (cudaStream_t)stream));
+  return APT_OK;
+}
+
 extern "C" int apt_p2p_poisoned(apt_p2p* ctx, int* out_poisoned) {
   using namespace apt;
   APT_CHECK_ARG(ctx && out_poisoned, "apt_p2p_poisoned: bad argument");
@@ -846,7 +880,8 @@ extern "C" int apt_p2p_pull(apt_p2p* ctx, const int64_t* recv_counts, const int6
   APT_CHECK_ARG(dst, "apt_p2p_pull: null destination");
   cudaStream_t s = (cudaStream_t)stream;
   const int w = vec_width_of((uint64_t)row_bytes | (uintptr_t)dst | (uint64_t)ctx->region_bytes);
-  const int grid = wave_grid(ceil_div(max_rows, (kMoveBlock / 32) * kMoveRows), 8, 4);
+  const int64_t rows_per_warp = (int64_t)(32 / lane_group_host(row_bytes / w)) * kMoveRows;
+  const int grid = wave_grid(ceil_div(max_rows, (kMoveBlock / 32) * rows_per_warp), 8, 4);
   const int mode = !dst_index ? 0 : (index_is_source ? 1 : 2);
   ProfScope prof("p2p_pull", s);
   char* dp = (char*)dst;

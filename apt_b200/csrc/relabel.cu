@@ -232,11 +232,11 @@ k_relabel(int64_t S_host, int64_t M_host, const int64_t* __restrict__ S_dev, int
 // table of kSmallCap 16-byte slots in the 227 KB of shared memory of one SM together with
 // each item's slot number. One block of 1024 threads then runs the three phases (insert,
 // ordered compaction, relabel) with block barriers between them: no global table traffic,
-// no clearing, one launch. With SAMPLE the block also draws the neighbours itself (the same
-// draws as sample_replace_kernel: they depend on the seed slot and the draw slot only), so
-// that a whole innermost hop, sampling and relabelling, is one launch. The order of first
-// occurrence is decided by the minimum position per id exactly as in the multi-block path,
-// so both give the same arrays.
+// no clearing, one launch. (Drawing the neighbours inside this one block as well was measured
+// slower than the separate sampling kernel: 28 us against 22 us for 1024 seeds x 5, because one
+// block walks the dependent seed -> row -> neighbour loads in five rounds.) The order of first
+// occurrence is decided by the minimum position per id exactly as in the multi-block path, so
+// both give the same arrays.
 static bool g_relabel_small = true;   // apt_set_tunable("relabel_small", 0) forces the multi-block path
 void set_relabel_small(bool on) { g_relabel_small = on; }
 
@@ -245,20 +245,13 @@ constexpr uint32_t kSmallCap = 12288;
 constexpr uint16_t kSmallNoSlot = 0xffffu;
 constexpr size_t kSmallSmem = (size_t)kSmallCap * sizeof(Slot) + (size_t)kSmallItems * sizeof(uint16_t);
 
-struct SmallSample {     // SAMPLE only
-  CscView g;
-  int fanout;
-  uint32_t k0, k1, call_id;
-  const int64_t* call_base_dev;
-  int64_t* out_neighbors;   // may be NULL
-};
-
-template <bool SAMPLE>
+// erase_nbrs: the neighbour list sits in the (otherwise unused) table region of the workspace and
+// every entry is put back to all-ones once read, so that the table stays empty between calls.
 __global__ void __launch_bounds__(kRelabelBlock)
-k_relabel_small(const int64_t* __restrict__ seeds, int64_t S_host, const int64_t* __restrict__ nbrs,
-                int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed,
+k_relabel_small(const int64_t* __restrict__ seeds, int64_t S_host, int64_t* __restrict__ nbrs,
+                int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed, int erase_nbrs,
                 int64_t* __restrict__ out_unique, int64_t* __restrict__ out_relabeled,
-                int64_t* __restrict__ out_num_unique, int32_t* status, SmallSample sp) {
+                int64_t* __restrict__ out_num_unique, int32_t* status) {
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ int scratch[33];
   Slot* slots = (Slot*)smem;
@@ -270,23 +263,11 @@ k_relabel_small(const int64_t* __restrict__ seeds, int64_t S_host, const int64_t
     slots[t].min_pos = kNoPos;
     slots[t].new_id = 0;
   }
-  uint32_t call_id = 0;
-  if (SAMPLE) call_id = sp.call_id + (sp.call_base_dev ? (uint32_t)*sp.call_base_dev : 0u);
   __syncthreads();
   int flags = 0;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    int64_t id;
-    if (!SAMPLE || i < d.S) {
-      id = item_at(seeds, d.S, nbrs, i);
-    } else {
-      const int64_t j = (i - d.S) / sp.fanout;
-      const int slot_i = (int)((i - d.S) % sp.fanout);
-      const int64_t v = seeds[j];
-      const int64_t* row = nullptr;
-      const int64_t deg = csc_row(sp.g, v, &row, &flags);
-      id = deg > 0 ? row[mod_deg(draw_word((uint64_t)j, (uint32_t)slot_i, call_id, sp.k0, sp.k1), deg)] : v;
-      if (sp.out_neighbors) sp.out_neighbors[i - d.S] = id;
-    }
+    const int64_t id = item_at(seeds, d.S, nbrs, i);
+    if (erase_nbrs && i >= d.S) nbrs[i - d.S] = -1;
     if (id < 0) {   // not an id (see table_insert): no slot, relabelled to -1
       flags |= APT_FLAG_ID_OUT_OF_RANGE;
       slot_of[i] = kSmallNoSlot;
@@ -327,14 +308,12 @@ k_relabel_small(const int64_t* __restrict__ seeds, int64_t S_host, const int64_t
     out_relabeled[i - d.S] = slot_of[i] == kSmallNoSlot ? (int64_t)-1 : (int64_t)slots[slot_of[i]].new_id;
 }
 
-template <bool SAMPLE>
 static int set_small_smem() {
   static bool attr_set[64] = {};
   int dev = 0;
   APT_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !attr_set[dev]) {
-    APT_CUDA(cudaFuncSetAttribute(k_relabel_small<SAMPLE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  (int)kSmallSmem));
+    APT_CUDA(cudaFuncSetAttribute(k_relabel_small, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmallSmem));
     attr_set[dev] = true;
   }
   return APT_OK;
@@ -400,11 +379,11 @@ extern "C" int apt_relabel_csc(const int64_t* seeds, int64_t num_seeds,
                 "apt_relabel_csc: null pointer");
   APT_CHECK_ARG(((uintptr_t)workspace & 255) == 0, "apt_relabel_csc: workspace must be 256-byte aligned");
   if (n <= kSmallItems && g_relabel_small) {
-    const int rc = set_small_smem<false>();
+    const int rc = set_small_smem();
     if (rc != APT_OK) return rc;
     ProfScope prof("relabel", s);
-    APT_LAUNCH(k_relabel_small<false>, 1, kRelabelBlock, kSmallSmem, s, seeds, num_seeds, neighbors, num_neighbors,
-               num_seeds_dev, per_seed, out_unique, out_relabeled, out_num_unique, status_word, SmallSample{});
+    APT_LAUNCH(k_relabel_small, 1, kRelabelBlock, kSmallSmem, s, seeds, num_seeds, (int64_t*)neighbors, num_neighbors,
+               num_seeds_dev, per_seed, 0, out_unique, out_relabeled, out_num_unique, status_word);
     return APT_OK;
   }
   RelabelWs ws;
@@ -445,29 +424,30 @@ extern "C" int apt_sample_relabel_csc(const int64_t* seeds, int64_t num_seeds, c
   APT_CHECK_ARG(((uintptr_t)workspace & 255) == 0, "apt_sample_relabel_csc: workspace must be 256-byte aligned");
   const uint32_t k0 = (uint32_t)key, k1 = (uint32_t)(key >> 32);
   const CscView g{adj_pos_map, num_nodes, dev_indptr, dev_indices, uva_indptr, uva_indices};
-  if (n <= kSmallItems && g_relabel_small) {
-    const int rc = set_small_smem<true>();
-    if (rc != APT_OK) return rc;
-    ProfScope prof("sample_relabel", s);
-    APT_LAUNCH(k_relabel_small<true>, 1, kRelabelBlock, kSmallSmem, s, seeds, num_seeds, (const int64_t*)nullptr,
-               num_neighbors, num_seeds_dev, (int64_t)fanout, out_unique, out_relabeled, out_num_unique, status_word,
-               SmallSample{g, fanout, k0, k1, call_id, call_id_base_dev, out_neighbors});
-    return APT_OK;
-  }
   RelabelWs ws;
   if (!relabel_layout((char*)workspace, workspace_bytes, &ws) || ws.items_ws < n) {
     set_error("apt_sample_relabel_csc: workspace of %zu bytes holds %lld items, %lld needed "
               "(apt_relabel_workspace_bytes)", workspace_bytes, (long long)ws.items_ws, (long long)n);
     return APT_ERR_CAPACITY;
   }
+  const bool small = n <= kSmallItems && g_relabel_small;
+  // small layers: the neighbours go to the caller's array or, when it wants none, to the table region of the
+  // workspace (16 bytes per slot, 1.5 slots per item: always room for 8 bytes per neighbour), which the
+  // one-block kernel does not use and wipes again as it reads
+  int64_t* nbr_buf = out_neighbors ? out_neighbors : (int64_t*)ws.slots;
   const SampleInsert ins{ws.slots, ws.slot_of};
   {
     ProfScope prof("sample", s);
 #define APT_SAMPLE_INSERT(G)                                                                         \
   do {                                                                                               \
     const int grid = wave_grid(ceil_div(num_seeds, 256 / G), 8);                                     \
-    APT_LAUNCH((sample_replace_kernel<G, true>), grid, 256, 0, s, seeds, num_seeds, num_seeds_dev,   \
-               fanout, g, k0, k1, call_id, call_id_base_dev, out_neighbors, status_word, ins);       \
+    if (small)                                                                                       \
+      APT_LAUNCH((sample_replace_kernel<G, false>), grid, 256, 0, s, seeds, num_seeds,               \
+                 num_seeds_dev, fanout, g, k0, k1, call_id, call_id_base_dev, nbr_buf, status_word,  \
+                 SampleInsert{nullptr, nullptr});                                                    \
+    else                                                                                             \
+      APT_LAUNCH((sample_replace_kernel<G, true>), grid, 256, 0, s, seeds, num_seeds, num_seeds_dev, \
+                 fanout, g, k0, k1, call_id, call_id_base_dev, out_neighbors, status_word, ins);     \
   } while (0)
     if (fanout <= 8) {
       APT_SAMPLE_INSERT(8);
@@ -479,6 +459,14 @@ extern "C" int apt_sample_relabel_csc(const int64_t* seeds, int64_t num_seeds, c
 #undef APT_SAMPLE_INSERT
   }
   ProfScope prof("relabel", s);
+  if (small) {
+    const int rc = set_small_smem();
+    if (rc != APT_OK) return rc;
+    APT_LAUNCH(k_relabel_small, 1, kRelabelBlock, kSmallSmem, s, seeds, num_seeds, nbr_buf, num_neighbors,
+               num_seeds_dev, (int64_t)fanout, out_neighbors ? 0 : 1, out_unique, out_relabeled, out_num_unique,
+               status_word);
+    return APT_OK;
+  }
   return scan_and_relabel(num_seeds, num_neighbors, num_seeds_dev, (int64_t)fanout, ws, out_unique, out_relabeled,
                           out_num_unique, status_word, s);
 }

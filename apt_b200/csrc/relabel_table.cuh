@@ -96,7 +96,9 @@ __device__ __forceinline__ int32_t table_insert(Slot* slots, uint32_t cap, int64
     unsigned long long prev = *(volatile unsigned long long*)&s->key;
     if (prev == kEmptyKey) prev = atomicCAS(&s->key, kEmptyKey, key);
     if (prev == kEmptyKey || prev == key) {
-      atomicMin(&s->min_pos, pos);
+      // the minimum only falls: an id that many items share (a hub) stops costing atomics on one
+      // address as soon as an early position has arrived
+      if (*(volatile uint32_t*)&s->min_pos > pos) atomicMin(&s->min_pos, pos);
       return (int32_t)at;
     }
     at = at + 1 == cap ? 0 : at + 1;

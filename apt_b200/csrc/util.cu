@@ -80,7 +80,39 @@ k_normal_rows(uint32_t k0, uint32_t k1, int64_t first_row, const int64_t* __rest
   }
 }
 
+// Zipf-distributed ranks in [1, num_ranks]: rank k with probability proportional to the integral of
+// x^-s over [k, k+1) (s > 1), drawn by inverting that integral at u in (0,1):
+//     k = floor((1 + u ((N+1)^(1-s) - 1))^(1/(1-s))),   u = (53 random bits + 0.5) / 2^53.
+// Draw i uses words 0 and 1 of Philox4x32-10 with counter (i, i >> 32, 0, "zipf").
+__global__ void __launch_bounds__(256)
+k_zipf_ranks(uint32_t k0, uint32_t k1, int64_t first_draw, int64_t num_draws, int64_t num_ranks, double s,
+             int64_t* __restrict__ out) {
+  const double e = 1.0 - s, span = pow((double)num_ranks + 1.0, e) - 1.0, inv = 1.0 / e;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < num_draws; i += stride) {
+    const uint64_t d = (uint64_t)(first_draw + i);
+    const Philox4 p = philox4x32_10((uint32_t)d, (uint32_t)(d >> 32), 0u, 0x7a697066u, k0, k1);
+    const uint64_t bits = (((uint64_t)p.w[0] << 32) | p.w[1]) >> 11;
+    const double u = ((double)bits + 0.5) * (1.0 / 9007199254740992.0);
+    int64_t k = (int64_t)floor(pow(1.0 + u * span, inv));
+    out[i] = k < 1 ? 1 : (k > num_ranks ? num_ranks : k);
+  }
+}
+
 }  // namespace apt
+
+extern "C" int apt_zipf_ranks(uint64_t seed, int64_t first_draw, int64_t num_draws, int64_t num_ranks, double s,
+                              int64_t* out, void* stream) {
+  using namespace apt;
+  APT_CHECK_ARG(num_draws >= 0 && num_ranks >= 1 && s > 1.0, "apt_zipf_ranks: bad argument (s must exceed 1)");
+  if (num_draws == 0) return APT_OK;
+  APT_CHECK_ARG(out, "apt_zipf_ranks: null pointer");
+  const int grid = wave_grid(ceil_div(num_draws, 256), 8);
+  APT_LAUNCH(k_zipf_ranks, grid, 256, 0, (cudaStream_t)stream, (uint32_t)seed, (uint32_t)(seed >> 32), first_draw,
+             num_draws, num_ranks, s, out);
+  return APT_OK;
+}
 
 extern "C" int apt_rmat_edges(uint64_t seed, int64_t first_edge, int64_t num_edges, int scale,
                               int64_t num_nodes, float a, float b, float c, int64_t* out_src,

@@ -199,6 +199,11 @@ class P2PExchange:
     def region_bytes(self):
         return int(lib.apt_p2p_region_bytes(self.ctx))
 
+    def probe_peer_copy(self, peer: int, nbytes: int):
+        """Enqueues one plain copy of nbytes from this rank's inbox into `peer`'s (apt_p2p_probe_copy):
+        the link rate a shuffle is compared with. Call it only between exchanges, behind a barrier."""
+        check(lib.apt_p2p_probe_copy(self.ctx, int(peer), int(nbytes), _stream()))
+
     def poisoned(self) -> bool:
         """True once a wait of this rank ran out of time. The inbox then refuses every further
         exchange (the kernels set the peer-timeout flag and store nothing): all ranks have to

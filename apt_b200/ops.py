@@ -162,11 +162,15 @@ class NPCState:
         w = self.words()
         self._host_words.copy_(w, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-        flags = int(self._host_words[self.NUM_WORDS - 1]) & 0xFFFFFFFF
-        if flags & ~_lib.FLAG_ZERO_DEGREE:
-            w[self.NUM_WORDS - 1] = 0
-            raise RuntimeError(f"apt_b200 device status flags 0x{flags:x}: " + _flag_text(flags))
+        self.check_host_words(self._host_words)
         return self._host_words
+
+    def check_host_words(self, host: torch.Tensor):
+        """Raises if a host copy of the word block carries a status flag (zero-degree is a notice)."""
+        flags = int(host[self.NUM_WORDS - 1]) & 0xFFFFFFFF
+        if flags & ~_lib.FLAG_ZERO_DEGREE:
+            self.words()[self.NUM_WORDS - 1] = 0
+            raise RuntimeError(f"apt_b200 device status flags 0x{flags:x}: " + _flag_text(flags))
 
 
 def _flag_text(flags):

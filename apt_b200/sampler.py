@@ -71,6 +71,11 @@ class _Plan:
         self.graph = None
         self.generation = -1
         self.keepalive = None
+        # pipelined use (sample_iter): the batch's own copy of the word block, the event behind that
+        # copy, and its own pinned word for the call-id base
+        self.host_words = None
+        self.done = None
+        self.host_base = None
 
 
 _CALL_BASE_SLOT = 100  # device word holding the sampler's call-id base for graph replays
@@ -105,9 +110,12 @@ class MixedNeighborSampler:
         self.prefetch_features = prefetch_features
         self.use_graph = use_graph and chained
         self.graph_buffers = max(1, int(graph_buffers))
-        # 0: one gather after the outermost hop; 1: the frontier's rows are gathered beside the
-        # outermost hop and the two meet before the remaining rows are gathered; 2: they meet at the end
-        self.gather_split = int(os.environ.get("APT_GATHER_SPLIT", "1"))
+        # 0 (default): one gather after the outermost hop; 1: the frontier's rows are gathered on a second
+        # stream beside the outermost hop and the two meet before the remaining rows are gathered; 2: they
+        # meet at the end. Measured on the papers-shaped run, 1 and 2 are slower (0.371 and 0.374 ms per
+        # mini-batch against 0.340): kernels that share SMs with the host-memory reads of the miss copy
+        # slow down by more than the overlap wins.
+        self.gather_split = int(os.environ.get("APT_GATHER_SPLIT", "0"))
         self._plans = {}
         self._turn = 0
         self._host_base = None
@@ -191,11 +199,13 @@ class MixedNeighborSampler:
         return dict(layers=layers, perm=perm, inv=inv, uniq2=uniq2, uniq3=uniq3, rel3=rel3, rows=rows,
                     u_slot=u_slot, in_slot=in_slot)
 
-    def _finish(self, seeds, bufs):
-        """The one host read of the mini-batch, then buffers narrowed to their real sizes."""
+    def _finish(self, seeds, bufs, host=None):
+        """The one host read of the mini-batch (or the copy of the word block a pipelined launch
+        left in `host`), then buffers narrowed to their real sizes."""
         st = ops.STATE
         ws = st.world_size
-        host = st.read_words()
+        if host is None:
+            host = st.read_words()
         u_slot, in_slot = bufs["u_slot"], bufs["in_slot"]
         count = [int(host[k]) for k in range(in_slot + 1)]
         recv_offset = host[16:16 + ws].clone().cumsum(0)
@@ -270,6 +280,51 @@ class MixedNeighborSampler:
         plan.graph.replay()
         st.sample_calls += self.num_layers
         return self._finish(seeds, plan.bufs)
+
+
+    # ------------------------------------------------------------ pipelined use
+    def sample_iter(self, graph, seed_batches):
+        """Yields what sample() returns for every tensor of `seed_batches`, with the next mini-batch
+        already enqueued while the previous one is read back and handed out, so that the GPU never
+        waits for the host between mini-batches (the role a prefetching DataLoader has around the
+        reference's sampler, examples/train.py:85-94). Needs the CUDA-graph path; otherwise it falls
+        back to one sample() per batch. A mini-batch's tensors stay valid until the one after the
+        next has been asked for (two buffer sets in turn)."""
+        if not (self.chained and self._graph_ok() and self.graph_buffers >= 2):
+            for seeds in seed_batches:
+                yield self.sample(graph, seeds)
+            return
+        pending = None
+        for seeds in seed_batches:
+            launched = self._launch(seeds)
+            if pending is not None:
+                yield self._collect(pending)
+            pending = launched
+        if pending is not None:
+            yield self._collect(pending)
+
+    def _launch(self, seeds):
+        st = ops.STATE
+        seeds = ops._need_cuda(seeds, "seeds")
+        plan = self._plan_for(seeds)
+        if plan.host_words is None:
+            plan.host_words = torch.zeros(st.NUM_WORDS, dtype=torch.int64).pin_memory()
+            plan.host_base = torch.zeros(1, dtype=torch.int64).pin_memory()
+            plan.done = torch.cuda.Event()
+        plan.host_base[0] = st.sample_calls
+        st.word(_CALL_BASE_SLOT).copy_(plan.host_base, non_blocking=True)
+        plan.seeds_buf.copy_(seeds)
+        plan.graph.replay()
+        st.sample_calls += self.num_layers
+        plan.host_words.copy_(st.words(), non_blocking=True)
+        plan.done.record()
+        return plan, seeds
+
+    def _collect(self, launched):
+        plan, seeds = launched
+        plan.done.synchronize()
+        ops.STATE.check_host_words(plan.host_words)
+        return self._finish(seeds, plan.bufs, plan.host_words)
 
 
 class SPGATSampler:

@@ -48,6 +48,12 @@ class Workload:
     train_seed: int = 4
     undirected: bool = False
     notes: str = ""
+    partition: str = "random"        # "random": contiguous ranges of randomly relabelled ids; "bfs": ranges of a
+                                     # breadth-first order from bfs_root (locality-preserving)
+    bfs_root_seed: int = 5
+    seed_dist: str = "uniform"       # "uniform": batches out of a seeded training split; "zipf": Zipf(zipf_s) over
+    zipf_s: float = 1.1              # the rank by in-degree
+    host_rows_cap: Optional[int] = None   # host table rows when the full table does not fit host memory
 
     @property
     def scale(self):
@@ -62,7 +68,19 @@ WORKLOADS = {
     # configs[3]: friendster-shaped DNP run
     "c3_friendster_np": Workload("c3_friendster_np", 65_608_366, 1_800_000_000, 256, "bf16", 0.40, [20, 15], 2048, 256,
                                  0.01, undirected=True),
-    # a miniature of c1 for quick checks and tests
+    # configs[2]: the papers-shaped graph with a locality-preserving partition, SNP with a 3-layer GAT
+    # (4 heads x 64, bf16): SDDMM edge scores and softmax-weighted SpMM on the sampled blocks
+    "c2_papers_snp_gat": Workload("c2_papers_snp_gat", 111_059_956, 1_600_000_000, 128, "f32", 0.25, [15, 10, 5], 1024,
+                                  256, 0.011, system="SP", partition="bfs"),
+    # configs[4]: skewed large-feature gather / shuffle stress test (1024-dim fp16 rows of 2 KiB, 60 GB of
+    # cached rows per GPU, Zipf(1.1) seeds over the degree rank)
+    "c4_stress": Workload("c4_stress", 100_000_000, 1_200_000_000, 1024, "f16", 0.0, [10, 10, 10], 4096, 256, 0.0,
+                          cache_bytes=60 * 10 ** 9, seed_dist="zipf", zipf_s=1.1, host_rows_cap=16_000_000),
+    # miniatures for quick checks and tests
+    "tiny_snp_gat": Workload("tiny_snp_gat", 1 << 15, 1 << 19, 64, "f32", 0.25, [6, 5, 4], 128, 256, 0.05,
+                             system="SP", partition="bfs"),
+    "tiny_stress": Workload("tiny_stress", 1 << 15, 1 << 19, 256, "f16", 0.0, [4, 4, 4], 256, 256, 0.0,
+                            cache_bytes=6000 * 512, seed_dist="zipf", zipf_s=1.1, host_rows_cap=5000),
     "tiny_np": Workload("tiny_np", 1 << 16, 1 << 20, 128, "f32", 0.25, [15, 10, 5], 256, 256, 0.05),
 }
 
@@ -140,11 +158,11 @@ def normal_rows(w: Workload, device, first_row=0, num_rows=0, row_ids=None):
     return out
 
 
-def _shared_host_table(w: Workload, rank: int, world_size: int, tag: str):
+def _shared_host_table(w: Workload, rank: int, world_size: int, tag: str, rows: Optional[int] = None):
     """One host table for all ranks of the box: a /dev/shm file mapped shared and
     page-locked by every process (the reference shares its feature tensor
     between the per-GPU processes and registers it, examples/train.py:43-46)."""
-    rows, dim = w.num_nodes, w.feat_dim
+    rows, dim = (w.num_nodes if rows is None else rows), w.feat_dim
     dt = _TORCH_DT[w.dtype]
     if world_size == 1:
         return hostmem.alloc_table(rows, dim, dt), None
@@ -162,6 +180,113 @@ def _shared_host_table(w: Workload, rank: int, world_size: int, tag: str):
     return t, path
 
 
+
+def bfs_order(indptr: torch.Tensor, indices: torch.Tensor, root: int, edge_chunk: int = 1 << 27) -> torch.Tensor:
+    """Breadth-first visiting order over the in-neighbour lists from `root` on the GPU: level by
+    level, ascending ids inside a level, unreached nodes last in id order. order[k] is the node
+    visited k-th. Contiguous blocks of this order are the locality-preserving partition that stands
+    in for the reference's METIS partition (scripts/preprocess_dataset.py:76-135)."""
+    n = indptr.numel() - 1
+    dev = indptr.device
+    deg = indptr[1:] - indptr[:-1]
+    visited = torch.zeros(n, dtype=torch.bool, device=dev)
+    order = torch.empty(n, dtype=torch.int64, device=dev)
+    frontier = torch.tensor([root], dtype=torch.int64, device=dev)
+    visited[root] = True
+    pos = 0
+    while frontier.numel():
+        k = frontier.numel()
+        order[pos:pos + k] = frontier
+        pos += k
+        mark = torch.zeros(n, dtype=torch.bool, device=dev)
+        d = deg[frontier]
+        ends = torch.cumsum(d, 0)
+        start, done = 0, 0
+        while start < k:      # expand the frontier's lists in pieces of about edge_chunk edges
+            stop = int(torch.searchsorted(ends, torch.tensor(done + edge_chunk, device=dev), right=True))
+            stop = min(max(stop, start + 1), k)
+            f, dd = frontier[start:stop], d[start:stop]
+            tot = int(ends[stop - 1]) - done
+            if tot:
+                first = indptr[f] - (torch.cumsum(dd, 0) - dd)
+                idx = torch.repeat_interleave(first, dd) + torch.arange(tot, device=dev)
+                mark[indices[idx]] = True
+                del idx
+            done += tot
+            start = stop
+        mark &= ~visited
+        frontier = mark.nonzero().view(-1)
+        visited |= mark
+    order[pos:] = (~visited).nonzero().view(-1)
+    return order
+
+
+def relabel_graph(indptr: torch.Tensor, indices: torch.Tensor, order: torch.Tensor, chunk: int = 1 << 27):
+    """The CSC after renumbering node order[k] to k (dgl.reorder_graph in
+    scripts/preprocess_dataset.py:128-130): (indptr, indices) with lists sorted by new source id."""
+    n = indptr.numel() - 1
+    dev = indptr.device
+    bits = max(1, (n - 1).bit_length())
+    new_id = torch.empty(n, dtype=torch.int64, device=dev)
+    new_id[order] = torch.arange(n, dtype=torch.int64, device=dev)
+    total = indices.numel()
+    keys = torch.empty(total, dtype=torch.int64, device=dev)
+    deg = indptr[1:] - indptr[:-1]
+    for first in range(0, n, chunk >> 4):        # by destination ranges, to bound the expanded temporaries
+        last = min(n, first + (chunk >> 4))
+        lo, hi = int(indptr[first]), int(indptr[last])
+        dst = torch.repeat_interleave(new_id[first:last], deg[first:last])
+        keys[lo:hi] = (dst << bits) | new_id[indices[lo:hi]]
+        del dst
+    out = torch.empty_like(keys)
+    tb = lib.apt_sort_u64_temp_bytes(total)
+    temp = torch.empty(tb, dtype=torch.uint8, device=dev)
+    check(lib.apt_sort_u64(_p(keys), _p(out), total, _p(temp), tb, 2 * bits, _s()))
+    del keys, temp
+    counts = deg[order]                              # the list of new node k is the list of order[k]
+    new_indptr = torch.zeros(n + 1, dtype=torch.int64, device=dev)
+    torch.cumsum(counts, 0, out=new_indptr[1:])
+    out.bitwise_and_((1 << bits) - 1)
+    return new_indptr, out
+
+
+def intra_partition_edge_share(indptr: torch.Tensor, indices: torch.Tensor, min_vids: torch.Tensor,
+                               chunk: int = 1 << 22) -> float:
+    """Share of the edges whose endpoints have the same owner under the contiguous ranges min_vids."""
+    n = indptr.numel() - 1
+    dev = indptr.device
+    cuts = min_vids[1:-1].to(dev)
+    deg = indptr[1:] - indptr[:-1]
+    same = 0
+    for first in range(0, n, chunk):
+        last = min(n, first + chunk)
+        lo, hi = int(indptr[first]), int(indptr[last])
+        owner_dst = torch.bucketize(torch.arange(first, last, device=dev), cuts, right=True)
+        same += int((torch.repeat_interleave(owner_dst, deg[first:last]) ==
+                     torch.bucketize(indices[lo:hi], cuts, right=True)).sum())
+    return same / max(indices.numel(), 1)
+
+
+def zipf_seed_batches(w: Workload, degree_order: torch.Tensor, rank: int, count: int, first_batch: int = 0):
+    """`count` batches of w.batch distinct seeds drawn Zipf(w.zipf_s) over the rank by in-degree
+    (degree_order[0] is the node of highest in-degree): each batch takes 4 x batch draws of its own
+    counter range, maps them to nodes, drops repeats keeping the first occurrence (the relabel kernel
+    does exactly that) and keeps the first w.batch."""
+    dev = degree_order.device
+    per = 4 * w.batch
+    out = []
+    e = torch.empty(0, dtype=torch.int64, device=dev)
+    for b in range(first_batch, first_batch + count):
+        ranks = torch.empty(per, dtype=torch.int64, device=dev)
+        check(lib.apt_zipf_ranks(w.train_seed + 1000 * rank, b * per, per, degree_order.numel(), float(w.zipf_s),
+                                 _p(ranks), _s()))
+        uniq, _ = ops.relabel_csc(e, degree_order[ranks - 1])
+        if uniq.numel() < w.batch:
+            raise RuntimeError(f"{uniq.numel()} distinct seeds out of {per} Zipf draws: fewer than the batch of {w.batch}")
+        out.append(uniq[:w.batch].contiguous())
+    return out
+
+
 @dataclass
 class Installed:
     workload: Workload
@@ -175,6 +300,7 @@ class Installed:
     train_ids: torch.Tensor
     shm_path: Optional[str] = None
     info: dict = field(default_factory=dict)
+    degree_order: Optional[torch.Tensor] = None     # node ids by falling in-degree (seed_dist == "zipf")
 
 
 def install(w: Workload, rank=0, world_size=1, row_chunk=1 << 22, tag="bench") -> Installed:
@@ -183,10 +309,25 @@ def install(w: Workload, rank=0, world_size=1, row_chunk=1 << 22, tag="bench") -
     device = torch.device("cuda", torch.cuda.current_device())
     indptr, indices = build_csc(w, device)
     n = w.num_nodes
+    min_vids = partition_min_vids(n, world_size)
+    info = {}
+    if w.partition == "bfs":
+        # locality-preserving partition: renumber by breadth-first order from a seeded root, then the
+        # same equal contiguous ranges; the share of edges inside one part is measured, not assumed
+        parts = max(world_size, 8) if world_size == 1 else world_size
+        probe = partition_min_vids(n, parts)
+        info["intra_partition_edge_share_random"] = round(intra_partition_edge_share(indptr, indices, probe), 4)
+        g0 = torch.Generator().manual_seed(w.bfs_root_seed)
+        root = int(torch.randint(0, n, (1,), generator=g0))
+        order = bfs_order(indptr, indices, root)
+        indptr, indices = relabel_graph(indptr, indices, order)
+        del order
+        info["intra_partition_edge_share"] = round(intra_partition_edge_share(indptr, indices, probe), 4)
+        info["partition_parts_measured"] = parts
+        info["bfs_root"] = root
     e = torch.empty(0, dtype=torch.int64)
     # whole topology resident in HBM: no adjacency cache is needed
     ops.mix_cache_graphs(0, e, e, e, indptr, indices)
-    min_vids = partition_min_vids(n, world_size)
     ops.register_min_vids(min_vids)
 
     deg = indptr[1:] - indptr[:-1]
@@ -194,12 +335,17 @@ def install(w: Workload, rank=0, world_size=1, row_chunk=1 << 22, tag="bench") -
     k = int(n * w.cache_frac) if w.cache_bytes is None else min(n, w.cache_bytes // (w.feat_dim * esz))
     order = torch.sort(deg, descending=True, stable=True).indices
     cached_idx = order[:k].contiguous()
+    degree_order = order if w.seed_dist == "zipf" else None
     del order, deg
-    dev_feats = normal_rows(w, device, row_ids=cached_idx)
+    # When the full host table does not fit host memory it holds host_rows rows and the features repeat
+    # with that period (node v has the row of node v mod host_rows), in the cache as in host memory:
+    # bytes per row, miss rate and access pattern stay those of the full table.
+    host_rows = n if w.host_rows_cap is None else min(n, int(w.host_rows_cap))
+    dev_feats = normal_rows(w, device, row_ids=cached_idx % host_rows if host_rows < n else cached_idx)
 
-    host, shm_path = _shared_host_table(w, rank, world_size, tag)
-    lo = (n * rank) // world_size
-    hi = (n * (rank + 1)) // world_size
+    host, shm_path = _shared_host_table(w, rank, world_size, tag, rows=host_rows)
+    lo = (host_rows * rank) // world_size
+    hi = (host_rows * (rank + 1)) // world_size
     for first in range(lo, hi, row_chunk):
         m = min(row_chunk, hi - first)
         host[first:first + m].copy_(normal_rows(w, device, first_row=first, num_rows=m))
@@ -208,16 +354,38 @@ def install(w: Workload, rank=0, world_size=1, row_chunk=1 << 22, tag="bench") -
         import torch.distributed as dist
 
         dist.barrier()
-    local_idx = torch.arange(n, dtype=torch.int64)
+    local_idx = torch.arange(host_rows, dtype=torch.int64)
     ops.cache_feats_shared(n, host, dev_feats, cached_idx.cpu(), local_idx, 0)
+    if host_rows < n:
+        m = ops.STATE.feat.feat_pos_map
+        absent = (m == -1).nonzero().view(-1)
+        m[absent] = -(absent % host_rows) - 2
+        del absent
+        ops.STATE.feat._cpu_map_args = None      # the CPU twin of the gather does not model the repeating table
+        info["host_rows"] = host_rows
 
     g = torch.Generator(device=device).manual_seed(w.train_seed)
     n_train = max(w.batch * world_size, int(n * w.train_frac))
     train = torch.randperm(n, generator=g, device=device)[:n_train]
     per = n_train // world_size            # rebalanced evenly (python/npc/ops.py:454-462)
     train_ids = train[rank * per:(rank + 1) * per].contiguous()
-    return Installed(w, rank, world_size, indptr, indices, min_vids, host, cached_idx, train_ids, shm_path,
-                     {"num_cached_rows": k, "num_csc_edges": int(indices.numel())})
+    info.update(num_cached_rows=k, num_csc_edges=int(indices.numel()))
+    return Installed(w, rank, world_size, indptr, indices, min_vids, host, cached_idx, train_ids, shm_path, info,
+                     degree_order)
+
+
+def seed_batches(inst: Installed, count: int, offset: int = 0):
+    """`count` consecutive seed batches of this rank: slices of its training ids (wrapping) or, for
+    a Zipf workload, batches of distinct Zipf-distributed seeds."""
+    w = inst.workload
+    if w.seed_dist == "zipf":
+        return zipf_seed_batches(w, inst.degree_order, inst.rank, count, first_batch=offset)
+    n = inst.train_ids.numel()
+    out = []
+    for i in range(count):
+        lo = ((offset + i) * w.batch) % max(n - w.batch + 1, 1)
+        out.append(inst.train_ids[lo:lo + w.batch].contiguous())
+    return out
 
 
 def cleanup(inst: Installed):

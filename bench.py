@@ -32,7 +32,7 @@ import torch.distributed as dist
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-STAGE_TAGS = ("sample_relabel", "sample", "relabel", "bucket", "unique_sorted", "gather_hit", "gather_miss",
+STAGE_TAGS = ("sample", "relabel", "bucket", "unique_sorted", "gather_classify", "gather_hit", "gather_miss",
               "p2p_push", "p2p_wait", "p2p_pull")
 # DRAM bytes (read + written) per algorithmic byte of the hit kernel, from an ncu capture of that kernel
 # alone at the mini-batch's size (143 000 rows of 512 bytes out of a 27.8 M-row cache table); None until
@@ -126,14 +126,28 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def batches_of(train_ids, batch, count, offset=0):
-    """`count` consecutive seed batches out of the rank's training ids (wrapping)."""
-    n = train_ids.numel()
-    out = []
-    for i in range(count):
-        lo = ((offset + i) * batch) % max(n - batch + 1, 1)
-        out.append(train_ids[lo:lo + batch].contiguous())
-    return out
+def batches_of(inst, count, offset=0):
+    """`count` consecutive seed batches of the rank (apt_b200.synthetic.seed_batches)."""
+    from apt_b200 import synthetic
+
+    return synthetic.seed_batches(inst, count, offset)
+
+
+def digest_np(a):
+    """Order-sensitive 64-bit digest of an integer array: sum of a[i] * (2 i + 1) modulo 2^64."""
+    import numpy as np
+
+    flat = np.ascontiguousarray(a).reshape(-1).astype(np.int64).view(np.uint64)
+    with np.errstate(over="ignore"):
+        k = np.arange(len(flat), dtype=np.uint64) * np.uint64(2) + np.uint64(1)
+        return int((flat * k).sum(dtype=np.uint64))
+
+
+def digest_torch(t):
+    """The same digest on the device (int64 arithmetic wraps like uint64)."""
+    flat = t.reshape(-1).to(torch.int64)
+    k = torch.arange(flat.numel(), dtype=torch.int64, device=flat.device) * 2 + 1
+    return int((flat * k).sum().item()) & 0xFFFFFFFFFFFFFFFF
 
 
 # ------------------------------------------------------------------ CPU baseline
@@ -160,7 +174,8 @@ class CpuPath:
             else inst.host_feats.numpy()
         self.row_bytes = inst.host_feats.shape[1] * inst.host_feats.element_size()
         n = self.w.num_nodes
-        self.pos_map = -np.arange(n, dtype=np.int64) - 2      # every row in the host table
+        # every row is read from the host table; a table shorter than the node count repeats with its length
+        self.pos_map = -(np.arange(n, dtype=np.int64) % inst.host_feats.shape[0]) - 2
         self.min_vids = inst.min_vids.numpy().astype(np.int64)
         # torchrun hands its workers OMP_NUM_THREADS=1: the baseline takes the host's threads explicitly
         self.lib.oracle_set_threads.restype = ctypes.c_int
@@ -186,29 +201,75 @@ class CpuPath:
                                     ctypes.c_int64(len(nbrs)), self._p(uniq), self._p(rel))
         return uniq[:u], rel
 
-    def batch(self, seeds):
+    def inner_hops(self, seeds):
+        """The local hops: returns (frontier, [(unique, relabelled) per hop, innermost first], next call id)."""
         np = self.np
         cur = np.ascontiguousarray(seeds, dtype=np.int64)
-        call = 0
+        call, layers = 0, []
         for f in reversed(self.w.fanouts[1:]):
             nbr = self._sample(cur, f, call)
             call += 1
-            cur, _ = self._relabel(cur, nbr)
+            cur, rel = self._relabel(cur, nbr)
+            layers.append((cur, rel))
+        return cur, layers, call
+
+    def bucket(self, ids, rank):
+        np = self.np
         ws = len(self.min_vids) - 1
-        sorted_ids, perm = np.empty_like(cur), np.empty_like(cur)
+        sorted_ids, perm = np.empty_like(ids), np.empty_like(ids)
         sizes, offs = np.empty(ws, dtype=np.int64), np.empty(ws, dtype=np.int64)
-        self.lib.oracle_bucket(self._p(cur), ctypes.c_int64(len(cur)), self._p(self.min_vids), ws, ctypes.c_int64(0),
-                               0, 0, ws, self._p(sorted_ids), self._p(perm), self._p(sizes), self._p(offs))
-        uniq, inv = np.empty_like(cur), np.empty_like(cur)
-        u = self.lib.oracle_unique_sorted(self._p(sorted_ids), ctypes.c_int64(len(cur)), self._p(uniq), self._p(inv))
-        uniq = uniq[:u]
+        self.lib.oracle_bucket(self._p(ids), ctypes.c_int64(len(ids)), self._p(self.min_vids), ws, ctypes.c_int64(0),
+                               rank, 0, ws, self._p(sorted_ids), self._p(perm), self._p(sizes), self._p(offs))
+        return sorted_ids, perm, sizes, offs
+
+    def outer_hop(self, received, call):
+        """Sorted unique of what a rank received, the outermost hop on it, its relabelling."""
+        np = self.np
+        uniq, inv = np.empty_like(received), np.empty_like(received)
+        u = self.lib.oracle_unique_sorted(self._p(received), ctypes.c_int64(len(received)), self._p(uniq), self._p(inv))
+        uniq = uniq[:u].copy()
         nbr = self._sample(uniq, self.w.fanouts[0], call)
-        inputs, _ = self._relabel(uniq, nbr)
+        inputs, rel = self._relabel(uniq, nbr)
+        return uniq, inv, inputs, rel
+
+    def gather(self, inputs):
+        np = self.np
         out = np.empty((len(inputs), self.row_bytes), dtype=np.uint8)
         self.lib.oracle_gather(self._p(inputs), ctypes.c_int64(len(inputs)), self._p(self.pos_map), None,
                                ctypes.c_int64(self.row_bytes), self._p(self.feats), ctypes.c_int64(self.row_bytes),
                                ctypes.c_int64(0), self._p(out))
+        return out
+
+    def batch(self, seeds):
+        cur, _, call = self.inner_hops(seeds)
+        sorted_ids, _, _, _ = self.bucket(cur, 0)
+        _, _, inputs, _ = self.outer_hop(sorted_ids, call)
+        self.gather(inputs)
         return len(inputs)
+
+    def replay(self, seeds_per_rank):
+        """One NP mini-batch of every rank at once (the seed exchange is a concatenation of the
+        buckets in rank order): per rank a dict of what the sampler and the gather must return."""
+        np = self.np
+        world = len(seeds_per_rank)
+        first = [self.inner_hops(s) for s in seeds_per_rank]
+        buckets = [self.bucket(first[r][0], r) for r in range(world)]
+        out = []
+        for r in range(world):
+            parts = []
+            for q in range(world):
+                sorted_q, _, sizes_q, offs_q = buckets[q]
+                lo = int(offs_q[r] - sizes_q[r])
+                parts.append(sorted_q[lo:int(offs_q[r])])
+            received = np.concatenate(parts) if parts else np.empty(0, dtype=np.int64)
+            uniq, inv, inputs, rel = self.outer_hop(received, first[r][2])
+            out.append({
+                "input_nodes": inputs, "outer_rel": rel, "inner_rel": [l[1] for l in first[r][1]],
+                "perm": buckets[r][1], "inverse_idx": inv[:len(received)],
+                "recv_counts": np.array([len(p) for p in parts], dtype=np.int64), "bucket_offsets": buckets[r][3],
+                "rows_digest": digest_np(self.gather(inputs).view(np.int32)),
+            })
+        return out
 
     def time(self, seed_batches, warmup=1):
         for b in seed_batches[:warmup]:
@@ -251,7 +312,7 @@ def stage_gather(args):
                          torch.randint(n_dev, n, (n_miss,), generator=g, device="cuda")])
         ids = ids[torch.randperm(args.rows, generator=g, device="cuda")].contiguous()
         if it == args.warmup:
-            for tag in (b"gather_hit", b"gather_miss"):
+            for tag in (b"gather_hit", b"gather_miss", b"gather_classify"):
                 t, k = ctypes.c_double(), ctypes.c_int64()
                 lib.apt_profile_read(tag, ctypes.byref(t), ctypes.byref(k))
         torch.cuda.nvtx.range_push("apt_timed")
@@ -264,14 +325,14 @@ def stage_gather(args):
             total_ms += ev0.elapsed_time(ev1)
     ops.check_status()
     res = {}
-    for tag in ("gather_hit", "gather_miss"):
+    for tag in ("gather_hit", "gather_miss", "gather_classify"):
         t, k = ctypes.c_double(), ctypes.c_int64()
         lib.apt_profile_read(tag.encode(), ctypes.byref(t), ctypes.byref(k))
         res[tag] = (t.value, k.value)
     hit_ms, hit_n = res["gather_hit"]
-    # the hit kernel reads an id and a position-map entry for every requested row (16 bytes) and moves
-    # every cached row once in and once out
-    hit_bytes = (args.rows - n_miss) * 2 * row_bytes + args.rows * 16
+    # the hit kernel reads the 8-byte position of every requested row and moves every cached row once in
+    # and once out
+    hit_bytes = (args.rows - n_miss) * 2 * row_bytes + args.rows * 8
     gbs = hit_bytes / (hit_ms / hit_n * 1e-3) / 1e9
     call_gbs = args.rows * (2 * row_bytes + 16) / (total_ms / args.steps * 1e-3) / 1e9
     print(json.dumps({
@@ -282,7 +343,7 @@ def stage_gather(args):
                    "miss_frac": args.miss_frac, "l2": "cache table larger than the 126 MB L2, new random ids every call"},
         "whole_call_gbs": call_gbs,
         "stage_us": {k: 1000.0 * v[0] / max(v[1], 1) for k, v in res.items()},
-        "roofline": {"kernel": "k_gather_hits", "bound": "hbm", "achieved": round(gbs, 1), "peak": peak,
+        "roofline": {"kernel": "k_copy_hits", "bound": "hbm", "achieved": round(gbs, 1), "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": round(gbs / peak, 4), "traffic": None}}))
 
 
@@ -600,6 +661,272 @@ def stage_strategies(args):
     dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------ parity check
+def parity_check(inst, w, rank, world, cpu_path, barrier):
+    """One NP mini-batch of the benchmarked configuration on every rank, compared on rank 0 with the
+    CPU restatement (oracle/) replaying all ranks at once: input nodes, every block's relabelled
+    neighbours, permutation, inverse index, exchange counts bit for bit, and the gathered rows through
+    a 64-bit digest. Then the feature shuffle forward and backward with rows that are a function of the
+    node id, so that each rank can tell locally what has to arrive where. Raises on any mismatch."""
+    import numpy as np
+
+    import apt_b200
+    from apt_b200 import ops
+
+    seeds = batches_of(inst, 1, offset=7)[0]
+    ops.set_sampling(key=7777777, call_id=0)
+    smp = apt_b200.MixedNeighborSampler(rank, w.fanouts, chained=True, use_graph=False)
+    barrier()
+    input_nodes, _, blocks, perm, send_off, recv_off, inv = smp.sample(None, seeds)
+    x = ops.load_subtensor(input_nodes)
+    ops.check_status()
+    counts = torch.cat([send_off[:1], send_off[1:] - send_off[:-1]])
+    mine = {
+        "seeds": seeds.cpu().numpy(), "input_nodes": digest_torch(input_nodes), "n_in": int(input_nodes.numel()),
+        "outer_rel": digest_torch(blocks[0].coo_row), "inner_rel": [digest_torch(b.coo_row) for b in blocks[:0:-1]],
+        "perm": digest_torch(perm), "inverse_idx": digest_torch(inv), "recv_counts": counts.numpy(),
+        "bucket_offsets": recv_off.numpy(), "rows_digest": digest_torch(x.view(torch.int32)),
+    }
+    if world > 1:
+        every = [None] * world
+        dist.all_gather_object(every, mine)
+    else:
+        every = [mine]
+    verdict = ["ok"]
+    if rank == 0:
+        want = cpu_path.replay([e["seeds"] for e in every])
+        for r in range(world):
+            g, o = every[r], want[r]
+            checks = {
+                "input_nodes": g["n_in"] == len(o["input_nodes"]) and g["input_nodes"] == digest_np(o["input_nodes"]),
+                "outer_rel": g["outer_rel"] == digest_np(o["outer_rel"]),
+                "inner_rel": g["inner_rel"] == [digest_np(a) for a in o["inner_rel"]],
+                "perm": g["perm"] == digest_np(o["perm"]), "inverse_idx": g["inverse_idx"] == digest_np(o["inverse_idx"]),
+                "recv_counts": np.array_equal(g["recv_counts"], o["recv_counts"]),
+                "bucket_offsets": np.array_equal(g["bucket_offsets"], o["bucket_offsets"]),
+                "rows": g["rows_digest"] == o["rows_digest"],
+            }
+            bad = [k for k, ok in checks.items() if not ok]
+            if bad:
+                verdict[0] = f"rank {r}: {', '.join(bad)} differ from the CPU restatement"
+                break
+    if world > 1:
+        dist.broadcast_object_list(verdict, src=0)
+    if verdict[0] != "ok":
+        raise RuntimeError("parity check of the NP mini-batch failed: " + verdict[0])
+
+    # feature shuffle: the owner's rows are f(node id); forward, each rank gets f(its frontier) in its
+    # own order; backward, what arrives at an owner for the k-th id it received is f(that id)
+    def rows_of(ids, width=16):
+        c = torch.arange(width, device=ids.device, dtype=torch.int64)
+        return ((ids.view(-1, 1) * 31 + c * 7) % 65521).to(torch.float32)
+
+    frontier = blocks[1].src_ids if len(blocks) > 1 else seeds
+    owned = blocks[0].src_ids[:blocks[0].num_dst]                  # sorted unique of what this rank received
+    y = ops.feat_shuffle(ops.rows_gather(rows_of(owned), inv), send_off, recv_off, perm, 16, 1)
+    ok_f = torch.equal(y, rows_of(frontier))
+    gb = ops.feat_shuffle(rows_of(frontier), recv_off, send_off, perm, 16, 0)
+    ok_b = torch.equal(gb, rows_of(owned[inv]))
+    ops.check_status()
+    flags = torch.tensor([int(ok_f), int(ok_b)], device="cuda")
+    if world > 1:
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    if not bool(flags[0]) or not bool(flags[1]):
+        raise RuntimeError(f"parity check of the feature shuffle failed (forward ok: {bool(flags[0])}, "
+                           f"backward ok: {bool(flags[1])})")
+    return {"np_minibatch": "ok", "feat_shuffle": "ok", "ranks": world,
+            "against": "CPU restatement (oracle/) replaying all ranks; blocks, permutation, inverse index and "
+                       "exchange counts bit for bit, gathered rows by 64-bit digest; feature shuffle forward "
+                       "and backward in closed form", "input_rows_rank0": every[0]["n_in"]}
+
+
+# ------------------------------------------------------------- shuffle record
+def shuffle_record(args, rank, world, barrier):
+    """The NPC feature shuffle alone, inside the benchmark run: forward shuffle of the stress shape
+    (495 616 rows of 2 KiB fp16 per GPU) and of the papers-shaped NP run (67 584 rows of 1 KiB fp32),
+    through the peer-to-peer path and through the library all-to-all, next to a peer copy measured in
+    the same run (every rank copies 256 MiB into its right neighbour's inbox with cudaMemcpyAsync)."""
+    import apt_b200  # noqa: F401
+    from apt_b200 import ops
+    from apt_b200.exchange import NcclExchange, P2PExchange
+
+    st = ops.STATE
+    keep = st.exchange
+    n_ids = 1 << 24
+    saved_mv = (st.shuffle_min_vids, st._min_vids_host, st.shuffle_id_offset)
+    ops.register_min_vids(torch.tensor([n_ids * r // world for r in range(world)] + [n_ids]))
+    shapes = {"c4_stress_2KiB_f16": (495_616, 1024, torch.float16), "c1_np_1KiB_f32": (67_584, 256, torch.float32)}
+    need = max(int(2.0 * rows / world * dim * torch.empty(0, dtype=dt).element_size()) + (8 << 20)
+               for rows, dim, dt in shapes.values())
+    p2p = keep if isinstance(keep, P2PExchange) and keep.region_bytes >= need else P2PExchange(st, need)
+    nccl = NcclExchange(st)
+    steps, warm = 10, 3
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    out = {}
+
+    def timed(fn):
+        for _ in range(warm):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda")
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    # peer copy: the denominator, measured here and now
+    copy_bytes = min(256 << 20, p2p.region_bytes)
+    right = (rank + 1) % world
+    copy_ms = timed(lambda: p2p.probe_peer_copy(right, copy_bytes))
+    peer_gbs = copy_bytes / (copy_ms * 1e-3) / 1e9
+    for name, (rows, dim, dt) in shapes.items():
+        row_bytes = dim * torch.empty(0, dtype=dt).element_size()
+        st.exchange = p2p
+        ids = torch.randint(0, n_ids, (rows,), generator=g, device="cuda")
+        recv_ids, perm, send_off, recv_off = ops.shuffle_seeds(ids)
+        x = torch.randn((recv_ids.numel(), dim), generator=g, device="cuda").to(dt)
+        counts = torch.cat([send_off[:1], send_off[1:] - send_off[:-1]])
+        remote = torch.tensor([float((int(counts.sum()) - int(counts[rank])) * row_bytes)], device="cuda")
+        dist.all_reduce(remote, op=dist.ReduceOp.MAX)
+        rec = {"rows_per_gpu": rows, "row_bytes": row_bytes, "remote_bytes_per_gpu": float(remote.item())}
+        for label, ex in (("p2p", p2p), ("nccl", nccl)):
+            st.exchange = ex
+            ms = timed(lambda: ops.feat_shuffle(x, send_off, recv_off, perm, dim, 1))
+            rec[f"{label}_ms"] = round(ms, 4)
+            rec[f"{label}_gbs"] = round(float(remote.item()) / (ms * 1e-3) / 1e9, 1)
+        rec["frac_of_measured_peer_copy"] = round(rec["p2p_gbs"] / peer_gbs, 4)
+        rec["frac_of_900_nominal"] = round(rec["p2p_gbs"] / 900.0, 4)
+        out[name] = rec
+        del x, ids, recv_ids
+    st.exchange = keep
+    ops.check_status()
+    if p2p is not keep:
+        barrier()
+        p2p.close()
+    st.shuffle_min_vids, st._min_vids_host, st.shuffle_id_offset = saved_mv
+    st.generation += 1
+    head = out["c4_stress_2KiB_f16"]
+    return {"gbs": head["p2p_gbs"], "nccl_gbs": head["nccl_gbs"],
+            "frac_of_measured_peer_copy": head["frac_of_measured_peer_copy"],
+            "frac_of_900_nominal": head["frac_of_900_nominal"],
+            "peer_copy_gbs": round(peer_gbs, 1),
+            "peer_copy": f"{copy_bytes >> 20} MiB cudaMemcpyAsync into the right neighbour's inbox, all ranks at once",
+            "unit": "GB/s per GPU and direction, remote rows only", "direction": "forward (rows back to the askers)",
+            "path": "direct placement" if getattr(p2p, "direct", False) else "push + wait + pull", "shapes": out}
+
+
+# ------------------------------------------------------------- SNP with a GAT model
+def run_snp_gat(args, inst, w, rank, world, config, run_info, barrier, reduce_max, phase):
+    """One step = one mini-batch per GPU of the SNP strategy with a GAT first layer
+    (python/npc/sampler.py:215-238, python/npc/model/gatconv.py:89-135): inner hops local, the
+    outermost hop's unique sources travel to their owners, which gather and project their rows
+    (bf16, 4 heads x 64; the projection is a library GEMM), the feature shuffle brings the projected
+    rows back in unique-source order, and the fused edge kernel (u_add_v scores, leaky_relu, edge
+    softmax, weighted sum) produces the layer output of the destination nodes."""
+    import apt_b200
+    from apt_b200 import ops
+
+    heads, head_dim = 4, 64
+    width = heads * head_dim
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    weight = (torch.randn((w.feat_dim, width), generator=gen, device="cuda") / w.feat_dim ** 0.5).bfloat16()
+    attn_l = torch.randn((1, heads, head_dim), generator=gen, device="cuda").bfloat16()
+    attn_r = torch.randn((1, heads, head_dim), generator=gen, device="cuda").bfloat16()
+    sampler = apt_b200.SPGATSampler(rank, w.fanouts)
+    total = args.warmup + args.steps
+    dev_batches = batches_of(inst, total)
+    marks = {}
+
+    def step(seeds, timed=None):
+        def mark(name):
+            if timed is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                timed.append((name, ev))
+
+        mark("start")
+        in_nodes, _, blocks, perm, send_off, recv_off = sampler.sample(None, seeds)
+        mark("sample")
+        x = ops.load_subtensor(in_nodes)
+        mark("gather")
+        b0 = blocks[0]
+        proj = x.bfloat16() @ weight
+        mark("project")
+        ft_src = ops.feat_shuffle(proj[b0.num_dst:].contiguous(), send_off, recv_off, perm, width, 1)
+        mark("feat_shuffle")
+        ft_dst = proj[:b0.num_dst]
+        el = (ft_src.view(-1, heads, head_dim) * attn_l).sum(-1)
+        er = (ft_dst.view(-1, heads, head_dim) * attn_r).sum(-1)
+        out = ops.gat_edge_softmax_sum(b0.coo_row, b0.coo_col, ft_src.view(-1, heads, head_dim), el.contiguous(),
+                                       er.contiguous(), b0.num_dst)
+        mark("gat_block")
+        return out, (in_nodes, blocks, perm, send_off, recv_off, x)
+
+    phase("parity_check")
+    barrier()
+    ops.set_sampling(key=7777777, call_id=0)
+    _, (in_nodes, blocks, perm, send_off, recv_off, x) = step(dev_batches[0])
+    b0 = blocks[0]
+    raw_back = ops.feat_shuffle(x[b0.num_dst:].contiguous(), send_off, recv_off, perm, w.feat_dim, 1)
+    ok = torch.equal(raw_back, ops.load_subtensor(b0.src_ids)) and \
+        torch.equal(in_nodes[:b0.num_dst], blocks[1].src_ids if len(blocks) > 1 else dev_batches[0])
+    flag = torch.tensor([int(ok)], device="cuda")
+    if world > 1:
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if not bool(flag[0]):
+        raise RuntimeError("parity check of the SNP-GAT mini-batch failed: the rows that came back are not the rows "
+                           "of the block's unique sources")
+    ops.check_status()
+
+    phase("warmup")
+    clocks = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    clocks.start()
+    barrier()
+    for b in dev_batches[:args.warmup]:
+        step(b)
+    ops.check_status()
+    phase("timed")
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for b in dev_batches[args.warmup:]:
+        step(b)
+    ev1.record()
+    barrier()
+    ms = reduce_max(ev0.elapsed_time(ev1))
+    phase("profiled")
+    sums, n_prof = {}, min(args.steps, 20)
+    rows_in = edges = 0
+    barrier()
+    for b in dev_batches[args.warmup:args.warmup + n_prof]:
+        timed = []
+        _, (in_nodes, blocks, *_rest) = step(b, timed)
+        torch.cuda.synchronize()
+        for (_, e_a), (name, e_b) in zip(timed[:-1], timed[1:]):
+            sums[name] = sums.get(name, 0.0) + e_a.elapsed_time(e_b)
+        rows_in += int(in_nodes.numel())
+        edges += int(blocks[0].coo_row.numel())
+    clock_info = clocks.stop()
+    ops.check_status()
+    line = {
+        "metric": METRIC, "value": world * args.steps / (ms / 1000.0), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int64 ids, f32 rows gathered, bf16 projected rows",
+        "data": "synthetic", "config": dict(config, strategy="SNP with a GAT first layer (4 heads x 64, bf16)"),
+        "run_info": run_info, "clocks": clock_info,
+        "launch_mode": "kernels enqueued one by one, one host read per operator",
+        "parity_check": {"snp_gat_minibatch": "ok", "ranks": world,
+                         "against": "closed form: rows shuffled back equal the gathered rows of the block's sources"},
+        "per_step": {"input_rows": rows_in / n_prof, "outer_block_edges": edges / n_prof,
+                     "stage_ms": {k: round(v / n_prof, 4) for k, v in sums.items()}},
+    }
+    return line
+
+
 # ------------------------------------------------------------------------- main
 PHASE = ["setup"]     # the part of the run an exception came from
 
@@ -658,19 +985,34 @@ def run():
     setup_s = time.time() - t_setup
     esz = inst.host_feats.element_size()
     row_bytes = w.feat_dim * esz
+    cache_gb = inst.info["num_cached_rows"] * row_bytes / 1e9
     config = {
         "workload": w.name, "num_nodes": w.num_nodes, "num_edges": w.num_edges, "csc_edges": inst.info["num_csc_edges"],
         "feat_dim": w.feat_dim, "feat_dtype": w.dtype, "cached_rows_per_gpu": inst.info["num_cached_rows"],
-        "cache_policy": f"top {w.cache_frac:.0%} rows by in-degree", "fanout": w.fanouts, "seeds_per_gpu": w.batch,
-        "strategy": "NP (outermost hop sampled at the owner, random contiguous partition)",
+        "cache_policy": (f"top {w.cache_frac:.0%} rows by in-degree" if w.cache_bytes is None else
+                         f"{cache_gb:.1f} GB of rows by falling in-degree"),
+        "fanout": w.fanouts, "seeds_per_gpu": w.batch,
+        "seeds": "uniform over a seeded training split" if w.seed_dist == "uniform" else
+                 f"Zipf({w.zipf_s}) over the rank by in-degree, distinct within a batch",
+        "strategy": "NP (outermost hop sampled at the owner)",
+        "partition": "random contiguous ranges" if w.partition == "random" else
+                     "contiguous ranges of a breadth-first order from a seeded root: "
+                     f"{inst.info['intra_partition_edge_share']:.1%} of the edges inside a part over "
+                     f"{inst.info['partition_parts_measured']} parts (random ranges: "
+                     f"{inst.info['intra_partition_edge_share_random']:.1%})",
         "topology": "int64 CSC resident in HBM", "host_features": "pinned host memory read by the gather kernel",
-        "l2": "inputs (CSC 13.7 GB, feature tables) exceed the 126 MB L2; every step touches other rows",
+        "l2": f"inputs (CSC {inst.info['num_csc_edges'] * 8 / 1e9:.1f} GB, feature tables) exceed the 126 MB L2; "
+              "every step touches other rows",
     }
+    if "host_rows" in inst.info:
+        config["host_table"] = (f"{inst.info['host_rows']} rows: the full table of {w.num_nodes * row_bytes / 1e9:.0f} GB "
+                                "does not fit host memory, features repeat with that period; bytes per row, miss "
+                                "rate and access pattern are those of the full table")
     run_info = {"setup_s": round(setup_s, 1), "shuffle_backend": ops.STATE.shuffle_backend if ws_eff > 1 else "local"}
 
     if args.impl == "reference":
         cpu = CpuPath(inst)
-        seeds = [b.cpu().numpy() for b in batches_of(inst.train_ids, w.batch, args.warmup + args.steps)]
+        seeds = [b.cpu().numpy() for b in batches_of(inst, args.warmup + args.steps)]
         rate, dt, rows = cpu.time(seeds, warmup=args.warmup)
         line = {
             "impl": "reference", "metric": METRIC, "value": rate, "unit": UNIT, "n_gpus": args.gpus,
@@ -687,13 +1029,22 @@ def run():
 
     sampler = apt_b200.MixedNeighborSampler(rank, w.fanouts)
     total = args.warmup + args.steps
-    dev_batches = batches_of(inst.train_ids, w.batch, total)
-    host_batches = [b.cpu().pin_memory() for b in batches_of(inst.train_ids, w.batch, total, offset=total)]
+    dev_batches = batches_of(inst, total)
+    host_batches = [b.cpu().pin_memory() for b in batches_of(inst, total, offset=total)]
 
     def step(seeds):
         sample = sampler.sample(None, seeds)
         x = ops.load_subtensor(sample[0])
         return sample, x
+
+    def run_steps(batches, after=None):
+        """One step per batch through the sampler's pipelined iterator (the next mini-batch is already
+        on the GPU while the previous one is read back, like a prefetching loader around the
+        reference's sampler) and load_subtensor; after(k, sample, rows) runs behind every step."""
+        for k, sample in enumerate(sampler.sample_iter(None, batches)):
+            x = ops.load_subtensor(sample[0])
+            if after is not None:
+                after(k, sample, x)
 
     def barrier():
         torch.cuda.synchronize()
@@ -718,6 +1069,15 @@ def run():
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         return float(t.item())
 
+    if w.system == "SP":
+        line = run_snp_gat(args, inst, w, rank, world, config, run_info, barrier, reduce_max, phase)
+        if rank == 0:
+            print(json.dumps(line))
+        synthetic.cleanup(inst)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
     # ---- device-resident run ------------------------------------------------
     ops.set_sampling(key=7777777, call_id=0)
     clocks = ClockSampler(local_rank)
@@ -726,16 +1086,14 @@ def run():
     # length (registering the host table, stopping the clock sampler) must not eat into the wait bound
     phase("warmup")
     barrier()
-    for b in dev_batches[:args.warmup]:
-        step(b)
+    run_steps(dev_batches[:args.warmup])
     ops.check_status()
     phase("timed")
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     torch.cuda.nvtx.range_push("apt_timed")
     ev0.record()
-    for b in dev_batches[args.warmup:]:
-        step(b)
+    run_steps(dev_batches[args.warmup:])
     ev1.record()
     torch.cuda.nvtx.range_pop()
     barrier()
@@ -750,9 +1108,7 @@ def run():
     marks = [torch.cuda.Event(enable_timing=True) for _ in range(n_spread + 1)]
     barrier()
     marks[0].record()
-    for k, b in enumerate(dev_batches[args.warmup:args.warmup + n_spread]):
-        step(b)
-        marks[k + 1].record()
+    run_steps(dev_batches[args.warmup:args.warmup + n_spread], after=lambda k, sample, x: marks[k + 1].record())
     barrier()
     per_step = sorted(marks[k].elapsed_time(marks[k + 1]) for k in range(n_spread))
     spread = {"steps": n_spread, "median": per_step[n_spread // 2], "p10": per_step[n_spread // 10],
@@ -800,19 +1156,17 @@ def run():
     peak, peak_kind = peaks()
     hit_ms, hit_n = stage_ms["gather_hit"]
     miss_ms, miss_n = stage_ms["gather_miss"]
-    # algorithmic bytes of one launch of the hit kernel: an id and a position-map entry per requested row
-    # (16 bytes), and every cached row once in and once out
-    hit_bytes = (hits_total * 2 * row_bytes + rows_total * 16) / max(hit_n, 1)
+    # algorithmic bytes of one launch of the hit kernel: each cached row once in and once out, plus the
+    # 8-byte position of every requested row
+    hit_bytes = (hits_total * 2 * row_bytes + rows_total * 8) / max(hit_n, 1)
     hit_gbs = hit_bytes / (hit_ms / max(hit_n, 1) * 1e-3) / 1e9 if hit_ms > 0 else 0.0
-    roofline = {"kernel": "k_gather_hits (gather: decode + copy of the cache hits)", "bound": "hbm",
+    roofline = {"kernel": "k_copy_hits (gather, cache hits)", "bound": "hbm",
                 "achieved": round(hit_gbs, 1), "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                 "frac": round(hit_gbs / peak, 4),
                 "traffic": round(hit_bytes * HIT_DRAM_BYTES_PER_ALGORITHMIC_BYTE)
                 if HIT_DRAM_BYTES_PER_ALGORITHMIC_BYTE else None,
                 "traffic_source": HIT_TRAFFIC_SOURCE,
-                "measured_in": "the pass that enqueues the kernels one by one with an event pair around each "
-                               "(one launch over all input rows of the mini-batch; the graph replay of the headline "
-                               "splits the same rows into two launches of this kernel)",
+                "measured_in": "the pass that enqueues the kernels one by one with an event pair around each",
                 "rows_per_launch": rows_total / max(hit_n, 1),
                 "hit_rows_per_launch": hits_total / max(hit_n, 1), "us_per_launch": 1000.0 * hit_ms / max(hit_n, 1)}
     miss_bytes = miss_total * row_bytes / max(miss_n, 1)
@@ -839,28 +1193,55 @@ def run():
                      "us_per_launch": 1000.0 * miss_ms / max(miss_n, 1)}
 
     # ---- end to end through host buffers --------------------------------------
-    def e2e_step(host_seeds):
-        seeds = host_seeds.to("cuda", non_blocking=True)
-        sample, x = step(seeds)
-        digest = torch.cat([x[0], x[-1]]).float().cpu()      # device -> host read of the step's result
-        return digest
+    # Every step copies its seeds from pinned host memory and reads a digest of the gathered rows (and,
+    # inside the sampler, the 2 KiB block of counts) back into pinned host memory. The digest of step k
+    # is looked at once step k + 1 has been enqueued, so that the read does not drain the GPU.
+    digests = [torch.empty(2 * w.feat_dim, dtype=torch.float32).pin_memory() for _ in range(2)]
+    digest_done = [torch.cuda.Event(), torch.cuda.Event()]
+    checksum = [0.0]
+
+    def e2e_run(host_seed_batches):
+        def read_back(k, sample, x):
+            digests[k % 2].copy_(torch.cat([x[0], x[-1]]).float(), non_blocking=True)   # device -> host
+            digest_done[k % 2].record()
+            if k >= 1:
+                digest_done[(k - 1) % 2].synchronize()
+                checksum[0] += float(digests[(k - 1) % 2][0])
+        n = len(host_seed_batches)
+        run_steps((b.to("cuda", non_blocking=True) for b in host_seed_batches), after=read_back)   # host -> device
+        if n:
+            digest_done[(n - 1) % 2].synchronize()
+            checksum[0] += float(digests[(n - 1) % 2][0])
 
     phase("e2e")
     barrier()
-    for b in host_batches[:args.warmup]:
-        e2e_step(b)
+    e2e_run(host_batches[:args.warmup])
     barrier()
     ev0.record()
-    for b in host_batches[args.warmup:]:
-        e2e_step(b)
+    e2e_run(host_batches[args.warmup:])
     ev1.record()
     barrier()
     ms_e2e = reduce_max(ev0.elapsed_time(ev1))
     e2e = {"value": world * args.steps / (ms_e2e / 1000.0), "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
            "h2d_bytes_per_step": w.batch * 8, "d2h_bytes_per_step": 2 * w.feat_dim * 4 + 64 * 4,
            "note": "seeds come from pinned host memory; a digest (first and last gathered row) and the per-hop "
-                   "unique counts are read back; the gathered rows stay on the GPU for the model"}
+                   "unique counts are read back into pinned host memory every step; the gathered rows stay on the "
+                   "GPU for the model"}
     ops.check_status()
+
+    # ---- parity of this very configuration, outside every timed region ----------------------
+    phase("parity_check")
+    cpu_path = None
+    if rank == 0:
+        cpu_path = CpuPath(inst)
+    parity = parity_check(inst, w, rank, world, cpu_path, barrier)
+
+    # ---- the feature shuffle alone (N >= 2): GB/s per GPU and direction over NVLink ----------
+    shuffle = None
+    if world > 1:
+        phase("shuffle")
+        barrier()
+        shuffle = shuffle_record(args, rank, world, barrier)
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -868,20 +1249,24 @@ def run():
         "dtype": "int64 ids, " + w.dtype + " rows", "data": "synthetic", "config": config, "run_info": run_info,
         "clocks": clock_info,
         "e2e": e2e, "gpu_launches": int(reduce_sum(launches)),
-        "launch_mode": "one CUDA graph replay per mini-batch" if graph_mode else
+        "launch_mode": "one CUDA graph replay per mini-batch, the next one enqueued before the previous one is "
+                       "read back" if graph_mode else
                        "kernels enqueued one by one, sizes chained on the device",
         "step_ms_spread": spread,
         "profiled_value": world * args.steps / (ms_prof / 1000.0),
-        "roofline": roofline, "roofline_link": roofline_link,
+        "roofline": roofline, "roofline_link": roofline_link, "parity_check": parity,
         "per_step": {"gathered_rows": rows_total / args.steps, "cache_hit_rate": hits_total / max(rows_total, 1),
                      "gather_gb": rows_total / args.steps * row_bytes / 1e9,
                      "stage_ms": {k: round(v[0] / args.steps, 4) for k, v in stage_ms.items()},
                      "stage_launches": {k: v[1] / args.steps for k, v in stage_ms.items()}},
     }
 
+    if shuffle is not None:
+        line["shuffle"] = shuffle
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu = CpuPath(inst)
-        seeds = [b.cpu().numpy() for b in batches_of(inst.train_ids, w.batch, args.cpu_batches + 1)]
+        phase("cpu_baseline")
+        cpu = cpu_path
+        seeds = [b.cpu().numpy() for b in batches_of(inst, args.cpu_batches + 1)]
         rate, dt, rows = cpu.time(seeds, warmup=1)
         line["cpu_baseline"] = {"value": rate, "unit": UNIT, "cores": cpu.cores, "kind": "port",
                                 "sample": f"{args.cpu_batches} mini-batches of {w.batch} seeds on the full graph "

@@ -75,7 +75,8 @@ int apt_profile_read(const char* tag, double* total_ms, int64_t* launches);
  *   gather_miss_mode   0 16-byte ld.global.nc loads (default),
  *                      1 bulk copies (cp.async.bulk) staged through shared memory
  *   gather_miss_blocks blocks of the miss-copy kernel (default 148)
- *   gather_hit_rows    rows in flight per warp of the hit copy, 8 (default, rows of up to 1 KiB) or 4
+ *   gather_hit_mode    0 register-staged 16-byte vector copy of the cache hits (default),
+ *                      1 bulk copies (cp.async.bulk) staged through shared memory
  *   relabel_small      1 (default): layers of up to 8192 items are relabelled by one block with
  *                      the hash table in shared memory; 0: always the multi-block path */
 int apt_set_tunable(const char* name, int64_t value);
@@ -219,8 +220,8 @@ int apt_unique_sorted(const int64_t* ids, int64_t num_ids,
  *   p == -1: out[r] = 0 and APT_FLAG_FEAT_NOT_EXIST (the reference reads out
  *            of bounds here)
  * Rows are opaque bytes, so fp32/bf16/fp16 tables share the code.
- * Two kernels on `stream`: one that decodes p, queues the misses and copies the
- * hits out of the HBM cache, and the miss copy over the host link.
+ * Three kernels on `stream`: classify (decode p, compact the miss list), the
+ * hit copy out of the HBM cache and the miss copy over the host link.
  * workspace: apt_gather_workspace_bytes(num_rows) bytes; needs no initialisation.
  * apt_gather_rows_from only produces output rows [*first_row_dev, num_rows) (a
  * device word; NULL: 0): a caller that already holds the leading rows, e.g. the
@@ -523,6 +524,11 @@ int apt_p2p_wait(apt_p2p* ctx, int64_t* out_recv_counts, int32_t* status_word,
 /* The default bound above in nanoseconds, and whether a wait of this context
  * has timed out (synchronous 4-byte read of the inbox header). */
 int64_t apt_p2p_default_timeout_ns(void);
+/* Measurement aid: one cudaMemcpyAsync of nbytes (at most one region) from this
+ * rank's inbox into the same place of `peer`'s inbox, i.e. a plain copy over the
+ * link the exchange uses; gives the link rate a shuffle is compared with. It
+ * overwrites inbox data, so no exchange may be in flight. */
+int apt_p2p_probe_copy(apt_p2p* ctx, int peer, size_t nbytes, void* stream);
 int apt_p2p_poisoned(apt_p2p* ctx, int* out_poisoned);
 /* Copy received rows out of the inbox in peer order (peer 0's rows first).
  * If dst_index is NULL row j of the concatenation lands at dst row j; else if
@@ -590,6 +596,11 @@ int apt_p2p_alltoall_fused(apt_p2p* ctx, const void* src, const int64_t* src_ind
 int apt_rmat_edges(uint64_t seed, int64_t first_edge, int64_t num_edges,
                    int scale, int64_t num_nodes, float a, float b, float c,
                    int64_t* out_src, int64_t* out_dst, void* stream);
+/* Zipf(s) ranks in [1, num_ranks] for skewed seed streams: draw i is
+ * floor((1 + u ((N+1)^(1-s) - 1))^(1/(1-s))) with u from Philox keyed by `seed`
+ * at counter first_draw + i (rank k has the mass of x^-s over [k, k+1)). */
+int apt_zipf_ranks(uint64_t seed, int64_t first_draw, int64_t num_draws,
+                   int64_t num_ranks, double s, int64_t* out, void* stream);
 /* Ascending radix sort (cub) of the low `end_bit` bits of uint64 keys from
  * keys_in into keys_out. temp: apt_sort_u64_temp_bytes(n) bytes. */
 size_t apt_sort_u64_temp_bytes(int64_t n);

@@ -800,3 +800,80 @@ def csc_from_edges(src, dst, num_nodes, add_self_loops=True):
     indptr = np.zeros(num_nodes + 1, dtype=I64)
     np.cumsum(np.bincount(d, minlength=num_nodes), out=indptr[1:])
     return indptr, indices
+
+
+# ------------------------------------------------- locality partition / skewed seeds
+def bfs_order(indptr, indices, root):
+    """Breadth-first visiting order over the in-neighbour lists of a CSC graph from `root`:
+    level by level, ascending ids inside a level; nodes the search does not reach follow in
+    ascending id order. Stands in for the partitioner of the reference's preprocessing
+    (scripts/preprocess_dataset.py:76-135 calls METIS through DGL and then renumbers every
+    part contiguously): contiguous blocks of this order are the locality-preserving partition
+    of the synthetic graphs. Returns order with order[k] = the node visited k-th."""
+    indptr = np.asarray(indptr, dtype=I64)
+    indices = np.asarray(indices, dtype=I64)
+    n = len(indptr) - 1
+    visited = np.zeros(n, dtype=bool)
+    order = np.empty(n, dtype=I64)
+    frontier = np.array([root], dtype=I64)
+    visited[root] = True
+    pos = 0
+    while len(frontier):
+        order[pos:pos + len(frontier)] = frontier
+        pos += len(frontier)
+        mark = np.zeros(n, dtype=bool)
+        for v in frontier:
+            mark[indices[indptr[v]:indptr[v + 1]]] = True
+        mark &= ~visited
+        frontier = np.nonzero(mark)[0].astype(I64)
+        visited |= mark
+    order[pos:] = np.nonzero(~visited)[0]
+    return order
+
+
+def relabel_graph(indptr, indices, order):
+    """The CSC after renumbering node order[k] to k (what dgl.reorder_graph does in
+    scripts/preprocess_dataset.py:128-130): in-neighbour lists sorted by new source id."""
+    indptr = np.asarray(indptr, dtype=I64)
+    indices = np.asarray(indices, dtype=I64)
+    n = len(indptr) - 1
+    new_id = np.empty(n, dtype=I64)
+    new_id[order] = np.arange(n, dtype=I64)
+    dst = new_id[np.repeat(np.arange(n, dtype=I64), np.diff(indptr))]
+    src = new_id[indices]
+    key = np.lexsort((src, dst))
+    counts = np.bincount(dst, minlength=n)
+    return np.concatenate([[0], np.cumsum(counts)]).astype(I64), src[key]
+
+
+def intra_partition_edge_share(indptr, indices, min_vids):
+    """Share of edges whose two endpoints have the same owner (contiguous ranges min_vids)."""
+    indptr = np.asarray(indptr, dtype=I64)
+    n = len(indptr) - 1
+    cuts = np.asarray(min_vids, dtype=I64)[1:-1]
+    dst_owner = np.searchsorted(cuts, np.repeat(np.arange(n, dtype=I64), np.diff(indptr)), side="right")
+    src_owner = np.searchsorted(cuts, np.asarray(indices, dtype=I64), side="right")
+    return float((dst_owner == src_owner).mean()) if len(indices) else 1.0
+
+
+def zipf_ranks(seed, first_draw, num_draws, num_ranks, s):
+    """Ranks in [1, num_ranks], rank k with the mass of x^-s over [k, k+1): the inverse of that
+    integral at u = (53 bits + 0.5) / 2^53, bits from words 0 and 1 of Philox4x32-10 with counter
+    (draw, draw >> 32, 0, 'zipf') keyed by `seed` (twin of apt_zipf_ranks)."""
+    d = np.arange(first_draw, first_draw + num_draws, dtype=U64)
+    w = philox4x32_10(d & _MASK, d >> U64(32), 0, 0x7A697066, seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
+    bits = ((w[0].astype(U64) << U64(32)) | w[1].astype(U64)) >> U64(11)
+    u = (bits.astype(np.float64) + 0.5) * (1.0 / 9007199254740992.0)
+    e = 1.0 - float(s)
+    span = np.power(float(num_ranks) + 1.0, e) - 1.0
+    k = np.floor(np.power(1.0 + u * span, 1.0 / e)).astype(I64)
+    return np.clip(k, 1, num_ranks)
+
+
+def zipf_seeds(seed, first_draw, num_draws, degree_order, s, batch):
+    """`batch` distinct seed nodes: Zipf(s) ranks over `degree_order` (node ids by falling
+    in-degree, ties by id), duplicates dropped keeping the first occurrence."""
+    ranks = zipf_ranks(seed, first_draw, num_draws, len(degree_order), s)
+    ids = np.asarray(degree_order, dtype=I64)[ranks - 1]
+    _, first = np.unique(ids, return_index=True)
+    return ids[np.sort(first)][:batch]

@@ -136,6 +136,42 @@ def test_frontier_rows_gathered_beside_the_outermost_hop(use_graph):
     ops.check_status()
 
 
+def test_pipelined_iterator_equals_one_sample_per_batch():
+    """sample_iter enqueues mini-batch k + 1 before it reads mini-batch k back; the tensors it hands
+    out are those of sample(), batch by batch, and stay valid while the next batch is in flight."""
+    n, indptr, indices = small_graph(scale=12, edge_factor=8)
+    install_graph(indptr, indices)
+    reset_world(1, 0)
+    ops.register_min_vids(torch.tensor([0, n]))
+    rng = np.random.default_rng(33)
+    feats, uva, devf, cached_idx, local_idx, pos_map, cpu_map = feature_setup(n, 32, 0.5, rng)
+    ops.cache_feats_shared(n, torch.from_numpy(uva).pin_memory(), dev(devf), torch.from_numpy(cached_idx),
+                           torch.from_numpy(local_idx), 0)
+    batches = [dev(rng.permutation(n)[:150].astype(I64)) for _ in range(5)]
+
+    def snapshot(res, x):
+        return (host(res[0]), host(res[2][0].coo_row), host(res[2][1].coo_row), host(res[3]), host(res[6]),
+                res[4].clone().numpy(), host(x))
+
+    ops.set_sampling(key=5150, call_id=2)
+    plain = apt_b200.MixedNeighborSampler(0, [7, 3], chained=False)
+    want = []
+    for b in batches:
+        res = plain.sample(None, b)
+        want.append(snapshot(res, ops.load_subtensor(res[0])))
+    ops.set_sampling(key=5150, call_id=2)
+    piped = apt_b200.MixedNeighborSampler(0, [7, 3], chained=True, use_graph=True)
+    got = []
+    for res in piped.sample_iter(None, iter(batches)):
+        got.append(snapshot(res, ops.load_subtensor(res[0])))      # the next batch is already in flight here
+    assert len(got) == len(want)
+    for g_, w_ in zip(got, want):
+        for a, b in zip(g_, w_):
+            assert np.array_equal(a, b)
+    assert apt_b200.STATE.sample_calls == 2 + 2 * len(batches)
+    ops.check_status()
+
+
 def test_gather_rows_from_a_device_side_first_row():
     rng = np.random.default_rng(4)
     n = 3000

@@ -1,5 +1,9 @@
-"""GPU parity of SpMM / SDDMM over sampled blocks against the fp64 CPU oracle:
-1e-5 relative for fp32, 1e-2 for bf16/fp16."""
+"""GPU parity of SpMM / SDDMM over sampled blocks against the fp64 CPU oracle: 1e-5 for fp32, 1e-2 for
+bf16/fp16. SDDMM (no summation) is held to the plain relative error |got - want| <= tol * |want|. A sum is
+held to |got - want| <= tol * (sum of the |terms|), the error bound of floating-point summation: equal to
+the relative error where the terms do not cancel, and the most any fp32 summation can promise where they
+do (the reference's own float-atomic sums of N(0,1) terms are off by up to 1e-4 relative at small outputs,
+tests/test_ref_golden.py)."""
 import numpy as np
 import pytest
 import torch
@@ -11,14 +15,22 @@ from tests.gpu_util import dev, host
 pytestmark = pytest.mark.gpu
 I64 = np.int64
 TOL = {torch.float32: 1e-5, torch.bfloat16: 1e-2, torch.float16: 1e-2}
+# absolute floor of the relative error: the smallest normal number of the type (below it the spacing
+# of representable values is fixed, so the error no longer shrinks with the value)
+FLOOR = {torch.float32: 1.2e-38, torch.bfloat16: 1.2e-38, torch.float16: 6.2e-5}
 
 
-def _close(got, want, dtype):
+def _close(got, want, dtype, magnitude=None):
+    """magnitude: the same operator applied to the absolute values of its inputs (sums); None: no sum."""
     got = host(got).astype(np.float64)
     tol = TOL[dtype]
-    scale = np.maximum(np.abs(want), 1.0)
-    err = np.abs(got - want) / scale
-    assert err.max() <= tol, f"max rel err {err.max():.3e} > {tol}"
+    scale = np.abs(want) if magnitude is None else magnitude
+    err = np.abs(got - want) / np.maximum(scale, FLOOR[dtype])
+    assert err.max() <= tol, f"max err {err.max():.3e} of the scale > {tol}"
+
+
+def _mag(op, row, col, x, e, *off):
+    return orc.spmm_sum(op, row, col, None if x is None else np.abs(x), None if e is None else np.abs(e), *off)
 
 
 def _block(S, f, n_src, rng):
@@ -42,7 +54,7 @@ def test_copy_u_sum_sorted_block(dtype, S, f, D):
     out = ops.spmm_copy_u_sum(dev(row), dev(col), dev(x, dtype), dev(off[0]), dev(off[1]), dev(off[2]))
     want = orc.spmm_sum("copy_u", row, col, x, None, *off)
     assert out.dtype == dtype and tuple(out.shape) == (S, D)
-    _close(out, want, dtype)
+    _close(out, want, dtype, _mag("copy_u", row, col, x, None, *off))
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -57,12 +69,9 @@ def test_copy_u_sum_unsorted_backward_shape(dtype):
     out = ops.spmm_copy_u_sum(dev(col), dev(row), dev(g, dtype), dev(off[0]), dev(off[1]), dev(off[2]))
     want = orc.spmm_sum("copy_u", col, row, g, None, *off)
     assert tuple(out.shape) == (n_src, D)
-    if dtype == torch.float32:
-        _close(out, want, dtype)
-    else:
-        # bf16 atomics round at every add; rows gather many terms, so the bound is looser
-        got = host(out).astype(np.float64)
-        assert np.abs(got - want).max() <= 0.05 * max(1.0, np.abs(want).max())
+    # rows that receive no edge are exactly zero; the others are summed in fp32 and rounded once
+    _close(out, want, dtype, np.maximum(_mag("copy_u", col, row, g, None, *off), 1e-30))
+    assert not host(out)[np.bincount(row, minlength=n_src) == 0].any()
 
 
 @pytest.mark.parametrize("grouped", [True, False])
@@ -80,11 +89,7 @@ def test_hub_rows_with_thousands_of_edges(grouped, dtype):
     assert np.bincount(col).max() > 5000
     out = ops.spmm_copy_u_sum(dev(row), dev(col), dev(x, dtype), dev(off[0]), dev(off[1]), dev(off[2]))
     want = orc.spmm_sum("copy_u", row, col, x, None, *off)
-    got = host(out).astype(np.float64)
-    # sums of thousands of terms: the bound is relative to the sum of magnitudes (fp32 accumulation)
-    scale = np.maximum(orc.spmm_sum("copy_u", row, col, np.abs(x), None, *off), 1.0)
-    tol = 1e-5 if dtype == torch.float32 else 1e-2
-    assert (np.abs(got - want) / scale).max() <= tol
+    _close(out, want, dtype, _mag("copy_u", row, col, x, None, *off))
 
 
 def test_empty_rows_and_empty_edges():
@@ -115,7 +120,8 @@ def test_segments_batched_blocks():
     ooff = np.concatenate([[0], np.cumsum(sizes_out)]).astype(I64)
     x = rng.standard_normal((sum(sizes_in), D)).astype(np.float32)
     out = ops.spmm_copy_u_sum(dev(row), dev(col), dev(x), dev(coo), dev(ioff), dev(ooff))
-    _close(out, orc.spmm_sum("copy_u", row, col, x, None, coo, ioff, ooff), torch.float32)
+    _close(out, orc.spmm_sum("copy_u", row, col, x, None, coo, ioff, ooff), torch.float32,
+           _mag("copy_u", row, col, x, None, coo, ioff, ooff))
     lhs = rng.standard_normal((sum(sizes_in), D)).astype(np.float32)
     rhs = rng.standard_normal((sum(sizes_out), D)).astype(np.float32)
     for name, fn in (("u_add_v", ops.sddmm_u_add_v), ("u_mul_v", ops.sddmm_u_mul_v)):
@@ -135,16 +141,16 @@ def test_copy_e_and_u_mul_e(dtype):
     e_full = _round(rng.standard_normal((S * f, D)).astype(np.float32), dtype)
     e_head = _round(rng.random((S * f, H)).astype(np.float32), dtype)
     out = ops.spmm_copy_e_sum(dev(row), dev(col), dev(e_full, dtype), dev(off[0]), dev(off[2]))
-    _close(out, orc.spmm_sum("copy_e", row, col, None, e_full, *off), dtype)
+    _close(out, orc.spmm_sum("copy_e", row, col, None, e_full, *off), dtype, _mag("copy_e", row, col, None, e_full, *off))
     out = ops.spmm_u_mul_e_sum(dev(row), dev(col), dev(x, dtype), dev(e_full, dtype), *[dev(o) for o in off])
-    _close(out, orc.spmm_sum("u_mul_e", row, col, x, e_full, *off), dtype)
+    _close(out, orc.spmm_sum("u_mul_e", row, col, x, e_full, *off), dtype, _mag("u_mul_e", row, col, x, e_full, *off))
     # one attention weight per head, broadcast over the head's columns (GAT, python/npc/model/gatconv.py:124)
     out = ops.spmm_u_mul_e_sum(dev(row), dev(col), dev(x, dtype), dev(e_head, dtype), *[dev(o) for o in off])
-    _close(out, orc.spmm_sum("u_mul_e", row, col, x, e_head, *off), dtype)
+    _close(out, orc.spmm_sum("u_mul_e", row, col, x, e_head, *off), dtype, _mag("u_mul_e", row, col, x, e_head, *off))
     # what the reference's kernel really computes (src/cuda/spmm.cu:78)
     out = ops.spmm_u_mul_e_sum(dev(row), dev(col), dev(x, dtype), dev(e_full, dtype), *[dev(o) for o in off],
                                ref_quirk_add=True)
-    _close(out, orc.spmm_sum("u_add_e", row, col, x, e_full, *off), dtype)
+    _close(out, orc.spmm_sum("u_add_e", row, col, x, e_full, *off), dtype, _mag("u_add_e", row, col, x, e_full, *off))
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])

@@ -70,3 +70,64 @@ def test_install_tiny_workload_structure():
     assert torch.equal(x.cpu(), inst.host_feats[cached[:1000]])
     assert inst.train_ids.numel() >= w.batch and int(inst.train_ids.max()) < n
     ops.check_status()
+
+
+@pytest.mark.parametrize("scale,n,edges,root", [(9, 500, 4000, 7), (12, 4096, 30000, 0), (13, 8000, 20000, 4321)])
+def test_bfs_order_and_renumbered_graph_match_oracle(scale, n, edges, root):
+    # the locality-preserving partition: breadth-first order, renumbering, share of edges inside a part
+    src, dst = orc.rmat_edges(3, 0, edges, scale, n)
+    indptr, indices = orc.csc_from_edges(src, dst, n)
+    ip, ix = torch.from_numpy(indptr).cuda(), torch.from_numpy(indices).cuda()
+    for chunk in (1 << 27, 997):                         # the second forces the frontier to be expanded in pieces
+        order = synthetic.bfs_order(ip, ix, root, edge_chunk=chunk)
+        want = orc.bfs_order(indptr, indices, root)
+        assert np.array_equal(host(order), want)
+    assert sorted(host(order).tolist()) == list(range(n)) and int(order[0]) == root
+    nip, nix = synthetic.relabel_graph(ip, ix, order)
+    wip, wix = orc.relabel_graph(indptr, indices, want)
+    assert np.array_equal(host(nip), wip) and np.array_equal(host(nix), wix)
+    mv = synthetic.partition_min_vids(n, 4)
+    share = synthetic.intra_partition_edge_share(nip, nix, mv)
+    assert abs(share - orc.intra_partition_edge_share(wip, wix, mv.numpy())) < 1e-12
+    assert share > synthetic.intra_partition_edge_share(ip, ix, mv)        # locality gained over the random ids
+
+
+@pytest.mark.parametrize("num_ranks,s", [(1000, 1.1), (100_000_000, 1.1), (50, 2.0)])
+def test_zipf_ranks_match_oracle(num_ranks, s):
+    m = 200_000
+    out = torch.empty(m, dtype=torch.int64, device="cuda")
+    check(lib.apt_zipf_ranks(9, 12345, m, num_ranks, s, out.data_ptr(), None))
+    want = orc.zipf_ranks(9, 12345, m, num_ranks, s)
+    got = host(out)
+    assert got.min() >= 1 and got.max() <= num_ranks
+    assert np.array_equal(got, want)
+    # rank 1 is the most likely, and the frequencies fall like k^-s
+    c = np.bincount(got, minlength=6)
+    assert c[1] > c[2] > c[3] > c[5]
+    assert abs(c[1] / c[2] - (1 - 2 ** (1 - s)) / (2 ** (1 - s) - 3 ** (1 - s))) < 0.1
+
+
+def test_install_stress_and_locality_miniatures():
+    ops.init(0, 0, 1, ops.nccl_get_unique_id(), 1)
+    w = synthetic.WORKLOADS["tiny_stress"]
+    inst = synthetic.install(w)
+    n, R = w.num_nodes, inst.info["host_rows"]
+    assert R == 5000 and inst.host_feats.shape[0] == R and inst.info["num_cached_rows"] == 6000
+    batches = synthetic.seed_batches(inst, 3)
+    order = host(inst.degree_order)
+    for k, b in enumerate(batches):
+        want = orc.zipf_seeds(w.train_seed, k * 4 * w.batch, 4 * w.batch, order, w.zipf_s, w.batch)
+        assert np.array_equal(host(b), want) and len(np.unique(want)) == w.batch
+    # every node has a row: its own period-R row, from the cache or from host memory
+    ids = torch.cat([batches[0], torch.arange(n - 50, n, device="cuda")])
+    x = ops.load_subtensor(ids)
+    assert torch.equal(x.cpu(), inst.host_feats[(ids % R).cpu()])
+    ops.check_status()
+    synthetic.cleanup(inst)
+
+    w2 = synthetic.WORKLOADS["tiny_snp_gat"]
+    inst2 = synthetic.install(w2)
+    assert inst2.info["intra_partition_edge_share"] > inst2.info["intra_partition_edge_share_random"]
+    indptr, indices = host(inst2.indptr), host(inst2.indices)
+    assert np.diff(indptr).min() >= 1 and all(v in indices[indptr[v]:indptr[v + 1]] for v in (0, 5, w2.num_nodes - 1))
+    synthetic.cleanup(inst2)

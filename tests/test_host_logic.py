@@ -24,11 +24,19 @@ def test_partition_and_batches():
 
     mv = synthetic.partition_min_vids(103, 4)
     assert mv.tolist() == [0, 25, 50, 75, 103]
-    ids = torch.arange(1000)
-    bs = bench.batches_of(ids, 64, 40)
-    assert all(b.numel() == 64 for b in bs) and bs[0][0] == 0 and bs[1][0] == 64
     w = synthetic.WORKLOADS["c1_papers_np"]
     assert w.scale == 27 and w.fanouts == [15, 10, 5] and w.batch == 1024
+    small = synthetic.Workload("x", 1000, 1000, 8, "f32", 0.1, [2], 64, 8, 0.1)
+    inst = synthetic.Installed(small, 0, 1, None, None, mv, None, None, torch.arange(1000))
+    bs = bench.batches_of(inst, 40)
+    assert all(b.numel() == 64 for b in bs) and bs[0][0] == 0 and bs[1][0] == 64
+    assert bench.batches_of(inst, 2, offset=3)[0][0] == 192
+    # the benchmark's digest is the same number on the host and on the device side
+    a = torch.randint(-2 ** 31, 2 ** 31, (5000,), dtype=torch.int64)
+    assert bench.digest_np(a.numpy()) == bench.digest_torch(a)
+    # every workload of the benchmark list is registered
+    for name in ("c0_small_np", "c1_papers_np", "c2_papers_snp_gat", "c3_friendster_np", "c4_stress"):
+        assert name in synthetic.WORKLOADS
 
 
 def test_handle_exchange_two_gloo_ranks(tmp_path):
