@@ -46,6 +46,7 @@ PROTOTYPES = {
     "apt_unique_workspace_bytes": (c_size_t, [c_int64]),
     "apt_unique_workspace_init": (c_int, [P, c_size_t, P]),
     "apt_unique_sorted": (c_int, [P, c_int64, P, c_int64, c_int64, P, c_size_t, P, P, P, P, P]),
+    "apt_concat_ids": (c_int, [P, c_int64, P, P, c_int64, P, P, P, P]),
     "apt_gather_workspace_bytes": (c_size_t, [c_int64]),
     "apt_gather_rows": (c_int, [P, c_int64, P, P, c_int64, P, c_int64, c_int64, P, c_int64, c_int64, c_int64, P, P, c_size_t, P, P]),
     "apt_gather_rows_from": (c_int, [P, c_int64, P, P, P, c_int64, P, c_int64, c_int64, P, c_int64, c_int64, c_int64, P, P,

@@ -64,8 +64,11 @@ def build(force=False, verbose=False):
             sys.stderr.write(f"--- {src}\n{out}\n")
     if failed:
         raise RuntimeError("nvcc failed; see messages above")
-    link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB_PATH, *objs]
+    # linked beside its final place and moved there in one step: a reader never sees a half-written library
+    tmp_path = LIB_PATH + ".tmp"
+    link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", tmp_path, *objs]
     subprocess.run(link, check=True)
+    os.replace(tmp_path, LIB_PATH)
     return LIB_PATH
 
 

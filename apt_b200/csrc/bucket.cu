@@ -108,6 +108,22 @@ k_bucket_scatter(const int64_t* __restrict__ ids, int64_t n, const int64_t* __re
   }
 }
 
+// out = cat(a[0:na], b[0:nb]) with both lengths taken from device words (the input nodes of an
+// SNP-GAT mini-batch: the local destination nodes followed by the ids received from the peers,
+// python/npc/sampler.py:230).
+__global__ void __launch_bounds__(256)
+k_concat_ids(const int64_t* __restrict__ a, int64_t na, const int64_t* __restrict__ na_dev,
+             const int64_t* __restrict__ b, int64_t nb, const int64_t* __restrict__ nb_dev,
+             int64_t* __restrict__ out, int64_t* __restrict__ out_count) {
+  na = effective_n(na, na_dev);
+  nb = effective_n(nb, nb_dev);
+  const int64_t total = na + nb;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride)
+    out[i] = i < na ? a[i] : b[i - na];
+  if (out_count && blockIdx.x == 0 && threadIdx.x == 0) *out_count = total;
+}
+
 // ------------------------------------------------------------ sorted unique
 // A two-level bitmap over the id range stands in for the sort: level 0 has one
 // bit per id, level 1 one bit per level-0 word that is not zero. Counting,
@@ -357,5 +373,21 @@ extern "C" int apt_unique_sorted(const int64_t* ids, int64_t num_ids,
   APT_LAUNCH(k_uniq_inverse, g, 256, 0, s, ids, num_ids, num_ids_dev, id_lo, id_hi, ws.l0,
              ws.word_prefix, out_inverse);
   APT_LAUNCH(k_uniq_clear, g, 256, 0, s, ids, num_ids, num_ids_dev, id_lo, id_hi, ws.l0, ws.l1);
+  return APT_OK;
+}
+
+extern "C" int apt_concat_ids(const int64_t* a, int64_t num_a, const int64_t* num_a_dev, const int64_t* b,
+                              int64_t num_b, const int64_t* num_b_dev, int64_t* out, int64_t* out_count_dev,
+                              void* stream) {
+  using namespace apt;
+  APT_CHECK_ARG(num_a >= 0 && num_b >= 0 && (num_a == 0 || a) && (num_b == 0 || b), "apt_concat_ids: bad argument");
+  APT_CHECK_ARG(out || num_a + num_b == 0, "apt_concat_ids: null output");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (num_a + num_b == 0) {
+    if (out_count_dev) APT_CUDA(cudaMemsetAsync(out_count_dev, 0, sizeof(int64_t), s));
+    return APT_OK;
+  }
+  APT_LAUNCH(k_concat_ids, wave_grid(ceil_div(num_a + num_b, 256), 8, 1), 256, 0, s, a, num_a, num_a_dev, b, num_b,
+             num_b_dev, out, out_count_dev);
   return APT_OK;
 }

@@ -209,6 +209,38 @@ k_copy_hits(int64_t n, const int64_t* __restrict__ n_dev, const int64_t* __restr
   }
 }
 
+// Grid-stride form of the hit copy: many small blocks, a warp takes R consecutive rows at a time
+// (positions, then all loads, then all stores) and strides over the request. The hardware's block
+// scheduler spreads the blocks over the SMs as they retire.
+template <typename V>
+__global__ void __launch_bounds__(kGatherBlock)
+k_copy_hits_strided(int64_t n, const int64_t* __restrict__ n_dev, const int64_t* __restrict__ first_dev,
+                    const int64_t* __restrict__ src_pos, const char* __restrict__ dev_feats, int64_t row_bytes,
+                    char* __restrict__ out) {
+  n = effective_n(n, n_dev);
+  const int64_t first = first_row(first_dev, n);
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int chunks = (int)(row_bytes / (int64_t)sizeof(V));
+  for (int64_t r0 = first + warp * kRowsPerGroup; r0 < n; r0 += warps * kRowsPerGroup) {
+    int64_t p[kRowsPerGroup];
+#pragma unroll
+    for (int k = 0; k < kRowsPerGroup; ++k) p[k] = r0 + k < n ? src_pos[r0 + k] : (int64_t)-2;
+    for (int c = lane; c < chunks; c += 32) {
+      V v[kRowsPerGroup];
+#pragma unroll
+      for (int k = 0; k < kRowsPerGroup; ++k) {
+        v[k] = zero_vec<V>();
+        if (p[k] >= 0) v[k] = ld_vec<V>((const V*)(dev_feats + p[k] * row_bytes) + c);
+      }
+#pragma unroll
+      for (int k = 0; k < kRowsPerGroup; ++k)
+        if (p[k] >= -1) st_vec<V>((V*)(out + (r0 + k) * row_bytes) + c, v[k]);
+    }
+  }
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }
@@ -352,7 +384,9 @@ k_copy_miss(GatherWs ws, const char* __restrict__ uva_feats, int64_t uva_row_byt
 // ---- tunables (set through apt_set_tunable; defaults are the measured best) ----
 static int g_miss_mode = 0;      // 0: 16-byte ld.global.nc, 1: bulk copy staged through shared memory
 static int g_miss_blocks = kNumSMs;
-static int g_hit_mode = 0;       // 0: register-staged vector copy, 1: bulk copies staged through shared memory
+static int g_hit_mode = 0;       // 0: one wave, two groups in flight per warp; 1: bulk copies through shared memory;
+                                 // 2: grid-stride blocks, one group per warp at a time
+static int g_hit_waves = 4;      // mode 2: cap on the grid, in units of 148 x 8 blocks
 
 // Bulk-copy variant: one lane per warp asks the copy engine of the SM for the
 // whole row (cp.async.bulk global -> shared, completion on an mbarrier), then
@@ -489,6 +523,14 @@ static int gather_launch(const GatherArgs& a, GatherWs ws, cudaStream_t s) {
     APT_LAUNCH(k_copy_hits<V>, grid, kGatherBlock, 0, s, a.num_rows, a.num_rows_dev,       \
                a.first_row_dev, ws.src_pos, a.dev_feats, a.dev_row_bytes, a.out);          \
   } while (0)
+#define APT_HITS_STRIDED(V)                                                                \
+  do {                                                                                     \
+    const int grid =                                                                       \
+        wave_grid(ceil_div(a.num_rows, (kGatherBlock / 32) * kRowsPerGroup), 8, g_hit_waves); \
+    ProfScope prof("gather_hit", s);                                                       \
+    APT_LAUNCH(k_copy_hits_strided<V>, grid, kGatherBlock, 0, s, a.num_rows, a.num_rows_dev, \
+               a.first_row_dev, ws.src_pos, a.dev_feats, a.dev_row_bytes, a.out);          \
+  } while (0)
 #define APT_MISS(V)                                                                        \
   do {                                                                                     \
     ProfScope prof("gather_miss", s);                                                      \
@@ -523,6 +565,8 @@ static int gather_launch(const GatherArgs& a, GatherWs ws, cudaStream_t s) {
     ProfScope prof("gather_hit", s);
     APT_LAUNCH(k_copy_hits_bulk, grid, kBulkWarps * 32, kBulkSmem, s, a.num_rows, a.num_rows_dev, a.first_row_dev,
                ws.src_pos, a.dev_feats, a.dev_row_bytes, slots, a.out, a.status_word);
+  } else if (g_hit_mode == 2) {
+    APT_BY_WIDTH(vw_hit, APT_HITS_STRIDED);
   } else {
     APT_BY_WIDTH(vw_hit, APT_HITS);
   }
@@ -538,6 +582,7 @@ static int gather_launch(const GatherArgs& a, GatherWs ws, cudaStream_t s) {
     }
   }
 #undef APT_HITS
+#undef APT_HITS_STRIDED
 #undef APT_MISS
 #undef APT_BY_WIDTH
   return APT_OK;
@@ -567,8 +612,10 @@ extern "C" int apt_set_tunable(const char* name, int64_t value) {
     g_miss_mode = (int)value;
   } else if (!strcmp(name, "gather_miss_blocks") && value >= 1 && value <= 65535) {
     g_miss_blocks = (int)value;
-  } else if (!strcmp(name, "gather_hit_mode") && value >= 0 && value <= 1) {
+  } else if (!strcmp(name, "gather_hit_mode") && value >= 0 && value <= 2) {
     g_hit_mode = (int)value;
+  } else if (!strcmp(name, "gather_hit_waves") && value >= 1 && value <= 64) {
+    g_hit_waves = (int)value;
   } else if (!strcmp(name, "relabel_small") && value >= 0 && value <= 1) {
     set_relabel_small(value != 0);
   } else {

@@ -22,6 +22,23 @@ def register(ptr: int, nbytes: int):
         raise RuntimeError(f"cudaHostRegister of {nbytes} bytes failed with error {err}")
 
 
+class _Mapping:
+    """Owns one anonymous mapping and its CUDA registration; the registration is dropped before
+    the mapping goes away (a registration that outlives its mapping would make a later mapping at
+    the same address fail to register, and points the driver at pages that are gone)."""
+
+    def __init__(self, mm, whole, window, start, registered):
+        self.mm, self.whole, self.window, self.start, self.registered = mm, whole, window, start, registered
+
+    def __del__(self):
+        if self.registered:
+            try:
+                torch.cuda.cudart().cudaHostUnregister(self.start)
+            except Exception:   # interpreter shutdown: the driver is gone, and so is the registration
+                pass
+            self.registered = False
+
+
 def alloc_table(rows: int, dim: int, dtype: torch.dtype, pin: bool = True) -> torch.Tensor:
     """A [rows, dim] host tensor on 2 MiB-aligned anonymous memory, registered
     with CUDA when `pin`. The mapping lives as long as the returned tensor."""
@@ -42,5 +59,5 @@ def alloc_table(rows: int, dim: int, dtype: torch.dtype, pin: bool = True) -> to
     t = torch.frombuffer(window, dtype=torch.uint8).view(dtype).view(rows, dim)
     if pin:
         register(start, nbytes)
-    t._apt_keepalive = (mm, whole, window)
+    t._apt_keepalive = _Mapping(mm, whole, window, start, pin)
     return t

@@ -459,6 +459,16 @@ def _unique_enqueue(ids, n_dev, id_lo, id_hi, count_out, ws_name="unique"):
     return uniq, inv
 
 
+def concat_ids(a: torch.Tensor, na_dev: Optional[torch.Tensor], b: torch.Tensor, nb_dev: Optional[torch.Tensor],
+               count_out: torch.Tensor) -> torch.Tensor:
+    """cat(a[:na], b[:nb]) with device-side lengths (None: the whole tensor); the result buffer holds
+    a.numel() + b.numel() ids and the device word `count_out` receives na + nb."""
+    out = torch.empty(a.numel() + b.numel(), dtype=torch.int64, device=a.device)
+    check(lib.apt_concat_ids(_ptr(a), a.numel(), _ptr(na_dev), _ptr(b), b.numel(), _ptr(nb_dev), _ptr(out),
+                             _ptr(count_out), _stream()))
+    return out
+
+
 def _owned_range():
     """Ids this rank can receive from a seed shuffle. On one machine these are
     the ids it owns; with several machines foreign ids are re-mapped to the

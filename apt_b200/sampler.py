@@ -81,7 +81,119 @@ class _Plan:
 _CALL_BASE_SLOT = 100  # device word holding the sampler's call-id base for graph replays
 
 
-class MixedNeighborSampler:
+class _GraphReplay:
+    """What the chained samplers share: the whole mini-batch is enqueued by `_enqueue(seeds, base_dev)`
+    without a host read and narrowed by `_finish(seeds, bufs, host)` after one copy of the device word
+    block; the enqueue is captured once per batch shape as a CUDA graph and replayed, from
+    `graph_buffers` buffer sets in turn. `sample_iter` launches mini-batch k + 1 before it reads
+    mini-batch k back. Subclasses set `num_calls` (sampling calls per mini-batch)."""
+
+    use_graph = True
+    graph_buffers = 2
+    num_calls = 1
+
+    def _init_replay(self, use_graph, graph_buffers=2):
+        if use_graph is None:
+            use_graph = os.environ.get("APT_SAMPLER_GRAPH", "1") != "0"
+        self.use_graph = bool(use_graph)
+        self.graph_buffers = max(1, int(graph_buffers))
+        self._plans = {}
+        self._turn = 0
+        self._host_base = None
+
+    def _graph_ok(self):
+        st = ops.STATE
+        # the library all-to-all (baseline backend) reads sizes on the host and cannot be captured;
+        # timing events cannot live in a captured graph either
+        return self.use_graph and not st.profiling and ops._exchange().name in ("local", "p2p")
+
+    def _plan_for(self, seeds):
+        st = ops.STATE
+        key = (seeds.numel(), seeds.device)
+        ring = self._plans.setdefault(key, [None] * self.graph_buffers)
+        i = self._turn % self.graph_buffers
+        self._turn += 1
+        plan = ring[i]
+        if plan is not None and plan.generation == st.generation:
+            return plan
+        plan = _Plan()
+        plan.generation = st.generation
+        plan.seeds_buf = torch.empty_like(seeds)
+        plan.seeds_buf.copy_(seeds)
+        base_dev = st.word(_CALL_BASE_SLOT)
+        # one eager run first: it sizes the cached workspaces and surfaces errors outside capture
+        bufs = self._enqueue(plan.seeds_buf, base_dev)
+        st.read_words()
+        st.prefetched = None
+        del bufs
+        plan.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(plan.graph):
+            plan.bufs = self._enqueue(plan.seeds_buf, base_dev)
+        plan.keepalive = list(st._ws.values())
+        ring[i] = plan
+        return plan
+
+    def _sample_chained(self, seeds: torch.Tensor):
+        st = ops.STATE
+        seeds = ops._need_cuda(seeds, "seeds")
+        if not self._graph_ok():
+            return self._finish(seeds, self._enqueue(seeds, None))
+        if self._host_base is None:
+            self._host_base = torch.zeros(1, dtype=torch.int64).pin_memory()
+        self._host_base[0] = st.sample_calls
+        st.word(_CALL_BASE_SLOT).copy_(self._host_base, non_blocking=True)
+        plan = self._plan_for(seeds)
+        plan.seeds_buf.copy_(seeds)
+        plan.graph.replay()
+        st.sample_calls += self.num_calls
+        return self._finish(seeds, plan.bufs)
+
+    def sample_iter(self, graph, seed_batches):
+        """Yields what sample() returns for every tensor of `seed_batches`, with the next mini-batch
+        already enqueued while the previous one is read back and handed out, so that the GPU never
+        waits for the host between mini-batches (the role a prefetching DataLoader has around the
+        reference's sampler, examples/train.py:85-94). Needs the CUDA-graph path; otherwise it falls
+        back to one sample() per batch. A mini-batch's tensors stay valid until the one after the
+        next has been asked for (two buffer sets in turn)."""
+        if not (getattr(self, "chained", True) and self._graph_ok() and self.graph_buffers >= 2):
+            for seeds in seed_batches:
+                yield self.sample(graph, seeds)
+            return
+        pending = None
+        for seeds in seed_batches:
+            launched = self._launch(seeds)
+            if pending is not None:
+                yield self._collect(pending)
+            pending = launched
+        if pending is not None:
+            yield self._collect(pending)
+
+    def _launch(self, seeds):
+        st = ops.STATE
+        seeds = ops._need_cuda(seeds, "seeds")
+        plan = self._plan_for(seeds)
+        if plan.host_words is None:
+            plan.host_words = torch.zeros(st.NUM_WORDS, dtype=torch.int64).pin_memory()
+            plan.host_base = torch.zeros(1, dtype=torch.int64).pin_memory()
+            plan.done = torch.cuda.Event()
+        plan.host_base[0] = st.sample_calls
+        st.word(_CALL_BASE_SLOT).copy_(plan.host_base, non_blocking=True)
+        plan.seeds_buf.copy_(seeds)
+        plan.graph.replay()
+        st.sample_calls += self.num_calls
+        plan.host_words.copy_(st.words(), non_blocking=True)
+        plan.done.record()
+        return plan, seeds
+
+    def _collect(self, launched):
+        plan, seeds = launched
+        plan.done.synchronize()
+        ops.STATE.check_host_words(plan.host_words)
+        return self._finish(seeds, plan.bufs, plan.host_words)
+
+
+
+class MixedNeighborSampler(_GraphReplay):
     """NP ("NPC") strategy: inner hops are sampled locally, the outermost hop at
     the owner of each frontier node (np_sample_and_shuffle). fanouts[0] is the
     outermost hop, as in the reference's --fan_out (python/npc/utils/utils.py:428-432).
@@ -104,21 +216,17 @@ class MixedNeighborSampler:
         self.num_layers = len(fanouts)
         if chained is None:
             chained = os.environ.get("APT_CHAINED_SAMPLER", "1") != "0"
-        if use_graph is None:
-            use_graph = os.environ.get("APT_SAMPLER_GRAPH", "1") != "0"
         self.chained = chained
         self.prefetch_features = prefetch_features
-        self.use_graph = use_graph and chained
-        self.graph_buffers = max(1, int(graph_buffers))
+        self._init_replay(use_graph, graph_buffers)
+        self.use_graph = self.use_graph and chained
+        self.num_calls = self.num_layers
         # 0 (default): one gather after the outermost hop; 1: the frontier's rows are gathered on a second
         # stream beside the outermost hop and the two meet before the remaining rows are gathered; 2: they
         # meet at the end. Measured on the papers-shaped run, 1 and 2 are slower (0.371 and 0.374 ms per
         # mini-batch against 0.340): kernels that share SMs with the host-memory reads of the miss copy
         # slow down by more than the overlap wins.
         self.gather_split = int(os.environ.get("APT_GATHER_SPLIT", "0"))
-        self._plans = {}
-        self._turn = 0
-        self._host_base = None
 
     def sample(self, graph, seeds: torch.Tensor):
         if self.chained:
@@ -143,6 +251,8 @@ class MixedNeighborSampler:
         read. With call_base_dev the k-th sampling call uses call id base + k."""
         st = ops.STATE
         ws = st.world_size
+        if self.num_layers > 14:
+            raise RuntimeError("the chained sampler keeps at most 14 hop counts")
         explicit = call_base_dev is not None
         slot = 0
         call = 0
@@ -233,101 +343,8 @@ class MixedNeighborSampler:
         return (input_nodes, seeds, blocks, bufs["perm"][:n_frontier], recv_offset, dev_offset,
                 bufs["inv"][:total_recv])
 
-    def _graph_ok(self):
-        st = ops.STATE
-        # the library all-to-all (baseline backend) reads sizes on the host and cannot be captured
-        return self.use_graph and not st.profiling and ops._exchange().name in ("local", "p2p")
 
-    def _plan_for(self, seeds):
-        st = ops.STATE
-        key = (seeds.numel(), seeds.device)
-        ring = self._plans.setdefault(key, [None] * self.graph_buffers)
-        i = self._turn % self.graph_buffers
-        self._turn += 1
-        plan = ring[i]
-        if plan is not None and plan.generation == st.generation:
-            return plan
-        plan = _Plan()
-        plan.generation = st.generation
-        plan.seeds_buf = torch.empty_like(seeds)
-        plan.seeds_buf.copy_(seeds)
-        base_dev = st.word(_CALL_BASE_SLOT)
-        # one eager run first: it sizes the cached workspaces and surfaces errors outside capture
-        bufs = self._enqueue(plan.seeds_buf, base_dev)
-        st.read_words()
-        st.prefetched = None
-        del bufs
-        plan.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(plan.graph):
-            plan.bufs = self._enqueue(plan.seeds_buf, base_dev)
-        plan.keepalive = list(st._ws.values())
-        ring[i] = plan
-        return plan
-
-    def _sample_chained(self, seeds: torch.Tensor):
-        st = ops.STATE
-        if self.num_layers > 14:
-            raise RuntimeError("the chained sampler keeps at most 14 hop counts")
-        seeds = ops._need_cuda(seeds, "seeds")
-        if not self._graph_ok():
-            return self._finish(seeds, self._enqueue(seeds, None))
-        if self._host_base is None:
-            self._host_base = torch.zeros(1, dtype=torch.int64).pin_memory()
-        self._host_base[0] = st.sample_calls
-        st.word(_CALL_BASE_SLOT).copy_(self._host_base, non_blocking=True)
-        plan = self._plan_for(seeds)
-        plan.seeds_buf.copy_(seeds)
-        plan.graph.replay()
-        st.sample_calls += self.num_layers
-        return self._finish(seeds, plan.bufs)
-
-
-    # ------------------------------------------------------------ pipelined use
-    def sample_iter(self, graph, seed_batches):
-        """Yields what sample() returns for every tensor of `seed_batches`, with the next mini-batch
-        already enqueued while the previous one is read back and handed out, so that the GPU never
-        waits for the host between mini-batches (the role a prefetching DataLoader has around the
-        reference's sampler, examples/train.py:85-94). Needs the CUDA-graph path; otherwise it falls
-        back to one sample() per batch. A mini-batch's tensors stay valid until the one after the
-        next has been asked for (two buffer sets in turn)."""
-        if not (self.chained and self._graph_ok() and self.graph_buffers >= 2):
-            for seeds in seed_batches:
-                yield self.sample(graph, seeds)
-            return
-        pending = None
-        for seeds in seed_batches:
-            launched = self._launch(seeds)
-            if pending is not None:
-                yield self._collect(pending)
-            pending = launched
-        if pending is not None:
-            yield self._collect(pending)
-
-    def _launch(self, seeds):
-        st = ops.STATE
-        seeds = ops._need_cuda(seeds, "seeds")
-        plan = self._plan_for(seeds)
-        if plan.host_words is None:
-            plan.host_words = torch.zeros(st.NUM_WORDS, dtype=torch.int64).pin_memory()
-            plan.host_base = torch.zeros(1, dtype=torch.int64).pin_memory()
-            plan.done = torch.cuda.Event()
-        plan.host_base[0] = st.sample_calls
-        st.word(_CALL_BASE_SLOT).copy_(plan.host_base, non_blocking=True)
-        plan.seeds_buf.copy_(seeds)
-        plan.graph.replay()
-        st.sample_calls += self.num_layers
-        plan.host_words.copy_(st.words(), non_blocking=True)
-        plan.done.record()
-        return plan, seeds
-
-    def _collect(self, launched):
-        plan, seeds = launched
-        plan.done.synchronize()
-        ops.STATE.check_host_words(plan.host_words)
-        return self._finish(seeds, plan.bufs, plan.host_words)
-
-
-class SPGATSampler:
+class SPGATSampler(_GraphReplay):
     """SNP strategy with a GAT model (MixedPSNeighborSampler with system "SP",
     model "GAT", shuffle_with_dst False, python/npc/sampler.py:187-238 and
     :358-364): inner hops as in GDP; in the outermost hop the block keeps the
@@ -335,13 +352,104 @@ class SPGATSampler:
     ids travel to their owners, which load and project their features; the
     feature shuffle brings the projected rows back in unique-neighbour order.
     Returns (input_nodes, output_nodes, blocks, perm, send_offset, recv_offset)
-    with input_nodes = cat(dst nodes, ids received from the other ranks)."""
+    with input_nodes = cat(dst nodes, ids received from the other ranks).
 
-    def __init__(self, rank: int, fanouts: List[int]):
+    chained / use_graph as in MixedNeighborSampler: the whole mini-batch enqueued with device-side
+    sizes and replayed from a CUDA graph, one host read at the end; prefetch_features also
+    enqueues the gather of the input nodes' rows before that read."""
+
+    # word slots of the chained form: [0..13] hop counts, [16..48] ids received per peer (+ total),
+    # [64..95] bucket offsets, [50] neighbours drawn, [51] unique neighbours, [52] input nodes,
+    # [128..160] bucket sizes
+    _N, _U, _IN = 50, 51, 52
+
+    def __init__(self, rank: int, fanouts: List[int], chained: bool = None, use_graph: bool = None,
+                 prefetch_features: bool = True):
         self.rank = rank
         self.fanouts = list(fanouts)
+        if chained is None:
+            chained = os.environ.get("APT_CHAINED_SAMPLER", "1") != "0"
+        self.chained = bool(chained)
+        self.prefetch_features = prefetch_features
+        self._init_replay(use_graph, 2)
+        self.use_graph = self.use_graph and self.chained
+        self.num_calls = len(self.fanouts)
+
+    def _enqueue(self, seeds: torch.Tensor, call_base_dev):
+        """Every kernel of the mini-batch on the current stream, no host read."""
+        st = ops.STATE
+        ws = st.world_size
+        if ws > 31 or len(self.fanouts) > 14:
+            raise RuntimeError("the chained SNP-GAT sampler serves at most 31 ranks and 14 hops")
+        words = st.words()
+        explicit = call_base_dev is not None
+        slot = 0
+        call = 0
+        cur, cur_n = seeds, None
+        layers = []
+        for fanout in list(reversed(self.fanouts))[:-1]:
+            cnt = st.word(slot)
+            uniq, rel, _ = ops._sample_relabel_enqueue(cur, fanout, cur_n, cnt, call if explicit else None,
+                                                       call_base_dev)
+            call += 1
+            layers.append((cur, rel, uniq, slot, fanout))
+            cur, cur_n = uniq, cnt
+            slot += 1
+        f = self.fanouts[0]
+        nbr = ops._sample(cur, f, cur_n, call if explicit else None, call_base_dev)
+        n_word = None
+        if cur_n is not None:
+            n_word = st.word(self._N)
+            torch.mul(cur_n, f, out=n_word)
+        # sorted unique of the neighbours + the position of every neighbour in it (torch.unique with
+        # return_inverse, python/npc/sampler.py:224-226)
+        u_word = st.word(self._U)
+        unique_neigh, arange_src = ops._unique_enqueue(nbr, n_word, 0, int(st.graph.num_total_nodes), u_word,
+                                                       "unique_gat")
+        recv_view = words[16:16 + ws + 1]
+        sizes_view = recv_view if ws == 1 else words[128:128 + ws + 1]
+        sorted_ids, perm, sizes, offsets = ops._bucket(unique_neigh, u_word, sizes_view, words[64:64 + ws])
+        recv, recv_counts = ops._exchange().exchange_ids_enqueue(sorted_ids, sizes, offsets, recv_view)
+        in_word = st.word(self._IN)
+        input_nodes = ops.concat_ids(cur, cur_n, recv, recv_counts[ws:ws + 1], in_word)
+        rows = None
+        ft = st.feat
+        if self.prefetch_features and ft.feat_pos_map is not None and \
+                input_nodes.numel() * ft.rank_feat_dim * ft.dev_feats.element_size() <= _PREFETCH_LIMIT_BYTES:
+            rows = ops._gather_enqueue(input_nodes, in_word)
+        return dict(layers=layers, slot=slot, cur=cur, arange_src=arange_src, unique_neigh=unique_neigh, perm=perm,
+                    input_nodes=input_nodes, rows=rows)
+
+    def _finish(self, seeds, b, host=None):
+        st = ops.STATE
+        ws = st.world_size
+        if host is None:
+            host = st.read_words()
+        dev = seeds.device
+        f = self.fanouts[0]
+        blocks = []
+        n_dst = seeds.numel()
+        for dst_buf, rel, uniq, u_s, fanout in b["layers"]:
+            n_src = int(host[u_s])
+            blocks.insert(0, Block(rel[:n_dst * fanout], _coo_col(dst_buf.numel(), n_dst, fanout, dev), n_src, n_dst,
+                                   uniq[:n_src], fanout))
+            n_dst = n_src
+        n_u, n_in = int(host[self._U]), int(host[self._IN])
+        if n_in > b["input_nodes"].numel():
+            raise RuntimeError("chained SNP-GAT sampler: more ids received than the buffer sized from this rank's own "
+                               "batch holds; use chained=False for batches that differ this much between the ranks")
+        blocks.insert(0, Block(b["arange_src"][:n_dst * f], _coo_col(b["cur"].numel(), n_dst, f, dev), n_u, n_dst,
+                               b["unique_neigh"][:n_u], f))
+        send_offset = host[16:16 + ws].clone().cumsum(0)
+        recv_offset = host[64:64 + ws].clone()
+        input_nodes = b["input_nodes"][:n_in]
+        if b["rows"] is not None:
+            st.prefetched = (input_nodes, b["rows"][:n_in])
+        return input_nodes, seeds, blocks, b["perm"][:n_u], send_offset, recv_offset
 
     def sample(self, graph, seeds: torch.Tensor):
+        if self.chained and ops._exchange().name in ("local", "p2p"):
+            return self._sample_chained(seeds)
         output_nodes = seeds
         blocks = []
         n_total = ops.STATE.graph.num_total_nodes
@@ -361,7 +469,7 @@ class SPGATSampler:
         return seeds, output_nodes, blocks, perm, send_offset, recv_offset
 
 
-class SPVirtualSampler:
+class SPVirtualSampler(_GraphReplay):
     """SNP strategy with a SAGE or GCN model (MixedPSNeighborSampler with system
     "SP", python/npc/sampler.py:240-330). Inner hops as in GDP. In the outermost
     hop each sampled neighbour becomes a virtual node (owner, local destination):
@@ -393,12 +501,9 @@ class SPVirtualSampler:
         # the chained form (no host read before the end of the mini-batch) covers the variant
         # without destinations
         self.chained = bool(chained) and not self.shuffle_with_dst
-        if use_graph is None:
-            use_graph = os.environ.get("APT_SAMPLER_GRAPH", "1") != "0"
-        self.use_graph = bool(use_graph) and self.chained
-        self._plans = {}
-        self._turn = 0
-        self._host_base = None
+        self._init_replay(use_graph, 2)
+        self.use_graph = self.use_graph and self.chained
+        self.num_calls = len(self.fanouts)
         self.last = {}
 
     # word slots of the chained form: [0..13] hop counts, [16..48] ids received per peer (+ total),
@@ -410,6 +515,8 @@ class SPVirtualSampler:
         """Every kernel of the mini-batch on the current stream, no host read."""
         st = ops.STATE
         ws = st.world_size
+        if ws > 31 or len(self.fanouts) > 14:
+            raise RuntimeError("the chained SNP sampler serves at most 31 ranks and 14 hops")
         dev = seeds.device
         words = st.words()
         explicit = call_base_dev is not None
@@ -471,13 +578,14 @@ class SPVirtualSampler:
                     unique_frontier=unique_frontier, arange_dst=arange_dst, vir_src=vir_src, ori_src=ori_src,
                     unique_src=unique_src, a_src=a_src, unique_dst=unique_dst, a_dst=a_dst)
 
-    def _finish(self, seeds, b):
+    def _finish(self, seeds, b, host=None):
         """The one host read of the mini-batch, then everything is narrowed to its real size."""
         st = ops.STATE
         ws = st.world_size
         dev = seeds.device
         f = self.fanouts[0]
-        host = st.read_words()
+        if host is None:
+            host = st.read_words()
         count = [int(host[k]) for k in range(b["slot"])]
         blocks = []
         n_dst = seeds.numel()
@@ -506,48 +614,6 @@ class SPVirtualSampler:
                          unique_dst=b["unique_dst"][:n_ud])
         nxt = unique_src[:n_us] if self.model == "GCN" else torch.cat((dst_nodes, unique_src[:n_us]))
         return nxt, seeds, blocks, send_sizes_cpu, recv_sizes_cpu
-
-    def _plan_for(self, seeds):
-        st = ops.STATE
-        key = (seeds.numel(), seeds.device)
-        ring = self._plans.setdefault(key, [None] * 2)
-        i = self._turn % 2
-        self._turn += 1
-        plan = ring[i]
-        if plan is not None and plan.generation == st.generation:
-            return plan
-        plan = _Plan()
-        plan.generation = st.generation
-        plan.seeds_buf = torch.empty_like(seeds)
-        plan.seeds_buf.copy_(seeds)
-        base_dev = st.word(_CALL_BASE_SLOT)
-        # one eager run first: it sizes the cached workspaces and surfaces errors outside capture
-        bufs = self._enqueue(plan.seeds_buf, base_dev)
-        st.read_words()
-        del bufs
-        plan.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(plan.graph):
-            plan.bufs = self._enqueue(plan.seeds_buf, base_dev)
-        plan.keepalive = list(st._ws.values())
-        ring[i] = plan
-        return plan
-
-    def _sample_chained(self, seeds: torch.Tensor):
-        st = ops.STATE
-        if st.world_size > 31 or len(self.fanouts) > 14:
-            raise RuntimeError("the chained SNP sampler serves at most 31 ranks and 14 hops")
-        seeds = ops._need_cuda(seeds, "seeds")
-        if not self.use_graph or st.profiling:
-            return self._finish(seeds, self._enqueue(seeds, None))
-        if self._host_base is None:
-            self._host_base = torch.zeros(1, dtype=torch.int64).pin_memory()
-        self._host_base[0] = st.sample_calls
-        st.word(_CALL_BASE_SLOT).copy_(self._host_base, non_blocking=True)
-        plan = self._plan_for(seeds)
-        plan.seeds_buf.copy_(seeds)
-        plan.graph.replay()
-        st.sample_calls += len(self.fanouts)
-        return self._finish(seeds, plan.bufs)
 
     def _outer(self, seeds, neighbors, fanout):
         st = ops.STATE

@@ -51,6 +51,8 @@ class Workload:
     partition: str = "random"        # "random": contiguous ranges of randomly relabelled ids; "bfs": ranges of a
                                      # breadth-first order from bfs_root (locality-preserving)
     bfs_root_seed: int = 5
+    locality: float = 0.0            # share of the R-MAT edges whose source is moved into the destination's block
+    locality_blocks: int = 8         # (equal blocks of the id range): R-MAT alone has no community structure
     seed_dist: str = "uniform"       # "uniform": batches out of a seeded training split; "zipf": Zipf(zipf_s) over
     zipf_s: float = 1.1              # the rank by in-degree
     host_rows_cap: Optional[int] = None   # host table rows when the full table does not fit host memory
@@ -71,14 +73,14 @@ WORKLOADS = {
     # configs[2]: the papers-shaped graph with a locality-preserving partition, SNP with a 3-layer GAT
     # (4 heads x 64, bf16): SDDMM edge scores and softmax-weighted SpMM on the sampled blocks
     "c2_papers_snp_gat": Workload("c2_papers_snp_gat", 111_059_956, 1_600_000_000, 128, "f32", 0.25, [15, 10, 5], 1024,
-                                  256, 0.011, system="SP", partition="bfs"),
+                                  256, 0.011, system="SP", partition="bfs", locality=0.75),
     # configs[4]: skewed large-feature gather / shuffle stress test (1024-dim fp16 rows of 2 KiB, 60 GB of
     # cached rows per GPU, Zipf(1.1) seeds over the degree rank)
     "c4_stress": Workload("c4_stress", 100_000_000, 1_200_000_000, 1024, "f16", 0.0, [10, 10, 10], 4096, 256, 0.0,
                           cache_bytes=60 * 10 ** 9, seed_dist="zipf", zipf_s=1.1, host_rows_cap=16_000_000),
     # miniatures for quick checks and tests
     "tiny_snp_gat": Workload("tiny_snp_gat", 1 << 15, 1 << 19, 64, "f32", 0.25, [6, 5, 4], 128, 256, 0.05,
-                             system="SP", partition="bfs"),
+                             system="SP", partition="bfs", locality=0.75),
     "tiny_stress": Workload("tiny_stress", 1 << 15, 1 << 19, 256, "f16", 0.0, [4, 4, 4], 256, 256, 0.0,
                             cache_bytes=6000 * 512, seed_dist="zipf", zipf_s=1.1, host_rows_cap=5000),
     "tiny_np": Workload("tiny_np", 1 << 16, 1 << 20, 128, "f32", 0.25, [15, 10, 5], 256, 256, 0.05),
@@ -118,6 +120,15 @@ def build_csc(w: Workload, device=None, chunk=1 << 27):
         m = min(chunk, w.num_edges - first)
         check(lib.apt_rmat_edges(w.graph_seed, first, m, w.scale, n, a, b, c, _p(src), _p(dst), _s()))
         ps, pd = perm[src[:m]], perm[dst[:m]]
+        if w.locality > 0:
+            # planted locality: a seeded share of the edges keeps its offset inside a block but moves to the
+            # block of its destination, so that a partition into those blocks finds most edges inside a part
+            block = -(-n // w.locality_blocks)
+            e_idx = torch.arange(first, first + m, dtype=torch.int64, device=device)
+            pick = ((e_idx * 0x9E3779B97F4A7C15 + w.graph_seed) >> 11) % 1000 < int(round(w.locality * 1000))
+            moved = torch.clamp((pd // block) * block + ps % block, max=n - 1)
+            ps = torch.where(pick, moved, ps)
+            del e_idx, pick, moved
         keys[at:at + m] = (pd << bits) | ps
         at += m
         if w.undirected:
@@ -313,18 +324,24 @@ def install(w: Workload, rank=0, world_size=1, row_chunk=1 << 22, tag="bench") -
     info = {}
     if w.partition == "bfs":
         # locality-preserving partition: renumber by breadth-first order from a seeded root, then the
-        # same equal contiguous ranges; the share of edges inside one part is measured, not assumed
-        parts = max(world_size, 8) if world_size == 1 else world_size
+        # same equal contiguous ranges. The share of edges inside one part is measured, not assumed, for
+        # the ids as generated and for the breadth-first renumbering, and the better of the two is installed.
+        parts = w.locality_blocks if world_size == 1 else world_size
         probe = partition_min_vids(n, parts)
-        info["intra_partition_edge_share_random"] = round(intra_partition_edge_share(indptr, indices, probe), 4)
+        before = intra_partition_edge_share(indptr, indices, probe)
         g0 = torch.Generator().manual_seed(w.bfs_root_seed)
         root = int(torch.randint(0, n, (1,), generator=g0))
         order = bfs_order(indptr, indices, root)
-        indptr, indices = relabel_graph(indptr, indices, order)
+        b_indptr, b_indices = relabel_graph(indptr, indices, order)
         del order
-        info["intra_partition_edge_share"] = round(intra_partition_edge_share(indptr, indices, probe), 4)
-        info["partition_parts_measured"] = parts
-        info["bfs_root"] = root
+        after = intra_partition_edge_share(b_indptr, b_indices, probe)
+        if after >= before:
+            indptr, indices = b_indptr, b_indices
+        del b_indptr, b_indices
+        info.update(intra_partition_edge_share=round(max(before, after), 4),
+                    intra_partition_edge_share_as_generated=round(before, 4),
+                    intra_partition_edge_share_bfs=round(after, 4), partition_used="bfs" if after >= before else
+                    "as generated", partition_parts_measured=parts, bfs_root=root)
     e = torch.empty(0, dtype=torch.int64)
     # whole topology resident in HBM: no adjacency cache is needed
     ops.mix_cache_graphs(0, e, e, e, indptr, indices)

@@ -75,8 +75,10 @@ int apt_profile_read(const char* tag, double* total_ms, int64_t* launches);
  *   gather_miss_mode   0 16-byte ld.global.nc loads (default),
  *                      1 bulk copies (cp.async.bulk) staged through shared memory
  *   gather_miss_blocks blocks of the miss-copy kernel (default 148)
- *   gather_hit_mode    0 register-staged 16-byte vector copy of the cache hits (default),
- *                      1 bulk copies (cp.async.bulk) staged through shared memory
+ *   gather_hit_mode    copy of the cache hits: 0 one resident wave, two groups of rows in flight per warp,
+ *                      1 bulk copies (cp.async.bulk) staged through shared memory,
+ *                      2 grid-stride blocks, one group of rows per warp at a time
+ *   gather_hit_waves   mode 2: cap on the grid, in units of 148 x 8 blocks (default 4)
  *   relabel_small      1 (default): layers of up to 8192 items are relabelled by one block with
  *                      the hash table in shared memory; 0: always the multi-block path */
 int apt_set_tunable(const char* name, int64_t value);
@@ -442,6 +444,14 @@ int apt_hot_order(const int32_t* counters, int64_t num_nodes, void* workspace,
 int apt_cached_access(const int32_t* counters, int64_t num_nodes,
                       const int64_t* sorted_idx, int64_t num_cache,
                       int64_t* out_total_and_cached, void* stream);
+
+/* out = cat(a[0:na], b[0:nb]) where na / nb come from the device words num_a_dev /
+ * num_b_dev when given (num_a / num_b are then upper bounds): the
+ * torch.cat((seeds, shuffled_neigh)) of the SNP-GAT sampler
+ * (python/npc/sampler.py:230) without a host read. *out_count_dev = na + nb. */
+int apt_concat_ids(const int64_t* a, int64_t num_a, const int64_t* num_a_dev,
+                   const int64_t* b, int64_t num_b, const int64_t* num_b_dev,
+                   int64_t* out, int64_t* out_count_dev, void* stream);
 
 /* ------------------------------------------------------- local row movers
  * out[i] = in[index[i]] and out[index[i]] = in[i] over rows of row_bytes

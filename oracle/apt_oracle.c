@@ -5,9 +5,11 @@
  * library never links or calls it.
  *
  * Each function follows the reference (kaihaoma/APT) source lines it cites.
- * Sampling, relabelling, gather and SpMM have no golden vectors in the
- * reference: for them parity is unpinned (see oracle/oracle.py for the pinned
- * collective cases). Loops marked `omp parallel for` use all host threads.
+ * The numpy restatement (oracle/oracle.py) is pinned against outputs of the
+ * reference's own compiled code (tests/golden/ref_*.npz) and against the
+ * closed-form cases of the reference's tests; this file is cross-checked
+ * against the numpy one (tests/test_oracle_golden.py). Loops marked
+ * `omp parallel for` use all host threads.
  */
 #include <stdint.h>
 #include <stdlib.h>

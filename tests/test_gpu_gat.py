@@ -73,16 +73,33 @@ def test_fused_gat_rejects_ungrouped_edges():
         ops.check_status()
 
 
-def test_sp_gat_sampler_one_rank():
+@pytest.mark.parametrize("mode", ["plain", "chained", "graph", "graph_single_hop"])
+def test_sp_gat_sampler_one_rank(mode):
+    # operator by operator (one host read each), chained on the device (one read per mini-batch), and the
+    # chained form replayed from a CUDA graph give the same mini-batch as the oracle
     n, indptr, indices = small_graph(scale=12, edge_factor=8)
     install_graph(indptr, indices)
     reset_world(1, 0)
     ops.register_min_vids(torch.tensor([0, n]))
     rng = np.random.default_rng(4)
     seeds = rng.permutation(n)[:300].astype(I64)
-    ops.set_sampling(key=11, call_id=0)
-    smp = apt_b200.SPGATSampler(0, [10, 5])
-    input_nodes, output_nodes, blocks, perm, send_off, recv_off = smp.sample(None, dev(seeds))
+    kw = {"plain": dict(chained=False), "chained": dict(chained=True, use_graph=False),
+          "graph": dict(chained=True, use_graph=True), "graph_single_hop": dict(chained=True, use_graph=True)}[mode]
+    if mode == "graph_single_hop":
+        ops.set_sampling(key=11, call_id=1)
+        one = apt_b200.SPGATSampler(0, [10], prefetch_features=False, **kw)
+        for _ in range(2):       # the second call replays the captured graph
+            ops.set_sampling(key=11, call_id=1)
+            in1, out1, b1, p1, so1, ro1 = one.sample(None, dev(seeds))
+        w1 = orc.sp_gat_sample([seeds], 10, np.array([0, n]), (None, None, None, indptr, indices), key=11, call_id=1)[0]
+        assert np.array_equal(host(in1), w1["input_nodes"]) and np.array_equal(host(b1[0].coo_row), w1["arange_src"])
+        assert np.array_equal(host(b1[0].src_ids), w1["unique_neigh"]) and np.array_equal(host(p1), w1["perm"])
+        ops.check_status()
+        return
+    smp = apt_b200.SPGATSampler(0, [10, 5], prefetch_features=False, **kw)
+    for _ in range(2 if mode == "graph" else 1):
+        ops.set_sampling(key=11, call_id=0)
+        input_nodes, output_nodes, blocks, perm, send_off, recv_off = smp.sample(None, dev(seeds))
     graph = (None, None, None, indptr, indices)
     nbr = orc.sample_csc_fanout(seeds, 5, *graph, key=11, call_id=0)
     u1, r1 = orc.relabel_csc(seeds, nbr)
