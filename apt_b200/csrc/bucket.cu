@@ -129,7 +129,8 @@ k_concat_ids(const int64_t* __restrict__ a, int64_t na, const int64_t* __restric
 // bit per id, level 1 one bit per level-0 word that is not zero. Counting,
 // ranking and emitting walk level 1 only (range/1024 words), so the cost of a
 // call follows the number of ids, not the width of the range. Both levels are
-// all-zero between calls: the call clears exactly the words it set.
+// all-zero between calls: the call clears exactly the words it set. Four launches:
+// mark, emit (count + ordered ranks in one pass), inverse, clear.
 constexpr int kUniqBlock = 1024;
 
 __global__ void __launch_bounds__(256)
@@ -167,30 +168,29 @@ __device__ __forceinline__ int l1_word_count(const uint32_t* __restrict__ l0, in
   return c;
 }
 
-__global__ void __launch_bounds__(kUniqBlock)
-k_uniq_count(const uint32_t* __restrict__ l0, const uint32_t* __restrict__ l1, int64_t nwords1,
-             int32_t* __restrict__ block_sums) {
-  __shared__ int warp_sums[33];
-  const int64_t w1 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const uint32_t bits = w1 < nwords1 ? l1[w1] : 0u;
-  int total;
-  block_exclusive_scan(l1_word_count(l0, w1, bits), warp_sums, &total);
-  if (threadIdx.x == 0) block_sums[blockIdx.x] = total;
-}
-
+// Counting, ranking and emitting in one launch: a tile of kUniqBlock level-1 words counts its ids,
+// the tiles' counts are chained by the look-back of common.cuh, and the tile writes its ids in order.
 __global__ void __launch_bounds__(kUniqBlock)
 k_uniq_emit(const uint32_t* __restrict__ l0, const uint32_t* __restrict__ l1, int64_t nwords1,
-            int64_t lo, const int32_t* __restrict__ block_sums,
+            int64_t lo, ScanCtrl* ctrl, uint64_t* tile_state,
             uint32_t* __restrict__ word_prefix, int64_t* __restrict__ out_unique,
-            int64_t* __restrict__ out_num_unique) {
+            int64_t* __restrict__ out_num_unique, int32_t* status) {
   __shared__ int warp_sums[33];
-  const int before = block_sum_of(block_sums, blockIdx.x, warp_sums);
-  const int64_t w1 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  __shared__ uint32_t s_tile, s_epoch, s_before;
+  if (threadIdx.x == 0) tile_ticket(ctrl, &s_tile, &s_epoch);
+  __syncthreads();
+  const uint32_t tile = s_tile;
+  const int64_t w1 = (int64_t)tile * blockDim.x + threadIdx.x;
   uint32_t bits1 = w1 < nwords1 ? l1[w1] : 0u;
   int total;
   const int ex = block_exclusive_scan(l1_word_count(l0, w1, bits1), warp_sums, &total);
-  if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) *out_num_unique = before + total;
-  int64_t at = (int64_t)before + ex;
+  if (threadIdx.x < 32) {
+    const uint32_t before = tile_lookback(tile_state, tile, s_epoch, (uint32_t)total, status, APT_FLAG_TABLE_FULL);
+    if (threadIdx.x == 0) s_before = before;
+  }
+  __syncthreads();
+  if (tile == gridDim.x - 1 && threadIdx.x == 0) *out_num_unique = (int64_t)s_before + total;
+  int64_t at = (int64_t)s_before + ex;
   while (bits1) {
     const int b1 = __ffs(bits1) - 1;
     bits1 &= bits1 - 1;
@@ -204,6 +204,8 @@ k_uniq_emit(const uint32_t* __restrict__ l0, const uint32_t* __restrict__ l1, in
       out_unique[at++] = base + b;
     }
   }
+  __syncthreads();
+  if (threadIdx.x == 0) tile_done(ctrl, s_epoch);
 }
 
 __global__ void __launch_bounds__(256)
@@ -299,7 +301,8 @@ struct UniqWs {
   uint32_t* l0;           // [nwords0] one bit per id
   uint32_t* l1;           // [nwords1] one bit per level-0 word
   uint32_t* word_prefix;  // [nwords0]
-  int32_t* block_sums;    // [nblocks + 1]
+  ScanCtrl* ctrl;         // [1]        control words of the ordered emit, zero once
+  uint64_t* tile_state;   // [nblocks]  its tile states, tagged by call
   int64_t nwords0, nwords1;
   int nblocks;
   size_t bitmap_bytes;    // l0 + l1: the part that has to be zero between calls
@@ -311,12 +314,13 @@ static size_t uniq_layout(int64_t range, char* base, UniqWs* ws) {
   const size_t b0 = align_up((size_t)nwords1 * 32 * 4, 256);  // level 0, padded to whole level-1 words
   const size_t b1 = align_up((size_t)nwords1 * 4, 256);
   const size_t b2 = align_up((size_t)nwords0 * 4, 256);
-  const size_t b3 = align_up((size_t)(nblocks + 1) * 4, 256);
+  const size_t b3 = align_up(sizeof(ScanCtrl) + (size_t)nblocks * 8, 256);
   if (ws) {
     ws->l0 = (uint32_t*)base;
     ws->l1 = (uint32_t*)(base + b0);
     ws->word_prefix = (uint32_t*)(base + b0 + b1);
-    ws->block_sums = (int32_t*)(base + b0 + b1 + b2);
+    ws->ctrl = (ScanCtrl*)(base + b0 + b1 + b2);
+    ws->tile_state = (uint64_t*)(base + b0 + b1 + b2 + sizeof(ScanCtrl));
     ws->nwords0 = nwords0;
     ws->nwords1 = nwords1;
     ws->nblocks = nblocks;
@@ -367,9 +371,8 @@ extern "C" int apt_unique_sorted(const int64_t* ids, int64_t num_ids,
   ProfScope prof("unique_sorted", s);
   const int g = wave_grid(ceil_div(num_ids, 256), 8);
   APT_LAUNCH(k_uniq_mark, g, 256, 0, s, ids, num_ids, num_ids_dev, id_lo, id_hi, ws.l0, ws.l1, status_word);
-  APT_LAUNCH(k_uniq_count, ws.nblocks, kUniqBlock, 0, s, ws.l0, ws.l1, ws.nwords1, ws.block_sums);
-  APT_LAUNCH(k_uniq_emit, ws.nblocks, kUniqBlock, 0, s, ws.l0, ws.l1, ws.nwords1, id_lo, ws.block_sums,
-             ws.word_prefix, out_unique, out_num_unique);
+  APT_LAUNCH(k_uniq_emit, ws.nblocks, kUniqBlock, 0, s, ws.l0, ws.l1, ws.nwords1, id_lo, ws.ctrl, ws.tile_state,
+             ws.word_prefix, out_unique, out_num_unique, status_word);
   APT_LAUNCH(k_uniq_inverse, g, 256, 0, s, ids, num_ids, num_ids_dev, id_lo, id_hi, ws.l0,
              ws.word_prefix, out_inverse);
   APT_LAUNCH(k_uniq_clear, g, 256, 0, s, ids, num_ids, num_ids_dev, id_lo, id_hi, ws.l0, ws.l1);

@@ -225,6 +225,92 @@ __device__ __forceinline__ int block_sum_of(const int32_t* __restrict__ sums, in
   return total;
 }
 
+// ---- single-pass ordered prefix over tiles (decoupled look-back) ----------------------
+// Tiles are handed out in launch order by a ticket, so every tile before a running tile is
+// running or finished. A tile publishes its own count as soon as it has it, then looks back
+// over the tiles before it (32 at a time, nearest first) until it meets one that has published
+// its inclusive prefix; its own inclusive prefix follows. State words carry the epoch of the
+// call (epoch << 34 | status << 32 | count), so nothing has to be cleared between calls; the
+// control words start at zero once and every call leaves ticket and done at zero.
+struct ScanCtrl {
+  uint32_t ticket;   // next tile number to hand out
+  uint32_t done;     // blocks that have finished
+  uint32_t epoch;    // calls completed on this workspace
+  uint32_t pad;
+};
+constexpr uint32_t kTileAggregate = 1u, kTileInclusive = 2u;
+constexpr int kLookbackSpinLimit = 1 << 22;   // about a second of polling; never reached unless a block died
+
+__device__ __forceinline__ uint64_t ld_tile_state(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_tile_state(uint64_t* p, uint64_t v) {
+  asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+// Thread 0 of the block: takes the block's tile number and the epoch of this call.
+__device__ __forceinline__ void tile_ticket(ScanCtrl* ctrl, uint32_t* tile, uint32_t* epoch) {
+  *epoch = *(volatile uint32_t*)&ctrl->epoch + 1u;   // moves only after the last block is done
+  *tile = atomicAdd(&ctrl->ticket, 1u);
+}
+
+// Called by all 32 lanes of one warp: publishes `total` for `tile` and returns the sum of the totals of
+// all tiles before it. A look-back that exhausts its polling limit raises `give_up_flag` in *status and
+// returns what it has (the ids of this tile are then wrong).
+__device__ __forceinline__ uint32_t tile_lookback(uint64_t* tile_state, uint32_t tile, uint32_t epoch_full,
+                                                  uint32_t total, int32_t* status, int give_up_flag) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t epoch = epoch_full & 0x3fffffffu;
+  uint32_t before = 0;
+  if (lane == 0)
+    st_tile_state(tile_state + tile,
+                  ((uint64_t)epoch << 34) | ((uint64_t)(tile == 0 ? kTileInclusive : kTileAggregate) << 32) | total);
+  if (tile > 0) {
+    int64_t look = (int64_t)tile - 1;
+    int spins = 0;
+    for (;;) {
+      const int64_t idx = look - lane;
+      const uint64_t w = idx >= 0 ? ld_tile_state(tile_state + idx) : 0ull;
+      const bool ready = idx < 0 || (uint32_t)(w >> 34) == epoch;
+      const bool incl = idx < 0 || (ready && ((uint32_t)(w >> 32) & 3u) == kTileInclusive);
+      const unsigned ready_mask = __ballot_sync(0xffffffffu, ready);
+      const unsigned incl_mask = __ballot_sync(0xffffffffu, incl);
+      const int stop = incl_mask ? __ffs(incl_mask) - 1 : 31;          // nearest tile with a full prefix
+      const unsigned need = stop == 31 ? 0xffffffffu : ((2u << stop) - 1u);
+      if ((ready_mask & need) == need) {
+        uint32_t v = (lane <= stop && idx >= 0) ? (uint32_t)w : 0u;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        before += v;
+        if (incl_mask) break;
+        look -= 32;
+        spins = 0;
+      } else if (++spins > kLookbackSpinLimit) {
+        if (lane == 0) atomicOr(status, give_up_flag);
+        break;
+      } else {
+        __nanosleep(40);
+      }
+    }
+    if (lane == 0)
+      st_tile_state(tile_state + tile, ((uint64_t)epoch << 34) | ((uint64_t)kTileInclusive << 32) | (before + total));
+  }
+  return before;
+}
+
+// Thread 0 of every block, at its end: the last block to finish puts the ticket back and advances the epoch.
+__device__ __forceinline__ void tile_done(ScanCtrl* ctrl, uint32_t epoch_full) {
+  __threadfence();
+  if (atomicAdd(&ctrl->done, 1u) == gridDim.x - 1) {
+    ctrl->done = 0;
+    ctrl->ticket = 0;
+    __threadfence();
+    *(volatile uint32_t*)&ctrl->epoch = epoch_full;
+  }
+}
+
 #endif  // __CUDACC__
 
 }  // namespace apt

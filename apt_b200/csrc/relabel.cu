@@ -75,23 +75,7 @@ k_insert(const int64_t* __restrict__ seeds, int64_t S_host, const int64_t* __res
 
 // ---- pass 2: ordered compaction in one launch ----------------------------------------
 // An item is a first occurrence iff its slot's smallest position is its own. Tiles of
-// kScanTile consecutive items are handed out in launch order by a ticket, so every tile
-// before a running tile is running or finished. A tile publishes its count as soon as it
-// has it, then looks back over the tiles before it (32 at a time, nearest first) until it
-// meets one that has published its inclusive prefix; its own inclusive prefix follows.
-// State words carry the epoch of the call, so nothing has to be cleared between calls.
-constexpr uint32_t kTileAggregate = 1u, kTileInclusive = 2u;
-constexpr int kLookbackSpinLimit = 1 << 22;   // about a second of polling; never reached unless a block died
-
-__device__ __forceinline__ uint64_t ld_state(const uint64_t* p) {
-  uint64_t v;
-  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_state(uint64_t* p, uint64_t v) {
-  asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-
+// kScanTile consecutive items; their counts are chained by the look-back of common.cuh.
 __global__ void __launch_bounds__(kScanThreads)
 k_scan_assign(int64_t S_host, int64_t M_host, const int64_t* __restrict__ S_dev, int64_t per_seed,
               RelabelWs ws, int64_t* __restrict__ out_unique, int64_t* __restrict__ out_num_unique,
@@ -99,12 +83,9 @@ k_scan_assign(int64_t S_host, int64_t M_host, const int64_t* __restrict__ S_dev,
   __shared__ int scratch[33];
   __shared__ uint32_t s_tile, s_epoch, s_before;
   const RelabelDims d = relabel_dims(S_host, M_host, S_dev, per_seed);
-  if (threadIdx.x == 0) {
-    s_epoch = *(volatile uint32_t*)&ws.ctrl->epoch + 1u;   // moves only after the last block is done
-    s_tile = atomicAdd(&ws.ctrl->ticket, 1u);
-  }
+  if (threadIdx.x == 0) tile_ticket(ws.ctrl, &s_tile, &s_epoch);
   __syncthreads();
-  const uint32_t tile = s_tile, epoch = s_epoch & 0x3fffffffu;
+  const uint32_t tile = s_tile;
   const int64_t first = (int64_t)tile * kScanTile;
   if (first < d.n || tile == 0) {
     // consecutive items of one thread: the block scan over thread sums keeps item order
@@ -126,44 +107,8 @@ k_scan_assign(int64_t S_host, int64_t M_host, const int64_t* __restrict__ S_dev,
     int total;
     const int ex = block_exclusive_scan(mine, scratch, &total);
     if (threadIdx.x < 32) {
-      const int lane = threadIdx.x;
-      uint32_t before = 0;
-      if (lane == 0)
-        st_state(ws.tile_state + tile,
-                 ((uint64_t)epoch << 34) | ((uint64_t)(tile == 0 ? kTileInclusive : kTileAggregate) << 32) |
-                     (uint32_t)total);
-      if (tile > 0) {
-        int64_t look = (int64_t)tile - 1;
-        int spins = 0;
-        for (;;) {
-          const int64_t idx = look - lane;
-          uint64_t w = idx >= 0 ? ld_state(ws.tile_state + idx) : 0ull;
-          const bool ready = idx < 0 || (uint32_t)(w >> 34) == epoch;
-          const bool incl = idx < 0 || (ready && ((uint32_t)(w >> 32) & 3u) == kTileInclusive);
-          const unsigned ready_mask = __ballot_sync(0xffffffffu, ready);
-          const unsigned incl_mask = __ballot_sync(0xffffffffu, incl);
-          const int stop = incl_mask ? __ffs(incl_mask) - 1 : 31;          // nearest tile with a full prefix
-          const unsigned need = stop == 31 ? 0xffffffffu : ((2u << stop) - 1u);
-          if ((ready_mask & need) == need) {
-            uint32_t v = (lane <= stop && idx >= 0) ? (uint32_t)w : 0u;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            before += v;
-            if (incl_mask) break;
-            look -= 32;
-            spins = 0;
-          } else if (++spins > kLookbackSpinLimit) {
-            if (lane == 0) atomicOr(status, APT_FLAG_TABLE_FULL);   // gave up: ids of this tile are wrong
-            break;
-          } else {
-            __nanosleep(40);
-          }
-        }
-        if (lane == 0)
-          st_state(ws.tile_state + tile,
-                   ((uint64_t)epoch << 34) | ((uint64_t)kTileInclusive << 32) | (uint32_t)(before + total));
-      }
-      if (lane == 0) s_before = before;
+      const uint32_t before = tile_lookback(ws.tile_state, tile, s_epoch, (uint32_t)total, status, APT_FLAG_TABLE_FULL);
+      if (threadIdx.x == 0) s_before = before;
     }
     __syncthreads();
     uint32_t id = s_before + (uint32_t)ex;
@@ -178,17 +123,8 @@ k_scan_assign(int64_t S_host, int64_t M_host, const int64_t* __restrict__ S_dev,
     // the tile that holds the last item (or the only, empty tile) knows the number of unique ids
     if (threadIdx.x == 0 && first + kScanTile >= d.n) *out_num_unique = (int64_t)s_before + total;
   }
-  // the last block to finish puts the ticket back and advances the epoch
   __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    if (atomicAdd(&ws.ctrl->done, 1u) == gridDim.x - 1) {
-      ws.ctrl->done = 0;
-      ws.ctrl->ticket = 0;
-      __threadfence();
-      *(volatile uint32_t*)&ws.ctrl->epoch = s_epoch;
-    }
-  }
+  if (threadIdx.x == 0) tile_done(ws.ctrl, s_epoch);
 }
 
 // ---- pass 3: neighbours -> new id through the remembered slot; the first occurrence

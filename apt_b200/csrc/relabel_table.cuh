@@ -22,16 +22,6 @@ constexpr int kScanThreads = 512;
 constexpr int kScanItems = 4;
 constexpr int kScanTile = kScanThreads * kScanItems;
 
-// Control words of the single-pass ordered compaction (zero after
-// apt_relabel_workspace_init; every call leaves ticket and done at zero and
-// advances epoch by one).
-struct ScanCtrl {
-  uint32_t ticket;   // next tile number to hand out
-  uint32_t done;     // blocks that have finished
-  uint32_t epoch;    // calls completed on this workspace
-  uint32_t pad;
-};
-
 struct RelabelWs {
   Slot* slots;            // [cap_ws] all-0xff between calls
   int32_t* slot_of;       // [items_ws] slot of every item of the running call, -1: not in the table

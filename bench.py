@@ -1165,6 +1165,18 @@ def run():
         return t.value, n.value
 
     stage_ms = {tag: prof(tag) for tag in STAGE_TAGS}
+    # what an event pair around one launch costs by itself: the same gather with a device-side row count of
+    # zero (same grids, every block returns at once), bracketed by the same events
+    ops.profile_enable(True)
+    zero_rows = torch.zeros(1, dtype=torch.int64, device="cuda")
+    for _ in range(20):
+        ops._gather_enqueue(kept[-1], zero_rows)
+    torch.cuda.synchronize()
+    ops.profile_enable(False)
+    empty_ms, empty_n = prof("gather_hit")
+    for tag in ("gather_classify", "gather_miss"):
+        prof(tag)
+    bracket_us = 1000.0 * empty_ms / max(empty_n, 1)
     pos_map = ops.STATE.feat.feat_pos_map
     rows_total = sum(int(k.numel()) for k in kept)
     hits_total = sum(int((pos_map[k] >= 0).sum().item()) for k in kept)
@@ -1184,7 +1196,10 @@ def run():
                 "traffic_source": HIT_TRAFFIC_SOURCE,
                 "measured_in": "the pass that enqueues the kernels one by one with an event pair around each",
                 "rows_per_launch": rows_total / max(hit_n, 1),
-                "hit_rows_per_launch": hits_total / max(hit_n, 1), "us_per_launch": 1000.0 * hit_ms / max(hit_n, 1)}
+                "hit_rows_per_launch": hits_total / max(hit_n, 1), "us_per_launch": 1000.0 * hit_ms / max(hit_n, 1),
+                "us_per_empty_launch": round(bracket_us, 2),
+                "empty_launch": "the same launch with a device-side row count of zero between the same event pair: "
+                                "what the events and the launch cost without any row moved"}
     miss_bytes = miss_total * row_bytes / max(miss_n, 1)
     miss_gbs = miss_bytes / (miss_ms / max(miss_n, 1) * 1e-3) / 1e9 if miss_ms > 0 else 0.0
 
