@@ -168,6 +168,108 @@ def select_cache_nodes(sorted_idx: torch.Tensor, localnode_mask: torch.Tensor, c
     return local_sorted[:k]
 
 
+def select_cache_costmodel(sorted_idx: torch.Tensor, idx_mem: torch.Tensor, cache_memory: int,
+                           num_total_nodes: int):
+    """The "costmodel" cache mode, python/npc/ops.py:118-142. `sorted_idx` ranks 2 N candidates by
+    benefit per byte: entry v < N is node v's feature row, entry N + v node v's adjacency list;
+    `idx_mem[c]` is candidate c's size in bytes. The first candidates whose sizes add up to at most
+    cache_memory are cached (the reference stops one short of the first prefix that exceeds the
+    budget). Returns (feature node ids, adjacency node ids), each in rank order."""
+    sorted_idx = sorted_idx.to(torch.int64)
+    cumsum = torch.cumsum(idx_mem.to(torch.int64)[sorted_idx], 0)
+    over = cumsum > int(cache_memory)
+    # torch.max over a bool vector returns the first True (or index 0 when none is set)
+    first_over = int(torch.max(over, 0)[1]) if over.numel() else 0
+    k = max(0, first_over - 1)
+    head = sorted_idx[:k]
+    return head[head < num_total_nodes], head[head >= num_total_nodes] - num_total_nodes
+
+
+def select_cache_greedy(feat_idx: torch.Tensor, graph_idx: torch.Tensor, mem_usage: torch.Tensor, cache_memory: int,
+                        feat_ratio: float, num_total_nodes: int):
+    """The "greedy" cache mode, python/npc/ops.py:144-180: feature rows and adjacency lists are
+    ranked separately; a binary search finds the largest m such that the first m * feat_ratio
+    feature rows plus the first m * (1 - feat_ratio) adjacency lists fit cache_memory. Returns
+    (feature node ids, adjacency node ids)."""
+    mem_usage = mem_usage.to(torch.int64)
+    feat_mem = torch.cumsum(mem_usage[feat_idx], 0)
+    graph_mem = torch.cumsum(mem_usage[graph_idx + num_total_nodes], 0)
+    lb, ub = 0, int(num_total_nodes)
+    while ub > lb + 1:
+        mid = (ub + lb) // 2
+        total = int(feat_mem[int(mid * feat_ratio)]) + int(graph_mem[int(mid * (1 - feat_ratio))])
+        if total <= cache_memory:
+            lb = mid
+        else:
+            ub = mid
+    return feat_idx[:int(lb * feat_ratio)], graph_idx[:int(lb * (1 - feat_ratio))]
+
+
+def dryrun_cache_order(system: str, rank: int, input_freqs: Sequence[torch.Tensor], min_vids=None) -> torch.Tensor:
+    """Node order the "dryrun" cache mode caches by on one machine, python/npc/ops.py:197-230, from
+    the per-rank input-node frequencies of a dry run (entry [1] of every rank's rk#{r}_epo100.pt):
+    NP ranks by this rank's own counts; GDP and NFP by the counts summed over the ranks (every rank
+    gets the same order); SNP by the summed counts of the nodes this rank owns (the others count as
+    never used)."""
+    if system == "NP":
+        return torch.sort(input_freqs[rank], descending=True)[1]
+    total = torch.stack(list(input_freqs), 0).sum(0)
+    if system in ("MP", "DP"):
+        return torch.sort(total, descending=True)[1]
+    if system == "SP":
+        own = torch.zeros_like(total)
+        lo, hi = int(min_vids[rank]), int(min_vids[rank + 1])
+        own[lo:hi] = total[lo:hi]
+        return torch.sort(own, descending=True)[1]
+    raise ValueError(f"unknown system {system!r}")
+
+
+def cache_adj_and_feats(cache_mode: str, rank: int, localnode_feats_idx: torch.Tensor, num_total_nodes: int, *,
+                        cache_memory: int = 0, input_dim: int = 0, system: str = "NP", world_size: int = 1,
+                        sorted_idx: Optional[torch.Tensor] = None, idx_mem: Optional[torch.Tensor] = None,
+                        greedy_idx=None, greedy_feat_ratio: float = 0.5, input_freqs=None, min_vids=None,
+                        feat_cache_ratio: float = 0.0, generator: Optional[torch.Generator] = None):
+    """cache_adj_and_feats, python/npc/ops.py:107-274, with the files it loads handed in as tensors:
+    which nodes' feature rows and which nodes' adjacency lists this rank caches. Returns (feature
+    node ids, adjacency node ids); the first goes to cache_feats_shared, the second, with the rows
+    it names, to mix_cache_graphs. Modes: "costmodel" (sorted_idx + idx_mem), "greedy" (greedy_idx =
+    (feature order, adjacency order) + idx_mem), "dryrun" (input_freqs of all ranks; no adjacency
+    cache), anything else: a random feat_cache_ratio of the local rows."""
+    none = torch.empty(0, dtype=torch.int64)
+    if cache_mode == "costmodel":
+        return select_cache_costmodel(sorted_idx, idx_mem, cache_memory, num_total_nodes)
+    if cache_mode == "greedy":
+        return select_cache_greedy(greedy_idx[0], greedy_idx[1], idx_mem, cache_memory, greedy_feat_ratio,
+                                   num_total_nodes)
+    if cache_mode == "dryrun":
+        order = dryrun_cache_order(system, rank, input_freqs, min_vids)
+        mask = torch.zeros(num_total_nodes, dtype=torch.bool)
+        mask[localnode_feats_idx] = True
+        return select_cache_nodes(order, mask, cache_memory, input_dim, world_size if system == "MP" else 1), none
+    n_local = localnode_feats_idx.numel()
+    k = int(feat_cache_ratio * n_local)
+    return localnode_feats_idx[torch.randperm(n_local, generator=generator)[:k]], none
+
+
+def append_costmodel_csv(path: str, result: "CostModelResult", *, tag: str, world_size: int, model: str,
+                         batch_size: int, input_dim: int, num_hidden: int, num_heads: int, fan_out: str,
+                         cache_mode: str, cache_memory: int, cache_value, warmup_epochs: int, dryrun_epochs: int,
+                         num_record_steps: int, warmup_time: float, dryrun_time: float) -> None:
+    """The four rows (one per strategy) the reference's cost model appends to its log,
+    python/npc/cost_model/estimator.py:643-689: the run's description, the strategy, its sampling,
+    feature-loading and reshuffle milliseconds rounded to 0.01, and their sum."""
+    import csv
+
+    info = [tag, world_size, model, batch_size, input_dim, num_hidden, num_heads, fan_out, cache_mode,
+            f"{round(cache_memory / (1024 * 1024 * 1024))}GB", cache_value, warmup_epochs, dryrun_epochs,
+            num_record_steps, round(warmup_time, 2), round(dryrun_time, 2)]
+    with open(path, "a") as f:
+        writer = csv.writer(f, lineterminator="\n")
+        for system in ("DP", "NP", "SP", "MP"):
+            record = result.records[system]
+            writer.writerow(info + [system] + [round(v, 2) for v in record] + [round(sum(record), 2)])
+
+
 def save_dryrun(path: str, seeds_counter: torch.Tensor, input_counter: torch.Tensor) -> None:
     """The file a dry run leaves per rank (rk#{r}_epo{n}.pt, examples/dryrun.py:86-108):
     a list of two int64 CPU tensors, [1] being the input-node frequencies the cache

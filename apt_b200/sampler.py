@@ -498,25 +498,26 @@ class SPVirtualSampler(_GraphReplay):
         self.shuffle_with_dst = bool(shuffle_with_dst)
         if chained is None:
             chained = os.environ.get("APT_CHAINED_SAMPLER", "1") != "0"
-        # the chained form (no host read before the end of the mini-batch) covers the variant
-        # without destinations
-        self.chained = bool(chained) and not self.shuffle_with_dst
+        self.chained = bool(chained)
         self._init_replay(use_graph, 2)
         self.use_graph = self.use_graph and self.chained
         self.num_calls = len(self.fanouts)
         self.last = {}
 
-    # word slots of the chained form: [0..13] hop counts, [16..48] ids received per peer (+ total),
+    # word slots of the chained form: [0..13] hop counts, [16..48] packed ids received per peer (+ total),
     # [50] neighbours, [51] unique virtual nodes, [52] unique received neighbours, [53] unique received
-    # virtual nodes, [128..191] send sizes, [192..253] receive sizes
-    _N, _UF, _US, _UD, _SEND, _RECV = 50, 51, 52, 53, 128, 192
+    # virtual nodes, [54] destinations + neighbours, [64..96] destinations received per peer (+ total),
+    # [128..191] send sizes, [192..253] receive sizes
+    _N, _UF, _US, _UD, _ALL, _RDST, _SEND, _RECV = 50, 51, 52, 53, 54, 64, 128, 192
 
     def _enqueue(self, seeds: torch.Tensor, call_base_dev):
         """Every kernel of the mini-batch on the current stream, no host read."""
         st = ops.STATE
         ws = st.world_size
-        if ws > 31 or len(self.fanouts) > 14:
-            raise RuntimeError("the chained SNP sampler serves at most 31 ranks and 14 hops")
+        with_dst = self.shuffle_with_dst
+        k = 3 if with_dst else 2
+        if k * ws > 62 or len(self.fanouts) > 14:
+            raise RuntimeError("the chained SNP sampler serves at most 31 ranks (20 with destinations) and 14 hops")
         dev = seeds.device
         words = st.words()
         explicit = call_base_dev is not None
@@ -544,39 +545,67 @@ class SPVirtualSampler(_GraphReplay):
         sorted_vir = torch.empty(n_max, dtype=torch.int64, device=dev)
         packed = torch.empty(n_max, dtype=torch.int64, device=dev)
         owner = ops._owner_args()
+        n_total = int(st.graph.num_total_nodes)
         check(lib.apt_sp_map_place_pack(ops._ptr(nbr), ops._ptr(pos), s_max, ops._ptr(cur_n), f, *owner, ops.SP_BASE,
-                                        int(st.graph.num_total_nodes), ops._ptr(sorted_vir), ops._ptr(packed), None,
-                                        ops._stream()))
+                                        n_total, ops._ptr(sorted_vir), ops._ptr(packed), None, ops._stream()))
         uf_word = st.word(self._UF)
+        # the unique virtual nodes come from the ids as they stand (owner x num_dst + destination); with
+        # destinations every neighbour's id is shifted by world_size x num_dst afterwards, which keeps the order
         unique_frontier, _ = ops._unique_enqueue(sorted_vir, n_word, 0, ws * max(s_max, 1), uf_word, "unique_vir")
-        send_sizes = words[self._SEND:self._SEND + 2 * ws]
-        recv_sizes = words[self._RECV:self._RECV + 2 * ws]
-        check(lib.apt_vir_send_sizes(ops._ptr(sorted_vir), n_max, ops._ptr(n_word), ops._ptr(unique_frontier),
-                                     unique_frontier.numel(), ops._ptr(uf_word), ws, s_max, ops._ptr(cur_n), 0, None,
-                                     ops._ptr(send_sizes), ops._stream()))
+        dst_sorted = None
+        if with_dst:
+            dst_sorted, dst_pos, _, _ = ops._bucket(cur, cur_n)
+            dst_vir = torch.empty(s_max, dtype=torch.int64, device=dev)
+            scratch = torch.empty(s_max, dtype=torch.int64, device=dev)
+            # a destination is a neighbour list of length one: owner(destination) x num_dst + its index,
+            # placed by the bucket's positions (MapSrcDsttoVir, src/cuda/npc_kernel.cu:15-70)
+            check(lib.apt_sp_map_place_pack(ops._ptr(cur), ops._ptr(dst_pos), s_max, ops._ptr(cur_n), 1, *owner,
+                                            ops.SP_BASE, n_total, ops._ptr(dst_vir), ops._ptr(scratch), None,
+                                            ops._stream()))
+            shift = cur_n * ws if cur_n is not None else ws * s_max
+            sorted_src = sorted_vir + shift
+            unique_frontier = unique_frontier + shift
+            sorted_all = ops.concat_ids(dst_vir, cur_n, sorted_src, n_word, st.word(self._ALL))
+            all_word = st.word(self._ALL)
+        else:
+            sorted_all, all_word = sorted_vir, n_word
+        send_sizes = words[self._SEND:self._SEND + k * ws]
+        recv_sizes = words[self._RECV:self._RECV + k * ws]
+        check(lib.apt_vir_send_sizes(ops._ptr(sorted_all), sorted_all.numel(), ops._ptr(all_word),
+                                     ops._ptr(unique_frontier), unique_frontier.numel(), ops._ptr(uf_word), ws, s_max,
+                                     ops._ptr(cur_n), int(with_dst), None, ops._ptr(send_sizes), ops._stream()))
         ex = ops._exchange()
-        ex.exchange_fixed(send_sizes.view(ws, 2), recv_sizes.view(ws, 2))
+        ex.exchange_fixed(send_sizes.view(ws, k), recv_sizes.view(ws, k))
         counts = words[16:16 + ws + 1]
+        dst_counts = words[self._RDST:self._RDST + ws + 1]
+        recv_dst = None
+        ids_at = 1 if with_dst else 0
         if ws == 1:
             recv = packed
-            counts[0:1].copy_(send_sizes[0:1])
-            counts[1:2].copy_(send_sizes[0:1])
+            counts[0:1].copy_(send_sizes[ids_at:ids_at + 1])
+            counts[1:2].copy_(send_sizes[ids_at:ids_at + 1])
+            if with_dst:
+                recv_dst = dst_sorted
+                dst_counts[0:1].copy_(send_sizes[0:1])
+                dst_counts[1:2].copy_(send_sizes[0:1])
         else:
-            send_off = torch.cumsum(send_sizes[0::2], 0)
-            recv, _ = ex.exchange_ids_enqueue(packed, None, send_off, counts)
+            if with_dst:
+                recv_dst, _ = ex.exchange_ids_enqueue(dst_sorted, None, torch.cumsum(send_sizes[0::k], 0), dst_counts)
+            recv, _ = ex.exchange_ids_enqueue(packed, None, torch.cumsum(send_sizes[ids_at::k], 0), counts)
         total = counts[ws:ws + 1]
         vir_src = torch.empty(recv.numel(), dtype=torch.int64, device=dev)
         ori_src = torch.empty(recv.numel(), dtype=torch.int64, device=dev)
-        check(lib.apt_sp_unpack_frontier(ops._ptr(recv), recv.numel(), ops._ptr(total), int(st.graph.num_total_nodes),
+        check(lib.apt_sp_unpack_frontier(ops._ptr(recv), recv.numel(), ops._ptr(total), n_total,
                                          ops._ptr(vir_src), ops._ptr(ori_src), ops._stream()))
         lo, hi = ops._owned_range()
         unique_src, a_src = ops._unique_enqueue(ori_src, total, lo, hi, st.word(self._US), "unique_sp_src")
         unique_dst, a_dst = ops._unique_enqueue(vir_src, total, 0, ws * ops.SP_BASE, st.word(self._UD), "unique_vdst")
         div = cur_n if cur_n is not None else max(s_max, 1)
         arange_dst = torch.remainder(unique_frontier, div)
-        return dict(layers=layers, slot=slot, cur=cur, nbr=nbr, sorted_vir=sorted_vir, packed=packed,
+        return dict(layers=layers, slot=slot, cur=cur, nbr=nbr, sorted_all=sorted_all, packed=packed,
                     unique_frontier=unique_frontier, arange_dst=arange_dst, vir_src=vir_src, ori_src=ori_src,
-                    unique_src=unique_src, a_src=a_src, unique_dst=unique_dst, a_dst=a_dst)
+                    unique_src=unique_src, a_src=a_src, unique_dst=unique_dst, a_dst=a_dst, dst_sorted=dst_sorted,
+                    recv_dst=recv_dst)
 
     def _finish(self, seeds, b, host=None):
         """The one host read of the mini-batch, then everything is narrowed to its real size."""
@@ -597,22 +626,36 @@ class SPVirtualSampler(_GraphReplay):
         num_dst = n_dst
         n_uf, n_us, n_ud = int(host[self._UF]), int(host[self._US]), int(host[self._UD])
         n_recv = int(host[16 + ws])
-        if n_recv > b["vir_src"].numel():
+        with_dst = self.shuffle_with_dst
+        k = 3 if with_dst else 2
+        n_rdst = int(host[self._RDST + ws]) if with_dst else 0
+        if n_recv > b["vir_src"].numel() or (with_dst and n_rdst > b["recv_dst"].numel()):
             raise RuntimeError("chained SNP sampler: more ids received than the buffer sized from this rank's own "
                                "batch holds; use chained=False for batches that differ this much between the ranks")
-        send_sizes_cpu = host[self._SEND:self._SEND + 2 * ws].clone()
-        recv_sizes_cpu = host[self._RECV:self._RECV + 2 * ws].clone()
+        send_sizes_cpu = host[self._SEND:self._SEND + k * ws].clone()
+        recv_sizes_cpu = host[self._RECV:self._RECV + k * ws].clone()
         unique_frontier, unique_src = b["unique_frontier"], b["unique_src"]
         block1 = Block(torch.arange(n_uf, device=dev), b["arange_dst"][:n_uf], n_uf, num_dst, unique_frontier[:n_uf], f)
         block2 = Block(b["a_src"][:n_recv], b["a_dst"][:n_recv], n_us, n_ud, unique_src[:n_us], f)
         blocks.insert(0, block1)
         blocks.insert(0, block2)
         dst_nodes = b["cur"][:num_dst]
-        self.last = dict(neighbors=b["nbr"][:num_dst * f], sorted_allnodes=b["sorted_vir"][:num_dst * f],
-                         unique_frontier=unique_frontier[:n_uf], send_frontier=b["packed"][:num_dst * f], recv_dst=None,
+        n_all = num_dst * f + (num_dst if with_dst else 0)
+        send_frontier = b["packed"][:num_dst * f]
+        recv_dst = None
+        if with_dst:
+            send_frontier = torch.cat((b["dst_sorted"][:num_dst], send_frontier))
+            recv_dst = b["recv_dst"][:n_rdst]
+        self.last = dict(neighbors=b["nbr"][:num_dst * f], sorted_allnodes=b["sorted_all"][:n_all],
+                         unique_frontier=unique_frontier[:n_uf], send_frontier=send_frontier, recv_dst=recv_dst,
                          vir_src=b["vir_src"][:n_recv], ori_src=b["ori_src"][:n_recv],
                          unique_dst=b["unique_dst"][:n_ud])
-        nxt = unique_src[:n_us] if self.model == "GCN" else torch.cat((dst_nodes, unique_src[:n_us]))
+        if with_dst:
+            nxt = torch.cat((recv_dst, unique_src[:n_us]))
+        elif self.model == "GCN":
+            nxt = unique_src[:n_us]
+        else:
+            nxt = torch.cat((dst_nodes, unique_src[:n_us]))
         return nxt, seeds, blocks, send_sizes_cpu, recv_sizes_cpu
 
     def _outer(self, seeds, neighbors, fanout):
@@ -680,7 +723,7 @@ class SPVirtualSampler(_GraphReplay):
         return seeds, output_nodes, blocks, send_sizes, recv_sizes
 
 
-class MPSampler:
+class MPSampler(_GraphReplay):
     """NFP strategy with a SAGE or GCN model (MixedPSNeighborSampler with system
     "MP", python/npc/sampler.py:332-356): every rank holds a slice of the feature
     columns of all nodes. Inner hops as in GDP; in the outermost hop every rank
@@ -692,41 +735,47 @@ class MPSampler:
     (all_coo_row, all_coo_col, recv_frontier_size, recv_coo_size, recv_size) as in
     the reference, input_nodes = the concatenation of all ranks' frontiers."""
 
-    def __init__(self, rank: int, fanouts: List[int], chained: bool = None):
+    def __init__(self, rank: int, fanouts: List[int], chained: bool = None, use_graph: bool = None):
         self.rank = rank
         self.fanouts = list(fanouts)
         if chained is None:
             chained = os.environ.get("APT_CHAINED_SAMPLER", "1") != "0"
         self.chained = bool(chained)
+        self._init_replay(use_graph, 2)
+        self.use_graph = self.use_graph and self.chained
+        self.num_calls = len(self.fanouts)
 
     # word slots of the chained form: [0..13] hop counts (the last one is the frontier of the outermost
     # hop), [54..56] this rank's (seeds, frontier, rows) sizes, [16..48] / [64..96] rows received per peer
     # for the two broadcasts, [128..223] every rank's three sizes
     _MINE, _ALL = 54, 128
 
-    def _sample_chained(self, seeds: torch.Tensor):
-        """Every kernel of the mini-batch enqueued without a host read (sizes stay in the device
-        word block, buffers are upper bounds, the broadcasts take device-side counts), then one
-        read and everything is narrowed."""
+    def _enqueue(self, seeds: torch.Tensor, call_base_dev):
+        """Every kernel of the mini-batch on the current stream without a host read: sizes stay in the
+        device word block, buffers are upper bounds, the broadcasts take device-side counts."""
         st = ops.STATE
         ws = st.world_size
         if ws > 31 or len(self.fanouts) > 13:
             raise RuntimeError("the chained NFP sampler serves at most 31 ranks and 13 hops")
-        seeds = ops._need_cuda(seeds, "seeds")
         dev = seeds.device
         words = st.words()
+        explicit = call_base_dev is not None
         slot = 0
+        call = 0
         cur, cur_n = seeds, None
         layers = []
         for fanout in list(reversed(self.fanouts))[:-1]:
             cnt = st.word(slot)
-            uniq, rel, _ = ops._sample_relabel_enqueue(cur, fanout, cur_n, cnt)
+            uniq, rel, _ = ops._sample_relabel_enqueue(cur, fanout, cur_n, cnt, call if explicit else None,
+                                                       call_base_dev)
+            call += 1
             layers.append((cur, rel, uniq, slot, fanout))
             cur, cur_n = uniq, cnt
             slot += 1
         f = self.fanouts[0]
         uf_word = st.word(slot)
-        unique_frontier, coo_row, _ = ops._sample_relabel_enqueue(cur, f, cur_n, uf_word)
+        unique_frontier, coo_row, _ = ops._sample_relabel_enqueue(cur, f, cur_n, uf_word, call if explicit else None,
+                                                                  call_base_dev)
         mine = words[self._MINE:self._MINE + 3]
         if cur_n is None:
             mine[0:1].fill_(cur.numel())
@@ -744,12 +793,20 @@ class MPSampler:
             all_sizes.copy_(got[:ws])
         recv_frontier, _ = ex.allbroadcast_enqueue(unique_frontier.view(-1, 1), mine[1:2], words[16:16 + ws + 1])
         recv_coo, _ = ex.allbroadcast_enqueue(coo_row.view(-1, 1), mine[2:3], words[64:64 + ws + 1])
+        return dict(layers=layers, slot=slot, recv_frontier=recv_frontier, recv_coo=recv_coo)
 
-        host = st.read_words()
-        count = [int(host[k]) for k in range(slot)]
+    def _finish(self, seeds, b, host=None):
+        """The one host read of the mini-batch, then everything is narrowed to its real size."""
+        st = ops.STATE
+        ws = st.world_size
+        dev = seeds.device
+        f = self.fanouts[0]
+        if host is None:
+            host = st.read_words()
+        count = [int(host[k]) for k in range(b["slot"])]
         blocks = []
         n_dst = seeds.numel()
-        for dst_buf, rel, uniq, u_s, fanout in layers:
+        for dst_buf, rel, uniq, u_s, fanout in b["layers"]:
             n_src = count[u_s]
             blocks.insert(0, Block(rel[:n_dst * fanout], _coo_col(dst_buf.numel(), n_dst, fanout, dev), n_src, n_dst,
                                    uniq[:n_src], fanout))
@@ -758,6 +815,7 @@ class MPSampler:
         recv_size = sizes[:, 0].clone()
         recv_frontier_size = sizes[:, 1].clone()
         recv_coo_size = sizes[:, 2].clone()
+        recv_frontier, recv_coo = b["recv_frontier"], b["recv_coo"]
         if int(recv_frontier_size.sum()) > recv_frontier.shape[0] or int(recv_coo_size.sum()) > recv_coo.shape[0]:
             raise RuntimeError("chained NFP sampler: the ranks sent more rows than the buffers sized from this rank's "
                                "own batch hold; it needs the same number of seeds on every rank (or chained=False)")

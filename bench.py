@@ -415,6 +415,10 @@ def stage_ops(args):
 
     items = S * (1 + f)
     timed("relabel_csc (1.08 M items, no host read)", relabel, 16 * items)
+    # the form the samplers use: the sampling kernel enters the ids it draws into the table itself
+    timed("sample + relabel in the sampler's fused form (67 584 seeds x 15)",
+          lambda s: ops._sample_relabel_enqueue(s, f, None, ops.STATE.word(0)), S * (32 + 16 * f) + 16 * items,
+          lambda: seed_pool[0], tags=("sample", "relabel"))
     uniq, rel = ops.relabel_csc(seed_pool[0], nbr_pool[0])
     n_src, E = uniq.numel(), rel.numel()
     col = torch.arange(S, device="cuda").repeat_interleave(f)

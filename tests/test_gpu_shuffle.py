@@ -364,21 +364,24 @@ def test_nfp_operators_single_rank(backend):
         for got, name in ((send_size, "send_size"), (recv_size, "recv_size"), (recv_frontier_size, "recv_frontier_size"),
                           (recv_coo_size, "recv_coo_size"), (recv_seed_size, "recv_size")):
             assert not got.is_cuda and np.array_equal(got.numpy(), want[name])
-        # three hops: the chained form (one host read per mini-batch) and the operator-by-operator form agree
-        seeds3 = dev(rng.permutation(n)[:100].astype(I64))
+        # three hops, two mini-batches in a row: the replayed CUDA graph, the chained form enqueued eagerly
+        # (one host read per mini-batch) and the operator-by-operator form agree
+        seeds3 = [dev(rng.permutation(n)[:100].astype(I64)) for _ in range(2)]
         res3 = []
-        for chained in (True, False):
+        for chained, use_graph in ((True, True), (True, False), (False, False)):
             ops.set_sampling(key=4, call_id=10)
-            smp = MPSampler(0, [5, 4, 3], chained=chained)
-            assert smp.chained == chained
-            res3.append(smp.sample(None, seeds3))
-        a, b = res3
-        assert torch.equal(a[0], b[0]) and torch.equal(a[3], b[3]) and torch.equal(a[4], b[4])
-        for x_, y_ in zip(a[2][0], b[2][0]):
-            assert torch.equal(x_, y_)
-        for x_, y_ in zip(a[2][1:], b[2][1:]):
-            assert torch.equal(x_.coo_row, y_.coo_row) and torch.equal(x_.src_ids, y_.src_ids)
-            assert (x_.num_src, x_.num_dst) == (y_.num_src, y_.num_dst)
+            smp = MPSampler(0, [5, 4, 3], chained=chained, use_graph=use_graph)
+            assert smp.chained == chained and smp.use_graph == use_graph
+            res3.append([smp.sample(None, sd) for sd in seeds3])
+        for other in res3[1:]:
+            for a, b in zip(res3[0], other):
+                assert torch.equal(a[0], b[0]) and torch.equal(a[3], b[3]) and torch.equal(a[4], b[4])
+                for x_, y_ in zip(a[2][0], b[2][0]):
+                    assert torch.equal(x_, y_)
+                for x_, y_ in zip(a[2][1:], b[2][1:]):
+                    assert torch.equal(x_.coo_row, y_.coo_row) and torch.equal(x_.src_ids, y_.src_ids)
+                    assert (x_.num_src, x_.num_dst) == (y_.num_src, y_.num_dst)
+        assert not torch.equal(res3[0][0][0], res3[0][1][0])
         x = torch.randn((400, 48), device="cuda")
         y = ops.mp_feat_shuffle_fwd(x, recv_size, send_size, 48)
         assert torch.equal(y, x)

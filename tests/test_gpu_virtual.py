@@ -99,7 +99,7 @@ def test_pack_and_unpack_round_trip():
         reset_world()
 
 
-@pytest.mark.parametrize("with_dst,chained", [(False, True), (False, False), (True, False)])
+@pytest.mark.parametrize("with_dst,chained", [(False, True), (False, False), (True, True), (True, False)])
 @pytest.mark.parametrize("model", ["SAGE", "GCN"])
 def test_outermost_hop_with_one_rank(with_dst, chained, model):
     n, indptr, indices = small_graph(scale=11, edge_factor=6)
@@ -161,7 +161,8 @@ def test_outermost_hop_with_one_rank(with_dst, chained, model):
     reset_world()
 
 
-def test_chained_sampler_equals_operator_by_operator_form():
+@pytest.mark.parametrize("with_dst", [False, True])
+def test_chained_sampler_equals_operator_by_operator_form(with_dst):
     # three hops, three mini-batches: the chained form (sizes stay on the device, one host read per
     # mini-batch), replayed from a CUDA graph or enqueued kernel by kernel, gives what the
     # operator-by-operator form gives
@@ -174,8 +175,9 @@ def test_chained_sampler_equals_operator_by_operator_form():
     outs = []
     for chained, use_graph in ((True, True), (True, False), (False, False)):
         ops.set_sampling(key=5, call_id=0)
-        smp = SPVirtualSampler(0, [6, 4, 3], model="SAGE", chained=chained, use_graph=use_graph)
-        assert smp.use_graph == use_graph
+        smp = SPVirtualSampler(0, [6, 4, 3], model="SAGE", shuffle_with_dst=with_dst, chained=chained,
+                               use_graph=use_graph)
+        assert smp.use_graph == use_graph and smp.chained == chained
         res = []
         for seeds in batches:
             out = smp.sample(None, seeds)
@@ -190,7 +192,7 @@ def test_chained_sampler_equals_operator_by_operator_form():
             for x, y in zip(ba, bb):
                 assert x[3:] == y[3:] and all(torch.equal(p, q) for p, q in zip(x[:3], y[:3]))
             for k in ("neighbors", "sorted_allnodes", "unique_frontier", "send_frontier", "vir_src", "ori_src",
-                      "unique_dst"):
+                      "unique_dst") + (("recv_dst",) if with_dst else ()):
                 assert torch.equal(la[k], lb[k]), k
     ops.check_status()
     reset_world()

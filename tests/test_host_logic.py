@@ -147,3 +147,57 @@ def test_cost_model_host_arithmetic_matches_oracle():
     assert planner.cachemiss_vol_to_time(vol) == orc.vol_to_seconds(vol, planner.REFERENCE_BW["pcie"])
     assert planner.reshuffle_vol_to_time(vol) == orc.vol_to_seconds(vol, planner.REFERENCE_BW["network"])
     assert planner.reshuffle_vol_to_time(vol, planner.B200_BW) < planner.reshuffle_vol_to_time(vol)
+
+
+def test_cache_selection_modes_and_costmodel_log(tmp_path):
+    """The cache modes of cache_adj_and_feats (python/npc/ops.py:107-274) and the cost model's log rows
+    (python/npc/cost_model/estimator.py:643-689) on closed-form inputs."""
+    from apt_b200 import planner
+
+    N = 10
+    # costmodel: candidates 0..9 are feature rows (40 bytes each), 10..19 adjacency lists (8 x degree bytes)
+    idx_mem = torch.tensor([40] * N + [8 * (v + 1) for v in range(N)])
+    order = torch.tensor([3, 12, 7, 19, 0, 10, 5, 11])          # best first
+    # prefix sums 40, 64, 104, 184, 224, ...: the first prefix above 190 is the fifth, the reference keeps one less
+    # than its index (index 4 -> 3 candidates)
+    feats, adj = planner.select_cache_costmodel(order, idx_mem, 190, N)
+    assert feats.tolist() == [3, 7] and adj.tolist() == [2]
+    feats, adj = planner.select_cache_costmodel(order, idx_mem, 10, N)
+    assert feats.numel() == 0 and adj.numel() == 0
+    # greedy: half features, half lists; m = 6 fits (3 x 40 + 8 (1 + 2 + 3 + 4) = 200 at the probed indices)
+    f_idx, g_idx = torch.arange(N), torch.arange(N)
+    feats, adj = planner.select_cache_greedy(f_idx, g_idx, idx_mem, 200, 0.5, N)
+    m = 2 * feats.numel()
+    assert feats.tolist() == list(range(feats.numel())) and adj.numel() == feats.numel()
+    used = 40 * (m // 2 + 1) + sum(8 * (v + 1) for v in range(m // 2 + 1))   # what the search compares (one past)
+    assert used <= 200 < 40 * (m // 2 + 2) + sum(8 * (v + 1) for v in range(m // 2 + 2))
+    # dryrun: the order depends on the strategy
+    fr = [torch.tensor([5, 0, 9, 1, 0, 0, 2, 0, 0, 0]), torch.tensor([0, 7, 0, 1, 8, 0, 0, 0, 3, 0])]
+    mv = [0, 5, 10]
+    assert planner.dryrun_cache_order("NP", 1, fr)[:3].tolist() == [4, 1, 8]
+    assert planner.dryrun_cache_order("DP", 0, fr)[:3].tolist() == [2, 4, 1]
+    assert planner.dryrun_cache_order("MP", 1, fr)[:3].tolist() == [2, 4, 1]
+    assert planner.dryrun_cache_order("SP", 1, fr, mv)[:2].tolist() == [8, 6]      # only nodes 5..9 count on rank 1
+    local = torch.tensor([0, 2, 4, 6, 8])
+    feats, adj = planner.cache_adj_and_feats("dryrun", 0, local, N, cache_memory=3 * 16 * 4, input_dim=16, system="DP",
+                                             input_freqs=fr)
+    assert feats.tolist() == [2, 4, 0] and adj.numel() == 0                       # hottest local rows, 3 fit
+    feats, _ = planner.cache_adj_and_feats("dryrun", 0, local, N, cache_memory=16 * 4, input_dim=16, system="MP",
+                                           world_size=2, input_freqs=fr)
+    assert feats.tolist() == [2, 4]                                               # NFP rows are world_size times narrower
+    feats, adj = planner.cache_adj_and_feats("random", 0, local, N, feat_cache_ratio=0.4,
+                                             generator=torch.Generator().manual_seed(1))
+    assert feats.numel() == 2 and set(feats.tolist()) <= set(local.tolist()) and adj.numel() == 0
+    # the log: four rows, one per strategy, sums in the last column
+    res = planner.CostModelResult(volumes={})
+    res.records = {"DP": [1.234, 5.0, 0.0], "NP": [1.0, 2.0, 3.004], "SP": [2.0, 2.0, 2.0], "MP": [9.0, 0.5, 0.25]}
+    log = tmp_path / "costmodel.csv"
+    planner.append_costmodel_csv(str(log), res, tag="papers_w8_x", world_size=8, model="SAGE", batch_size=1024,
+                                 input_dim=128, num_hidden=256, num_heads=1, fan_out="15,10,5", cache_mode="dryrun",
+                                 cache_memory=4 << 30, cache_value="x", warmup_epochs=1, dryrun_epochs=2,
+                                 num_record_steps=10, warmup_time=1.234, dryrun_time=2.5)
+    import csv
+    with open(log) as f:
+        rows = list(csv.reader(f))
+    assert len(rows) == 4 and [r[-5] for r in rows] == ["DP", "NP", "SP", "MP"]
+    assert rows[0][-4:] == ["1.23", "5.0", "0.0", "6.23"] and rows[1][-1] == "6.0" and rows[0][9] == "4GB"
