@@ -268,7 +268,8 @@ class P2PExchange:
         if max_rows_per_peer * row_bytes > self.region_bytes:
             raise RuntimeError(
                 f"p2p inbox region of {self.region_bytes} bytes cannot hold {max_rows_per_peer} rows of "
-                f"{row_bytes} bytes; raise APT_P2P_REGION_MB")
+                f"{row_bytes} bytes; raise APT_P2P_REGION_MB (APT_P2P_LANE_REGION_MB for the inboxes of a "
+                f"sampler's extra lanes)")
 
     def exchange_ids(self, sorted_ids, sizes, offsets):
         st = self.state

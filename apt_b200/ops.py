@@ -110,15 +110,22 @@ class NPCState:
         self.sample_calls = 0
         self.sample_replace = True
         self._ws = {}
-        self._words = None
-        self._host_words = None
+        self._lane_words = {}
+        # mini-batches that run beside one another on the GPU (each on a stream of its own) must not
+        # share scratch: workspaces, the word block and the exchange context are kept per lane
+        self.lane = 0
+        self._lane_exchange = {}
+        self._lane_streams = {}
         self.prefetched = None  # (input ids, gathered rows) left by a sampler that gathers ahead
         self.generation = 0     # bumped whenever installed state changes; captured graphs check it
         self.profiling = False
         self.exchange = None  # set by apt_b200.exchange.make_exchange at init
+        self.exchange_generation = 0
         self._side_stream = None
         self.shuffle_backend = os.environ.get("APT_SHUFFLE_BACKEND", "p2p")
         self.p2p_region_bytes = int(os.environ.get("APT_P2P_REGION_MB", "256")) << 20
+        # inboxes of the lanes beside the first carry the samplers' id exchanges only
+        self.p2p_lane_region_bytes = int(os.environ.get("APT_P2P_LANE_REGION_MB", "64")) << 20
 
     # -- device scratch --------------------------------------------------
     def device(self):
@@ -126,7 +133,7 @@ class NPCState:
 
     def workspace(self, name: str, nbytes: int) -> torch.Tensor:
         """A cached, 256-byte aligned scratch tensor of at least nbytes."""
-        key = (name, torch.cuda.current_device())
+        key = (name, torch.cuda.current_device(), self.lane)
         buf = self._ws.get(key)
         if buf is None or buf.numel() < nbytes:
             buf = torch.empty(max(int(nbytes * 1.25), 1 << 16), dtype=torch.uint8, device=self.device())
@@ -139,15 +146,26 @@ class NPCState:
             self._side_stream = torch.cuda.Stream(device=self.device())
         return self._side_stream
 
+    def lane_stream(self, lane: int) -> torch.cuda.Stream:
+        """The one stream on which work that uses lane `lane`'s scratch is enqueued: everything on
+        a lane runs in order, whichever sampler put it there."""
+        key = (lane, torch.cuda.current_device())
+        stream = self._lane_streams.get(key)
+        if stream is None:
+            stream = self._lane_streams[key] = torch.cuda.Stream(device=self.device())
+        return stream
+
     NUM_WORDS = 256
 
     def words(self) -> torch.Tensor:
         """int64[256] device words: [0..254] small results (counts a kernel leaves for
         the next kernel and, later, for the host), [255] status flags."""
-        if self._words is None or self._words.device != self.device():
-            self._words = torch.zeros(self.NUM_WORDS, dtype=torch.int64, device=self.device())
-            self._host_words = torch.zeros(self.NUM_WORDS, dtype=torch.int64).pin_memory()
-        return self._words
+        pair = self._lane_words.get(self.lane)
+        if pair is None or pair[0].device != self.device():
+            pair = (torch.zeros(self.NUM_WORDS, dtype=torch.int64, device=self.device()),
+                    torch.zeros(self.NUM_WORDS, dtype=torch.int64).pin_memory())
+            self._lane_words[self.lane] = pair
+        return pair[0]
 
     def word(self, k: int) -> torch.Tensor:
         """One-element view of device word k (a device-side count)."""
@@ -160,10 +178,11 @@ class NPCState:
         """Copies the device words to the host (one stream sync) and raises on
         any status flag except zero-degree, which is only a notice."""
         w = self.words()
-        self._host_words.copy_(w, non_blocking=True)
+        host = self._lane_words[self.lane][1]
+        host.copy_(w, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-        self.check_host_words(self._host_words)
-        return self._host_words
+        self.check_host_words(host)
+        return host
 
     def check_host_words(self, host: torch.Tensor):
         """Raises if a host copy of the word block carries a status flag (zero-degree is a notice)."""
@@ -191,12 +210,22 @@ STATE = NPCState()
 
 
 def _exchange():
-    """The exchange backend; a process that never called init() is a world of one."""
-    if STATE.exchange is None:
-        from .exchange import make_exchange
+    """The exchange backend; a process that never called init() is a world of one. Lanes other
+    than the first get a context of their own on first use (a collective step: every rank has to
+    reach it, which holds when the ranks run the same sampler), since the flags of one context
+    order its exchanges as one sequence."""
+    from .exchange import P2PExchange, make_exchange
 
+    if STATE.exchange is None:
         STATE.exchange = make_exchange(STATE)
-    return STATE.exchange
+    if STATE.lane == 0 or STATE.exchange.name != "p2p" or STATE.world_size == 1:
+        return STATE.exchange
+    ex = STATE._lane_exchange.get(STATE.lane)
+    if ex is None or ex.generation != STATE.exchange_generation:
+        ex = P2PExchange(STATE, min(STATE.p2p_region_bytes, STATE.p2p_lane_region_bytes))
+        ex.generation = STATE.exchange_generation
+        STATE._lane_exchange[STATE.lane] = ex
+    return ex
 
 
 def profile_enable(on: bool):
@@ -227,6 +256,10 @@ def init(rank: int, local_rank: int, world_size: int, nccl_id_tensor_list: torch
     s.rank, s.local_rank, s.world_size, s.node_size = int(rank), int(local_rank), int(world_size), int(node_size)
     torch.cuda.set_device(s.local_rank)
     s.exchange = make_exchange(s)
+    s.exchange_generation += 1
+    for ex in s._lane_exchange.values():
+        ex.close()
+    s._lane_exchange = {}
     s.initialized = True
     s.generation += 1
 

@@ -76,6 +76,11 @@ class _Plan:
         self.host_words = None
         self.done = None
         self.host_base = None
+        # the lane whose scratch the plan was built on; with more than one lane, the lane's stream
+        # and the event that orders a new launch behind the consumer of the plan's last results
+        self.lane = 0
+        self.stream = None
+        self.ready = None
 
 
 _CALL_BASE_SLOT = 100  # device word holding the sampler's call-id base for graph replays
@@ -86,16 +91,26 @@ class _GraphReplay:
     without a host read and narrowed by `_finish(seeds, bufs, host)` after one copy of the device word
     block; the enqueue is captured once per batch shape as a CUDA graph and replayed, from
     `graph_buffers` buffer sets in turn. `sample_iter` launches mini-batch k + 1 before it reads
-    mini-batch k back. Subclasses set `num_calls` (sampling calls per mini-batch)."""
+    mini-batch k back. Subclasses set `num_calls` (sampling calls per mini-batch).
+
+    With `lanes` > 1 (APT_SAMPLER_LANES, default 4) the buffer sets of `sample_iter` also get
+    scratch of their own (workspaces, word block, exchange context: a "lane" of the operator state)
+    and a stream of their own, so that the mini-batches it keeps in flight run beside one another
+    on the GPU instead of one behind the other: most kernels of a mini-batch wait on dependent
+    loads at low occupancy and leave room for another mini-batch's. sample() is not affected."""
 
     use_graph = True
     graph_buffers = 2
+    lanes = 1
     num_calls = 1
 
-    def _init_replay(self, use_graph, graph_buffers=2):
+    def _init_replay(self, use_graph, graph_buffers=2, lanes=None):
         if use_graph is None:
             use_graph = os.environ.get("APT_SAMPLER_GRAPH", "1") != "0"
         self.use_graph = bool(use_graph)
+        if lanes is None:
+            lanes = int(os.environ.get("APT_SAMPLER_LANES", "4"))
+        self.lanes = max(1, min(int(lanes), 8))
         self.graph_buffers = max(1, int(graph_buffers))
         self._plans = {}
         self._turn = 0
@@ -107,11 +122,19 @@ class _GraphReplay:
         # timing events cannot live in a captured graph either
         return self.use_graph and not st.profiling and ops._exchange().name in ("local", "p2p")
 
-    def _plan_for(self, seeds):
+    def _in_flight(self):
+        """Buffer sets sample_iter takes turns with."""
+        return max(self.graph_buffers, self.lanes) if self.lanes > 1 else self.graph_buffers
+
+    def _plan_for(self, seeds, piped=False):
+        """The plan the next mini-batch of this shape runs on. sample() takes `graph_buffers` plans in
+        turn on the caller's stream; sample_iter (piped) has plans of its own, on lanes when lanes > 1."""
         st = ops.STATE
-        key = (seeds.numel(), seeds.device)
-        ring = self._plans.setdefault(key, [None] * self.graph_buffers)
-        i = self._turn % self.graph_buffers
+        on_lanes = piped and self.lanes > 1
+        count = self._in_flight() if piped else self.graph_buffers
+        key = (seeds.numel(), seeds.device, piped)
+        ring = self._plans.setdefault(key, [None] * count)
+        i = self._turn % count
         self._turn += 1
         plan = ring[i]
         if plan is not None and plan.generation == st.generation:
@@ -120,18 +143,62 @@ class _GraphReplay:
         plan.generation = st.generation
         plan.seeds_buf = torch.empty_like(seeds)
         plan.seeds_buf.copy_(seeds)
-        base_dev = st.word(_CALL_BASE_SLOT)
-        # one eager run first: it sizes the cached workspaces and surfaces errors outside capture
-        bufs = self._enqueue(plan.seeds_buf, base_dev)
-        st.read_words()
-        st.prefetched = None
-        del bufs
-        plan.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(plan.graph):
-            plan.bufs = self._enqueue(plan.seeds_buf, base_dev)
-        plan.keepalive = list(st._ws.values())
+        if on_lanes:
+            # lane 0 stays with the caller: its exchange context also carries the feature shuffles
+            # the model side runs on its own stream while the samplers' lanes are in flight
+            plan.lane = 1 + i % self.lanes
+            plan.stream = st.lane_stream(plan.lane)
+            plan.ready = torch.cuda.Event()
+            torch.cuda.synchronize()     # no other lane's mini-batch is in flight while this one is built
+        st.lane = plan.lane
+        try:
+            base_dev = st.word(_CALL_BASE_SLOT)
+            # one eager run first: it sizes the cached workspaces and surfaces errors outside capture
+            bufs = self._enqueue(plan.seeds_buf, base_dev)
+            st.read_words()
+            st.prefetched = None
+            del bufs
+            plan.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(plan.graph):
+                plan.bufs = self._enqueue(plan.seeds_buf, base_dev)
+            plan.keepalive = [v for k, v in st._ws.items() if k[2] == plan.lane]
+        finally:
+            st.lane = 0
         ring[i] = plan
         return plan
+
+    def _replay(self, plan, seeds, host_base, read_back):
+        """Enqueues one replay of `plan` for `seeds`: on the current stream and lane 0's scratch, or,
+        with lanes, on the plan's own stream behind everything the current stream holds so far (the
+        seeds' producer and the consumer of the plan's previous results)."""
+        st = ops.STATE
+        host_base[0] = st.sample_calls
+        st.sample_calls += self.num_calls
+        st.lane = plan.lane
+        try:
+            if plan.stream is None:
+                st.word(_CALL_BASE_SLOT).copy_(host_base, non_blocking=True)
+                plan.seeds_buf.copy_(seeds)
+                plan.graph.replay()
+                if read_back:
+                    plan.host_words.copy_(st.words(), non_blocking=True)
+                    plan.done.record()
+                return
+            plan.ready.record()
+            plan.stream.wait_event(plan.ready)
+            with torch.cuda.stream(plan.stream):
+                st.word(_CALL_BASE_SLOT).copy_(host_base, non_blocking=True)
+                plan.seeds_buf.copy_(seeds)
+                plan.graph.replay()
+                if read_back:
+                    plan.host_words.copy_(st.words(), non_blocking=True)
+                    plan.done.record()
+                else:
+                    plan.ready.record()
+            if not read_back:
+                torch.cuda.current_stream().wait_event(plan.ready)
+        finally:
+            st.lane = 0
 
     def _sample_chained(self, seeds: torch.Tensor):
         st = ops.STATE
@@ -140,56 +207,56 @@ class _GraphReplay:
             return self._finish(seeds, self._enqueue(seeds, None))
         if self._host_base is None:
             self._host_base = torch.zeros(1, dtype=torch.int64).pin_memory()
-        self._host_base[0] = st.sample_calls
-        st.word(_CALL_BASE_SLOT).copy_(self._host_base, non_blocking=True)
         plan = self._plan_for(seeds)
-        plan.seeds_buf.copy_(seeds)
-        plan.graph.replay()
-        st.sample_calls += self.num_calls
-        return self._finish(seeds, plan.bufs)
+        self._replay(plan, seeds, self._host_base, False)
+        st.lane = plan.lane
+        try:
+            return self._finish(seeds, plan.bufs)
+        finally:
+            st.lane = 0
 
     def sample_iter(self, graph, seed_batches):
         """Yields what sample() returns for every tensor of `seed_batches`, with the next mini-batch
         already enqueued while the previous one is read back and handed out, so that the GPU never
         waits for the host between mini-batches (the role a prefetching DataLoader has around the
         reference's sampler, examples/train.py:85-94). Needs the CUDA-graph path; otherwise it falls
-        back to one sample() per batch. A mini-batch's tensors stay valid until the one after the
-        next has been asked for (two buffer sets in turn)."""
-        if not (getattr(self, "chained", True) and self._graph_ok() and self.graph_buffers >= 2):
+        back to one sample() per batch. A mini-batch's tensors stay valid until the next one has
+        been asked for (the buffer sets take turns)."""
+        depth = self._in_flight()
+        if not (getattr(self, "chained", True) and self._graph_ok() and depth >= 2):
             for seeds in seed_batches:
                 yield self.sample(graph, seeds)
             return
-        pending = None
+        # depth - 1 mini-batches are in flight behind the one the caller holds
+        pending = []
         for seeds in seed_batches:
-            launched = self._launch(seeds)
-            if pending is not None:
-                yield self._collect(pending)
-            pending = launched
-        if pending is not None:
-            yield self._collect(pending)
+            pending.append(self._launch(seeds))
+            if len(pending) >= depth:
+                yield self._collect(pending.pop(0))
+        while pending:
+            yield self._collect(pending.pop(0))
 
     def _launch(self, seeds):
         st = ops.STATE
         seeds = ops._need_cuda(seeds, "seeds")
-        plan = self._plan_for(seeds)
+        plan = self._plan_for(seeds, piped=True)
         if plan.host_words is None:
             plan.host_words = torch.zeros(st.NUM_WORDS, dtype=torch.int64).pin_memory()
             plan.host_base = torch.zeros(1, dtype=torch.int64).pin_memory()
             plan.done = torch.cuda.Event()
-        plan.host_base[0] = st.sample_calls
-        st.word(_CALL_BASE_SLOT).copy_(plan.host_base, non_blocking=True)
-        plan.seeds_buf.copy_(seeds)
-        plan.graph.replay()
-        st.sample_calls += self.num_calls
-        plan.host_words.copy_(st.words(), non_blocking=True)
-        plan.done.record()
+        self._replay(plan, seeds, plan.host_base, True)
         return plan, seeds
 
     def _collect(self, launched):
         plan, seeds = launched
         plan.done.synchronize()
-        ops.STATE.check_host_words(plan.host_words)
-        return self._finish(seeds, plan.bufs, plan.host_words)
+        st = ops.STATE
+        st.lane = plan.lane
+        try:
+            st.check_host_words(plan.host_words)
+            return self._finish(seeds, plan.bufs, plan.host_words)
+        finally:
+            st.lane = 0
 
 
 
@@ -206,10 +273,13 @@ class MixedNeighborSampler(_GraphReplay):
                        replay it (one launch per mini-batch). The results of a batch
                        live in the graph's buffers: they stay valid until
                        `graph_buffers` further batches have been sampled.
+    lanes              buffer sets with scratch and a stream of their own, so that the
+                       mini-batches sample_iter keeps in flight overlap on the GPU
+                       (default: APT_SAMPLER_LANES, else 4)
     """
 
     def __init__(self, rank: int, fanouts: List[int], chained: bool = None, prefetch_features: bool = True,
-                 use_graph: bool = None, graph_buffers: int = 2):
+                 use_graph: bool = None, graph_buffers: int = 2, lanes: int = None):
         self.rank = rank
         self.fir_fanouts = list(fanouts[1:])
         self.las_fanouts = fanouts[0]
@@ -218,7 +288,7 @@ class MixedNeighborSampler(_GraphReplay):
             chained = os.environ.get("APT_CHAINED_SAMPLER", "1") != "0"
         self.chained = chained
         self.prefetch_features = prefetch_features
-        self._init_replay(use_graph, graph_buffers)
+        self._init_replay(use_graph, graph_buffers, lanes)
         self.use_graph = self.use_graph and chained
         self.num_calls = self.num_layers
         # 0 (default): one gather after the outermost hop; 1: the frontier's rows are gathered on a second
@@ -364,14 +434,14 @@ class SPGATSampler(_GraphReplay):
     _N, _U, _IN = 50, 51, 52
 
     def __init__(self, rank: int, fanouts: List[int], chained: bool = None, use_graph: bool = None,
-                 prefetch_features: bool = True):
+                 prefetch_features: bool = True, lanes: int = None):
         self.rank = rank
         self.fanouts = list(fanouts)
         if chained is None:
             chained = os.environ.get("APT_CHAINED_SAMPLER", "1") != "0"
         self.chained = bool(chained)
         self.prefetch_features = prefetch_features
-        self._init_replay(use_graph, 2)
+        self._init_replay(use_graph, 2, lanes)
         self.use_graph = self.use_graph and self.chained
         self.num_calls = len(self.fanouts)
 
@@ -489,7 +559,7 @@ class SPVirtualSampler(_GraphReplay):
     (`self.last["unique_dst"]`)."""
 
     def __init__(self, rank: int, fanouts: List[int], model: str = "SAGE", shuffle_with_dst: bool = False,
-                 chained: bool = None, use_graph: bool = None):
+                 chained: bool = None, use_graph: bool = None, lanes: int = None):
         if model not in ("SAGE", "GCN"):
             raise ValueError("SPVirtualSampler serves SAGE and GCN; GAT uses SPGATSampler")
         self.rank = rank
@@ -499,7 +569,7 @@ class SPVirtualSampler(_GraphReplay):
         if chained is None:
             chained = os.environ.get("APT_CHAINED_SAMPLER", "1") != "0"
         self.chained = bool(chained)
-        self._init_replay(use_graph, 2)
+        self._init_replay(use_graph, 2, lanes)
         self.use_graph = self.use_graph and self.chained
         self.num_calls = len(self.fanouts)
         self.last = {}
@@ -735,13 +805,14 @@ class MPSampler(_GraphReplay):
     (all_coo_row, all_coo_col, recv_frontier_size, recv_coo_size, recv_size) as in
     the reference, input_nodes = the concatenation of all ranks' frontiers."""
 
-    def __init__(self, rank: int, fanouts: List[int], chained: bool = None, use_graph: bool = None):
+    def __init__(self, rank: int, fanouts: List[int], chained: bool = None, use_graph: bool = None,
+                 lanes: int = None):
         self.rank = rank
         self.fanouts = list(fanouts)
         if chained is None:
             chained = os.environ.get("APT_CHAINED_SAMPLER", "1") != "0"
         self.chained = bool(chained)
-        self._init_replay(use_graph, 2)
+        self._init_replay(use_graph, 2, lanes)
         self.use_graph = self.use_graph and self.chained
         self.num_calls = len(self.fanouts)
 

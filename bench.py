@@ -371,7 +371,7 @@ def stage_ops(args):
         for tag in tags:
             t_, k_ = ctypes.c_double(), ctypes.c_int64()
             lib.apt_profile_read(tag.encode(), ctypes.byref(t_), ctypes.byref(k_))
-            out[tag] = round(1e6 * t_.value / max(k_.value, 1), 2)
+            out[tag] = round(1e3 * t_.value / max(k_.value, 1), 2)      # milliseconds -> us per launch
         return out
 
     def timed(name, fn, algo_bytes, fresh=None, tags=()):
@@ -841,6 +841,7 @@ def run_snp_gat(args, inst, w, rank, world, config, run_info, barrier, reduce_ma
     attn_l = torch.randn((1, heads, head_dim), generator=gen, device="cuda").bfloat16()
     attn_r = torch.randn((1, heads, head_dim), generator=gen, device="cuda").bfloat16()
     sampler = apt_b200.SPGATSampler(rank, w.fanouts)
+    run_info["sampler_lanes"] = sampler.lanes
     total = args.warmup + args.steps
     dev_batches = batches_of(inst, total)
     marks = {}
@@ -1048,6 +1049,7 @@ def run():
         return
 
     sampler = apt_b200.MixedNeighborSampler(rank, w.fanouts)
+    run_info["sampler_lanes"] = sampler.lanes
     total = args.warmup + args.steps
     dev_batches = batches_of(inst, total)
     host_batches = [b.cpu().pin_memory() for b in batches_of(inst, total, offset=total)]
@@ -1284,8 +1286,10 @@ def run():
         "dtype": "int64 ids, " + w.dtype + " rows", "data": "synthetic", "config": config, "run_info": run_info,
         "clocks": clock_info,
         "e2e": e2e, "gpu_launches": int(reduce_sum(launches)),
-        "launch_mode": "one CUDA graph replay per mini-batch, the next one enqueued before the previous one is "
-                       "read back" if graph_mode else
+        "launch_mode": (f"one CUDA graph replay per mini-batch, {sampler._in_flight()} mini-batches in flight on "
+                        f"{sampler.lanes} streams with scratch of their own" if sampler.lanes > 1 else
+                        "one CUDA graph replay per mini-batch, the next one enqueued before the previous one is "
+                        "read back") if graph_mode else
                        "kernels enqueued one by one, sizes chained on the device",
         "step_ms_spread": spread,
         "profiled_value": world * args.steps / (ms_prof / 1000.0),

@@ -40,3 +40,4 @@ def reset_world(world_size=1, rank=0):
     s = apt_b200.STATE
     s.rank, s.world_size, s.node_size = rank, world_size, world_size
     s.exchange = None
+    s.lane = 0

@@ -418,6 +418,21 @@ def main():
             for name, a_, b_ in zip(("input_nodes", "outer coo_row", "inner coo_row", "perm", "send_offset",
                                      "recv_offset", "inverse_idx"), all_o0[r], want0):
                 assert np.array_equal(a_, b_), f"rank {r}: small NP configuration: {name} differs from the oracle"
+    # the same configuration through the pipelined iterator, one lane against three: with lanes every
+    # mini-batch in flight runs on a stream, scratch and inbox of its own, and gives the same tensors
+    batches0 = [torch.randperm(w0.num_nodes, generator=gsd, device="cuda")[:w0.batch] for _ in range(7)]
+    runs0 = []
+    for lanes in (1, 3):
+        ops.set_sampling(key=2027, call_id=0)
+        smp_l = apt_b200.MixedNeighborSampler(rank, w0.fanouts, prefetch_features=False, lanes=lanes)
+        assert smp_l.lanes == lanes
+        runs0.append([(host(o[0]), host(o[2][0].coo_row), host(o[2][1].coo_row), host(o[3]), o[4].numpy().copy(),
+                       o[5].numpy().copy(), host(o[6])) for o in smp_l.sample_iter(None, batches0)])
+    for k_, (a_, b_) in enumerate(zip(*runs0)):
+        for x_, y_ in zip(a_, b_):
+            assert np.array_equal(x_, y_), f"rank {rank}: mini-batch {k_} differs between one lane and three"
+    assert ops.STATE.lane == 0 and len(ops.STATE._lane_exchange) == 3
+    dist.barrier()
     # put the small test graph back for the timing below
     ops.mix_cache_graphs(0, e, e, e, torch.from_numpy(indptr).cuda(), torch.from_numpy(indices).cuda())
     ops.register_min_vids(torch.from_numpy(mv))

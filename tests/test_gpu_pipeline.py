@@ -136,9 +136,11 @@ def test_frontier_rows_gathered_beside_the_outermost_hop(use_graph):
     ops.check_status()
 
 
-def test_pipelined_iterator_equals_one_sample_per_batch():
+@pytest.mark.parametrize("lanes", [1, 2, 3])
+def test_pipelined_iterator_equals_one_sample_per_batch(lanes):
     """sample_iter enqueues mini-batch k + 1 before it reads mini-batch k back; the tensors it hands
-    out are those of sample(), batch by batch, and stay valid while the next batch is in flight."""
+    out are those of sample(), batch by batch, and stay valid while the next batch is in flight.
+    With lanes the mini-batches in flight run on streams and scratch of their own."""
     n, indptr, indices = small_graph(scale=12, edge_factor=8)
     install_graph(indptr, indices)
     reset_world(1, 0)
@@ -147,7 +149,7 @@ def test_pipelined_iterator_equals_one_sample_per_batch():
     feats, uva, devf, cached_idx, local_idx, pos_map, cpu_map = feature_setup(n, 32, 0.5, rng)
     ops.cache_feats_shared(n, torch.from_numpy(uva).pin_memory(), dev(devf), torch.from_numpy(cached_idx),
                            torch.from_numpy(local_idx), 0)
-    batches = [dev(rng.permutation(n)[:150].astype(I64)) for _ in range(5)]
+    batches = [dev(rng.permutation(n)[:150].astype(I64)) for _ in range(9)]
 
     def snapshot(res, x):
         return (host(res[0]), host(res[2][0].coo_row), host(res[2][1].coo_row), host(res[3]), host(res[6]),
@@ -160,7 +162,8 @@ def test_pipelined_iterator_equals_one_sample_per_batch():
         res = plain.sample(None, b)
         want.append(snapshot(res, ops.load_subtensor(res[0])))
     ops.set_sampling(key=5150, call_id=2)
-    piped = apt_b200.MixedNeighborSampler(0, [7, 3], chained=True, use_graph=True)
+    piped = apt_b200.MixedNeighborSampler(0, [7, 3], chained=True, use_graph=True, lanes=lanes)
+    assert piped.lanes == lanes and piped._in_flight() == max(2, lanes)
     got = []
     for res in piped.sample_iter(None, iter(batches)):
         got.append(snapshot(res, ops.load_subtensor(res[0])))      # the next batch is already in flight here
@@ -169,6 +172,13 @@ def test_pipelined_iterator_equals_one_sample_per_batch():
         for a, b in zip(g_, w_):
             assert np.array_equal(a, b)
     assert apt_b200.STATE.sample_calls == 2 + 2 * len(batches)
+    # one call at a time: sample() has plans of its own on the caller's stream
+    ops.set_sampling(key=5150, call_id=2)
+    for b, w_ in zip(batches[:4], want):
+        res = piped.sample(None, b)
+        for a, c in zip(snapshot(res, ops.load_subtensor(res[0])), w_):
+            assert np.array_equal(a, c)
+    assert apt_b200.STATE.lane == 0
     ops.check_status()
 
 
