@@ -387,7 +387,7 @@ class MixedNeighborSampler(_GraphReplay):
         if host is None:
             host = st.read_words()
         u_slot, in_slot = bufs["u_slot"], bufs["in_slot"]
-        count = [int(host[k]) for k in range(in_slot + 1)]
+        count = host[:in_slot + 1].tolist()
         recv_offset = host[16:16 + ws].clone().cumsum(0)
         dev_offset = host[64:64 + ws].clone()
         total_recv = int(recv_offset[-1])

@@ -1124,17 +1124,20 @@ def run():
     value = world * args.steps / (ms / 1000.0)
     ops.check_status()
 
-    # ---- spread of the single steps: an event pair around each of up to 100 of the same steps
+    # ---- spread: an event behind every step of up to 100 of the same steps. With several mini-batches in
+    # flight the steps complete in bursts, so the spread is taken over windows of 10 steps (ms per step).
     phase("spread")
     n_spread = min(args.steps, 100)
+    window = 10 if sampler.lanes > 1 and n_spread >= 30 else 1
     marks = [torch.cuda.Event(enable_timing=True) for _ in range(n_spread + 1)]
     barrier()
     marks[0].record()
     run_steps(dev_batches[args.warmup:args.warmup + n_spread], after=lambda k, sample, x: marks[k + 1].record())
     barrier()
-    per_step = sorted(marks[k].elapsed_time(marks[k + 1]) for k in range(n_spread))
-    spread = {"steps": n_spread, "median": per_step[n_spread // 2], "p10": per_step[n_spread // 10],
-              "p90": per_step[min(n_spread - 1, (9 * n_spread) // 10)]}
+    n_win = n_spread // window
+    per_step = sorted(marks[k * window].elapsed_time(marks[(k + 1) * window]) / window for k in range(n_win))
+    spread = {"steps": n_spread, "window": window, "median": per_step[n_win // 2], "p10": per_step[n_win // 10],
+              "p90": per_step[min(n_win - 1, (9 * n_win) // 10)]}
     ops.check_status()
 
     # ---- the same steps once more with per-kernel CUDA events (for the roofline and the
