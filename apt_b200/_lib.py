@@ -32,6 +32,7 @@ PROTOTYPES = {
     "apt_version": (c_int, []),
     "apt_launch_count": (c_int64, []),
     "apt_launch_count_reset": (None, []),
+    "apt_memcpy_async": (c_int, [P, P, c_size_t, P]),
     "apt_set_tunable": (c_int, [c_char_p, c_int64]),
     "apt_profile_enable": (c_int, [c_int]),
     "apt_profile_read": (c_int, [c_char_p, ctypes.POINTER(c_double), ctypes.POINTER(c_int64)]),

@@ -76,6 +76,13 @@ int apt_version(void) { return 100; }
 int64_t apt_launch_count(void) { return apt::g_launches.load(); }
 void apt_launch_count_reset(void) { apt::g_launches.store(0); }
 
+int apt_memcpy_async(void* dst, const void* src, size_t nbytes, void* stream) {
+  if (nbytes == 0) return APT_OK;
+  APT_CHECK_ARG(dst && src, "apt_memcpy_async: null pointer");
+  APT_CUDA(cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDefault, (cudaStream_t)stream));
+  return APT_OK;
+}
+
 int apt_profile_enable(int on) {
   apt::g_prof_on.store(on ? 1 : 0);
   return APT_OK;

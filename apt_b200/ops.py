@@ -11,6 +11,7 @@ State lives in one process-wide object like the reference's ``NPCState``
 """
 import ctypes
 import os
+import threading
 from typing import List, Optional, Tuple
 
 import torch
@@ -113,7 +114,7 @@ class NPCState:
         self._lane_words = {}
         # mini-batches that run beside one another on the GPU (each on a stream of its own) must not
         # share scratch: workspaces, the word block and the exchange context are kept per lane
-        self.lane = 0
+        self._tls = threading.local()
         self._lane_exchange = {}
         self._lane_streams = {}
         self.prefetched = None  # (input ids, gathered rows) left by a sampler that gathers ahead
@@ -126,6 +127,15 @@ class NPCState:
         self.p2p_region_bytes = int(os.environ.get("APT_P2P_REGION_MB", "256")) << 20
         # inboxes of the lanes beside the first carry the samplers' id exchanges only
         self.p2p_lane_region_bytes = int(os.environ.get("APT_P2P_LANE_REGION_MB", "64")) << 20
+
+    @property
+    def lane(self) -> int:
+        """The lane whose scratch the calling thread's operators use (0: the caller's own)."""
+        return getattr(self._tls, "lane", 0)
+
+    @lane.setter
+    def lane(self, value: int):
+        self._tls.lane = int(value)
 
     # -- device scratch --------------------------------------------------
     def device(self):

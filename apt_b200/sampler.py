@@ -12,7 +12,10 @@ buffers are narrowed to their real lengths. The results are identical to
 calling the operators one by one (``chained=False``), which reads a count
 after every relabelling like the reference does (src/cuda/relabel.cu:119).
 """
+import itertools
 import os
+import queue
+import threading
 from dataclasses import dataclass
 from typing import List
 
@@ -114,7 +117,8 @@ class _GraphReplay:
         self.graph_buffers = max(1, int(graph_buffers))
         self._plans = {}
         self._turn = 0
-        self._host_base = None
+        # launches of sample_iter on a thread of their own (APT_SAMPLER_THREAD)
+        self.launch_thread = os.environ.get("APT_SAMPLER_THREAD", "0") == "1"
 
     def _graph_ok(self):
         st = ops.STATE
@@ -132,7 +136,8 @@ class _GraphReplay:
         st = ops.STATE
         on_lanes = piped and self.lanes > 1
         count = self._in_flight() if piped else self.graph_buffers
-        key = (seeds.numel(), seeds.device, piped)
+        dev = seeds.device if seeds.is_cuda else st.device()
+        key = (seeds.numel(), dev, piped)
         ring = self._plans.setdefault(key, [None] * count)
         i = self._turn % count
         self._turn += 1
@@ -141,8 +146,11 @@ class _GraphReplay:
             return plan
         plan = _Plan()
         plan.generation = st.generation
-        plan.seeds_buf = torch.empty_like(seeds)
+        plan.seeds_buf = torch.empty(seeds.numel(), dtype=torch.int64, device=dev)
         plan.seeds_buf.copy_(seeds)
+        plan.host_words = torch.zeros(st.NUM_WORDS, dtype=torch.int64).pin_memory()
+        plan.host_base = torch.zeros(1, dtype=torch.int64).pin_memory()
+        plan.done = torch.cuda.Event()
         if on_lanes:
             # lane 0 stays with the caller: its exchange context also carries the feature shuffles
             # the model side runs on its own stream while the samplers' lanes are in flight
@@ -160,60 +168,50 @@ class _GraphReplay:
             del bufs
             plan.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(plan.graph):
+                # the two small host copies are nodes of the graph: the call-id base is read from the
+                # plan's pinned word when the replay runs, and the word block lands in the plan's
+                # pinned copy behind the last kernel
+                # (apt_memcpy_async and not Tensor.copy_: the latter also records an event for the
+                # pinned block, which may not be queried once it was recorded in a capture)
+                check(lib.apt_memcpy_async(ops._ptr(base_dev), ops._ptr(plan.host_base), 8, ops._stream()))
                 plan.bufs = self._enqueue(plan.seeds_buf, base_dev)
+                check(lib.apt_memcpy_async(ops._ptr(plan.host_words), ops._ptr(st.words()), 8 * st.NUM_WORDS,
+                                           ops._stream()))
             plan.keepalive = [v for k, v in st._ws.items() if k[2] == plan.lane]
         finally:
             st.lane = 0
         ring[i] = plan
         return plan
 
-    def _replay(self, plan, seeds, host_base, read_back):
-        """Enqueues one replay of `plan` for `seeds`: on the current stream and lane 0's scratch, or,
-        with lanes, on the plan's own stream behind everything the current stream holds so far (the
-        seeds' producer and the consumer of the plan's previous results)."""
+    def _replay(self, plan, seeds):
+        """Enqueues one replay of `plan` for `seeds` and records `plan.done` behind it: on the current
+        stream, or, with lanes, on the plan's own stream behind everything the current stream holds
+        so far (the seeds' producer and the consumer of the plan's previous results)."""
         st = ops.STATE
-        host_base[0] = st.sample_calls
+        plan.host_base[0] = st.sample_calls
         st.sample_calls += self.num_calls
-        st.lane = plan.lane
+        # explicit streams throughout: looking the current stream up costs more host time than a launch
+        cur = torch.cuda.current_stream()
+        if plan.stream is None:
+            plan.seeds_buf.copy_(seeds, non_blocking=True)
+            plan.graph.replay()
+            plan.done.record(cur)
+            return
+        plan.ready.record(cur)
+        plan.stream.wait_event(plan.ready)
+        torch.cuda.set_stream(plan.stream)
         try:
-            if plan.stream is None:
-                st.word(_CALL_BASE_SLOT).copy_(host_base, non_blocking=True)
-                plan.seeds_buf.copy_(seeds)
-                plan.graph.replay()
-                if read_back:
-                    plan.host_words.copy_(st.words(), non_blocking=True)
-                    plan.done.record()
-                return
-            plan.ready.record()
-            plan.stream.wait_event(plan.ready)
-            with torch.cuda.stream(plan.stream):
-                st.word(_CALL_BASE_SLOT).copy_(host_base, non_blocking=True)
-                plan.seeds_buf.copy_(seeds)
-                plan.graph.replay()
-                if read_back:
-                    plan.host_words.copy_(st.words(), non_blocking=True)
-                    plan.done.record()
-                else:
-                    plan.ready.record()
-            if not read_back:
-                torch.cuda.current_stream().wait_event(plan.ready)
+            plan.seeds_buf.copy_(seeds, non_blocking=True)
+            plan.graph.replay()
         finally:
-            st.lane = 0
+            torch.cuda.set_stream(cur)
+        plan.done.record(plan.stream)
 
     def _sample_chained(self, seeds: torch.Tensor):
-        st = ops.STATE
         seeds = ops._need_cuda(seeds, "seeds")
         if not self._graph_ok():
             return self._finish(seeds, self._enqueue(seeds, None))
-        if self._host_base is None:
-            self._host_base = torch.zeros(1, dtype=torch.int64).pin_memory()
-        plan = self._plan_for(seeds)
-        self._replay(plan, seeds, self._host_base, False)
-        st.lane = plan.lane
-        try:
-            return self._finish(seeds, plan.bufs)
-        finally:
-            st.lane = 0
+        return self._collect(self._launch(seeds, piped=False))
 
     def sample_iter(self, graph, seed_batches):
         """Yields what sample() returns for every tensor of `seed_batches`, with the next mini-batch
@@ -221,11 +219,16 @@ class _GraphReplay:
         waits for the host between mini-batches (the role a prefetching DataLoader has around the
         reference's sampler, examples/train.py:85-94). Needs the CUDA-graph path; otherwise it falls
         back to one sample() per batch. A mini-batch's tensors stay valid until the next one has
-        been asked for (the buffer sets take turns)."""
+        been asked for (the buffer sets take turns). The seed batches may be CUDA tensors or int64
+        tensors in page-locked host memory; the latter are copied straight into the plan's buffer,
+        and the output nodes handed out are then that buffer."""
         depth = self._in_flight()
         if not (getattr(self, "chained", True) and self._graph_ok() and depth >= 2):
             for seeds in seed_batches:
-                yield self.sample(graph, seeds)
+                yield self.sample(graph, seeds if seeds.is_cuda else seeds.to(ops.STATE.device()))
+            return
+        if self.launch_thread:
+            yield from self._iter_threaded(seed_batches, depth)
             return
         # depth - 1 mini-batches are in flight behind the one the caller holds
         pending = []
@@ -236,16 +239,73 @@ class _GraphReplay:
         while pending:
             yield self._collect(pending.pop(0))
 
-    def _launch(self, seeds):
+    def _iter_threaded(self, seed_batches, depth):
+        """sample_iter with the launches on a thread of their own: the driver's part of a graph launch
+        runs without the interpreter lock, beside the caller's thread narrowing the previous
+        mini-batch. A buffer set is launched on again only after the caller asked for the mini-batch
+        behind the one it held; plans are built (captured, inboxes created) by the calling thread."""
+        out_q, handback = queue.SimpleQueue(), queue.SimpleQueue()
+        slots = threading.Semaphore(depth)
+        stop = threading.Event()
+        device = torch.cuda.current_device()
+        stream = torch.cuda.current_stream()
+
+        def launcher():
+            try:
+                torch.cuda.set_device(device)
+                torch.cuda.set_stream(stream)
+                for seeds in seed_batches:
+                    slots.acquire()
+                    if stop.is_set():
+                        return
+                    if self._has_plan(seeds):
+                        out_q.put(("launched", self._launch(seeds)))
+                    else:
+                        out_q.put(("build", seeds))
+                        handback.get()            # the calling thread built the plan and launched on it
+                out_q.put(("end", None))
+            except BaseException as exc:          # handed to the calling thread, which raises it
+                out_q.put(("error", exc))
+
+        thread = threading.Thread(target=launcher, name="apt-sampler-launch", daemon=True)
+        thread.start()
+        try:
+            while True:
+                kind, item = out_q.get()
+                if kind == "end":
+                    break
+                if kind == "error":
+                    raise item
+                if kind == "build":
+                    item = self._launch(item)
+                    handback.put(None)
+                yield self._collect(item)
+                slots.release()
+        finally:
+            stop.set()
+            slots.release()
+            handback.put(None)
+            thread.join(timeout=60)
+
+    def _has_plan(self, seeds):
+        """True when the plan the next piped launch of this shape takes exists already."""
         st = ops.STATE
-        seeds = ops._need_cuda(seeds, "seeds")
-        plan = self._plan_for(seeds, piped=True)
-        if plan.host_words is None:
-            plan.host_words = torch.zeros(st.NUM_WORDS, dtype=torch.int64).pin_memory()
-            plan.host_base = torch.zeros(1, dtype=torch.int64).pin_memory()
-            plan.done = torch.cuda.Event()
-        self._replay(plan, seeds, plan.host_base, True)
-        return plan, seeds
+        dev = seeds.device if seeds.is_cuda else st.device()
+        ring = self._plans.get((seeds.numel(), dev, True))
+        if ring is None:
+            return False
+        plan = ring[self._turn % len(ring)]
+        return plan is not None and plan.generation == st.generation
+
+    def _launch(self, seeds, piped=True):
+        if seeds.is_cuda or not piped:
+            seeds = ops._need_cuda(seeds, "seeds")
+        elif seeds.dtype != torch.int64 or not seeds.is_contiguous():
+            seeds = seeds.to(torch.int64).contiguous()
+        plan = self._plan_for(seeds, piped)
+        self._replay(plan, seeds)
+        # seeds handed over in host memory went straight into the plan's buffer, which then stands for them
+        return plan, (seeds if seeds.is_cuda else plan.seeds_buf)
 
     def _collect(self, launched):
         plan, seeds = launched
@@ -387,10 +447,14 @@ class MixedNeighborSampler(_GraphReplay):
         if host is None:
             host = st.read_words()
         u_slot, in_slot = bufs["u_slot"], bufs["in_slot"]
-        count = host[:in_slot + 1].tolist()
-        recv_offset = host[16:16 + ws].clone().cumsum(0)
-        dev_offset = host[64:64 + ws].clone()
-        total_recv = int(recv_offset[-1])
+        # one tolist() of the word block: python ints from here on (every slice, clone or int() of the
+        # pinned block costs microseconds of host time per mini-batch)
+        h = host.tolist()
+        count = h[:in_slot + 1]
+        recv_cum = list(itertools.accumulate(h[16:16 + ws]))
+        recv_offset = torch.tensor(recv_cum, dtype=torch.int64)
+        dev_offset = torch.tensor(h[64:64 + ws], dtype=torch.int64)
+        total_recv = recv_cum[-1]
         if total_recv > bufs["inv"].numel():
             raise RuntimeError("chained NP sampler: more ids received than the buffer sized from this rank's own "
                                "batch holds; use chained=False for batches that differ this much between the ranks")
@@ -510,8 +574,9 @@ class SPGATSampler(_GraphReplay):
                                "batch holds; use chained=False for batches that differ this much between the ranks")
         blocks.insert(0, Block(b["arange_src"][:n_dst * f], _coo_col(b["cur"].numel(), n_dst, f, dev), n_u, n_dst,
                                b["unique_neigh"][:n_u], f))
-        send_offset = host[16:16 + ws].clone().cumsum(0)
-        recv_offset = host[64:64 + ws].clone()
+        h = host.tolist()
+        send_offset = torch.tensor(list(itertools.accumulate(h[16:16 + ws])), dtype=torch.int64)
+        recv_offset = torch.tensor(h[64:64 + ws], dtype=torch.int64)
         input_nodes = b["input_nodes"][:n_in]
         if b["rows"] is not None:
             st.prefetched = (input_nodes, b["rows"][:n_in])
@@ -702,8 +767,9 @@ class SPVirtualSampler(_GraphReplay):
         if n_recv > b["vir_src"].numel() or (with_dst and n_rdst > b["recv_dst"].numel()):
             raise RuntimeError("chained SNP sampler: more ids received than the buffer sized from this rank's own "
                                "batch holds; use chained=False for batches that differ this much between the ranks")
-        send_sizes_cpu = host[self._SEND:self._SEND + k * ws].clone()
-        recv_sizes_cpu = host[self._RECV:self._RECV + k * ws].clone()
+        h = host.tolist()
+        send_sizes_cpu = torch.tensor(h[self._SEND:self._SEND + k * ws], dtype=torch.int64)
+        recv_sizes_cpu = torch.tensor(h[self._RECV:self._RECV + k * ws], dtype=torch.int64)
         unique_frontier, unique_src = b["unique_frontier"], b["unique_src"]
         block1 = Block(torch.arange(n_uf, device=dev), b["arange_dst"][:n_uf], n_uf, num_dst, unique_frontier[:n_uf], f)
         block2 = Block(b["a_src"][:n_recv], b["a_dst"][:n_recv], n_us, n_ud, unique_src[:n_us], f)
@@ -883,9 +949,10 @@ class MPSampler(_GraphReplay):
                                    uniq[:n_src], fanout))
             n_dst = n_src
         sizes = host[self._ALL:self._ALL + 3 * ws].view(ws, 3)
-        recv_size = sizes[:, 0].clone()
-        recv_frontier_size = sizes[:, 1].clone()
-        recv_coo_size = sizes[:, 2].clone()
+        sizes = torch.tensor(sizes.tolist(), dtype=torch.int64)        # off the pinned block
+        recv_size = sizes[:, 0].contiguous()
+        recv_frontier_size = sizes[:, 1].contiguous()
+        recv_coo_size = sizes[:, 2].contiguous()
         recv_frontier, recv_coo = b["recv_frontier"], b["recv_coo"]
         if int(recv_frontier_size.sum()) > recv_frontier.shape[0] or int(recv_coo_size.sum()) > recv_coo.shape[0]:
             raise RuntimeError("chained NFP sampler: the ranks sent more rows than the buffers sized from this rank's "

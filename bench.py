@@ -35,10 +35,13 @@ sys.path.insert(0, ROOT)
 STAGE_TAGS = ("sample", "relabel", "bucket", "unique_sorted", "gather_classify", "gather_hit", "gather_miss",
               "p2p_push", "p2p_wait", "p2p_pull")
 # DRAM bytes (read + written) per algorithmic byte of the hit kernel, from an ncu capture of that kernel
-# alone at the mini-batch's size (143 000 rows of 512 bytes out of a 27.8 M-row cache table); None until
-# such a capture exists for the current kernel.
-HIT_DRAM_BYTES_PER_ALGORITHMIC_BYTE = None
-HIT_TRAFFIC_SOURCE = "not captured for this kernel yet"
+# alone at the mini-batch's size: 143 000 random rows of 512 bytes out of a 2 GB cache table moved
+# 73.3 MB of DRAM reads (every row once) and 21.5 MB of DRAM writes (the rest of the 73.2 MB written was
+# still in the 126 MB L2 when the kernel ended) for 147.6 MB algorithmic. Traffic grows with the rows.
+HIT_DRAM_BYTES_PER_ALGORITHMIC_BYTE = (73.3 + 21.5) / 147.6
+HIT_TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of k_copy_hits at 143 000 rows x 512 B "
+                      "(94.8 MB per 147.6 MB algorithmic), scaled by this launch's algorithmic bytes; writes that "
+                      "stay in L2 past the kernel's end are not in it")
 METRIC = "sampled+gathered mini-batches/sec (whole box)"
 UNIT = "mini-batches/s"
 
@@ -1200,9 +1203,11 @@ def run():
     roofline = {"kernel": "k_copy_hits (gather, cache hits)", "bound": "hbm",
                 "achieved": round(hit_gbs, 1), "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                 "frac": round(hit_gbs / peak, 4),
+                # the capture holds for launches of its kind: 512-byte rows, a batch that fits the L2 twice over
                 "traffic": round(hit_bytes * HIT_DRAM_BYTES_PER_ALGORITHMIC_BYTE)
-                if HIT_DRAM_BYTES_PER_ALGORITHMIC_BYTE else None,
-                "traffic_source": HIT_TRAFFIC_SOURCE,
+                if row_bytes == 512 and hit_bytes < 4e8 else None,
+                "traffic_source": HIT_TRAFFIC_SOURCE if row_bytes == 512 and hit_bytes < 4e8 else
+                "not captured for launches of this size",
                 "measured_in": "the pass that enqueues the kernels one by one with an event pair around each",
                 "rows_per_launch": rows_total / max(hit_n, 1),
                 "hit_rows_per_launch": hits_total / max(hit_n, 1), "us_per_launch": 1000.0 * hit_ms / max(hit_n, 1),
@@ -1236,19 +1241,20 @@ def run():
     # Every step copies its seeds from pinned host memory and reads a digest of the gathered rows (and,
     # inside the sampler, the 2 KiB block of counts) back into pinned host memory. The digest of step k
     # is looked at once step k + 1 has been enqueued, so that the read does not drain the GPU.
-    digests = [torch.empty(2 * w.feat_dim, dtype=torch.float32).pin_memory() for _ in range(2)]
+    row_dtype = ops.STATE.feat.dev_feats.dtype
+    digests = [torch.empty(w.feat_dim, dtype=row_dtype).pin_memory() for _ in range(2)]
     digest_done = [torch.cuda.Event(), torch.cuda.Event()]
     checksum = [0.0]
 
     def e2e_run(host_seed_batches):
         def read_back(k, sample, x):
-            digests[k % 2].copy_(torch.cat([x[0], x[-1]]).float(), non_blocking=True)   # device -> host
+            digests[k % 2].copy_(x[-1], non_blocking=True)     # the last gathered row: device -> host
             digest_done[k % 2].record()
             if k >= 1:
                 digest_done[(k - 1) % 2].synchronize()
                 checksum[0] += float(digests[(k - 1) % 2][0])
         n = len(host_seed_batches)
-        run_steps((b.to("cuda", non_blocking=True) for b in host_seed_batches), after=read_back)   # host -> device
+        run_steps(host_seed_batches, after=read_back)     # the iterator copies each batch host -> device itself
         if n:
             digest_done[(n - 1) % 2].synchronize()
             checksum[0] += float(digests[(n - 1) % 2][0])
@@ -1263,10 +1269,10 @@ def run():
     barrier()
     ms_e2e = reduce_max(ev0.elapsed_time(ev1))
     e2e = {"value": world * args.steps / (ms_e2e / 1000.0), "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
-           "h2d_bytes_per_step": w.batch * 8, "d2h_bytes_per_step": 2 * w.feat_dim * 4 + 64 * 4,
-           "note": "seeds come from pinned host memory; a digest (first and last gathered row) and the per-hop "
-                   "unique counts are read back into pinned host memory every step; the gathered rows stay on the "
-                   "GPU for the model"}
+           "h2d_bytes_per_step": w.batch * 8, "d2h_bytes_per_step": row_bytes + 8 * ops.STATE.NUM_WORDS,
+           "note": "seeds come from pinned host memory; the last gathered row and the block of device-side counts "
+                   "(per-hop unique counts, exchange sizes, status flags) are read back into pinned host memory "
+                   "every step; the gathered rows stay on the GPU for the model"}
     ops.check_status()
 
     # ---- parity of this very configuration, outside every timed region ----------------------

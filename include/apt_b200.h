@@ -63,6 +63,14 @@ int apt_version(void);
 int64_t apt_launch_count(void);
 void apt_launch_count_reset(void);
 
+/* One stream-ordered copy of nbytes between any two of device memory and
+ * page-locked host memory (the direction follows from the pointers). It is
+ * what the samplers put into a captured CUDA graph to bring the call-id base
+ * in and the block of device-side counts out: a captured copy reads its host
+ * source when the replay runs. No counterpart in the reference, which reads
+ * its sizes with blocking copies (src/sampling.cc:176-185). */
+int apt_memcpy_async(void* dst, const void* src, size_t nbytes, void* stream);
+
 /* Optional per-kernel timing. When enabled, every launch of a tagged kernel
  * is bracketed by CUDA events on its own stream; apt_profile_read
  * synchronises those events and returns the summed milliseconds and launch

@@ -136,11 +136,12 @@ def test_frontier_rows_gathered_beside_the_outermost_hop(use_graph):
     ops.check_status()
 
 
-@pytest.mark.parametrize("lanes", [1, 2, 3])
-def test_pipelined_iterator_equals_one_sample_per_batch(lanes):
+@pytest.mark.parametrize("lanes,thread", [(1, False), (2, False), (3, False), (1, True), (4, True)])
+def test_pipelined_iterator_equals_one_sample_per_batch(lanes, thread):
     """sample_iter enqueues mini-batch k + 1 before it reads mini-batch k back; the tensors it hands
     out are those of sample(), batch by batch, and stay valid while the next batch is in flight.
-    With lanes the mini-batches in flight run on streams and scratch of their own."""
+    With lanes the mini-batches in flight run on streams and scratch of their own; with the launch
+    thread the replays are enqueued by a second host thread."""
     n, indptr, indices = small_graph(scale=12, edge_factor=8)
     install_graph(indptr, indices)
     reset_world(1, 0)
@@ -164,6 +165,7 @@ def test_pipelined_iterator_equals_one_sample_per_batch(lanes):
     ops.set_sampling(key=5150, call_id=2)
     piped = apt_b200.MixedNeighborSampler(0, [7, 3], chained=True, use_graph=True, lanes=lanes)
     assert piped.lanes == lanes and piped._in_flight() == max(2, lanes)
+    piped.launch_thread = thread          # launches from a thread of their own
     got = []
     for res in piped.sample_iter(None, iter(batches)):
         got.append(snapshot(res, ops.load_subtensor(res[0])))      # the next batch is already in flight here
@@ -172,6 +174,19 @@ def test_pipelined_iterator_equals_one_sample_per_batch(lanes):
         for a, b in zip(g_, w_):
             assert np.array_equal(a, b)
     assert apt_b200.STATE.sample_calls == 2 + 2 * len(batches)
+    # seed batches handed over in page-locked host memory: same mini-batches, output nodes on the device
+    ops.set_sampling(key=5150, call_id=2)
+    pinned = [b.cpu().pin_memory() for b in batches]
+    for k, res in enumerate(piped.sample_iter(None, pinned)):
+        assert res[1].is_cuda and torch.equal(res[1], batches[k])
+        for a, c in zip(snapshot(res, ops.load_subtensor(res[0])), want[k]):
+            assert np.array_equal(a, c)
+    # a consumer that stops early leaves nothing behind
+    ops.set_sampling(key=5150, call_id=2)
+    for k, res in enumerate(piped.sample_iter(None, iter(batches))):
+        if k == 2:
+            break
+    torch.cuda.synchronize()
     # one call at a time: sample() has plans of its own on the caller's stream
     ops.set_sampling(key=5150, call_id=2)
     for b, w_ in zip(batches[:4], want):
