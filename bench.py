@@ -42,6 +42,9 @@ HIT_DRAM_BYTES_PER_ALGORITHMIC_BYTE = (73.3 + 21.5) / 147.6
 HIT_TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of k_copy_hits at 143 000 rows x 512 B "
                       "(94.8 MB per 147.6 MB algorithmic), scaled by this launch's algorithmic bytes; writes that "
                       "stay in L2 past the kernel's end are not in it")
+# the pool's reference figure for a peer copy over NVLink, GB/s per direction (900 nominal); the benchmark
+# also measures a copy-engine peer copy in its own run and reports fractions of all three
+POOL_PEER_COPY_GBS = 770.0
 METRIC = "sampled+gathered mini-batches/sec (whole box)"
 UNIT = "mini-batches/s"
 
@@ -767,6 +770,22 @@ def shuffle_record(args, rank, world, barrier):
                for rows, dim, dt in shapes.values())
     p2p = keep if isinstance(keep, P2PExchange) and keep.region_bytes >= need else P2PExchange(st, need)
     nccl = NcclExchange(st)
+    # a second inbox with two landing buffers for the direct-placement leg (opt-in path of the library)
+    rows_c4, dim_c4, dt_c4 = shapes["c4_stress_2KiB_f16"]
+    landing_mb = int(1.08 * rows_c4 * dim_c4 * torch.empty(0, dtype=dt_c4).element_size()) >> 20
+    env_keep = {k: os.environ.get(k) for k in ("APT_P2P_DIRECT", "APT_P2P_DIRECT_SLOTS", "APT_P2P_LANDING_MB")}
+    os.environ.update(APT_P2P_DIRECT="1", APT_P2P_DIRECT_SLOTS="2", APT_P2P_LANDING_MB=str(landing_mb))
+    try:
+        direct = P2PExchange(st, need)
+    finally:
+        for k, v in env_keep.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+    if not direct.direct:
+        direct.close()
+        direct = None
     steps, warm = 10, 3
     g = torch.Generator(device="cuda").manual_seed(100 + rank)
     out = {}
@@ -807,9 +826,27 @@ def shuffle_record(args, rank, world, barrier):
             rec[f"{label}_gbs"] = round(float(remote.item()) / (ms * 1e-3) / 1e9, 1)
         rec["frac_of_measured_peer_copy"] = round(rec["p2p_gbs"] / peer_gbs, 4)
         rec["frac_of_900_nominal"] = round(rec["p2p_gbs"] / 900.0, 4)
+        rec["frac_of_770_pool_reference"] = round(rec["p2p_gbs"] / POOL_PEER_COPY_GBS, 4)
+        if direct is not None and name == "c4_stress_2KiB_f16":
+            # the opt-in path of large shuffles: the askers send the final slot of every row first, the owners
+            # store the rows there, no pull pass; the result is a view of a landing buffer of the inbox
+            st.exchange = direct
+            try:
+                ms = timed(lambda: ops.feat_shuffle(x, send_off, recv_off, perm, dim, 1))
+                ops.check_status()
+                gbs = float(remote.item()) / (ms * 1e-3) / 1e9
+                rec["direct_placement"] = {"ms": round(ms, 4), "gbs": round(gbs, 1),
+                                           "frac_of_measured_peer_copy": round(gbs / peer_gbs, 4),
+                                           "frac_of_900_nominal": round(gbs / 900.0, 4),
+                                           "frac_of_770_pool_reference": round(gbs / POOL_PEER_COPY_GBS, 4)}
+            except RuntimeError as exc:       # an extra leg: its failure is reported, the line stands
+                rec["direct_placement"] = {"error": str(exc)[:200]}
         out[name] = rec
         del x, ids, recv_ids
     st.exchange = keep
+    if direct is not None:
+        barrier()
+        direct.close()
     ops.check_status()
     if p2p is not keep:
         barrier()
@@ -820,8 +857,12 @@ def shuffle_record(args, rank, world, barrier):
     return {"gbs": head["p2p_gbs"], "nccl_gbs": head["nccl_gbs"],
             "frac_of_measured_peer_copy": head["frac_of_measured_peer_copy"],
             "frac_of_900_nominal": head["frac_of_900_nominal"],
+            "frac_of_770_pool_reference": head["frac_of_770_pool_reference"],
+            "direct_placement": head.get("direct_placement"),
             "peer_copy_gbs": round(peer_gbs, 1),
-            "peer_copy": f"{copy_bytes >> 20} MiB cudaMemcpyAsync into the right neighbour's inbox, all ranks at once",
+            "peer_copy": f"{copy_bytes >> 20} MiB cudaMemcpyAsync into the right neighbour's inbox, all ranks at once "
+                         f"(a copy-engine copy; the pool's reference figure for a peer copy is {POOL_PEER_COPY_GBS:.0f} "
+                         "GB/s per direction)",
             "unit": "GB/s per GPU and direction, remote rows only", "direction": "forward (rows back to the askers)",
             "path": "direct placement" if getattr(p2p, "direct", False) else "push + wait + pull", "shapes": out}
 
