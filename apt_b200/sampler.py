@@ -114,6 +114,7 @@ class _GraphReplay:
         if lanes is None:
             lanes = int(os.environ.get("APT_SAMPLER_LANES", "4"))
         self.lanes = max(1, min(int(lanes), 8))
+        self.plans_per_lane = max(1, min(int(os.environ.get("APT_SAMPLER_PLANS_PER_LANE", "2")), 4))
         self.graph_buffers = max(1, int(graph_buffers))
         self._plans = {}
         self._turn = 0
@@ -127,8 +128,12 @@ class _GraphReplay:
         return self.use_graph and not st.profiling and ops._exchange().name in ("local", "p2p")
 
     def _in_flight(self):
-        """Buffer sets sample_iter takes turns with."""
-        return max(self.graph_buffers, self.lanes) if self.lanes > 1 else self.graph_buffers
+        """Buffer sets sample_iter takes turns with. With lanes every lane has `plans_per_lane` of them:
+        a lane's next replay is then already queued on its stream when the running one ends, and the
+        lane does not idle while the host reads the finished mini-batch back and hands it out."""
+        if self.lanes > 1:
+            return max(self.graph_buffers, self.lanes * self.plans_per_lane)
+        return self.graph_buffers
 
     def _plan_for(self, seeds, piped=False):
         """The plan the next mini-batch of this shape runs on. sample() takes `graph_buffers` plans in

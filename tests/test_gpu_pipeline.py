@@ -164,7 +164,7 @@ def test_pipelined_iterator_equals_one_sample_per_batch(lanes, thread):
         want.append(snapshot(res, ops.load_subtensor(res[0])))
     ops.set_sampling(key=5150, call_id=2)
     piped = apt_b200.MixedNeighborSampler(0, [7, 3], chained=True, use_graph=True, lanes=lanes)
-    assert piped.lanes == lanes and piped._in_flight() == max(2, lanes)
+    assert piped.lanes == lanes and piped._in_flight() == (2 if lanes == 1 else lanes * piped.plans_per_lane)
     piped.launch_thread = thread          # launches from a thread of their own
     got = []
     for res in piped.sample_iter(None, iter(batches)):

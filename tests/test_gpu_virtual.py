@@ -198,6 +198,53 @@ def test_chained_sampler_equals_operator_by_operator_form(with_dst):
     reset_world()
 
 
+@pytest.mark.parametrize("kind", ["snp", "snp_dst", "nfp", "snp_gat"])
+def test_pipelined_iterator_of_the_other_samplers(kind):
+    # sample_iter with three mini-batches in flight on lanes of their own hands out what sample() returns,
+    # for every sampler on the shared replay base
+    from apt_b200.sampler import MPSampler, SPGATSampler
+
+    n, indptr, indices = small_graph(scale=12, edge_factor=8)
+    reset_world()
+    install_graph(indptr, indices)
+    _world(1, 0, n)
+    rng = np.random.default_rng(77)
+    batches = [dev(rng.permutation(n)[:96].astype(I64)) for _ in range(7)]
+
+    def make(lanes):
+        if kind == "nfp":
+            return MPSampler(0, [5, 3], lanes=lanes)
+        if kind == "snp_gat":
+            return SPGATSampler(0, [5, 3], prefetch_features=False, lanes=lanes)
+        return SPVirtualSampler(0, [5, 3], model="SAGE", shuffle_with_dst=(kind == "snp_dst"), lanes=lanes)
+
+    def flat(out):
+        res = [out[0].clone(), out[1].clone()]
+        for b in out[2]:
+            if isinstance(b, tuple):
+                res += [t.clone() for t in b]
+            else:
+                res += [b.coo_row.clone(), b.coo_col.clone(), b.src_ids.clone(),
+                        torch.tensor([b.num_src, b.num_dst])]
+        return res + [t.clone() for t in out[3:]]
+
+    ops.set_sampling(key=12, call_id=3)
+    one = make(1)
+    want = [flat(one.sample(None, b)) for b in batches]
+    ops.set_sampling(key=12, call_id=3)
+    piped = make(3)
+    assert piped.lanes == 3
+    got = [flat(out) for out in piped.sample_iter(None, batches)]
+    assert len(got) == len(want)
+    for g_, w_ in zip(got, want):
+        assert len(g_) == len(w_)
+        for a, b in zip(g_, w_):
+            assert torch.equal(a.cpu(), b.cpu())
+    assert ops.STATE.lane == 0
+    ops.check_status()
+    reset_world()
+
+
 def test_committed_strategy_fixture_one_rank():
     # tests/golden/strategies_small.npz, one-rank cases: SNP with virtual nodes (both variants) and NFP
     import os
