@@ -5,7 +5,15 @@ sm_100a CUDA behind the reference's ``torch.ops.npc`` operator interface.
 Importing the package loads libapt_b200.so (raising if it is not built) and
 registers the ``npc`` operators.
 """
-from . import _lib  # noqa: F401  (raises when the CUDA library is missing)
+import os as _os
+
+# The samplers' pipelined iterator runs mini-batches on streams of their own. With CUDA's default of 8
+# hardware queues the caller's stream shares a queue with one of them, and the caller's kernels and
+# copies then wait behind that lane's queued mini-batches. The setting is read when CUDA starts, so
+# it only takes effect when this package is imported before the first CUDA call of the process.
+_os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+
+from . import _lib  # noqa: E402,F401  (raises when the CUDA library is missing)
 from . import npc_ops  # noqa: F401  (registers torch.ops.npc.*)
 from . import ops
 from .ops import (  # noqa: F401

@@ -96,7 +96,7 @@ class _GraphReplay:
     `graph_buffers` buffer sets in turn. `sample_iter` launches mini-batch k + 1 before it reads
     mini-batch k back. Subclasses set `num_calls` (sampling calls per mini-batch).
 
-    With `lanes` > 1 (APT_SAMPLER_LANES, default 4) the buffer sets of `sample_iter` also get
+    With `lanes` > 1 (APT_SAMPLER_LANES, default 8) the buffer sets of `sample_iter` also get
     scratch of their own (workspaces, word block, exchange context: a "lane" of the operator state)
     and a stream of their own, so that the mini-batches it keeps in flight run beside one another
     on the GPU instead of one behind the other: most kernels of a mini-batch wait on dependent
@@ -112,7 +112,7 @@ class _GraphReplay:
             use_graph = os.environ.get("APT_SAMPLER_GRAPH", "1") != "0"
         self.use_graph = bool(use_graph)
         if lanes is None:
-            lanes = int(os.environ.get("APT_SAMPLER_LANES", "4"))
+            lanes = int(os.environ.get("APT_SAMPLER_LANES", "8"))
         self.lanes = max(1, min(int(lanes), 8))
         self.plans_per_lane = max(1, min(int(os.environ.get("APT_SAMPLER_PLANS_PER_LANE", "2")), 4))
         self.graph_buffers = max(1, int(graph_buffers))
@@ -340,7 +340,7 @@ class MixedNeighborSampler(_GraphReplay):
                        `graph_buffers` further batches have been sampled.
     lanes              buffer sets with scratch and a stream of their own, so that the
                        mini-batches sample_iter keeps in flight overlap on the GPU
-                       (default: APT_SAMPLER_LANES, else 4)
+                       (default: APT_SAMPLER_LANES, else 8)
     """
 
     def __init__(self, rank: int, fanouts: List[int], chained: bool = None, prefetch_features: bool = True,

@@ -26,8 +26,13 @@ import sys
 import tempfile
 import time
 
-import torch
-import torch.distributed as dist
+# Before CUDA starts: one hardware queue per stream. With the default of 8 the caller's stream shares a
+# queue with one of the sampler's lane streams, and whatever the caller enqueues (here: the read-back of
+# a step's result) waits behind that lane's queued mini-batches.
+os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -942,6 +947,11 @@ def run_snp_gat(args, inst, w, rank, world, config, run_info, barrier, reduce_ma
                            "of the block's unique sources")
     ops.check_status()
 
+    # set-up, like the installation of the graph: every buffer set of the sampler's iterator is built (one
+    # eager run and one graph capture each) before the warm-up steps, whatever their number
+    phase("prime")
+    barrier()
+    run_steps([dev_batches[0]] * sampler._in_flight())
     phase("warmup")
     clocks = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
     clocks.start()
@@ -1150,6 +1160,11 @@ def run():
     clocks.start()          # sampled from the warm-up on: the timed region alone can be shorter than one sample period
     # every phase that exchanges between the ranks starts behind a barrier: host-side work of different
     # length (registering the host table, stopping the clock sampler) must not eat into the wait bound
+    # set-up, like the installation of the graph: every buffer set of the sampler's iterator is built (one
+    # eager run and one graph capture each) before the warm-up steps, whatever their number
+    phase("prime")
+    barrier()
+    run_steps([dev_batches[0]] * sampler._in_flight())
     phase("warmup")
     barrier()
     run_steps(dev_batches[:args.warmup])
