@@ -35,6 +35,7 @@
 namespace apt {
 
 constexpr int kRowsPerGroup = 4;   // rows whose loads are in flight together
+constexpr int kMinMissBlocks = 16; // blocks of the miss copy that always take part
 constexpr int kGatherBlock = 256;
 
 struct GatherWs {
@@ -353,11 +354,23 @@ k_copy_hits_bulk(int64_t n, const int64_t* __restrict__ n_dev, const int64_t* __
 template <typename V>
 __global__ void __launch_bounds__(kGatherBlock)
 k_copy_miss(GatherWs ws, const char* __restrict__ uva_feats, int64_t uva_row_bytes,
-            int64_t col_offset_bytes, int64_t row_bytes, char* __restrict__ out) {
+            int64_t col_offset_bytes, int64_t row_bytes, int64_t bytes_per_block,
+            char* __restrict__ out) {
   const int lane = threadIdx.x & 31;
-  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
-  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int64_t n = *ws.miss_count;
+  // With bytes_per_block set, only as many blocks take part as the bytes to fetch ask for (at least
+  // kMinMissBlocks, at most the grid); the others leave at once. A copy from host memory holds its
+  // SM slots for a long time without using the SMs; when several mini-batches are in flight the slots
+  // it does not need are worth more to their kernels than to the copy.
+  int64_t blocks = gridDim.x;
+  if (bytes_per_block > 0) {
+    const int64_t want = (n * row_bytes + bytes_per_block - 1) / bytes_per_block;
+    blocks = want < kMinMissBlocks ? kMinMissBlocks : want;
+    if (blocks > (int64_t)gridDim.x) blocks = gridDim.x;
+    if ((int64_t)blockIdx.x >= blocks) return;
+  }
+  const int64_t warps = blocks * (blockDim.x >> 5);
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int chunks = (int)(row_bytes / (int64_t)sizeof(V));
   for (int64_t m0 = warp * kRowsPerGroup; m0 < n; m0 += warps * kRowsPerGroup) {
     int64_t r[kRowsPerGroup], p[kRowsPerGroup];
@@ -384,6 +397,7 @@ k_copy_miss(GatherWs ws, const char* __restrict__ uva_feats, int64_t uva_row_byt
 // ---- tunables (set through apt_set_tunable; defaults are the measured best) ----
 static int g_miss_mode = 0;      // 0: 16-byte ld.global.nc, 1: bulk copy staged through shared memory
 static int g_miss_blocks = kNumSMs;
+static int g_miss_kb_per_block = 0;  // > 0: blocks of the miss copy beyond one per this many KiB to fetch leave at once
 static int g_hit_mode = 0;       // 0: one wave, two groups in flight per warp; 1: bulk copies through shared memory;
                                  // 2: grid-stride blocks, one group per warp at a time
 static int g_hit_waves = 4;      // mode 2: cap on the grid, in units of 148 x 8 blocks
@@ -535,7 +549,8 @@ static int gather_launch(const GatherArgs& a, GatherWs ws, cudaStream_t s) {
   do {                                                                                     \
     ProfScope prof("gather_miss", s);                                                      \
     APT_LAUNCH(k_copy_miss<V>, g_miss_blocks, kGatherBlock, 0, s, ws, a.uva_feats,         \
-               a.uva_row_bytes, a.uva_col_offset_bytes, a.dev_row_bytes, a.out);           \
+               a.uva_row_bytes, a.uva_col_offset_bytes, a.dev_row_bytes,                   \
+               (int64_t)g_miss_kb_per_block << 10, a.out);                                 \
   } while (0)
 #define APT_BY_WIDTH(W, MACRO)                                                             \
   do {                                                                                     \
@@ -612,6 +627,8 @@ extern "C" int apt_set_tunable(const char* name, int64_t value) {
     g_miss_mode = (int)value;
   } else if (!strcmp(name, "gather_miss_blocks") && value >= 1 && value <= 65535) {
     g_miss_blocks = (int)value;
+  } else if (!strcmp(name, "gather_miss_kb_per_block") && value >= 0 && value <= (1 << 20)) {
+    g_miss_kb_per_block = (int)value;
   } else if (!strcmp(name, "gather_hit_mode") && value >= 0 && value <= 2) {
     g_hit_mode = (int)value;
   } else if (!strcmp(name, "gather_hit_waves") && value >= 1 && value <= 64) {

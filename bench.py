@@ -1351,8 +1351,9 @@ def run():
         "dtype": "int64 ids, " + w.dtype + " rows", "data": "synthetic", "config": config, "run_info": run_info,
         "clocks": clock_info,
         "e2e": e2e, "gpu_launches": int(reduce_sum(launches)),
-        "launch_mode": (f"one CUDA graph replay per mini-batch, {sampler._in_flight()} mini-batches in flight on "
-                        f"{sampler.lanes} streams with scratch of their own" if sampler.lanes > 1 else
+        "launch_mode": (f"one CUDA graph replay per mini-batch, {sampler.buffer_sets()} mini-batches in flight on "
+                        f"{min(sampler.lanes, sampler.buffer_sets())} streams with scratch of their own"
+                        if sampler.lanes > 1 else
                         "one CUDA graph replay per mini-batch, the next one enqueued before the previous one is "
                         "read back") if graph_mode else
                        "kernels enqueued one by one, sizes chained on the device",

@@ -83,6 +83,10 @@ int apt_profile_read(const char* tag, double* total_ms, int64_t* launches);
  *   gather_miss_mode   0 16-byte ld.global.nc loads (default),
  *                      1 bulk copies (cp.async.bulk) staged through shared memory
  *   gather_miss_blocks blocks of the miss-copy kernel (default 148)
+ *   gather_miss_kb_per_block  0 (default): every block of the miss copy takes part; k > 0: one block per
+ *                      k KiB to fetch (at least 16), the rest leave at once and keep their SM slots free.
+ *                      The samplers set 128 for the launches they capture on a lane, where other
+ *                      mini-batches' kernels run beside the copy.
  *   gather_hit_mode    copy of the cache hits: 0 one resident wave, two groups of rows in flight per warp,
  *                      1 bulk copies (cp.async.bulk) staged through shared memory,
  *                      2 grid-stride blocks, one group of rows per warp at a time

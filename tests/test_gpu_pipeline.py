@@ -230,3 +230,56 @@ def test_row_movers(row_elems, dtype):
     ref = torch.zeros_like(x)
     ref[p[:100]] = x[:100]
     assert torch.equal(z, ref)
+
+
+def test_memory_budget_cuts_the_number_of_buffer_sets():
+    """Buffer sets are sized for upper bounds; a budget (APT_SAMPLER_PLAN_GB) keeps a shape's ring from
+    taking more device memory, down to two sets, and the mini-batches stay what they were."""
+    n, indptr, indices = small_graph(scale=12, edge_factor=8)
+    install_graph(indptr, indices)
+    reset_world(1, 0)
+    ops.register_min_vids(torch.tensor([0, n]))
+    rng = np.random.default_rng(8)
+    batches = [dev(rng.permutation(n)[:120].astype(I64)) for _ in range(7)]
+    runs = []
+    for budget in (None, 1):
+        ops.set_sampling(key=31, call_id=0)
+        smp = apt_b200.MixedNeighborSampler(0, [6, 4], prefetch_features=False, lanes=3)
+        if budget is not None:
+            smp.plan_budget_bytes = budget
+        runs.append([(host(r[0]), host(r[2][0].coo_row), host(r[3])) for r in smp.sample_iter(None, batches)])
+        assert smp.buffer_sets() == (2 if budget else 3 * smp.plans_per_lane)
+    for a, b in zip(*runs):
+        for x, y in zip(a, b):
+            assert np.array_equal(x, y)
+    ops.check_status()
+
+
+def test_memcpy_async_both_directions_and_inside_a_captured_graph():
+    """apt_memcpy_async between page-locked host memory and the device; as a node of a captured graph it
+    reads its host source when the replay runs (what the samplers' plans rely on for the call-id base)."""
+    import ctypes
+
+    from apt_b200._lib import check, lib
+
+    host_in = torch.arange(16, dtype=torch.int64).pin_memory()
+    host_out = torch.zeros(16, dtype=torch.int64).pin_memory()
+    dev_buf = torch.zeros(16, dtype=torch.int64, device="cuda")
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+    stream = lambda: ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    check(lib.apt_memcpy_async(ptr(dev_buf), ptr(host_in), 128, stream()))
+    check(lib.apt_memcpy_async(ptr(host_out), ptr(dev_buf), 128, stream()))
+    torch.cuda.synchronize()
+    assert torch.equal(host_out, host_in)
+    assert lib.apt_memcpy_async(None, ptr(host_in), 8, stream()) != 0          # null pointer: refused
+    assert lib.apt_memcpy_async(None, None, 0, stream()) == 0                  # nothing to copy
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        check(lib.apt_memcpy_async(ptr(dev_buf), ptr(host_in), 128, stream()))
+        dev_buf.add_(1)
+        check(lib.apt_memcpy_async(ptr(host_out), ptr(dev_buf), 128, stream()))
+    for base in (100, 200):
+        host_in.fill_(base)                                                     # changed between replays
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(host_out, torch.full((16,), base + 1, dtype=torch.int64))
