@@ -136,12 +136,12 @@ class _GraphReplay:
         self.use_graph = bool(use_graph)
         if lanes is None:
             lanes = int(os.environ.get("APT_SAMPLER_LANES", "8"))
-        self.lanes = max(1, min(int(lanes), 8))
+        self.lanes = max(1, min(int(lanes), 16))
         self.plans_per_lane = max(1, min(int(os.environ.get("APT_SAMPLER_PLANS_PER_LANE", "2")), 4))
         self.graph_buffers = max(1, int(graph_buffers))
         self._plans = {}
         # device memory the buffer sets of one batch shape may take together (APT_SAMPLER_PLAN_GB)
-        self.plan_budget_bytes = int(float(os.environ.get("APT_SAMPLER_PLAN_GB", "24")) * (1 << 30))
+        self.plan_budget_bytes = int(float(os.environ.get("APT_SAMPLER_PLAN_GB", "40")) * (1 << 30))
         # KiB to fetch per block of the copy from host memory inside a lane's graph (0: all blocks)
         self.miss_kb_per_block = int(os.environ.get("APT_SAMPLER_MISS_KB_PER_BLOCK", "128"))
         # launches of sample_iter on a thread of their own (APT_SAMPLER_THREAD)
